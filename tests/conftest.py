@@ -1,0 +1,28 @@
+import os
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run on a B200)")
+
+
+@pytest.fixture(scope="session")
+def cpu_oracle():
+    import oracle
+
+    return oracle.CpuOracle()
+
+
+@pytest.fixture(scope="session")
+def metal_ref():
+    import oracle
+
+    if not oracle.MetalRef.available():
+        pytest.skip("reference shader build (oracle/_ref) not present")
+    return oracle.MetalRef()
