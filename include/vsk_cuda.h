@@ -1,0 +1,228 @@
+/*
+ * vsk_cuda.h — C ABI of the B200 (sm_100a) similarity-search library.
+ *
+ * This is the boundary a VectorStoreKit host binds instead of its Metal
+ * acceleration layer.  Every entry point names the reference interface it
+ * replaces (paths are relative to the VectorStoreKit source tree).
+ *
+ * Conventions
+ *   - All functions return a vsk_status (int32_t); VSK_OK == 0.  No C++ types
+ *     and no exceptions cross the boundary.  vsk_last_error() gives the text
+ *     of the most recent failure on a context.
+ *   - Matrices are dense row-major fp32 (`rows[n*dim + i]`), the layout the
+ *     reference flattens into before every dispatch
+ *     (Acceleration/MetalAccelerationEngine.swift:393-405).
+ *   - Host-pointer calls copy in/out during the call and never keep a host
+ *     pointer.  `_dev` calls take pointers to memory of the context's GPU and
+ *     run on the context's stream; they return after the stream has drained.
+ *   - Row ids are dense int64 insertion indices (the host keeps the
+ *     index -> VectorID(String) table, as Indexes/IVFIndex.swift:104-111 does).
+ *     Missing results (fewer than k eligible rows) have id -1, distance +inf.
+ *   - Results per query are ascending by distance, ties by id.
+ *   - A context is used by one thread at a time (the reference serialises
+ *     through an actor); distinct contexts are independent.
+ *   - There is no CPU path: without a CUDA device vsk_open fails with
+ *     VSK_ERR_DEVICE_NOT_AVAILABLE.
+ */
+#ifndef VSK_CUDA_H_
+#define VSK_CUDA_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Status codes.  Mirrors MetalComputeError (Acceleration/Metal/MetalErrors.swift:10-39)
+ * and IVFError (Indexes/IVFIndex.swift:619-637). */
+typedef enum vsk_status {
+  VSK_OK = 0,
+  VSK_ERR_DEVICE_NOT_AVAILABLE = 1,      /* deviceNotAvailable */
+  VSK_ERR_OUT_OF_MEMORY = 2,             /* deviceOutOfMemory(required, available) */
+  VSK_ERR_UNSUPPORTED_OPERATION = 3,     /* unsupportedOperation: metric outside the four */
+  VSK_ERR_INVALID_BUFFER_SIZE = 4,       /* invalidBufferSize */
+  VSK_ERR_EXECUTION_FAILED = 5,          /* commandBufferExecutionFailed */
+  VSK_ERR_TIMEOUT = 6,                   /* commandBufferTimeout: a bounded device wait ran out */
+  VSK_ERR_INVALID_INPUT = 7,             /* invalidInput */
+  VSK_ERR_DIMENSION_MISMATCH = 8,        /* dimensionMismatch */
+  VSK_ERR_EMPTY_INPUT = 9,               /* emptyInput (MetalDistanceCompute.swift:51-53) */
+  VSK_ERR_NOT_TRAINED = 10,              /* IVFError.notTrained */
+  VSK_ERR_INSUFFICIENT_TRAINING_DATA = 11/* IVFError.insufficientTrainingData */
+} vsk_status;
+
+/* The four cases of DistanceMetric the accelerated path supports
+ * (Core/SearchTypes.swift:105-118; MetalDistanceCompute.swift:342-344 rejects the rest).
+ *   euclidean   sqrt(sum (q-x)^2)            cosine      1 - q.x/(|q||x| + 1e-8)
+ *   dotProduct  -(q.x)                        manhattan   sum |q-x|
+ * (Acceleration/AccelerateOptimizer.swift:251-383, Shaders/DistanceShaders.metal:62-218) */
+typedef enum vsk_metric {
+  VSK_METRIC_EUCLIDEAN = 0,
+  VSK_METRIC_COSINE = 1,
+  VSK_METRIC_DOT_PRODUCT = 2,
+  VSK_METRIC_MANHATTAN = 3
+} vsk_metric;
+
+typedef enum vsk_sq8_mode {
+  VSK_SQ8_GLOBAL = 0,  /* one min/max over all values: ScalarQuantizer.swift:389-418 */
+  VSK_SQ8_PER_DIM = 1  /* the same formulas column by column */
+} vsk_sq8_mode;
+
+/* Which kernels a flat fp32 search runs. */
+typedef enum vsk_search_path {
+  VSK_PATH_TENSOR_RERANK = 0, /* fp16 tcgen05 contraction + bounded-error filter + exact fp32 rerank;
+                                 queries whose result cannot be certified exact are re-run on the
+                                 fp32 scan.  Manhattan always uses the fp32 scan. */
+  VSK_PATH_FP32_SCAN = 1      /* direct fp32 formulas on CUDA cores for every pair */
+} vsk_search_path;
+
+typedef struct vsk_ctx vsk_ctx;
+typedef struct vsk_index vsk_index;
+
+/* Capabilities of the opened device.  Stands in for the CapabilitiesType of the reference's
+ * ComputeAccelerator strategies (API/Strategies/AcceleratorStrategies.swift:437-455). */
+typedef struct vsk_device_info {
+  int32_t device;
+  int32_t sm_count;
+  int32_t cc_major, cc_minor;
+  int64_t hbm_bytes;
+  int64_t l2_bytes;
+  int32_t max_smem_per_block;
+  char name[128];
+} vsk_device_info;
+
+/* Counters since vsk_open.  Stands in for MetalAccelerationEngine.getPerformanceStatistics()
+ * (Acceleration/MetalAccelerationEngine.swift:987-998). */
+typedef struct vsk_stats {
+  int64_t searches;            /* search calls */
+  int64_t queries;             /* queries answered */
+  int64_t kernel_launches;     /* kernels of this library launched */
+  int64_t tensor_tiles;        /* tcgen05 output tiles computed */
+  int64_t reranked_rows;       /* rows re-scored by the exact rerank */
+  int64_t fallback_queries;    /* queries re-run on the fp32 scan after a failed certificate */
+  int64_t h2d_bytes, d2h_bytes;
+  int64_t scan_kernel_launches; /* with vsk_profile on: launches of the dominant scan kernels ... */
+  double scan_kernel_ms;        /* ... and their summed device time (CUDA events on the stream) */
+} vsk_stats;
+
+/* --- context ------------------------------------------------------------------------------
+ * Replaces ComputeAccelerator.initialize()/capabilities() (Core/Protocols.swift:11-20) and the
+ * process-wide MetalAccelerationEngine.shared (MetalAccelerationEngine.swift:25-30). */
+int32_t vsk_open(int32_t device, vsk_ctx** out_ctx);
+int32_t vsk_close(vsk_ctx* ctx);
+int32_t vsk_device_info_get(vsk_ctx* ctx, vsk_device_info* out);
+int32_t vsk_stats_get(vsk_ctx* ctx, vsk_stats* out);
+const char* vsk_last_error(vsk_ctx* ctx);
+const char* vsk_status_string(int32_t status);
+/* vsk_search_path; default VSK_PATH_TENSOR_RERANK. */
+int32_t vsk_set_search_path(vsk_ctx* ctx, int32_t path);
+/* Time the scan kernels (tcgen05 contraction, fp32 tile scan, IVF list scan) with CUDA events on the
+ * context's stream; totals appear in vsk_stats.  Stands in for MetalProfiler's per-operation timing
+ * (Acceleration/Metal/MetalProfiler.swift:74-110). */
+int32_t vsk_profile(vsk_ctx* ctx, int32_t enable);
+/* The CUDA stream (cudaStream_t) every call on this context is enqueued on. */
+void* vsk_stream(vsk_ctx* ctx);
+
+/* --- stateless distances -------------------------------------------------------------------
+ * Full nq x nx matrix, out[q*nx + c].  Replaces MetalAccelerationEngine.batchComputeDistances
+ * with topK == nil (MetalAccelerationEngine.swift:139-204,377-478), MetalDistanceCompute
+ * .batchComputeDistances (Metal/MetalDistanceCompute.swift:260-318) and, with nq == 1,
+ * computeDistances (MetalAccelerationEngine.swift:76-136). */
+int32_t vsk_batch_distances(vsk_ctx* ctx, int32_t metric, const float* queries, int64_t nq,
+                            const float* rows, int64_t nx, int32_t dim, float* out);
+int32_t vsk_batch_distances_dev(vsk_ctx* ctx, int32_t metric, const float* queries, int64_t nq,
+                                const float* rows, int64_t nx, int32_t dim, float* out);
+
+/* --- flat exact k-NN -----------------------------------------------------------------------
+ * A resident database searched by many query batches.  Replaces
+ * MetalAccelerationEngine.batchComputeDistances(queries:candidates:metric:topK:)
+ * (MetalAccelerationEngine.swift:139-204), which re-uploads the candidates on every call and
+ * sorts on the CPU (:465-471), and the flat scan of InMemoryVectorStore.search
+ * (LLM/LLMVectorStore.swift:83-114).  `masks` (may be NULL) gives each row a 64-bit metadata
+ * bitmask; a search with query masks keeps row r for query q iff (masks[r] & qmasks[q]) != 0,
+ * applied before distances as the reference's filters are (Indexes/IVFIndex.swift:163-172). */
+int32_t vsk_flat_create(vsk_ctx* ctx, int32_t metric, int32_t dim, vsk_index** out_index);
+int32_t vsk_flat_add_f32(vsk_index* index, const float* rows, int64_t n, const uint64_t* masks);
+int32_t vsk_flat_add_f32_dev(vsk_index* index, const float* rows, int64_t n, const uint64_t* masks);
+int32_t vsk_index_destroy(vsk_index* index);
+int64_t vsk_index_size(vsk_index* index);
+/* Added to every returned id (row-sharded databases: the shard's first global row). */
+int32_t vsk_index_set_id_base(vsk_index* index, int64_t id_base);
+
+/* out_dist[nq*k], out_ids[nq*k].  qmasks may be NULL. */
+int32_t vsk_search(vsk_index* index, const float* queries, int64_t nq, int32_t k,
+                   const uint64_t* qmasks, float* out_dist, int64_t* out_ids);
+int32_t vsk_search_dev(vsk_index* index, const float* queries, int64_t nq, int32_t k,
+                       const uint64_t* qmasks, float* out_dist, int64_t* out_ids);
+
+/* Merge of per-shard results: `g` lists of k (distance, global id) per query, laid out
+ * [g][nq][k], into the k best per query by (distance, id) — what one unsharded search returns.
+ * Device pointers.  The reference has no sharded search; this is the step after the NCCL gather. */
+int32_t vsk_merge_topk_dev(vsk_ctx* ctx, const float* dist, const int64_t* ids, int32_t g,
+                           int64_t nq, int32_t k, float* out_dist, int64_t* out_ids);
+
+/* --- k-means / IVF -------------------------------------------------------------------------
+ * Lloyd iterations from caller-supplied initial centroids.  Replaces KMeansClustering.cluster
+ * (Clustering/KMeansClustering.swift:48-113; `.custom` initialisation :189-193) and the shader
+ * kernels assign_to_centroids / accumulate_centroids / finalize_centroids
+ * (Shaders/ClusteringShaders.metal:29-177).  Assignment: rooted L2, lowest index wins ties.
+ * Empty cluster keeps its previous centroid (ClusteringShaders.metal:171-176).  inertia = sum of
+ * un-squared distances (KMeansClustering.swift:97).  tolerance < 0: run exactly max_iters. */
+int32_t vsk_kmeans(vsk_ctx* ctx, const float* rows, int64_t n, int32_t dim, int32_t k,
+                   int32_t max_iters, float tolerance, const float* init_centroids,
+                   float* centroids, int32_t* assign, float* inertia, int32_t* iters_run);
+int32_t vsk_kmeans_dev(vsk_ctx* ctx, const float* rows, int64_t n, int32_t dim, int32_t k,
+                       int32_t max_iters, float tolerance, const float* init_centroids,
+                       float* centroids, int32_t* assign, float* inertia, int32_t* iters_run);
+/* Nearest centroid of every row (IVFIndex.findNearestCentroid, Indexes/IVFIndex.swift:514-527). */
+int32_t vsk_assign_dev(vsk_ctx* ctx, const float* rows, int64_t n, int32_t dim,
+                       const float* centroids, int32_t k, int32_t* assign, float* dist);
+
+/* IVF index over trained centroids: rows are assigned to their nearest centroid and stored
+ * list by list.  Replaces IVFIndex.train/insert (Indexes/IVFIndex.swift:397-446,80-122). */
+int32_t vsk_ivf_build(vsk_ctx* ctx, const float* centroids, int32_t nlist, const float* rows,
+                      int64_t n, int32_t dim, vsk_index** out_index);
+int32_t vsk_ivf_build_dev(vsk_ctx* ctx, const float* centroids, int32_t nlist, const float* rows,
+                          int64_t n, int32_t dim, vsk_index** out_index);
+/* Row -> list of the built index (host buffer of n int32). */
+int32_t vsk_ivf_assignments(vsk_index* index, int32_t* assign);
+/* Probe the nprobe nearest lists, rooted L2, ascending top-k.  Replaces IVFIndex.search
+ * (Indexes/IVFIndex.swift:124-202); nprobe == nlist is its `.exact` strategy (:551-560). */
+int32_t vsk_ivf_search(vsk_index* index, const float* queries, int64_t nq, int32_t k,
+                       int32_t nprobe, float* out_dist, int64_t* out_ids);
+int32_t vsk_ivf_search_dev(vsk_index* index, const float* queries, int64_t nq, int32_t k,
+                           int32_t nprobe, float* out_dist, int64_t* out_ids);
+
+/* --- int8 scalar quantiser -----------------------------------------------------------------
+ * Replaces ScalarQuantizer.quantizeBatch for `.int8` (Quantization/ScalarQuantizer.swift:129-164):
+ *   train   min/max -> scale = 255/(max-min), offset = -min*scale - 128     (:389-451)
+ *   encode  code = truncate_toward_zero(x*scale + offset)                   (:251-270)
+ *   decode  x^ = (code - offset)/scale                                      (:568-580)
+ * scale/offset are arrays of `dim` floats (equal entries in VSK_SQ8_GLOBAL mode).
+ * vsk_sq8_index_create accepts host or device scale/offset arrays. */
+/* Per-dimension minimum and maximum of device rows into device arrays minv[dim], maxv[dim]; with a
+ * row-sharded database the host reduces these across shards (min / max) before vsk_sq8_params_dev. */
+int32_t vsk_sq8_minmax_dev(vsk_ctx* ctx, const float* rows, int64_t n, int32_t dim, float* minv,
+                           float* maxv);
+int32_t vsk_sq8_params_dev(vsk_ctx* ctx, const float* minv, const float* maxv, int32_t dim,
+                           int32_t mode, float* scale, float* offset);
+int32_t vsk_sq8_train(vsk_ctx* ctx, const float* rows, int64_t n, int32_t dim, int32_t mode,
+                      float* scale, float* offset);
+int32_t vsk_sq8_encode(vsk_ctx* ctx, const float* rows, int64_t n, int32_t dim,
+                       const float* scale, const float* offset, int8_t* codes);
+int32_t vsk_sq8_encode_dev(vsk_ctx* ctx, const float* rows, int64_t n, int32_t dim,
+                           const float* scale, const float* offset, int8_t* codes);
+int32_t vsk_sq8_decode(vsk_ctx* ctx, const int8_t* codes, int64_t n, int32_t dim,
+                       const float* scale, const float* offset, float* rows);
+/* Flat index over int8 codes; search distances are the metric between the fp32 query and the
+ * dequantised row.  The reference stores codes but has no scan over them
+ * (ScalarQuantizer.swift:453-464 asks for a kernel that does not exist). */
+int32_t vsk_sq8_index_create(vsk_ctx* ctx, int32_t metric, int32_t dim, const float* scale,
+                             const float* offset, vsk_index** out_index);
+int32_t vsk_sq8_index_add(vsk_index* index, const int8_t* codes, int64_t n);
+int32_t vsk_sq8_index_add_dev(vsk_index* index, const int8_t* codes, int64_t n);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VSK_CUDA_H_ */

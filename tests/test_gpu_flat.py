@@ -1,0 +1,267 @@
+"""GPU parity of distances and flat exact k-NN against the CPU oracle, through the C ABI."""
+import math
+import os
+
+import numpy as np
+import pytest
+
+import oracle
+from parity import assert_topk_parity
+
+pytestmark = pytest.mark.gpu
+GOLD = np.load(os.path.join(os.path.dirname(__file__), "golden", "metal_shader_vectors.npz"))
+NAMES = ["euclidean", "cosine", "dotProduct", "manhattan"]
+
+
+@pytest.fixture(scope="module")
+def vsk():
+    import vectorstorekit_b200 as v
+    return v
+
+
+@pytest.fixture(scope="module")
+def dev(vsk):
+    return vsk.CUDAAcceleratorStrategy(0).initialize()
+
+
+@pytest.fixture(scope="module")
+def engine(vsk, dev):
+    return vsk.CUDAAccelerationEngine(dev)
+
+
+def test_device_is_b200(dev):
+    info = dev.info()
+    assert info["compute_capability"][0] == 10 and info["sm_count"] > 0
+
+
+# known answers of the reference's tests, through the library
+def test_kat(engine):
+    e = engine
+    f = lambda *a: np.array(a, np.float32)
+    assert abs(e.computeDistances(f(1, 0, 0, 0), f(0, 1, 0, 0)[None], "euclidean")[0] - math.sqrt(2)) < 1e-4
+    assert abs(e.computeDistances(f(1, 0, 0, 0), f(0, 1, 0, 0)[None], "cosine")[0] - 1.0) < 1e-4
+    assert abs(e.computeDistances(f(1, 0, 0, 0), f(1, 1, 1, 1)[None], "manhattan")[0] - 3.0) < 1e-4
+    z = np.zeros(512, np.float32)
+    assert abs(e.computeDistances(z, np.ones((1, 512), np.float32), "euclidean")[0] - math.sqrt(512)) < 1e-3
+    q = np.stack([np.full(512, float(i), np.float32) for i in range(10)])
+    c = np.stack([np.full(512, float(j), np.float32) for j in range(100)])
+    dm = e.batchComputeDistances(q, c, "euclidean")
+    exp = np.sqrt(512.0 * (np.arange(10)[:, None] - np.arange(100)[None, :]) ** 2)
+    assert np.max(np.abs(dm - exp)) < 1e-2
+    one, two = np.ones((1, 512), np.float32), 2 * np.ones((1, 512), np.float32)
+    assert abs(e.batchComputeDistances(one, two, "manhattan")[0, 0] - 512.0) < 1e-2
+    assert abs(e.batchComputeDistances(one, two, "cosine")[0, 0]) < 1e-2
+    # Phase1ValidationTests.swift:117-140: 100 queries x 1000 candidates, d = 256, k = 10 -> 100 rows of 10
+    rng = np.random.default_rng(0)
+    r = e.batchComputeDistances(rng.standard_normal((100, 256)).astype(np.float32),
+                                rng.standard_normal((1000, 256)).astype(np.float32), "cosine", topK=10)
+    assert r.shape == (100, 10) and np.all(np.diff(r, axis=1) >= 0)
+
+
+@pytest.mark.parametrize("mid", range(4))
+def test_golden_shader_vectors(engine, mid):
+    got = engine.batchComputeDistances(GOLD["dist_q"], GOLD["dist_x"], NAMES[mid])
+    ref = GOLD[f"dist_{NAMES[mid]}"]
+    assert np.allclose(got, ref, rtol=1e-4, atol=1e-5)
+    got1 = engine.computeDistances(GOLD["single_q"], GOLD["single_x"], NAMES[mid])
+    assert np.allclose(got1, GOLD[f"single_{NAMES[mid]}"], rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.parametrize("mid", range(4))
+@pytest.mark.parametrize("shape", [(1, 1, 1), (3, 31, 3), (33, 257, 127), (130, 129, 128), (5, 300, 129), (64, 1000, 768)])
+def test_batch_distances_vs_oracle(engine, cpu_oracle, mid, shape):
+    nq, nx, d = shape
+    rng = np.random.default_rng(1000 * mid + nq + nx + d)
+    q = rng.standard_normal((nq, d)).astype(np.float32)
+    x = rng.standard_normal((nx, d)).astype(np.float32)
+    got = engine.batchComputeDistances(q, x, NAMES[mid])
+    ref = cpu_oracle.batch_distances(mid, q, x)
+    assert np.allclose(got, ref, rtol=1e-4, atol=1e-4)
+
+
+def _flat(vsk, dev, metric, x, masks=None):
+    ix = vsk.FlatIndex(dev, x.shape[1], metric)
+    ix.add(x, masks)
+    return ix
+
+
+@pytest.mark.parametrize("path", [1, 0])
+@pytest.mark.parametrize("mid", range(4))
+@pytest.mark.parametrize("shape", [(1, 1, 1, 1), (7, 31, 3, 5), (33, 255, 127, 10), (130, 5000, 128, 10),
+                                   (257, 20000, 64, 100), (16, 9000, 129, 33)])
+def test_flat_search_vs_oracle(vsk, dev, cpu_oracle, path, mid, shape):
+    nq, nx, d, k = shape
+    dev.set_search_path(path)
+    rng = np.random.default_rng(77 * mid + nx + d)
+    q = rng.standard_normal((nq, d)).astype(np.float32)
+    x = rng.standard_normal((nx, d)).astype(np.float32)
+    ix = _flat(vsk, dev, NAMES[mid], x)
+    try:
+        gd, gi = ix.batchSearch(q, min(k, nx))
+    finally:
+        ix.close()
+        dev.set_search_path(0)
+    rd, ri = cpu_oracle.flat_search(mid, q, x, min(k, nx))
+    assert_topk_parity(gd, gi, rd, ri)
+
+
+@pytest.mark.parametrize("path", [1, 0])
+def test_config1_flat_euclidean_100k(vsk, dev, cpu_oracle, path):
+    """Flat exact k-NN, Euclidean: N = 100 000 x d = 128, 1 000 queries, k = 10, i.i.d. N(0,1)."""
+    rng = np.random.default_rng(202611251)
+    x = rng.standard_normal((100_000, 128)).astype(np.float32)
+    q = rng.standard_normal((1000, 128)).astype(np.float32)
+    dev.set_search_path(path)
+    ix = _flat(vsk, dev, "euclidean", x)
+    try:
+        gd, gi = ix.batchSearch(q, 10)
+    finally:
+        ix.close()
+        dev.set_search_path(0)
+    rd, ri = cpu_oracle.flat_search(oracle.EUCLIDEAN, q, x, 10, nthreads=0)
+    assert_topk_parity(gd, gi, rd, ri)
+
+
+@pytest.mark.parametrize("path", [1, 0])
+def test_config2_shape_cosine_reduced(vsk, dev, cpu_oracle, path):
+    """Cosine, d = 768, k = 100, rows and queries L2-normalised (the headline configuration at
+    reduced N so that the CPU oracle finishes in seconds)."""
+    rng = np.random.default_rng(202611252)
+    x = cpu_oracle.normalize_rows(rng.standard_normal((30_000, 768)).astype(np.float32))
+    q = cpu_oracle.normalize_rows(rng.standard_normal((256, 768)).astype(np.float32))
+    dev.set_search_path(path)
+    ix = _flat(vsk, dev, "cosine", x)
+    try:
+        gd, gi = ix.batchSearch(q, 100)
+    finally:
+        ix.close()
+        dev.set_search_path(0)
+    rd, ri = cpu_oracle.flat_search(oracle.COSINE, q, x, 100)
+    assert_topk_parity(gd, gi, rd, ri)
+
+
+def test_filtered_manhattan(vsk, dev, cpu_oracle):
+    """Filtered flat search, Manhattan, uniform [-1,1], uint64 row masks with Bernoulli(0.5) bits,
+    one-hot query masks (about half the rows pass), k = 50."""
+    rng = np.random.default_rng(202611255)
+    x = rng.uniform(-1, 1, (30_000, 256)).astype(np.float32)
+    q = rng.uniform(-1, 1, (200, 256)).astype(np.float32)
+    rm = rng.integers(0, 2 ** 64, 30_000, dtype=np.uint64)
+    qm = (np.uint64(1) << rng.integers(0, 64, 200).astype(np.uint64))
+    ix = _flat(vsk, dev, "manhattan", x, rm)
+    try:
+        gd, gi = ix.batchSearch(q, 50, qm)
+        ud, ui = ix.batchSearch(q, 50)          # same index, unfiltered
+    finally:
+        ix.close()
+    rd, ri = cpu_oracle.flat_search(oracle.MANHATTAN, q, x, 50, rm, qm)
+    assert_topk_parity(gd, gi, rd, ri)
+    assert np.all((rm[gi] & qm[:, None]) != 0)
+    rd2, ri2 = cpu_oracle.flat_search(oracle.MANHATTAN, q, x, 50)
+    assert_topk_parity(ud, ui, rd2, ri2)
+
+
+def test_selective_filter_and_short_results(vsk, dev, cpu_oracle):
+    rng = np.random.default_rng(9)
+    x = rng.standard_normal((6000, 16)).astype(np.float32)
+    q = rng.standard_normal((5, 16)).astype(np.float32)
+    rm = np.zeros(6000, np.uint64)
+    rm[::500] = 1          # 12 rows pass bit 0
+    rm[7] |= 2             # one row passes bit 1
+    qm = np.array([1, 2, 4, 3, 1], np.uint64)   # bit 2: nothing passes
+    ix = _flat(vsk, dev, "euclidean", x, rm)
+    try:
+        gd, gi = ix.batchSearch(q, 20, qm)
+    finally:
+        ix.close()
+    rd, ri = cpu_oracle.flat_search(oracle.EUCLIDEAN, q, x, 20, rm, qm)
+    assert_topk_parity(gd, gi, rd, ri)
+    assert np.all(gi[2] == -1) and np.all(np.isinf(gd[2]))
+    assert (gi[1] >= 0).sum() == 1 and gi[1, 0] == 7
+
+
+@pytest.mark.parametrize("path", [1, 0])
+def test_adversarial_order_overflows_lists_and_is_still_exact(vsk, dev, cpu_oracle, path):
+    """Rows sorted farthest-first make every later row beat the running threshold, so the candidate
+    lists overflow and the flagged queries take the non-overflowing re-run."""
+    rng = np.random.default_rng(11)
+    x = rng.standard_normal((40_000, 32)).astype(np.float32)
+    q = np.zeros((3, 32), np.float32)
+    q[1] += 0.01
+    q[2] -= 0.01
+    order = np.argsort(-np.linalg.norm(x, axis=1))
+    x = np.ascontiguousarray(x[order])
+    dev.set_search_path(path)
+    before = dev.stats()["fallback_queries"]
+    ix = _flat(vsk, dev, "euclidean", x)
+    try:
+        gd, gi = ix.batchSearch(q, 10)
+    finally:
+        ix.close()
+        dev.set_search_path(0)
+    rd, ri = cpu_oracle.flat_search(oracle.EUCLIDEAN, q, x, 10)
+    assert_topk_parity(gd, gi, rd, ri)
+    assert dev.stats()["fallback_queries"] > before
+
+
+def test_incremental_add_and_id_base(vsk, dev, cpu_oracle):
+    rng = np.random.default_rng(12)
+    x = rng.standard_normal((3000, 24)).astype(np.float32)
+    q = rng.standard_normal((9, 24)).astype(np.float32)
+    ix = vsk.FlatIndex(dev, 24, "dotProduct")
+    try:
+        ix.add(x[:1000]); ix.add(x[1000:1001]); ix.add(x[1001:])
+        assert ix.count == 3000
+        ix.set_id_base(5_000_000_000)
+        gd, gi = ix.batchSearch(q, 7)
+    finally:
+        ix.close()
+    rd, ri = cpu_oracle.flat_search(oracle.DOT, q, x, 7)
+    assert_topk_parity(gd, gi - 5_000_000_000, rd, ri)
+
+
+def test_device_pointers_and_merge(vsk, dev, engine, cpu_oracle):
+    import torch
+    rng = np.random.default_rng(13)
+    x = rng.standard_normal((8000, 48)).astype(np.float32)
+    q = rng.standard_normal((70, 48)).astype(np.float32)
+    xd, qd = torch.from_numpy(x).cuda(), torch.from_numpy(q).cuda()
+    parts_d, parts_i = [], []
+    for s in range(4):
+        ix = vsk.FlatIndex(dev, 48, "euclidean")
+        ix.add(xd[s * 2000:(s + 1) * 2000])
+        ix.set_id_base(s * 2000)
+        d, i = ix.batchSearch(qd, 10)
+        assert d.is_cuda and i.dtype == torch.int64
+        parts_d.append(d); parts_i.append(i)
+        ix.close()
+    md, mi = engine.mergeTopK(torch.stack(parts_d), torch.stack(parts_i))
+    rd, ri = cpu_oracle.flat_search(oracle.EUCLIDEAN, q, x, 10)
+    assert_topk_parity(md.cpu().numpy(), mi.cpu().numpy(), rd, ri)
+    od, oi = cpu_oracle.merge_topk(torch.stack(parts_d).cpu().numpy(), torch.stack(parts_i).cpu().numpy())
+    assert np.array_equal(mi.cpu().numpy(), oi) and np.array_equal(md.cpu().numpy(), od)
+
+
+def test_errors(vsk, dev, engine):
+    x = np.zeros((4, 8), np.float32)
+    with pytest.raises(vsk.EmptyInput):
+        engine.batchComputeDistances(x, np.zeros((0, 8), np.float32), "euclidean")
+    with pytest.raises(vsk.UnsupportedOperation):
+        engine.batchComputeDistances(x, x, "hamming")
+    with pytest.raises(vsk.DimensionMismatch):
+        engine.batchComputeDistances(x, np.zeros((4, 9), np.float32), "euclidean")
+    ix = vsk.FlatIndex(dev, 8, "euclidean")
+    try:
+        with pytest.raises(vsk.EmptyInput):
+            ix.batchSearch(x, 3)               # empty index
+        ix.add(x)
+        with pytest.raises(vsk.DimensionMismatch):
+            ix.batchSearch(np.zeros((1, 7), np.float32), 3)
+        with pytest.raises(vsk.InvalidInput):
+            ix.batchSearch(x, 0)
+        with pytest.raises(vsk.InvalidInput):
+            ix.batchSearch(x, 3, np.ones(4, np.uint64))   # no row masks in the index
+        d, i = ix.batchSearch(x, 6)            # k > n: padded
+        assert np.all(i[:, 4:] == -1) and np.all(np.isinf(d[:, 4:]))
+    finally:
+        ix.close()

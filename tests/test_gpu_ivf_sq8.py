@@ -1,0 +1,156 @@
+"""GPU parity of k-means, IVF build/search and the int8 quantiser/scan against the CPU oracle."""
+import os
+
+import numpy as np
+import pytest
+
+import oracle
+from parity import assert_topk_parity
+
+pytestmark = pytest.mark.gpu
+GOLD = np.load(os.path.join(os.path.dirname(__file__), "golden", "metal_shader_vectors.npz"))
+
+
+@pytest.fixture(scope="module")
+def vsk():
+    import vectorstorekit_b200 as v
+    return v
+
+
+@pytest.fixture(scope="module")
+def dev(vsk):
+    return vsk.CUDAAcceleratorStrategy(0).initialize()
+
+
+def _mixture(rng, n, d, centres, sigma=0.1):
+    c = rng.integers(0, centres.shape[0], n)
+    return (centres[c] + sigma * rng.standard_normal((n, d))).astype(np.float32)
+
+
+def test_kmeans_golden_shader_steps(vsk, dev):
+    """Three Lloyd steps of the reference's shader kernels; centroid 5 starts far away, receives no
+    row and keeps its value."""
+    x, c0 = GOLD["km_x"], GOLD["km_c0"]
+    for it in (1, 2, 3):
+        km = vsk.KMeansClustering(dev, maxIterations=it, tolerance=-1.0)
+        cent, asg, iters, inertia = km.cluster(x, 6, c0)
+        assert iters == it
+        assert np.allclose(cent, GOLD[f"km_c{it}"], rtol=1e-5, atol=1e-6)
+        assert np.array_equal(cent[5], c0[5])
+    assert np.array_equal(asg, GOLD["km_assign3"])
+
+
+@pytest.mark.parametrize("shape", [(500, 12, 9, 4), (20_000, 128, 64, 5), (5000, 33, 300, 3)])
+def test_kmeans_vs_oracle(vsk, dev, cpu_oracle, shape):
+    n, d, k, iters = shape
+    rng = np.random.default_rng(n + d)
+    centres = rng.standard_normal((k, d)).astype(np.float32)
+    x = _mixture(rng, n, d, centres, 0.3)
+    km = vsk.KMeansClustering(dev, maxIterations=iters, tolerance=-1.0)
+    cent, asg, it, inertia = km.cluster(x, k, x[:k])
+    rc, ra, rin, rit = cpu_oracle.kmeans(x, x[:k], iters)
+    assert it == rit == iters
+    agree = np.mean(asg == ra)
+    assert agree > 0.999, agree
+    assert np.max(np.abs(cent - rc)) < 1e-3
+    assert abs(inertia - rin) <= 1e-3 * abs(rin)
+
+
+def test_kmeans_convergence_and_errors(vsk, dev, cpu_oracle):
+    rng = np.random.default_rng(4)
+    x = np.concatenate([rng.standard_normal((200, 4)) * 0.01 + 5, rng.standard_normal((200, 4)) * 0.01 - 5]).astype(np.float32)
+    km = vsk.KMeansClustering(dev, maxIterations=50, tolerance=1e-4)
+    cent, asg, it, inertia = km.cluster(x, 2, x[[0, 399]])
+    rc, ra, rin, rit = cpu_oracle.kmeans(x, x[[0, 399]], 50, 1e-4)
+    assert it == rit and it < 50 and np.array_equal(asg, ra)
+    with pytest.raises(vsk.InsufficientTrainingData):
+        km.cluster(x[:3], 5, x[:5])
+
+
+def test_ivf_kat_and_errors(vsk, dev):
+    """IVFIndexTests.swift:140-201: untrained use throws; basic search finds the inserted row."""
+    ix = vsk.IVFIndex(dev, 4, numberOfCentroids=2, numberOfProbes=2, maxIterations=25)
+    with pytest.raises(vsk.NotTrained):
+        ix.insert(np.zeros((1, 4), np.float32))
+    with pytest.raises(vsk.NotTrained):
+        ix.batchSearch(np.zeros((1, 4), np.float32), 1)
+    with pytest.raises(vsk.InsufficientTrainingData):
+        ix.train(np.zeros((1, 4), np.float32))
+    train = np.array([[1, 0, 0, 0], [0, 1, 0, 0], [0, 0, 1, 0], [0, 0, 0, 1],
+                      [.9, .1, 0, 0], [.1, .9, 0, 0], [0, .1, .9, 0], [0, 0, .1, .9]], np.float32)
+    ix.train(train)
+    ix.insert(np.array([[1, 0, 0, 0], [0, 1, 0, 0], [0, 0, 1, 0]], np.float32))
+    d, i = ix.search(np.array([.9, .1, 0, 0], np.float32), 1)
+    assert i[0] == 0
+    ix.close()
+
+
+@pytest.mark.parametrize("cfg", [(20_000, 32, 64, 8, 10, 300), (50_000, 128, 256, 16, 10, 500),
+                                 (3000, 17, 10, 10, 25, 40), (12_000, 16, 2, 1, 5, 64)])
+def test_ivf_search_vs_oracle(vsk, dev, cpu_oracle, cfg):
+    """Search parity on shared state: the GPU-trained centroids and list membership are handed to
+    the oracle, which applies IVFIndex.search semantics to them."""
+    n, d, nlist, nprobe, k, nq = cfg
+    rng = np.random.default_rng(n + nlist)
+    centres = rng.standard_normal((max(nlist, 4), d)).astype(np.float32)
+    x = _mixture(rng, n, d, centres)
+    q = _mixture(rng, nq, d, centres)
+    ix = vsk.IVFIndex(dev, d, numberOfCentroids=nlist, numberOfProbes=nprobe, maxIterations=5, tolerance=-1.0)
+    ix.train(x)
+    ix.insert(x)
+    asg = ix.assignments()
+    ra, _ = cpu_oracle.assign(x, ix.centroids)
+    assert np.mean(asg == ra) > 0.999
+    gd, gi = ix.batchSearch(q, k)
+    rd, ri = cpu_oracle.ivf_search(q, x, ix.centroids, asg, nprobe, k)
+    assert_topk_parity(gd, gi, rd, ri)
+    # `.exact` probes every list and equals the flat search (IVFIndexTests.swift:203-260)
+    ed, ei = ix.batchSearch(q[:32], k, vsk.SearchStrategy.exact)
+    fd, fi = cpu_oracle.flat_search(oracle.EUCLIDEAN, q[:32], x, k)
+    assert_topk_parity(ed, ei, fd, fi)
+    ix.close()
+
+
+def test_sq8_codes_bit_exact(vsk, dev, cpu_oracle):
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((5000, 37)).astype(np.float32)
+    for per_dim in (False, True):
+        sq = vsk.ScalarQuantizer(dev, per_dim=per_dim)
+        s, o = sq.train(x)
+        rs, ro = cpu_oracle.sq8_train(x, per_dim)
+        assert np.array_equal(s, rs) and np.array_equal(o, ro)
+        codes = sq.quantizeBatch(x)
+        assert np.array_equal(codes, cpu_oracle.sq8_encode(x, rs, ro))
+        assert np.array_equal(sq.dequantizeBatch(codes), cpu_oracle.sq8_decode(codes, rs, ro))
+    # the reference's round-trip pins (ScalarQuantizerTests.swift:55-94, VerifyComponents/main.swift:101-119)
+    sq = vsk.ScalarQuantizer(dev)
+    v = np.array([[-1.0, -0.5, 0.0, 0.5, 1.0]], np.float32)
+    sq.train(v)
+    assert np.max(np.abs(sq.dequantizeBatch(sq.quantizeBatch(v)) - v)) < 0.1
+    w = (np.arange(128, dtype=np.float32) / 128.0)[None]
+    sq.train(w)
+    assert np.max(np.abs(sq.dequantizeBatch(sq.quantizeBatch(w)) - w)) < 0.01
+
+
+@pytest.mark.parametrize("metric", ["dotProduct", "euclidean", "cosine", "manhattan"])
+def test_sq8_search_vs_oracle(vsk, dev, cpu_oracle, metric):
+    """Int8 scalar-quantised flat search: N(0,1) rows quantised per dimension with min/max scaling,
+    fp32 queries, k = 10 (reduced N)."""
+    import torch
+    rng = np.random.default_rng(202611254)
+    x = rng.standard_normal((20_000, 384)).astype(np.float32)
+    q = rng.standard_normal((100, 384)).astype(np.float32)
+    sq = vsk.ScalarQuantizer(dev, per_dim=True)
+    xd = torch.from_numpy(x).cuda()
+    s, o = sq.train(xd)
+    codes = sq.quantizeBatch(xd)
+    rs, ro = cpu_oracle.sq8_train(x, True)
+    assert np.array_equal(s.cpu().numpy(), rs) and np.array_equal(o.cpu().numpy(), ro)
+    rcodes = cpu_oracle.sq8_encode(x, rs, ro)
+    assert np.array_equal(codes.cpu().numpy(), rcodes)
+    ix = vsk.QuantizedFlatIndex(dev, 384, metric, s, o)
+    ix.add(codes)
+    gd, gi = ix.batchSearch(q, 10)
+    ix.close()
+    rd, ri = cpu_oracle.sq8_search(oracle.METRIC_IDS[metric], q, rcodes, rs, ro, 10)
+    assert_topk_parity(gd, gi, rd, ri)

@@ -1,0 +1,97 @@
+"""ctypes binding of ``libvsk_cuda.so`` (``include/vsk_cuda.h``).
+
+There is no CPU implementation behind this package: if the library is missing it must be
+built (``python -m vectorstorekit_b200.build``), and opening a context without a B200 raises
+``DeviceNotAvailable``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libvsk_cuda.so")
+
+c_f32p = C.POINTER(C.c_float)
+c_i64p = C.POINTER(C.c_int64)
+c_i32p = C.POINTER(C.c_int32)
+c_u64p = C.POINTER(C.c_uint64)
+c_i8p = C.POINTER(C.c_int8)
+vp = C.c_void_p
+
+
+class DeviceInfo(C.Structure):
+    _fields_ = [("device", C.c_int32), ("sm_count", C.c_int32), ("cc_major", C.c_int32), ("cc_minor", C.c_int32),
+                ("hbm_bytes", C.c_int64), ("l2_bytes", C.c_int64), ("max_smem_per_block", C.c_int32),
+                ("name", C.c_char * 128)]
+
+
+class Stats(C.Structure):
+    _fields_ = [("searches", C.c_int64), ("queries", C.c_int64), ("kernel_launches", C.c_int64),
+                ("tensor_tiles", C.c_int64), ("reranked_rows", C.c_int64), ("fallback_queries", C.c_int64),
+                ("h2d_bytes", C.c_int64), ("d2h_bytes", C.c_int64), ("scan_kernel_launches", C.c_int64),
+                ("scan_kernel_ms", C.c_double)]
+
+
+# name -> (restype, argtypes).  Pointers that may be host or device memory are void*.
+SIGNATURES = {
+    "vsk_open": (C.c_int32, [C.c_int32, C.POINTER(vp)]),
+    "vsk_close": (C.c_int32, [vp]),
+    "vsk_device_info_get": (C.c_int32, [vp, C.POINTER(DeviceInfo)]),
+    "vsk_stats_get": (C.c_int32, [vp, C.POINTER(Stats)]),
+    "vsk_last_error": (C.c_char_p, [vp]),
+    "vsk_status_string": (C.c_char_p, [C.c_int32]),
+    "vsk_set_search_path": (C.c_int32, [vp, C.c_int32]),
+    "vsk_stream": (vp, [vp]),
+    "vsk_profile": (C.c_int32, [vp, C.c_int32]),
+    "vsk_batch_distances": (C.c_int32, [vp, C.c_int32, vp, C.c_int64, vp, C.c_int64, C.c_int32, vp]),
+    "vsk_batch_distances_dev": (C.c_int32, [vp, C.c_int32, vp, C.c_int64, vp, C.c_int64, C.c_int32, vp]),
+    "vsk_flat_create": (C.c_int32, [vp, C.c_int32, C.c_int32, C.POINTER(vp)]),
+    "vsk_flat_add_f32": (C.c_int32, [vp, vp, C.c_int64, vp]),
+    "vsk_flat_add_f32_dev": (C.c_int32, [vp, vp, C.c_int64, vp]),
+    "vsk_index_destroy": (C.c_int32, [vp]),
+    "vsk_index_size": (C.c_int64, [vp]),
+    "vsk_index_set_id_base": (C.c_int32, [vp, C.c_int64]),
+    "vsk_search": (C.c_int32, [vp, vp, C.c_int64, C.c_int32, vp, vp, vp]),
+    "vsk_search_dev": (C.c_int32, [vp, vp, C.c_int64, C.c_int32, vp, vp, vp]),
+    "vsk_merge_topk_dev": (C.c_int32, [vp, vp, vp, C.c_int32, C.c_int64, C.c_int32, vp, vp]),
+    "vsk_kmeans": (C.c_int32, [vp, vp, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_float, vp, vp, vp,
+                               C.POINTER(C.c_float), C.POINTER(C.c_int32)]),
+    "vsk_kmeans_dev": (C.c_int32, [vp, vp, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_float, vp, vp, vp,
+                                   C.POINTER(C.c_float), C.POINTER(C.c_int32)]),
+    "vsk_assign_dev": (C.c_int32, [vp, vp, C.c_int64, C.c_int32, vp, C.c_int32, vp, vp]),
+    "vsk_ivf_build": (C.c_int32, [vp, vp, C.c_int32, vp, C.c_int64, C.c_int32, C.POINTER(vp)]),
+    "vsk_ivf_build_dev": (C.c_int32, [vp, vp, C.c_int32, vp, C.c_int64, C.c_int32, C.POINTER(vp)]),
+    "vsk_ivf_assignments": (C.c_int32, [vp, vp]),
+    "vsk_ivf_search": (C.c_int32, [vp, vp, C.c_int64, C.c_int32, C.c_int32, vp, vp]),
+    "vsk_ivf_search_dev": (C.c_int32, [vp, vp, C.c_int64, C.c_int32, C.c_int32, vp, vp]),
+    "vsk_sq8_train": (C.c_int32, [vp, vp, C.c_int64, C.c_int32, C.c_int32, vp, vp]),
+    "vsk_sq8_minmax_dev": (C.c_int32, [vp, vp, C.c_int64, C.c_int32, vp, vp]),
+    "vsk_sq8_params_dev": (C.c_int32, [vp, vp, vp, C.c_int32, C.c_int32, vp, vp]),
+    "vsk_sq8_encode": (C.c_int32, [vp, vp, C.c_int64, C.c_int32, vp, vp, vp]),
+    "vsk_sq8_encode_dev": (C.c_int32, [vp, vp, C.c_int64, C.c_int32, vp, vp, vp]),
+    "vsk_sq8_decode": (C.c_int32, [vp, vp, C.c_int64, C.c_int32, vp, vp, vp]),
+    "vsk_sq8_index_create": (C.c_int32, [vp, C.c_int32, C.c_int32, vp, vp, C.POINTER(vp)]),
+    "vsk_sq8_index_add": (C.c_int32, [vp, vp, C.c_int64]),
+    "vsk_sq8_index_add_dev": (C.c_int32, [vp, vp, C.c_int64]),
+}
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """Loads the library and binds every declared symbol; raises if one is missing."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m vectorstorekit_b200.build` "
+            "(there is no CPU implementation to fall back on)")
+    lib = C.CDLL(LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError if the symbol is not exported
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib

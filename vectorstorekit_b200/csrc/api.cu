@@ -1,0 +1,597 @@
+// C ABI: context, flat fp32 index, stateless distances, merge.  The search schedule lives here:
+// how a batch of queries walks the resident database in chunks, with per-query thresholds that
+// tighten between chunks so that only a few thousand of the N values per query ever leave the
+// scan kernels.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <functional>
+
+#include "common.cuh"
+#include "tensor_scan.cuh"
+
+namespace vsk {
+
+int32_t fail(Ctx* ctx, int32_t status, const char* fmt, ...) {
+  char buf[1024];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  if (ctx) ctx->err = buf;
+  return status;
+}
+
+int32_t dev_alloc(Ctx* ctx, void** p, size_t bytes) {
+  *p = nullptr;
+  if (bytes == 0) return VSK_OK;
+  cudaError_t e = cudaMalloc(p, bytes);
+  if (e != cudaSuccess) {
+    size_t fr = 0, tot = 0;
+    cudaMemGetInfo(&fr, &tot);
+    cudaGetLastError();
+    return fail(ctx, VSK_ERR_OUT_OF_MEMORY, "device out of memory: required %zu bytes, available %zu", bytes, fr);
+  }
+  return VSK_OK;
+}
+void dev_free(void* p) {
+  if (p) cudaFree(p);
+}
+
+int32_t scratch(Ctx* ctx, int slot, size_t bytes, void** out) {
+  if (ctx->scratch_bytes[slot] < bytes) {
+    // in-flight work may still use the old buffer
+    VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    dev_free(ctx->scratch[slot]);
+    ctx->scratch[slot] = nullptr;
+    ctx->scratch_bytes[slot] = 0;
+    size_t want = bytes + bytes / 8 + 256;
+    VSK_TRY(dev_alloc(ctx, &ctx->scratch[slot], want));
+    ctx->scratch_bytes[slot] = want;
+  }
+  *out = ctx->scratch[slot];
+  return VSK_OK;
+}
+
+void prof_begin(Ctx* ctx) {
+  if (!ctx->profile) return;
+  if (ctx->prof_used + 2 > ctx->prof_events.size()) {
+    cudaEvent_t a, b;
+    if (cudaEventCreate(&a) != cudaSuccess || cudaEventCreate(&b) != cudaSuccess) return;
+    ctx->prof_events.push_back(a);
+    ctx->prof_events.push_back(b);
+  }
+  cudaEventRecord(ctx->prof_events[ctx->prof_used], ctx->stream);
+}
+void prof_end(Ctx* ctx) {
+  if (!ctx->profile || ctx->prof_used + 2 > ctx->prof_events.size()) return;
+  cudaEventRecord(ctx->prof_events[ctx->prof_used + 1], ctx->stream);
+  ctx->prof_used += 2;
+  ctx->stats.scan_kernel_launches++;
+}
+void prof_collect(Ctx* ctx) {
+  for (size_t i = 0; i + 1 < ctx->prof_used; i += 2) {
+    float ms = 0.f;
+    if (cudaEventElapsedTime(&ms, ctx->prof_events[i], ctx->prof_events[i + 1]) == cudaSuccess)
+      ctx->stats.scan_kernel_ms += ms;
+  }
+  ctx->prof_used = 0;
+}
+
+static bool metric_ok(int32_t m) { return m >= VSK_METRIC_EUCLIDEAN && m <= VSK_METRIC_MANHATTAN; }
+
+// Candidate-list workspace for `nq` queries.
+static int32_t cand_workspace(Ctx* ctx, int64_t nq, CandLists* c) {
+  void* p;
+  VSK_TRY(scratch(ctx, SLOT_CAND_KEYS, (size_t)nq * kCandCap * sizeof(uint64_t), &p));
+  c->keys = (uint64_t*)p;
+  VSK_TRY(scratch(ctx, SLOT_CAND_COUNT, (size_t)nq * sizeof(int32_t), &p));
+  c->count = (int32_t*)p;
+  VSK_TRY(scratch(ctx, SLOT_CAND_THR, (size_t)nq * sizeof(float), &p));
+  c->thr = (float*)p;
+  VSK_TRY(scratch(ctx, SLOT_CAND_FLAGS, (size_t)nq * sizeof(int32_t), &p));
+  c->flags = (int32_t*)p;
+  c->nq = nq;
+  return VSK_OK;
+}
+
+// scan(mode, row_begin, row_end): appends to the lists.
+using ScanFn = std::function<int32_t(int mode, int64_t row_begin, int64_t row_end)>;
+
+// Walks rows [0, n) in chunks.  The first chunk (at most kCandCap rows) is written densely, one
+// slot per row; it is compacted to the best `keep`, whose worst value becomes the threshold.
+// Each later chunk appends only rows at or below the threshold and is sized so that the expected
+// number of appends (keep * chunk / rows_seen) is at most half the free room of a list; a list
+// that overflows all the same is flagged and its query is re-run with `safe` chunks, which are
+// no larger than the free room and therefore cannot overflow.
+static int32_t run_schedule(Ctx* ctx, const ScanFn& scan, int64_t n, int64_t nq, int32_t keep,
+                            const CandLists& cand, bool safe) {
+  VSK_TRY(launch_init_cand(ctx, cand, nq));
+  SelectArgs sel{};
+  sel.cand = cand;
+  sel.nq = nq;
+  sel.keep = keep;
+  const int64_t room = kCandCap - keep;
+  int64_t seen = std::min<int64_t>(n, kCandCap);
+  VSK_TRY(scan(SCAN_DENSE, 0, seen));
+  sel.dense_count = (int32_t)seen;
+  VSK_TRY(launch_select(ctx, sel));
+  sel.dense_count = -1;
+  while (seen < n) {
+    int64_t chunk = safe ? room : std::max<int64_t>(room, seen * room / (2 * (int64_t)keep));
+    chunk = std::min(chunk, n - seen);
+    VSK_TRY(scan(SCAN_THRESHOLD, seen, seen + chunk));
+    VSK_TRY(launch_select(ctx, sel));
+    seen += chunk;
+  }
+  return VSK_OK;
+}
+
+// Indices of flagged queries, gathered on the host (a few bytes per query, once per batch).
+static int32_t flagged_queries(Ctx* ctx, const CandLists& cand, int64_t nq, std::vector<int32_t>* out) {
+  std::vector<int32_t> flags((size_t)nq);
+  VSK_CUDA(ctx, cudaMemcpyAsync(flags.data(), cand.flags, nq * sizeof(int32_t), cudaMemcpyDeviceToHost, ctx->stream));
+  VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  out->clear();
+  for (int64_t i = 0; i < nq; ++i)
+    if (flags[i]) out->push_back((int32_t)i);
+  return VSK_OK;
+}
+
+// fp32 scan of `nq` queries (optionally the subset `sub_dev` of a larger batch) over n rows
+// described by `proto` (metric, operands, norms, masks), with final output.
+int32_t fp32_topk(Ctx* ctx, const ExactScanArgs& proto, int64_t n, int64_t nq, const int32_t* sub_dev, int32_t k,
+                  int64_t id_base, float* out_dist, int64_t* out_ids, bool safe) {
+  CandLists cand;
+  VSK_TRY(cand_workspace(ctx, nq, &cand));
+  ExactScanArgs a = proto;
+  a.nq = nq;
+  a.q_subset = sub_dev;
+  a.cand = cand;
+  ScanFn scan = [&](int mode, int64_t b, int64_t e) {
+    a.mode = mode;
+    a.row_begin = b;
+    a.row_end = e;
+    return launch_exact_scan(ctx, a);
+  };
+  VSK_TRY(run_schedule(ctx, scan, n, nq, k, cand, safe));
+  SelectArgs fin{};
+  fin.cand = cand;
+  fin.nq = nq;
+  fin.dense_count = -1;
+  fin.keep = k;
+  fin.out_dist = out_dist;
+  fin.out_ids = out_ids;
+  fin.k = k;
+  fin.metric = a.metric;
+  fin.id_base = id_base;
+  fin.q_subset = sub_dev;
+  fin.final_sqrt = a.metric == VSK_METRIC_EUCLIDEAN;
+  VSK_TRY(launch_select(ctx, fin));
+  if (!safe) {
+    std::vector<int32_t> bad;
+    VSK_TRY(flagged_queries(ctx, cand, nq, &bad));
+    if (!bad.empty()) {
+      // map list positions back to query indices of the caller's batch
+      if (sub_dev) {
+        std::vector<int32_t> sub_h((size_t)nq);
+        VSK_CUDA(ctx, cudaMemcpy(sub_h.data(), sub_dev, nq * sizeof(int32_t), cudaMemcpyDeviceToHost));
+        for (auto& b : bad) b = sub_h[b];
+      }
+      void* p;
+      VSK_TRY(scratch(ctx, SLOT_MISC0, bad.size() * sizeof(int32_t), &p));
+      VSK_CUDA(ctx, cudaMemcpyAsync(p, bad.data(), bad.size() * sizeof(int32_t), cudaMemcpyHostToDevice, ctx->stream));
+      VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+      ctx->stats.fallback_queries += (int64_t)bad.size();
+      VSK_TRY(fp32_topk(ctx, proto, n, (int64_t)bad.size(), (const int32_t*)p, k, id_base, out_dist, out_ids, true));
+    }
+  }
+  return VSK_OK;
+}
+
+static int32_t fp32_search(Index* ix, const float* q, int64_t nq, const int32_t* sub_dev, int32_t k,
+                           const float* qnorm, const uint64_t* qmasks, float* out_dist, int64_t* out_ids,
+                           bool safe) {
+  ExactScanArgs a{};
+  a.metric = ix->metric;
+  a.q = q;
+  a.x = ix->rows;
+  a.dim = ix->dim;
+  a.qnorm = qnorm;
+  a.xnorm = ix->row_norm;
+  a.row_masks = (qmasks && ix->has_masks) ? ix->masks : nullptr;
+  a.q_masks = a.row_masks ? qmasks : nullptr;
+  return fp32_topk(ix->ctx, a, ix->n, nq, sub_dev, k, ix->id_base, out_dist, out_ids, safe);
+}
+
+constexpr int64_t kQueryBatch = 16384;  // queries per pass: bounds the candidate workspace at 512 MB
+
+static int32_t flat_search_dev(Index* ix, const float* q, int64_t nq, int32_t k, const uint64_t* qmasks,
+                               float* out_dist, int64_t* out_ids) {
+  Ctx* ctx = ix->ctx;
+  if (ix->kind != INDEX_FLAT_F32) return fail(ctx, VSK_ERR_INVALID_INPUT, "not a flat fp32 index");
+  if (nq <= 0 || ix->n <= 0) return fail(ctx, VSK_ERR_EMPTY_INPUT, "empty queries or empty index");
+  if (k <= 0 || k > kCandCap / 2) return fail(ctx, VSK_ERR_INVALID_INPUT, "k must be in [1, %d]", kCandCap / 2);
+  if (!q || !out_dist || !out_ids) return fail(ctx, VSK_ERR_INVALID_INPUT, "null pointer");
+  if (qmasks && !ix->has_masks) return fail(ctx, VSK_ERR_INVALID_INPUT, "query masks given but the index has no row masks");
+  ctx->stats.searches++;
+  ctx->stats.queries += nq;
+  for (int64_t b = 0; b < nq; b += kQueryBatch) {
+    const int64_t bn = std::min(kQueryBatch, nq - b);
+    const float* qb = q + b * ix->dim;
+    const uint64_t* mb = qmasks ? qmasks + b : nullptr;
+    float* qnorm = nullptr;
+    if (ix->metric == VSK_METRIC_COSINE) {
+      void* p;
+      VSK_TRY(scratch(ctx, SLOT_QNORM, bn * sizeof(float), &p));
+      qnorm = (float*)p;
+      VSK_TRY(launch_row_norms(ctx, qb, bn, ix->dim, 0, qnorm));
+    }
+    const bool tensor = ctx->search_path == VSK_PATH_TENSOR_RERANK && ix->metric != VSK_METRIC_MANHATTAN &&
+                        !qmasks;
+    if (tensor) {
+      VSK_TRY(tensor_search(ix, qb, bn, k, qnorm, out_dist + b * k, out_ids + b * k));
+    } else {
+      VSK_TRY(fp32_search(ix, qb, bn, nullptr, k, qnorm, mb, out_dist + b * k, out_ids + b * k, false));
+    }
+  }
+  VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return VSK_OK;
+}
+
+// Entry used by the tensor path for queries whose certificate failed.
+int32_t fp32_search_subset(Index* ix, const float* q, const std::vector<int32_t>& subset, int32_t k,
+                           const float* qnorm, float* out_dist, int64_t* out_ids) {
+  Ctx* ctx = ix->ctx;
+  if (subset.empty()) return VSK_OK;
+  void* p;
+  VSK_TRY(scratch(ctx, SLOT_SUBSET, subset.size() * sizeof(int32_t), &p));
+  VSK_CUDA(ctx, cudaMemcpyAsync(p, subset.data(), subset.size() * sizeof(int32_t), cudaMemcpyHostToDevice, ctx->stream));
+  VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  ctx->stats.fallback_queries += (int64_t)subset.size();
+  return fp32_search(ix, q, (int64_t)subset.size(), (const int32_t*)p, k, qnorm, nullptr, out_dist, out_ids, false);
+}
+
+static int32_t flat_reserve(Index* ix, int64_t need) {
+  Ctx* ctx = ix->ctx;
+  if (need <= ix->capacity) return VSK_OK;
+  int64_t cap = std::max<int64_t>(need, ix->capacity + ix->capacity / 2);
+  float* rows = nullptr;
+  float* norm = nullptr;
+  uint64_t* masks = nullptr;
+  VSK_TRY(dev_alloc(ctx, (void**)&rows, (size_t)cap * ix->dim * sizeof(float)));
+  VSK_TRY(dev_alloc(ctx, (void**)&norm, (size_t)cap * sizeof(float)));
+  VSK_TRY(dev_alloc(ctx, (void**)&masks, (size_t)cap * sizeof(uint64_t)));
+  if (ix->n > 0) {
+    VSK_CUDA(ctx, cudaMemcpyAsync(rows, ix->rows, (size_t)ix->n * ix->dim * sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream));
+    VSK_CUDA(ctx, cudaMemcpyAsync(norm, ix->row_norm, (size_t)ix->n * sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream));
+    if (ix->has_masks)
+      VSK_CUDA(ctx, cudaMemcpyAsync(masks, ix->masks, (size_t)ix->n * sizeof(uint64_t), cudaMemcpyDeviceToDevice, ctx->stream));
+    VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  }
+  dev_free(ix->rows);
+  dev_free(ix->row_norm);
+  dev_free(ix->masks);
+  ix->rows = rows;
+  ix->row_norm = norm;
+  ix->masks = masks;
+  ix->capacity = cap;
+  return VSK_OK;
+}
+
+static int32_t flat_add(Index* ix, const float* rows, int64_t n, const uint64_t* masks, bool on_device) {
+  Ctx* ctx = ix->ctx;
+  if (ix->kind != INDEX_FLAT_F32) return fail(ctx, VSK_ERR_INVALID_INPUT, "not a flat fp32 index");
+  if (n <= 0) return fail(ctx, VSK_ERR_EMPTY_INPUT, "no rows to add");
+  if (!rows) return fail(ctx, VSK_ERR_INVALID_INPUT, "null rows");
+  if (ix->n + n > 0x7fffffffLL) return fail(ctx, VSK_ERR_INVALID_BUFFER_SIZE, "a flat index holds at most 2^31-1 rows");
+  if (ix->n > 0 && ((masks != nullptr) != ix->has_masks))
+    return fail(ctx, VSK_ERR_INVALID_INPUT, "either every added block carries masks or none does");
+  VSK_TRY(flat_reserve(ix, ix->n + n));
+  if (masks) ix->has_masks = true;
+  const cudaMemcpyKind kind = on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice;
+  VSK_CUDA(ctx, cudaMemcpyAsync(ix->rows + ix->n * ix->dim, rows, (size_t)n * ix->dim * sizeof(float), kind, ctx->stream));
+  if (masks)
+    VSK_CUDA(ctx, cudaMemcpyAsync(ix->masks + ix->n, masks, (size_t)n * sizeof(uint64_t), kind, ctx->stream));
+  if (!on_device) ctx->stats.h2d_bytes += (int64_t)n * ix->dim * 4 + (masks ? n * 8 : 0);
+  if (ix->metric == VSK_METRIC_COSINE || ix->metric == VSK_METRIC_EUCLIDEAN)
+    VSK_TRY(launch_row_norms(ctx, ix->rows + ix->n * ix->dim, n, ix->dim, ix->metric == VSK_METRIC_EUCLIDEAN,
+                             ix->row_norm + ix->n));
+  ix->n += n;
+  tensor_invalidate(ix);
+  VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return VSK_OK;
+}
+
+}  // namespace vsk
+
+using namespace vsk;
+
+extern "C" {
+
+const char* vsk_status_string(int32_t s) {
+  switch (s) {
+    case VSK_OK: return "ok";
+    case VSK_ERR_DEVICE_NOT_AVAILABLE: return "device not available";
+    case VSK_ERR_OUT_OF_MEMORY: return "device out of memory";
+    case VSK_ERR_UNSUPPORTED_OPERATION: return "unsupported operation";
+    case VSK_ERR_INVALID_BUFFER_SIZE: return "invalid buffer size";
+    case VSK_ERR_EXECUTION_FAILED: return "execution failed";
+    case VSK_ERR_TIMEOUT: return "timeout";
+    case VSK_ERR_INVALID_INPUT: return "invalid input";
+    case VSK_ERR_DIMENSION_MISMATCH: return "dimension mismatch";
+    case VSK_ERR_EMPTY_INPUT: return "empty input";
+    case VSK_ERR_NOT_TRAINED: return "index not trained";
+    case VSK_ERR_INSUFFICIENT_TRAINING_DATA: return "insufficient training data";
+    default: return "unknown status";
+  }
+}
+
+int32_t vsk_open(int32_t device, vsk_ctx** out_ctx) {
+  if (!out_ctx) return VSK_ERR_INVALID_INPUT;
+  *out_ctx = nullptr;
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess || count <= 0 || device < 0 || device >= count) {
+    cudaGetLastError();
+    return VSK_ERR_DEVICE_NOT_AVAILABLE;
+  }
+  Ctx* ctx = new Ctx();
+  ctx->device = device;
+  if (cudaSetDevice(device) != cudaSuccess || cudaGetDeviceProperties(&ctx->prop, device) != cudaSuccess) {
+    delete ctx;
+    return VSK_ERR_DEVICE_NOT_AVAILABLE;
+  }
+  if (ctx->prop.major != 10) {
+    // the kernels are built for sm_100a only
+    delete ctx;
+    return VSK_ERR_DEVICE_NOT_AVAILABLE;
+  }
+  if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess) {
+    delete ctx;
+    return VSK_ERR_DEVICE_NOT_AVAILABLE;
+  }
+  *out_ctx = reinterpret_cast<vsk_ctx*>(ctx);
+  return VSK_OK;
+}
+
+int32_t vsk_close(vsk_ctx* c) {
+  Ctx* ctx = reinterpret_cast<Ctx*>(c);
+  if (!ctx) return VSK_ERR_INVALID_INPUT;
+  cudaSetDevice(ctx->device);
+  cudaStreamSynchronize(ctx->stream);
+  for (auto& p : ctx->scratch) dev_free(p);
+  for (auto& e : ctx->prof_events) cudaEventDestroy(e);
+  cudaStreamDestroy(ctx->stream);
+  delete ctx;
+  return VSK_OK;
+}
+
+int32_t vsk_device_info_get(vsk_ctx* c, vsk_device_info* out) {
+  Ctx* ctx = reinterpret_cast<Ctx*>(c);
+  if (!ctx || !out) return VSK_ERR_INVALID_INPUT;
+  memset(out, 0, sizeof(*out));
+  out->device = ctx->device;
+  out->sm_count = ctx->prop.multiProcessorCount;
+  out->cc_major = ctx->prop.major;
+  out->cc_minor = ctx->prop.minor;
+  out->hbm_bytes = (int64_t)ctx->prop.totalGlobalMem;
+  out->l2_bytes = ctx->prop.l2CacheSize;
+  out->max_smem_per_block = (int32_t)ctx->prop.sharedMemPerBlockOptin;
+  strncpy(out->name, ctx->prop.name, sizeof(out->name) - 1);
+  return VSK_OK;
+}
+
+int32_t vsk_stats_get(vsk_ctx* c, vsk_stats* out) {
+  Ctx* ctx = reinterpret_cast<Ctx*>(c);
+  if (!ctx || !out) return VSK_ERR_INVALID_INPUT;
+  if (ctx->profile) {
+    cudaStreamSynchronize(ctx->stream);
+    prof_collect(ctx);
+  }
+  *out = ctx->stats;
+  return VSK_OK;
+}
+
+const char* vsk_last_error(vsk_ctx* c) {
+  Ctx* ctx = reinterpret_cast<Ctx*>(c);
+  return ctx ? ctx->err.c_str() : "null context";
+}
+
+int32_t vsk_set_search_path(vsk_ctx* c, int32_t path) {
+  Ctx* ctx = reinterpret_cast<Ctx*>(c);
+  if (!ctx) return VSK_ERR_INVALID_INPUT;
+  if (path != VSK_PATH_TENSOR_RERANK && path != VSK_PATH_FP32_SCAN)
+    return fail(ctx, VSK_ERR_INVALID_INPUT, "unknown search path %d", path);
+  ctx->search_path = path;
+  return VSK_OK;
+}
+
+int32_t vsk_profile(vsk_ctx* c, int32_t enable) {
+  Ctx* ctx = reinterpret_cast<Ctx*>(c);
+  if (!ctx) return VSK_ERR_INVALID_INPUT;
+  cudaStreamSynchronize(ctx->stream);
+  prof_collect(ctx);
+  ctx->profile = enable != 0;
+  return VSK_OK;
+}
+
+void* vsk_stream(vsk_ctx* c) {
+  Ctx* ctx = reinterpret_cast<Ctx*>(c);
+  return ctx ? (void*)ctx->stream : nullptr;
+}
+
+int32_t vsk_batch_distances_dev(vsk_ctx* c, int32_t metric, const float* q, int64_t nq, const float* x,
+                                int64_t nx, int32_t dim, float* out) {
+  Ctx* ctx = reinterpret_cast<Ctx*>(c);
+  if (!ctx) return VSK_ERR_INVALID_INPUT;
+  cudaSetDevice(ctx->device);
+  if (!metric_ok(metric)) return fail(ctx, VSK_ERR_UNSUPPORTED_OPERATION, "metric %d is not supported", metric);
+  if (nq <= 0 || nx <= 0) return fail(ctx, VSK_ERR_EMPTY_INPUT, "empty queries or candidates");
+  if (dim <= 0) return fail(ctx, VSK_ERR_DIMENSION_MISMATCH, "dimension must be positive");
+  if (!q || !x || !out) return fail(ctx, VSK_ERR_INVALID_INPUT, "null pointer");
+  ExactScanArgs a{};
+  a.metric = metric;
+  a.mode = SCAN_MATRIX;
+  a.q = q;
+  a.x = x;
+  a.dim = dim;
+  a.nq = nq;
+  a.row_begin = 0;
+  a.row_end = nx;
+  a.out = out;
+  a.ld_out = nx;
+  if (metric == VSK_METRIC_COSINE) {
+    void* p;
+    VSK_TRY(scratch(ctx, SLOT_QNORM, nq * sizeof(float), &p));
+    VSK_TRY(launch_row_norms(ctx, q, nq, dim, 0, (float*)p));
+    a.qnorm = (float*)p;
+    VSK_TRY(scratch(ctx, SLOT_X_TMP, nx * sizeof(float), &p));
+    VSK_TRY(launch_row_norms(ctx, x, nx, dim, 0, (float*)p));
+    a.xnorm = (float*)p;
+  }
+  VSK_TRY(launch_exact_scan(ctx, a));
+  VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return VSK_OK;
+}
+
+int32_t vsk_batch_distances(vsk_ctx* c, int32_t metric, const float* q, int64_t nq, const float* x, int64_t nx,
+                            int32_t dim, float* out) {
+  Ctx* ctx = reinterpret_cast<Ctx*>(c);
+  if (!ctx) return VSK_ERR_INVALID_INPUT;
+  cudaSetDevice(ctx->device);
+  if (!metric_ok(metric)) return fail(ctx, VSK_ERR_UNSUPPORTED_OPERATION, "metric %d is not supported", metric);
+  if (nq <= 0 || nx <= 0) return fail(ctx, VSK_ERR_EMPTY_INPUT, "empty queries or candidates");
+  if (dim <= 0) return fail(ctx, VSK_ERR_DIMENSION_MISMATCH, "dimension must be positive");
+  if (!q || !x || !out) return fail(ctx, VSK_ERR_INVALID_INPUT, "null pointer");
+  float *dq = nullptr, *dx = nullptr, *dout = nullptr;
+  int32_t st = VSK_OK;
+  if ((st = dev_alloc(ctx, (void**)&dq, (size_t)nq * dim * 4)) == VSK_OK &&
+      (st = dev_alloc(ctx, (void**)&dx, (size_t)nx * dim * 4)) == VSK_OK &&
+      (st = dev_alloc(ctx, (void**)&dout, (size_t)nq * nx * 4)) == VSK_OK) {
+    cudaMemcpyAsync(dq, q, (size_t)nq * dim * 4, cudaMemcpyHostToDevice, ctx->stream);
+    cudaMemcpyAsync(dx, x, (size_t)nx * dim * 4, cudaMemcpyHostToDevice, ctx->stream);
+    st = vsk_batch_distances_dev(c, metric, dq, nq, dx, nx, dim, dout);
+    if (st == VSK_OK) {
+      cudaError_t e = cudaMemcpy(out, dout, (size_t)nq * nx * 4, cudaMemcpyDeviceToHost);
+      if (e != cudaSuccess) st = fail(ctx, VSK_ERR_EXECUTION_FAILED, "copy out failed: %s", cudaGetErrorString(e));
+    }
+    ctx->stats.h2d_bytes += (nq + nx) * dim * 4;
+    ctx->stats.d2h_bytes += nq * nx * 4;
+  }
+  dev_free(dq);
+  dev_free(dx);
+  dev_free(dout);
+  return st;
+}
+
+int32_t vsk_flat_create(vsk_ctx* c, int32_t metric, int32_t dim, vsk_index** out) {
+  Ctx* ctx = reinterpret_cast<Ctx*>(c);
+  if (!ctx || !out) return VSK_ERR_INVALID_INPUT;
+  *out = nullptr;
+  if (!metric_ok(metric)) return fail(ctx, VSK_ERR_UNSUPPORTED_OPERATION, "metric %d is not supported", metric);
+  if (dim <= 0) return fail(ctx, VSK_ERR_DIMENSION_MISMATCH, "dimension must be positive");
+  Index* ix = new Index();
+  ix->ctx = ctx;
+  ix->kind = INDEX_FLAT_F32;
+  ix->metric = metric;
+  ix->dim = dim;
+  *out = reinterpret_cast<vsk_index*>(ix);
+  return VSK_OK;
+}
+
+int32_t vsk_flat_add_f32(vsk_index* i, const float* rows, int64_t n, const uint64_t* masks) {
+  Index* ix = reinterpret_cast<Index*>(i);
+  if (!ix) return VSK_ERR_INVALID_INPUT;
+  cudaSetDevice(ix->ctx->device);
+  return flat_add(ix, rows, n, masks, false);
+}
+
+int32_t vsk_flat_add_f32_dev(vsk_index* i, const float* rows, int64_t n, const uint64_t* masks) {
+  Index* ix = reinterpret_cast<Index*>(i);
+  if (!ix) return VSK_ERR_INVALID_INPUT;
+  cudaSetDevice(ix->ctx->device);
+  return flat_add(ix, rows, n, masks, true);
+}
+
+int32_t vsk_index_destroy(vsk_index* i) {
+  Index* ix = reinterpret_cast<Index*>(i);
+  if (!ix) return VSK_ERR_INVALID_INPUT;
+  cudaSetDevice(ix->ctx->device);
+  cudaStreamSynchronize(ix->ctx->stream);
+  dev_free(ix->rows);
+  dev_free(ix->row_norm);
+  dev_free(ix->masks);
+  dev_free(ix->rows16);
+  dev_free(ix->row_aux);
+  dev_free(ix->codes);
+  dev_free(ix->sq_scale);
+  dev_free(ix->sq_offset);
+  dev_free(ix->centroids);
+  dev_free(ix->list_offsets);
+  dev_free(ix->list_rows);
+  dev_free(ix->assign);
+  delete ix;
+  return VSK_OK;
+}
+
+int64_t vsk_index_size(vsk_index* i) {
+  Index* ix = reinterpret_cast<Index*>(i);
+  return ix ? ix->n : -1;
+}
+
+int32_t vsk_index_set_id_base(vsk_index* i, int64_t id_base) {
+  Index* ix = reinterpret_cast<Index*>(i);
+  if (!ix) return VSK_ERR_INVALID_INPUT;
+  ix->id_base = id_base;
+  return VSK_OK;
+}
+
+int32_t vsk_search_dev(vsk_index* i, const float* q, int64_t nq, int32_t k, const uint64_t* qmasks,
+                       float* out_dist, int64_t* out_ids) {
+  Index* ix = reinterpret_cast<Index*>(i);
+  if (!ix) return VSK_ERR_INVALID_INPUT;
+  cudaSetDevice(ix->ctx->device);
+  if (ix->kind == INDEX_FLAT_I8) return sq8_search_dev(ix, q, nq, k, out_dist, out_ids);
+  return flat_search_dev(ix, q, nq, k, qmasks, out_dist, out_ids);
+}
+
+int32_t vsk_search(vsk_index* i, const float* q, int64_t nq, int32_t k, const uint64_t* qmasks, float* out_dist,
+                   int64_t* out_ids) {
+  Index* ix = reinterpret_cast<Index*>(i);
+  if (!ix) return VSK_ERR_INVALID_INPUT;
+  Ctx* ctx = ix->ctx;
+  cudaSetDevice(ctx->device);
+  if (nq <= 0) return fail(ctx, VSK_ERR_EMPTY_INPUT, "no queries");
+  if (k <= 0) return fail(ctx, VSK_ERR_INVALID_INPUT, "k must be positive");
+  if (!q || !out_dist || !out_ids) return fail(ctx, VSK_ERR_INVALID_INPUT, "null pointer");
+  void *dq, *dd, *di, *dm = nullptr;
+  VSK_TRY(scratch(ctx, SLOT_Q, (size_t)nq * ix->dim * 4, &dq));
+  VSK_TRY(scratch(ctx, SLOT_OUT_D, (size_t)nq * k * 4, &dd));
+  VSK_TRY(scratch(ctx, SLOT_OUT_I, (size_t)nq * k * 8, &di));
+  VSK_CUDA(ctx, cudaMemcpyAsync(dq, q, (size_t)nq * ix->dim * 4, cudaMemcpyHostToDevice, ctx->stream));
+  if (qmasks) {
+    VSK_TRY(scratch(ctx, SLOT_QMASK, (size_t)nq * 8, &dm));
+    VSK_CUDA(ctx, cudaMemcpyAsync(dm, qmasks, (size_t)nq * 8, cudaMemcpyHostToDevice, ctx->stream));
+  }
+  VSK_TRY(vsk_search_dev(i, (const float*)dq, nq, k, (const uint64_t*)dm, (float*)dd, (int64_t*)di));
+  VSK_CUDA(ctx, cudaMemcpyAsync(out_dist, dd, (size_t)nq * k * 4, cudaMemcpyDeviceToHost, ctx->stream));
+  VSK_CUDA(ctx, cudaMemcpyAsync(out_ids, di, (size_t)nq * k * 8, cudaMemcpyDeviceToHost, ctx->stream));
+  VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  ctx->stats.h2d_bytes += nq * ix->dim * 4 + (qmasks ? nq * 8 : 0);
+  ctx->stats.d2h_bytes += nq * k * 12;
+  return VSK_OK;
+}
+
+int32_t vsk_merge_topk_dev(vsk_ctx* c, const float* dist, const int64_t* ids, int32_t g, int64_t nq, int32_t k,
+                           float* out_dist, int64_t* out_ids) {
+  Ctx* ctx = reinterpret_cast<Ctx*>(c);
+  if (!ctx) return VSK_ERR_INVALID_INPUT;
+  cudaSetDevice(ctx->device);
+  if (g <= 0 || nq <= 0 || k <= 0) return fail(ctx, VSK_ERR_EMPTY_INPUT, "nothing to merge");
+  if (!dist || !ids || !out_dist || !out_ids) return fail(ctx, VSK_ERR_INVALID_INPUT, "null pointer");
+  VSK_TRY(launch_merge_topk(ctx, dist, ids, g, nq, k, out_dist, out_ids));
+  VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return VSK_OK;
+}
+
+}  // extern "C"

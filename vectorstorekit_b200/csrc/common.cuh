@@ -1,0 +1,229 @@
+// Shared declarations of the similarity-search library: context, index, candidate-list
+// workspace and the launch functions each .cu file exports to the C ABI layer.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+#include <string>
+#include <vector>
+
+#include "../../include/vsk_cuda.h"
+
+namespace vsk {
+
+// ------------------------------------------------------------------------------------------
+// Error plumbing: every CUDA call is checked; a failure records text on the context and
+// returns a status, never throws.
+// ------------------------------------------------------------------------------------------
+struct Ctx;
+int32_t fail(Ctx* ctx, int32_t status, const char* fmt, ...);
+
+#define VSK_CUDA(ctx, expr)                                                                   \
+  do {                                                                                        \
+    cudaError_t e__ = (expr);                                                                 \
+    if (e__ != cudaSuccess)                                                                   \
+      return vsk::fail((ctx),                                                                 \
+                       e__ == cudaErrorMemoryAllocation ? VSK_ERR_OUT_OF_MEMORY               \
+                                                        : VSK_ERR_EXECUTION_FAILED,           \
+                       "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e__), __FILE__,     \
+                       __LINE__);                                                             \
+  } while (0)
+
+#define VSK_TRY(expr)                  \
+  do {                                 \
+    int32_t s__ = (expr);              \
+    if (s__ != VSK_OK) return s__;     \
+  } while (0)
+
+// ------------------------------------------------------------------------------------------
+// Orderable keys: a (distance, row) pair packed so that unsigned 64-bit order is
+// (distance ascending, row ascending).  The all-ones key marks an empty slot.
+// ------------------------------------------------------------------------------------------
+__host__ __device__ inline uint32_t float_to_ordered(float f) {
+#ifdef __CUDA_ARCH__
+  uint32_t u = __float_as_uint(f);
+#else
+  uint32_t u;
+  memcpy(&u, &f, 4);
+#endif
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__host__ __device__ inline float ordered_to_float(uint32_t o) {
+  uint32_t u = (o & 0x80000000u) ? (o & 0x7fffffffu) : ~o;
+#ifdef __CUDA_ARCH__
+  return __uint_as_float(u);
+#else
+  float f;
+  memcpy(&f, &u, 4);
+  return f;
+#endif
+}
+__host__ __device__ inline uint64_t make_key(float v, uint32_t id) {
+  return ((uint64_t)float_to_ordered(v) << 32) | id;
+}
+constexpr uint64_t kEmptyKey = ~0ull;
+
+// ------------------------------------------------------------------------------------------
+// Candidate lists: per query a fixed-capacity list of (value, row) keys in HBM.
+// Scan kernels append every row whose value is <= the query's current threshold;
+// compaction keeps the best `keep` and tightens the threshold.
+// ------------------------------------------------------------------------------------------
+constexpr int kCandCap = 4096;  // keys per query
+
+struct CandLists {
+  uint64_t* keys = nullptr;   // [nq][kCandCap]
+  int32_t* count = nullptr;   // [nq] appended so far (may exceed cap: overflow)
+  float* thr = nullptr;       // [nq] rows with value <= thr are appended
+  int32_t* flags = nullptr;   // [nq] bit0: list overflowed; bit1: certificate failed
+  int64_t nq = 0;
+};
+
+enum ScanMode : int { SCAN_DENSE = 0, SCAN_THRESHOLD = 1, SCAN_MATRIX = 2, SCAN_ARGMIN = 3 };
+
+struct Ctx {
+  int device = 0;
+  cudaStream_t stream = nullptr;
+  cudaDeviceProp prop{};
+  std::string err;
+  int32_t search_path = VSK_PATH_TENSOR_RERANK;
+  vsk_stats stats{};
+  // optional timing of the dominant (scan) kernels with CUDA events on `stream`
+  bool profile = false;
+  std::vector<cudaEvent_t> prof_events;  // begin/end pairs
+  size_t prof_used = 0;
+  // grow-only device scratch, one buffer per slot (see Slot)
+  void* scratch[48] = {};
+  size_t scratch_bytes[48] = {};
+};
+
+enum Slot : int {
+  SLOT_Q = 0, SLOT_OUT_D, SLOT_OUT_I, SLOT_QMASK, SLOT_CAND_KEYS, SLOT_CAND_COUNT, SLOT_CAND_THR,
+  SLOT_CAND_FLAGS, SLOT_QNORM, SLOT_SUBSET, SLOT_Q16, SLOT_QAUX, SLOT_X_TMP, SLOT_MISC0, SLOT_MISC1,
+  SLOT_MISC2, SLOT_MISC3, SLOT_MISC4, SLOT_MISC5, SLOT_MISC6,
+  SLOT_IVF_PROBE_D, SLOT_IVF_PROBE_I, SLOT_IVF_KEYS, SLOT_IVF_ORDER, SLOT_IVF_PAIR_OFF, SLOT_IVF_ITEM_CNT,
+  SLOT_IVF_ITEM_OFF, SLOT_IVF_SUBSET, SLOT_SQ_A, SLOT_SQ_B, SLOT_TC_A, SLOT_TC_B, SLOT_TC_C, SLOT_TC_D,
+  SLOT_COUNT
+};
+static_assert(SLOT_COUNT <= 48, "grow Ctx::scratch");
+// Event pair around a scan-kernel launch when profiling is on (api.cu).
+void prof_begin(Ctx* ctx);
+void prof_end(Ctx* ctx);
+// After the stream has drained: adds the recorded intervals to stats.scan_kernel_ms.
+void prof_collect(Ctx* ctx);
+
+// Device pointer of at least `bytes` for the slot; contents are not preserved across growth.
+int32_t scratch(Ctx* ctx, int slot, size_t bytes, void** out);
+
+enum IndexKind : int { INDEX_FLAT_F32 = 0, INDEX_FLAT_I8 = 1, INDEX_IVF = 2 };
+
+struct DevBuf {
+  void* p = nullptr;
+  size_t bytes = 0;
+};
+
+// One block of rows added to a flat index.  Blocks are concatenated logically.
+struct Index {
+  Ctx* ctx = nullptr;
+  int kind = INDEX_FLAT_F32;
+  int32_t metric = 0;
+  int32_t dim = 0;
+  int64_t n = 0;
+  int64_t capacity = 0;
+  int64_t id_base = 0;
+  float* rows = nullptr;       // [capacity][dim] fp32
+  float* row_norm = nullptr;   // [capacity] |x| (cosine), |x|^2 (euclidean)
+  uint64_t* masks = nullptr;   // [capacity]; meaningful when has_masks
+  bool has_masks = false;
+  // fp16 operand copy for the tensor path (built lazily, invalidated by add)
+  __half* rows16 = nullptr;    // [n16_rows][dim16]
+  int32_t dim16 = 0;
+  int64_t n16 = 0;             // rows converted
+  float* row_aux = nullptr;    // [n] per-row epilogue term (|x*s|^2 in operand units for L2)
+  float scale16 = 1.0f;        // power-of-two operand scale s_x
+  float max_xnorm16 = 0.f;     // max |x'| over rows
+  float max_xerr16 = 0.f;      // max |x*s - x'| over rows
+  float min_xnorm_nz = 0.f;    // min nonzero |x|
+  float max_xnorm = 0.f;       // max |x|
+  // int8
+  int8_t* codes = nullptr;     // [capacity][dim]
+  float* sq_scale = nullptr;   // [dim]
+  float* sq_offset = nullptr;  // [dim]
+  // ivf
+  int32_t nlist = 0;
+  float* centroids = nullptr;      // [nlist][dim]
+  int64_t* list_offsets = nullptr; // [nlist+1] device
+  std::vector<int64_t> list_offsets_h;
+  int32_t* list_rows = nullptr;    // [n] original row of each stored row
+  int32_t* assign = nullptr;       // [n] row -> list (original order)
+};
+
+// ---- exact_scan.cu -----------------------------------------------------------------------
+struct ExactScanArgs {
+  int32_t metric;
+  int mode;                 // ScanMode
+  const float* q;           // [nq][dim]
+  const float* x;           // [n][dim] fp32 rows, or
+  const int8_t* x_codes;    // [n][dim] int8 codes with per-dimension sq_scale / sq_offset
+  const float* sq_scale;
+  const float* sq_offset;
+  int32_t dim;
+  int64_t nq;
+  int64_t row_begin, row_end;   // rows of this launch
+  const float* qnorm;       // [nq] |q| (cosine)
+  const float* xnorm;       // [n] |x| (cosine)
+  const uint64_t* row_masks;  // or null
+  const uint64_t* q_masks;    // or null
+  const int32_t* q_subset;  // or null: indices of the queries to run (nq = subset size)
+  CandLists cand;           // SCAN_DENSE / SCAN_THRESHOLD
+  float* out;               // SCAN_MATRIX: [nq][ld_out]
+  int64_t ld_out;
+  unsigned long long* best; // SCAN_ARGMIN: [nq] smallest (value, row) key, pre-set to all ones
+};
+int32_t launch_exact_scan(Ctx* ctx, const ExactScanArgs& a);
+int32_t launch_row_norms(Ctx* ctx, const float* x, int64_t n, int32_t dim, int squared, float* out);
+
+// ---- group.cu ----------------------------------------------------------------------------
+// Stable grouping of n items by key in [0, nkeys): order[] lists item indices key by key, ascending
+// item index inside a key; offsets[nkeys+1] (int64) bounds each key's run.  Deterministic.
+int32_t launch_stable_group(Ctx* ctx, const int32_t* keys, int64_t n, int32_t nkeys, int32_t* order,
+                            int64_t* offsets);
+
+// ---- kmeans.cu ---------------------------------------------------------------------------
+int32_t assign_rows(Ctx* ctx, const float* rows, int64_t n, int32_t dim, const float* centroids, int32_t k,
+                    int32_t* assign, float* dist);
+
+// ---- select.cu ---------------------------------------------------------------------------
+struct SelectArgs {
+  CandLists cand;
+  int64_t nq;
+  int32_t dense_count;      // >=0: list holds exactly this many slots (dense chunk); <0: use count[]
+  int32_t keep;             // keep the best `keep`
+  // final output (null while compacting)
+  float* out_dist;          // [nq][k]
+  int64_t* out_ids;
+  int32_t k;
+  int32_t metric;           // output transform of the stored value
+  int64_t id_base;
+  const int32_t* q_subset;  // or null; lists are indexed by position, outputs by q_subset[pos]
+  int final_sqrt;           // 1: stored value is a squared L2 distance
+};
+int32_t launch_select(Ctx* ctx, const SelectArgs& a);
+int32_t launch_merge_topk(Ctx* ctx, const float* dist, const int64_t* ids, int32_t g, int64_t nq,
+                          int32_t k, float* out_dist, int64_t* out_ids);
+int32_t launch_init_cand(Ctx* ctx, const CandLists& c, int64_t nq);
+
+// ---- search schedule in api.cu -------------------------------------------------------------
+// Exact top-k of nq queries over n rows with the fp32 scan; `proto` carries metric, operands,
+// norms and masks.  Outputs are device pointers [nq][k] (indexed by sub_dev[pos] when given).
+int32_t fp32_topk(Ctx* ctx, const ExactScanArgs& proto, int64_t n, int64_t nq, const int32_t* sub_dev, int32_t k,
+                  int64_t id_base, float* out_dist, int64_t* out_ids, bool safe);
+
+// ---- helpers in api.cu ---------------------------------------------------------------------
+int32_t dev_alloc(Ctx* ctx, void** p, size_t bytes);
+void dev_free(void* p);
+
+inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+}  // namespace vsk

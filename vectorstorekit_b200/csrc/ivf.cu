@@ -1,0 +1,456 @@
+// Inverted-file index: build (assign rows to trained centroids, store them list by list) and
+// search (probe the nprobe nearest lists, exact rooted L2 over their rows, ascending top-k).
+// Replaces IVFIndex.insert / IVFIndex.search (Indexes/IVFIndex.swift:80-122,124-202), which walk
+// the probed lists one query at a time with scalar loops and a full sort.
+//
+// Search is LIST-major.  The (query, probe) pairs of a batch are grouped by list, so that the
+// rows of a list are read once for all the queries that probe it: one CTA computes a block of
+// 128 probing queries x 128 list rows with the fp32 tile, and appends the rows at or below each
+// query's threshold to that query's candidate list.  Probes are processed in stages by probe rank
+// (rank 0; 1; 2-3; 4-7; ...), compacting the candidate lists and tightening the thresholds between
+// stages, so the number of appended rows per stage stays near k.
+#include <algorithm>
+
+#include "common.cuh"
+#include "tile_core.cuh"
+
+namespace vsk {
+namespace {
+
+using namespace tile;
+
+constexpr int kPilotRows = kCandCap;  // rows of the nearest list scanned before the first compaction
+
+struct IvfScanArgs {
+  const float* q;            // [nq][dim]
+  const float* rows;         // list-major rows
+  int32_t dim;
+  const int64_t* list_off;   // [nlist+1] storage range of each list
+  const int32_t* list_rows;  // [n] original row id of each stored row
+  int32_t nlist;
+  int32_t slots;             // items per query = nprobe + 1 (last slot: remainder of the rank-0 list)
+  const int32_t* order;      // pair items grouped by (stage, list)
+  const int64_t* pair_off;   // [nkeys+1]
+  int32_t stage;
+  const int64_t* item_off;   // [nlist+1] first CTA of each list in this launch
+  int64_t win_lo, win_hi;    // row window inside every list for this launch
+  int32_t remainder_lo;      // remainder items only take rows >= this
+  const int32_t* q_subset;   // or null: list position -> query
+  CandLists cand;
+};
+
+__global__ void __launch_bounds__(THREADS, 2) ivf_scan_kernel(IvfScanArgs a) {
+  __shared__ __align__(16) Smem sm;
+  __shared__ int s_list;
+  // which list does this CTA belong to: last l with item_off[l] <= blockIdx.x
+  if (threadIdx.x == 0) {
+    int lo = 0, hi = a.nlist;
+    const int64_t b = blockIdx.x;
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (a.item_off[mid] <= b) lo = mid; else hi = mid;
+    }
+    s_list = lo;
+  }
+  __syncthreads();
+  const int l = s_list;
+  const int64_t local = (int64_t)blockIdx.x - a.item_off[l];
+  const int64_t lbeg = a.list_off[l], len = a.list_off[l + 1] - lbeg;
+  const int64_t wlo = min(a.win_lo, len), whi = min(a.win_hi, len);
+  const int64_t rtiles = (whi - wlo + BN - 1) / BN;
+  const int64_t qt = local / rtiles, rt = local % rtiles;
+  const int64_t pbeg = a.pair_off[(int64_t)a.stage * a.nlist + l] + qt * BM;
+  const int64_t pend = a.pair_off[(int64_t)a.stage * a.nlist + l + 1];
+  const int64_t r0 = wlo + rt * BN;  // first row (inside the list) of this block
+  const int dim = a.dim;
+
+  F32Row ar[2], br[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int64_t p = pbeg + stage_row(h);
+    ar[h].ok = p < pend;
+    int64_t q = 0;
+    if (ar[h].ok) {
+      const int pos = a.order[p] / a.slots;
+      q = a.q_subset ? a.q_subset[pos] : pos;
+    }
+    ar[h].base = a.q + q * dim;
+    ar[h].vec = (dim % 4 == 0) && aligned16(a.q);
+    const int64_t r = r0 + stage_row(h);
+    br[h].ok = r < whi;
+    br[h].base = a.rows + (lbeg + (br[h].ok ? r : 0)) * dim;
+    br[h].vec = (dim % 4 == 0) && aligned16(a.rows);
+  }
+  float acc[8][8];
+  mainloop<VSK_METRIC_EUCLIDEAN>(acc, ar, br, dim, sm);
+
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int64_t p = pbeg + tile_row(i);
+    if (p >= pend) continue;
+    const int item = a.order[p];
+    const int pos = item / a.slots;
+    const bool remainder = (item - pos * a.slots) == a.slots - 1;
+    const float thr = a.cand.thr[pos];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int64_t r = r0 + tile_col(j);
+      if (r >= whi || (remainder && r < a.remainder_lo)) continue;
+      const float v = acc[i][j];
+      if (v <= thr) {
+        const int slot = atomicAdd(&a.cand.count[pos], 1);
+        if (slot < kCandCap) a.cand.keys[(int64_t)pos * kCandCap + slot] = make_key(v, (uint32_t)a.list_rows[lbeg + r]);
+      }
+    }
+  }
+}
+
+// Grouping key of every (query, slot) item: stage(rank) * nlist + list, or the null key.
+// stage: rank 0 -> 0; rank p >= 1 -> 1 + floor(log2 p); the remainder slot -> stage 1.
+// per_rank: every rank is its own stage and there is no remainder item (safe re-run).
+__global__ void ivf_pair_keys_kernel(const int64_t* __restrict__ probes, int64_t npos, int nprobe, int nlist,
+                                     const int64_t* __restrict__ list_off, int per_rank, int null_key,
+                                     const int32_t* __restrict__ q_subset, int32_t* __restrict__ keys) {
+  const int slots = nprobe + 1;
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= npos * slots) return;
+  const int64_t pos = i / slots;
+  const int p = (int)(i - pos * slots);
+  const int64_t q = q_subset ? q_subset[pos] : pos;
+  int key = null_key;
+  if (p < nprobe) {
+    const int64_t l = probes[q * nprobe + p];
+    if (l >= 0) {
+      const int stage = per_rank ? p : (p == 0 ? 0 : 32 - __clz(p));
+      key = stage * nlist + (int)l;
+    }
+  } else if (!per_rank) {
+    const int64_t l = probes[q * nprobe];
+    if (l >= 0 && list_off[l + 1] - list_off[l] > kPilotRows) key = 1 * nlist + (int)l;
+  }
+  keys[i] = key;
+}
+
+// CTAs per list for one launch: ceil(pairs/128) * ceil(window rows/128)
+__global__ void ivf_item_count_kernel(const int64_t* pair_off, int stage, int nlist, const int64_t* list_off,
+                                      int64_t win_lo, int64_t win_hi, int64_t* counts) {
+  const int l = blockIdx.x * blockDim.x + threadIdx.x;
+  if (l >= nlist) return;
+  const int64_t pc = pair_off[(int64_t)stage * nlist + l + 1] - pair_off[(int64_t)stage * nlist + l];
+  const int64_t len = list_off[l + 1] - list_off[l];
+  const int64_t rows = min(win_hi, len) - min(win_lo, len);
+  counts[l] = ((pc + BM - 1) / BM) * ((rows + BN - 1) / BN);
+}
+
+__global__ void scan_i64_kernel(const int64_t* totals, int32_t n, int64_t* offsets) {
+  __shared__ int64_t carry;
+  __shared__ int64_t buf[1024];
+  if (threadIdx.x == 0) carry = 0;
+  __syncthreads();
+  for (int base = 0; base < n; base += 1024) {
+    const int i = base + threadIdx.x;
+    const int64_t v = i < n ? totals[i] : 0;
+    buf[threadIdx.x] = v;
+    __syncthreads();
+    for (int o = 1; o < 1024; o <<= 1) {
+      const int64_t t = threadIdx.x >= o ? buf[threadIdx.x - o] : 0;
+      __syncthreads();
+      buf[threadIdx.x] += t;
+      __syncthreads();
+    }
+    if (i < n) offsets[i] = carry + buf[threadIdx.x] - v;
+    __syncthreads();
+    if (threadIdx.x == 0) carry += buf[1023];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) offsets[n] = carry;
+}
+
+__global__ void gather_rows_kernel(const float* __restrict__ src, const int32_t* __restrict__ order, int64_t n,
+                                   int dim, float* __restrict__ dst) {
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= n) return;
+  const float* s = src + (int64_t)order[row] * dim;
+  float* d = dst + row * dim;
+  for (int i = threadIdx.x & 31; i < dim; i += 32) d[i] = __ldg(s + i);
+}
+
+// One launch of the list scan for `stage` and a row window, followed by a compaction.
+int32_t ivf_pass(Ctx* ctx, Index* ix, IvfScanArgs a, int64_t npos, int32_t keep) {
+  void *cnt, *off;
+  VSK_TRY(scratch(ctx, SLOT_IVF_ITEM_CNT, (size_t)(ix->nlist + 1) * 8, &cnt));
+  VSK_TRY(scratch(ctx, SLOT_IVF_ITEM_OFF, (size_t)(ix->nlist + 1) * 8, &off));
+  ivf_item_count_kernel<<<(unsigned)ceil_div(ix->nlist, 256), 256, 0, ctx->stream>>>(
+      a.pair_off, a.stage, ix->nlist, ix->list_offsets, a.win_lo, a.win_hi, (int64_t*)cnt);
+  scan_i64_kernel<<<1, 1024, 0, ctx->stream>>>((const int64_t*)cnt, ix->nlist, (int64_t*)off);
+  ctx->stats.kernel_launches += 2;
+  int64_t total = 0;
+  VSK_CUDA(ctx, cudaMemcpyAsync(&total, (int64_t*)off + ix->nlist, 8, cudaMemcpyDeviceToHost, ctx->stream));
+  VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  if (total > 0x7fffffffLL) return fail(ctx, VSK_ERR_INVALID_BUFFER_SIZE, "too many list tiles in one launch");
+  if (total > 0) {
+    a.item_off = (const int64_t*)off;
+    prof_begin(ctx);
+    ivf_scan_kernel<<<(unsigned)total, THREADS, 0, ctx->stream>>>(a);
+    prof_end(ctx);
+    ctx->stats.kernel_launches++;
+    VSK_CUDA(ctx, cudaGetLastError());
+  }
+  SelectArgs sel{};
+  sel.cand = a.cand;
+  sel.nq = npos;
+  sel.dense_count = -1;
+  sel.keep = keep;
+  return launch_select(ctx, sel);
+}
+
+int32_t ivf_search_positions(Ctx* ctx, Index* ix, const float* q, int64_t npos, const int32_t* sub_dev,
+                             const int64_t* probes, int32_t nprobe, int32_t k, float* out_dist, int64_t* out_ids,
+                             bool safe) {
+  const int slots = nprobe + 1;
+  const int nstages = safe ? nprobe : (nprobe <= 1 ? 2 : 2 + (31 - __builtin_clz((unsigned)(nprobe - 1))));
+  const int nkeys = nstages * ix->nlist + 1;  // + the null key
+  const int64_t nitems = npos * slots;
+  if (nitems > 0x7fffffffLL) return fail(ctx, VSK_ERR_INVALID_BUFFER_SIZE, "too many (query, probe) pairs");
+  void *keys, *order, *pair_off;
+  VSK_TRY(scratch(ctx, SLOT_IVF_KEYS, (size_t)nitems * 4, &keys));
+  VSK_TRY(scratch(ctx, SLOT_IVF_ORDER, (size_t)nitems * 4, &order));
+  VSK_TRY(scratch(ctx, SLOT_IVF_PAIR_OFF, (size_t)(nkeys + 1) * 8, &pair_off));
+  ivf_pair_keys_kernel<<<(unsigned)ceil_div(nitems, 256), 256, 0, ctx->stream>>>(
+      probes, npos, nprobe, ix->nlist, ix->list_offsets, safe ? 1 : 0, nkeys - 1, sub_dev, (int32_t*)keys);
+  ctx->stats.kernel_launches++;
+  VSK_TRY(launch_stable_group(ctx, (const int32_t*)keys, nitems, nkeys, (int32_t*)order, (int64_t*)pair_off));
+
+  CandLists cand;
+  {
+    void* p;
+    VSK_TRY(scratch(ctx, SLOT_CAND_KEYS, (size_t)npos * kCandCap * sizeof(uint64_t), &p));
+    cand.keys = (uint64_t*)p;
+    VSK_TRY(scratch(ctx, SLOT_CAND_COUNT, (size_t)npos * 4, &p));
+    cand.count = (int32_t*)p;
+    VSK_TRY(scratch(ctx, SLOT_CAND_THR, (size_t)npos * 4, &p));
+    cand.thr = (float*)p;
+    VSK_TRY(scratch(ctx, SLOT_CAND_FLAGS, (size_t)npos * 4, &p));
+    cand.flags = (int32_t*)p;
+    cand.nq = npos;
+  }
+  VSK_TRY(launch_init_cand(ctx, cand, npos));
+
+  IvfScanArgs a{};
+  a.q = q;
+  a.rows = ix->rows;
+  a.dim = ix->dim;
+  a.list_off = ix->list_offsets;
+  a.list_rows = ix->list_rows;
+  a.nlist = ix->nlist;
+  a.slots = slots;
+  a.order = (const int32_t*)order;
+  a.pair_off = (const int64_t*)pair_off;
+  a.q_subset = sub_dev;
+  a.cand = cand;
+  a.remainder_lo = kPilotRows;
+  int64_t max_len = 0;
+  for (int l = 0; l < ix->nlist; ++l) max_len = std::max(max_len, ix->list_offsets_h[l + 1] - ix->list_offsets_h[l]);
+  const int64_t room = kCandCap - k;
+  for (int s = 0; s < nstages; ++s) {
+    a.stage = s;
+    if (!safe) {
+      a.win_lo = 0;
+      a.win_hi = s == 0 ? kPilotRows : (1ll << 62);
+      VSK_TRY(ivf_pass(ctx, ix, a, npos, k));
+    } else {
+      for (int64_t w = 0; w < std::max<int64_t>(max_len, 1); w += room) {
+        a.win_lo = w;
+        a.win_hi = w + room;
+        VSK_TRY(ivf_pass(ctx, ix, a, npos, k));
+      }
+    }
+  }
+  SelectArgs fin{};
+  fin.cand = cand;
+  fin.nq = npos;
+  fin.dense_count = -1;
+  fin.keep = k;
+  fin.out_dist = out_dist;
+  fin.out_ids = out_ids;
+  fin.k = k;
+  fin.metric = VSK_METRIC_EUCLIDEAN;
+  fin.id_base = ix->id_base;
+  fin.q_subset = sub_dev;
+  fin.final_sqrt = 1;
+  VSK_TRY(launch_select(ctx, fin));
+  if (!safe) {
+    std::vector<int32_t> flags((size_t)npos), bad;
+    VSK_CUDA(ctx, cudaMemcpyAsync(flags.data(), cand.flags, npos * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    for (int64_t i = 0; i < npos; ++i)
+      if (flags[i]) bad.push_back((int32_t)i);
+    if (!bad.empty()) {
+      void* p;
+      VSK_TRY(scratch(ctx, SLOT_IVF_SUBSET, bad.size() * 4, &p));
+      VSK_CUDA(ctx, cudaMemcpyAsync(p, bad.data(), bad.size() * 4, cudaMemcpyHostToDevice, ctx->stream));
+      VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+      ctx->stats.fallback_queries += (int64_t)bad.size();
+      VSK_TRY(ivf_search_positions(ctx, ix, q, (int64_t)bad.size(), (const int32_t*)p, probes, nprobe, k, out_dist,
+                                   out_ids, true));
+    }
+  }
+  return VSK_OK;
+}
+
+int32_t ivf_build_dev(Ctx* ctx, const float* centroids, int32_t nlist, const float* rows, int64_t n, int32_t dim,
+                      Index** out) {
+  *out = nullptr;
+  if (nlist <= 0 || !centroids) return fail(ctx, VSK_ERR_NOT_TRAINED, "no centroids: train the index first");
+  if (n <= 0 || !rows) return fail(ctx, VSK_ERR_EMPTY_INPUT, "no rows");
+  if (dim <= 0) return fail(ctx, VSK_ERR_DIMENSION_MISMATCH, "dimension must be positive");
+  if (n > 0x7fffffffLL) return fail(ctx, VSK_ERR_INVALID_BUFFER_SIZE, "at most 2^31-1 rows");
+  Index* ix = new Index();
+  ix->ctx = ctx;
+  ix->kind = INDEX_IVF;
+  ix->metric = VSK_METRIC_EUCLIDEAN;
+  ix->dim = dim;
+  ix->n = n;
+  ix->capacity = n;
+  ix->nlist = nlist;
+  int32_t st;
+  if ((st = dev_alloc(ctx, (void**)&ix->centroids, (size_t)nlist * dim * 4)) != VSK_OK ||
+      (st = dev_alloc(ctx, (void**)&ix->assign, (size_t)n * 4)) != VSK_OK ||
+      (st = dev_alloc(ctx, (void**)&ix->list_rows, (size_t)n * 4)) != VSK_OK ||
+      (st = dev_alloc(ctx, (void**)&ix->list_offsets, (size_t)(nlist + 1) * 8)) != VSK_OK ||
+      (st = dev_alloc(ctx, (void**)&ix->rows, (size_t)n * dim * 4)) != VSK_OK) {
+    vsk_index_destroy(reinterpret_cast<vsk_index*>(ix));
+    return st;
+  }
+  auto body = [&]() -> int32_t {
+    VSK_CUDA(ctx, cudaMemcpyAsync(ix->centroids, centroids, (size_t)nlist * dim * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+    VSK_TRY(assign_rows(ctx, rows, n, dim, ix->centroids, nlist, ix->assign, nullptr));
+    VSK_TRY(launch_stable_group(ctx, ix->assign, n, nlist, ix->list_rows, ix->list_offsets));
+    gather_rows_kernel<<<(unsigned)ceil_div(n, 8), 256, 0, ctx->stream>>>(rows, ix->list_rows, n, dim, ix->rows);
+    ctx->stats.kernel_launches++;
+    ix->list_offsets_h.resize((size_t)nlist + 1);
+    VSK_CUDA(ctx, cudaMemcpyAsync(ix->list_offsets_h.data(), ix->list_offsets, (size_t)(nlist + 1) * 8, cudaMemcpyDeviceToHost, ctx->stream));
+    VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return VSK_OK;
+  };
+  st = body();
+  if (st != VSK_OK) {
+    vsk_index_destroy(reinterpret_cast<vsk_index*>(ix));
+    return st;
+  }
+  *out = ix;
+  return VSK_OK;
+}
+
+int32_t ivf_search_dev(Index* ix, const float* q, int64_t nq, int32_t k, int32_t nprobe, float* out_dist,
+                       int64_t* out_ids) {
+  Ctx* ctx = ix->ctx;
+  if (ix->kind != INDEX_IVF) return fail(ctx, VSK_ERR_INVALID_INPUT, "not an IVF index");
+  if (nq <= 0) return fail(ctx, VSK_ERR_EMPTY_INPUT, "no queries");
+  if (k <= 0 || k > kCandCap / 2) return fail(ctx, VSK_ERR_INVALID_INPUT, "k must be in [1, %d]", kCandCap / 2);
+  if (nprobe <= 0) return fail(ctx, VSK_ERR_INVALID_INPUT, "nprobe must be positive");
+  if (!q || !out_dist || !out_ids) return fail(ctx, VSK_ERR_INVALID_INPUT, "null pointer");
+  nprobe = std::min(nprobe, ix->nlist);
+  ctx->stats.searches++;
+  ctx->stats.queries += nq;
+  constexpr int64_t kBatch = 16384;
+  for (int64_t b = 0; b < nq; b += kBatch) {
+    const int64_t bn = std::min(kBatch, nq - b);
+    const float* qb = q + b * ix->dim;
+    // coarse quantiser: the nprobe nearest centroids, ascending (IVFIndex.findNearestCentroids, :529-540)
+    void *pd, *pi;
+    VSK_TRY(scratch(ctx, SLOT_IVF_PROBE_D, (size_t)bn * nprobe * 4, &pd));
+    VSK_TRY(scratch(ctx, SLOT_IVF_PROBE_I, (size_t)bn * nprobe * 8, &pi));
+    ExactScanArgs c{};
+    c.metric = VSK_METRIC_EUCLIDEAN;
+    c.q = qb;
+    c.x = ix->centroids;
+    c.dim = ix->dim;
+    VSK_TRY(fp32_topk(ctx, c, ix->nlist, bn, nullptr, nprobe, 0, (float*)pd, (int64_t*)pi, false));
+    VSK_TRY(ivf_search_positions(ctx, ix, qb, bn, nullptr, (const int64_t*)pi, nprobe, k, out_dist + b * k,
+                                 out_ids + b * k, false));
+  }
+  VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return VSK_OK;
+}
+
+}  // namespace
+}  // namespace vsk
+
+using namespace vsk;
+
+extern "C" {
+
+int32_t vsk_ivf_build_dev(vsk_ctx* c, const float* centroids, int32_t nlist, const float* rows, int64_t n, int32_t dim,
+                          vsk_index** out) {
+  Ctx* ctx = reinterpret_cast<Ctx*>(c);
+  if (!ctx || !out) return VSK_ERR_INVALID_INPUT;
+  cudaSetDevice(ctx->device);
+  return ivf_build_dev(ctx, centroids, nlist, rows, n, dim, reinterpret_cast<Index**>(out));
+}
+
+int32_t vsk_ivf_build(vsk_ctx* c, const float* centroids, int32_t nlist, const float* rows, int64_t n, int32_t dim,
+                      vsk_index** out) {
+  Ctx* ctx = reinterpret_cast<Ctx*>(c);
+  if (!ctx || !out) return VSK_ERR_INVALID_INPUT;
+  cudaSetDevice(ctx->device);
+  *out = nullptr;
+  if (nlist <= 0 || !centroids) return fail(ctx, VSK_ERR_NOT_TRAINED, "no centroids: train the index first");
+  if (n <= 0 || !rows) return fail(ctx, VSK_ERR_EMPTY_INPUT, "no rows");
+  if (dim <= 0) return fail(ctx, VSK_ERR_DIMENSION_MISMATCH, "dimension must be positive");
+  float *dc = nullptr, *dx = nullptr;
+  int32_t st;
+  if ((st = dev_alloc(ctx, (void**)&dc, (size_t)nlist * dim * 4)) == VSK_OK &&
+      (st = dev_alloc(ctx, (void**)&dx, (size_t)n * dim * 4)) == VSK_OK) {
+    cudaMemcpyAsync(dc, centroids, (size_t)nlist * dim * 4, cudaMemcpyHostToDevice, ctx->stream);
+    cudaMemcpyAsync(dx, rows, (size_t)n * dim * 4, cudaMemcpyHostToDevice, ctx->stream);
+    ctx->stats.h2d_bytes += ((int64_t)nlist + n) * dim * 4;
+    st = ivf_build_dev(ctx, dc, nlist, dx, n, dim, reinterpret_cast<Index**>(out));
+  }
+  dev_free(dc);
+  dev_free(dx);
+  return st;
+}
+
+int32_t vsk_ivf_assignments(vsk_index* i, int32_t* assign) {
+  Index* ix = reinterpret_cast<Index*>(i);
+  if (!ix || !assign) return VSK_ERR_INVALID_INPUT;
+  Ctx* ctx = ix->ctx;
+  cudaSetDevice(ctx->device);
+  if (ix->kind != INDEX_IVF) return fail(ctx, VSK_ERR_INVALID_INPUT, "not an IVF index");
+  VSK_CUDA(ctx, cudaMemcpy(assign, ix->assign, (size_t)ix->n * 4, cudaMemcpyDeviceToHost));
+  return VSK_OK;
+}
+
+int32_t vsk_ivf_search_dev(vsk_index* i, const float* q, int64_t nq, int32_t k, int32_t nprobe, float* out_dist,
+                           int64_t* out_ids) {
+  Index* ix = reinterpret_cast<Index*>(i);
+  if (!ix) return VSK_ERR_INVALID_INPUT;
+  cudaSetDevice(ix->ctx->device);
+  return ivf_search_dev(ix, q, nq, k, nprobe, out_dist, out_ids);
+}
+
+int32_t vsk_ivf_search(vsk_index* i, const float* q, int64_t nq, int32_t k, int32_t nprobe, float* out_dist,
+                       int64_t* out_ids) {
+  Index* ix = reinterpret_cast<Index*>(i);
+  if (!ix) return VSK_ERR_INVALID_INPUT;
+  Ctx* ctx = ix->ctx;
+  cudaSetDevice(ctx->device);
+  if (nq <= 0) return fail(ctx, VSK_ERR_EMPTY_INPUT, "no queries");
+  if (k <= 0) return fail(ctx, VSK_ERR_INVALID_INPUT, "k must be positive");
+  if (!q || !out_dist || !out_ids) return fail(ctx, VSK_ERR_INVALID_INPUT, "null pointer");
+  void *dq, *dd, *di;
+  VSK_TRY(scratch(ctx, SLOT_Q, (size_t)nq * ix->dim * 4, &dq));
+  VSK_TRY(scratch(ctx, SLOT_OUT_D, (size_t)nq * k * 4, &dd));
+  VSK_TRY(scratch(ctx, SLOT_OUT_I, (size_t)nq * k * 8, &di));
+  VSK_CUDA(ctx, cudaMemcpyAsync(dq, q, (size_t)nq * ix->dim * 4, cudaMemcpyHostToDevice, ctx->stream));
+  VSK_TRY(ivf_search_dev(ix, (const float*)dq, nq, k, nprobe, (float*)dd, (int64_t*)di));
+  VSK_CUDA(ctx, cudaMemcpyAsync(out_dist, dd, (size_t)nq * k * 4, cudaMemcpyDeviceToHost, ctx->stream));
+  VSK_CUDA(ctx, cudaMemcpyAsync(out_ids, di, (size_t)nq * k * 8, cudaMemcpyDeviceToHost, ctx->stream));
+  VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  ctx->stats.h2d_bytes += nq * ix->dim * 4;
+  ctx->stats.d2h_bytes += nq * k * 12;
+  return VSK_OK;
+}
+
+}  // extern "C"

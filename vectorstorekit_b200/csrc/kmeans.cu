@@ -1,0 +1,209 @@
+// Lloyd k-means on the GPU.  Replaces KMeansClustering.cluster
+// (Clustering/KMeansClustering.swift:48-113) and the shader kernels assign_to_centroids,
+// accumulate_centroids, finalize_centroids, compute_inertia
+// (Acceleration/Metal/Shaders/ClusteringShaders.metal:29-177,317-331).
+//
+//   assignment  the fp32 tile kernel with an arg-min epilogue: per row the smallest
+//               (squared distance, centroid index) key, so the lowest index wins ties exactly as
+//               the reference's strict '<' scan does (KMeansClustering.swift:283-288)
+//   update      rows are grouped by centroid with a stable counting sort, then one CTA per
+//               centroid adds its rows IN ROW ORDER, one thread per dimension — the same fp32
+//               summation order as KMeansClustering.updateCentroids (:342-380), with no float
+//               atomics, so the result is deterministic
+//   empty       an empty cluster keeps its previous centroid (ClusteringShaders.metal:171-176)
+//   inertia     sum of the un-squared distances (KMeansClustering.swift:97), reduced in fp64
+#include "common.cuh"
+
+namespace vsk {
+namespace {
+
+__global__ void decode_best_kernel(const unsigned long long* best, int64_t n, int32_t* assign, float* dist) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const unsigned long long b = best[i];
+  assign[i] = (int32_t)(uint32_t)b;
+  if (dist) dist[i] = sqrtf(ordered_to_float((uint32_t)(b >> 32)));
+}
+
+__global__ void centroid_update_kernel(const float* __restrict__ x, int dim, const int32_t* __restrict__ order,
+                                       const int64_t* __restrict__ offsets, const float* __restrict__ old_c,
+                                       float* __restrict__ new_c) {
+  const int c = blockIdx.x;
+  const int64_t begin = offsets[c], end = offsets[c + 1];
+  const int64_t cnt = end - begin;
+  for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+    if (cnt == 0) {
+      new_c[(int64_t)c * dim + d] = old_c[(int64_t)c * dim + d];
+      continue;
+    }
+    float s = 0.f;
+    int64_t r = begin;
+    for (; r + 4 <= end; r += 4) {
+      const float v0 = __ldg(x + (int64_t)order[r + 0] * dim + d);
+      const float v1 = __ldg(x + (int64_t)order[r + 1] * dim + d);
+      const float v2 = __ldg(x + (int64_t)order[r + 2] * dim + d);
+      const float v3 = __ldg(x + (int64_t)order[r + 3] * dim + d);
+      s += v0; s += v1; s += v2; s += v3;
+    }
+    for (; r < end; ++r) s += __ldg(x + (int64_t)order[r] * dim + d);
+    new_c[(int64_t)c * dim + d] = s / (float)cnt;
+  }
+}
+
+// fixed-shape fp64 reduction: 1024 partial sums, then one block
+__global__ void sum_partial_kernel(const float* v, int64_t n, double* partial) {
+  __shared__ double sh[256];
+  const int64_t per = (n + gridDim.x - 1) / gridDim.x;
+  const int64_t b = (int64_t)blockIdx.x * per, e = min(n, b + per);
+  double s = 0.0;
+  for (int64_t i = b + threadIdx.x; i < e; i += blockDim.x) s += (double)v[i];
+  sh[threadIdx.x] = s;
+  __syncthreads();
+  for (int o = 128; o > 0; o >>= 1) {
+    if (threadIdx.x < o) sh[threadIdx.x] += sh[threadIdx.x + o];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) partial[blockIdx.x] = sh[0];
+}
+__global__ void sum_final_kernel(const double* partial, int np, float* out) {
+  __shared__ double sh[1024];
+  sh[threadIdx.x] = threadIdx.x < np ? partial[threadIdx.x] : 0.0;
+  __syncthreads();
+  for (int o = 512; o > 0; o >>= 1) {
+    if (threadIdx.x < o) sh[threadIdx.x] += sh[threadIdx.x + o];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) *out = (float)sh[0];
+}
+
+}  // namespace
+
+// Nearest centroid (and rooted distance) of every row.
+int32_t assign_rows(Ctx* ctx, const float* rows, int64_t n, int32_t dim, const float* centroids, int32_t k,
+                    int32_t* assign, float* dist) {
+  void* best;
+  VSK_TRY(scratch(ctx, SLOT_MISC4, (size_t)n * sizeof(unsigned long long), &best));
+  VSK_CUDA(ctx, cudaMemsetAsync(best, 0xff, (size_t)n * sizeof(unsigned long long), ctx->stream));
+  ExactScanArgs a{};
+  a.metric = VSK_METRIC_EUCLIDEAN;
+  a.mode = SCAN_ARGMIN;
+  a.q = rows;
+  a.nq = n;
+  a.x = centroids;
+  a.dim = dim;
+  a.row_begin = 0;
+  a.row_end = k;
+  a.best = (unsigned long long*)best;
+  VSK_TRY(launch_exact_scan(ctx, a));
+  decode_best_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, ctx->stream>>>((const unsigned long long*)best, n, assign, dist);
+  ctx->stats.kernel_launches++;
+  VSK_CUDA(ctx, cudaGetLastError());
+  return VSK_OK;
+}
+
+int32_t kmeans_dev(Ctx* ctx, const float* rows, int64_t n, int32_t dim, int32_t k, int32_t max_iters,
+                   float tolerance, const float* init, float* centroids, int32_t* assign, float* inertia,
+                   int32_t* iters_run) {
+  if (n <= 0) return fail(ctx, VSK_ERR_EMPTY_INPUT, "empty dataset");
+  if (k <= 0 || k > n) return fail(ctx, VSK_ERR_INSUFFICIENT_TRAINING_DATA, "k = %d needs 1 <= k <= %lld rows", k, (long long)n);
+  if (dim <= 0) return fail(ctx, VSK_ERR_DIMENSION_MISMATCH, "dimension must be positive");
+  if (n > 0x7fffffffLL) return fail(ctx, VSK_ERR_INVALID_BUFFER_SIZE, "at most 2^31-1 rows");
+  if (!rows || !init || !centroids || !assign) return fail(ctx, VSK_ERR_INVALID_INPUT, "null pointer");
+  void *cur, *nxt, *dist, *order, *offsets, *partial, *inert;
+  VSK_TRY(scratch(ctx, SLOT_MISC0, (size_t)k * dim * 4, &cur));
+  VSK_TRY(scratch(ctx, SLOT_MISC1, (size_t)k * dim * 4, &nxt));
+  VSK_TRY(scratch(ctx, SLOT_MISC2, (size_t)n * 4, &dist));
+  VSK_TRY(scratch(ctx, SLOT_MISC3, (size_t)n * 4, &order));
+  VSK_TRY(scratch(ctx, SLOT_X_TMP, (size_t)(k + 1) * 8, &offsets));
+  VSK_TRY(scratch(ctx, SLOT_QAUX, 1024 * 8 + 16, &partial));
+  inert = (char*)partial + 1024 * 8;
+  VSK_CUDA(ctx, cudaMemcpyAsync(cur, init, (size_t)k * dim * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+  float prev = INFINITY, last = INFINITY;
+  int it = 0;
+  bool converged = false;
+  while (it < max_iters && !converged) {
+    VSK_TRY(assign_rows(ctx, rows, n, dim, (const float*)cur, k, assign, (float*)dist));
+    VSK_TRY(launch_stable_group(ctx, assign, n, k, (int32_t*)order, (int64_t*)offsets));
+    centroid_update_kernel<<<k, 128, 0, ctx->stream>>>(rows, dim, (const int32_t*)order, (const int64_t*)offsets,
+                                                       (const float*)cur, (float*)nxt);
+    sum_partial_kernel<<<1024, 256, 0, ctx->stream>>>((const float*)dist, n, (double*)partial);
+    sum_final_kernel<<<1, 1024, 0, ctx->stream>>>((const double*)partial, 1024, (float*)inert);
+    ctx->stats.kernel_launches += 3;
+    VSK_CUDA(ctx, cudaGetLastError());
+    std::swap(cur, nxt);
+    ++it;
+    if (tolerance >= 0.f || it == max_iters) {
+      VSK_CUDA(ctx, cudaMemcpyAsync(&last, inert, 4, cudaMemcpyDeviceToHost, ctx->stream));
+      VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+      converged = tolerance >= 0.f && fabsf(last - prev) < tolerance;
+      prev = last;
+    }
+  }
+  VSK_CUDA(ctx, cudaMemcpyAsync(centroids, cur, (size_t)k * dim * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+  VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  if (inertia) *inertia = last;
+  if (iters_run) *iters_run = it;
+  return VSK_OK;
+}
+
+}  // namespace vsk
+
+using namespace vsk;
+
+extern "C" {
+
+int32_t vsk_kmeans_dev(vsk_ctx* c, const float* rows, int64_t n, int32_t dim, int32_t k, int32_t max_iters,
+                       float tolerance, const float* init, float* centroids, int32_t* assign, float* inertia,
+                       int32_t* iters_run) {
+  Ctx* ctx = reinterpret_cast<Ctx*>(c);
+  if (!ctx) return VSK_ERR_INVALID_INPUT;
+  cudaSetDevice(ctx->device);
+  return kmeans_dev(ctx, rows, n, dim, k, max_iters, tolerance, init, centroids, assign, inertia, iters_run);
+}
+
+int32_t vsk_kmeans(vsk_ctx* c, const float* rows, int64_t n, int32_t dim, int32_t k, int32_t max_iters,
+                   float tolerance, const float* init, float* centroids, int32_t* assign, float* inertia,
+                   int32_t* iters_run) {
+  Ctx* ctx = reinterpret_cast<Ctx*>(c);
+  if (!ctx) return VSK_ERR_INVALID_INPUT;
+  cudaSetDevice(ctx->device);
+  if (n <= 0) return fail(ctx, VSK_ERR_EMPTY_INPUT, "empty dataset");
+  if (k <= 0 || k > n) return fail(ctx, VSK_ERR_INSUFFICIENT_TRAINING_DATA, "k = %d needs 1 <= k <= %lld rows", k, (long long)n);
+  if (dim <= 0) return fail(ctx, VSK_ERR_DIMENSION_MISMATCH, "dimension must be positive");
+  if (!rows || !init || !centroids || !assign) return fail(ctx, VSK_ERR_INVALID_INPUT, "null pointer");
+  float *dx = nullptr, *dinit = nullptr, *dcent = nullptr;
+  int32_t* dassign = nullptr;
+  int32_t st;
+  if ((st = dev_alloc(ctx, (void**)&dx, (size_t)n * dim * 4)) == VSK_OK &&
+      (st = dev_alloc(ctx, (void**)&dinit, (size_t)k * dim * 4)) == VSK_OK &&
+      (st = dev_alloc(ctx, (void**)&dcent, (size_t)k * dim * 4)) == VSK_OK &&
+      (st = dev_alloc(ctx, (void**)&dassign, (size_t)n * 4)) == VSK_OK) {
+    cudaMemcpyAsync(dx, rows, (size_t)n * dim * 4, cudaMemcpyHostToDevice, ctx->stream);
+    cudaMemcpyAsync(dinit, init, (size_t)k * dim * 4, cudaMemcpyHostToDevice, ctx->stream);
+    st = kmeans_dev(ctx, dx, n, dim, k, max_iters, tolerance, dinit, dcent, dassign, inertia, iters_run);
+    if (st == VSK_OK) {
+      cudaMemcpy(centroids, dcent, (size_t)k * dim * 4, cudaMemcpyDeviceToHost);
+      cudaError_t e = cudaMemcpy(assign, dassign, (size_t)n * 4, cudaMemcpyDeviceToHost);
+      if (e != cudaSuccess) st = fail(ctx, VSK_ERR_EXECUTION_FAILED, "copy out failed: %s", cudaGetErrorString(e));
+    }
+  }
+  dev_free(dx);
+  dev_free(dinit);
+  dev_free(dcent);
+  dev_free(dassign);
+  return st;
+}
+
+int32_t vsk_assign_dev(vsk_ctx* c, const float* rows, int64_t n, int32_t dim, const float* centroids, int32_t k,
+                       int32_t* assign, float* dist) {
+  Ctx* ctx = reinterpret_cast<Ctx*>(c);
+  if (!ctx) return VSK_ERR_INVALID_INPUT;
+  cudaSetDevice(ctx->device);
+  if (n <= 0 || k <= 0) return fail(ctx, VSK_ERR_EMPTY_INPUT, "empty rows or centroids");
+  if (!rows || !centroids || !assign) return fail(ctx, VSK_ERR_INVALID_INPUT, "null pointer");
+  VSK_TRY(assign_rows(ctx, rows, n, dim, centroids, k, assign, dist));
+  VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return VSK_OK;
+}
+
+}  // extern "C"

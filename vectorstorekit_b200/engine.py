@@ -1,0 +1,567 @@
+"""Host-side mirror of VectorStoreKit's acceleration interface over the CUDA C ABI.
+
+Names, argument meaning and error behaviour follow the reference's Swift types for this path
+(paths relative to ``Sources/VectorStoreKit``):
+
+* ``DistanceMetric``              — ``Core/SearchTypes.swift:105-118``
+* ``CUDAAcceleratorStrategy``     — a ``ComputeAccelerator`` (``Core/Protocols.swift:11-20``), the
+  plug-in point the Metal strategies implement (``API/Strategies/AcceleratorStrategies.swift``)
+* ``CUDAAccelerationEngine``      — ``MetalAccelerationEngine.computeDistances`` /
+  ``batchComputeDistances(queries:candidates:metric:topK:)``
+  (``Acceleration/MetalAccelerationEngine.swift:76-204``)
+* ``FlatIndex``                   — the resident flat exact search behind ``VectorStore.search`` /
+  batch search (``API/VectorStore.swift:271-318``, ``LLM/LLMVectorStore.swift:83-114``)
+* ``IVFIndex``                    — ``Indexes/IVFIndex.swift`` train / insert / search
+* ``ScalarQuantizer``             — ``Quantization/ScalarQuantizer.swift`` (int8)
+
+Arrays may be numpy arrays (host memory: copied in and out by the library) or torch CUDA tensors
+(device memory of the engine's GPU: used in place, results returned as CUDA tensors).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import enum
+from typing import Optional, Sequence
+
+import numpy as np
+
+from . import _lib
+
+try:  # torch is plumbing for device memory only
+    import torch
+except Exception:  # pragma: no cover
+    torch = None
+
+
+class DistanceMetric(enum.Enum):
+    """``DistanceMetric`` of the reference; only the first four run on the accelerated path
+    (``MetalDistanceCompute.swift:342-344`` throws ``unsupportedOperation`` for the rest)."""
+    euclidean = "euclidean"
+    cosine = "cosine"
+    dotProduct = "dotProduct"
+    manhattan = "manhattan"
+    chebyshev = "chebyshev"
+    minkowski = "minkowski"
+    hamming = "hamming"
+    jaccard = "jaccard"
+    mahalanobis = "mahalanobis"
+    earth_mover = "earth_mover"
+    learned = "learned"
+    adaptive = "adaptive"
+
+
+_METRIC_ID = {DistanceMetric.euclidean: 0, DistanceMetric.cosine: 1, DistanceMetric.dotProduct: 2,
+              DistanceMetric.manhattan: 3}
+
+
+class SearchStrategy(enum.Enum):
+    """``SearchStrategy`` cases that matter to IVF probing (``IVFIndex.swift:551-560``)."""
+    exact = "exact"
+    approximate = "approximate"
+    adaptive = "adaptive"
+
+
+# ---- errors: MetalComputeError (Metal/MetalErrors.swift:10-39), IVFError (IVFIndex.swift:619-637)
+class VSKError(RuntimeError):
+    status = -1
+
+
+class DeviceNotAvailable(VSKError):
+    status = 1
+
+
+class DeviceOutOfMemory(VSKError):
+    status = 2
+
+
+class UnsupportedOperation(VSKError):
+    status = 3
+
+
+class InvalidBufferSize(VSKError):
+    status = 4
+
+
+class ExecutionFailed(VSKError):
+    status = 5
+
+
+class Timeout(VSKError):
+    status = 6
+
+
+class InvalidInput(VSKError):
+    status = 7
+
+
+class DimensionMismatch(VSKError):
+    status = 8
+
+
+class EmptyInput(VSKError):
+    status = 9
+
+
+class NotTrained(VSKError):
+    status = 10
+
+
+class InsufficientTrainingData(VSKError):
+    status = 11
+
+
+_ERRORS = {c.status: c for c in (DeviceNotAvailable, DeviceOutOfMemory, UnsupportedOperation, InvalidBufferSize,
+                                 ExecutionFailed, Timeout, InvalidInput, DimensionMismatch, EmptyInput, NotTrained,
+                                 InsufficientTrainingData)}
+
+
+def _metric_id(metric) -> int:
+    if isinstance(metric, str):
+        metric = DistanceMetric(metric)
+    if metric not in _METRIC_ID:
+        raise UnsupportedOperation(f"Distance metric {metric.value} not supported on GPU")
+    return _METRIC_ID[metric]
+
+
+def _is_dev(a) -> bool:
+    return torch is not None and isinstance(a, torch.Tensor) and a.is_cuda
+
+
+def _host(a, dtype):
+    if torch is not None and isinstance(a, torch.Tensor):
+        a = a.detach().cpu().numpy()
+    return np.ascontiguousarray(a, dtype=dtype)
+
+
+def _ptr(a):
+    if a is None:
+        return None
+    if _is_dev(a):
+        return C.c_void_p(a.data_ptr())
+    return C.c_void_p(a.ctypes.data)
+
+
+class CUDAComputeDevice:
+    """What ``CUDAAcceleratorStrategy.initialize()`` returns: an opened context on one GPU."""
+
+    def __init__(self, device: int = 0):
+        self._lib = _lib.load()
+        h = C.c_void_p()
+        st = self._lib.vsk_open(device, C.byref(h))
+        if st != 0:
+            raise _ERRORS.get(st, VSKError)(
+                f"cannot open CUDA device {device}: {self._lib.vsk_status_string(st).decode()}")
+        self._h = h
+        self.device = device
+
+    def close(self):
+        if getattr(self, "_h", None):
+            self._lib.vsk_close(self._h)
+            self._h = None
+
+    def __del__(self):  # pragma: no cover
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def check(self, st: int):
+        if st != 0:
+            msg = self._lib.vsk_last_error(self._h).decode()
+            raise _ERRORS.get(st, VSKError)(msg or self._lib.vsk_status_string(st).decode())
+
+    def info(self) -> dict:
+        d = _lib.DeviceInfo()
+        self.check(self._lib.vsk_device_info_get(self._h, C.byref(d)))
+        return {"device": d.device, "name": d.name.decode(), "sm_count": d.sm_count,
+                "compute_capability": (d.cc_major, d.cc_minor), "hbm_bytes": d.hbm_bytes, "l2_bytes": d.l2_bytes,
+                "max_smem_per_block": d.max_smem_per_block}
+
+    def stats(self) -> dict:
+        s = _lib.Stats()
+        self.check(self._lib.vsk_stats_get(self._h, C.byref(s)))
+        return {f: getattr(s, f) for f, _ in s._fields_}
+
+    def profile(self, enable: bool):
+        self.check(self._lib.vsk_profile(self._h, 1 if enable else 0))
+
+    def set_search_path(self, path: int):
+        self.check(self._lib.vsk_set_search_path(self._h, path))
+
+    @property
+    def stream(self) -> int:
+        return int(self._lib.vsk_stream(self._h) or 0)
+
+
+class CUDAAcceleratorStrategy:
+    """``ComputeAccelerator`` conformance for a B200 (``Core/Protocols.swift:11-20``)."""
+
+    identifier = "cuda-sm100a"
+    requirements = {"minimumMemory": 1 << 30, "requiredFeatures": ["cuda", "sm_100a"], "optionalFeatures": ["nvlink"]}
+
+    def __init__(self, device: int = 0):
+        self.device_index = device
+        self._dev: Optional[CUDAComputeDevice] = None
+
+    def initialize(self) -> CUDAComputeDevice:
+        """Raises ``DeviceNotAvailable`` (the reference's ``AcceleratorError.noDevice``) without a B200."""
+        if self._dev is None:
+            self._dev = CUDAComputeDevice(self.device_index)
+        return self._dev
+
+    def capabilities(self) -> dict:
+        return self.initialize().info()
+
+
+PATH_TENSOR_RERANK, PATH_FP32_SCAN = 0, 1
+
+
+class CUDAAccelerationEngine:
+    """Signature mirror of ``MetalAccelerationEngine`` for distances and batch top-k."""
+
+    def __init__(self, device: Optional[CUDAComputeDevice] = None):
+        self.dev = device or CUDAComputeDevice(0)
+        self._lib = self.dev._lib
+
+    # MetalAccelerationEngine.computeDistances(query:candidates:metric:) -> [Float]
+    def computeDistances(self, query, candidates, metric):
+        q = query.reshape(1, -1) if hasattr(query, "reshape") else np.asarray(query, np.float32).reshape(1, -1)
+        return self.batchComputeDistances(q, candidates, metric)[0]
+
+    # MetalAccelerationEngine.batchComputeDistances(queries:candidates:metric:topK:) -> [[Float]]
+    def batchComputeDistances(self, queries, candidates, metric, topK: Optional[int] = None):
+        """Q x N distances, or per query the ``topK`` smallest ascending (distances only, as the
+        reference returns)."""
+        mid = _metric_id(metric)
+        if len(candidates) == 0 or len(queries) == 0:
+            raise EmptyInput("Empty input provided for distance computation")
+        if topK is not None:
+            index = FlatIndex(self.dev, queries.shape[1], metric)
+            try:
+                index.add(candidates)
+                d, _ = index.batchSearch(queries, min(topK, len(candidates)))
+            finally:
+                index.close()
+            return d
+        if _is_dev(queries) != _is_dev(candidates):
+            raise InvalidInput("queries and candidates must both be host arrays or both CUDA tensors")
+        if queries.shape[1] != candidates.shape[1]:
+            raise DimensionMismatch(f"expected {queries.shape[1]}, got {candidates.shape[1]}")
+        nq, d = queries.shape
+        nx = candidates.shape[0]
+        if _is_dev(queries):
+            q = queries.contiguous().float()
+            x = candidates.contiguous().float()
+            out = torch.empty((nq, nx), dtype=torch.float32, device=q.device)
+            self.dev.check(self._lib.vsk_batch_distances_dev(self.dev._h, mid, _ptr(q), nq, _ptr(x), nx, d, _ptr(out)))
+            return out
+        q, x = _host(queries, np.float32), _host(candidates, np.float32)
+        out = np.empty((nq, nx), np.float32)
+        self.dev.check(self._lib.vsk_batch_distances(self.dev._h, mid, _ptr(q), nq, _ptr(x), nx, d, _ptr(out)))
+        return out
+
+    def mergeTopK(self, dist, ids):
+        """[G, Q, k] per-shard results with global ids (CUDA tensors) -> merged [Q, k]."""
+        g, nq, k = dist.shape
+        dist = dist.contiguous()
+        ids = ids.contiguous()
+        od = torch.empty((nq, k), dtype=torch.float32, device=dist.device)
+        oi = torch.empty((nq, k), dtype=torch.int64, device=dist.device)
+        self.dev.check(self._lib.vsk_merge_topk_dev(self.dev._h, _ptr(dist), _ptr(ids), g, nq, k, _ptr(od), _ptr(oi)))
+        return od, oi
+
+
+class _IndexBase:
+    def __init__(self, dev: CUDAComputeDevice):
+        self.dev = dev
+        self._lib = dev._lib
+        self._h = None
+
+    def close(self):
+        if self._h:
+            self._lib.vsk_index_destroy(self._h)
+            self._h = None
+
+    def __del__(self):  # pragma: no cover
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @property
+    def count(self) -> int:
+        return int(self._lib.vsk_index_size(self._h)) if self._h else 0
+
+    def set_id_base(self, base: int):
+        self.dev.check(self._lib.vsk_index_set_id_base(self._h, base))
+
+    def _search(self, queries, k, qmasks=None):
+        nq = queries.shape[0]
+        if _is_dev(queries):
+            q = queries.contiguous().float()
+            od = torch.empty((nq, k), dtype=torch.float32, device=q.device)
+            oi = torch.empty((nq, k), dtype=torch.int64, device=q.device)
+            qm = qmasks.contiguous() if qmasks is not None else None
+            self.dev.check(self._lib.vsk_search_dev(self._h, _ptr(q), nq, k, _ptr(qm), _ptr(od), _ptr(oi)))
+            return od, oi
+        q = _host(queries, np.float32)
+        od = np.empty((nq, k), np.float32)
+        oi = np.empty((nq, k), np.int64)
+        qm = _host(qmasks, np.uint64) if qmasks is not None else None
+        self.dev.check(self._lib.vsk_search(self._h, _ptr(q), nq, k, _ptr(qm), _ptr(od), _ptr(oi)))
+        return od, oi
+
+
+class FlatIndex(_IndexBase):
+    """Resident database + exact k-NN.  ``masks`` are per-row uint64 metadata bitmasks; a search
+    with ``filter_masks`` keeps row r for query q iff ``masks[r] & filter_masks[q] != 0`` — the
+    bitmask form of the reference's pre-filter (``Indexes/IVFIndex.swift:163-172``)."""
+
+    def __init__(self, dev: CUDAComputeDevice, dimensions: int, metric=DistanceMetric.euclidean):
+        super().__init__(dev)
+        h = C.c_void_p()
+        dev.check(self._lib.vsk_flat_create(dev._h, _metric_id(metric), int(dimensions), C.byref(h)))
+        self._h = h
+        self.dimensions = int(dimensions)
+
+    def add(self, rows, masks=None):
+        if len(rows) == 0:
+            raise EmptyInput("no rows to add")
+        if rows.shape[1] != self.dimensions:
+            raise DimensionMismatch(f"expected {self.dimensions}, got {rows.shape[1]}")
+        if _is_dev(rows):
+            r = rows.contiguous().float()
+            m = masks.contiguous() if masks is not None else None
+            self.dev.check(self._lib.vsk_flat_add_f32_dev(self._h, _ptr(r), r.shape[0], _ptr(m)))
+        else:
+            r = _host(rows, np.float32)
+            m = _host(masks, np.uint64) if masks is not None else None
+            self.dev.check(self._lib.vsk_flat_add_f32(self._h, _ptr(r), r.shape[0], _ptr(m)))
+
+    # VectorStore.search(query:k:strategy:filter:) for one query
+    def search(self, query, k: int, filter_mask: Optional[int] = None):
+        q = query.reshape(1, -1)
+        fm = None
+        if filter_mask is not None:
+            fm = (torch.tensor([filter_mask], dtype=torch.int64, device=q.device).view(torch.int64) if _is_dev(q)
+                  else np.array([filter_mask], np.uint64))
+        d, i = self.batchSearch(q, k, fm)
+        return d[0], i[0]
+
+    # batchSearch(queries:k:filter:) — one ascending row of k hits per query, in query order
+    def batchSearch(self, queries, k: int, filter_masks=None):
+        if len(queries) == 0:
+            raise EmptyInput("no queries")
+        if queries.shape[1] != self.dimensions:
+            raise DimensionMismatch(f"expected {self.dimensions}, got {queries.shape[1]}")
+        return self._search(queries, int(k), filter_masks)
+
+
+class KMeansClustering:
+    """``KMeansClustering.cluster`` (``Clustering/KMeansClustering.swift:48-113``) with ``.custom``
+    initial centroids (:189-193).  Returns (centroids, assignments, iterations, inertia)."""
+
+    def __init__(self, dev: CUDAComputeDevice, maxIterations: int = 100, tolerance: float = 1e-4):
+        self.dev = dev
+        self._lib = dev._lib
+        self.maxIterations = maxIterations
+        self.tolerance = tolerance
+
+    def cluster(self, vectors, k: int, initialCentroids):
+        if len(vectors) == 0:
+            raise EmptyInput("emptyDataset")
+        n, d = vectors.shape
+        inertia = C.c_float()
+        iters = C.c_int32()
+        if _is_dev(vectors):
+            x = vectors.contiguous().float()
+            init = initialCentroids.contiguous().float()
+            cent = torch.empty((k, d), dtype=torch.float32, device=x.device)
+            asg = torch.empty(n, dtype=torch.int32, device=x.device)
+            self.dev.check(self._lib.vsk_kmeans_dev(self.dev._h, _ptr(x), n, d, k, self.maxIterations, self.tolerance,
+                                                    _ptr(init), _ptr(cent), _ptr(asg), C.byref(inertia),
+                                                    C.byref(iters)))
+        else:
+            x = _host(vectors, np.float32)
+            init = _host(initialCentroids, np.float32)
+            cent = np.empty((k, d), np.float32)
+            asg = np.empty(n, np.int32)
+            self.dev.check(self._lib.vsk_kmeans(self.dev._h, _ptr(x), n, d, k, self.maxIterations, self.tolerance,
+                                                _ptr(init), _ptr(cent), _ptr(asg), C.byref(inertia), C.byref(iters)))
+        return cent, asg, int(iters.value), float(inertia.value)
+
+    def assign(self, vectors, centroids):
+        """Nearest centroid and rooted distance per row (CUDA tensors)."""
+        x = vectors.contiguous().float()
+        c = centroids.contiguous().float()
+        asg = torch.empty(x.shape[0], dtype=torch.int32, device=x.device)
+        dist = torch.empty(x.shape[0], dtype=torch.float32, device=x.device)
+        self.dev.check(self._lib.vsk_assign_dev(self.dev._h, _ptr(x), x.shape[0], x.shape[1], _ptr(c), c.shape[0],
+                                                _ptr(asg), _ptr(dist)))
+        return asg, dist
+
+
+class IVFIndex(_IndexBase):
+    """``IVFIndex`` (``Indexes/IVFIndex.swift``): ``train(on:)`` runs k-means for the centroids,
+    ``insert`` assigns rows to their nearest centroid's list, ``search`` probes ``numberOfProbes``
+    lists (all of them for ``SearchStrategy.exact``) with rooted L2.  Rows are inserted in one
+    batch; ids are insertion indices."""
+
+    def __init__(self, dev: CUDAComputeDevice, dimensions: int, numberOfCentroids: int = 1024,
+                 numberOfProbes: int = 10, maxIterations: int = 100, tolerance: float = 1e-4):
+        super().__init__(dev)
+        if dimensions <= 0 or numberOfCentroids <= 0 or not (0 < numberOfProbes <= numberOfCentroids):
+            raise InvalidInput("IVFConfiguration.validate failed")  # IVFConfiguration.swift:49-59
+        self.dimensions = dimensions
+        self.numberOfCentroids = numberOfCentroids
+        self.numberOfProbes = numberOfProbes
+        self.clustering = KMeansClustering(dev, maxIterations, tolerance)
+        self.centroids = None
+        self.trained = False
+
+    def train(self, samples, initialCentroids=None):
+        if len(samples) < self.numberOfCentroids:
+            raise InsufficientTrainingData(f"provided {len(samples)}, required {self.numberOfCentroids}")
+        if initialCentroids is None:
+            initialCentroids = samples[: self.numberOfCentroids]
+        self.centroids, _, iters, inertia = self.clustering.cluster(samples, self.numberOfCentroids, initialCentroids)
+        self.trained = True
+        self.close()
+        return iters, inertia
+
+    def insert(self, rows):
+        if not self.trained:
+            raise NotTrained("Index must be trained before use")
+        self.close()
+        h = C.c_void_p()
+        n, d = rows.shape
+        if _is_dev(rows):
+            r = rows.contiguous().float()
+            c = self.centroids if _is_dev(self.centroids) else torch.as_tensor(self.centroids, device=r.device)
+            self.dev.check(self._lib.vsk_ivf_build_dev(self.dev._h, _ptr(c.contiguous()), self.numberOfCentroids,
+                                                       _ptr(r), n, d, C.byref(h)))
+        else:
+            r = _host(rows, np.float32)
+            c = _host(self.centroids, np.float32)
+            self.dev.check(self._lib.vsk_ivf_build(self.dev._h, _ptr(c), self.numberOfCentroids, _ptr(r), n, d,
+                                                   C.byref(h)))
+        self._h = h
+
+    def assignments(self):
+        out = np.empty(self.count, np.int32)
+        self.dev.check(self._lib.vsk_ivf_assignments(self._h, _ptr(out)))
+        return out
+
+    def batchSearch(self, queries, k: int, strategy: SearchStrategy = SearchStrategy.adaptive):
+        if not self.trained or not self._h:
+            raise NotTrained("Index must be trained before use")
+        nprobe = self.numberOfCentroids if strategy == SearchStrategy.exact else self.numberOfProbes
+        nq = queries.shape[0]
+        if _is_dev(queries):
+            q = queries.contiguous().float()
+            od = torch.empty((nq, k), dtype=torch.float32, device=q.device)
+            oi = torch.empty((nq, k), dtype=torch.int64, device=q.device)
+            self.dev.check(self._lib.vsk_ivf_search_dev(self._h, _ptr(q), nq, k, nprobe, _ptr(od), _ptr(oi)))
+            return od, oi
+        q = _host(queries, np.float32)
+        od = np.empty((nq, k), np.float32)
+        oi = np.empty((nq, k), np.int64)
+        self.dev.check(self._lib.vsk_ivf_search(self._h, _ptr(q), nq, k, nprobe, _ptr(od), _ptr(oi)))
+        return od, oi
+
+    def search(self, query, k: int, strategy: SearchStrategy = SearchStrategy.adaptive):
+        d, i = self.batchSearch(query.reshape(1, -1), k, strategy)
+        return d[0], i[0]
+
+
+class ScalarQuantizer:
+    """``ScalarQuantizer`` for ``.int8`` (``Quantization/ScalarQuantizer.swift``).  ``per_dim=False``
+    is the reference's behaviour (one scale/offset for the whole batch)."""
+
+    def __init__(self, dev: CUDAComputeDevice, per_dim: bool = False):
+        self.dev = dev
+        self._lib = dev._lib
+        self.per_dim = per_dim
+        self.scale = None
+        self.offset = None
+
+    def train(self, vectors):
+        n, d = vectors.shape
+        mode = 1 if self.per_dim else 0
+        if _is_dev(vectors):
+            x = vectors.contiguous().float()
+            mn = torch.empty(d, dtype=torch.float32, device=x.device)
+            mx = torch.empty_like(mn)
+            self.dev.check(self._lib.vsk_sq8_minmax_dev(self.dev._h, _ptr(x), n, d, _ptr(mn), _ptr(mx)))
+            return self.set_range(mn, mx)
+        x = _host(vectors, np.float32)
+        self.scale = np.empty(d, np.float32)
+        self.offset = np.empty(d, np.float32)
+        self.dev.check(self._lib.vsk_sq8_train(self.dev._h, _ptr(x), n, d, mode, _ptr(self.scale), _ptr(self.offset)))
+        return self.scale, self.offset
+
+    def minmax(self, vectors):
+        """Per-dimension min/max of CUDA rows (to be reduced across shards by the caller)."""
+        x = vectors.contiguous().float()
+        mn = torch.empty(x.shape[1], dtype=torch.float32, device=x.device)
+        mx = torch.empty_like(mn)
+        self.dev.check(self._lib.vsk_sq8_minmax_dev(self.dev._h, _ptr(x), x.shape[0], x.shape[1], _ptr(mn), _ptr(mx)))
+        return mn, mx
+
+    def set_range(self, mn, mx):
+        d = mn.shape[0]
+        self.scale = torch.empty(d, dtype=torch.float32, device=mn.device)
+        self.offset = torch.empty_like(self.scale)
+        self.dev.check(self._lib.vsk_sq8_params_dev(self.dev._h, _ptr(mn.contiguous()), _ptr(mx.contiguous()), d,
+                                                    1 if self.per_dim else 0, _ptr(self.scale), _ptr(self.offset)))
+        return self.scale, self.offset
+
+    def quantizeBatch(self, vectors):
+        n, d = vectors.shape
+        if _is_dev(vectors):
+            x = vectors.contiguous().float()
+            codes = torch.empty((n, d), dtype=torch.int8, device=x.device)
+            s = self.scale if _is_dev(self.scale) else torch.as_tensor(self.scale, device=x.device)
+            o = self.offset if _is_dev(self.offset) else torch.as_tensor(self.offset, device=x.device)
+            self.dev.check(self._lib.vsk_sq8_encode_dev(self.dev._h, _ptr(x), n, d, _ptr(s), _ptr(o), _ptr(codes)))
+            return codes
+        x = _host(vectors, np.float32)
+        codes = np.empty((n, d), np.int8)
+        self.dev.check(self._lib.vsk_sq8_encode(self.dev._h, _ptr(x), n, d, _ptr(_host(self.scale, np.float32)),
+                                                _ptr(_host(self.offset, np.float32)), _ptr(codes)))
+        return codes
+
+    def dequantizeBatch(self, codes):
+        codes = _host(codes, np.int8)
+        out = np.empty(codes.shape, np.float32)
+        self.dev.check(self._lib.vsk_sq8_decode(self.dev._h, _ptr(codes), codes.shape[0], codes.shape[1],
+                                                _ptr(_host(self.scale, np.float32)),
+                                                _ptr(_host(self.offset, np.float32)), _ptr(out)))
+        return out
+
+
+class QuantizedFlatIndex(_IndexBase):
+    """Flat index over int8 codes; distances are taken against the dequantised rows."""
+
+    def __init__(self, dev: CUDAComputeDevice, dimensions: int, metric, scale, offset):
+        super().__init__(dev)
+        h = C.c_void_p()
+        s = scale.contiguous() if _is_dev(scale) else _host(scale, np.float32)
+        o = offset.contiguous() if _is_dev(offset) else _host(offset, np.float32)
+        dev.check(self._lib.vsk_sq8_index_create(dev._h, _metric_id(metric), int(dimensions), _ptr(s), _ptr(o),
+                                                 C.byref(h)))
+        self._h = h
+        self.dimensions = int(dimensions)
+
+    def add(self, codes):
+        if _is_dev(codes):
+            c = codes.contiguous()
+            self.dev.check(self._lib.vsk_sq8_index_add_dev(self._h, _ptr(c), c.shape[0]))
+        else:
+            c = _host(codes, np.int8)
+            self.dev.check(self._lib.vsk_sq8_index_add(self._h, _ptr(c), c.shape[0]))
+
+    def batchSearch(self, queries, k: int):
+        if queries.shape[1] != self.dimensions:
+            raise DimensionMismatch(f"expected {self.dimensions}, got {queries.shape[1]}")
+        return self._search(queries, int(k))
