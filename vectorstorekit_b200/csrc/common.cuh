@@ -208,6 +208,7 @@ struct SelectArgs {
   int64_t id_base;
   const int32_t* q_subset;  // or null; lists are indexed by position, outputs by q_subset[pos]
   int final_sqrt;           // 1: stored value is a squared L2 distance
+  const float* cert_eps;    // non-null: last compaction of a coarse scan (see select.cu); uses k
 };
 int32_t launch_select(Ctx* ctx, const SelectArgs& a);
 int32_t launch_merge_topk(Ctx* ctx, const float* dist, const int64_t* ids, int32_t g, int64_t nq,

@@ -56,7 +56,26 @@ __global__ void __launch_bounds__(SEL_THREADS) select_kernel(SelectArgs a) {
   __syncthreads();
   const int valid = s_valid;
 
-  if (a.out_ids == nullptr) {
+  if (a.cert_eps != nullptr) {
+    // Last compaction of a coarse (bounded-error) scan.  Let c_k be the k-th smallest coarse value and
+    // eps the query's error bound: a row of the true top-k has coarse value <= c_k + 2 eps, so those
+    // rows are kept for the exact re-scoring.  The list is complete only below the threshold t that
+    // filtered the scan, so the result can be certified only if c_k + 2 eps < t.
+    int kept = valid;
+    if (valid >= a.k) {
+      const float bound = ordered_to_float((uint32_t)(s[a.k - 1] >> 32)) + 2.0f * a.cert_eps[q];
+      // first index whose value exceeds the bound (the list is sorted)
+      int lo = a.k, hi = valid;
+      while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (ordered_to_float((uint32_t)(s[mid] >> 32)) <= bound) lo = mid + 1; else hi = mid;
+      }
+      kept = lo;
+      if (threadIdx.x == 0 && !(bound < a.cand.thr[q])) atomicOr(&a.cand.flags[q], 2);
+    }
+    for (int i = threadIdx.x; i < kept; i += blockDim.x) keys[i] = s[i];
+    if (threadIdx.x == 0) a.cand.count[q] = kept;
+  } else if (a.out_ids == nullptr) {
     const int kept = min(a.keep, valid);
     for (int i = threadIdx.x; i < kept; i += blockDim.x) keys[i] = s[i];
     if (threadIdx.x == 0) {

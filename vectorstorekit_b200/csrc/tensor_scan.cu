@@ -1,0 +1,778 @@
+// Tensor-core search path for euclidean, cosine and dot-product over a flat fp32 index.
+//
+//   coarse   queries x rows contraction on the 5th-generation tensor cores (tcgen05.mma, fp16
+//            operands, fp32 accumulators in tensor memory), operands staged by TMA into
+//            128-byte-swizzled shared-memory tiles.  The epilogue turns each accumulator into a
+//            coarse distance and appends only the rows at or below the query's running threshold
+//            to that query's candidate list: the query x row matrix never reaches HBM.
+//   bound    every operand is the fp16 rounding of a power-of-two scaled fp32 value, and the
+//            rounding residuals are measured when the operands are made, so |coarse - exact| <= eps
+//            holds with eps computed per query from measured norms (see prep kernels).
+//   rerank   the few candidates per query that can still be in the true top-k are re-scored with
+//            the reference's direct fp32 formulas (AccelerateOptimizer.swift:251-383) and sorted.
+//   proof    a query's result is accepted only if  c_k + 2 eps < t,  where c_k is the k-th smallest
+//            coarse value kept and t the threshold below which no row was ever dropped; then every
+//            true top-k row is among the re-scored candidates.  Otherwise the query is re-run on
+//            the fp32 scan.
+//
+// Kernel structure (one CTA per SM, persistent over 128-query x 256-row tiles, query tile fastest
+// so that concurrently running CTAs share the same rows in L2):
+//   warp 0      TMA producer: 4-stage ring of {128 x 64 query, 256 x 64 row} fp16 tiles
+//   warp 1      tensor-memory allocation; one lane issues tcgen05.mma (M128 N256 K16 x 4 per stage)
+//   warps 2..5  epilogue: tcgen05.ld of the thread's accumulator row (one query per thread),
+//               threshold filter, candidate append; double-buffered accumulators (2 x 256 columns)
+// Every mbarrier wait is bounded: on expiry the kernel raises an error word, stops issuing work,
+// drains its copies and frees tensor memory, and the host call returns VSK_ERR_TIMEOUT.
+#include <cuda.h>
+#include <math_constants.h>
+
+#include "common.cuh"
+#include "tensor_scan.cuh"
+
+namespace vsk {
+namespace {
+
+constexpr int TM = 128;        // queries per tile (UMMA M)
+constexpr int TN = 256;        // rows per tile (UMMA N)
+constexpr int TK = 64;         // fp16 elements per k-block (128 bytes: one swizzle atom)
+constexpr int STAGES = 4;
+constexpr int A_BYTES = TM * TK * 2;   // 16 KB
+constexpr int B_BYTES = TN * TK * 2;   // 32 KB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int TC_THREADS = 192;
+constexpr uint32_t WAIT_LIMIT = 1u << 23;
+constexpr int TMEM_COLS = 512;
+
+struct TcSmem {
+  // stage buffers first: each must start on a 1024-byte boundary for the 128B swizzle
+  uint8_t stage[STAGES][STAGE_BYTES];
+  float beta[2][4][TN];   // per accumulator buffer and epilogue warp: the tile's per-row terms
+  uint64_t full[STAGES];
+  uint64_t empty[STAGES];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint64_t drain;
+  uint32_t tmem_base;
+  volatile int abort_flag;
+};
+constexpr size_t TC_SMEM_BYTES = sizeof(TcSmem) + 1024;  // + alignment slack
+
+struct TcArgs {
+  int64_t nq;                 // queries (list positions)
+  int64_t row_begin, row_end; // rows of this launch
+  int32_t kblocks;            // dim16 / 64
+  int mode;                   // SCAN_DENSE or SCAN_THRESHOLD
+  const float* alpha;         // device scalar: value = alpha * acc + beta[row]
+  const float* beta;          // [n] or null (treated as 0)
+  CandLists cand;
+  int32_t* err;               // device error word
+};
+
+// ---- PTX wrappers --------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false (and raises the abort flag and the error word) when the limit runs out
+// or another role has already aborted.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, TcSmem* sm, int32_t* err, int code) {
+  for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (it > 64) {
+      if ((it & 63) == 0 && sm->abort_flag) return false;
+      __nanosleep(64);
+    }
+  }
+  sm->abort_flag = 1;
+  atomicCAS(err, 0, code);
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int32_t c0, int32_t c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+          smem_u32(dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// D[tmem] (+)= A[smem desc] * B[smem desc]; M = 128, N = 256, K = 16, fp16 x fp16 -> fp32
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// 32 consecutive fp32 columns of this thread's tensor-memory lane
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 fp16), 128-byte
+// swizzled, rows packed: 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3fff);  // start address, 16-byte units
+  d |= (uint64_t)1 << 16;                      // leading-dimension byte offset (unused with swizzle): 1
+  d |= (uint64_t)(1024 >> 4) << 32;            // stride between 8-row groups: 1024 bytes
+  d |= (uint64_t)1 << 46;                      // descriptor version of this architecture
+  d |= (uint64_t)2 << 61;                      // 128-byte swizzle
+  return d;
+}
+
+// Instruction descriptor: fp32 accumulate, fp16 A and B, both K-major, N = 256, M = 128.
+constexpr uint32_t kIdesc = (1u << 4) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(TM >> 4) << 24);
+
+template <int MODE, bool HAS_BETA>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_x, TcArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  TcSmem* sm = reinterpret_cast<TcSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  const int64_t qtiles = (a.nq + TM - 1) / TM;
+  const int64_t ntiles = (a.row_end - a.row_begin + TN - 1) / TN;
+  const int64_t tiles = qtiles * ntiles;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&sm->full[s], 1);
+      mbar_init(&sm->empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&sm->tmem_full[b], 1);
+      mbar_init(&sm->tmem_empty[b], 4);
+    }
+    mbar_init(&sm->drain, 1);
+    sm->abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm->tmem_base)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = sm->tmem_base;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      uint32_t issued = 0;       // bit s: a copy into stage s was issued ...
+      uint32_t issued_ph = 0;    // ... with this full-barrier parity
+      bool ok = true;
+      for (int64_t t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+        const int64_t nt = t / qtiles, qt = t - nt * qtiles;
+        const int32_t qrow = (int32_t)(qt * TM);
+        const int32_t xrow = (int32_t)(a.row_begin + nt * TN);
+        for (int kb = 0; kb < a.kblocks; ++kb) {
+          if (!mbar_wait(&sm->empty[s], ph ^ 1, sm, a.err, 1)) { ok = false; break; }
+          mbar_expect_tx(&sm->full[s], STAGE_BYTES);
+          tma_load_2d(&sm->stage[s][0], &map_q, &sm->full[s], kb * TK, qrow);
+          tma_load_2d(&sm->stage[s][A_BYTES], &map_x, &sm->full[s], kb * TK, xrow);
+          issued |= 1u << s;
+          issued_ph = (issued_ph & ~(1u << s)) | (ph << s);
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
+      }
+      // copies still in flight must land before the CTA's shared memory is released
+      for (int i = 0; i < STAGES; ++i)
+        if (issued & (1u << i)) {
+          for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
+            if (mbar_try_wait(&sm->full[i], (issued_ph >> i) & 1)) break;
+            __nanosleep(64);
+          }
+        }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      int64_t local = 0;
+      bool ok = true;
+      for (int64_t t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++local) {
+        const int acc = (int)(local & 1);
+        const uint32_t aph = (uint32_t)((local >> 1) & 1);
+        if (!mbar_wait(&sm->tmem_empty[acc], aph ^ 1, sm, a.err, 2)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + (uint32_t)(acc * TN);
+        for (int kb = 0; kb < a.kblocks; ++kb) {
+          if (!mbar_wait(&sm->full[s], ph, sm, a.err, 3)) { ok = false; break; }
+          tc_fence_after();
+          const uint64_t adesc = make_desc(smem_u32(&sm->stage[s][0]));
+          const uint64_t bdesc = make_desc(smem_u32(&sm->stage[s][A_BYTES]));
+#pragma unroll
+          for (int k4 = 0; k4 < TK / 16; ++k4) {
+            // 16 fp16 = 32 bytes further along K inside the swizzle atom: +2 in 16-byte units
+            tc_mma(tmem_d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), kIdesc, (kb | k4) ? 1u : 0u);
+          }
+          tc_commit(&sm->empty[s]);  // stage is free once these MMAs have read it
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
+        if (ok) tc_commit(&sm->tmem_full[acc]);
+      }
+      // all issued MMAs must retire before tensor memory is freed
+      tc_commit(&sm->drain);
+      for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
+        if (mbar_try_wait(&sm->drain, 0)) break;
+        __nanosleep(64);
+      }
+    }
+  } else {
+    // ---------------- epilogue: one query per thread ----------------
+    const int quarter = warp & 3;                 // tensor-memory lanes this warp may read
+    const int et = quarter * 32 + lane;           // row of the tile owned by this thread
+    const float alpha = __ldg(a.alpha);
+    int64_t local = 0;
+    bool ok = true;
+    for (int64_t t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++local) {
+      const int acc = (int)(local & 1);
+      const uint32_t aph = (uint32_t)((local >> 1) & 1);
+      const int64_t nt = t / qtiles, qt = t - nt * qtiles;
+      const int64_t q = qt * TM + et;
+      const int64_t n0 = a.row_begin + nt * TN;
+      const bool qok = q < a.nq;
+      if (HAS_BETA) {
+        // the tile's per-row terms; each warp stages its own copy, so no CTA-wide barrier is needed
+        for (int i = lane; i < TN; i += 32) sm->beta[acc][quarter][i] = (n0 + i < a.row_end) ? __ldg(a.beta + n0 + i) : 0.f;
+        __syncwarp();
+      }
+      float thr = CUDART_INF_F;
+      if (MODE == SCAN_THRESHOLD && qok) thr = a.cand.thr[q];
+      // every lane of the warp must take part in the wait result
+      bool got = mbar_wait(&sm->tmem_full[acc], aph, sm, a.err, 4);
+      got = __all_sync(0xffffffffu, got);
+      if (!got) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t trow = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * TN);
+#pragma unroll 1
+      for (int c = 0; c < TN / 32; ++c) {
+        float v[32];
+        tc_ld32(trow + (uint32_t)(c * 32), v);
+        const int64_t nc = n0 + c * 32;
+        float vmin = CUDART_INF_F;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          v[j] = HAS_BETA ? fmaf(v[j], alpha, sm->beta[acc][quarter][c * 32 + j]) : v[j] * alpha;
+          vmin = fminf(vmin, v[j]);
+        }
+        if (!qok) continue;
+        if (MODE == SCAN_DENSE) {
+          uint64_t* dst = a.cand.keys + q * kCandCap + (nc - a.row_begin);
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (nc + j < a.row_end) dst[j] = make_key(v[j], (uint32_t)(nc + j));
+        } else if (vmin <= thr) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if (v[j] <= thr && nc + j < a.row_end) {
+              const int pos = atomicAdd(&a.cand.count[q], 1);
+              if (pos < kCandCap) a.cand.keys[q * kCandCap + pos] = make_key(v[j], (uint32_t)(nc + j));
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sm->tmem_empty[acc]);
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// ---- operand preparation --------------------------------------------------------------------
+// Statistics accumulated with atomics on order-preserving integer images of non-negative floats.
+struct PrepStats {
+  unsigned absmax;      // max |x_i|
+  unsigned max_norm16;  // max over rows of |x'| (operand units)
+  unsigned max_err16;   // max over rows of |s*x - x'|
+  unsigned max_norm;    // max |x|
+  unsigned min_norm_nz; // min nonzero |x| (initialised to +inf)
+};
+
+__global__ void absmax_kernel(const float* __restrict__ x, int64_t total, unsigned* out) {
+  float m = 0.f;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x)
+    m = fmaxf(m, fabsf(__ldg(x + i)));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if ((threadIdx.x & 31) == 0) atomicMax(out, __float_as_uint(m));  // non-negative floats order as uints
+}
+
+// scale = 2^e with 2^13 < absmax * scale <= 2^14 (1 when absmax is 0 or not finite); cosine: 2^14
+__global__ void choose_scale_kernel(const unsigned* absmax, int cosine, float* scale) {
+  float s = 16384.f;
+  if (!cosine) {
+    const float m = __uint_as_float(*absmax);
+    s = 1.f;
+    if (m > 0.f && m < CUDART_INF_F) {
+      int e;
+      frexpf(m, &e);               // m = f * 2^e, f in [0.5, 1)
+      s = ldexpf(1.f, 14 - e);
+    }
+  }
+  *scale = s;
+}
+
+// One warp per row: fp32 row -> fp16 operand row x' = fp16(s * x) (cosine: s * x/|x|), padded with
+// zeros to dim16, and the measured quantities the error bound needs.
+//   aux[row]   = |x|^2 (euclidean), unused otherwise
+//   nrm16[row] = |x'|, err16[row] = |s*x^ - x'|   (optional per-row outputs, used for queries)
+template <int METRIC>
+__global__ void prep_rows_kernel(const float* __restrict__ x, int64_t n, int dim, int dim16, const float* scale_p,
+                                 __half* __restrict__ out, float* __restrict__ aux, float* __restrict__ nrm16,
+                                 float* __restrict__ err16, float* __restrict__ nrm, PrepStats* stats) {
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= n) return;
+  const int lane = threadIdx.x & 31;
+  const float s = *scale_p;
+  const float* p = x + row * dim;
+  float ss = 0.f;
+  for (int i = lane; i < dim; i += 32) {
+    const float v = __ldg(p + i);
+    ss = fmaf(v, v, ss);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  const float norm = sqrtf(ss);
+  const float inv = (METRIC == VSK_METRIC_COSINE) ? (norm > 0.f ? 1.0f / norm : 0.f) : 1.0f;
+  float n2 = 0.f, e2 = 0.f;
+  for (int i = lane; i < dim16; i += 32) {
+    float t = 0.f;
+    if (i < dim) t = (METRIC == VSK_METRIC_COSINE) ? (__ldg(p + i) * inv) * s : __ldg(p + i) * s;
+    const __half h = __float2half_rn(t);
+    out[row * dim16 + i] = h;
+    const float back = __half2float(h);
+    n2 = fmaf(back, back, n2);
+    const float e = t - back;
+    e2 = fmaf(e, e, e2);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    n2 += __shfl_xor_sync(0xffffffffu, n2, o);
+    e2 += __shfl_xor_sync(0xffffffffu, e2, o);
+  }
+  if (lane == 0) {
+    // round the measured norms up a little: they are used as upper bounds
+    const float up = 1.0f + 1e-5f;
+    const float a16 = sqrtf(n2) * up, r16 = sqrtf(e2) * up;
+    if (aux && METRIC == VSK_METRIC_EUCLIDEAN) aux[row] = ss;
+    if (nrm16) nrm16[row] = a16;
+    if (err16) err16[row] = r16;
+    if (nrm) nrm[row] = norm;
+    if (stats) {
+      atomicMax(&stats->max_norm16, __float_as_uint(a16));
+      atomicMax(&stats->max_err16, __float_as_uint(r16));
+      atomicMax(&stats->max_norm, __float_as_uint(norm));
+      if (norm > 0.f) atomicMin(&stats->min_norm_nz, __float_as_uint(norm));
+    }
+  }
+}
+
+struct BoundConsts {
+  float scale_x;       // s_x
+  float max_norm16;    // X' = max |x'|
+  float max_err16;     // E' = max |s_x x - x'|
+  float max_norm;      // max |x|
+  float min_norm_nz;   // min nonzero |x|
+  int dim16;
+};
+
+// eps[q]: |coarse - exact| <= eps for every row, in the units of the stored coarse value.
+//   contraction error (operand units) <= |q'| E' + |e_q| X' + |e_q| E'      (Cauchy-Schwarz on the residuals)
+//                                       + dim16 * 2^-22 * |q'| X'            (fp32 accumulation in the tensor core)
+//   divided by s_q s_x; doubled for euclidean (value = |x|^2 - 2 q.x) plus the fp32 rounding of |x|^2;
+//   cosine adds the effect of the reference's +1e-8 in the denominator and of normalising in fp32.
+// Also writes alpha = coefficient / (s_q s_x).
+template <int METRIC>
+__global__ void bound_kernel(const float* __restrict__ qn16, const float* __restrict__ qe16,
+                             const float* __restrict__ qnorm, int64_t nq, const float* scale_q, BoundConsts c,
+                             float* __restrict__ eps, float* alpha) {
+  const int64_t q = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const float inv = 1.0f / ((*scale_q) * c.scale_x);
+  if (q == 0) *alpha = (METRIC == VSK_METRIC_EUCLIDEAN ? -2.0f : -1.0f) * inv;
+  if (q >= nq) return;
+  const float a = qn16[q], e = qe16[q];
+  float dot_err = (a * c.max_err16 + e * c.max_norm16 + e * c.max_err16) + (float)c.dim16 * 2.3841858e-7f * a * c.max_norm16;
+  dot_err *= inv;
+  float r;
+  if (METRIC == VSK_METRIC_EUCLIDEAN) {
+    // + fp32 rounding of the stored |x|^2 (a sum of dim squares) and of the final multiply-add
+    const float qn = qnorm[q];
+    r = 2.0f * dot_err + 4.0f * 5.9604645e-8f * (float)c.dim16 * c.max_norm * c.max_norm +
+        2.0f * 5.9604645e-8f * (c.max_norm * c.max_norm + 2.0f * qn * c.max_norm);
+  } else if (METRIC == VSK_METRIC_COSINE) {
+    const float qn = qnorm[q];
+    const float den = qn * c.min_norm_nz;
+    r = dot_err + 1e-8f / (den + 1e-8f) + 4.0f * 5.9604645e-8f;
+    if (!(den > 0.f)) r = dot_err + 4.0f * 5.9604645e-8f;  // zero query (or no nonzero row): every value is exactly 0
+  } else {
+    r = dot_err;
+  }
+  eps[q] = r * 1.0001f + 1e-30f;
+}
+
+// ---- exact rerank -------------------------------------------------------------------------
+// One CTA per query: replaces every kept candidate's coarse value with the reference's direct fp32 value:
+//   euclidean sum (q-x)^2 (rooted at output), cosine 1 - q.x/(|q||x| + 1e-8), dotProduct -(q.x).
+template <int METRIC>
+__global__ void __launch_bounds__(256) rerank_kernel(const float* __restrict__ q, const float* __restrict__ x, int dim,
+                                                     const float* __restrict__ qnorm, const float* __restrict__ xnorm,
+                                                     CandLists cand, unsigned long long* total) {
+  extern __shared__ float qs[];
+  const int64_t qi = blockIdx.x;
+  const int cnt = min(cand.count[qi], kCandCap);
+  uint64_t* keys = cand.keys + qi * kCandCap;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) qs[i] = q[qi * dim + i];
+  if (threadIdx.x == 0) atomicAdd(total, (unsigned long long)cnt);
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  const float qn = (METRIC == VSK_METRIC_COSINE) ? qnorm[qi] : 0.f;
+  for (int c = warp; c < cnt; c += nwarps) {
+    const uint32_t id = (uint32_t)keys[c];
+    const float* xr = x + (int64_t)id * dim;
+    float s = 0.f;
+    for (int i = lane; i < dim; i += 32) {
+      const float xv = __ldg(xr + i), qv = qs[i];
+      if (METRIC == VSK_METRIC_EUCLIDEAN) {
+        const float d = qv - xv;
+        s = fmaf(d, d, s);
+      } else {
+        s = fmaf(qv, xv, s);
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) {
+      float v;
+      if (METRIC == VSK_METRIC_COSINE) v = 1.0f - s / (qn * xnorm[id] + 1e-8f);
+      else if (METRIC == VSK_METRIC_DOT_PRODUCT) v = -s;
+      else v = s;
+      keys[c] = make_key(v, id);
+    }
+  }
+}
+
+// ---- host side ------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) == cudaSuccess &&
+        qr == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// fp16 matrix [rows][dim16] row-major; box = 64 columns x box_rows, 128-byte swizzle, zero fill
+int32_t make_map(Ctx* ctx, const __half* base, int64_t rows, int32_t dim16, int box_rows, CUtensorMap* map) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(ctx, VSK_ERR_EXECUTION_FAILED, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t gdim[2] = {(cuuint64_t)dim16, (cuuint64_t)rows};
+  cuuint64_t gstride[1] = {(cuuint64_t)dim16 * 2};
+  cuuint32_t box[2] = {(cuuint32_t)TK, (cuuint32_t)box_rows};
+  cuuint32_t estride[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(base), gdim, gstride, box, estride,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(ctx, VSK_ERR_EXECUTION_FAILED, "cuTensorMapEncodeTiled failed with %d", (int)r);
+  return VSK_OK;
+}
+
+template <int METRIC>
+void launch_prep(Ctx* ctx, const float* x, int64_t n, int dim, int dim16, const float* scale, __half* out, float* aux,
+                 float* nrm16, float* err16, float* nrm, PrepStats* stats) {
+  prep_rows_kernel<METRIC><<<(unsigned)ceil_div(n, 8), 256, 0, ctx->stream>>>(x, n, dim, dim16, scale, out, aux, nrm16,
+                                                                               err16, nrm, stats);
+  ctx->stats.kernel_launches++;
+}
+
+// fp16 operand copy of the index rows + the constants of the error bound (once per index state)
+int32_t tensor_prepare(Index* ix) {
+  Ctx* ctx = ix->ctx;
+  if (ix->n16 == ix->n && ix->rows16) return VSK_OK;
+  dev_free(ix->rows16);
+  dev_free(ix->row_aux);
+  ix->rows16 = nullptr;
+  ix->row_aux = nullptr;
+  ix->dim16 = (int32_t)(ceil_div(ix->dim, TK) * TK);
+  VSK_TRY(dev_alloc(ctx, (void**)&ix->rows16, (size_t)ix->n * ix->dim16 * sizeof(__half)));
+  VSK_TRY(dev_alloc(ctx, (void**)&ix->row_aux, (size_t)ix->n * sizeof(float)));
+  void* p;
+  VSK_TRY(scratch(ctx, SLOT_TC_A, sizeof(PrepStats) + 16, &p));
+  PrepStats* st = (PrepStats*)p;
+  float* scale = (float*)((char*)p + sizeof(PrepStats));
+  PrepStats init{0u, 0u, 0u, 0u, 0x7f800000u};
+  VSK_CUDA(ctx, cudaMemcpyAsync(st, &init, sizeof(init), cudaMemcpyHostToDevice, ctx->stream));
+  const bool cosine = ix->metric == VSK_METRIC_COSINE;
+  if (!cosine) {
+    absmax_kernel<<<1184, 256, 0, ctx->stream>>>(ix->rows, ix->n * (int64_t)ix->dim, &st->absmax);
+    ctx->stats.kernel_launches++;
+  }
+  choose_scale_kernel<<<1, 1, 0, ctx->stream>>>(&st->absmax, cosine ? 1 : 0, scale);
+  ctx->stats.kernel_launches++;
+  switch (ix->metric) {
+    case VSK_METRIC_EUCLIDEAN:
+      launch_prep<VSK_METRIC_EUCLIDEAN>(ctx, ix->rows, ix->n, ix->dim, ix->dim16, scale, ix->rows16, ix->row_aux, nullptr, nullptr, nullptr, st);
+      break;
+    case VSK_METRIC_COSINE:
+      launch_prep<VSK_METRIC_COSINE>(ctx, ix->rows, ix->n, ix->dim, ix->dim16, scale, ix->rows16, ix->row_aux, nullptr, nullptr, nullptr, st);
+      break;
+    default:
+      launch_prep<VSK_METRIC_DOT_PRODUCT>(ctx, ix->rows, ix->n, ix->dim, ix->dim16, scale, ix->rows16, ix->row_aux, nullptr, nullptr, nullptr, st);
+      break;
+  }
+  VSK_CUDA(ctx, cudaGetLastError());
+  PrepStats h;
+  float hs;
+  VSK_CUDA(ctx, cudaMemcpyAsync(&h, st, sizeof(h), cudaMemcpyDeviceToHost, ctx->stream));
+  VSK_CUDA(ctx, cudaMemcpyAsync(&hs, scale, 4, cudaMemcpyDeviceToHost, ctx->stream));
+  VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  auto f = [](unsigned u) { float v; memcpy(&v, &u, 4); return v; };
+  ix->scale16 = hs;
+  ix->max_xnorm16 = f(h.max_norm16);
+  ix->max_xerr16 = f(h.max_err16);
+  ix->max_xnorm = f(h.max_norm);
+  ix->min_xnorm_nz = h.min_norm_nz == 0x7f800000u ? 0.f : f(h.min_norm_nz);
+  ix->n16 = ix->n;
+  return VSK_OK;
+}
+
+template <int MODE>
+int32_t launch_tc(Ctx* ctx, const CUtensorMap& mq, const CUtensorMap& mx, const TcArgs& a, bool has_beta) {
+  static bool attr_done[2][2] = {};
+  auto kern = has_beta ? tc_scan_kernel<MODE, true> : tc_scan_kernel<MODE, false>;
+  if (!attr_done[MODE][has_beta]) {
+    VSK_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_BYTES));
+    attr_done[MODE][has_beta] = true;
+  }
+  const int64_t tiles = ceil_div(a.nq, TM) * ceil_div(a.row_end - a.row_begin, TN);
+  if (tiles <= 0) return VSK_OK;
+  const unsigned grid = (unsigned)std::min<int64_t>(tiles, ctx->prop.multiProcessorCount);
+  prof_begin(ctx);
+  kern<<<grid, TC_THREADS, TC_SMEM_BYTES, ctx->stream>>>(mq, mx, a);
+  prof_end(ctx);
+  ctx->stats.kernel_launches++;
+  ctx->stats.tensor_tiles += tiles;
+  VSK_CUDA(ctx, cudaGetLastError());
+  return VSK_OK;
+}
+
+}  // namespace
+
+void tensor_invalidate(Index* ix) { ix->n16 = -1; }
+
+int32_t tensor_search(Index* ix, const float* q, int64_t nq, int32_t k, const float* qnorm, float* out_dist,
+                      int64_t* out_ids) {
+  Ctx* ctx = ix->ctx;
+  VSK_TRY(tensor_prepare(ix));
+  const int metric = ix->metric;
+  const int dim = ix->dim, dim16 = ix->dim16;
+  const int32_t keep = std::min<int32_t>(kCandCap / 2, k + std::max(8, k / 8));
+
+  // ---- query operands, bound, alpha ----
+  void* p;
+  VSK_TRY(scratch(ctx, SLOT_Q16, (size_t)nq * dim16 * sizeof(__half), &p));
+  __half* q16 = (__half*)p;
+  VSK_TRY(scratch(ctx, SLOT_QAUX, (size_t)nq * 4 * sizeof(float) + 64, &p));
+  float* qn16 = (float*)p;
+  float* qe16 = qn16 + nq;
+  float* eps = qe16 + nq;
+  float* qn_tmp = eps + nq;
+  VSK_TRY(scratch(ctx, SLOT_TC_B, 64, &p));
+  unsigned* q_absmax = (unsigned*)p;
+  float* q_scale = (float*)p + 1;
+  float* alpha = (float*)p + 2;
+  int32_t* err = (int32_t*)p + 3;
+  unsigned long long* rr_total = (unsigned long long*)((char*)p + 16);
+  VSK_CUDA(ctx, cudaMemsetAsync(p, 0, 64, ctx->stream));
+  const bool cosine = metric == VSK_METRIC_COSINE;
+  if (!cosine) {
+    absmax_kernel<<<296, 256, 0, ctx->stream>>>(q, nq * (int64_t)dim, q_absmax);
+    ctx->stats.kernel_launches++;
+  }
+  choose_scale_kernel<<<1, 1, 0, ctx->stream>>>(q_absmax, cosine ? 1 : 0, q_scale);
+  ctx->stats.kernel_launches++;
+  BoundConsts bc{ix->scale16, ix->max_xnorm16, ix->max_xerr16, ix->max_xnorm, ix->min_xnorm_nz, dim16};
+  const unsigned bgrid = (unsigned)ceil_div(nq, 256);
+  switch (metric) {
+    case VSK_METRIC_EUCLIDEAN:
+      launch_prep<VSK_METRIC_EUCLIDEAN>(ctx, q, nq, dim, dim16, q_scale, q16, nullptr, qn16, qe16, qn_tmp, nullptr);
+      bound_kernel<VSK_METRIC_EUCLIDEAN><<<bgrid, 256, 0, ctx->stream>>>(qn16, qe16, qn_tmp, nq, q_scale, bc, eps, alpha);
+      break;
+    case VSK_METRIC_COSINE:
+      launch_prep<VSK_METRIC_COSINE>(ctx, q, nq, dim, dim16, q_scale, q16, nullptr, qn16, qe16, qn_tmp, nullptr);
+      bound_kernel<VSK_METRIC_COSINE><<<bgrid, 256, 0, ctx->stream>>>(qn16, qe16, qn_tmp, nq, q_scale, bc, eps, alpha);
+      break;
+    default:
+      launch_prep<VSK_METRIC_DOT_PRODUCT>(ctx, q, nq, dim, dim16, q_scale, q16, nullptr, qn16, qe16, qn_tmp, nullptr);
+      bound_kernel<VSK_METRIC_DOT_PRODUCT><<<bgrid, 256, 0, ctx->stream>>>(qn16, qe16, qn_tmp, nq, q_scale, bc, eps, alpha);
+      break;
+  }
+  ctx->stats.kernel_launches++;
+  VSK_CUDA(ctx, cudaGetLastError());
+
+  CUtensorMap mq, mx;
+  VSK_TRY(make_map(ctx, q16, nq, dim16, TM, &mq));
+  VSK_TRY(make_map(ctx, ix->rows16, ix->n, dim16, TN, &mx));
+
+  // ---- candidate lists and the chunk schedule ----
+  CandLists cand;
+  VSK_TRY(scratch(ctx, SLOT_CAND_KEYS, (size_t)nq * kCandCap * sizeof(uint64_t), &p));
+  cand.keys = (uint64_t*)p;
+  VSK_TRY(scratch(ctx, SLOT_CAND_COUNT, (size_t)nq * 4, &p));
+  cand.count = (int32_t*)p;
+  VSK_TRY(scratch(ctx, SLOT_CAND_THR, (size_t)nq * 4, &p));
+  cand.thr = (float*)p;
+  VSK_TRY(scratch(ctx, SLOT_CAND_FLAGS, (size_t)nq * 4, &p));
+  cand.flags = (int32_t*)p;
+  cand.nq = nq;
+  VSK_TRY(launch_init_cand(ctx, cand, nq));
+
+  TcArgs a{};
+  a.nq = nq;
+  a.kblocks = dim16 / TK;
+  a.alpha = alpha;
+  a.beta = metric == VSK_METRIC_EUCLIDEAN ? ix->row_aux : nullptr;
+  a.cand = cand;
+  a.err = err;
+  const bool has_beta = a.beta != nullptr;
+  SelectArgs sel{};
+  sel.cand = cand;
+  sel.nq = nq;
+  sel.keep = keep;
+  const int64_t n = ix->n;
+  const int64_t room = kCandCap - keep;
+  int64_t seen = std::min<int64_t>(n, kCandCap);
+  a.mode = SCAN_DENSE;
+  a.row_begin = 0;
+  a.row_end = seen;
+  VSK_TRY(launch_tc<SCAN_DENSE>(ctx, mq, mx, a, has_beta));
+  sel.dense_count = (int32_t)seen;
+  sel.k = k;
+  // the compaction after the last chunk keeps what the exact re-scoring needs and certifies the query
+  if (seen == n) sel.cert_eps = eps;
+  VSK_TRY(launch_select(ctx, sel));
+  sel.dense_count = -1;
+  a.mode = SCAN_THRESHOLD;
+  while (seen < n) {
+    int64_t chunk = std::max<int64_t>(room, seen * room / (2 * (int64_t)keep));
+    chunk = std::max<int64_t>(TN, chunk / TN * TN);   // whole row tiles
+    chunk = std::min(chunk, n - seen);
+    a.row_begin = seen;
+    a.row_end = seen + chunk;
+    VSK_TRY(launch_tc<SCAN_THRESHOLD>(ctx, mq, mx, a, has_beta));
+    seen += chunk;
+    if (seen == n) sel.cert_eps = eps;
+    VSK_TRY(launch_select(ctx, sel));
+  }
+
+  // ---- certificate + exact rerank + final order ----
+  const size_t qsm = (size_t)dim * sizeof(float);
+  if (qsm > 200 * 1024) return fail(ctx, VSK_ERR_INVALID_BUFFER_SIZE, "dimension %d is too large for the rerank kernel", dim);
+#define VSK_RERANK(M_)                                                                                          \
+  do {                                                                                                          \
+    if (qsm > 48 * 1024)                                                                                        \
+      VSK_CUDA(ctx, cudaFuncSetAttribute(rerank_kernel<M_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)qsm)); \
+    rerank_kernel<M_><<<(unsigned)nq, 256, qsm, ctx->stream>>>(q, ix->rows, dim, qnorm, ix->row_norm, cand, rr_total); \
+  } while (0)
+  switch (metric) {
+    case VSK_METRIC_EUCLIDEAN: VSK_RERANK(VSK_METRIC_EUCLIDEAN); break;
+    case VSK_METRIC_COSINE: VSK_RERANK(VSK_METRIC_COSINE); break;
+    default: VSK_RERANK(VSK_METRIC_DOT_PRODUCT); break;
+  }
+#undef VSK_RERANK
+  ctx->stats.kernel_launches++;
+  VSK_CUDA(ctx, cudaGetLastError());
+  SelectArgs fin{};
+  fin.cand = cand;
+  fin.nq = nq;
+  fin.dense_count = -1;
+  fin.keep = k;
+  fin.out_dist = out_dist;
+  fin.out_ids = out_ids;
+  fin.k = k;
+  fin.metric = metric;
+  fin.id_base = ix->id_base;
+  fin.final_sqrt = metric == VSK_METRIC_EUCLIDEAN;
+  VSK_TRY(launch_select(ctx, fin));
+
+  // ---- flags: bounded-wait expiry, overflowed lists, failed certificates ----
+  std::vector<int32_t> flags((size_t)nq);
+  int32_t herr = 0;
+  VSK_CUDA(ctx, cudaMemcpyAsync(flags.data(), cand.flags, nq * 4, cudaMemcpyDeviceToHost, ctx->stream));
+  VSK_CUDA(ctx, cudaMemcpyAsync(&herr, err, 4, cudaMemcpyDeviceToHost, ctx->stream));
+  unsigned long long hrr = 0;
+  VSK_CUDA(ctx, cudaMemcpyAsync(&hrr, rr_total, 8, cudaMemcpyDeviceToHost, ctx->stream));
+  VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  ctx->stats.reranked_rows += (int64_t)hrr;
+  if (herr != 0)
+    return fail(ctx, VSK_ERR_TIMEOUT, "tensor-core scan: a bounded pipeline wait ran out (role %d)", herr);
+  std::vector<int32_t> bad;
+  for (int64_t i = 0; i < nq; ++i)
+    if (flags[i]) bad.push_back((int32_t)i);
+  if (!bad.empty()) VSK_TRY(fp32_search_subset(ix, q, bad, k, qnorm, out_dist, out_ids));
+  return VSK_OK;
+}
+
+}  // namespace vsk
