@@ -1,7 +1,9 @@
-// Per-query selection over the candidate lists: one CTA per query sorts the list's 64-bit
-// (value, row) keys in shared memory (bitonic network, at most 4096 keys = 32 KB), then either
-// compacts the list to its best `keep` keys and tightens the query's threshold, or writes the
-// final ascending top-k.  Replaces the reference's CPU-side `sorted().prefix(k)` per query
+// Per-query selection over the candidate lists, one CTA per query.
+//   compaction  the list's 64-bit (value, row) keys are held in registers (8 per thread); a block-wide
+//               radix select finds the key of rank `keep`, every key at or below it is written back
+//               (unordered) and its value becomes the query's threshold
+//   final       the short list left by the last compaction is sorted in shared memory (bitonic
+//               network) and written out as the ascending top-k  Replaces the reference's CPU-side `sorted().prefix(k)` per query
 // (Acceleration/MetalAccelerationEngine.swift:465-471).
 #include <math_constants.h>
 
@@ -33,57 +35,83 @@ __device__ __forceinline__ int next_pow2(int c) {
   return p;
 }
 
+constexpr int SEL_ITEMS = kCandCap / SEL_THREADS;  // keys per thread, held in registers
+
+// Block-wide radix select over the 64-bit keys each thread holds: returns the key of rank `rank`
+// (1-based, ascending).  One pass per byte from the top; a pass histograms the byte among the keys that
+// still match the decided prefix.  After the four value bytes, if the rest of the rank is made up of ALL
+// keys with exactly that value, the id bytes need not be resolved and the pivot is (value, max id).
+__device__ __forceinline__ uint64_t block_radix_select(const uint64_t (&key)[SEL_ITEMS], int rank, int* hist,
+                                                       int* s_bin, int* s_less, int* s_in_bin) {
+  uint64_t prefix = 0, mask = 0;
+  for (int shift = 56; shift >= 0; shift -= 8) {
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0;
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < SEL_ITEMS; ++i)
+      if ((key[i] & mask) == prefix) atomicAdd(&hist[(int)((key[i] >> shift) & 255)], 1);
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      // lane l owns bins 8l .. 8l+7
+      int local[8], sum = 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { local[j] = hist[threadIdx.x * 8 + j]; sum += local[j]; }
+      int incl = sum;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, incl, o);
+        if ((int)threadIdx.x >= o) incl += t;
+      }
+      int before = incl - sum;
+      if (before < rank && rank <= incl) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (before < rank && rank <= before + local[j]) {
+            *s_bin = threadIdx.x * 8 + j;
+            *s_less = before;
+            *s_in_bin = local[j];
+          }
+          before += local[j];
+        }
+      }
+    }
+    __syncthreads();
+    const int bin = *s_bin, less = *s_less, in_bin = *s_in_bin;
+    __syncthreads();
+    rank -= less;
+    prefix |= (uint64_t)bin << shift;
+    mask |= (uint64_t)255 << shift;
+    if (shift == 32 && in_bin == rank) return prefix | 0xffffffffull;  // every key with this value is taken
+  }
+  return prefix;
+}
+
 __global__ void __launch_bounds__(SEL_THREADS) select_kernel(SelectArgs a) {
   extern __shared__ __align__(16) uint64_t s[];
-  __shared__ int s_valid;
+  __shared__ int hist[256];
+  __shared__ int s_valid, s_bin, s_less, s_in_bin, s_out;
   const int64_t q = blockIdx.x;
   uint64_t* keys = a.cand.keys + q * kCandCap;
   int c;
   if (a.dense_count >= 0) {
     c = a.dense_count;
   } else {
-    int raw = a.cand.count[q];
+    const int raw = a.cand.count[q];
     c = min(raw, kCandCap);
     if (raw > kCandCap && threadIdx.x == 0) atomicOr(&a.cand.flags[q], 1);
   }
-  const int P = next_pow2(c);
-  for (int i = threadIdx.x; i < P; i += blockDim.x) s[i] = i < c ? keys[i] : kEmptyKey;
-  if (threadIdx.x == 0) s_valid = 0;
-  __syncthreads();
-  bitonic_sort(s, P);
-  for (int i = threadIdx.x; i < P; i += blockDim.x)
-    if (s[i] != kEmptyKey && (i + 1 == P || s[i + 1] == kEmptyKey)) s_valid = i + 1;
-  __syncthreads();
-  const int valid = s_valid;
 
-  if (a.cert_eps != nullptr) {
-    // Last compaction of a coarse (bounded-error) scan.  Let c_k be the k-th smallest coarse value and
-    // eps the query's error bound: a row of the true top-k has coarse value <= c_k + 2 eps, so those
-    // rows are kept for the exact re-scoring.  The list is complete only below the threshold t that
-    // filtered the scan, so the result can be certified only if c_k + 2 eps < t.
-    int kept = valid;
-    if (valid >= a.k) {
-      const float bound = ordered_to_float((uint32_t)(s[a.k - 1] >> 32)) + 2.0f * a.cert_eps[q];
-      // first index whose value exceeds the bound (the list is sorted)
-      int lo = a.k, hi = valid;
-      while (lo < hi) {
-        const int mid = (lo + hi) >> 1;
-        if (ordered_to_float((uint32_t)(s[mid] >> 32)) <= bound) lo = mid + 1; else hi = mid;
-      }
-      kept = lo;
-      if (threadIdx.x == 0 && !(bound < a.cand.thr[q])) atomicOr(&a.cand.flags[q], 2);
-    }
-    for (int i = threadIdx.x; i < kept; i += blockDim.x) keys[i] = s[i];
-    if (threadIdx.x == 0) a.cand.count[q] = kept;
-  } else if (a.out_ids == nullptr) {
-    const int kept = min(a.keep, valid);
-    for (int i = threadIdx.x; i < kept; i += blockDim.x) keys[i] = s[i];
-    if (threadIdx.x == 0) {
-      a.cand.count[q] = kept;
-      // The threshold only tightens once `keep` real candidates exist.
-      if (valid >= a.keep) a.cand.thr[q] = ordered_to_float((uint32_t)(s[a.keep - 1] >> 32));
-    }
-  } else {
+  if (a.out_ids != nullptr) {
+    // ---- final order: sort the (short) list in shared memory and write the ascending top-k ----
+    const int P = next_pow2(c);
+    for (int i = threadIdx.x; i < P; i += blockDim.x) s[i] = i < c ? keys[i] : kEmptyKey;
+    if (threadIdx.x == 0) s_valid = 0;
+    __syncthreads();
+    bitonic_sort(s, P);
+    for (int i = threadIdx.x; i < P; i += blockDim.x)
+      if (s[i] != kEmptyKey && (i + 1 == P || s[i + 1] == kEmptyKey)) s_valid = i + 1;
+    __syncthreads();
+    const int valid = s_valid;
     const int64_t qo = a.q_subset ? (int64_t)a.q_subset[q] : q;
     for (int j = threadIdx.x; j < a.k; j += blockDim.x) {
       float d = CUDART_INF_F;
@@ -96,7 +124,58 @@ __global__ void __launch_bounds__(SEL_THREADS) select_kernel(SelectArgs a) {
       a.out_dist[qo * a.k + j] = d;
       a.out_ids[qo * a.k + j] = id;
     }
+    return;
   }
+
+  // ---- compaction: keys in registers, radix select of the pivot, keep everything at or below it ----
+  uint64_t key[SEL_ITEMS];
+  int nvalid = 0;
+#pragma unroll
+  for (int i = 0; i < SEL_ITEMS; ++i) {
+    const int idx = threadIdx.x + i * SEL_THREADS;
+    key[i] = idx < c ? keys[idx] : kEmptyKey;
+    nvalid += key[i] != kEmptyKey;
+  }
+  if (threadIdx.x == 0) { s_valid = 0; s_out = 0; }
+  __syncthreads();
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) nvalid += __shfl_xor_sync(0xffffffffu, nvalid, o);
+  if ((threadIdx.x & 31) == 0) atomicAdd(&s_valid, nvalid);
+  __syncthreads();
+  const int valid = s_valid;
+
+  uint64_t pivot = kEmptyKey - 1;  // keep every real key
+  if (a.cert_eps != nullptr) {
+    // Last compaction of a coarse (bounded-error) scan.  Let c_k be the k-th smallest coarse value and
+    // eps the query's error bound: a row of the true top-k has coarse value <= c_k + 2 eps, so those
+    // rows are kept for the exact re-scoring.  The list is complete only below the threshold t that
+    // filtered the scan, so the result can be certified only if c_k + 2 eps < t.
+    if (valid >= a.k) {
+      const uint64_t kth = block_radix_select(key, a.k, hist, &s_bin, &s_less, &s_in_bin);
+      const float bound = ordered_to_float((uint32_t)(kth >> 32)) + 2.0f * a.cert_eps[q];
+      pivot = ((uint64_t)float_to_ordered(bound) << 32) | 0xffffffffull;
+      if (pivot == kEmptyKey) pivot = kEmptyKey - 1;
+      if (threadIdx.x == 0 && !(bound < a.cand.thr[q])) atomicOr(&a.cand.flags[q], 2);
+    }
+  } else if (valid > a.keep) {
+    pivot = block_radix_select(key, a.keep, hist, &s_bin, &s_less, &s_in_bin);
+    // the keep-th smallest value becomes the query's threshold
+    if (threadIdx.x == 0) a.cand.thr[q] = ordered_to_float((uint32_t)(pivot >> 32));
+  } else if (valid == a.keep && a.keep > 0) {
+    // exactly `keep` real keys: nothing to drop, but the threshold may tighten to their largest value
+    const uint64_t last = block_radix_select(key, a.keep, hist, &s_bin, &s_less, &s_in_bin);
+    if (threadIdx.x == 0) a.cand.thr[q] = ordered_to_float((uint32_t)(last >> 32));
+  }
+  // every thread has loaded its keys (barriers above), so the list can be rewritten in place
+#pragma unroll
+  for (int i = 0; i < SEL_ITEMS; ++i) {
+    if (key[i] <= pivot && key[i] != kEmptyKey) {
+      const int pos = atomicAdd(&s_out, 1);
+      keys[pos] = key[i];
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) a.cand.count[q] = s_out;
 }
 
 __global__ void init_cand_kernel(CandLists c, int64_t nq) {
@@ -149,7 +228,9 @@ __global__ void __launch_bounds__(SEL_THREADS) merge_kernel(const float* __restr
 
 int32_t launch_select(Ctx* ctx, const SelectArgs& a) {
   if (a.nq <= 0) return VSK_OK;
-  select_kernel<<<(unsigned)a.nq, SEL_THREADS, kCandCap * sizeof(uint64_t), ctx->stream>>>(a);
+  // only the final ordering sorts in shared memory
+  const size_t smem = a.out_ids ? kCandCap * sizeof(uint64_t) : 0;
+  select_kernel<<<(unsigned)a.nq, SEL_THREADS, smem, ctx->stream>>>(a);
   ctx->stats.kernel_launches++;
   VSK_CUDA(ctx, cudaGetLastError());
   return VSK_OK;

@@ -47,6 +47,7 @@ struct TcSmem {
   // stage buffers first: each must start on a 1024-byte boundary for the 128B swizzle
   uint8_t stage[STAGES][STAGE_BYTES];
   float beta[2][4][TN];   // per accumulator buffer and epilogue warp: the tile's per-row terms
+  uint32_t masks[TM][TN / 32 + 1];  // per epilogue thread: pass bits of its 256 values (padded row)
   uint64_t full[STAGES];
   uint64_t empty[STAGES];
   uint64_t tmem_full[2];
@@ -292,31 +293,64 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       if (!got) { ok = false; break; }
       tc_fence_after();
       const uint32_t trow = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * TN);
+      if (MODE == SCAN_DENSE) {
 #pragma unroll 1
-      for (int c = 0; c < TN / 32; ++c) {
-        float v[32];
-        tc_ld32(trow + (uint32_t)(c * 32), v);
-        const int64_t nc = n0 + c * 32;
-        float vmin = CUDART_INF_F;
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          v[j] = HAS_BETA ? fmaf(v[j], alpha, sm->beta[acc][quarter][c * 32 + j]) : v[j] * alpha;
-          vmin = fminf(vmin, v[j]);
-        }
-        if (!qok) continue;
-        if (MODE == SCAN_DENSE) {
+        for (int c = 0; c < TN / 32; ++c) {
+          float v[32];
+          tc_ld32(trow + (uint32_t)(c * 32), v);
+          const int64_t nc = n0 + c * 32;
+          if (!qok) continue;
           uint64_t* dst = a.cand.keys + q * kCandCap + (nc - a.row_begin);
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (nc + j < a.row_end) dst[j] = make_key(v[j], (uint32_t)(nc + j));
-        } else if (vmin <= thr) {
+          for (int j = 0; j < 32; ++j) {
+            const float val = HAS_BETA ? fmaf(v[j], alpha, sm->beta[acc][quarter][c * 32 + j]) : v[j] * alpha;
+            if (nc + j < a.row_end) dst[j] = make_key(val, (uint32_t)(nc + j));
+          }
+        }
+      } else {
+        // Pass 1: which of this query's 256 values pass the threshold (one bit each).  A thread then
+        // reserves all its slots with ONE atomic per tile; pass 2 re-reads the accumulator groups that
+        // have a passing value and stores the keys.  A per-value atomic would serialise the warp on an
+        // L2 round trip for every column in which any of its 32 queries has a hit.
+        // The masks live in shared memory so that both loops stay rolled (small code, no dynamic
+        // register indexing).
+        uint32_t* m = sm->masks[et];
+        int cnt = 0;
+#pragma unroll 1
+        for (int c = 0; c < TN / 32; ++c) {
+          float v[32];
+          tc_ld32(trow + (uint32_t)(c * 32), v);
+          const int64_t left = a.row_end - (n0 + c * 32);   // columns of this group inside the launch
+          const uint32_t colmask = left >= 32 ? 0xffffffffu : (left > 0 ? ((1u << (int)left) - 1u) : 0u);
+          uint32_t bits = 0;
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
-            if (v[j] <= thr && nc + j < a.row_end) {
-              const int pos = atomicAdd(&a.cand.count[q], 1);
-              if (pos < kCandCap) a.cand.keys[q * kCandCap + pos] = make_key(v[j], (uint32_t)(nc + j));
+            const float val = HAS_BETA ? fmaf(v[j], alpha, sm->beta[acc][quarter][c * 32 + j]) : v[j] * alpha;
+            bits |= (val <= thr) ? (1u << j) : 0u;
+          }
+          bits = qok ? (bits & colmask) : 0u;
+          m[c] = bits;
+          cnt += __popc(bits);
+        }
+        int base = 0;
+        if (cnt) base = atomicAdd(&a.cand.count[q], cnt);
+#pragma unroll 1
+        for (int c = 0; c < TN / 32; ++c) {
+          const uint32_t bits = m[c];
+          if (!__any_sync(0xffffffffu, bits != 0u)) continue;
+          float v[32];
+          tc_ld32(trow + (uint32_t)(c * 32), v);
+          const int64_t nc = n0 + c * 32;
+          uint64_t* dst = a.cand.keys + q * kCandCap;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if ((bits >> j) & 1u) {
+              const float val = HAS_BETA ? fmaf(v[j], alpha, sm->beta[acc][quarter][c * 32 + j]) : v[j] * alpha;
+              const int pos = base + __popc(bits & ((1u << j) - 1u));
+              if (pos < kCandCap) dst[pos] = make_key(val, (uint32_t)(nc + j));
             }
           }
+          base += __popc(bits);
         }
       }
       tc_fence_before();
