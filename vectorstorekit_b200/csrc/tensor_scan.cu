@@ -750,7 +750,12 @@ int32_t tensor_search(Index* ix, const float* q, int64_t nq, int32_t k, const fl
   sel.dense_count = -1;
   a.mode = SCAN_THRESHOLD;
   while (seen < n) {
+    // Expected appends per query in a chunk are keep * chunk / seen.  Half the free room of a list
+    // bounds the chunk from above; below that, chunks grow geometrically (each no larger than three
+    // times the rows seen so far), which keeps the share of rows scanned under a loose threshold small:
+    // the epilogue's append path costs far more than its filter path.
     int64_t chunk = std::max<int64_t>(room, seen * room / (2 * (int64_t)keep));
+    chunk = std::min<int64_t>(chunk, std::max<int64_t>(room, 3 * seen));
     chunk = std::max<int64_t>(TN, chunk / TN * TN);   // whole row tiles
     chunk = std::min(chunk, n - seen);
     a.row_begin = seen;
