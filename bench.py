@@ -195,16 +195,11 @@ def main():
     out_i_host = torch.empty((nq, k), dtype=torch.int64).pin_memory()
     ext = torch.cuda.ExternalStream(dev.stream, device=device)
 
+    from vectorstorekit_b200.sharded import ShardedSearch
+    sharded = ShardedSearch(lambda qq, kk: index.batchSearch(qq, kk), engine.mergeTopK)
+
     def step_device():
-        d, i = index.batchSearch(queries, k)
-        if world > 1:
-            gd = torch.empty((world, nq, k), dtype=torch.float32, device=device)
-            gi = torch.empty((world, nq, k), dtype=torch.int64, device=device)
-            dist.all_gather_into_tensor(gd, d)
-            dist.all_gather_into_tensor(gi, i)
-            torch.cuda.current_stream().synchronize()
-            d, i = engine.mergeTopK(gd, gi)
-        return d, i
+        return sharded.batchSearch(queries, k)
 
     def step_host():
         import ctypes as C
@@ -214,12 +209,7 @@ def main():
         if world > 1:
             d = out_d_host.to(device, non_blocking=True)
             i = out_i_host.to(device, non_blocking=True)
-            gd = torch.empty((world, nq, k), dtype=torch.float32, device=device)
-            gi = torch.empty((world, nq, k), dtype=torch.int64, device=device)
-            dist.all_gather_into_tensor(gd, d)
-            dist.all_gather_into_tensor(gi, i)
-            torch.cuda.current_stream().synchronize()
-            d, i = engine.mergeTopK(gd, gi)
+            d, i = ShardedSearch(lambda qq, kk: (d, i), engine.mergeTopK).batchSearch(None, k)
             out_d_host.copy_(d)
             out_i_host.copy_(i)
             torch.cuda.synchronize()

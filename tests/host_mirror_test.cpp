@@ -1,0 +1,36 @@
+// Compiles the header-only C++ host layer and links it against the library.  Without a B200 the
+// strategy must refuse to initialise (there is no CPU path); with one, a tiny search is checked
+// against values worked out by hand.
+#include <cmath>
+#include <cstdio>
+
+#include "../vectorstorekit_b200/host/vsk.hpp"
+
+int main() {
+  vsk::CUDAAcceleratorStrategy strategy;
+  std::shared_ptr<vsk::CUDAComputeDevice> dev;
+  try {
+    dev = strategy.initialize();
+  } catch (const vsk::DeviceNotAvailable&) {
+    std::puts("no-device");
+    return 0;
+  }
+  try {
+    vsk::metric_id(vsk::DistanceMetric::hamming);
+    return 2;
+  } catch (const vsk::UnsupportedOperation&) {
+  }
+  const float rows[] = {1, 0, 0, 0, 0, 1, 0, 0, 1, 1, 1, 1};
+  const float q[] = {1, 0, 0, 0};
+  vsk::CUDAAccelerationEngine engine(dev);
+  auto d = engine.computeDistances(q, rows, 3, 4, vsk::DistanceMetric::euclidean);
+  if (std::fabs(d[0]) > 1e-6f || std::fabs(d[1] - std::sqrt(2.0f)) > 1e-4f) return 3;
+  auto m = engine.computeDistances(q, rows, 3, 4, vsk::DistanceMetric::manhattan);
+  if (std::fabs(m[2] - 3.0f) > 1e-4f) return 4;
+  vsk::FlatIndex ix(dev, 4, vsk::DistanceMetric::cosine);
+  ix.add(rows, 3);
+  auto r = ix.batchSearch(q, 1, 2);
+  if (r.ids[0] != 0 || r.ids[1] != 2) return 5;
+  std::puts("ok");
+  return 0;
+}

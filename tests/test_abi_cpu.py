@@ -71,3 +71,21 @@ def test_unsupported_metric_raises():
     with pytest.raises(vsk.UnsupportedOperation):
         _metric_id(vsk.DistanceMetric.hamming)
     assert _metric_id("cosine") == 1
+
+
+def _build_host_mirror(tmp):
+    import subprocess
+    exe = os.path.join(tmp, "host_mirror_test")
+    subprocess.run(["g++", "-std=c++17", "-O1", os.path.join(ROOT, "tests", "host_mirror_test.cpp"), "-o", exe,
+                    "-L", os.path.join(ROOT, "vectorstorekit_b200"), "-lvsk_cuda",
+                    "-Wl,-rpath," + os.path.join(ROOT, "vectorstorekit_b200")], check=True)
+    return exe
+
+
+def test_cpp_host_mirror_compiles_and_refuses_without_gpu(lib, tmp_path):
+    import subprocess
+    import torch
+    exe = _build_host_mirror(str(tmp_path))
+    out = subprocess.run([exe], capture_output=True, text=True)
+    assert out.returncode == 0, out
+    assert out.stdout.strip() == ("ok" if torch.cuda.is_available() else "no-device")

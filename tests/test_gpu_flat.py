@@ -265,3 +265,10 @@ def test_errors(vsk, dev, engine):
         assert np.all(i[:, 4:] == -1) and np.all(np.isinf(d[:, 4:]))
     finally:
         ix.close()
+
+
+def test_cpp_host_mirror_on_gpu(tmp_path):
+    import subprocess
+    from test_abi_cpu import _build_host_mirror
+    out = subprocess.run([_build_host_mirror(str(tmp_path))], capture_output=True, text=True)
+    assert out.returncode == 0 and out.stdout.strip() == "ok", out

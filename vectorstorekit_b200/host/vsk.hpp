@@ -1,0 +1,209 @@
+// Header-only C++ host layer over the C ABI (include/vsk_cuda.h), mirroring the names, argument
+// meaning and error behaviour of VectorStoreKit's Swift types for the accelerated search path
+// (paths relative to Sources/VectorStoreKit):
+//   DistanceMetric                 Core/SearchTypes.swift:105-118
+//   CUDAAcceleratorStrategy        a ComputeAccelerator, Core/Protocols.swift:11-20
+//   CUDAAccelerationEngine         MetalAccelerationEngine.computeDistances / batchComputeDistances,
+//                                  Acceleration/MetalAccelerationEngine.swift:76-204
+//   FlatIndex, IVFIndex            VectorStore.search / IVFIndex.train/insert/search,
+//                                  API/VectorStore.swift:271-318, Indexes/IVFIndex.swift:80-202,397-446
+//   ScalarQuantizer                Quantization/ScalarQuantizer.swift (int8)
+// Errors are thrown as exceptions named after MetalComputeError / IVFError cases.
+#pragma once
+#include <cstdint>
+#include <memory>
+#include <stdexcept>
+#include <string>
+#include <utility>
+#include <vector>
+
+#include "../../include/vsk_cuda.h"
+
+namespace vsk {
+
+enum class DistanceMetric { euclidean = 0, cosine = 1, dotProduct = 2, manhattan = 3,
+                            chebyshev, minkowski, hamming, jaccard, mahalanobis, earth_mover, learned, adaptive };
+
+struct Error : std::runtime_error {
+  int32_t status;
+  Error(int32_t s, const std::string& m) : std::runtime_error(m), status(s) {}
+};
+struct DeviceNotAvailable : Error { using Error::Error; };
+struct DeviceOutOfMemory : Error { using Error::Error; };
+struct UnsupportedOperation : Error { using Error::Error; };
+struct InvalidInput : Error { using Error::Error; };
+struct DimensionMismatch : Error { using Error::Error; };
+struct EmptyInput : Error { using Error::Error; };
+struct Timeout : Error { using Error::Error; };
+struct NotTrained : Error { using Error::Error; };
+struct InsufficientTrainingData : Error { using Error::Error; };
+
+inline void check(int32_t st, vsk_ctx* ctx) {
+  if (st == VSK_OK) return;
+  std::string msg = ctx ? vsk_last_error(ctx) : "";
+  if (msg.empty()) msg = vsk_status_string(st);
+  switch (st) {
+    case VSK_ERR_DEVICE_NOT_AVAILABLE: throw DeviceNotAvailable(st, msg);
+    case VSK_ERR_OUT_OF_MEMORY: throw DeviceOutOfMemory(st, msg);
+    case VSK_ERR_UNSUPPORTED_OPERATION: throw UnsupportedOperation(st, msg);
+    case VSK_ERR_DIMENSION_MISMATCH: throw DimensionMismatch(st, msg);
+    case VSK_ERR_EMPTY_INPUT: throw EmptyInput(st, msg);
+    case VSK_ERR_TIMEOUT: throw Timeout(st, msg);
+    case VSK_ERR_NOT_TRAINED: throw NotTrained(st, msg);
+    case VSK_ERR_INSUFFICIENT_TRAINING_DATA: throw InsufficientTrainingData(st, msg);
+    case VSK_ERR_INVALID_INPUT: case VSK_ERR_INVALID_BUFFER_SIZE: throw InvalidInput(st, msg);
+    default: throw Error(st, msg);
+  }
+}
+
+inline int32_t metric_id(DistanceMetric m) {
+  if (static_cast<int>(m) > 3)  // MetalDistanceCompute.swift:342-344
+    throw UnsupportedOperation(VSK_ERR_UNSUPPORTED_OPERATION, "Distance metric not supported on GPU");
+  return static_cast<int32_t>(m);
+}
+
+// What CUDAAcceleratorStrategy::initialize() returns.
+class CUDAComputeDevice {
+ public:
+  explicit CUDAComputeDevice(int device = 0) {
+    int32_t st = vsk_open(device, &ctx_);
+    if (st != VSK_OK) throw DeviceNotAvailable(st, vsk_status_string(st));
+  }
+  ~CUDAComputeDevice() { if (ctx_) vsk_close(ctx_); }
+  CUDAComputeDevice(const CUDAComputeDevice&) = delete;
+  CUDAComputeDevice& operator=(const CUDAComputeDevice&) = delete;
+  vsk_ctx* ctx() const { return ctx_; }
+  vsk_device_info capabilities() const { vsk_device_info i{}; check(vsk_device_info_get(ctx_, &i), ctx_); return i; }
+  vsk_stats statistics() const { vsk_stats s{}; check(vsk_stats_get(ctx_, &s), ctx_); return s; }
+ private:
+  vsk_ctx* ctx_ = nullptr;
+};
+
+struct CUDAAcceleratorStrategy {
+  const char* identifier = "cuda-sm100a";
+  int device = 0;
+  std::shared_ptr<CUDAComputeDevice> initialize() const { return std::make_shared<CUDAComputeDevice>(device); }
+};
+
+struct SearchResults {            // one ascending row of k hits per query
+  int64_t nq = 0; int32_t k = 0;
+  std::vector<float> distances;   // [nq*k]
+  std::vector<int64_t> ids;       // [nq*k], -1 where fewer than k rows were eligible
+};
+
+class FlatIndex {
+ public:
+  FlatIndex(std::shared_ptr<CUDAComputeDevice> dev, int32_t dimensions, DistanceMetric metric)
+      : dev_(std::move(dev)), dim_(dimensions) {
+    check(vsk_flat_create(dev_->ctx(), metric_id(metric), dimensions, &ix_), dev_->ctx());
+  }
+  ~FlatIndex() { if (ix_) vsk_index_destroy(ix_); }
+  FlatIndex(const FlatIndex&) = delete;
+  FlatIndex& operator=(const FlatIndex&) = delete;
+  void add(const float* rows, int64_t n, const uint64_t* masks = nullptr) { check(vsk_flat_add_f32(ix_, rows, n, masks), dev_->ctx()); }
+  int64_t count() const { return vsk_index_size(ix_); }
+  SearchResults batchSearch(const float* queries, int64_t nq, int32_t k, const uint64_t* filter_masks = nullptr) const {
+    SearchResults r; r.nq = nq; r.k = k;
+    if (nq <= 0) throw EmptyInput(VSK_ERR_EMPTY_INPUT, "no queries");
+    r.distances.resize((size_t)nq * k); r.ids.resize((size_t)nq * k);
+    check(vsk_search(ix_, queries, nq, k, filter_masks, r.distances.data(), r.ids.data()), dev_->ctx());
+    return r;
+  }
+ private:
+  std::shared_ptr<CUDAComputeDevice> dev_;
+  vsk_index* ix_ = nullptr;
+  int32_t dim_;
+};
+
+// MetalAccelerationEngine's distance surface.
+class CUDAAccelerationEngine {
+ public:
+  explicit CUDAAccelerationEngine(std::shared_ptr<CUDAComputeDevice> dev) : dev_(std::move(dev)) {}
+  // batchComputeDistances(queries:candidates:metric:topK: nil): Q x N, row-major
+  std::vector<float> batchComputeDistances(const float* q, int64_t nq, const float* x, int64_t nx, int32_t dim,
+                                           DistanceMetric metric) const {
+    if (nq <= 0 || nx <= 0) throw EmptyInput(VSK_ERR_EMPTY_INPUT, "Empty input provided for distance computation");
+    std::vector<float> out((size_t)nq * nx);
+    check(vsk_batch_distances(dev_->ctx(), metric_id(metric), q, nq, x, nx, dim, out.data()), dev_->ctx());
+    return out;
+  }
+  // computeDistances(query:candidates:metric:)
+  std::vector<float> computeDistances(const float* query, const float* x, int64_t nx, int32_t dim, DistanceMetric m) const {
+    return batchComputeDistances(query, 1, x, nx, dim, m);
+  }
+  // batchComputeDistances(...topK: k): per query the k smallest distances, ascending (distances only)
+  std::vector<float> batchComputeDistances(const float* q, int64_t nq, const float* x, int64_t nx, int32_t dim,
+                                           DistanceMetric metric, int32_t topK) const {
+    FlatIndex ix(dev_, dim, metric);
+    ix.add(x, nx);
+    return ix.batchSearch(q, nq, topK < nx ? topK : (int32_t)nx).distances;
+  }
+ private:
+  std::shared_ptr<CUDAComputeDevice> dev_;
+};
+
+class IVFIndex {
+ public:
+  IVFIndex(std::shared_ptr<CUDAComputeDevice> dev, int32_t dimensions, int32_t numberOfCentroids = 1024,
+           int32_t numberOfProbes = 10, int32_t maxIterations = 100, float tolerance = 1e-4f)
+      : dev_(std::move(dev)), dim_(dimensions), nlist_(numberOfCentroids), nprobe_(numberOfProbes), iters_(maxIterations), tol_(tolerance) {
+    if (dimensions <= 0 || numberOfCentroids <= 0 || numberOfProbes <= 0 || numberOfProbes > numberOfCentroids)
+      throw InvalidInput(VSK_ERR_INVALID_INPUT, "IVFConfiguration.validate failed");  // IVFConfiguration.swift:49-59
+  }
+  ~IVFIndex() { if (ix_) vsk_index_destroy(ix_); }
+  // train(on:) with `.custom` initial centroids (default: the first numberOfCentroids samples)
+  void train(const float* samples, int64_t n, const float* initial = nullptr) {
+    if (n < nlist_) throw InsufficientTrainingData(VSK_ERR_INSUFFICIENT_TRAINING_DATA, "insufficient training data");
+    centroids_.resize((size_t)nlist_ * dim_);
+    std::vector<int32_t> assign((size_t)n);
+    float inertia = 0; int32_t iters = 0;
+    check(vsk_kmeans(dev_->ctx(), samples, n, dim_, nlist_, iters_, tol_, initial ? initial : samples, centroids_.data(),
+                     assign.data(), &inertia, &iters), dev_->ctx());
+    trained_ = true;
+  }
+  void insert(const float* rows, int64_t n) {
+    if (!trained_) throw NotTrained(VSK_ERR_NOT_TRAINED, "Index must be trained before use");
+    if (ix_) { vsk_index_destroy(ix_); ix_ = nullptr; }
+    check(vsk_ivf_build(dev_->ctx(), centroids_.data(), nlist_, rows, n, dim_, &ix_), dev_->ctx());
+  }
+  SearchResults batchSearch(const float* queries, int64_t nq, int32_t k, bool exact = false) const {
+    if (!trained_ || !ix_) throw NotTrained(VSK_ERR_NOT_TRAINED, "Index must be trained before use");
+    SearchResults r; r.nq = nq; r.k = k;
+    r.distances.resize((size_t)nq * k); r.ids.resize((size_t)nq * k);
+    check(vsk_ivf_search(ix_, queries, nq, k, exact ? nlist_ : nprobe_, r.distances.data(), r.ids.data()), dev_->ctx());
+    return r;
+  }
+  const std::vector<float>& centroids() const { return centroids_; }
+ private:
+  std::shared_ptr<CUDAComputeDevice> dev_;
+  vsk_index* ix_ = nullptr;
+  int32_t dim_, nlist_, nprobe_, iters_;
+  float tol_;
+  bool trained_ = false;
+  std::vector<float> centroids_;
+};
+
+class ScalarQuantizer {
+ public:
+  ScalarQuantizer(std::shared_ptr<CUDAComputeDevice> dev, bool per_dim = false) : dev_(std::move(dev)), per_dim_(per_dim) {}
+  void train(const float* rows, int64_t n, int32_t dim) {
+    scale.resize(dim); offset.resize(dim);
+    check(vsk_sq8_train(dev_->ctx(), rows, n, dim, per_dim_ ? VSK_SQ8_PER_DIM : VSK_SQ8_GLOBAL, scale.data(), offset.data()), dev_->ctx());
+  }
+  std::vector<int8_t> quantizeBatch(const float* rows, int64_t n, int32_t dim) const {
+    std::vector<int8_t> codes((size_t)n * dim);
+    check(vsk_sq8_encode(dev_->ctx(), rows, n, dim, scale.data(), offset.data(), codes.data()), dev_->ctx());
+    return codes;
+  }
+  std::vector<float> dequantizeBatch(const int8_t* codes, int64_t n, int32_t dim) const {
+    std::vector<float> rows((size_t)n * dim);
+    check(vsk_sq8_decode(dev_->ctx(), codes, n, dim, scale.data(), offset.data(), rows.data()), dev_->ctx());
+    return rows;
+  }
+  std::vector<float> scale, offset;
+ private:
+  std::shared_ptr<CUDAComputeDevice> dev_;
+  bool per_dim_;
+};
+
+}  // namespace vsk
