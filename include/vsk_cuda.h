@@ -178,6 +178,22 @@ int32_t vsk_kmeans_dev(vsk_ctx* ctx, const float* rows, int64_t n, int32_t dim, 
 int32_t vsk_assign_dev(vsk_ctx* ctx, const float* rows, int64_t n, int32_t dim,
                        const float* centroids, int32_t k, int32_t* assign, float* dist);
 
+/* The same result as vsk_assign_dev (device pointers, same outputs) for callers that must not allocate
+ * device memory.  It has no counterpart in the reference.  Who needs it: code that places incoming rows
+ * into IVF lists from inside a latency-sensitive loop, or on a GPU whose memory has been handed out in full
+ * to other buffers.  cudaMalloc and cudaFree stall every stream of the device while they run and fail once
+ * memory is exhausted; vsk_assign_dev may call them to grow its scratch.  This entry point calls neither,
+ * nor any other allocating routine: its scratch (one 64-bit key per row) is a fixed array inside the library,
+ * 8 MB that each GPU using the library keeps until the process ends.
+ *   - At most 1 048 576 rows per call; more returns VSK_ERR_INVALID_BUFFER_SIZE (split the rows).
+ *   - The first call on a GPU also looks up the array's device address.  Make that first call during
+ *     start-up, before any stream capture is begun.
+ *   - All calls on a GPU, from every context, share the one array and it keeps the last call's contents; each
+ *     call re-initialises the part it uses.  Two calls whose work overlaps on the GPU race on it: run them
+ *     one after the other. */
+int32_t vsk_assign_static_dev(vsk_ctx* ctx, const float* rows, int64_t n, int32_t dim,
+                              const float* centroids, int32_t k, int32_t* assign, float* dist);
+
 /* IVF index over trained centroids: rows are assigned to their nearest centroid and stored
  * list by list.  Replaces IVFIndex.train/insert (Indexes/IVFIndex.swift:397-446,80-122). */
 int32_t vsk_ivf_build(vsk_ctx* ctx, const float* centroids, int32_t nlist, const float* rows,

@@ -60,6 +60,7 @@ SIGNATURES = {
     "vsk_kmeans_dev": (C.c_int32, [vp, vp, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_float, vp, vp, vp,
                                    C.POINTER(C.c_float), C.POINTER(C.c_int32)]),
     "vsk_assign_dev": (C.c_int32, [vp, vp, C.c_int64, C.c_int32, vp, C.c_int32, vp, vp]),
+    "vsk_assign_static_dev": (C.c_int32, [vp, vp, C.c_int64, C.c_int32, vp, C.c_int32, vp, vp]),
     "vsk_ivf_build": (C.c_int32, [vp, vp, C.c_int32, vp, C.c_int64, C.c_int32, C.POINTER(vp)]),
     "vsk_ivf_build_dev": (C.c_int32, [vp, vp, C.c_int32, vp, C.c_int64, C.c_int32, C.POINTER(vp)]),
     "vsk_ivf_assignments": (C.c_int32, [vp, vp]),

@@ -101,6 +101,48 @@ int32_t assign_rows(Ctx* ctx, const float* rows, int64_t n, int32_t dim, const f
   return VSK_OK;
 }
 
+// ---- nearest-centroid assignment without any allocation ------------------------------------
+// Scratch for vsk_assign_static_dev: one 64-bit (distance, centroid) key per row.  The array is part
+// of the library image, so every GPU that loads the library holds these 8 MB until the process exits.
+constexpr int64_t kAssignStaticMaxRows = 1 << 20;
+static __device__ __align__(256) unsigned long long g_assign_static_keys[kAssignStaticMaxRows];
+// Device address of the array on each GPU, looked up once per device.  In host code the array's name is
+// only a handle for the runtime, not an address a kernel could use.
+static unsigned long long* g_assign_static_ptr[64] = {};
+
+int32_t assign_rows_static(Ctx* ctx, const float* rows, int64_t n, int32_t dim, const float* centroids, int32_t k,
+                           int32_t* assign, float* dist) {
+  if (ctx->device < 0 || ctx->device >= 64) return fail(ctx, VSK_ERR_INVALID_INPUT, "device index out of range");
+  unsigned long long* keys = g_assign_static_ptr[ctx->device];
+  if (!keys) {
+    // first call on this GPU (the context's device is current here)
+    void* p = nullptr;
+    VSK_CUDA(ctx, cudaGetSymbolAddress(&p, g_assign_static_keys));
+    keys = g_assign_static_ptr[ctx->device] = static_cast<unsigned long long*>(p);
+  }
+  // The array still holds the previous call's keys: every key this call reads must start as all ones.
+  VSK_CUDA(ctx, cudaMemsetAsync(keys, 0xff, (size_t)n * sizeof(unsigned long long), ctx->stream));
+  ExactScanArgs a{};
+  a.metric = VSK_METRIC_EUCLIDEAN;
+  a.mode = SCAN_ARGMIN;
+  a.q = rows;
+  a.nq = n;
+  a.x = centroids;
+  a.dim = dim;
+  a.row_begin = 0;
+  a.row_end = k;
+  a.best = keys;
+  const bool was_profiling = ctx->profile;   // timing events are created on demand: keep them out of this path
+  ctx->profile = false;
+  const int32_t st = launch_exact_scan(ctx, a);
+  ctx->profile = was_profiling;
+  VSK_TRY(st);
+  decode_best_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, ctx->stream>>>(keys, n, assign, dist);
+  ctx->stats.kernel_launches++;
+  VSK_CUDA(ctx, cudaGetLastError());
+  return VSK_OK;
+}
+
 int32_t kmeans_dev(Ctx* ctx, const float* rows, int64_t n, int32_t dim, int32_t k, int32_t max_iters,
                    float tolerance, const float* init, float* centroids, int32_t* assign, float* inertia,
                    int32_t* iters_run) {
@@ -202,6 +244,24 @@ int32_t vsk_assign_dev(vsk_ctx* c, const float* rows, int64_t n, int32_t dim, co
   if (n <= 0 || k <= 0) return fail(ctx, VSK_ERR_EMPTY_INPUT, "empty rows or centroids");
   if (!rows || !centroids || !assign) return fail(ctx, VSK_ERR_INVALID_INPUT, "null pointer");
   VSK_TRY(assign_rows(ctx, rows, n, dim, centroids, k, assign, dist));
+  VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return VSK_OK;
+}
+
+int32_t vsk_assign_static_dev(vsk_ctx* c, const float* rows, int64_t n, int32_t dim, const float* centroids,
+                              int32_t k, int32_t* assign, float* dist) {
+  Ctx* ctx = reinterpret_cast<Ctx*>(c);
+  if (!ctx) return VSK_ERR_INVALID_INPUT;
+  cudaSetDevice(ctx->device);
+  if (n <= 0 || k <= 0) return fail(ctx, VSK_ERR_EMPTY_INPUT, "empty rows or centroids");
+  if (dim <= 0) return fail(ctx, VSK_ERR_DIMENSION_MISMATCH, "dimension must be positive");
+  if (!rows || !centroids || !assign) return fail(ctx, VSK_ERR_INVALID_INPUT, "null pointer");
+  if (n > kAssignStaticMaxRows)
+    return fail(ctx, VSK_ERR_INVALID_BUFFER_SIZE,
+                "vsk_assign_static_dev handles at most %lld rows per call (got %lld): split the rows, or use "
+                "vsk_assign_dev, which allocates its scratch",
+                (long long)kAssignStaticMaxRows, (long long)n);
+  VSK_TRY(assign_rows_static(ctx, rows, n, dim, centroids, k, assign, dist));
   VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   return VSK_OK;
 }
