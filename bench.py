@@ -2,17 +2,23 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload c2]
 
-Metric: queries/sec of exact top-k search (BASELINE.json).  At N = 1 the default workload is the
+Metric: queries/sec of exact top-k search (BASELINE.json).  The default workload (c2) is the
 configuration the metric is quoted on: flat cosine, 1 000 000 x 768 fp32 rows (N(0,1), L2-normalised),
 10 000 queries, k = 100.  A step is one batch search of all queries over the resident database.
-With N > 1 (one process per GPU under torchrun) the rows are sharded across ranks, each rank
-searches its shard, the per-shard top-k lists are all-gathered over NCCL and merged.
+With N > 1 (one process per GPU under torchrun) the rows are sharded across ranks, each rank searches
+its shard, the per-shard top-k lists are all-gathered over NCCL and merged ("scaling": "strong").
 
-value   queries/s with queries already in HBM (CUDA events, max over ranks)
-e2e     queries/s through the host-pointer C-ABI call: pinned host queries in, results out
-roofline / cpu_baseline: see DESIGN.md
+Other workloads (not the default line): c1 flat euclidean 100k x 128; c3 IVF (10M x 128, nlist 4096,
+20 Lloyd iterations, nprobe 32); c4 int8 dot product 50M x 384; c5 filtered Manhattan 5M x 256; and
+reduced copies (suffix s) for profiler captures.
+
+value     queries/s with queries already in HBM (CUDA events on the library's stream, max over ranks)
+e2e       queries/s through the host-pointer C-ABI call: pinned host queries in, host results out
+roofline  the scan kernels' device time from CUDA events recorded around each launch
+cpu_baseline / --impl reference: the CPU restatement of the reference's search on the host cores
 """
 import argparse
+import ctypes as C
 import json
 import os
 import subprocess
@@ -25,12 +31,28 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+SEED = 20261125 * 10
+
+# kind, metric, rows, dim, queries, k, name, extra
 WORKLOADS = {
-    # name: (metric, rows, dim, queries, k, description)
-    "c1": ("euclidean", 100_000, 128, 1_000, 10, "flat-euclidean-100k-d128-q1000-k10"),
-    "c2": ("cosine", 1_000_000, 768, 10_000, 100, "flat-cosine-1M-d768-q10000-k100"),
-    # reduced copy of c2 for profiler captures: database still larger than L2, under 1 GB on the device
-    "c2s": ("cosine", 200_000, 768, 2_048, 100, "flat-cosine-200k-d768-q2048-k100"),
+    "c1": dict(kind="flat", metric="euclidean", rows=100_000, dim=128, queries=1_000, k=10, cfg=1,
+               name="flat-euclidean-100k-d128-q1000-k10"),
+    "c2": dict(kind="flat", metric="cosine", rows=1_000_000, dim=768, queries=10_000, k=100, cfg=2,
+               name="flat-cosine-1M-d768-q10000-k100"),
+    "c2s": dict(kind="flat", metric="cosine", rows=200_000, dim=768, queries=2_048, k=100, cfg=2,
+                name="flat-cosine-200k-d768-q2048-k100"),
+    "c3": dict(kind="ivf", metric="euclidean", rows=10_000_000, dim=128, queries=10_000, k=10, cfg=3, nlist=4096,
+               nprobe=32, iters=20, name="ivf-euclidean-10M-d128-nlist4096-nprobe32-q10000-k10"),
+    "c3s": dict(kind="ivf", metric="euclidean", rows=1_000_000, dim=128, queries=2_048, k=10, cfg=3, nlist=1024,
+                nprobe=32, iters=5, name="ivf-euclidean-1M-d128-nlist1024-nprobe32-q2048-k10"),
+    "c4": dict(kind="sq8", metric="dotProduct", rows=50_000_000, dim=384, queries=10_000, k=10, cfg=4,
+               name="int8-dot-50M-d384-q10000-k10"),
+    "c4s": dict(kind="sq8", metric="dotProduct", rows=2_000_000, dim=384, queries=2_048, k=10, cfg=4,
+                name="int8-dot-2M-d384-q2048-k10"),
+    "c5": dict(kind="filtered", metric="manhattan", rows=5_000_000, dim=256, queries=10_000, k=50, cfg=5,
+               name="filtered-manhattan-5M-d256-q10000-k50"),
+    "c5s": dict(kind="filtered", metric="manhattan", rows=500_000, dim=256, queries=1_024, k=50, cfg=5,
+                name="filtered-manhattan-500k-d256-q1024-k50"),
 }
 
 
@@ -62,7 +84,7 @@ class ClockSampler(threading.Thread):
                     self.samples.append(f)
             except Exception:
                 pass
-            time.sleep(0.1)
+            time.sleep(0.05)
 
     def summary(self):
         if not self.samples:
@@ -75,41 +97,249 @@ class ClockSampler(threading.Thread):
                 "samples": len(self.samples)}
 
 
-def gen_rows(torch, n, dim, seed, device, normalise):
-    """Seeded N(0,1) rows generated on the GPU, optionally L2-normalised (x_i / |x|, fp32)."""
+# ---------------------------------------------------------------------------------------------
+# synthetic data (seeded, generated on the GPU in slabs; the union over ranks is the same database
+# at every world size because every slab has its own seed derived from its first row)
+# ---------------------------------------------------------------------------------------------
+SLAB = 1 << 18
+
+
+def _gen_slab(torch, wl, first_row, count, device, centres=None):
     g = torch.Generator(device=device)
-    g.manual_seed(seed)
-    out = torch.empty((n, dim), dtype=torch.float32, device=device)
-    step = 1 << 18
-    for b in range(0, n, step):
-        e = min(n, b + step)
-        t = torch.randn((e - b, dim), generator=g, dtype=torch.float32, device=device)
-        if normalise:
-            t = t / t.norm(dim=1, keepdim=True)
-        out[b:e] = t
-    return out
+    g.manual_seed(SEED + wl["cfg"] * 1_000_003 + first_row)
+    dim = wl["dim"]
+    if wl["kind"] == "filtered":
+        return torch.rand((count, dim), generator=g, dtype=torch.float32, device=device) * 2 - 1
+    t = torch.randn((count, dim), generator=g, dtype=torch.float32, device=device)
+    if wl["kind"] == "ivf":
+        c = torch.randint(0, centres.shape[0], (count,), generator=g, device=device)
+        return centres[c] + 0.1 * t
+    if wl["metric"] == "cosine":
+        t = t / t.norm(dim=1, keepdim=True)
+    return t
 
 
-def cpu_search_rate(metric_id, q_host, x_host, k, seconds_target=15.0, nthreads=0):
-    """Times the CPU restatement of the reference's search on a bounded query sample of the same
-    workload (full database).  Returns (queries/s, cores, description)."""
+def gen_rows(torch, wl, lo, hi, device, centres=None, out=None):
+    """Rows [lo, hi) of the workload's database; slabs are aligned to SLAB so shards reproduce them."""
+    res = out if out is not None else torch.empty((hi - lo, wl["dim"]), dtype=torch.float32, device=device)
+    s = (lo // SLAB) * SLAB
+    while s < hi:
+        e = s + SLAB
+        slab = _gen_slab(torch, wl, s, SLAB, device, centres)
+        a, b = max(s, lo), min(e, hi)
+        res[a - lo:b - lo] = slab[a - s:b - s]
+        s = e
+    return res
+
+
+def gen_queries(torch, wl, device, centres=None):
+    q = dict(wl)
+    q["cfg"] = wl["cfg"] + 50
+    return _gen_slab(torch, q, 0, wl["queries"], device, centres)
+
+
+def gen_masks(torch, wl, lo, hi, device):
+    g = torch.Generator(device=device)
+    g.manual_seed(SEED + 777 + lo)
+    # 64 Bernoulli(0.5) bits per row
+    a = torch.randint(0, 2 ** 31, (hi - lo, 2), generator=g, device=device, dtype=torch.int64)
+    b = torch.randint(0, 2 ** 2, (hi - lo,), generator=g, device=device, dtype=torch.int64)
+    return (a[:, 0] | (a[:, 1] << 31) | (b << 62)).contiguous()
+
+
+# ---------------------------------------------------------------------------------------------
+# CPU baseline: the C++ restatement of the reference's CPU search, OpenMP over queries
+# ---------------------------------------------------------------------------------------------
+def cpu_rate(fn, nq_total, cores, seconds_target):
+    """fn(nq) runs the CPU search on the first nq queries.  Sizes the sample for ~seconds_target."""
+    n0 = min(nq_total, max(cores, 4))
+    t0 = time.perf_counter()
+    fn(n0)
+    dt = time.perf_counter() - t0
+    nq = int(min(nq_total, max(n0, seconds_target / max(dt / n0, 1e-9))))
+    nq = min(nq_total, max(cores, (nq // cores) * cores))
+    t0 = time.perf_counter()
+    fn(nq)
+    dt = time.perf_counter() - t0
+    return nq / dt, nq, dt
+
+
+def get_oracle():
     import oracle
     try:
         oracle.build(native=True)
-        o = oracle.CpuOracle(native=True)
+        return oracle, oracle.CpuOracle(native=True)
     except Exception:
-        o = oracle.CpuOracle()
-    cores = o.num_threads() if nthreads == 0 else nthreads
-    n0 = min(len(q_host), max(cores, 4))
-    t0 = time.perf_counter()
-    o.flat_search(metric_id, q_host[:n0], x_host, k, fast=True, nthreads=nthreads)
-    dt = time.perf_counter() - t0
-    nq = int(min(len(q_host), max(n0, seconds_target / max(dt / n0, 1e-9))))
-    nq = max(cores, (nq // cores) * cores)
-    t0 = time.perf_counter()
-    o.flat_search(metric_id, q_host[:nq], x_host, k, fast=True, nthreads=nthreads)
-    dt = time.perf_counter() - t0
-    return nq / dt, cores, f"{nq} of {len(q_host)} queries over all {len(x_host)} rows, {dt:.1f} s"
+        return oracle, oracle.CpuOracle()
+
+
+class Bench:
+    """One workload on this rank's shard."""
+
+    def __init__(self, torch, vsk, dev, engine, wl, rank, world, device, path):
+        self.torch, self.vsk, self.dev, self.engine, self.wl = torch, vsk, dev, engine, wl
+        self.rank, self.world, self.device = rank, world, device
+        self.lo, self.hi = rank * wl["rows"] // world, (rank + 1) * wl["rows"] // world
+        self.k, self.nq = wl["k"], wl["queries"]
+        self.extra = {}
+        self.qmasks = None
+        getattr(self, "_build_" + wl["kind"])()
+        self.q_pinned = self.queries.cpu().pin_memory()
+        self.out_d_host = torch.empty((self.nq, self.k), dtype=torch.float32).pin_memory()
+        self.out_i_host = torch.empty((self.nq, self.k), dtype=torch.int64).pin_memory()
+        self.qm_pinned = self.qmasks.cpu().pin_memory() if self.qmasks is not None else None
+        from vectorstorekit_b200.sharded import ShardedSearch
+        self.sharded = ShardedSearch(self.local_search, engine.mergeTopK)
+
+    # ---- builders ----
+    def _build_flat(self):
+        wl, t = self.wl, self.torch
+        self.rows = gen_rows(t, wl, self.lo, self.hi, self.device)
+        self.queries = gen_queries(t, wl, self.device)
+        self.index = self.vsk.FlatIndex(self.dev, wl["dim"], wl["metric"])
+        self.index.add(self.rows)
+        self.index.set_id_base(self.lo)
+        self.flops = 2.0 * self.nq * (self.hi - self.lo) * wl["dim"]
+        self.bound = "tensor"
+
+    def _build_filtered(self):
+        wl, t = self.wl, self.torch
+        self.rows = gen_rows(t, wl, self.lo, self.hi, self.device)
+        self.masks = gen_masks(t, wl, self.lo, self.hi, self.device)
+        self.queries = gen_queries(t, wl, self.device)
+        g = t.Generator(device=self.device)
+        g.manual_seed(SEED + 4242)
+        self.qmasks = (t.ones(self.nq, dtype=t.int64, device=self.device)
+                       << t.randint(0, 63, (self.nq,), generator=g, device=self.device)).contiguous()
+        self.index = self.vsk.FlatIndex(self.dev, wl["dim"], wl["metric"])
+        self.index.add(self.rows, self.masks)
+        self.index.set_id_base(self.lo)
+        # FP32 lane-instructions of the eligible pairs: 2 per pair-dimension (subtract; add |.|)
+        self.flops = 2.0 * self.nq * (self.hi - self.lo) * 0.5 * wl["dim"]
+        self.bound = "fp32"
+
+    def _build_ivf(self):
+        wl, t = self.wl, self.torch
+        g = t.Generator(device=self.device)
+        g.manual_seed(SEED + 31337)
+        centres = t.randn((wl["nlist"], wl["dim"]), generator=g, dtype=t.float32, device=self.device)
+        self.rows = gen_rows(t, wl, self.lo, self.hi, self.device, centres)
+        self.queries = gen_queries(t, wl, self.device, centres)
+        ix = self.vsk.IVFIndex(self.dev, wl["dim"], numberOfCentroids=wl["nlist"], numberOfProbes=wl["nprobe"],
+                               maxIterations=wl["iters"], tolerance=-1.0)
+        t.cuda.synchronize()
+        t0 = time.perf_counter()
+        ix.train(self.rows, self.rows[:wl["nlist"]].contiguous())
+        t.cuda.synchronize()
+        t1 = time.perf_counter()
+        ix.insert(self.rows)
+        t.cuda.synchronize()
+        t2 = time.perf_counter()
+        self.index = ix
+        n = self.hi - self.lo
+        self.extra = {"train_s": t1 - t0, "train_s_per_iteration": (t1 - t0) / wl["iters"], "build_s": t2 - t1,
+                      "train_flops_per_iteration": 2.0 * n * wl["nlist"] * wl["dim"]}
+        asg = ix.assignments()
+        sizes = np.bincount(asg, minlength=wl["nlist"])
+        self.extra["list_len_mean"] = float(sizes.mean())
+        self.extra["list_len_max"] = int(sizes.max())
+        # query-major algorithmic bytes: every query reads the rows of its nprobe lists once
+        self.bytes_per_query = wl["nprobe"] * float(sizes.mean()) * wl["dim"] * 4
+        self.flops = 2.0 * self.nq * wl["nprobe"] * float(sizes.mean()) * wl["dim"]
+        self.bound = "hbm"
+        self.centroids_host = ix.centroids.cpu().numpy() if hasattr(ix.centroids, "cpu") else ix.centroids
+        self.assign_host = asg
+
+    def _build_sq8(self):
+        wl, t = self.wl, self.torch
+        import torch.distributed as dist
+        sq = self.vsk.ScalarQuantizer(self.dev, per_dim=True)
+        n = self.hi - self.lo
+        step = 1 << 20
+        mn = mx = None
+        for b in range(self.lo, self.hi, step):
+            e = min(self.hi, b + step)
+            x = gen_rows(t, wl, b, e, self.device)
+            a, c = sq.minmax(x)
+            mn = a if mn is None else t.minimum(mn, a)
+            mx = c if mx is None else t.maximum(mx, c)
+        if self.world > 1:
+            dist.all_reduce(mn, op=dist.ReduceOp.MIN)
+            dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        scale, offset = sq.set_range(mn, mx)
+        self.index = self.vsk.QuantizedFlatIndex(self.dev, wl["dim"], wl["metric"], scale, offset)
+        for b in range(self.lo, self.hi, step):
+            e = min(self.hi, b + step)
+            x = gen_rows(t, wl, b, e, self.device)
+            self.index.add(sq.quantizeBatch(x))      # the fp32 source is dropped after encoding
+        self.index.set_id_base(self.lo)
+        self.queries = gen_queries(t, wl, self.device)
+        self.sq = sq
+        self.rows = None
+        self.flops = 2.0 * self.nq * n * wl["dim"]
+        self.bound = "tensor"
+
+    # ---- steps ----
+    def local_search(self, queries, k):
+        if self.wl["kind"] == "ivf":
+            return self.index.batchSearch(queries, k)
+        if self.wl["kind"] == "filtered":
+            return self.index.batchSearch(queries, k, self.qmasks)
+        return self.index.batchSearch(queries, k)
+
+    def step_device(self):
+        return self.sharded.batchSearch(self.queries, self.k)
+
+    def step_host(self):
+        lib, t = self.dev._lib, self.torch
+        qp, od, oi = (C.c_void_p(x.data_ptr()) for x in (self.q_pinned, self.out_d_host, self.out_i_host))
+        if self.wl["kind"] == "ivf":
+            self.dev.check(lib.vsk_ivf_search(self.index._h, qp, self.nq, self.k, self.wl["nprobe"], od, oi))
+        else:
+            qm = C.c_void_p(self.qm_pinned.data_ptr()) if self.qm_pinned is not None else None
+            self.dev.check(lib.vsk_search(self.index._h, qp, self.nq, self.k, qm, od, oi))
+        if self.world > 1:
+            from vectorstorekit_b200.sharded import ShardedSearch
+            d = self.out_d_host.to(self.device, non_blocking=True)
+            i = self.out_i_host.to(self.device, non_blocking=True)
+            d, i = ShardedSearch(lambda qq, kk: (d, i), self.engine.mergeTopK).batchSearch(None, self.k)
+            self.out_d_host.copy_(d)
+            self.out_i_host.copy_(i)
+            t.cuda.synchronize()
+
+    # ---- CPU baseline on this rank's data ----
+    def cpu_baseline(self, seconds_target=15.0):
+        oracle, o = get_oracle()
+        wl = self.wl
+        cores = o.num_threads()
+        q = self.queries.cpu().numpy()
+        mid = oracle.METRIC_IDS[wl["metric"]]
+        if wl["kind"] in ("flat", "filtered"):
+            x = self.rows.cpu().numpy()
+            rm = self.masks.cpu().numpy().view(np.uint64) if wl["kind"] == "filtered" else None
+            qm = self.qmasks.cpu().numpy().view(np.uint64) if wl["kind"] == "filtered" else None
+            fn = lambda n: o.flat_search(mid, q[:n], x, self.k, rm, qm[:n] if qm is not None else None, fast=True)
+        elif wl["kind"] == "ivf":
+            x = self.rows.cpu().numpy()
+            fn = lambda n: o.ivf_search(q[:n], x, self.centroids_host, self.assign_host, wl["nprobe"], self.k)
+        else:
+            # codes of a bounded prefix of the shard (regenerated and re-encoded on the GPU); the rate is scaled
+            # by the row ratio and labelled as extrapolated
+            n_all = self.hi - self.lo
+            n_cpu = min(n_all, 4_000_000)
+            xs = gen_rows(self.torch, wl, self.lo, self.lo + n_cpu, self.device)
+            codes = self.sq.quantizeBatch(xs).cpu().numpy()
+            del xs
+            sc, of = self.sq.scale.cpu().numpy(), self.sq.offset.cpu().numpy()
+            fn = lambda n: o.sq8_search(mid, q[:n], codes, sc, of, self.k)
+            v, nq, dt = cpu_rate(fn, self.nq, cores, seconds_target)
+            v *= n_cpu / n_all
+            return {"value": v, "unit": "queries/s", "cores": cores, "kind": "port",
+                    "sample": f"{nq} of {self.nq} queries over {n_cpu} of {n_all} rows, {dt:.1f} s"
+                              + (" (rate scaled by the row ratio: extrapolated)" if n_cpu < n_all else "")}
+        v, nq, dt = cpu_rate(fn, self.nq, cores, seconds_target)
+        return {"value": v, "unit": "queries/s", "cores": cores, "kind": "port",
+                "sample": f"{nq} of {self.nq} queries over all {self.hi - self.lo} rows, {dt:.1f} s"}
 
 
 def run_reference(args, wl):
@@ -118,21 +348,24 @@ def run_reference(args, wl):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    metric, n, dim, nq, k, name = wl
-    import oracle
-    rng = np.random.default_rng(20261125)
+    oracle, o = get_oracle()
+    n, dim, nq, k = wl["rows"], wl["dim"], wl["queries"], wl["k"]
+    if wl["kind"] != "flat":
+        print(json.dumps({"impl": "reference", "unavailable": "the reference arm is defined for the flat workloads (c1, c2)"}))
+        return
+    rng = np.random.default_rng(SEED)
     x = rng.standard_normal((n, dim), dtype=np.float32)
     q = rng.standard_normal((nq, dim), dtype=np.float32)
-    if metric == "cosine":
+    if wl["metric"] == "cosine":
         x /= np.linalg.norm(x, axis=1, keepdims=True)
         q /= np.linalg.norm(q, axis=1, keepdims=True)
-    mid = oracle.METRIC_IDS[{"euclidean": "euclidean", "cosine": "cosine"}[metric]]
+    mid = oracle.METRIC_IDS[wl["metric"]]
+    cores = o.num_threads()
     per_step = max(5.0, min(30.0, 120.0 / max(1, args.steps + args.warmup)))
-    rates = []
-    desc = ""
-    cores = 1
+    rates, desc = [], ""
     for s in range(args.warmup + args.steps):
-        r, cores, desc = cpu_search_rate(mid, q, x, k, seconds_target=per_step)
+        r, m, dt = cpu_rate(lambda c: o.flat_search(mid, q[:c], x, k, fast=True), nq, cores, per_step)
+        desc = f"{m} of {nq} queries over all {n} rows, {dt:.1f} s"
         if s >= args.warmup:
             rates.append(r)
     v = float(np.mean(rates))
@@ -140,7 +373,7 @@ def run_reference(args, wl):
         "impl": "reference", "metric": "queries/sec (k-NN, exact top-k match)", "value": v, "unit": "queries/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * nq / v,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": name, "rows": n, "dim": dim, "queries": nq, "k": k, "metric": metric},
+        "config": {"workload": wl["name"], "rows": n, "dim": dim, "queries": nq, "k": k, "metric": wl["metric"]},
         "cpu_baseline": {"value": v, "unit": "queries/s", "cores": cores, "kind": "port", "sample": desc},
         "e2e": {"value": v, "unit": "queries/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0}))
@@ -155,6 +388,7 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--path", default="tensor", choices=["tensor", "fp32"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]
     if args.impl == "reference":
@@ -164,7 +398,6 @@ def main():
     import torch.distributed as dist
     import vectorstorekit_b200 as vsk
 
-    metric, n_total, dim, nq, k, name = wl
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -175,44 +408,9 @@ def main():
     dev = vsk.CUDAComputeDevice(local)
     dev.set_search_path(vsk.PATH_TENSOR_RERANK if args.path == "tensor" else vsk.PATH_FP32_SCAN)
     engine = vsk.CUDAAccelerationEngine(dev)
-
-    # rows [lo, hi) of the global database live on this rank
-    lo, hi = rank * n_total // world, (rank + 1) * n_total // world
-    seed = 20261125 * 10 + 2
-    # every rank generates the full query set (replicated) and only its rows: the generator is
-    # advanced shard by shard so that the union over ranks is the same database at every world size
-    shard_rows = []
-    for r in range(world):
-        rl, rh = r * n_total // world, (r + 1) * n_total // world
-        if r == rank:
-            shard_rows = gen_rows(torch, rh - rl, dim, seed + 100 + rl, device, metric == "cosine")
-    queries = gen_rows(torch, nq, dim, seed + 1000, device, metric == "cosine")
-    index = vsk.FlatIndex(dev, dim, metric)
-    index.add(shard_rows)
-    index.set_id_base(lo)
-    q_pinned = queries.cpu().pin_memory()
-    out_d_host = torch.empty((nq, k), dtype=torch.float32).pin_memory()
-    out_i_host = torch.empty((nq, k), dtype=torch.int64).pin_memory()
+    b = Bench(torch, vsk, dev, engine, wl, rank, world, device, args.path)
+    nq, k = b.nq, b.k
     ext = torch.cuda.ExternalStream(dev.stream, device=device)
-
-    from vectorstorekit_b200.sharded import ShardedSearch
-    sharded = ShardedSearch(lambda qq, kk: index.batchSearch(qq, kk), engine.mergeTopK)
-
-    def step_device():
-        return sharded.batchSearch(queries, k)
-
-    def step_host():
-        import ctypes as C
-        lib = dev._lib
-        dev.check(lib.vsk_search(index._h, C.c_void_p(q_pinned.data_ptr()), nq, k, None,
-                                 C.c_void_p(out_d_host.data_ptr()), C.c_void_p(out_i_host.data_ptr())))
-        if world > 1:
-            d = out_d_host.to(device, non_blocking=True)
-            i = out_i_host.to(device, non_blocking=True)
-            d, i = ShardedSearch(lambda qq, kk: (d, i), engine.mergeTopK).batchSearch(None, k)
-            out_d_host.copy_(d)
-            out_i_host.copy_(i)
-            torch.cuda.synchronize()
 
     def barrier():
         torch.cuda.synchronize()
@@ -221,7 +419,7 @@ def main():
         torch.cuda.synchronize()
 
     for _ in range(args.warmup):
-        step_device()
+        b.step_device()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
@@ -229,40 +427,39 @@ def main():
     st0 = dev.stats()
     barrier()
     t0 = time.perf_counter()
-    with torch.cuda.stream(ext):
-        e0 = torch.cuda.Event(enable_timing=True)
-        e0.record(ext)
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record(ext)
     for _ in range(args.steps):
-        d_last, i_last = step_device()
-    with torch.cuda.stream(ext):
-        e1 = torch.cuda.Event(enable_timing=True)
-        e1.record(ext)
+        b.step_device()
+    e1.record(ext)
     barrier()
     wall = time.perf_counter() - t0
     dev_ms = e0.elapsed_time(e1)
     st1 = dev.stats()
     dev.profile(False)
-    # multi-GPU: the all-gather runs on torch's stream, so the step time is the wall clock between the
-    # two barriers (both sides synchronised); single GPU: CUDA events on the library's stream
+    # multi-GPU: the all-gather runs on torch's stream, so the step time is the wall clock between the two
+    # barriers (both sides synchronised); single GPU: CUDA events on the library's stream
     elapsed_ms = dev_ms if world == 1 else wall * 1e3
-    t = torch.tensor([elapsed_ms], dtype=torch.float64, device=device)
+    tt = torch.tensor([elapsed_ms], dtype=torch.float64, device=device)
     if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    elapsed_ms = float(t.item())
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+    elapsed_ms = float(tt.item())
 
-    # end to end through the host-pointer call
-    for _ in range(2):
-        step_host()
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        step_host()
-    barrier()
-    e2e_s = time.perf_counter() - t0
-    t = torch.tensor([e2e_s], dtype=torch.float64, device=device)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_s = float(t.item())
+    e2e = None
+    if not args.no_e2e:
+        for _ in range(2):
+            b.step_host()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            b.step_host()
+        barrier()
+        e2e_s = time.perf_counter() - t0
+        tt = torch.tensor([e2e_s], dtype=torch.float64, device=device)
+        if world > 1:
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        e2e = nq * args.steps / float(tt.item())
     if rank == 0:
         sampler.stop_flag = True
         sampler.join(timeout=2)
@@ -271,28 +468,36 @@ def main():
     scan_ms = st1["scan_kernel_ms"] - st0["scan_kernel_ms"]
     scan_n = max(1, st1["scan_kernel_launches"] - st0["scan_kernel_launches"])
     pk = peaks()
-    n_local = hi - lo
-    flops_step = 2.0 * nq * n_local * dim      # algorithmic flops of one batch on this rank
-    roof = {
-        "bound": "tensor", "unit": "TFLOP/s",
-        "achieved": flops_step * args.steps / (scan_ms * 1e-3) / 1e12 if scan_ms > 0 else None,
-        "peak": pk["bf16_tflops"], "peak_source": pk["source"] + " (cuBLAS bf16, sustained)",
-        "kernel": "scan kernels (contraction + fused candidate filter)",
-        "kernel_ms_per_step": scan_ms / args.steps, "kernel_launches_per_step": scan_n / args.steps,
-        "traffic": None,
-    }
-    roof["frac"] = roof["achieved"] / roof["peak"] if roof["achieved"] else None
+    roof = {"bound": b.bound, "kernel": "scan kernels (distance computation + fused candidate filter)",
+            "kernel_ms_per_step": scan_ms / args.steps, "kernel_launches_per_step": scan_n / args.steps, "traffic": None}
+    secs = scan_ms * 1e-3
+    if b.bound == "tensor":
+        roof.update(unit="TFLOP/s", achieved=b.flops * args.steps / secs / 1e12 if secs > 0 else None,
+                    peak=pk["bf16_tflops"], peak_source=pk["source"] + " (cuBLAS bf16, sustained)")
+    elif b.bound == "hbm":
+        roof.update(unit="GB/s", achieved=b.bytes_per_query * nq * args.steps / secs / 1e9 if secs > 0 else None,
+                    peak=pk["hbm_gbs"], peak_source=pk["source"] + " (copy)",
+                    note="algorithmic bytes are query-major (each query reads its probed lists once); the list-major "
+                         "kernel reuses a list across the queries that probe it, so achieved may exceed peak")
+    else:
+        sm = dev.info()["sm_count"]
+        roof.update(unit="T lane-instr/s", achieved=b.flops * args.steps / secs / 1e12 if secs > 0 else None,
+                    peak=sm * 128 * 1.965e9 / 1e12, peak_source="nominal: SMs x 128 FP32 lanes x 1965 MHz")
+    roof["frac"] = roof["achieved"] / roof["peak"] if roof.get("achieved") else None
 
     line = {
         "metric": "queries/sec (k-NN, exact top-k match)", "value": nq * args.steps / (elapsed_ms * 1e-3),
         "unit": "queries/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-        "dtype": "f16 operands, f32 accumulate, f32 rerank" if args.path == "tensor" else "f32", "data": "synthetic",
-        "config": {"workload": name, "rows": n_total, "dim": dim, "queries": nq, "k": k, "metric": metric,
-                   "sharding": f"rows/{world}", "search_path": args.path,
-                   "l2": "database (>= 1.5 GB per pass) is larger than L2"},
+        "dtype": ("f16 operands, f32 accumulate, f32 rerank" if args.path == "tensor" and b.bound == "tensor" else "f32"),
+        "data": "synthetic",
+        "config": dict({"workload": wl["name"], "rows": wl["rows"], "dim": wl["dim"], "queries": nq, "k": k,
+                        "metric": wl["metric"], "sharding": f"rows/{world}", "search_path": args.path,
+                        "l2": "the database read by every pass is larger than L2 (126 MB)"
+                        if (b.hi - b.lo) * wl["dim"] * 2 > 126e6 else "L2 flushed by the candidate-list traffic only"},
+                       **b.extra),
         "roofline": roof,
-        "e2e": {"value": nq * args.steps / e2e_s, "unit": "queries/s", "h2d_bytes_per_step": nq * dim * 4,
+        "e2e": {"value": e2e, "unit": "queries/s", "h2d_bytes_per_step": nq * wl["dim"] * 4 + (nq * 8 if b.qmasks is not None else 0),
                 "d2h_bytes_per_step": nq * k * 12},
         "gpu_launches": int(launches),
         "stats": {"fallback_queries": st1["fallback_queries"] - st0["fallback_queries"],
@@ -302,11 +507,8 @@ def main():
     if rank == 0:
         line["clocks"] = sampler.summary()
         if world == 1 and not args.no_cpu_baseline:
-            import oracle
-            v, cores, desc = cpu_search_rate(oracle.METRIC_IDS[metric], queries.cpu().numpy(), shard_rows.cpu().numpy(), k)
-            line["cpu_baseline"] = {"value": v, "unit": "queries/s", "cores": cores, "kind": "port", "sample": desc}
+            line["cpu_baseline"] = b.cpu_baseline()
         print(json.dumps(line))
-    index.close()
     if world > 1:
         dist.destroy_process_group()
 

@@ -22,6 +22,7 @@ def _call(lib, fn, ctx, x, c):
     n, d = x.shape
     asg = torch.empty(n, dtype=torch.int32, device=x.device)
     dist = torch.empty(n, dtype=torch.float32, device=x.device)
+    torch.cuda.synchronize()   # the library's stream does not wait for torch's: inputs must be complete
     st = fn(ctx, C.c_void_p(x.data_ptr()), n, d, C.c_void_p(c.data_ptr()), c.shape[0],
             C.c_void_p(asg.data_ptr()), C.c_void_p(dist.data_ptr()))
     return st, asg.cpu().numpy(), dist.cpu().numpy()

@@ -4,6 +4,7 @@
 // scan kernels.
 #include <cstdarg>
 #include <cstdio>
+#include <cmath>
 #include <cstring>
 #include <functional>
 
@@ -98,28 +99,37 @@ static int32_t cand_workspace(Ctx* ctx, int64_t nq, CandLists* c) {
 // scan(mode, row_begin, row_end): appends to the lists.
 using ScanFn = std::function<int32_t(int mode, int64_t row_begin, int64_t row_end)>;
 
-// Walks rows [0, n) in chunks.  The first chunk (at most kCandCap rows) is written densely, one
-// slot per row; it is compacted to the best `keep`, whose worst value becomes the threshold.
-// Each later chunk appends only rows at or below the threshold and is sized so that the expected
-// number of appends (keep * chunk / rows_seen) is at most half the free room of a list; a list
-// that overflows all the same is flagged and its query is re-run with `safe` chunks, which are
-// no larger than the free room and therefore cannot overflow.
+// Rows per chunk after `seen` rows, for lists compacted to `keep` keys.  A chunk of g * seen rows appends
+// about keep * g keys to a list, with a relative spread of 1/sqrt(keep) (the threshold is the keep-th order
+// statistic of the rows seen); g is chosen so that the mean plus six such deviations still fits the free
+// room of a list.  level 1 divides g by 8 (for the rare query whose list overflowed all the same), level 2
+// uses chunks no larger than the free room, which cannot overflow whatever the row order.
+int64_t schedule_chunk(int64_t seen, int32_t keep, int level) {
+  const int64_t room = kCandCap - keep;
+  if (level >= 2) return room;
+  double g = (double)room / ((double)keep * (1.0 + 6.0 / sqrt((double)keep)));
+  if (level == 1) g /= 8.0;
+  return std::max<int64_t>(room, (int64_t)(g * (double)seen));
+}
+
+// Walks rows [0, n) in chunks.  The first chunk (at most kCandCap rows) is written densely, one slot per
+// row; it is compacted to the best `keep`, whose worst value becomes the threshold.  Each later chunk appends
+// only rows at or below the threshold (see schedule_chunk for its size).  A list that overflows is flagged
+// and its query is re-run at the next level.
 static int32_t run_schedule(Ctx* ctx, const ScanFn& scan, int64_t n, int64_t nq, int32_t keep,
-                            const CandLists& cand, bool safe) {
+                            const CandLists& cand, int level) {
   VSK_TRY(launch_init_cand(ctx, cand, nq));
   SelectArgs sel{};
   sel.cand = cand;
   sel.nq = nq;
   sel.keep = keep;
-  const int64_t room = kCandCap - keep;
   int64_t seen = std::min<int64_t>(n, kCandCap);
   VSK_TRY(scan(SCAN_DENSE, 0, seen));
   sel.dense_count = (int32_t)seen;
   VSK_TRY(launch_select(ctx, sel));
   sel.dense_count = -1;
   while (seen < n) {
-    int64_t chunk = safe ? room : std::max<int64_t>(room, seen * room / (2 * (int64_t)keep));
-    chunk = std::min(chunk, n - seen);
+    const int64_t chunk = std::min(schedule_chunk(seen, keep, level), n - seen);
     VSK_TRY(scan(SCAN_THRESHOLD, seen, seen + chunk));
     VSK_TRY(launch_select(ctx, sel));
     seen += chunk;
@@ -141,7 +151,7 @@ static int32_t flagged_queries(Ctx* ctx, const CandLists& cand, int64_t nq, std:
 // fp32 scan of `nq` queries (optionally the subset `sub_dev` of a larger batch) over n rows
 // described by `proto` (metric, operands, norms, masks), with final output.
 int32_t fp32_topk(Ctx* ctx, const ExactScanArgs& proto, int64_t n, int64_t nq, const int32_t* sub_dev, int32_t k,
-                  int64_t id_base, float* out_dist, int64_t* out_ids, bool safe) {
+                  int64_t id_base, float* out_dist, int64_t* out_ids, int level) {
   CandLists cand;
   VSK_TRY(cand_workspace(ctx, nq, &cand));
   ExactScanArgs a = proto;
@@ -154,7 +164,7 @@ int32_t fp32_topk(Ctx* ctx, const ExactScanArgs& proto, int64_t n, int64_t nq, c
     a.row_end = e;
     return launch_exact_scan(ctx, a);
   };
-  VSK_TRY(run_schedule(ctx, scan, n, nq, k, cand, safe));
+  VSK_TRY(run_schedule(ctx, scan, n, nq, k, cand, level));
   SelectArgs fin{};
   fin.cand = cand;
   fin.nq = nq;
@@ -168,7 +178,7 @@ int32_t fp32_topk(Ctx* ctx, const ExactScanArgs& proto, int64_t n, int64_t nq, c
   fin.q_subset = sub_dev;
   fin.final_sqrt = a.metric == VSK_METRIC_EUCLIDEAN;
   VSK_TRY(launch_select(ctx, fin));
-  if (!safe) {
+  if (level < 2) {
     std::vector<int32_t> bad;
     VSK_TRY(flagged_queries(ctx, cand, nq, &bad));
     if (!bad.empty()) {
@@ -179,11 +189,11 @@ int32_t fp32_topk(Ctx* ctx, const ExactScanArgs& proto, int64_t n, int64_t nq, c
         for (auto& b : bad) b = sub_h[b];
       }
       void* p;
-      VSK_TRY(scratch(ctx, SLOT_MISC0, bad.size() * sizeof(int32_t), &p));
+      VSK_TRY(scratch(ctx, level == 0 ? SLOT_MISC0 : SLOT_MISC1, bad.size() * sizeof(int32_t), &p));
       VSK_CUDA(ctx, cudaMemcpyAsync(p, bad.data(), bad.size() * sizeof(int32_t), cudaMemcpyHostToDevice, ctx->stream));
       VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
       ctx->stats.fallback_queries += (int64_t)bad.size();
-      VSK_TRY(fp32_topk(ctx, proto, n, (int64_t)bad.size(), (const int32_t*)p, k, id_base, out_dist, out_ids, true));
+      VSK_TRY(fp32_topk(ctx, proto, n, (int64_t)bad.size(), (const int32_t*)p, k, id_base, out_dist, out_ids, level + 1));
     }
   }
   return VSK_OK;
@@ -191,17 +201,23 @@ int32_t fp32_topk(Ctx* ctx, const ExactScanArgs& proto, int64_t n, int64_t nq, c
 
 static int32_t fp32_search(Index* ix, const float* q, int64_t nq, const int32_t* sub_dev, int32_t k,
                            const float* qnorm, const uint64_t* qmasks, float* out_dist, int64_t* out_ids,
-                           bool safe) {
+                           int level) {
   ExactScanArgs a{};
   a.metric = ix->metric;
   a.q = q;
   a.x = ix->rows;
+  if (ix->kind == INDEX_FLAT_I8) {
+    a.x = nullptr;
+    a.x_codes = ix->codes;
+    a.sq_scale = ix->sq_scale;
+    a.sq_offset = ix->sq_offset;
+  }
   a.dim = ix->dim;
   a.qnorm = qnorm;
   a.xnorm = ix->row_norm;
   a.row_masks = (qmasks && ix->has_masks) ? ix->masks : nullptr;
   a.q_masks = a.row_masks ? qmasks : nullptr;
-  return fp32_topk(ix->ctx, a, ix->n, nq, sub_dev, k, ix->id_base, out_dist, out_ids, safe);
+  return fp32_topk(ix->ctx, a, ix->n, nq, sub_dev, k, ix->id_base, out_dist, out_ids, level);
 }
 
 constexpr int64_t kQueryBatch = 16384;  // queries per pass: bounds the candidate workspace at 512 MB
@@ -232,7 +248,7 @@ static int32_t flat_search_dev(Index* ix, const float* q, int64_t nq, int32_t k,
     if (tensor) {
       VSK_TRY(tensor_search(ix, qb, bn, k, qnorm, out_dist + b * k, out_ids + b * k));
     } else {
-      VSK_TRY(fp32_search(ix, qb, bn, nullptr, k, qnorm, mb, out_dist + b * k, out_ids + b * k, false));
+      VSK_TRY(fp32_search(ix, qb, bn, nullptr, k, qnorm, mb, out_dist + b * k, out_ids + b * k, 0));
     }
   }
   VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
@@ -249,7 +265,7 @@ int32_t fp32_search_subset(Index* ix, const float* q, const std::vector<int32_t>
   VSK_CUDA(ctx, cudaMemcpyAsync(p, subset.data(), subset.size() * sizeof(int32_t), cudaMemcpyHostToDevice, ctx->stream));
   VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   ctx->stats.fallback_queries += (int64_t)subset.size();
-  return fp32_search(ix, q, (int64_t)subset.size(), (const int32_t*)p, k, qnorm, nullptr, out_dist, out_ids, false);
+  return fp32_search(ix, q, (int64_t)subset.size(), (const int32_t*)p, k, qnorm, nullptr, out_dist, out_ids, 0);
 }
 
 static int32_t flat_reserve(Index* ix, int64_t need) {

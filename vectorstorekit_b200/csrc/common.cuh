@@ -219,7 +219,9 @@ int32_t launch_init_cand(Ctx* ctx, const CandLists& c, int64_t nq);
 // Exact top-k of nq queries over n rows with the fp32 scan; `proto` carries metric, operands,
 // norms and masks.  Outputs are device pointers [nq][k] (indexed by sub_dev[pos] when given).
 int32_t fp32_topk(Ctx* ctx, const ExactScanArgs& proto, int64_t n, int64_t nq, const int32_t* sub_dev, int32_t k,
-                  int64_t id_base, float* out_dist, int64_t* out_ids, bool safe);
+                  int64_t id_base, float* out_dist, int64_t* out_ids, int level);
+// Rows of the next chunk of the search schedule (api.cu).
+int64_t schedule_chunk(int64_t seen, int32_t keep, int level);
 
 // ---- helpers in api.cu ---------------------------------------------------------------------
 int32_t dev_alloc(Ctx* ctx, void** p, size_t bytes);

@@ -366,7 +366,7 @@ int32_t ivf_search_dev(Index* ix, const float* q, int64_t nq, int32_t k, int32_t
     c.q = qb;
     c.x = ix->centroids;
     c.dim = ix->dim;
-    VSK_TRY(fp32_topk(ctx, c, ix->nlist, bn, nullptr, nprobe, 0, (float*)pd, (int64_t*)pi, false));
+    VSK_TRY(fp32_topk(ctx, c, ix->nlist, bn, nullptr, nprobe, 0, (float*)pd, (int64_t*)pi, 0));
     VSK_TRY(ivf_search_positions(ctx, ix, qb, bn, nullptr, (const int64_t*)pi, nprobe, k, out_dist + b * k,
                                  out_ids + b * k, false));
   }

@@ -177,6 +177,7 @@ int32_t sq8_add(Index* ix, const int8_t* codes, int64_t n, bool on_device) {
     ctx->stats.kernel_launches++;
   }
   ix->n += n;
+  tensor_invalidate(ix);
   VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   return VSK_OK;
 }
@@ -191,8 +192,14 @@ int32_t sq8_search_dev(Index* ix, const float* q, int64_t nq, int32_t k, float* 
   ctx->stats.searches++;
   ctx->stats.queries += nq;
   constexpr int64_t kBatch = 16384;
+  const bool tensor = ctx->search_path == VSK_PATH_TENSOR_RERANK &&
+                      (ix->metric == VSK_METRIC_DOT_PRODUCT || ix->metric == VSK_METRIC_EUCLIDEAN);
   for (int64_t b = 0; b < nq; b += kBatch) {
     const int64_t bn = std::min(kBatch, nq - b);
+    if (tensor) {
+      VSK_TRY(tensor_search(ix, q + b * ix->dim, bn, k, nullptr, out_dist + b * k, out_ids + b * k));
+      continue;
+    }
     ExactScanArgs a{};
     a.metric = ix->metric;
     a.q = q + b * ix->dim;
@@ -207,7 +214,7 @@ int32_t sq8_search_dev(Index* ix, const float* q, int64_t nq, int32_t k, float* 
       VSK_TRY(launch_row_norms(ctx, a.q, bn, ix->dim, 0, (float*)p));
       a.qnorm = (float*)p;
     }
-    VSK_TRY(fp32_topk(ctx, a, ix->n, bn, nullptr, k, ix->id_base, out_dist + b * k, out_ids + b * k, false));
+    VSK_TRY(fp32_topk(ctx, a, ix->n, bn, nullptr, k, ix->id_base, out_dist + b * k, out_ids + b * k, 0));
   }
   VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   return VSK_OK;

@@ -500,6 +500,106 @@ __global__ void bound_kernel(const float* __restrict__ qn16, const float* __rest
   eps[q] = r * 1.0001f + 1e-30f;
 }
 
+// ---- int8-coded rows -----------------------------------------------------------------------
+// One warp per row of int8 codes: the fp16 operand row is the code itself (exact: |code| <= 128), so the
+// operand residual of the rows is zero.  aux = |x^|^2 of the dequantised row x^ = (code - offset)/scale
+// (euclidean); stats: max |code row|, max |x^|.
+__global__ void prep_codes_kernel(const int8_t* __restrict__ codes, int64_t n, int dim, int dim16,
+                                  const float* __restrict__ scale, const float* __restrict__ offset,
+                                  __half* __restrict__ out, float* __restrict__ aux, PrepStats* stats) {
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= n) return;
+  const int lane = threadIdx.x & 31;
+  const int8_t* p = codes + row * dim;
+  float c2 = 0.f, x2 = 0.f;
+  for (int i = lane; i < dim16; i += 32) {
+    float c = 0.f;
+    if (i < dim) {
+      c = (float)p[i];
+      const float xh = __fdiv_rn(__fsub_rn(c, __ldg(offset + i)), __ldg(scale + i));
+      x2 = fmaf(xh, xh, x2);
+    }
+    out[row * dim16 + i] = __float2half_rn(c);
+    c2 = fmaf(c, c, c2);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    c2 += __shfl_xor_sync(0xffffffffu, c2, o);
+    x2 += __shfl_xor_sync(0xffffffffu, x2, o);
+  }
+  if (lane == 0) {
+    const float up = 1.0f + 1e-5f;
+    aux[row] = x2;
+    atomicMax(&stats->max_norm16, __float_as_uint(sqrtf(c2) * up));
+    atomicMax(&stats->max_norm, __float_as_uint(sqrtf(x2) * up));
+  }
+}
+
+// q~ = q / scale per dimension: sum_i q_i x^_i = sum_i q~_i code_i - sum_i q_i offset_i / scale_i, and the
+// second term does not depend on the row.
+__global__ void scale_queries_kernel(const float* __restrict__ q, int64_t total, int dim,
+                                     const float* __restrict__ scale, float* __restrict__ out) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < total) out[i] = __fdiv_rn(q[i], __ldg(scale + (int)(i % dim)));
+}
+
+// eps for int8-coded rows (operand residual of the rows is zero; the query operand is fp16(s_q q~)):
+//   contraction   |e_q| C + dim16 2^-22 |q'| C, divided by s_q          (C = max |code row|)
+//   formula       2^-22 (|q| max|x^| + |q~| C): fp32 rounding of x^ = (code - offset)/scale and of q~
+// doubled for euclidean (value = |x^|^2 - 2 q.x^) plus the rounding of |x^|^2 and of the final multiply-add.
+template <int METRIC>
+__global__ void bound_i8_kernel(const float* __restrict__ qn16, const float* __restrict__ qe16,
+                                const float* __restrict__ qt_norm, const float* __restrict__ q_norm, int64_t nq,
+                                const float* scale_q, BoundConsts c, float* __restrict__ eps, float* alpha) {
+  const int64_t q = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const float inv = 1.0f / (*scale_q);
+  if (q == 0) *alpha = (METRIC == VSK_METRIC_EUCLIDEAN ? -2.0f : -1.0f) * inv;
+  if (q >= nq) return;
+  const float a = qn16[q], e = qe16[q];
+  float dot_err = (e * c.max_norm16 + (float)c.dim16 * 2.3841858e-7f * a * c.max_norm16) * inv;
+  dot_err += 2.3841858e-7f * (q_norm[q] * c.max_norm + qt_norm[q] * c.max_norm16);
+  float r = dot_err;
+  if (METRIC == VSK_METRIC_EUCLIDEAN)
+    r = 2.0f * dot_err + 4.0f * 5.9604645e-8f * (float)c.dim16 * c.max_norm * c.max_norm +
+        2.0f * 5.9604645e-8f * (c.max_norm * c.max_norm + 2.0f * q_norm[q] * c.max_norm);
+  eps[q] = r * 1.0001f + 1e-30f;
+}
+
+// Exact re-scoring against dequantised rows (the int8 scan's definition: the metric between the fp32 query
+// and x^ = (code - offset)/scale, ScalarQuantizer.swift:576-578).
+template <int METRIC>
+__global__ void __launch_bounds__(256) rerank_i8_kernel(const float* __restrict__ q, const int8_t* __restrict__ codes,
+                                                        int dim, const float* __restrict__ scale,
+                                                        const float* __restrict__ offset, CandLists cand,
+                                                        unsigned long long* total) {
+  extern __shared__ float qs[];
+  const int64_t qi = blockIdx.x;
+  const int cnt = min(cand.count[qi], kCandCap);
+  uint64_t* keys = cand.keys + qi * kCandCap;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) qs[i] = q[qi * dim + i];
+  if (threadIdx.x == 0) atomicAdd(total, (unsigned long long)cnt);
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  for (int c = warp; c < cnt; c += nwarps) {
+    const uint32_t id = (uint32_t)keys[c];
+    const int8_t* xr = codes + (int64_t)id * dim;
+    float s = 0.f;
+    for (int i = lane; i < dim; i += 32) {
+      const float xv = __fdiv_rn(__fsub_rn((float)xr[i], __ldg(offset + i)), __ldg(scale + i));
+      const float qv = qs[i];
+      if (METRIC == VSK_METRIC_EUCLIDEAN) {
+        const float d = qv - xv;
+        s = fmaf(d, d, s);
+      } else {
+        s = fmaf(qv, xv, s);
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) keys[c] = make_key(METRIC == VSK_METRIC_EUCLIDEAN ? s : -s, id);
+  }
+}
+
 // ---- exact rerank -------------------------------------------------------------------------
 // One CTA per query: replaces every kept candidate's coarse value with the reference's direct fp32 value:
 //   euclidean sum (q-x)^2 (rooted at output), cosine 1 - q.x/(|q||x| + 1e-8), dotProduct -(q.x).
@@ -599,6 +699,13 @@ int32_t tensor_prepare(Index* ix) {
   PrepStats init{0u, 0u, 0u, 0u, 0x7f800000u};
   VSK_CUDA(ctx, cudaMemcpyAsync(st, &init, sizeof(init), cudaMemcpyHostToDevice, ctx->stream));
   const bool cosine = ix->metric == VSK_METRIC_COSINE;
+  if (ix->kind == INDEX_FLAT_I8) {
+    const float one = 1.0f;
+    VSK_CUDA(ctx, cudaMemcpyAsync(scale, &one, 4, cudaMemcpyHostToDevice, ctx->stream));
+    prep_codes_kernel<<<(unsigned)ceil_div(ix->n, 8), 256, 0, ctx->stream>>>(ix->codes, ix->n, ix->dim, ix->dim16, ix->sq_scale,
+                                                                            ix->sq_offset, ix->rows16, ix->row_aux, st);
+    ctx->stats.kernel_launches++;
+  } else {
   if (!cosine) {
     absmax_kernel<<<1184, 256, 0, ctx->stream>>>(ix->rows, ix->n * (int64_t)ix->dim, &st->absmax);
     ctx->stats.kernel_launches++;
@@ -615,6 +722,7 @@ int32_t tensor_prepare(Index* ix) {
     default:
       launch_prep<VSK_METRIC_DOT_PRODUCT>(ctx, ix->rows, ix->n, ix->dim, ix->dim16, scale, ix->rows16, ix->row_aux, nullptr, nullptr, nullptr, st);
       break;
+  }
   }
   VSK_CUDA(ctx, cudaGetLastError());
   PrepStats h;
@@ -681,14 +789,36 @@ int32_t tensor_search(Index* ix, const float* q, int64_t nq, int32_t k, const fl
   unsigned long long* rr_total = (unsigned long long*)((char*)p + 16);
   VSK_CUDA(ctx, cudaMemsetAsync(p, 0, 64, ctx->stream));
   const bool cosine = metric == VSK_METRIC_COSINE;
+  const bool i8 = ix->kind == INDEX_FLAT_I8;
+  if (i8 && metric != VSK_METRIC_EUCLIDEAN && metric != VSK_METRIC_DOT_PRODUCT)
+    return fail(ctx, VSK_ERR_UNSUPPORTED_OPERATION, "the tensor path over int8 codes covers euclidean and dotProduct");
+  const float* qsrc = q;   // what the query operand is made from
+  float* q_true_norm = nullptr;
+  if (i8) {
+    VSK_TRY(scratch(ctx, SLOT_TC_C, (size_t)nq * dim * sizeof(float), &p));
+    float* qt = (float*)p;
+    scale_queries_kernel<<<(unsigned)ceil_div(nq * (int64_t)dim, 256), 256, 0, ctx->stream>>>(q, nq * (int64_t)dim, dim, ix->sq_scale, qt);
+    ctx->stats.kernel_launches++;
+    qsrc = qt;
+    VSK_TRY(scratch(ctx, SLOT_TC_D, (size_t)nq * sizeof(float), &p));
+    q_true_norm = (float*)p;
+    VSK_TRY(launch_row_norms(ctx, q, nq, dim, 0, q_true_norm));
+  }
   if (!cosine) {
-    absmax_kernel<<<296, 256, 0, ctx->stream>>>(q, nq * (int64_t)dim, q_absmax);
+    absmax_kernel<<<296, 256, 0, ctx->stream>>>(qsrc, nq * (int64_t)dim, q_absmax);
     ctx->stats.kernel_launches++;
   }
   choose_scale_kernel<<<1, 1, 0, ctx->stream>>>(q_absmax, cosine ? 1 : 0, q_scale);
   ctx->stats.kernel_launches++;
   BoundConsts bc{ix->scale16, ix->max_xnorm16, ix->max_xerr16, ix->max_xnorm, ix->min_xnorm_nz, dim16};
   const unsigned bgrid = (unsigned)ceil_div(nq, 256);
+  if (i8) {
+    launch_prep<VSK_METRIC_DOT_PRODUCT>(ctx, qsrc, nq, dim, dim16, q_scale, q16, nullptr, qn16, qe16, qn_tmp, nullptr);
+    if (metric == VSK_METRIC_EUCLIDEAN)
+      bound_i8_kernel<VSK_METRIC_EUCLIDEAN><<<bgrid, 256, 0, ctx->stream>>>(qn16, qe16, qn_tmp, q_true_norm, nq, q_scale, bc, eps, alpha);
+    else
+      bound_i8_kernel<VSK_METRIC_DOT_PRODUCT><<<bgrid, 256, 0, ctx->stream>>>(qn16, qe16, qn_tmp, q_true_norm, nq, q_scale, bc, eps, alpha);
+  } else
   switch (metric) {
     case VSK_METRIC_EUCLIDEAN:
       launch_prep<VSK_METRIC_EUCLIDEAN>(ctx, q, nq, dim, dim16, q_scale, q16, nullptr, qn16, qe16, qn_tmp, nullptr);
@@ -750,11 +880,10 @@ int32_t tensor_search(Index* ix, const float* q, int64_t nq, int32_t k, const fl
   sel.dense_count = -1;
   a.mode = SCAN_THRESHOLD;
   while (seen < n) {
-    // Expected appends per query in a chunk are keep * chunk / seen.  Half the free room of a list
-    // bounds the chunk from above; below that, chunks grow geometrically (each no larger than three
-    // times the rows seen so far), which keeps the share of rows scanned under a loose threshold small:
-    // the epilogue's append path costs far more than its filter path.
-    int64_t chunk = std::max<int64_t>(room, seen * room / (2 * (int64_t)keep));
+    // schedule_chunk bounds the chunk so that a list cannot plausibly overflow; below that bound chunks
+    // grow geometrically (each no larger than three times the rows seen so far), which keeps the share of
+    // rows scanned under a loose threshold small: the epilogue's append path costs far more than its filter.
+    int64_t chunk = schedule_chunk(seen, keep, 0);
     chunk = std::min<int64_t>(chunk, std::max<int64_t>(room, 3 * seen));
     chunk = std::max<int64_t>(TN, chunk / TN * TN);   // whole row tiles
     chunk = std::min(chunk, n - seen);
@@ -775,6 +904,13 @@ int32_t tensor_search(Index* ix, const float* q, int64_t nq, int32_t k, const fl
       VSK_CUDA(ctx, cudaFuncSetAttribute(rerank_kernel<M_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)qsm)); \
     rerank_kernel<M_><<<(unsigned)nq, 256, qsm, ctx->stream>>>(q, ix->rows, dim, qnorm, ix->row_norm, cand, rr_total); \
   } while (0)
+  if (i8) {
+    if (qsm > 48 * 1024) return fail(ctx, VSK_ERR_INVALID_BUFFER_SIZE, "dimension %d is too large for the int8 rerank kernel", dim);
+    if (metric == VSK_METRIC_EUCLIDEAN)
+      rerank_i8_kernel<VSK_METRIC_EUCLIDEAN><<<(unsigned)nq, 256, qsm, ctx->stream>>>(q, ix->codes, dim, ix->sq_scale, ix->sq_offset, cand, rr_total);
+    else
+      rerank_i8_kernel<VSK_METRIC_DOT_PRODUCT><<<(unsigned)nq, 256, qsm, ctx->stream>>>(q, ix->codes, dim, ix->sq_scale, ix->sq_offset, cand, rr_total);
+  } else
   switch (metric) {
     case VSK_METRIC_EUCLIDEAN: VSK_RERANK(VSK_METRIC_EUCLIDEAN); break;
     case VSK_METRIC_COSINE: VSK_RERANK(VSK_METRIC_COSINE); break;

@@ -134,9 +134,12 @@ def _host(a, dtype):
 
 
 def _ptr(a):
+    """Address of an array for the C ABI.  The library works on its own CUDA stream, which does not wait for
+    torch's: a CUDA tensor is handed over only after the torch stream that produced it has drained."""
     if a is None:
         return None
     if _is_dev(a):
+        torch.cuda.current_stream(a.device).synchronize()
         return C.c_void_p(a.data_ptr())
     return C.c_void_p(a.ctypes.data)
 
