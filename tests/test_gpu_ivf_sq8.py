@@ -40,7 +40,8 @@ def test_kmeans_golden_shader_steps(vsk, dev):
     assert np.array_equal(asg, GOLD["km_assign3"])
 
 
-@pytest.mark.parametrize("shape", [(500, 12, 9, 4), (20_000, 128, 64, 5), (5000, 33, 300, 3)])
+@pytest.mark.parametrize("shape", [(500, 12, 9, 4), (20_000, 128, 64, 5), (5000, 33, 300, 3), (100_000, 128, 256, 3),
+                                   (60_000, 40, 100, 2)])
 def test_kmeans_vs_oracle(vsk, dev, cpu_oracle, shape):
     n, d, k, iters = shape
     rng = np.random.default_rng(n + d)
@@ -54,6 +55,26 @@ def test_kmeans_vs_oracle(vsk, dev, cpu_oracle, shape):
     assert agree > 0.999, agree
     assert np.max(np.abs(cent - rc)) < 1e-3
     assert abs(inertia - rin) <= 1e-3 * abs(rin)
+
+
+def test_tensor_assign_equals_fp32_assign(vsk, dev):
+    """The tensor-core assignment (coarse arg-min, near-tie lists, exact decision) against the fp32 tile on the
+    same inputs, including exact duplicates of centroids among the rows and duplicate centroids."""
+    import torch
+    g = torch.Generator(device="cuda").manual_seed(3)
+    x = torch.randn((200_000, 96), generator=g, device="cuda")
+    c = torch.randn((500, 96), generator=g, device="cuda")
+    c[7] = c[3]                      # duplicate centroid: the lower index must win
+    x[:500] = c                      # rows that coincide with centroids
+    km = vsk.KMeansClustering(dev)
+    dev.set_search_path(vsk.PATH_FP32_SCAN)
+    a0, d0 = km.assign(x, c)
+    dev.set_search_path(vsk.PATH_TENSOR_RERANK)
+    a1, d1 = km.assign(x, c)
+    a0, a1, d0, d1 = (t.cpu().numpy() for t in (a0, a1, d0, d1))
+    assert np.mean(a0 == a1) > 0.9999
+    assert np.allclose(d0, d1, rtol=1e-4, atol=1e-4)
+    assert a1[7] == 3 and a1[3] == 3 and np.array_equal(a1[:500][np.arange(500) != 7], np.arange(500)[np.arange(500) != 7])
 
 
 def test_kmeans_convergence_and_errors(vsk, dev, cpu_oracle):

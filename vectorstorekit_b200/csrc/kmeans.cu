@@ -13,6 +13,7 @@
 //   empty       an empty cluster keeps its previous centroid (ClusteringShaders.metal:171-176)
 //   inertia     sum of the un-squared distances (KMeansClustering.swift:97), reduced in fp64
 #include "common.cuh"
+#include "tensor_scan.cuh"
 
 namespace vsk {
 namespace {
@@ -78,9 +79,30 @@ __global__ void sum_final_kernel(const double* partial, int np, float* out) {
 
 }  // namespace
 
+int32_t assign_rows_fp32(Ctx* ctx, const float* rows, int64_t n, int32_t dim, const float* centroids, int32_t k,
+                         int32_t* assign, float* dist);
+
 // Nearest centroid (and rooted distance) of every row.
+static bool use_tensor_assign(const Ctx* ctx, int64_t n, int32_t k) {
+  // the tensor path pays for making fp16 operands; tiny problems stay on the fp32 tile
+  return ctx->search_path == VSK_PATH_TENSOR_RERANK && n * (int64_t)k >= (1ll << 22) && n >= 1024;
+}
+
 int32_t assign_rows(Ctx* ctx, const float* rows, int64_t n, int32_t dim, const float* centroids, int32_t k,
                     int32_t* assign, float* dist) {
+  if (use_tensor_assign(ctx, n, k)) {
+    TensorAssign ta;
+    int32_t st = tensor_assign_prepare(ctx, rows, n, dim, &ta);
+    if (st == VSK_OK) st = tensor_assign(ctx, &ta, rows, centroids, k, assign, dist);
+    if (st == VSK_OK && cudaStreamSynchronize(ctx->stream) != cudaSuccess) st = VSK_ERR_EXECUTION_FAILED;
+    tensor_assign_release(&ta);
+    return st;
+  }
+  return assign_rows_fp32(ctx, rows, n, dim, centroids, k, assign, dist);
+}
+
+int32_t assign_rows_fp32(Ctx* ctx, const float* rows, int64_t n, int32_t dim, const float* centroids, int32_t k,
+                         int32_t* assign, float* dist) {
   void* best;
   VSK_TRY(scratch(ctx, SLOT_MISC4, (size_t)n * sizeof(unsigned long long), &best));
   VSK_CUDA(ctx, cudaMemsetAsync(best, 0xff, (size_t)n * sizeof(unsigned long long), ctx->stream));
@@ -163,8 +185,16 @@ int32_t kmeans_dev(Ctx* ctx, const float* rows, int64_t n, int32_t dim, int32_t 
   float prev = INFINITY, last = INFINITY;
   int it = 0;
   bool converged = false;
+  TensorAssign ta;
+  const bool tc = use_tensor_assign(ctx, n, k);
+  struct Release {
+    TensorAssign* t;
+    ~Release() { tensor_assign_release(t); }
+  } release{&ta};
+  if (tc) VSK_TRY(tensor_assign_prepare(ctx, rows, n, dim, &ta));
   while (it < max_iters && !converged) {
-    VSK_TRY(assign_rows(ctx, rows, n, dim, (const float*)cur, k, assign, (float*)dist));
+    if (tc) VSK_TRY(tensor_assign(ctx, &ta, rows, (const float*)cur, k, assign, (float*)dist));
+    else VSK_TRY(assign_rows_fp32(ctx, rows, n, dim, (const float*)cur, k, assign, (float*)dist));
     VSK_TRY(launch_stable_group(ctx, assign, n, k, (int32_t*)order, (int64_t*)offsets));
     centroid_update_kernel<<<k, 128, 0, ctx->stream>>>(rows, dim, (const int32_t*)order, (const int64_t*)offsets,
                                                        (const float*)cur, (float*)nxt);

@@ -66,6 +66,10 @@ struct TcArgs {
   const float* alpha;         // device scalar: value = alpha * acc + beta[row]
   const float* beta;          // [n] or null (treated as 0)
   CandLists cand;
+  int32_t cap;                // keys per candidate list (SCAN_THRESHOLD)
+  unsigned long long* best;   // SCAN_ARGMIN: [nq] smallest (value, row) key, pre-set to all ones
+  int32_t row_tile_fastest;   // tile order: 0 = query tile fastest (rows are the operand streamed once),
+                              //             1 = row tile fastest (the "queries" are the operand streamed once)
   int32_t* err;               // device error word
 };
 
@@ -209,7 +213,8 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       uint32_t issued_ph = 0;    // ... with this full-barrier parity
       bool ok = true;
       for (int64_t t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
-        const int64_t nt = t / qtiles, qt = t - nt * qtiles;
+        const int64_t nt = a.row_tile_fastest ? t % ntiles : t / qtiles;
+        const int64_t qt = a.row_tile_fastest ? t / ntiles : t - nt * qtiles;
         const int32_t qrow = (int32_t)(qt * TM);
         const int32_t xrow = (int32_t)(a.row_begin + nt * TN);
         for (int kb = 0; kb < a.kblocks; ++kb) {
@@ -276,7 +281,8 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     for (int64_t t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++local) {
       const int acc = (int)(local & 1);
       const uint32_t aph = (uint32_t)((local >> 1) & 1);
-      const int64_t nt = t / qtiles, qt = t - nt * qtiles;
+      const int64_t nt = a.row_tile_fastest ? t % ntiles : t / qtiles;
+      const int64_t qt = a.row_tile_fastest ? t / ntiles : t - nt * qtiles;
       const int64_t q = qt * TM + et;
       const int64_t n0 = a.row_begin + nt * TN;
       const bool qok = q < a.nq;
@@ -307,6 +313,22 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             if (nc + j < a.row_end) dst[j] = make_key(val, (uint32_t)(nc + j));
           }
         }
+      } else if (MODE == SCAN_ARGMIN) {
+        // smallest (value, row) key of this query over the tile's 256 rows, merged into best[q]
+        float bv = CUDART_INF_F;
+        int bj = 0;
+#pragma unroll 1
+        for (int c = 0; c < TN / 32; ++c) {
+          float v[32];
+          tc_ld32(trow + (uint32_t)(c * 32), v);
+          const int64_t left = a.row_end - (n0 + c * 32);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float val = HAS_BETA ? fmaf(v[j], alpha, sm->beta[acc][quarter][c * 32 + j]) : v[j] * alpha;
+            if (j < left && val < bv) { bv = val; bj = c * 32 + j; }   // strict '<': the lowest row wins ties
+          }
+        }
+        if (qok && bv < CUDART_INF_F) atomicMin(a.best + q, (unsigned long long)make_key(bv, (uint32_t)(n0 + bj)));
       } else {
         // Pass 1: which of this query's 256 values pass the threshold (one bit each).  A thread then
         // reserves all its slots with ONE atomic per tile; pass 2 re-reads the accumulator groups that
@@ -341,13 +363,13 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           float v[32];
           tc_ld32(trow + (uint32_t)(c * 32), v);
           const int64_t nc = n0 + c * 32;
-          uint64_t* dst = a.cand.keys + q * kCandCap;
+          uint64_t* dst = a.cand.keys + q * a.cap;
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             if ((bits >> j) & 1u) {
               const float val = HAS_BETA ? fmaf(v[j], alpha, sm->beta[acc][quarter][c * 32 + j]) : v[j] * alpha;
               const int pos = base + __popc(bits & ((1u << j) - 1u));
-              if (pos < kCandCap) dst[pos] = make_key(val, (uint32_t)(nc + j));
+              if (pos < a.cap) dst[pos] = make_key(val, (uint32_t)(nc + j));
             }
           }
           base += __popc(bits);
@@ -742,7 +764,7 @@ int32_t tensor_prepare(Index* ix) {
 
 template <int MODE>
 int32_t launch_tc(Ctx* ctx, const CUtensorMap& mq, const CUtensorMap& mx, const TcArgs& a, bool has_beta) {
-  static bool attr_done[2][2] = {};
+  static bool attr_done[4][2] = {};
   auto kern = has_beta ? tc_scan_kernel<MODE, true> : tc_scan_kernel<MODE, false>;
   if (!attr_done[MODE][has_beta]) {
     VSK_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_BYTES));
@@ -758,6 +780,86 @@ int32_t launch_tc(Ctx* ctx, const CUtensorMap& mq, const CUtensorMap& mx, const 
   ctx->stats.tensor_tiles += tiles;
   VSK_CUDA(ctx, cudaGetLastError());
   return VSK_OK;
+}
+
+
+// ---- k-means assignment on the tensor cores ----------------------------------------------------
+// Data rows are the streamed operand (the "query" side of the tile), centroids the small one.
+//   pass 1  coarse arg-min: best[row] = smallest coarse (|c|^2 - 2 x.c, centroid) key
+//   pass 2  every centroid whose coarse value is within 2 eps(row) of that minimum is appended to the
+//           row's short list (the true nearest centroid is among them: its exact value is <= the exact
+//           value of the coarse winner <= coarse minimum + eps, so its coarse value <= minimum + 2 eps)
+//   exact   the listed centroids are compared with the direct fp32 formula sum (x-c)^2; the smallest
+//           (value, index) wins, as the reference's strict '<' scan does (KMeansClustering.swift:283-288)
+// A row whose list overflows (more than kAssignCap near-ties) is re-done by the fp32 tile.
+constexpr int kAssignCap = 8;
+
+// eps per data row against the current centroids; stats of the centroid operand are read on the device.
+__global__ void assign_bound_kernel(const float* __restrict__ xn16, const float* __restrict__ xe16,
+                                    const float* __restrict__ xnorm, int64_t n, const float* scale_x,
+                                    const float* scale_c, const PrepStats* cs, int dim16, float* __restrict__ eps,
+                                    float* alpha) {
+  const int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const float inv = 1.0f / ((*scale_x) * (*scale_c));
+  if (r == 0) *alpha = -2.0f * inv;
+  if (r >= n) return;
+  const float C16 = __uint_as_float(cs->max_norm16), E16 = __uint_as_float(cs->max_err16);
+  const float Cn = __uint_as_float(cs->max_norm);
+  const float a = xn16[r], e = xe16[r];
+  const float dot_err = ((a * E16 + e * C16 + e * E16) + (float)dim16 * 2.3841858e-7f * a * C16) * inv;
+  const float v = 2.0f * dot_err + 4.0f * 5.9604645e-8f * (float)dim16 * Cn * Cn +
+                  2.0f * 5.9604645e-8f * (Cn * Cn + 2.0f * xnorm[r] * Cn);
+  eps[r] = v * 1.0001f + 1e-30f;
+}
+
+__global__ void assign_threshold_kernel(const unsigned long long* __restrict__ best, const float* __restrict__ eps,
+                                        int64_t n, float* __restrict__ thr, int32_t* __restrict__ count) {
+  const int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= n) return;
+  thr[r] = ordered_to_float((uint32_t)(best[r] >> 32)) + 2.0f * eps[r];
+  count[r] = 0;
+}
+
+// one warp per data row: exact squared distances to the listed centroids
+__global__ void assign_exact_kernel(const float* __restrict__ x, int64_t n, int dim, const float* __restrict__ cent,
+                                    const uint64_t* __restrict__ keys, const int32_t* __restrict__ count,
+                                    int32_t* __restrict__ assign, float* __restrict__ dist, int32_t* __restrict__ bad_rows,
+                                    int32_t* bad_count) {
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= n) return;
+  const int lane = threadIdx.x & 31;
+  const int cnt = count[row];
+  if (cnt > kAssignCap || cnt <= 0) {
+    if (lane == 0) bad_rows[atomicAdd(bad_count, 1)] = (int32_t)row;
+    return;
+  }
+  const float* xr = x + row * dim;
+  uint64_t bestk = kEmptyKey;
+  for (int c = 0; c < cnt; ++c) {
+    const uint32_t id = (uint32_t)keys[row * kAssignCap + c];
+    const float* cr = cent + (int64_t)id * dim;
+    float s = 0.f;
+    for (int i = lane; i < dim; i += 32) {
+      const float d = __ldg(xr + i) - __ldg(cr + i);
+      s = fmaf(d, d, s);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    bestk = min(bestk, make_key(s, id));
+  }
+  if (lane == 0) {
+    assign[row] = (int32_t)(uint32_t)bestk;
+    if (dist) dist[row] = sqrtf(ordered_to_float((uint32_t)(bestk >> 32)));
+  }
+}
+
+__global__ void scatter_best_kernel(const unsigned long long* __restrict__ best, const int32_t* __restrict__ rows,
+                                    int64_t m, int32_t* __restrict__ assign, float* __restrict__ dist) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= m) return;
+  const unsigned long long b = best[i];
+  assign[rows[i]] = (int32_t)(uint32_t)b;
+  if (dist) dist[rows[i]] = sqrtf(ordered_to_float((uint32_t)(b >> 32)));
 }
 
 }  // namespace
@@ -859,6 +961,7 @@ int32_t tensor_search(Index* ix, const float* q, int64_t nq, int32_t k, const fl
   a.alpha = alpha;
   a.beta = metric == VSK_METRIC_EUCLIDEAN ? ix->row_aux : nullptr;
   a.cand = cand;
+  a.cap = kCandCap;
   a.err = err;
   const bool has_beta = a.beta != nullptr;
   SelectArgs sel{};
@@ -947,6 +1050,123 @@ int32_t tensor_search(Index* ix, const float* q, int64_t nq, int32_t k, const fl
   for (int64_t i = 0; i < nq; ++i)
     if (flags[i]) bad.push_back((int32_t)i);
   if (!bad.empty()) VSK_TRY(fp32_search_subset(ix, q, bad, k, qnorm, out_dist, out_ids));
+  return VSK_OK;
+}
+
+
+// ---- public: tensor-core nearest-centroid assignment (used by kmeans.cu) ---------------------------
+int32_t tensor_assign_prepare(Ctx* ctx, const float* rows, int64_t n, int32_t dim, TensorAssign* ta) {
+  ta->n = n;
+  ta->dim = dim;
+  ta->dim16 = (int32_t)(ceil_div(dim, TK) * TK);
+  VSK_TRY(dev_alloc(ctx, (void**)&ta->rows16, (size_t)n * ta->dim16 * sizeof(__half)));
+  VSK_TRY(dev_alloc(ctx, (void**)&ta->stats, (size_t)n * 4 * sizeof(float)));
+  VSK_TRY(dev_alloc(ctx, (void**)&ta->keys, (size_t)n * kAssignCap * sizeof(uint64_t)));
+  VSK_TRY(dev_alloc(ctx, (void**)&ta->best, (size_t)n * sizeof(unsigned long long)));
+  VSK_TRY(dev_alloc(ctx, (void**)&ta->count, (size_t)n * sizeof(int32_t)));
+  VSK_TRY(dev_alloc(ctx, (void**)&ta->thr, (size_t)n * sizeof(float)));
+  VSK_TRY(dev_alloc(ctx, (void**)&ta->bad_rows, (size_t)n * sizeof(int32_t)));
+  VSK_TRY(dev_alloc(ctx, (void**)&ta->small, 256));
+  VSK_CUDA(ctx, cudaMemsetAsync(ta->small, 0, 256, ctx->stream));
+  // small: [0] absmax(rows) [1] scale_x [2] absmax(cent) [3] scale_c [4] alpha [5] err [6] bad_count, then PrepStats at +64
+  unsigned* sm = (unsigned*)ta->small;
+  absmax_kernel<<<1184, 256, 0, ctx->stream>>>(rows, n * (int64_t)dim, sm + 0);
+  choose_scale_kernel<<<1, 1, 0, ctx->stream>>>(sm + 0, 0, (float*)sm + 1);
+  float* st = (float*)ta->stats;
+  launch_prep<VSK_METRIC_DOT_PRODUCT>(ctx, rows, n, dim, ta->dim16, (float*)sm + 1, ta->rows16, nullptr, st, st + n, st + 2 * n, nullptr);
+  ctx->stats.kernel_launches += 2;
+  VSK_CUDA(ctx, cudaGetLastError());
+  VSK_TRY(make_map(ctx, ta->rows16, n, ta->dim16, TM, (CUtensorMap*)ta->map_rows));
+  return VSK_OK;
+}
+
+void tensor_assign_release(TensorAssign* ta) {
+  dev_free(ta->rows16); dev_free(ta->stats); dev_free(ta->keys); dev_free(ta->best); dev_free(ta->count);
+  dev_free(ta->thr); dev_free(ta->bad_rows); dev_free(ta->small);
+  *ta = TensorAssign{};
+}
+
+int32_t tensor_assign(Ctx* ctx, TensorAssign* ta, const float* rows, const float* centroids, int32_t k,
+                      int32_t* assign, float* dist) {
+  static_assert(sizeof(CUtensorMap) <= sizeof(ta->map_rows), "tensor map storage too small");
+  const int64_t n = ta->n;
+  const int dim = ta->dim, dim16 = ta->dim16;
+  unsigned* sm = (unsigned*)ta->small;
+  float* fsm = (float*)ta->small;
+  PrepStats* cs = (PrepStats*)((char*)ta->small + 64);
+  float* st = (float*)ta->stats;
+  float* eps = st + 3 * n;
+  // centroid operand: fp16 rows, |c|^2, stats
+  void* p;
+  VSK_TRY(scratch(ctx, SLOT_TC_C, (size_t)k * dim16 * sizeof(__half), &p));
+  __half* c16 = (__half*)p;
+  VSK_TRY(scratch(ctx, SLOT_TC_D, (size_t)k * sizeof(float), &p));
+  float* caux = (float*)p;
+  PrepStats init{0u, 0u, 0u, 0u, 0x7f800000u};
+  VSK_CUDA(ctx, cudaMemcpyAsync(cs, &init, sizeof(init), cudaMemcpyHostToDevice, ctx->stream));
+  VSK_CUDA(ctx, cudaMemsetAsync(sm + 2, 0, 4, ctx->stream));
+  VSK_CUDA(ctx, cudaMemsetAsync(sm + 5, 0, 8, ctx->stream));
+  absmax_kernel<<<64, 256, 0, ctx->stream>>>(centroids, (int64_t)k * dim, sm + 2);
+  choose_scale_kernel<<<1, 1, 0, ctx->stream>>>(sm + 2, 0, fsm + 3);
+  launch_prep<VSK_METRIC_EUCLIDEAN>(ctx, centroids, k, dim, dim16, fsm + 3, c16, caux, nullptr, nullptr, nullptr, cs);
+  assign_bound_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, ctx->stream>>>(st, st + n, st + 2 * n, n, fsm + 1, fsm + 3, cs, dim16, eps, fsm + 4);
+  ctx->stats.kernel_launches += 3;
+  VSK_CUDA(ctx, cudaGetLastError());
+  CUtensorMap mc;
+  VSK_TRY(make_map(ctx, c16, k, dim16, TN, &mc));
+  const CUtensorMap& mr = *(const CUtensorMap*)ta->map_rows;
+
+  TcArgs a{};
+  a.nq = n;
+  a.row_begin = 0;
+  a.row_end = k;
+  a.kblocks = dim16 / TK;
+  a.alpha = fsm + 4;
+  a.beta = caux;
+  a.row_tile_fastest = 1;
+  a.err = (int32_t*)(sm + 5);
+  a.best = ta->best;
+  a.cap = kAssignCap;
+  a.cand.keys = ta->keys;
+  a.cand.count = ta->count;
+  a.cand.thr = ta->thr;
+  a.cand.flags = nullptr;
+  a.cand.nq = n;
+  VSK_CUDA(ctx, cudaMemsetAsync(ta->best, 0xff, (size_t)n * sizeof(unsigned long long), ctx->stream));
+  a.mode = SCAN_ARGMIN;
+  VSK_TRY(launch_tc<SCAN_ARGMIN>(ctx, mr, mc, a, true));
+  assign_threshold_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, ctx->stream>>>(ta->best, eps, n, ta->thr, ta->count);
+  a.mode = SCAN_THRESHOLD;
+  VSK_TRY(launch_tc<SCAN_THRESHOLD>(ctx, mr, mc, a, true));
+  assign_exact_kernel<<<(unsigned)ceil_div(n, 8), 256, 0, ctx->stream>>>(rows, n, dim, centroids, ta->keys, ta->count, assign, dist,
+                                                                         ta->bad_rows, (int32_t*)(sm + 6));
+  ctx->stats.kernel_launches += 2;
+  VSK_CUDA(ctx, cudaGetLastError());
+  int32_t h[2] = {0, 0};
+  VSK_CUDA(ctx, cudaMemcpyAsync(h, sm + 5, 8, cudaMemcpyDeviceToHost, ctx->stream));
+  VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  if (h[0] != 0) return fail(ctx, VSK_ERR_TIMEOUT, "tensor-core assignment: a bounded pipeline wait ran out (role %d)", h[0]);
+  if (h[1] > 0) {
+    // rows with too many near-ties (or none listed): the fp32 tile decides
+    const int64_t m = h[1];
+    ctx->stats.fallback_queries += m;
+    VSK_CUDA(ctx, cudaMemsetAsync(ta->best, 0xff, (size_t)m * sizeof(unsigned long long), ctx->stream));
+    ExactScanArgs e{};
+    e.metric = VSK_METRIC_EUCLIDEAN;
+    e.mode = SCAN_ARGMIN;
+    e.q = rows;
+    e.nq = m;
+    e.q_subset = ta->bad_rows;
+    e.x = centroids;
+    e.dim = dim;
+    e.row_begin = 0;
+    e.row_end = k;
+    e.best = ta->best;
+    VSK_TRY(launch_exact_scan(ctx, e));
+    scatter_best_kernel<<<(unsigned)ceil_div(m, 256), 256, 0, ctx->stream>>>(ta->best, ta->bad_rows, m, assign, dist);
+    ctx->stats.kernel_launches++;
+    VSK_CUDA(ctx, cudaGetLastError());
+  }
   return VSK_OK;
 }
 

@@ -18,6 +18,27 @@ void tensor_invalidate(Index* ix);
 int32_t fp32_search_subset(Index* ix, const float* q, const std::vector<int32_t>& subset, int32_t k,
                            const float* qnorm, float* out_dist, int64_t* out_ids);
 
+// Nearest-centroid assignment on the tensor cores for one k-means run over fixed data rows: the fp16
+// operand copy of the rows and the work buffers are made once, then every Lloyd iteration calls
+// tensor_assign with the current centroids.
+struct TensorAssign {
+  int64_t n = 0;
+  int32_t dim = 0, dim16 = 0;
+  __half* rows16 = nullptr;           // [n][dim16]
+  float* stats = nullptr;             // [4][n]: |x'|, |s x - x'|, |x|, eps
+  uint64_t* keys = nullptr;           // [n][8] candidate centroids per row
+  unsigned long long* best = nullptr; // [n]
+  int32_t* count = nullptr;           // [n]
+  float* thr = nullptr;               // [n]
+  int32_t* bad_rows = nullptr;        // [n] rows handed to the fp32 tile
+  void* small = nullptr;              // scalars and centroid-operand statistics
+  alignas(64) unsigned char map_rows[128] = {};  // TMA tensor map of rows16
+};
+int32_t tensor_assign_prepare(Ctx* ctx, const float* rows, int64_t n, int32_t dim, TensorAssign* ta);
+int32_t tensor_assign(Ctx* ctx, TensorAssign* ta, const float* rows, const float* centroids, int32_t k,
+                      int32_t* assign, float* dist);
+void tensor_assign_release(TensorAssign* ta);
+
 // Search over an int8-coded flat index (sq8.cu).
 int32_t sq8_search_dev(Index* ix, const float* q, int64_t nq, int32_t k, float* out_dist, int64_t* out_ids);
 
