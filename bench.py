@@ -243,9 +243,16 @@ class Bench:
         sizes = np.bincount(asg, minlength=wl["nlist"])
         self.extra["list_len_mean"] = float(sizes.mean())
         self.extra["list_len_max"] = int(sizes.max())
+        # rows each query has to scan: the sizes of its nprobe nearest lists (computed with torch, outside the
+        # timed region); lists differ in length, and a long list is also probed by more queries
+        cent = ix.centroids if hasattr(ix.centroids, "is_cuda") else t.as_tensor(ix.centroids, device=self.device)
+        probe = t.cdist(self.queries, cent).topk(wl["nprobe"], largest=False).indices
+        scanned = t.as_tensor(sizes, device=self.device)[probe].sum(dim=1).double()
+        self.extra["scanned_rows_per_query_mean"] = float(scanned.mean())
+        self.extra["scanned_rows_per_query_max"] = float(scanned.max())
         # query-major algorithmic bytes: every query reads the rows of its nprobe lists once
-        self.bytes_per_query = wl["nprobe"] * float(sizes.mean()) * wl["dim"] * 4
-        self.flops = 2.0 * self.nq * wl["nprobe"] * float(sizes.mean()) * wl["dim"]
+        self.bytes_per_query = float(scanned.mean()) * wl["dim"] * 4
+        self.flops = 2.0 * self.nq * float(scanned.mean()) * wl["dim"]
         self.bound = "hbm"
         self.centroids_host = ix.centroids.cpu().numpy() if hasattr(ix.centroids, "cpu") else ix.centroids
         self.assign_host = asg

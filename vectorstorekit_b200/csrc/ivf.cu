@@ -10,6 +10,7 @@
 // (rank 0; 1; 2-3; 4-7; ...), compacting the candidate lists and tightening the thresholds between
 // stages, so the number of appended rows per stage stays near k.
 #include <algorithm>
+#include <type_traits>
 
 #include "common.cuh"
 #include "tile_core.cuh"
@@ -19,7 +20,6 @@ namespace {
 
 using namespace tile;
 
-constexpr int kPilotRows = kCandCap;  // rows of the nearest list scanned before the first compaction
 
 struct IvfScanArgs {
   const float* q;            // [nq][dim]
@@ -34,13 +34,16 @@ struct IvfScanArgs {
   int32_t stage;
   const int64_t* item_off;   // [nlist+1] first CTA of each list in this launch
   int64_t win_lo, win_hi;    // row window inside every list for this launch
-  int32_t remainder_lo;      // remainder items only take rows >= this
+  int32_t remainder_lo;      // remainder items only take rows >= this (the pilot window of stage 0)
+  int32_t bm;                // "a" rows per CTA for this launch: 32, 64 or 128
   const int32_t* q_subset;   // or null: list position -> query
   CandLists cand;
 };
 
+template <int BM_>
 __global__ void __launch_bounds__(THREADS, 2) ivf_scan_kernel(IvfScanArgs a) {
-  __shared__ __align__(16) Smem sm;
+  constexpr int QM = BM_ / 16;
+  __shared__ __align__(16) typename std::conditional<BM_ == 128, Smem, SmemM<(BM_ == 128 ? 64 : BM_)>>::type sm;
   __shared__ int s_list;
   // which list does this CTA belong to: last l with item_off[l] <= blockIdx.x
   if (threadIdx.x == 0) {
@@ -59,34 +62,44 @@ __global__ void __launch_bounds__(THREADS, 2) ivf_scan_kernel(IvfScanArgs a) {
   const int64_t wlo = min(a.win_lo, len), whi = min(a.win_hi, len);
   const int64_t rtiles = (whi - wlo + BN - 1) / BN;
   const int64_t qt = local / rtiles, rt = local % rtiles;
-  const int64_t pbeg = a.pair_off[(int64_t)a.stage * a.nlist + l] + qt * BM;
+  const int64_t pbeg = a.pair_off[(int64_t)a.stage * a.nlist + l] + qt * BM_;
   const int64_t pend = a.pair_off[(int64_t)a.stage * a.nlist + l + 1];
   const int64_t r0 = wlo + rt * BN;  // first row (inside the list) of this block
   const int dim = a.dim;
 
-  F32Row ar[2], br[2];
-#pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    const int64_t p = pbeg + stage_row(h);
-    ar[h].ok = p < pend;
+  auto query_row = [&](int64_t p) {
+    F32Row r;
+    r.ok = p < pend;
     int64_t q = 0;
-    if (ar[h].ok) {
+    if (r.ok) {
       const int pos = a.order[p] / a.slots;
       q = a.q_subset ? a.q_subset[pos] : pos;
     }
-    ar[h].base = a.q + q * dim;
-    ar[h].vec = (dim % 4 == 0) && aligned16(a.q);
+    r.base = a.q + q * dim;
+    r.vec = (dim % 4 == 0) && aligned16(a.q);
+    return r;
+  };
+  F32Row br[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
     const int64_t r = r0 + stage_row(h);
     br[h].ok = r < whi;
     br[h].base = a.rows + (lbeg + (br[h].ok ? r : 0)) * dim;
     br[h].vec = (dim % 4 == 0) && aligned16(a.rows);
   }
-  float acc[8][8];
-  mainloop<VSK_METRIC_EUCLIDEAN>(acc, ar, br, dim, sm);
+  float acc[QM][8];
+  if constexpr (BM_ == 128) {
+    F32Row ar[2] = {query_row(pbeg + stage_row(0)), query_row(pbeg + stage_row(1))};
+    mainloop<VSK_METRIC_EUCLIDEAN>(acc, ar, br, dim, sm);
+  } else {
+    F32Row ar = query_row(pbeg + stage_row(0));
+    if (stage_row(0) >= BM_) ar.ok = false;
+    mainloop_m<VSK_METRIC_EUCLIDEAN, BM_>(acc, ar, br, dim, sm);
+  }
 
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const int64_t p = pbeg + tile_row(i);
+  for (int i = 0; i < QM; ++i) {
+    const int64_t p = pbeg + (BM_ == 128 ? tile_row(i) : mrow<BM_>(i));
     if (p >= pend) continue;
     const int item = a.order[p];
     const int pos = item / a.slots;
@@ -105,11 +118,13 @@ __global__ void __launch_bounds__(THREADS, 2) ivf_scan_kernel(IvfScanArgs a) {
   }
 }
 
-// Grouping key of every (query, slot) item: stage(rank) * nlist + list, or the null key.
-// stage: rank 0 -> 0; rank p >= 1 -> 1 + floor(log2 p); the remainder slot -> stage 1.
-// per_rank: every rank is its own stage and there is no remainder item (safe re-run).
+// Grouping key of every (query, slot) item: stage * nlist + list, or the null key.  stage_of_rank[p] is the
+// stage of probe rank p; the remainder slot (rows of the nearest list beyond the pilot window) joins stage 1
+// when that list is longer than the pilot window.  per_rank: every rank is its own stage, no remainder item
+// (the re-run of overflowed queries).
 __global__ void ivf_pair_keys_kernel(const int64_t* __restrict__ probes, int64_t npos, int nprobe, int nlist,
-                                     const int64_t* __restrict__ list_off, int per_rank, int null_key,
+                                     const int64_t* __restrict__ list_off, int per_rank, int pilot_rows,
+                                     const int32_t* __restrict__ stage_of_rank, int null_key,
                                      const int32_t* __restrict__ q_subset, int32_t* __restrict__ keys) {
   const int slots = nprobe + 1;
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -120,26 +135,23 @@ __global__ void ivf_pair_keys_kernel(const int64_t* __restrict__ probes, int64_t
   int key = null_key;
   if (p < nprobe) {
     const int64_t l = probes[q * nprobe + p];
-    if (l >= 0) {
-      const int stage = per_rank ? p : (p == 0 ? 0 : 32 - __clz(p));
-      key = stage * nlist + (int)l;
-    }
+    if (l >= 0) key = (per_rank ? p : stage_of_rank[p]) * nlist + (int)l;
   } else if (!per_rank) {
     const int64_t l = probes[q * nprobe];
-    if (l >= 0 && list_off[l + 1] - list_off[l] > kPilotRows) key = 1 * nlist + (int)l;
+    if (l >= 0 && list_off[l + 1] - list_off[l] > pilot_rows) key = 1 * nlist + (int)l;
   }
   keys[i] = key;
 }
 
 // CTAs per list for one launch: ceil(pairs/128) * ceil(window rows/128)
 __global__ void ivf_item_count_kernel(const int64_t* pair_off, int stage, int nlist, const int64_t* list_off,
-                                      int64_t win_lo, int64_t win_hi, int64_t* counts) {
+                                      int64_t win_lo, int64_t win_hi, int bm, int64_t* counts) {
   const int l = blockIdx.x * blockDim.x + threadIdx.x;
   if (l >= nlist) return;
   const int64_t pc = pair_off[(int64_t)stage * nlist + l + 1] - pair_off[(int64_t)stage * nlist + l];
   const int64_t len = list_off[l + 1] - list_off[l];
   const int64_t rows = min(win_hi, len) - min(win_lo, len);
-  counts[l] = ((pc + BM - 1) / BM) * ((rows + BN - 1) / BN);
+  counts[l] = ((pc + bm - 1) / bm) * ((rows + BN - 1) / BN);
 }
 
 __global__ void scan_i64_kernel(const int64_t* totals, int32_t n, int64_t* offsets) {
@@ -181,7 +193,7 @@ int32_t ivf_pass(Ctx* ctx, Index* ix, IvfScanArgs a, int64_t npos, int32_t keep)
   VSK_TRY(scratch(ctx, SLOT_IVF_ITEM_CNT, (size_t)(ix->nlist + 1) * 8, &cnt));
   VSK_TRY(scratch(ctx, SLOT_IVF_ITEM_OFF, (size_t)(ix->nlist + 1) * 8, &off));
   ivf_item_count_kernel<<<(unsigned)ceil_div(ix->nlist, 256), 256, 0, ctx->stream>>>(
-      a.pair_off, a.stage, ix->nlist, ix->list_offsets, a.win_lo, a.win_hi, (int64_t*)cnt);
+      a.pair_off, a.stage, ix->nlist, ix->list_offsets, a.win_lo, a.win_hi, a.bm, (int64_t*)cnt);
   scan_i64_kernel<<<1, 1024, 0, ctx->stream>>>((const int64_t*)cnt, ix->nlist, (int64_t*)off);
   ctx->stats.kernel_launches += 2;
   int64_t total = 0;
@@ -191,7 +203,9 @@ int32_t ivf_pass(Ctx* ctx, Index* ix, IvfScanArgs a, int64_t npos, int32_t keep)
   if (total > 0) {
     a.item_off = (const int64_t*)off;
     prof_begin(ctx);
-    ivf_scan_kernel<<<(unsigned)total, THREADS, 0, ctx->stream>>>(a);
+    if (a.bm == 32) ivf_scan_kernel<32><<<(unsigned)total, THREADS, 0, ctx->stream>>>(a);
+    else if (a.bm == 64) ivf_scan_kernel<64><<<(unsigned)total, THREADS, 0, ctx->stream>>>(a);
+    else ivf_scan_kernel<128><<<(unsigned)total, THREADS, 0, ctx->stream>>>(a);
     prof_end(ctx);
     ctx->stats.kernel_launches++;
     VSK_CUDA(ctx, cudaGetLastError());
@@ -208,16 +222,54 @@ int32_t ivf_search_positions(Ctx* ctx, Index* ix, const float* q, int64_t npos, 
                              const int64_t* probes, int32_t nprobe, int32_t k, float* out_dist, int64_t* out_ids,
                              bool safe) {
   const int slots = nprobe + 1;
-  const int nstages = safe ? nprobe : (nprobe <= 1 ? 2 : 2 + (31 - __builtin_clz((unsigned)(nprobe - 1))));
+  // ---- stage plan -------------------------------------------------------------------------------------
+  // Stage 0 (the pilot) scans a window of each query's nearest list and sets the first thresholds.  Later
+  // stages take probe ranks in order; how many ranks a stage may take follows the same rule as the flat
+  // schedule (schedule_chunk): the rows a stage adds, relative to the rows already seen, bound the keys it
+  // can append to a list.  Rows per rank are estimated by the mean list length.
+  const double mean_len = std::max(1.0, (double)ix->n / (double)ix->nlist);
+  const int pilot_rows = (int)std::min<int64_t>(kCandCap, std::max<int64_t>(256, ceil_div(16 * (int64_t)k, 128) * 128));
+  std::vector<int32_t> stage_of_rank((size_t)nprobe, 0);
+  std::vector<int> ranks_in_stage;   // probe ranks per stage (stage 1 also holds the remainder items)
+  int nstages;
+  if (safe) {
+    nstages = nprobe;
+    for (int p = 0; p < nprobe; ++p) stage_of_rank[p] = p;
+    ranks_in_stage.assign((size_t)nprobe, 1);
+  } else {
+    ranks_in_stage.push_back(1);
+    double seen = std::min<double>(pilot_rows, mean_len);
+    int p = 1, st = 1;
+    bool first = true;
+    while (p < nprobe || first) {
+      const double chunk = (double)schedule_chunk((int64_t)seen, k, 0);
+      // stage 1 also pays for the rest of the nearest list
+      double budget = chunk - (first ? std::max(0.0, mean_len - pilot_rows) : 0.0);
+      int take = (int)std::max(1.0, std::floor(budget / mean_len));
+      take = std::min(take, nprobe - p);
+      for (int i = 0; i < take; ++i) stage_of_rank[p + i] = st;
+      ranks_in_stage.push_back(std::max(take, 0));
+      seen += (first ? std::max(0.0, mean_len - pilot_rows) : 0.0) + take * mean_len;
+      p += std::max(take, 0);
+      ++st;
+      first = false;
+      if (take <= 0) break;
+    }
+    nstages = st;
+  }
   const int nkeys = nstages * ix->nlist + 1;  // + the null key
   const int64_t nitems = npos * slots;
   if (nitems > 0x7fffffffLL) return fail(ctx, VSK_ERR_INVALID_BUFFER_SIZE, "too many (query, probe) pairs");
-  void *keys, *order, *pair_off;
+  void *keys, *order, *pair_off, *sor;
   VSK_TRY(scratch(ctx, SLOT_IVF_KEYS, (size_t)nitems * 4, &keys));
   VSK_TRY(scratch(ctx, SLOT_IVF_ORDER, (size_t)nitems * 4, &order));
   VSK_TRY(scratch(ctx, SLOT_IVF_PAIR_OFF, (size_t)(nkeys + 1) * 8, &pair_off));
+  VSK_TRY(scratch(ctx, SLOT_IVF_STAGES, (size_t)nprobe * 4, &sor));
+  VSK_CUDA(ctx, cudaMemcpyAsync(sor, stage_of_rank.data(), (size_t)nprobe * 4, cudaMemcpyHostToDevice, ctx->stream));
+  VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));   // stage_of_rank is a local
   ivf_pair_keys_kernel<<<(unsigned)ceil_div(nitems, 256), 256, 0, ctx->stream>>>(
-      probes, npos, nprobe, ix->nlist, ix->list_offsets, safe ? 1 : 0, nkeys - 1, sub_dev, (int32_t*)keys);
+      probes, npos, nprobe, ix->nlist, ix->list_offsets, safe ? 1 : 0, pilot_rows, (const int32_t*)sor, nkeys - 1, sub_dev,
+      (int32_t*)keys);
   ctx->stats.kernel_launches++;
   VSK_TRY(launch_stable_group(ctx, (const int32_t*)keys, nitems, nkeys, (int32_t*)order, (int64_t*)pair_off));
 
@@ -248,15 +300,18 @@ int32_t ivf_search_positions(Ctx* ctx, Index* ix, const float* q, int64_t npos, 
   a.pair_off = (const int64_t*)pair_off;
   a.q_subset = sub_dev;
   a.cand = cand;
-  a.remainder_lo = kPilotRows;
+  a.remainder_lo = pilot_rows;
   int64_t max_len = 0;
   for (int l = 0; l < ix->nlist; ++l) max_len = std::max(max_len, ix->list_offsets_h[l + 1] - ix->list_offsets_h[l]);
   const int64_t room = kCandCap - k;
   for (int s = 0; s < nstages; ++s) {
     a.stage = s;
+    // "a" rows per CTA from the mean number of probing queries per list in this stage
+    const double per_list = (double)npos * ranks_in_stage[(size_t)s] / (double)ix->nlist + (s == 1 && !safe ? (double)npos / ix->nlist : 0.0);
+    a.bm = per_list <= 20.0 ? 32 : (per_list <= 80.0 ? 64 : 128);
     if (!safe) {
       a.win_lo = 0;
-      a.win_hi = s == 0 ? kPilotRows : (1ll << 62);
+      a.win_hi = s == 0 ? pilot_rows : (1ll << 62);
       VSK_TRY(ivf_pass(ctx, ix, a, npos, k));
     } else {
       for (int64_t w = 0; w < std::max<int64_t>(max_len, 1); w += room) {

@@ -144,3 +144,81 @@ __device__ __forceinline__ bool aligned4(const void* p) { return (reinterpret_ca
 
 }  // namespace tile
 }  // namespace vsk
+
+// ---- the same tile with a narrower "a" side ---------------------------------------------------
+// BM_ = 32 or 64 "a" rows x 128 "b" rows per CTA (256 threads, BM_/16 x 8 values per thread).
+// Used where the number of "a" rows that share a "b" block is small (IVF: the queries probing one list),
+// so that a block's cost follows the rows it actually holds.
+namespace vsk {
+namespace tile {
+
+template <int BM_>
+struct SmemM {
+  float As[2][BK][BM_ + PAD];
+  float Bs[2][BK][BN + PAD];
+};
+
+template <int BM_>
+__device__ __forceinline__ int mrow(int i) { return (threadIdx.x >> 4) * (BM_ / 16) + i; }
+
+template <int METRIC, int BM_, class ARow, class BRow>
+__device__ __forceinline__ void mainloop_m(float (&acc)[BM_ / 16][8], const ARow& ar, const BRow (&br)[2], int dim,
+                                           SmemM<BM_>& sm) {
+  static_assert(BM_ == 32 || BM_ == 64, "the narrow tile stages at most one \"a\" row per thread");
+  constexpr int QM = BM_ / 16;
+  // "a" staging: thread t stages dimensions lk..lk+3 of row t>>2 when that row exists (t>>2 < BM_)
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const int lr = threadIdx.x >> 2, lk = stage_k();
+  const bool a_stage = lr < BM_;
+#pragma unroll
+  for (int i = 0; i < QM; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+  const int nk = (dim + BK - 1) / BK;
+  float4 ra = make_float4(0.f, 0.f, 0.f, 0.f), rb[2];
+  if (a_stage) ra = ar.load(lk, dim);
+#pragma unroll
+  for (int h = 0; h < 2; ++h) rb[h] = br[h].load(lk, dim);
+  if (a_stage) { sm.As[0][lk + 0][lr] = ra.x; sm.As[0][lk + 1][lr] = ra.y; sm.As[0][lk + 2][lr] = ra.z; sm.As[0][lk + 3][lr] = ra.w; }
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = lr + h * 64;
+    sm.Bs[0][lk + 0][r] = rb[h].x; sm.Bs[0][lk + 1][r] = rb[h].y; sm.Bs[0][lk + 2][r] = rb[h].z; sm.Bs[0][lk + 3][r] = rb[h].w;
+  }
+  __syncthreads();
+  for (int kb = 0; kb < nk; ++kb) {
+    const int s = kb & 1;
+    if (kb + 1 < nk) {
+      const int k = (kb + 1) * BK + lk;
+      if (a_stage) ra = ar.load(k, dim);
+#pragma unroll
+      for (int h = 0; h < 2; ++h) rb[h] = br[h].load(k, dim);
+    }
+#pragma unroll
+    for (int kk = 0; kk < BK; ++kk) {
+      float av[QM];
+#pragma unroll
+      for (int i = 0; i < QM; ++i) av[i] = sm.As[s][kk][ty * QM + i];
+      const float4 b0 = *reinterpret_cast<const float4*>(&sm.Bs[s][kk][tx * 4]);
+      const float4 b1 = *reinterpret_cast<const float4*>(&sm.Bs[s][kk][64 + tx * 4]);
+      const float bv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+      for (int i = 0; i < QM; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) accum<METRIC>(acc[i][j], av[i], bv[j]);
+    }
+    if (kb + 1 < nk) {
+      const int s2 = s ^ 1;
+      if (a_stage) { sm.As[s2][lk + 0][lr] = ra.x; sm.As[s2][lk + 1][lr] = ra.y; sm.As[s2][lk + 2][lr] = ra.z; sm.As[s2][lk + 3][lr] = ra.w; }
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int r = lr + h * 64;
+        sm.Bs[s2][lk + 0][r] = rb[h].x; sm.Bs[s2][lk + 1][r] = rb[h].y; sm.Bs[s2][lk + 2][r] = rb[h].z; sm.Bs[s2][lk + 3][r] = rb[h].w;
+      }
+    }
+    __syncthreads();
+  }
+}
+
+}  // namespace tile
+}  // namespace vsk
