@@ -5,6 +5,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <functional>
 
@@ -112,7 +113,25 @@ int64_t schedule_chunk(int64_t seen, int32_t keep, int level) {
   return std::max<int64_t>(room, (int64_t)(g * (double)seen));
 }
 
-// Walks rows [0, n) in chunks.  The first chunk (at most kCandCap rows) is written densely, one slot per
+// Tuning overrides for experiments (unset in normal use): VSK_DENSE_ROWS, VSK_GROWTH.
+int64_t schedule_tuning(const char* name, int64_t dflt) {
+  const char* v = getenv(name);
+  return v && *v ? atoll(v) : dflt;
+}
+
+int64_t schedule_dense_rows(int32_t keep) {
+  static const int64_t forced = schedule_tuning("VSK_DENSE_ROWS", 0);
+  if (forced > 0) return std::min<int64_t>(kCandCap, forced);
+  return std::min<int64_t>(kCandCap, std::max<int64_t>(1024, ceil_div(8 * (int64_t)keep, 256) * 256));
+}
+
+int32_t schedule_max_count(int64_t seen, int64_t chunk, int32_t keep) {
+  const double mean = (double)keep * (double)chunk / (double)std::max<int64_t>(seen, 1);
+  const double bound = (double)keep + mean * (1.0 + 8.0 / sqrt((double)keep)) + 8.0;
+  return (int32_t)std::min<double>(bound, 1e9);
+}
+
+// Walks rows [0, n) in chunks.  The first chunk (schedule_dense_rows) is written densely, one slot per
 // row; it is compacted to the best `keep`, whose worst value becomes the threshold.  Each later chunk appends
 // only rows at or below the threshold (see schedule_chunk for its size).  A list that overflows is flagged
 // and its query is re-run at the next level.
@@ -123,14 +142,16 @@ static int32_t run_schedule(Ctx* ctx, const ScanFn& scan, int64_t n, int64_t nq,
   sel.cand = cand;
   sel.nq = nq;
   sel.keep = keep;
-  int64_t seen = std::min<int64_t>(n, kCandCap);
+  int64_t seen = std::min<int64_t>(n, schedule_dense_rows(keep));
   VSK_TRY(scan(SCAN_DENSE, 0, seen));
   sel.dense_count = (int32_t)seen;
+  sel.max_count = (int32_t)seen;
   VSK_TRY(launch_select(ctx, sel));
   sel.dense_count = -1;
   while (seen < n) {
     const int64_t chunk = std::min(schedule_chunk(seen, keep, level), n - seen);
     VSK_TRY(scan(SCAN_THRESHOLD, seen, seen + chunk));
+    sel.max_count = level >= 2 ? kCandCap : schedule_max_count(seen, chunk, keep);
     VSK_TRY(launch_select(ctx, sel));
     seen += chunk;
   }
@@ -177,6 +198,7 @@ int32_t fp32_topk(Ctx* ctx, const ExactScanArgs& proto, int64_t n, int64_t nq, c
   fin.id_base = id_base;
   fin.q_subset = sub_dev;
   fin.final_sqrt = a.metric == VSK_METRIC_EUCLIDEAN;
+  fin.max_count = k;
   VSK_TRY(launch_select(ctx, fin));
   if (level < 2) {
     std::vector<int32_t> bad;

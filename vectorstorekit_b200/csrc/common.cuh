@@ -209,6 +209,7 @@ struct SelectArgs {
   const int32_t* q_subset;  // or null; lists are indexed by position, outputs by q_subset[pos]
   int final_sqrt;           // 1: stored value is a squared L2 distance
   const float* cert_eps;    // non-null: last compaction of a coarse scan (see select.cu); uses k
+  int32_t max_count;        // > 0: no list of this launch is expected to hold more keys (picks the kernel width)
 };
 int32_t launch_select(Ctx* ctx, const SelectArgs& a);
 int32_t launch_merge_topk(Ctx* ctx, const float* dist, const int64_t* ids, int32_t g, int64_t nq,
@@ -222,6 +223,11 @@ int32_t fp32_topk(Ctx* ctx, const ExactScanArgs& proto, int64_t n, int64_t nq, c
                   int64_t id_base, float* out_dist, int64_t* out_ids, int level);
 // Rows of the next chunk of the search schedule (api.cu).
 int64_t schedule_chunk(int64_t seen, int32_t keep, int level);
+// Rows of the dense first chunk, and an upper bound (mean + 8 deviations) on the keys a list holds after a
+// thresholded chunk of `chunk` rows that followed `seen` rows.
+int64_t schedule_dense_rows(int32_t keep);
+int64_t schedule_tuning(const char* name, int64_t dflt);
+int32_t schedule_max_count(int64_t seen, int64_t chunk, int32_t keep);
 
 // ---- helpers in api.cu ---------------------------------------------------------------------
 int32_t dev_alloc(Ctx* ctx, void** p, size_t bytes);

@@ -12,7 +12,7 @@
 namespace vsk {
 namespace {
 
-constexpr int SEL_THREADS = 512;
+constexpr int SEL_THREADS = 512;   // widest variant: 512 threads x 8 keys = the full list capacity
 
 __device__ __forceinline__ void bitonic_sort(uint64_t* s, int P) {
   for (int size = 2; size <= P; size <<= 1) {
@@ -35,7 +35,7 @@ __device__ __forceinline__ int next_pow2(int c) {
   return p;
 }
 
-constexpr int SEL_ITEMS = kCandCap / SEL_THREADS;  // keys per thread, held in registers
+constexpr int SEL_ITEMS = 8;  // keys per thread, held in registers
 
 // Block-wide radix select over the 64-bit keys each thread holds: returns the key of rank `rank`
 // (1-based, ascending).  One pass per byte from the top; a pass histograms the byte among the keys that
@@ -86,8 +86,13 @@ __device__ __forceinline__ uint64_t block_radix_select(const uint64_t (&key)[SEL
   return prefix;
 }
 
-__global__ void __launch_bounds__(SEL_THREADS) select_kernel(SelectArgs a) {
+// NT threads handle a list of at most NT * 8 keys.  The host picks NT from an upper bound on the list
+// lengths of the launch (SelectArgs::max_count); a list that is longer all the same is flagged like an
+// overflowed list and its query is re-run.
+template <int NT>
+__global__ void __launch_bounds__(NT) select_kernel(SelectArgs a) {
   extern __shared__ __align__(16) uint64_t s[];
+  constexpr int CAPACITY = NT * SEL_ITEMS;
   __shared__ int hist[256];
   __shared__ int s_valid, s_bin, s_less, s_in_bin, s_out;
   const int64_t q = blockIdx.x;
@@ -97,9 +102,10 @@ __global__ void __launch_bounds__(SEL_THREADS) select_kernel(SelectArgs a) {
     c = a.dense_count;
   } else {
     const int raw = a.cand.count[q];
-    c = min(raw, kCandCap);
-    if (raw > kCandCap && threadIdx.x == 0) atomicOr(&a.cand.flags[q], 1);
+    c = min(raw, CAPACITY);
+    if (raw > CAPACITY && threadIdx.x == 0) atomicOr(&a.cand.flags[q], 1);
   }
+  c = min(c, CAPACITY);
 
   if (a.out_ids != nullptr) {
     // ---- final order: sort the (short) list in shared memory and write the ascending top-k ----
@@ -132,7 +138,7 @@ __global__ void __launch_bounds__(SEL_THREADS) select_kernel(SelectArgs a) {
   int nvalid = 0;
 #pragma unroll
   for (int i = 0; i < SEL_ITEMS; ++i) {
-    const int idx = threadIdx.x + i * SEL_THREADS;
+    const int idx = threadIdx.x + i * NT;
     key[i] = idx < c ? keys[idx] : kEmptyKey;
     nvalid += key[i] != kEmptyKey;
   }
@@ -228,9 +234,16 @@ __global__ void __launch_bounds__(SEL_THREADS) merge_kernel(const float* __restr
 
 int32_t launch_select(Ctx* ctx, const SelectArgs& a) {
   if (a.nq <= 0) return VSK_OK;
+  // lists known to hold at most 1024 keys take the 128-thread variant (four times as many CTAs per SM);
   // only the final ordering sorts in shared memory
-  const size_t smem = a.out_ids ? kCandCap * sizeof(uint64_t) : 0;
-  select_kernel<<<(unsigned)a.nq, SEL_THREADS, smem, ctx->stream>>>(a);
+  const bool small = a.max_count > 0 && a.max_count <= 128 * SEL_ITEMS && (a.dense_count < 0 || a.dense_count <= 128 * SEL_ITEMS);
+  if (small) {
+    const size_t smem = a.out_ids ? 128 * SEL_ITEMS * sizeof(uint64_t) : 0;
+    select_kernel<128><<<(unsigned)a.nq, 128, smem, ctx->stream>>>(a);
+  } else {
+    const size_t smem = a.out_ids ? kCandCap * sizeof(uint64_t) : 0;
+    select_kernel<SEL_THREADS><<<(unsigned)a.nq, SEL_THREADS, smem, ctx->stream>>>(a);
+  }
   ctx->stats.kernel_launches++;
   VSK_CUDA(ctx, cudaGetLastError());
   return VSK_OK;

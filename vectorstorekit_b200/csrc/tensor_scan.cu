@@ -970,12 +970,13 @@ int32_t tensor_search(Index* ix, const float* q, int64_t nq, int32_t k, const fl
   sel.keep = keep;
   const int64_t n = ix->n;
   const int64_t room = kCandCap - keep;
-  int64_t seen = std::min<int64_t>(n, kCandCap);
+  int64_t seen = std::min<int64_t>(n, schedule_dense_rows(keep));
   a.mode = SCAN_DENSE;
   a.row_begin = 0;
   a.row_end = seen;
   VSK_TRY(launch_tc<SCAN_DENSE>(ctx, mq, mx, a, has_beta));
   sel.dense_count = (int32_t)seen;
+  sel.max_count = (int32_t)seen;
   sel.k = k;
   // the compaction after the last chunk keeps what the exact re-scoring needs and certifies the query
   if (seen == n) sel.cert_eps = eps;
@@ -987,12 +988,14 @@ int32_t tensor_search(Index* ix, const float* q, int64_t nq, int32_t k, const fl
     // grow geometrically (each no larger than three times the rows seen so far), which keeps the share of
     // rows scanned under a loose threshold small: the epilogue's append path costs far more than its filter.
     int64_t chunk = schedule_chunk(seen, keep, 0);
-    chunk = std::min<int64_t>(chunk, std::max<int64_t>(room, 3 * seen));
+    static const int64_t growth = schedule_tuning("VSK_GROWTH", 3);
+    chunk = std::min<int64_t>(chunk, std::max<int64_t>(growth >= 100 ? room : 1024, growth * seen));
     chunk = std::max<int64_t>(TN, chunk / TN * TN);   // whole row tiles
     chunk = std::min(chunk, n - seen);
     a.row_begin = seen;
     a.row_end = seen + chunk;
     VSK_TRY(launch_tc<SCAN_THRESHOLD>(ctx, mq, mx, a, has_beta));
+    sel.max_count = schedule_max_count(seen, chunk, keep);
     seen += chunk;
     if (seen == n) sel.cert_eps = eps;
     VSK_TRY(launch_select(ctx, sel));
@@ -1033,6 +1036,7 @@ int32_t tensor_search(Index* ix, const float* q, int64_t nq, int32_t k, const fl
   fin.metric = metric;
   fin.id_base = ix->id_base;
   fin.final_sqrt = metric == VSK_METRIC_EUCLIDEAN;
+  fin.max_count = keep;
   VSK_TRY(launch_select(ctx, fin));
 
   // ---- flags: bounded-wait expiry, overflowed lists, failed certificates ----
