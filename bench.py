@@ -41,6 +41,9 @@ WORKLOADS = {
                name="flat-cosine-1M-d768-q10000-k100"),
     "c2s": dict(kind="flat", metric="cosine", rows=200_000, dim=768, queries=2_048, k=100, cfg=2,
                 name="flat-cosine-200k-d768-q2048-k100"),
+    # one eighth of c2's rows with all of its queries: what one rank of an 8-GPU run searches
+    "c2e": dict(kind="flat", metric="cosine", rows=125_000, dim=768, queries=10_000, k=100, cfg=2,
+                name="flat-cosine-125k-d768-q10000-k100"),
     "c3": dict(kind="ivf", metric="euclidean", rows=10_000_000, dim=128, queries=10_000, k=10, cfg=3, nlist=4096,
                nprobe=32, iters=20, name="ivf-euclidean-10M-d128-nlist4096-nprobe32-q10000-k10"),
     "c3s": dict(kind="ivf", metric="euclidean", rows=1_000_000, dim=128, queries=2_048, k=10, cfg=3, nlist=1024,

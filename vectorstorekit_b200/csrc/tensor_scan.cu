@@ -19,8 +19,9 @@
 // so that concurrently running CTAs share the same rows in L2):
 //   warp 0      TMA producer: 4-stage ring of {128 x 64 query, 256 x 64 row} fp16 tiles
 //   warp 1      tensor-memory allocation; one lane issues tcgen05.mma (M128 N256 K16 x 4 per stage)
-//   warps 2..5  epilogue: tcgen05.ld of the thread's accumulator row (one query per thread),
-//               threshold filter, candidate append; double-buffered accumulators (2 x 256 columns)
+//   warps 2..9  epilogue: tcgen05.ld of the thread's accumulator row (one query per thread, two warps per
+//               lane quarter, 128 columns each), threshold filter, candidate append; double-buffered
+//               accumulators (2 x 256 columns)
 // Every mbarrier wait is bounded: on expiry the kernel raises an error word, stops issuing work,
 // drains its copies and frees tensor memory, and the host call returns VSK_ERR_TIMEOUT.
 #include <cuda.h>
@@ -39,15 +40,18 @@ constexpr int STAGES = 4;
 constexpr int A_BYTES = TM * TK * 2;   // 16 KB
 constexpr int B_BYTES = TN * TK * 2;   // 32 KB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int TC_THREADS = 192;
+constexpr int TC_THREADS = 320;        // warp 0 producer, warp 1 MMA issuer, warps 2..9 epilogue
+constexpr int EPI_WARPS = 8;           // two per tensor-memory lane quarter: each takes half of the tile's columns
+constexpr int EPI_COLS = TN / 2;       // columns per epilogue warp
+constexpr int EPI_GROUPS = EPI_COLS / 32;
 constexpr uint32_t WAIT_LIMIT = 1u << 23;
 constexpr int TMEM_COLS = 512;
 
 struct TcSmem {
   // stage buffers first: each must start on a 1024-byte boundary for the 128B swizzle
   uint8_t stage[STAGES][STAGE_BYTES];
-  float beta[2][4][TN];   // per accumulator buffer and epilogue warp: the tile's per-row terms
-  uint32_t masks[TM][TN / 32 + 1];  // per epilogue thread: pass bits of its 256 values (padded row)
+  float beta[2][EPI_WARPS][EPI_COLS];   // per accumulator buffer and epilogue warp: its columns' per-row terms
+  uint32_t masks[EPI_WARPS * 32][EPI_GROUPS + 1];  // per epilogue thread: pass bits of its 128 values (padded row)
   uint64_t full[STAGES];
   uint64_t empty[STAGES];
   uint64_t tmem_full[2];
@@ -187,7 +191,7 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&sm->tmem_full[b], 1);
-      mbar_init(&sm->tmem_empty[b], 4);
+      mbar_init(&sm->tmem_empty[b], EPI_WARPS);
     }
     mbar_init(&sm->drain, 1);
     sm->abort_flag = 0;
@@ -272,9 +276,11 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       }
     }
   } else {
-    // ---------------- epilogue: one query per thread ----------------
+    // ---------------- epilogue: one query per thread, half of the tile's columns per warp ----------------
     const int quarter = warp & 3;                 // tensor-memory lanes this warp may read
     const int et = quarter * 32 + lane;           // row of the tile owned by this thread
+    const int ew = warp - 2;                      // epilogue warp 0..7
+    const int c0 = (ew >> 2) * EPI_GROUPS;        // first 32-column group of this warp's half
     const float alpha = __ldg(a.alpha);
     int64_t local = 0;
     bool ok = true;
@@ -288,7 +294,8 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       const bool qok = q < a.nq;
       if (HAS_BETA) {
         // the tile's per-row terms; each warp stages its own copy, so no CTA-wide barrier is needed
-        for (int i = lane; i < TN; i += 32) sm->beta[acc][quarter][i] = (n0 + i < a.row_end) ? __ldg(a.beta + n0 + i) : 0.f;
+        for (int i = lane; i < EPI_COLS; i += 32)
+          sm->beta[acc][ew][i] = (n0 + c0 * 32 + i < a.row_end) ? __ldg(a.beta + n0 + c0 * 32 + i) : 0.f;
         __syncwarp();
       }
       float thr = CUDART_INF_F;
@@ -301,7 +308,7 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       const uint32_t trow = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * TN);
       if (MODE == SCAN_DENSE) {
 #pragma unroll 1
-        for (int c = 0; c < TN / 32; ++c) {
+        for (int c = c0; c < c0 + EPI_GROUPS; ++c) {
           float v[32];
           tc_ld32(trow + (uint32_t)(c * 32), v);
           const int64_t nc = n0 + c * 32;
@@ -309,7 +316,7 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           uint64_t* dst = a.cand.keys + q * kCandCap + (nc - a.row_begin);
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
-            const float val = HAS_BETA ? fmaf(v[j], alpha, sm->beta[acc][quarter][c * 32 + j]) : v[j] * alpha;
+            const float val = HAS_BETA ? fmaf(v[j], alpha, sm->beta[acc][ew][(c - c0) * 32 + j]) : v[j] * alpha;
             if (nc + j < a.row_end) dst[j] = make_key(val, (uint32_t)(nc + j));
           }
         }
@@ -318,13 +325,13 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         float bv = CUDART_INF_F;
         int bj = 0;
 #pragma unroll 1
-        for (int c = 0; c < TN / 32; ++c) {
+        for (int c = c0; c < c0 + EPI_GROUPS; ++c) {
           float v[32];
           tc_ld32(trow + (uint32_t)(c * 32), v);
           const int64_t left = a.row_end - (n0 + c * 32);
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
-            const float val = HAS_BETA ? fmaf(v[j], alpha, sm->beta[acc][quarter][c * 32 + j]) : v[j] * alpha;
+            const float val = HAS_BETA ? fmaf(v[j], alpha, sm->beta[acc][ew][(c - c0) * 32 + j]) : v[j] * alpha;
             if (j < left && val < bv) { bv = val; bj = c * 32 + j; }   // strict '<': the lowest row wins ties
           }
         }
@@ -336,10 +343,10 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         // L2 round trip for every column in which any of its 32 queries has a hit.
         // The masks live in shared memory so that both loops stay rolled (small code, no dynamic
         // register indexing).
-        uint32_t* m = sm->masks[et];
+        uint32_t* m = sm->masks[ew * 32 + lane];
         int cnt = 0;
 #pragma unroll 1
-        for (int c = 0; c < TN / 32; ++c) {
+        for (int c = c0; c < c0 + EPI_GROUPS; ++c) {
           float v[32];
           tc_ld32(trow + (uint32_t)(c * 32), v);
           const int64_t left = a.row_end - (n0 + c * 32);   // columns of this group inside the launch
@@ -347,18 +354,18 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           uint32_t bits = 0;
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
-            const float val = HAS_BETA ? fmaf(v[j], alpha, sm->beta[acc][quarter][c * 32 + j]) : v[j] * alpha;
+            const float val = HAS_BETA ? fmaf(v[j], alpha, sm->beta[acc][ew][(c - c0) * 32 + j]) : v[j] * alpha;
             bits |= (val <= thr) ? (1u << j) : 0u;
           }
           bits = qok ? (bits & colmask) : 0u;
-          m[c] = bits;
+          m[c - c0] = bits;
           cnt += __popc(bits);
         }
         int base = 0;
         if (cnt) base = atomicAdd(&a.cand.count[q], cnt);
 #pragma unroll 1
-        for (int c = 0; c < TN / 32; ++c) {
-          const uint32_t bits = m[c];
+        for (int c = c0; c < c0 + EPI_GROUPS; ++c) {
+          const uint32_t bits = m[c - c0];
           if (!__any_sync(0xffffffffu, bits != 0u)) continue;
           float v[32];
           tc_ld32(trow + (uint32_t)(c * 32), v);
@@ -367,7 +374,7 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             if ((bits >> j) & 1u) {
-              const float val = HAS_BETA ? fmaf(v[j], alpha, sm->beta[acc][quarter][c * 32 + j]) : v[j] * alpha;
+              const float val = HAS_BETA ? fmaf(v[j], alpha, sm->beta[acc][ew][(c - c0) * 32 + j]) : v[j] * alpha;
               const int pos = base + __popc(bits & ((1u << j) - 1u));
               if (pos < a.cap) dst[pos] = make_key(val, (uint32_t)(nc + j));
             }
