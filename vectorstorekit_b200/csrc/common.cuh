@@ -103,7 +103,7 @@ enum Slot : int {
   SLOT_CAND_FLAGS, SLOT_QNORM, SLOT_SUBSET, SLOT_Q16, SLOT_QAUX, SLOT_X_TMP, SLOT_MISC0, SLOT_MISC1,
   SLOT_MISC2, SLOT_MISC3, SLOT_MISC4, SLOT_MISC5, SLOT_MISC6,
   SLOT_IVF_PROBE_D, SLOT_IVF_PROBE_I, SLOT_IVF_KEYS, SLOT_IVF_ORDER, SLOT_IVF_PAIR_OFF, SLOT_IVF_ITEM_CNT,
-  SLOT_IVF_ITEM_OFF, SLOT_IVF_SUBSET, SLOT_IVF_STAGES, SLOT_SQ_A, SLOT_SQ_B, SLOT_TC_A, SLOT_TC_B, SLOT_TC_C, SLOT_TC_D,
+  SLOT_IVF_ITEM_OFF, SLOT_IVF_SUBSET, SLOT_IVF_STAGES, SLOT_KM_NSEG, SLOT_KM_SEGOFF, SLOT_KM_PARTIAL, SLOT_SQ_A, SLOT_SQ_B, SLOT_TC_A, SLOT_TC_B, SLOT_TC_C, SLOT_TC_D,
   SLOT_COUNT
 };
 static_assert(SLOT_COUNT <= 48, "grow Ctx::scratch");
@@ -193,6 +193,9 @@ int32_t launch_stable_group(Ctx* ctx, const int32_t* keys, int64_t n, int32_t nk
 // ---- kmeans.cu ---------------------------------------------------------------------------
 int32_t assign_rows(Ctx* ctx, const float* rows, int64_t n, int32_t dim, const float* centroids, int32_t k,
                     int32_t* assign, float* dist);
+
+// offsets[0..n] = exclusive scan of totals[0..n) (single block; group.cu)
+int32_t launch_scan_i64(Ctx* ctx, const int64_t* totals, int32_t n, int64_t* offsets);
 
 // ---- select.cu ---------------------------------------------------------------------------
 struct SelectArgs {

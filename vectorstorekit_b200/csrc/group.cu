@@ -87,6 +87,13 @@ __global__ void key_scan_kernel(const int64_t* totals, int32_t nkeys, int64_t* o
 
 }  // namespace
 
+int32_t launch_scan_i64(Ctx* ctx, const int64_t* totals, int32_t n, int64_t* offsets) {
+  key_scan_kernel<<<1, 1024, 0, ctx->stream>>>(totals, n, offsets);
+  ctx->stats.kernel_launches++;
+  VSK_CUDA(ctx, cudaGetLastError());
+  return VSK_OK;
+}
+
 int32_t launch_stable_group(Ctx* ctx, const int32_t* keys, int64_t n, int32_t nkeys, int32_t* order,
                             int64_t* offsets) {
   if (n <= 0 || nkeys <= 0) return fail(ctx, VSK_ERR_EMPTY_INPUT, "nothing to group");

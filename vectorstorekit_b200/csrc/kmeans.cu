@@ -26,17 +26,36 @@ __global__ void decode_best_kernel(const unsigned long long* best, int64_t n, in
   if (dist) dist[i] = sqrtf(ordered_to_float((uint32_t)(b >> 32)));
 }
 
-__global__ void centroid_update_kernel(const float* __restrict__ x, int dim, const int32_t* __restrict__ order,
-                                       const int64_t* __restrict__ offsets, const float* __restrict__ old_c,
-                                       float* __restrict__ new_c) {
-  const int c = blockIdx.x;
-  const int64_t begin = offsets[c], end = offsets[c + 1];
-  const int64_t cnt = end - begin;
-  for (int d = threadIdx.x; d < dim; d += blockDim.x) {
-    if (cnt == 0) {
-      new_c[(int64_t)c * dim + d] = old_c[(int64_t)c * dim + d];
-      continue;
+// Centroid update in two steps, both in a fixed order (deterministic, no float atomics).
+// Rows are already grouped by centroid (`order`, row order inside a group).  A group is cut into segments of
+// kSegRows rows; one CTA sums one segment, one thread per dimension, adding rows in row order; then one CTA per
+// centroid adds its segments' partial sums in segment order and divides by the count.  A group of at most
+// kSegRows rows is therefore summed exactly in the reference's order (KMeansClustering.swift:342-380).
+constexpr int kSegRows = 256;
+
+__global__ void segment_count_kernel(const int64_t* __restrict__ offsets, int k, int64_t* __restrict__ nseg) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c < k) nseg[c] = (offsets[c + 1] - offsets[c] + kSegRows - 1) / kSegRows;
+}
+
+__global__ void segment_sum_kernel(const float* __restrict__ x, int dim, const int32_t* __restrict__ order,
+                                   const int64_t* __restrict__ offsets, const int64_t* __restrict__ seg_off, int k,
+                                   float* __restrict__ partial) {
+  __shared__ int s_c;
+  const int64_t seg = blockIdx.x;
+  if (threadIdx.x == 0) {
+    int lo = 0, hi = k;   // last centroid whose first segment is <= seg
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (seg_off[mid] <= seg) lo = mid; else hi = mid;
     }
+    s_c = lo;
+  }
+  __syncthreads();
+  const int c = s_c;
+  const int64_t begin = offsets[c] + (seg - seg_off[c]) * kSegRows;
+  const int64_t end = min(offsets[c + 1], begin + kSegRows);
+  for (int d = threadIdx.x; d < dim; d += blockDim.x) {
     float s = 0.f;
     int64_t r = begin;
     for (; r + 4 <= end; r += 4) {
@@ -47,6 +66,23 @@ __global__ void centroid_update_kernel(const float* __restrict__ x, int dim, con
       s += v0; s += v1; s += v2; s += v3;
     }
     for (; r < end; ++r) s += __ldg(x + (int64_t)order[r] * dim + d);
+    partial[seg * dim + d] = s;
+  }
+}
+
+__global__ void centroid_finish_kernel(const float* __restrict__ partial, int dim, const int64_t* __restrict__ offsets,
+                                       const int64_t* __restrict__ seg_off, const float* __restrict__ old_c,
+                                       float* __restrict__ new_c) {
+  const int c = blockIdx.x;
+  const int64_t cnt = offsets[c + 1] - offsets[c];
+  const int64_t s0 = seg_off[c], s1 = seg_off[c + 1];
+  for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+    if (cnt == 0) {
+      new_c[(int64_t)c * dim + d] = old_c[(int64_t)c * dim + d];   // an empty cluster keeps its centroid
+      continue;
+    }
+    float s = partial[s0 * dim + d];
+    for (int64_t g = s0 + 1; g < s1; ++g) s += partial[g * dim + d];
     new_c[(int64_t)c * dim + d] = s / (float)cnt;
   }
 }
@@ -93,7 +129,7 @@ int32_t assign_rows(Ctx* ctx, const float* rows, int64_t n, int32_t dim, const f
   if (use_tensor_assign(ctx, n, k)) {
     TensorAssign ta;
     int32_t st = tensor_assign_prepare(ctx, rows, n, dim, &ta);
-    if (st == VSK_OK) st = tensor_assign(ctx, &ta, rows, centroids, k, assign, dist);
+    if (st == VSK_OK) st = tensor_assign(ctx, &ta, rows, centroids, k, assign, dist, false);
     if (st == VSK_OK && cudaStreamSynchronize(ctx->stream) != cudaSuccess) st = VSK_ERR_EXECUTION_FAILED;
     tensor_assign_release(&ta);
     return st;
@@ -193,11 +229,25 @@ int32_t kmeans_dev(Ctx* ctx, const float* rows, int64_t n, int32_t dim, int32_t 
   } release{&ta};
   if (tc) VSK_TRY(tensor_assign_prepare(ctx, rows, n, dim, &ta));
   while (it < max_iters && !converged) {
-    if (tc) VSK_TRY(tensor_assign(ctx, &ta, rows, (const float*)cur, k, assign, (float*)dist));
+    if (tc) VSK_TRY(tensor_assign(ctx, &ta, rows, (const float*)cur, k, assign, (float*)dist, it > 0));
     else VSK_TRY(assign_rows_fp32(ctx, rows, n, dim, (const float*)cur, k, assign, (float*)dist));
     VSK_TRY(launch_stable_group(ctx, assign, n, k, (int32_t*)order, (int64_t*)offsets));
-    centroid_update_kernel<<<k, 128, 0, ctx->stream>>>(rows, dim, (const int32_t*)order, (const int64_t*)offsets,
-                                                       (const float*)cur, (float*)nxt);
+    {
+      // segments per centroid -> first segment of each centroid -> partial sums -> means
+      const int64_t max_segs = n / kSegRows + k + 1;
+      void *nseg, *seg_off, *partial;
+      VSK_TRY(scratch(ctx, SLOT_KM_NSEG, (size_t)(k + 1) * 8, &nseg));
+      VSK_TRY(scratch(ctx, SLOT_KM_SEGOFF, (size_t)(k + 1) * 8, &seg_off));
+      VSK_TRY(scratch(ctx, SLOT_KM_PARTIAL, (size_t)max_segs * dim * 4, &partial));
+      segment_count_kernel<<<(unsigned)ceil_div(k, 256), 256, 0, ctx->stream>>>((const int64_t*)offsets, k, (int64_t*)nseg);
+      VSK_TRY(launch_scan_i64(ctx, (const int64_t*)nseg, k, (int64_t*)seg_off));
+      const int threads = std::min(256, (dim + 31) / 32 * 32);
+      segment_sum_kernel<<<(unsigned)max_segs, threads, 0, ctx->stream>>>(rows, dim, (const int32_t*)order, (const int64_t*)offsets,
+                                                                         (const int64_t*)seg_off, k, (float*)partial);
+      centroid_finish_kernel<<<k, threads, 0, ctx->stream>>>((const float*)partial, dim, (const int64_t*)offsets,
+                                                             (const int64_t*)seg_off, (const float*)cur, (float*)nxt);
+      ctx->stats.kernel_launches += 2;
+    }
     sum_partial_kernel<<<1024, 256, 0, ctx->stream>>>((const float*)dist, n, (double*)partial);
     sum_final_kernel<<<1, 1024, 0, ctx->stream>>>((const double*)partial, 1024, (float*)inert);
     ctx->stats.kernel_launches += 3;

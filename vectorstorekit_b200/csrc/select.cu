@@ -264,8 +264,9 @@ int32_t launch_merge_topk(Ctx* ctx, const float* dist, const int64_t* ids, int32
     return fail(ctx, VSK_ERR_INVALID_BUFFER_SIZE, "merge of %d lists of %d exceeds %d keys", g, k, kCandCap);
   int P = 2;
   while (P < g * k) P <<= 1;
-  merge_kernel<<<(unsigned)nq, SEL_THREADS, P * sizeof(uint64_t), ctx->stream>>>(dist, ids, g, nq, k,
-                                                                                   out_dist, out_ids);
+  // short merges run four times as many CTAs per SM with 128 threads each
+  const int threads = P <= 1024 ? 128 : SEL_THREADS;
+  merge_kernel<<<(unsigned)nq, threads, P * sizeof(uint64_t), ctx->stream>>>(dist, ids, g, nq, k, out_dist, out_ids);
   ctx->stats.kernel_launches++;
   VSK_CUDA(ctx, cudaGetLastError());
   return VSK_OK;

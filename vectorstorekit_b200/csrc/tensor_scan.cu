@@ -36,10 +36,19 @@ namespace {
 constexpr int TM = 128;        // queries per tile (UMMA M)
 constexpr int TN = 256;        // rows per tile (UMMA N)
 constexpr int TK = 64;         // fp16 elements per k-block (128 bytes: one swizzle atom)
-constexpr int STAGES = 4;
-constexpr int A_BYTES = TM * TK * 2;   // 16 KB
-constexpr int B_BYTES = TN * TK * 2;   // 32 KB
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int A_BYTES = TM * TK * 2;   // 16 KB: 128 query rows x 64 fp16
+constexpr int RING_BYTES = 192 * 1024; // operand ring: 4 stages of 48 KB (one CTA per tile) or 6 of 32 KB (CTA pair)
+constexpr int MAX_STAGES = 6;
+// CTAS = 1: a CTA computes a 128-query x 256-row tile from a 16 KB query box and a 32 KB row box per stage.
+// CTAS = 2: a pair of CTAs (a cluster of two SMs) computes a 256-query x 256-row tile with one
+//           tcgen05.mma.cta_group::2; each CTA stages its 128 queries and HALF of the rows (16 KB + 16 KB),
+//           so every CTA moves a third fewer operand bytes from L2 per flop and the ring holds six stages.
+template <int CTAS> struct Geo {
+  static constexpr int B_BYTES = (TN / CTAS) * TK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = RING_BYTES / STAGE_BYTES;
+  static constexpr int TX_BYTES = STAGE_BYTES * CTAS;   // bytes that complete a stage's full barrier
+};
 constexpr int TC_THREADS = 320;        // warp 0 producer, warp 1 MMA issuer, warps 2..9 epilogue
 constexpr int EPI_WARPS = 8;           // two per tensor-memory lane quarter: each takes half of the tile's columns
 constexpr int EPI_COLS = TN / 2;       // columns per epilogue warp
@@ -49,11 +58,11 @@ constexpr int TMEM_COLS = 512;
 
 struct TcSmem {
   // stage buffers first: each must start on a 1024-byte boundary for the 128B swizzle
-  uint8_t stage[STAGES][STAGE_BYTES];
+  uint8_t ring[RING_BYTES];
   float beta[2][EPI_WARPS][EPI_COLS];   // per accumulator buffer and epilogue warp: its columns' per-row terms
   uint32_t masks[EPI_WARPS * 32][EPI_GROUPS + 1];  // per epilogue thread: pass bits of its 128 values (padded row)
-  uint64_t full[STAGES];
-  uint64_t empty[STAGES];
+  uint64_t full[MAX_STAGES];
+  uint64_t empty[MAX_STAGES];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
   uint64_t drain;
@@ -123,6 +132,42 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, u
       : "memory");
 }
 
+// ---- helpers for a pair of CTAs (cluster of two) ---------------------------------------------
+// shared::cluster address of the same shared-memory location in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// TMA load issued by either CTA of the pair; the bytes are counted on the barrier at `bar_cluster_addr`
+// (the leader's full barrier).  No multicast: each CTA fetches only its own boxes.
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int32_t c0, int32_t c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+          smem_u32(dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
+      : "memory");
+}
+// completion of all MMAs issued so far by this thread -> one arrival on the barrier at a shared::cluster address
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar_cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tc_mma_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
@@ -172,17 +217,43 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
 
 // Instruction descriptor: fp32 accumulate, fp16 A and B, both K-major, N = 256, M = 128.
 constexpr uint32_t kIdesc = (1u << 4) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(TM >> 4) << 24);
+// the pair's instruction: M = 256 (128 rows in each CTA's tensor memory), N = 256
+constexpr uint32_t kIdescPair = (1u << 4) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)((2 * TM) >> 4) << 24);
 
-template <int MODE, bool HAS_BETA>
+template <int MODE, bool HAS_BETA, int CTAS>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_x, TcArgs a) {
+  using G = Geo<CTAS>;
+  constexpr int STAGES = G::STAGES;
+  constexpr int STAGE_BYTES = G::STAGE_BYTES;
   extern __shared__ uint8_t smem_raw[];
   TcSmem* sm = reinterpret_cast<TcSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // a pair shares tiles: `unit` counts single CTAs (CTAS = 1) or pairs (CTAS = 2); `rank` is the CTA's place in its pair
+  const uint32_t rank = CTAS == 2 ? (blockIdx.x & 1u) : 0u;
+  const int64_t unit = CTAS == 2 ? (blockIdx.x >> 1) : blockIdx.x;
+  const int64_t units = CTAS == 2 ? (gridDim.x >> 1) : gridDim.x;
+  constexpr int QT = TM * CTAS;  // queries per tile
 
-  const int64_t qtiles = (a.nq + TM - 1) / TM;
+  const int64_t qtiles = (a.nq + QT - 1) / QT;
   const int64_t ntiles = (a.row_end - a.row_begin + TN - 1) / TN;
   const int64_t tiles = qtiles * ntiles;
+  // i-th tile of this unit.  Query-tile-fastest order interleaves units over the tile list (units that run
+  // together read the same rows).  In row-tile-fastest order a unit OWNS whole query tiles and walks all their
+  // row tiles in turn, so a query's running state (slot count, best key) stays in its thread's registers.
+  auto tile_at = [&](int64_t i, int64_t& qt, int64_t& nt) -> bool {
+    if (a.row_tile_fastest) {
+      const int64_t qi = i / ntiles;
+      nt = i - qi * ntiles;
+      qt = unit + qi * units;
+      return qt < qtiles;
+    }
+    const int64_t t = unit + i * units;
+    if (t >= tiles) return false;
+    nt = t / qtiles;
+    qt = t - nt * qtiles;
+    return true;
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -191,20 +262,28 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&sm->tmem_full[b], 1);
-      mbar_init(&sm->tmem_empty[b], EPI_WARPS);
+      mbar_init(&sm->tmem_empty[b], EPI_WARPS * CTAS);   // the leader's copy collects both CTAs' epilogue warps
     }
     mbar_init(&sm->drain, 1);
     sm->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm->tmem_base)),
-                 "r"(TMEM_COLS)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (CTAS == 2) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm->tmem_base)),
+                   "r"(TMEM_COLS)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm->tmem_base)),
+                   "r"(TMEM_COLS)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (CTAS == 2) cluster_sync();   // both CTAs' barriers exist before anything arrives on them remotely
   tc_fence_after();
   const uint32_t tmem_base = sm->tmem_base;
 
@@ -216,23 +295,34 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       uint32_t issued = 0;       // bit s: a copy into stage s was issued ...
       uint32_t issued_ph = 0;    // ... with this full-barrier parity
       bool ok = true;
-      for (int64_t t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
-        const int64_t nt = a.row_tile_fastest ? t % ntiles : t / qtiles;
-        const int64_t qt = a.row_tile_fastest ? t / ntiles : t - nt * qtiles;
-        const int32_t qrow = (int32_t)(qt * TM);
-        const int32_t xrow = (int32_t)(a.row_begin + nt * TN);
+      for (int64_t i = 0; ok; ++i) {
+        int64_t qt, nt;
+        if (!tile_at(i, qt, nt)) break;
+        const int32_t qrow = (int32_t)(qt * QT + rank * TM);                       // this CTA's 128 queries
+        const int32_t xrow = (int32_t)(a.row_begin + nt * TN + rank * (TN / CTAS)); // its share of the 256 rows
         for (int kb = 0; kb < a.kblocks; ++kb) {
           if (!mbar_wait(&sm->empty[s], ph ^ 1, sm, a.err, 1)) { ok = false; break; }
-          mbar_expect_tx(&sm->full[s], STAGE_BYTES);
-          tma_load_2d(&sm->stage[s][0], &map_q, &sm->full[s], kb * TK, qrow);
-          tma_load_2d(&sm->stage[s][A_BYTES], &map_x, &sm->full[s], kb * TK, xrow);
+          uint8_t* st = sm->ring + s * STAGE_BYTES;
+          if (CTAS == 2) {
+            // the leader's full barrier counts the bytes of both CTAs
+            if (rank == 0) mbar_expect_tx(&sm->full[s], G::TX_BYTES);
+            const uint32_t bar = map_to_cta(smem_u32(&sm->full[s]), 0);
+            tma_load_2d_pair(st, &map_q, bar, kb * TK, qrow);
+            tma_load_2d_pair(st + A_BYTES, &map_x, bar, kb * TK, xrow);
+          } else {
+            mbar_expect_tx(&sm->full[s], G::TX_BYTES);
+            tma_load_2d(st, &map_q, &sm->full[s], kb * TK, qrow);
+            tma_load_2d(st + A_BYTES, &map_x, &sm->full[s], kb * TK, xrow);
+          }
           issued |= 1u << s;
           issued_ph = (issued_ph & ~(1u << s)) | (ph << s);
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
       }
-      // copies still in flight must land before the CTA's shared memory is released
-      for (int i = 0; i < STAGES; ++i)
+      // copies still in flight must land before the CTA's shared memory is released (the second CTA of a pair
+      // cannot poll the leader's barrier: the cluster barrier at the end covers it, since the leader consumes
+      // every stage it was told to expect)
+      for (int i = 0; i < STAGES && rank == 0; ++i)
         if (issued & (1u << i)) {
           for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
             if (mbar_try_wait(&sm->full[i], (issued_ph >> i) & 1)) break;
@@ -241,13 +331,15 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         }
     }
   } else if (warp == 1) {
-    // ---------------- MMA issuer ----------------
-    if (lane == 0) {
+    // ---------------- MMA issuer (the leader of a pair issues for both CTAs) ----------------
+    if (lane == 0 && rank == 0) {
       int s = 0;
       uint32_t ph = 0;
       int64_t local = 0;
       bool ok = true;
-      for (int64_t t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++local) {
+      for (;; ++local) {
+        int64_t qt_unused, nt_unused;
+        if (!ok || !tile_at(local, qt_unused, nt_unused)) break;
         const int acc = (int)(local & 1);
         const uint32_t aph = (uint32_t)((local >> 1) & 1);
         if (!mbar_wait(&sm->tmem_empty[acc], aph ^ 1, sm, a.err, 2)) { ok = false; break; }
@@ -256,20 +348,35 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         for (int kb = 0; kb < a.kblocks; ++kb) {
           if (!mbar_wait(&sm->full[s], ph, sm, a.err, 3)) { ok = false; break; }
           tc_fence_after();
-          const uint64_t adesc = make_desc(smem_u32(&sm->stage[s][0]));
-          const uint64_t bdesc = make_desc(smem_u32(&sm->stage[s][A_BYTES]));
+          const uint64_t adesc = make_desc(smem_u32(sm->ring + s * STAGE_BYTES));
+          const uint64_t bdesc = make_desc(smem_u32(sm->ring + s * STAGE_BYTES + A_BYTES));
 #pragma unroll
           for (int k4 = 0; k4 < TK / 16; ++k4) {
             // 16 fp16 = 32 bytes further along K inside the swizzle atom: +2 in 16-byte units
-            tc_mma(tmem_d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), kIdesc, (kb | k4) ? 1u : 0u);
+            if (CTAS == 2) tc_mma_pair(tmem_d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), kIdescPair, (kb | k4) ? 1u : 0u);
+            else tc_mma(tmem_d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), kIdesc, (kb | k4) ? 1u : 0u);
           }
-          tc_commit(&sm->empty[s]);  // stage is free once these MMAs have read it
+          // the stage is free, in both CTAs, once these MMAs have read it
+          if (CTAS == 2) {
+            tc_commit_pair(map_to_cta(smem_u32(&sm->empty[s]), 0));
+            tc_commit_pair(map_to_cta(smem_u32(&sm->empty[s]), 1));
+          } else {
+            tc_commit(&sm->empty[s]);
+          }
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
-        if (ok) tc_commit(&sm->tmem_full[acc]);
+        if (ok) {
+          if (CTAS == 2) {
+            tc_commit_pair(map_to_cta(smem_u32(&sm->tmem_full[acc]), 0));
+            tc_commit_pair(map_to_cta(smem_u32(&sm->tmem_full[acc]), 1));
+          } else {
+            tc_commit(&sm->tmem_full[acc]);
+          }
+        }
       }
       // all issued MMAs must retire before tensor memory is freed
-      tc_commit(&sm->drain);
+      if (CTAS == 2) tc_commit_pair(map_to_cta(smem_u32(&sm->drain), 0));
+      else tc_commit(&sm->drain);
       for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
         if (mbar_try_wait(&sm->drain, 0)) break;
         __nanosleep(64);
@@ -284,12 +391,17 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     const float alpha = __ldg(a.alpha);
     int64_t local = 0;
     bool ok = true;
-    for (int64_t t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++local) {
+    int run_cnt = 0;                 // row-tile-fastest order: keys this thread has stored for its query so far
+    float run_bv = CUDART_INF_F;     // ... and its best value / row so far (SCAN_ARGMIN)
+    int64_t run_bn = 0;
+    for (;; ++local) {
+      int64_t qt, nt;
+      if (!ok || !tile_at(local, qt, nt)) break;
       const int acc = (int)(local & 1);
       const uint32_t aph = (uint32_t)((local >> 1) & 1);
-      const int64_t nt = a.row_tile_fastest ? t % ntiles : t / qtiles;
-      const int64_t qt = a.row_tile_fastest ? t / ntiles : t - nt * qtiles;
-      const int64_t q = qt * TM + et;
+      const int64_t q = qt * QT + rank * TM + et;
+      const bool owned = a.row_tile_fastest != 0;
+      if (owned && nt == 0) { run_cnt = 0; run_bv = CUDART_INF_F; run_bn = 0; }
       const int64_t n0 = a.row_begin + nt * TN;
       const bool qok = q < a.nq;
       if (HAS_BETA) {
@@ -335,7 +447,13 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             if (j < left && val < bv) { bv = val; bj = c * 32 + j; }   // strict '<': the lowest row wins ties
           }
         }
-        if (qok && bv < CUDART_INF_F) atomicMin(a.best + q, (unsigned long long)make_key(bv, (uint32_t)(n0 + bj)));
+        if (owned) {
+          if (bv < run_bv) { run_bv = bv; run_bn = n0 + bj; }   // row tiles come in ascending order: '<' keeps the lowest row
+          if (nt == ntiles - 1 && qok && run_bv < CUDART_INF_F)
+            atomicMin(a.best + q, (unsigned long long)make_key(run_bv, (uint32_t)run_bn));
+        } else if (qok && bv < CUDART_INF_F) {
+          atomicMin(a.best + q, (unsigned long long)make_key(bv, (uint32_t)(n0 + bj)));
+        }
       } else {
         // Pass 1: which of this query's 256 values pass the threshold (one bit each).  A thread then
         // reserves all its slots with ONE atomic per tile; pass 2 re-reads the accumulator groups that
@@ -361,8 +479,13 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           m[c - c0] = bits;
           cnt += __popc(bits);
         }
+        // Slot reservation.  Interleaved order: one atomic per tile.  Owned order: this warp's half of the
+        // columns appends to its own half of the query's list, counted in a register; the two 16-bit counts are
+        // stored after the last row tile.
         int base = 0;
-        if (cnt) base = atomicAdd(&a.cand.count[q], cnt);
+        const int cap_here = owned ? a.cap / 2 : a.cap;
+        if (owned) base = run_cnt;
+        else if (cnt) base = atomicAdd(&a.cand.count[q], cnt);
 #pragma unroll 1
         for (int c = c0; c < c0 + EPI_GROUPS; ++c) {
           const uint32_t bits = m[c - c0];
@@ -370,30 +493,40 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           float v[32];
           tc_ld32(trow + (uint32_t)(c * 32), v);
           const int64_t nc = n0 + c * 32;
-          uint64_t* dst = a.cand.keys + q * a.cap;
+          uint64_t* dst = a.cand.keys + q * a.cap + (owned ? (ew >> 2) * cap_here : 0);
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             if ((bits >> j) & 1u) {
               const float val = HAS_BETA ? fmaf(v[j], alpha, sm->beta[acc][ew][(c - c0) * 32 + j]) : v[j] * alpha;
               const int pos = base + __popc(bits & ((1u << j) - 1u));
-              if (pos < a.cap) dst[pos] = make_key(val, (uint32_t)(nc + j));
+              if (pos < cap_here) dst[pos] = make_key(val, (uint32_t)(nc + j));
             }
           }
           base += __popc(bits);
         }
+        if (owned) {
+          run_cnt += cnt;
+          if (nt == ntiles - 1 && qok)
+            reinterpret_cast<unsigned short*>(a.cand.count)[q * 2 + (ew >> 2)] = (unsigned short)min(run_cnt, 65535);
+        }
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&sm->tmem_empty[acc]);
+      if (lane == 0) {
+        if (CTAS == 2) mbar_arrive_cluster(map_to_cta(smem_u32(&sm->tmem_empty[acc]), 0));
+        else mbar_arrive(&sm->tmem_empty[acc]);
+      }
     }
   }
 
   // ---------------- teardown ----------------
   tc_fence_before();
   __syncthreads();
+  if (CTAS == 2) cluster_sync();   // neither CTA leaves (or frees tensor memory) while its partner may still reach it
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    if (CTAS == 2) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
 }
 
@@ -769,26 +902,47 @@ int32_t tensor_prepare(Index* ix) {
   return VSK_OK;
 }
 
+// Launches the scan over tiles.  pair = true: clusters of two CTAs (tcgen05 cta_group::2); `mx` must then be a
+// tensor map with 128-row boxes (each CTA stages half of a 256-row tile).
 template <int MODE>
-int32_t launch_tc(Ctx* ctx, const CUtensorMap& mq, const CUtensorMap& mx, const TcArgs& a, bool has_beta) {
-  static bool attr_done[4][2] = {};
-  auto kern = has_beta ? tc_scan_kernel<MODE, true> : tc_scan_kernel<MODE, false>;
-  if (!attr_done[MODE][has_beta]) {
+int32_t launch_tc(Ctx* ctx, const CUtensorMap& mq, const CUtensorMap& mx, const TcArgs& a, bool has_beta, bool pair) {
+  static bool attr_done[4][2][2] = {};
+  void (*kern)(CUtensorMap, CUtensorMap, TcArgs) =
+      pair ? (has_beta ? tc_scan_kernel<MODE, true, 2> : tc_scan_kernel<MODE, false, 2>)
+           : (has_beta ? tc_scan_kernel<MODE, true, 1> : tc_scan_kernel<MODE, false, 1>);
+  if (!attr_done[MODE][has_beta][pair]) {
     VSK_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_BYTES));
-    attr_done[MODE][has_beta] = true;
+    attr_done[MODE][has_beta][pair] = true;
   }
-  const int64_t tiles = ceil_div(a.nq, TM) * ceil_div(a.row_end - a.row_begin, TN);
+  const int per_tile = pair ? 2 * TM : TM;
+  const int64_t tiles = ceil_div(a.nq, per_tile) * ceil_div(a.row_end - a.row_begin, TN);
   if (tiles <= 0) return VSK_OK;
-  const unsigned grid = (unsigned)std::min<int64_t>(tiles, ctx->prop.multiProcessorCount);
+  const int sms = ctx->prop.multiProcessorCount;
+  unsigned grid = pair ? 2u * (unsigned)std::min<int64_t>(tiles, sms / 2) : (unsigned)std::min<int64_t>(tiles, sms);
   prof_begin(ctx);
-  kern<<<grid, TC_THREADS, TC_SMEM_BYTES, ctx->stream>>>(mq, mx, a);
+  if (pair) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(TC_THREADS);
+    cfg.dynamicSmemBytes = TC_SMEM_BYTES;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 2;
+    at[0].val.clusterDim.y = 1;
+    at[0].val.clusterDim.z = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    VSK_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, mq, mx, a));
+  } else {
+    kern<<<grid, TC_THREADS, TC_SMEM_BYTES, ctx->stream>>>(mq, mx, a);
+  }
   prof_end(ctx);
   ctx->stats.kernel_launches++;
-  ctx->stats.tensor_tiles += tiles;
+  ctx->stats.tensor_tiles += tiles * (pair ? 2 : 1);
   VSK_CUDA(ctx, cudaGetLastError());
   return VSK_OK;
 }
-
 
 // ---- k-means assignment on the tensor cores ----------------------------------------------------
 // Data rows are the streamed operand (the "query" side of the tile), centroids the small one.
@@ -799,7 +953,7 @@ int32_t launch_tc(Ctx* ctx, const CUtensorMap& mq, const CUtensorMap& mx, const 
 //   exact   the listed centroids are compared with the direct fp32 formula sum (x-c)^2; the smallest
 //           (value, index) wins, as the reference's strict '<' scan does (KMeansClustering.swift:283-288)
 // A row whose list overflows (more than kAssignCap near-ties) is re-done by the fp32 tile.
-constexpr int kAssignCap = 8;
+constexpr int kAssignCap = 16;   // two sub-lists of 8: one per half of the centroid columns of a tile
 
 // eps per data row against the current centroids; stats of the centroid operand are read on the device.
 __global__ void assign_bound_kernel(const float* __restrict__ xn16, const float* __restrict__ xe16,
@@ -827,6 +981,35 @@ __global__ void assign_threshold_kernel(const unsigned long long* __restrict__ b
   count[r] = 0;
 }
 
+// Threshold from the previous assignment (Lloyd iterations after the first): with u the exact value
+// |c_p|^2 - 2 x.c_p of the centroid the row was assigned to last time, the nearest centroid c* has exact value
+// <= u, hence coarse value <= u + eps.  One warp per row computes u = sum (x-c_p)^2 - |x|^2 in fp32; the
+// threshold is u + 2 eps (the second eps covers the fp32 rounding of u itself).  This replaces pass 1.
+__global__ void assign_prev_threshold_kernel(const float* __restrict__ x, int64_t n, int dim, const float* __restrict__ cent,
+                                             const int32_t* __restrict__ prev, const float* __restrict__ eps,
+                                             float* __restrict__ thr, int32_t* __restrict__ count) {
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= n) return;
+  const int lane = threadIdx.x & 31;
+  const float* xr = x + row * dim;
+  const float* cr = cent + (int64_t)prev[row] * dim;
+  float d2 = 0.f, x2 = 0.f;
+  for (int i = lane; i < dim; i += 32) {
+    const float xv = __ldg(xr + i), d = xv - __ldg(cr + i);
+    d2 = fmaf(d, d, d2);
+    x2 = fmaf(xv, xv, x2);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    d2 += __shfl_xor_sync(0xffffffffu, d2, o);
+    x2 += __shfl_xor_sync(0xffffffffu, x2, o);
+  }
+  if (lane == 0) {
+    thr[row] = (d2 - x2) + 2.0f * eps[row] + 4.0f * 5.9604645e-8f * (d2 + x2);
+    count[row] = 0;
+  }
+}
+
 // one warp per data row: exact squared distances to the listed centroids
 __global__ void assign_exact_kernel(const float* __restrict__ x, int64_t n, int dim, const float* __restrict__ cent,
                                     const uint64_t* __restrict__ keys, const int32_t* __restrict__ count,
@@ -835,15 +1018,17 @@ __global__ void assign_exact_kernel(const float* __restrict__ x, int64_t n, int 
   const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= n) return;
   const int lane = threadIdx.x & 31;
-  const int cnt = count[row];
-  if (cnt > kAssignCap || cnt <= 0) {
+  // two 16-bit counts: the sub-lists written by the two halves of the tile columns
+  const unsigned packed = (unsigned)count[row];
+  const int cnt_a = (int)(packed & 0xffffu), cnt_b = (int)(packed >> 16);
+  if (cnt_a > kAssignCap / 2 || cnt_b > kAssignCap / 2 || cnt_a + cnt_b <= 0) {
     if (lane == 0) bad_rows[atomicAdd(bad_count, 1)] = (int32_t)row;
     return;
   }
   const float* xr = x + row * dim;
   uint64_t bestk = kEmptyKey;
-  for (int c = 0; c < cnt; ++c) {
-    const uint32_t id = (uint32_t)keys[row * kAssignCap + c];
+  for (int c = 0; c < cnt_a + cnt_b; ++c) {
+    const uint32_t id = (uint32_t)keys[row * kAssignCap + (c < cnt_a ? c : kAssignCap / 2 + (c - cnt_a))];
     const float* cr = cent + (int64_t)id * dim;
     float s = 0.f;
     for (int i = lane; i < dim; i += 32) {
@@ -945,9 +1130,12 @@ int32_t tensor_search(Index* ix, const float* q, int64_t nq, int32_t k, const fl
   ctx->stats.kernel_launches++;
   VSK_CUDA(ctx, cudaGetLastError());
 
+  // CTA pairs (cta_group::2) when there are at least two query tiles to pair up
+  static const int64_t pair_mode = schedule_tuning("VSK_TC_PAIR", 0);
+  const bool pair = pair_mode != 0 && nq > TM;
   CUtensorMap mq, mx;
   VSK_TRY(make_map(ctx, q16, nq, dim16, TM, &mq));
-  VSK_TRY(make_map(ctx, ix->rows16, ix->n, dim16, TN, &mx));
+  VSK_TRY(make_map(ctx, ix->rows16, ix->n, dim16, pair ? TN / 2 : TN, &mx));
 
   // ---- candidate lists and the chunk schedule ----
   CandLists cand;
@@ -981,7 +1169,7 @@ int32_t tensor_search(Index* ix, const float* q, int64_t nq, int32_t k, const fl
   a.mode = SCAN_DENSE;
   a.row_begin = 0;
   a.row_end = seen;
-  VSK_TRY(launch_tc<SCAN_DENSE>(ctx, mq, mx, a, has_beta));
+  VSK_TRY(launch_tc<SCAN_DENSE>(ctx, mq, mx, a, has_beta, pair));
   sel.dense_count = (int32_t)seen;
   sel.max_count = (int32_t)seen;
   sel.k = k;
@@ -1001,7 +1189,7 @@ int32_t tensor_search(Index* ix, const float* q, int64_t nq, int32_t k, const fl
     chunk = std::min(chunk, n - seen);
     a.row_begin = seen;
     a.row_end = seen + chunk;
-    VSK_TRY(launch_tc<SCAN_THRESHOLD>(ctx, mq, mx, a, has_beta));
+    VSK_TRY(launch_tc<SCAN_THRESHOLD>(ctx, mq, mx, a, has_beta, pair));
     sel.max_count = schedule_max_count(seen, chunk, keep);
     seen += chunk;
     if (seen == n) sel.cert_eps = eps;
@@ -1098,7 +1286,7 @@ void tensor_assign_release(TensorAssign* ta) {
 }
 
 int32_t tensor_assign(Ctx* ctx, TensorAssign* ta, const float* rows, const float* centroids, int32_t k,
-                      int32_t* assign, float* dist) {
+                      int32_t* assign, float* dist, bool assign_holds_previous) {
   static_assert(sizeof(CUtensorMap) <= sizeof(ta->map_rows), "tensor map storage too small");
   const int64_t n = ta->n;
   const int dim = ta->dim, dim16 = ta->dim16;
@@ -1143,12 +1331,16 @@ int32_t tensor_assign(Ctx* ctx, TensorAssign* ta, const float* rows, const float
   a.cand.thr = ta->thr;
   a.cand.flags = nullptr;
   a.cand.nq = n;
-  VSK_CUDA(ctx, cudaMemsetAsync(ta->best, 0xff, (size_t)n * sizeof(unsigned long long), ctx->stream));
-  a.mode = SCAN_ARGMIN;
-  VSK_TRY(launch_tc<SCAN_ARGMIN>(ctx, mr, mc, a, true));
-  assign_threshold_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, ctx->stream>>>(ta->best, eps, n, ta->thr, ta->count);
+  if (assign_holds_previous) {
+    assign_prev_threshold_kernel<<<(unsigned)ceil_div(n, 8), 256, 0, ctx->stream>>>(rows, n, dim, centroids, assign, eps, ta->thr, ta->count);
+  } else {
+    VSK_CUDA(ctx, cudaMemsetAsync(ta->best, 0xff, (size_t)n * sizeof(unsigned long long), ctx->stream));
+    a.mode = SCAN_ARGMIN;
+    VSK_TRY(launch_tc<SCAN_ARGMIN>(ctx, mr, mc, a, true, false));
+    assign_threshold_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, ctx->stream>>>(ta->best, eps, n, ta->thr, ta->count);
+  }
   a.mode = SCAN_THRESHOLD;
-  VSK_TRY(launch_tc<SCAN_THRESHOLD>(ctx, mr, mc, a, true));
+  VSK_TRY(launch_tc<SCAN_THRESHOLD>(ctx, mr, mc, a, true, false));
   assign_exact_kernel<<<(unsigned)ceil_div(n, 8), 256, 0, ctx->stream>>>(rows, n, dim, centroids, ta->keys, ta->count, assign, dist,
                                                                          ta->bad_rows, (int32_t*)(sm + 6));
   ctx->stats.kernel_launches += 2;

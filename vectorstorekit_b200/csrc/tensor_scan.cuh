@@ -35,8 +35,10 @@ struct TensorAssign {
   alignas(64) unsigned char map_rows[128] = {};  // TMA tensor map of rows16
 };
 int32_t tensor_assign_prepare(Ctx* ctx, const float* rows, int64_t n, int32_t dim, TensorAssign* ta);
+// assign_holds_previous: `assign` holds, for every row, a valid centroid index (the previous iteration's
+// assignment), which gives the candidate threshold without the coarse arg-min pass.
 int32_t tensor_assign(Ctx* ctx, TensorAssign* ta, const float* rows, const float* centroids, int32_t k,
-                      int32_t* assign, float* dist);
+                      int32_t* assign, float* dist, bool assign_holds_previous);
 void tensor_assign_release(TensorAssign* ta);
 
 // Search over an int8-coded flat index (sq8.cu).
