@@ -161,6 +161,34 @@ def test_filtered_manhattan(vsk, dev, cpu_oracle):
     assert_topk_parity(ud, ui, rd2, ri2)
 
 
+@pytest.mark.parametrize("metric", ["manhattan", "euclidean", "cosine"])
+def test_filtered_search_grouped_by_mask(vsk, dev, cpu_oracle, metric):
+    """Few distinct query masks: each group of queries is scanned only against its eligible rows (row lists,
+    narrow query tiles for small groups).  Group sizes 130 / 70 / 40 / 33 / 9, one mask that matches nothing,
+    one that combines two bits."""
+    rng = np.random.default_rng(21)
+    n, d = 40_000, 48
+    x = rng.uniform(-1, 1, (n, d)).astype(np.float32)
+    rm = rng.integers(0, 2 ** 16, n, dtype=np.uint64)          # bits 0..15 set at random, higher bits clear
+    masks = [1 << 2, 1 << 9, (1 << 3) | (1 << 4), 1 << 40, 1 << 15]
+    sizes = [130, 70, 40, 33, 9]
+    qm = np.concatenate([np.full(s, m, np.uint64) for m, s in zip(masks, sizes)])
+    perm = rng.permutation(qm.size)
+    qm = qm[perm]                                               # groups interleaved in the batch
+    q = rng.uniform(-1, 1, (qm.size, d)).astype(np.float32)
+    ix = _flat(vsk, dev, metric, x, rm)
+    try:
+        gd, gi = ix.batchSearch(q, 20, qm)
+    finally:
+        ix.close()
+    rd, ri = cpu_oracle.flat_search(oracle.METRIC_IDS[metric], q, x, 20, rm, qm)
+    assert_topk_parity(gd, gi, rd, ri)
+    none = qm == np.uint64(1 << 40)
+    assert none.sum() == 33 and np.all(gi[none] == -1) and np.all(np.isinf(gd[none]))
+    ok = ~none
+    assert np.all((rm[gi[ok]] & qm[ok][:, None]) != 0)
+
+
 def test_selective_filter_and_short_results(vsk, dev, cpu_oracle):
     rng = np.random.default_rng(9)
     x = rng.standard_normal((6000, 16)).astype(np.float32)

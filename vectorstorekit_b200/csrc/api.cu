@@ -6,6 +6,7 @@
 #include <cstdio>
 #include <cmath>
 #include <cstdlib>
+#include <algorithm>
 #include <cstring>
 #include <functional>
 
@@ -242,6 +243,109 @@ static int32_t fp32_search(Index* ix, const float* q, int64_t nq, const int32_t*
   return fp32_topk(ix->ctx, a, ix->n, nq, sub_dev, k, ix->id_base, out_dist, out_ids, level);
 }
 
+// ---- filtered search, grouped by mask ---------------------------------------------------------
+// Queries that carry the same filter mask share one set of eligible rows.  When a batch has few distinct
+// masks, each group of queries is scanned only against its eligible rows (a list of row numbers made by one
+// compaction pass over the 8-byte row masks), instead of computing every (query, row) value and discarding the
+// ineligible ones afterwards: the FP32 work drops by the share of rows the filter rejects.
+__global__ void mask_compact_kernel(const uint64_t* __restrict__ masks, int64_t n, uint64_t qmask,
+                                    int32_t* __restrict__ rows, int32_t* counter) {
+  __shared__ int warp_base[8];
+  __shared__ int block_base;
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const bool pass = i < n && (masks[i] & qmask) != 0;
+  const unsigned bal = __ballot_sync(0xffffffffu, pass);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) warp_base[warp] = __popc(bal);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int tot = 0;
+    for (int w = 0; w < 8; ++w) { const int c = warp_base[w]; warp_base[w] = tot; tot += c; }
+    block_base = tot ? atomicAdd(counter, tot) : 0;
+  }
+  __syncthreads();
+  if (pass) rows[block_base + warp_base[warp] + __popc(bal & ((1u << lane) - 1u))] = (int32_t)i;
+}
+
+__global__ void fill_empty_results_kernel(const int32_t* __restrict__ qpos, int64_t m, int k, float* out_dist,
+                                          int64_t* out_ids) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= m * k) return;
+  const int64_t q = qpos[i / k];
+  out_dist[q * k + i % k] = INFINITY;
+  out_ids[q * k + i % k] = -1;
+}
+
+static int pick_query_tile(int64_t g) {
+  auto pad = [&](int bm) { return ceil_div(g, bm) * bm; };
+  const double best = (double)pad(32);
+  if ((double)pad(128) <= 1.1 * best) return 128;
+  if ((double)pad(64) <= 1.1 * best) return 64;
+  return 32;
+}
+
+// Returns *handled = false (and does nothing) when the batch has too many distinct masks to profit.
+static int32_t filtered_grouped_search(Index* ix, const float* q, int64_t nq, int32_t k, const float* qnorm,
+                                       const uint64_t* qmasks, float* out_dist, int64_t* out_ids, bool* handled) {
+  Ctx* ctx = ix->ctx;
+  *handled = false;
+  std::vector<uint64_t> hm((size_t)nq);
+  VSK_CUDA(ctx, cudaMemcpyAsync(hm.data(), qmasks, (size_t)nq * 8, cudaMemcpyDeviceToHost, ctx->stream));
+  VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  std::vector<int32_t> perm((size_t)nq);
+  for (int64_t i = 0; i < nq; ++i) perm[(size_t)i] = (int32_t)i;
+  std::stable_sort(perm.begin(), perm.end(), [&](int32_t a, int32_t b) { return hm[(size_t)a] < hm[(size_t)b]; });
+  std::vector<int64_t> starts;
+  for (int64_t i = 0; i < nq; ++i)
+    if (i == 0 || hm[(size_t)perm[(size_t)i]] != hm[(size_t)perm[(size_t)i - 1]]) starts.push_back(i);
+  starts.push_back(nq);
+  const int64_t groups = (int64_t)starts.size() - 1;
+  // Worth it?  Cost is proportional to (padded queries) x (rows scanned).  Grouped: each group's queries padded
+  // to its query tile, over its eligible rows (assumed to be at most 60 % of the rows); ungrouped: all queries
+  // padded to 128, over all rows.
+  int64_t padded = 0;
+  for (int64_t g = 0; g < groups; ++g) {
+    const int64_t sz = starts[(size_t)g + 1] - starts[(size_t)g];
+    padded += ceil_div(sz, pick_query_tile(sz)) * pick_query_tile(sz);
+  }
+  if (groups > 256 || (double)padded * 0.6 > (double)(ceil_div(nq, 128) * 128)) return VSK_OK;
+  *handled = true;
+  void *dperm, *drows, *dcount;
+  VSK_TRY(scratch(ctx, SLOT_FILTER_PERM, (size_t)nq * 4, &dperm));
+  VSK_TRY(scratch(ctx, SLOT_FILTER_ROWS, (size_t)ix->n * 4, &drows));
+  VSK_TRY(scratch(ctx, SLOT_FILTER_COUNT, 16, &dcount));
+  VSK_CUDA(ctx, cudaMemcpyAsync(dperm, perm.data(), (size_t)nq * 4, cudaMemcpyHostToDevice, ctx->stream));
+  VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));   // perm is a local
+  for (int64_t g = 0; g < groups; ++g) {
+    const int64_t b = starts[(size_t)g], e = starts[(size_t)g + 1];
+    const uint64_t m = hm[(size_t)perm[(size_t)b]];
+    const int32_t* qpos = (const int32_t*)dperm + b;
+    VSK_CUDA(ctx, cudaMemsetAsync(dcount, 0, 4, ctx->stream));
+    mask_compact_kernel<<<(unsigned)ceil_div(ix->n, 256), 256, 0, ctx->stream>>>(ix->masks, ix->n, m, (int32_t*)drows, (int32_t*)dcount);
+    ctx->stats.kernel_launches++;
+    int32_t cnt = 0;
+    VSK_CUDA(ctx, cudaMemcpyAsync(&cnt, dcount, 4, cudaMemcpyDeviceToHost, ctx->stream));
+    VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (cnt == 0) {
+      fill_empty_results_kernel<<<(unsigned)ceil_div((e - b) * k, 256), 256, 0, ctx->stream>>>(qpos, e - b, k, out_dist, out_ids);
+      ctx->stats.kernel_launches++;
+      continue;
+    }
+    ExactScanArgs a{};
+    a.metric = ix->metric;
+    a.q = q;
+    a.x = ix->rows;
+    a.x_rows = (const int32_t*)drows;
+    a.bm_hint = pick_query_tile(e - b);
+    a.dim = ix->dim;
+    a.qnorm = qnorm;
+    a.xnorm = ix->row_norm;
+    VSK_TRY(fp32_topk(ctx, a, cnt, e - b, qpos, k, ix->id_base, out_dist, out_ids, 0));
+  }
+  VSK_CUDA(ctx, cudaGetLastError());
+  return VSK_OK;
+}
+
 constexpr int64_t kQueryBatch = 16384;  // queries per pass: bounds the candidate workspace at 512 MB
 
 static int32_t flat_search_dev(Index* ix, const float* q, int64_t nq, int32_t k, const uint64_t* qmasks,
@@ -267,7 +371,12 @@ static int32_t flat_search_dev(Index* ix, const float* q, int64_t nq, int32_t k,
     }
     const bool tensor = ctx->search_path == VSK_PATH_TENSOR_RERANK && ix->metric != VSK_METRIC_MANHATTAN &&
                         !qmasks;
-    if (tensor) {
+    bool grouped = false;
+    if (mb && ix->has_masks)
+      VSK_TRY(filtered_grouped_search(ix, qb, bn, k, qnorm, mb, out_dist + b * k, out_ids + b * k, &grouped));
+    if (grouped) {
+      // done: every group of equal masks was scanned against its own eligible rows
+    } else if (tensor) {
       VSK_TRY(tensor_search(ix, qb, bn, k, qnorm, out_dist + b * k, out_ids + b * k));
     } else {
       VSK_TRY(fp32_search(ix, qb, bn, nullptr, k, qnorm, mb, out_dist + b * k, out_ids + b * k, 0));

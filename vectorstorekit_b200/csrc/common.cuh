@@ -94,8 +94,8 @@ struct Ctx {
   std::vector<cudaEvent_t> prof_events;  // begin/end pairs
   size_t prof_used = 0;
   // grow-only device scratch, one buffer per slot (see Slot)
-  void* scratch[48] = {};
-  size_t scratch_bytes[48] = {};
+  void* scratch[64] = {};
+  size_t scratch_bytes[64] = {};
 };
 
 enum Slot : int {
@@ -103,10 +103,10 @@ enum Slot : int {
   SLOT_CAND_FLAGS, SLOT_QNORM, SLOT_SUBSET, SLOT_Q16, SLOT_QAUX, SLOT_X_TMP, SLOT_MISC0, SLOT_MISC1,
   SLOT_MISC2, SLOT_MISC3, SLOT_MISC4, SLOT_MISC5, SLOT_MISC6,
   SLOT_IVF_PROBE_D, SLOT_IVF_PROBE_I, SLOT_IVF_KEYS, SLOT_IVF_ORDER, SLOT_IVF_PAIR_OFF, SLOT_IVF_ITEM_CNT,
-  SLOT_IVF_ITEM_OFF, SLOT_IVF_SUBSET, SLOT_IVF_STAGES, SLOT_KM_NSEG, SLOT_KM_SEGOFF, SLOT_KM_PARTIAL, SLOT_SQ_A, SLOT_SQ_B, SLOT_TC_A, SLOT_TC_B, SLOT_TC_C, SLOT_TC_D,
+  SLOT_IVF_ITEM_OFF, SLOT_IVF_SUBSET, SLOT_IVF_STAGES, SLOT_KM_NSEG, SLOT_KM_SEGOFF, SLOT_KM_PARTIAL, SLOT_FILTER_PERM, SLOT_FILTER_ROWS, SLOT_FILTER_COUNT, SLOT_SQ_A, SLOT_SQ_B, SLOT_TC_A, SLOT_TC_B, SLOT_TC_C, SLOT_TC_D,
   SLOT_COUNT
 };
-static_assert(SLOT_COUNT <= 48, "grow Ctx::scratch");
+static_assert(SLOT_COUNT <= 64, "grow Ctx::scratch");
 // Event pair around a scan-kernel launch when profiling is on (api.cu).
 void prof_begin(Ctx* ctx);
 void prof_end(Ctx* ctx);
@@ -176,6 +176,8 @@ struct ExactScanArgs {
   const uint64_t* row_masks;  // or null
   const uint64_t* q_masks;    // or null
   const int32_t* q_subset;  // or null: indices of the queries to run (nq = subset size)
+  const int32_t* x_rows;    // or null: the rows to scan, as a list of row numbers (row_begin/row_end index the list)
+  int32_t bm_hint;          // 0, or 32 / 64: query rows per CTA for launches with few queries
   CandLists cand;           // SCAN_DENSE / SCAN_THRESHOLD
   float* out;               // SCAN_MATRIX: [nq][ld_out]
   int64_t ld_out;

@@ -21,54 +21,69 @@ namespace {
 
 using namespace tile;
 
-template <int METRIC, int MODE, bool B_INT8>
+// BM_ = 128 (the default tile) or 32 / 64 query rows per CTA: the narrow tiles keep the padding small when a
+// launch has few queries (a group of queries that share a filter mask).
+template <int METRIC, int MODE, bool B_INT8, int BM_>
 __global__ void __launch_bounds__(THREADS, 2) exact_scan_kernel(ExactScanArgs a) {
-  __shared__ __align__(16) Smem sm;
+  constexpr int QM = BM_ / 16;
+  __shared__ __align__(16) typename std::conditional<BM_ == 128, Smem, SmemM<(BM_ == 128 ? 64 : BM_)>>::type sm;
   // 1-D grid over (row tile, query tile): no 65535 limit on either extent
   const int64_t tiles_x = (a.row_end - a.row_begin + BN - 1) / BN;
-  const int64_t m0 = ((int64_t)blockIdx.x / tiles_x) * BM;
+  const int64_t m0 = ((int64_t)blockIdx.x / tiles_x) * BM_;
   const int64_t n0 = a.row_begin + ((int64_t)blockIdx.x % tiles_x) * BN;
   const int dim = a.dim;
 
-  F32Row ar[2];
+  auto query_row = [&](int64_t m, bool in_tile) {
+    F32Row r;
+    r.ok = in_tile && m < a.nq;
+    const int64_t qi = r.ok ? (a.q_subset ? (int64_t)a.q_subset[m] : m) : 0;
+    r.base = a.q + qi * dim;
+    r.vec = (dim % 4 == 0) && aligned16(a.q);
+    return r;
+  };
   typename std::conditional<B_INT8, I8Row, F32Row>::type br[2];
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
-    const int64_t m = m0 + stage_row(h);
-    ar[h].ok = m < a.nq;
-    const int64_t qi = ar[h].ok ? (a.q_subset ? (int64_t)a.q_subset[m] : m) : 0;
-    ar[h].base = a.q + qi * dim;
-    ar[h].vec = (dim % 4 == 0) && aligned16(a.q);
     const int64_t n = n0 + stage_row(h);
     br[h].ok = n < a.row_end;
+    // x_rows: the scan walks a list of row numbers instead of a contiguous range
+    const int64_t row = br[h].ok ? (a.x_rows ? (int64_t)a.x_rows[n] : n) : 0;
     if constexpr (B_INT8) {
-      br[h].base = a.x_codes + (br[h].ok ? n : 0) * dim;
+      br[h].base = a.x_codes + row * dim;
       br[h].scale = a.sq_scale;
       br[h].offset = a.sq_offset;
       br[h].vec = (dim % 4 == 0) && aligned4(a.x_codes);
     } else {
-      br[h].base = a.x + (br[h].ok ? n : 0) * dim;
+      br[h].base = a.x + row * dim;
       br[h].vec = (dim % 4 == 0) && aligned16(a.x);
     }
   }
 
-  float acc[8][8];
-  mainloop<METRIC>(acc, ar, br, dim, sm);
+  float acc[QM][8];
+  if constexpr (BM_ == 128) {
+    F32Row ar[2] = {query_row(m0 + stage_row(0), true), query_row(m0 + stage_row(1), true)};
+    mainloop<METRIC>(acc, ar, br, dim, sm);
+  } else {
+    F32Row ar = query_row(m0 + stage_row(0), stage_row(0) < BM_);
+    mainloop_m<METRIC, BM_>(acc, ar, br, dim, sm);
+  }
 
   // ---- epilogue: distance value, filter, candidate append --------------------------------
   int64_t ncol[8];
+  uint32_t rid[8];     // row id stored in a key
   float xn[8];
   uint64_t rmask[8];
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
     ncol[j] = n0 + tile_col(j);
     const bool ok = ncol[j] < a.row_end;
-    xn[j] = (METRIC == VSK_METRIC_COSINE && ok) ? a.xnorm[ncol[j]] : 0.f;
-    rmask[j] = (a.row_masks && ok) ? a.row_masks[ncol[j]] : ~0ull;
+    rid[j] = ok ? (a.x_rows ? (uint32_t)a.x_rows[ncol[j]] : (uint32_t)ncol[j]) : 0u;
+    xn[j] = (METRIC == VSK_METRIC_COSINE && ok) ? a.xnorm[rid[j]] : 0.f;
+    rmask[j] = (a.row_masks && ok) ? a.row_masks[rid[j]] : ~0ull;
   }
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const int64_t m = m0 + tile_row(i);
+  for (int i = 0; i < QM; ++i) {
+    const int64_t m = m0 + (BM_ == 128 ? tile_row(i) : mrow<BM_>(i));
     const bool mok = m < a.nq;
     const int64_t qi = mok ? (a.q_subset ? (int64_t)a.q_subset[m] : m) : 0;
     const float qn = (METRIC == VSK_METRIC_COSINE && mok) ? a.qnorm[qi] : 0.f;
@@ -88,14 +103,14 @@ __global__ void __launch_bounds__(THREADS, 2) exact_scan_kernel(ExactScanArgs a)
         if (ok) a.out[m * a.ld_out + (ncol[j] - a.row_begin)] = v;
       } else if (MODE == SCAN_DENSE) {
         if (ok)
-          a.cand.keys[m * kCandCap + (ncol[j] - a.row_begin)] = elig ? make_key(v, (uint32_t)ncol[j]) : kEmptyKey;
+          a.cand.keys[m * kCandCap + (ncol[j] - a.row_begin)] = elig ? make_key(v, rid[j]) : kEmptyKey;
       } else if (MODE == SCAN_THRESHOLD) {
         if (ok && elig && v <= thr) {
           const int pos = atomicAdd(&a.cand.count[m], 1);
-          if (pos < kCandCap) a.cand.keys[m * kCandCap + pos] = make_key(v, (uint32_t)ncol[j]);
+          if (pos < kCandCap) a.cand.keys[m * kCandCap + pos] = make_key(v, rid[j]);
         }
       } else {  // SCAN_ARGMIN: smallest (value, column) key of the row
-        if (ok) best = min(best, make_key(v, (uint32_t)ncol[j]));
+        if (ok) best = min(best, make_key(v, rid[j]));
       }
     }
     if (MODE == SCAN_ARGMIN) {
@@ -111,20 +126,28 @@ template <int METRIC>
 int32_t launch_metric(Ctx* ctx, const ExactScanArgs& a) {
   const int64_t rows = a.row_end - a.row_begin;
   if (rows <= 0 || a.nq <= 0) return VSK_OK;
-  const int64_t tiles = ceil_div(rows, BN) * ceil_div(a.nq, BM);
+  const bool i8 = a.x_codes != nullptr;
+  // narrow query tiles (fp32 rows, candidate modes only) when they waste clearly fewer padded query rows
+  int bm = 128;
+  if (!i8 && (a.mode == SCAN_DENSE || a.mode == SCAN_THRESHOLD) && a.bm_hint > 0) bm = a.bm_hint;
+  const int64_t tiles = ceil_div(rows, BN) * ceil_div(a.nq, bm);
   if (tiles > 0x7fffffffLL) return fail(ctx, VSK_ERR_INVALID_BUFFER_SIZE, "too many tiles in one launch");
   dim3 grid((unsigned)tiles);
-  const bool i8 = a.x_codes != nullptr;
   prof_begin(ctx);
-#define VSK_LAUNCH(MODE_)                                                                        \
-  if (i8) exact_scan_kernel<METRIC, MODE_, true><<<grid, THREADS, 0, ctx->stream>>>(a);          \
-  else exact_scan_kernel<METRIC, MODE_, false><<<grid, THREADS, 0, ctx->stream>>>(a)
+#define VSK_LAUNCH(MODE_)                                                                             \
+  if (i8) exact_scan_kernel<METRIC, MODE_, true, 128><<<grid, THREADS, 0, ctx->stream>>>(a);          \
+  else exact_scan_kernel<METRIC, MODE_, false, 128><<<grid, THREADS, 0, ctx->stream>>>(a)
+#define VSK_LAUNCH_M(MODE_)                                                                           \
+  if (bm == 32) exact_scan_kernel<METRIC, MODE_, false, 32><<<grid, THREADS, 0, ctx->stream>>>(a);    \
+  else if (bm == 64) exact_scan_kernel<METRIC, MODE_, false, 64><<<grid, THREADS, 0, ctx->stream>>>(a); \
+  else { VSK_LAUNCH(MODE_); }
   switch (a.mode) {
-    case SCAN_DENSE: VSK_LAUNCH(SCAN_DENSE); break;
-    case SCAN_THRESHOLD: VSK_LAUNCH(SCAN_THRESHOLD); break;
+    case SCAN_DENSE: VSK_LAUNCH_M(SCAN_DENSE); break;
+    case SCAN_THRESHOLD: VSK_LAUNCH_M(SCAN_THRESHOLD); break;
     case SCAN_ARGMIN: VSK_LAUNCH(SCAN_ARGMIN); break;
     default: VSK_LAUNCH(SCAN_MATRIX); break;
   }
+#undef VSK_LAUNCH_M
 #undef VSK_LAUNCH
   prof_end(ctx);
   ctx->stats.kernel_launches++;
