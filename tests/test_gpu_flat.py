@@ -9,6 +9,7 @@ import oracle
 from parity import assert_topk_parity
 
 pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 GOLD = np.load(os.path.join(os.path.dirname(__file__), "golden", "metal_shader_vectors.npz"))
 NAMES = ["euclidean", "cosine", "dotProduct", "manhattan"]
 
@@ -300,3 +301,29 @@ def test_cpp_host_mirror_on_gpu(tmp_path):
     from test_abi_cpu import _build_host_mirror
     out = subprocess.run([_build_host_mirror(str(tmp_path))], capture_output=True, text=True)
     assert out.returncode == 0 and out.stdout.strip() == "ok", out
+
+
+def test_cta_pair_kernel_in_subprocess():
+    """The cta_group::2 variant of the tensor scan (opt-in through VSK_TC_PAIR, read once per process)."""
+    import subprocess, sys, textwrap
+    code = textwrap.dedent("""
+        import sys, numpy as np
+        sys.path.insert(0, %r); sys.path.insert(0, %r)
+        import vectorstorekit_b200 as vsk, oracle
+        from parity import assert_topk_parity
+        dev = vsk.CUDAComputeDevice(0)
+        rng = np.random.default_rng(5)
+        for metric, mid in (("cosine", oracle.COSINE), ("euclidean", oracle.EUCLIDEAN)):
+            x = rng.standard_normal((30000, 200)).astype(np.float32)
+            q = rng.standard_normal((300, 200)).astype(np.float32)
+            ix = vsk.FlatIndex(dev, 200, metric); ix.add(x)
+            d, i = ix.batchSearch(q, 25)
+            rd, ri = oracle.CpuOracle().flat_search(mid, q, x, 25)
+            assert_topk_parity(d, i, rd, ri)
+        st = dev.stats()
+        assert st["tensor_tiles"] > 0 and st["fallback_queries"] == 0
+        print("pair-ok")
+    """) % (ROOT, os.path.join(ROOT, "tests"))
+    env = dict(os.environ, VSK_TC_PAIR="1")
+    out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, timeout=300)
+    assert out.returncode == 0 and "pair-ok" in out.stdout, out.stderr[-2000:]

@@ -36,8 +36,12 @@ class ShardedSearch:
             return d, i
         gd = torch.empty((self.world,) + tuple(d.shape), dtype=d.dtype, device=d.device)
         gi = torch.empty((self.world,) + tuple(i.shape), dtype=i.dtype, device=i.device)
-        self._dist.all_gather(list(gd.unbind(0)), d.contiguous(), group=self.group)
-        self._dist.all_gather(list(gi.unbind(0)), i.contiguous(), group=self.group)
+        if d.is_cuda:   # NCCL: one collective straight into the stacked buffer
+            self._dist.all_gather_into_tensor(gd, d.contiguous(), group=self.group)
+            self._dist.all_gather_into_tensor(gi, i.contiguous(), group=self.group)
+        else:           # gloo (CPU tests)
+            self._dist.all_gather(list(gd.unbind(0)), d.contiguous(), group=self.group)
+            self._dist.all_gather(list(gi.unbind(0)), i.contiguous(), group=self.group)
         if d.is_cuda:
             torch.cuda.current_stream().synchronize()
         return self.merge(gd, gi)
