@@ -141,6 +141,26 @@ def test_config2_shape_cosine_reduced(vsk, dev, cpu_oracle, path):
     assert_topk_parity(gd, gi, rd, ri)
 
 
+@pytest.mark.parametrize("path", [1, 0])
+@pytest.mark.parametrize("k", [1000, 2048])
+def test_large_k(vsk, dev, cpu_oracle, path, k):
+    """k near the limits of the candidate lists (k = 2048 is the largest accepted)."""
+    rng = np.random.default_rng(31)
+    x = rng.standard_normal((30_000, 40)).astype(np.float32)
+    q = rng.standard_normal((20, 40)).astype(np.float32)
+    dev.set_search_path(path)
+    ix = _flat(vsk, dev, "euclidean", x)
+    try:
+        gd, gi = ix.batchSearch(q, k)
+        with pytest.raises(vsk.InvalidInput):
+            ix.batchSearch(q, 2049)
+    finally:
+        ix.close()
+        dev.set_search_path(0)
+    rd, ri = cpu_oracle.flat_search(oracle.EUCLIDEAN, q, x, k)
+    assert_topk_parity(gd, gi, rd, ri)
+
+
 def test_filtered_manhattan(vsk, dev, cpu_oracle):
     """Filtered flat search, Manhattan, uniform [-1,1], uint64 row masks with Bernoulli(0.5) bits,
     one-hot query masks (about half the rows pass), k = 50."""
