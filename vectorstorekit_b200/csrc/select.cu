@@ -230,6 +230,62 @@ __global__ void __launch_bounds__(SEL_THREADS) merge_kernel(const float* __restr
   }
 }
 
+// The same merge for at most 1024 gathered keys per query: the keys stay in registers (128 threads x 8), a
+// radix select finds the k-th, and only the k survivors are sorted — instead of sorting all g*k keys.
+__global__ void __launch_bounds__(128) merge_select_kernel(const float* __restrict__ dist, const int64_t* __restrict__ ids,
+                                                           int g, int64_t nq, int k, float* out_dist, int64_t* out_ids) {
+  __shared__ __align__(16) uint64_t s[128 * SEL_ITEMS];
+  __shared__ int hist[256];
+  __shared__ int s_valid, s_bin, s_less, s_in_bin, s_out;
+  const int64_t q = blockIdx.x;
+  const int c = g * k;
+  uint64_t key[SEL_ITEMS];
+  int nvalid = 0;
+#pragma unroll
+  for (int i = 0; i < SEL_ITEMS; ++i) {
+    const int idx = threadIdx.x + i * 128;
+    key[i] = kEmptyKey;
+    if (idx < c) {
+      const int sh = idx / k, j = idx - sh * k;
+      const int64_t src = ((int64_t)sh * nq + q) * k + j;
+      if (ids[src] >= 0) key[i] = make_key(dist[src], (uint32_t)idx);
+    }
+    nvalid += key[i] != kEmptyKey;
+  }
+  if (threadIdx.x == 0) { s_valid = 0; s_out = 0; }
+  __syncthreads();
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) nvalid += __shfl_xor_sync(0xffffffffu, nvalid, o);
+  if ((threadIdx.x & 31) == 0) atomicAdd(&s_valid, nvalid);
+  __syncthreads();
+  const int valid = s_valid;
+  uint64_t pivot = kEmptyKey - 1;
+  if (valid > k) pivot = block_radix_select(key, k, hist, &s_bin, &s_less, &s_in_bin);
+  const int P = next_pow2(min(valid, 128 * SEL_ITEMS));
+  for (int i = threadIdx.x; i < P; i += blockDim.x) s[i] = kEmptyKey;
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < SEL_ITEMS; ++i)
+    if (key[i] <= pivot && key[i] != kEmptyKey) s[atomicAdd(&s_out, 1)] = key[i];
+  __syncthreads();
+  const int kept = s_out;          // k, or more when the k-th value is tied across keys that were all taken
+  const int PS = next_pow2(kept);
+  bitonic_sort(s, PS);
+  for (int j = threadIdx.x; j < k; j += blockDim.x) {
+    float d = CUDART_INF_F;
+    int64_t id = -1;
+    if (j < kept) {
+      const int i = (int)(uint32_t)s[j];
+      const int sh = i / k, jj = i - sh * k;
+      const int64_t src = ((int64_t)sh * nq + q) * k + jj;
+      d = dist[src];
+      id = ids[src];
+    }
+    out_dist[q * k + j] = d;
+    out_ids[q * k + j] = id;
+  }
+}
+
 }  // namespace
 
 int32_t launch_select(Ctx* ctx, const SelectArgs& a) {
@@ -264,9 +320,10 @@ int32_t launch_merge_topk(Ctx* ctx, const float* dist, const int64_t* ids, int32
     return fail(ctx, VSK_ERR_INVALID_BUFFER_SIZE, "merge of %d lists of %d exceeds %d keys", g, k, kCandCap);
   int P = 2;
   while (P < g * k) P <<= 1;
-  // short merges run four times as many CTAs per SM with 128 threads each
-  const int threads = P <= 1024 ? 128 : SEL_THREADS;
-  merge_kernel<<<(unsigned)nq, threads, P * sizeof(uint64_t), ctx->stream>>>(dist, ids, g, nq, k, out_dist, out_ids);
+  if (g * k <= 128 * SEL_ITEMS)
+    merge_select_kernel<<<(unsigned)nq, 128, 0, ctx->stream>>>(dist, ids, g, nq, k, out_dist, out_ids);
+  else
+    merge_kernel<<<(unsigned)nq, SEL_THREADS, P * sizeof(uint64_t), ctx->stream>>>(dist, ids, g, nq, k, out_dist, out_ids);
   ctx->stats.kernel_launches++;
   VSK_CUDA(ctx, cudaGetLastError());
   return VSK_OK;
