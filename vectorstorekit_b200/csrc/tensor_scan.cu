@@ -61,6 +61,7 @@ struct TcSmem {
   uint8_t ring[RING_BYTES];
   float beta[2][EPI_WARPS][EPI_COLS];   // per accumulator buffer and epilogue warp: its columns' per-row terms
   uint32_t masks[EPI_WARPS * 32][EPI_GROUPS + 1];  // per epilogue thread: pass bits of its 128 values (padded row)
+  float hitval[EPI_WARPS * 32][EPI_GROUPS + 1];    // ... and per group the value of its last hit
   uint64_t full[MAX_STAGES];
   uint64_t empty[MAX_STAGES];
   uint64_t tmem_full[2];
@@ -426,10 +427,17 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           const int64_t nc = n0 + c * 32;
           if (!qok) continue;
           uint64_t* dst = a.cand.keys + q * kCandCap + (nc - a.row_begin);
+          // a query's keys are contiguous (16-byte aligned at every even column): two keys per store halve the
+          // number of scattered store transactions, which is what bounds this epilogue
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const float val = HAS_BETA ? fmaf(v[j], alpha, sm->beta[acc][ew][(c - c0) * 32 + j]) : v[j] * alpha;
-            if (nc + j < a.row_end) dst[j] = make_key(val, (uint32_t)(nc + j));
+          for (int j = 0; j < 32; j += 2) {
+            const float v0 = HAS_BETA ? fmaf(v[j], alpha, sm->beta[acc][ew][(c - c0) * 32 + j]) : v[j] * alpha;
+            const float v1 = HAS_BETA ? fmaf(v[j + 1], alpha, sm->beta[acc][ew][(c - c0) * 32 + j + 1]) : v[j + 1] * alpha;
+            if (nc + j + 1 < a.row_end)
+              *reinterpret_cast<ulonglong2*>(dst + j) =
+                  make_ulonglong2(make_key(v0, (uint32_t)(nc + j)), make_key(v1, (uint32_t)(nc + j + 1)));
+            else if (nc + j < a.row_end)
+              dst[j] = make_key(v0, (uint32_t)(nc + j));
           }
         }
       } else if (MODE == SCAN_ARGMIN) {
@@ -462,6 +470,7 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         // The masks live in shared memory so that both loops stay rolled (small code, no dynamic
         // register indexing).
         uint32_t* m = sm->masks[ew * 32 + lane];
+        float* mv = sm->hitval[ew * 32 + lane];
         int cnt = 0;
 #pragma unroll 1
         for (int c = c0; c < c0 + EPI_GROUPS; ++c) {
@@ -470,13 +479,17 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           const int64_t left = a.row_end - (n0 + c * 32);   // columns of this group inside the launch
           const uint32_t colmask = left >= 32 ? 0xffffffffu : (left > 0 ? ((1u << (int)left) - 1u) : 0u);
           uint32_t bits = 0;
+          float hv = 0.f;   // the value of the (last) hit: all that pass 2 needs when a query has one hit in the group
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             const float val = HAS_BETA ? fmaf(v[j], alpha, sm->beta[acc][ew][(c - c0) * 32 + j]) : v[j] * alpha;
-            bits |= (val <= thr) ? (1u << j) : 0u;
+            const bool hit = val <= thr;
+            bits |= hit ? (1u << j) : 0u;
+            hv = hit ? val : hv;
           }
           bits = qok ? (bits & colmask) : 0u;
           m[c - c0] = bits;
+          mv[c - c0] = hv;
           cnt += __popc(bits);
         }
         // Slot reservation.  Interleaved order: one atomic per tile.  Owned order: this warp's half of the
@@ -489,17 +502,45 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 #pragma unroll 1
         for (int c = c0; c < c0 + EPI_GROUPS; ++c) {
           const uint32_t bits = m[c - c0];
-          if (!__any_sync(0xffffffffu, bits != 0u)) continue;
+          const uint32_t colbits = __reduce_or_sync(0xffffffffu, bits);   // columns in which any query has a hit
+          if (colbits == 0u) continue;
+          if (!__any_sync(0xffffffffu, (bits & (bits - 1u)) != 0u) && n0 + c * 32 + 32 <= a.row_end) {
+            // no query has more than one hit in this (whole) group: its value was kept by pass 1
+            const uint32_t ok1 = (bits != 0u && base < cap_here) ? 1u : 0u;
+            const uint64_t key1 = make_key(mv[c - c0], (uint32_t)(n0 + c * 32 + (__ffs((int)bits) - 1)));
+            uint64_t* d1 = a.cand.keys + q * a.cap + (owned ? (ew >> 2) * cap_here : 0) + base;
+            asm volatile(
+                "{\n\t.reg .pred p;\n\t"
+                "setp.ne.u32 p, %2, 0;\n\t"
+                "@p st.global.u64 [%0], %1;\n\t}" ::"l"(d1),
+                "l"(key1), "r"(ok1)
+                : "memory");
+            base += bits != 0u ? 1 : 0;
+            continue;
+          }
           float v[32];
           tc_ld32(trow + (uint32_t)(c * 32), v);
           const int64_t nc = n0 + c * 32;
-          uint64_t* dst = a.cand.keys + q * a.cap + (owned ? (ew >> 2) * cap_here : 0);
+          uint64_t* dst = a.cand.keys + q * a.cap + (owned ? (ew >> 2) * cap_here : 0) + base;
+          // Straight-line code with predicated stores: a branch around every store makes the warp wait out each
+          // store's address chain in turn (measured: four times the cost of this form at 1 hit in 150 values).
+          // Only whole octets of columns without any hit are skipped, on a warp-uniform test.
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            if ((bits >> j) & 1u) {
+          for (int o = 0; o < 4; ++o) {
+            if (((colbits >> (8 * o)) & 0xffu) == 0u) continue;
+#pragma unroll
+            for (int jj = 0; jj < 8; ++jj) {
+              const int j = o * 8 + jj;
               const float val = HAS_BETA ? fmaf(v[j], alpha, sm->beta[acc][ew][(c - c0) * 32 + j]) : v[j] * alpha;
-              const int pos = base + __popc(bits & ((1u << j) - 1u));
-              if (pos < cap_here) dst[pos] = make_key(val, (uint32_t)(nc + j));
+              const int rank = __popc(bits & ((1u << j) - 1u));
+              const uint32_t ok = (((bits >> j) & 1u) != 0u && base + rank < cap_here) ? 1u : 0u;
+              const uint64_t key = make_key(val, (uint32_t)(nc + j));
+              asm volatile(
+                  "{\n\t.reg .pred p;\n\t"
+                  "setp.ne.u32 p, %2, 0;\n\t"
+                  "@p st.global.u64 [%0], %1;\n\t}" ::"l"(dst + rank),
+                  "l"(key), "r"(ok)
+                  : "memory");
             }
           }
           base += __popc(bits);
