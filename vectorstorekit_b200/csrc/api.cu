@@ -172,12 +172,19 @@ static int32_t flagged_queries(Ctx* ctx, const CandLists& cand, int64_t nq, std:
 
 // fp32 scan of `nq` queries (optionally the subset `sub_dev` of a larger batch) over n rows
 // described by `proto` (metric, operands, norms, masks), with final output.
+static int pick_query_tile(int64_t g);
+
 int32_t fp32_topk(Ctx* ctx, const ExactScanArgs& proto, int64_t n, int64_t nq, const int32_t* sub_dev, int32_t k,
                   int64_t id_base, float* out_dist, int64_t* out_ids, int level) {
   CandLists cand;
   VSK_TRY(cand_workspace(ctx, nq, &cand));
   ExactScanArgs a = proto;
   a.nq = nq;
+  // a small batch (a few queries, or the handful of queries a fallback re-runs): narrow query tiles
+  if (a.bm_hint == 0 && nq < 128) {
+    const int bm = pick_query_tile(nq);
+    if (bm < 128) a.bm_hint = bm;
+  }
   a.q_subset = sub_dev;
   a.cand = cand;
   ScanFn scan = [&](int mode, int64_t b, int64_t e) {
