@@ -48,7 +48,9 @@ typedef enum vsk_status {
   VSK_ERR_DIMENSION_MISMATCH = 8,        /* dimensionMismatch */
   VSK_ERR_EMPTY_INPUT = 9,               /* emptyInput (MetalDistanceCompute.swift:51-53) */
   VSK_ERR_NOT_TRAINED = 10,              /* IVFError.notTrained */
-  VSK_ERR_INSUFFICIENT_TRAINING_DATA = 11/* IVFError.insufficientTrainingData */
+  VSK_ERR_INSUFFICIENT_TRAINING_DATA = 11,/* IVFError.insufficientTrainingData */
+  VSK_ERR_IMPORT_FAILED = 12,            /* ImportError.decodingFailed (Indexes/IVFIndex.swift:640-643), VectorStoreError.importError */
+  VSK_ERR_EXPORT_FAILED = 13             /* VectorStoreError.exportError (Core/Errors.swift:661-680) */
 } vsk_status;
 
 /* The four cases of DistanceMetric the accelerated path supports
@@ -105,6 +107,19 @@ typedef struct vsk_stats {
   double scan_kernel_ms;        /* ... and their summed device time (CUDA events on the stream) */
 } vsk_stats;
 
+/* What a handle holds (vsk_index_info_get); a loaded index image is described the same way. */
+typedef enum vsk_index_kind { VSK_INDEX_FLAT_F32 = 0, VSK_INDEX_FLAT_I8 = 1, VSK_INDEX_IVF = 2 } vsk_index_kind;
+typedef struct vsk_index_info {
+  int32_t kind;        /* vsk_index_kind */
+  int32_t metric;      /* vsk_metric */
+  int32_t dimensions;
+  int32_t nlist;       /* IVF lists, else 0 */
+  int64_t count;       /* rows */
+  int64_t id_base;
+  int32_t has_masks;   /* rows carry 64-bit filter masks */
+  int32_t reserved;
+} vsk_index_info;
+
 /* --- context ------------------------------------------------------------------------------
  * Replaces ComputeAccelerator.initialize()/capabilities() (Core/Protocols.swift:11-20) and the
  * process-wide MetalAccelerationEngine.shared (MetalAccelerationEngine.swift:25-30). */
@@ -148,6 +163,23 @@ int32_t vsk_index_destroy(vsk_index* index);
 int64_t vsk_index_size(vsk_index* index);
 /* Added to every returned id (row-sharded databases: the shard's first global row). */
 int32_t vsk_index_set_id_base(vsk_index* index, int64_t id_base);
+
+int32_t vsk_index_info_get(vsk_index* index, vsk_index_info* out);
+
+/* --- index image (export / import) -----------------------------------------------------------
+ * Replaces VectorIndex.export(format: .binary) -> Data / import(data:format:) (Core/Protocols.swift:157-160;
+ * Indexes/IVFIndex.swift:297-326) and the store envelope of VectorStore.combineExport
+ * (API/VectorStore.swift:707-727): "VSTR", version bytes 1,0,0,0, u64 metadata length, JSON metadata, index data.
+ * Unlike the reference's IVF export (centroids only, IVFIndex.swift:612-616) the image carries the rows, the
+ * inverted lists, masks and quantiser parameters, so a loaded index answers searches identically.  Each data
+ * section carries a 64-bit checksum computed on the GPU; a mismatch on load gives VSK_ERR_IMPORT_FAILED.
+ * vsk_index_image_size gives the exact byte count vsk_index_export writes.  save/load stream through two
+ * 32 MiB pinned buffers and never hold the whole image in host memory. */
+int32_t vsk_index_image_size(vsk_index* index, int64_t* bytes);
+int32_t vsk_index_export(vsk_index* index, void* dst, int64_t capacity, int64_t* written);
+int32_t vsk_index_import(vsk_ctx* ctx, const void* src, int64_t bytes, vsk_index** out_index);
+int32_t vsk_index_save(vsk_index* index, const char* path);
+int32_t vsk_index_load(vsk_ctx* ctx, const char* path, vsk_index** out_index);
 
 /* out_dist[nq*k], out_ids[nq*k].  qmasks may be NULL. */
 int32_t vsk_search(vsk_index* index, const float* queries, int64_t nq, int32_t k,
@@ -202,6 +234,8 @@ int32_t vsk_ivf_build_dev(vsk_ctx* ctx, const float* centroids, int32_t nlist, c
                           int64_t n, int32_t dim, vsk_index** out_index);
 /* Row -> list of the built index (host buffer of n int32). */
 int32_t vsk_ivf_assignments(vsk_index* index, int32_t* assign);
+/* The index's centroids, [nlist][dim] floats to host memory (what IVFIndex.export keeps, IVFIndex.swift:297-302). */
+int32_t vsk_ivf_centroids(vsk_index* index, float* centroids);
 /* Probe the nprobe nearest lists, rooted L2, ascending top-k.  Replaces IVFIndex.search
  * (Indexes/IVFIndex.swift:124-202); nprobe == nlist is its `.exact` strategy (:551-560). */
 int32_t vsk_ivf_search(vsk_index* index, const float* queries, int64_t nq, int32_t k,

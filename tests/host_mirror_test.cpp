@@ -3,6 +3,7 @@
 // against values worked out by hand.
 #include <cmath>
 #include <cstdio>
+#include <cstring>
 
 #include "../vectorstorekit_b200/host/vsk.hpp"
 
@@ -31,6 +32,18 @@ int main() {
   ix.add(rows, 3);
   auto r = ix.batchSearch(q, 1, 2);
   if (r.ids[0] != 0 || r.ids[1] != 2) return 5;
+  // export -> import: the rebuilt index answers the same
+  auto image = ix.exportBinary();
+  if (image.size() < 16 || std::memcmp(image.data(), "VSTR", 4) != 0) return 6;
+  vsk::FlatIndex back(dev, image.data(), (int64_t)image.size());
+  auto r2 = back.batchSearch(q, 1, 2);
+  if (back.count() != 3 || r2.ids != r.ids || r2.distances != r.distances) return 7;
+  image[image.size() - 60] ^= 1;   // inside the rows section (48 bytes of rows + 16 of padding end the image)
+  try {
+    vsk::FlatIndex broken(dev, image.data(), (int64_t)image.size());
+    return 8;
+  } catch (const vsk::ImportFailed&) {
+  }
   std::puts("ok");
   return 0;
 }

@@ -8,6 +8,7 @@ from .engine import (CUDAAccelerationEngine, CUDAAcceleratorStrategy, CUDAComput
                      DeviceOutOfMemory, DimensionMismatch, DistanceMetric, EmptyInput, ExecutionFailed, FlatIndex,
                      InsufficientTrainingData, InvalidBufferSize, IVFIndex, KMeansClustering, QuantizedFlatIndex,
                      ScalarQuantizer, InvalidInput, NotTrained, SearchStrategy, Timeout,
-                     UnsupportedOperation, VSKError, PATH_FP32_SCAN, PATH_TENSOR_RERANK)
+                     UnsupportedOperation, VSKError, PATH_FP32_SCAN, PATH_TENSOR_RERANK, ImportFailed,
+                     ExportFailed, import_index, load_index)
 
 __all__ = [n for n in dir() if not n.startswith("_")]

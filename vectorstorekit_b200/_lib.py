@@ -33,6 +33,11 @@ class Stats(C.Structure):
                 ("scan_kernel_ms", C.c_double)]
 
 
+class IndexInfo(C.Structure):
+    _fields_ = [("kind", C.c_int32), ("metric", C.c_int32), ("dimensions", C.c_int32), ("nlist", C.c_int32),
+                ("count", C.c_int64), ("id_base", C.c_int64), ("has_masks", C.c_int32), ("reserved", C.c_int32)]
+
+
 # name -> (restype, argtypes).  Pointers that may be host or device memory are void*.
 SIGNATURES = {
     "vsk_open": (C.c_int32, [C.c_int32, C.POINTER(vp)]),
@@ -52,6 +57,13 @@ SIGNATURES = {
     "vsk_index_destroy": (C.c_int32, [vp]),
     "vsk_index_size": (C.c_int64, [vp]),
     "vsk_index_set_id_base": (C.c_int32, [vp, C.c_int64]),
+    "vsk_index_info_get": (C.c_int32, [vp, C.POINTER(IndexInfo)]),
+    "vsk_ivf_centroids": (C.c_int32, [vp, vp]),
+    "vsk_index_image_size": (C.c_int32, [vp, C.POINTER(C.c_int64)]),
+    "vsk_index_export": (C.c_int32, [vp, vp, C.c_int64, C.POINTER(C.c_int64)]),
+    "vsk_index_import": (C.c_int32, [vp, vp, C.c_int64, C.POINTER(vp)]),
+    "vsk_index_save": (C.c_int32, [vp, C.c_char_p]),
+    "vsk_index_load": (C.c_int32, [vp, C.c_char_p, C.POINTER(vp)]),
     "vsk_search": (C.c_int32, [vp, vp, C.c_int64, C.c_int32, vp, vp, vp]),
     "vsk_search_dev": (C.c_int32, [vp, vp, C.c_int64, C.c_int32, vp, vp, vp]),
     "vsk_merge_topk_dev": (C.c_int32, [vp, vp, vp, C.c_int32, C.c_int64, C.c_int32, vp, vp]),

@@ -406,7 +406,7 @@ int32_t fp32_search_subset(Index* ix, const float* q, const std::vector<int32_t>
   return fp32_search(ix, q, (int64_t)subset.size(), (const int32_t*)p, k, qnorm, nullptr, out_dist, out_ids, 0);
 }
 
-static int32_t flat_reserve(Index* ix, int64_t need) {
+int32_t flat_reserve(Index* ix, int64_t need) {
   Ctx* ctx = ix->ctx;
   if (need <= ix->capacity) return VSK_OK;
   int64_t cap = std::max<int64_t>(need, ix->capacity + ix->capacity / 2);
@@ -430,6 +430,20 @@ static int32_t flat_reserve(Index* ix, int64_t need) {
   ix->row_norm = norm;
   ix->masks = masks;
   ix->capacity = cap;
+  return VSK_OK;
+}
+
+// Rows (and masks) were written straight into the reserved storage (an index image being loaded): compute what
+// an add computes and count them in.
+int32_t flat_adopt_rows(Index* ix, int64_t n, bool has_masks) {
+  Ctx* ctx = ix->ctx;
+  if (n > ix->capacity) return fail(ctx, VSK_ERR_INVALID_BUFFER_SIZE, "more rows than reserved");
+  ix->has_masks = has_masks;
+  if (ix->metric == VSK_METRIC_COSINE || ix->metric == VSK_METRIC_EUCLIDEAN)
+    VSK_TRY(launch_row_norms(ctx, ix->rows, n, ix->dim, ix->metric == VSK_METRIC_EUCLIDEAN, ix->row_norm));
+  ix->n = n;
+  tensor_invalidate(ix);
+  VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   return VSK_OK;
 }
 
@@ -477,6 +491,8 @@ const char* vsk_status_string(int32_t s) {
     case VSK_ERR_EMPTY_INPUT: return "empty input";
     case VSK_ERR_NOT_TRAINED: return "index not trained";
     case VSK_ERR_INSUFFICIENT_TRAINING_DATA: return "insufficient training data";
+    case VSK_ERR_IMPORT_FAILED: return "index image could not be imported";
+    case VSK_ERR_EXPORT_FAILED: return "index image could not be exported";
     default: return "unknown status";
   }
 }

@@ -477,6 +477,16 @@ int32_t vsk_ivf_assignments(vsk_index* i, int32_t* assign) {
   return VSK_OK;
 }
 
+int32_t vsk_ivf_centroids(vsk_index* i, float* centroids) {
+  Index* ix = reinterpret_cast<Index*>(i);
+  if (!ix || !centroids) return VSK_ERR_INVALID_INPUT;
+  Ctx* ctx = ix->ctx;
+  cudaSetDevice(ctx->device);
+  if (ix->kind != INDEX_IVF) return fail(ctx, VSK_ERR_INVALID_INPUT, "not an IVF index");
+  VSK_CUDA(ctx, cudaMemcpy(centroids, ix->centroids, (size_t)ix->nlist * ix->dim * 4, cudaMemcpyDeviceToHost));
+  return VSK_OK;
+}
+
 int32_t vsk_ivf_search_dev(vsk_index* i, const float* q, int64_t nq, int32_t k, int32_t nprobe, float* out_dist,
                            int64_t* out_ids) {
   Index* ix = reinterpret_cast<Index*>(i);

@@ -140,6 +140,8 @@ int32_t check_ctx(vsk_ctx* c, Ctx** ctx) {
   return VSK_OK;
 }
 
+}  // namespace
+
 int32_t sq8_reserve(Index* ix, int64_t need) {
   Ctx* ctx = ix->ctx;
   if (need <= ix->capacity) return VSK_OK;
@@ -160,6 +162,24 @@ int32_t sq8_reserve(Index* ix, int64_t need) {
   ix->capacity = cap;
   return VSK_OK;
 }
+
+// Codes were written straight into the reserved storage (an index image being loaded): compute what an add
+// computes and count them in.
+int32_t sq8_adopt_rows(Index* ix, int64_t n) {
+  Ctx* ctx = ix->ctx;
+  if (n > ix->capacity) return fail(ctx, VSK_ERR_INVALID_BUFFER_SIZE, "more rows than reserved");
+  if (ix->metric == VSK_METRIC_COSINE) {
+    sq8_row_norm_kernel<<<(unsigned)ceil_div(n, 8), 256, 0, ctx->stream>>>(ix->codes, n, ix->dim, ix->sq_scale,
+                                                                           ix->sq_offset, ix->row_norm);
+    ctx->stats.kernel_launches++;
+  }
+  ix->n = n;
+  tensor_invalidate(ix);
+  VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return VSK_OK;
+}
+
+namespace {
 
 int32_t sq8_add(Index* ix, const int8_t* codes, int64_t n, bool on_device) {
   Ctx* ctx = ix->ctx;

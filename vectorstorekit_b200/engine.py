@@ -52,6 +52,7 @@ class DistanceMetric(enum.Enum):
 
 _METRIC_ID = {DistanceMetric.euclidean: 0, DistanceMetric.cosine: 1, DistanceMetric.dotProduct: 2,
               DistanceMetric.manhattan: 3}
+_METRIC_OF_ID = {v: k for k, v in _METRIC_ID.items()}
 
 
 class SearchStrategy(enum.Enum):
@@ -110,9 +111,20 @@ class InsufficientTrainingData(VSKError):
     status = 11
 
 
+class ImportFailed(VSKError):
+    """``ImportError.decodingFailed`` (``Indexes/IVFIndex.swift:640-643``): not an index image, truncated, or a
+    section's checksum does not match."""
+    status = 12
+
+
+class ExportFailed(VSKError):
+    """``VectorStoreError.exportError`` (``Core/Errors.swift:661-680``)."""
+    status = 13
+
+
 _ERRORS = {c.status: c for c in (DeviceNotAvailable, DeviceOutOfMemory, UnsupportedOperation, InvalidBufferSize,
                                  ExecutionFailed, Timeout, InvalidInput, DimensionMismatch, EmptyInput, NotTrained,
-                                 InsufficientTrainingData)}
+                                 InsufficientTrainingData, ImportFailed, ExportFailed)}
 
 
 def _metric_id(metric) -> int:
@@ -298,6 +310,28 @@ class _IndexBase:
     def set_id_base(self, base: int):
         self.dev.check(self._lib.vsk_index_set_id_base(self._h, base))
 
+    def info(self) -> dict:
+        d = _lib.IndexInfo()
+        self.dev.check(self._lib.vsk_index_info_get(self._h, C.byref(d)))
+        return {"kind": ("flat_f32", "flat_i8", "ivf")[d.kind], "metric": _METRIC_OF_ID[d.metric],
+                "dimensions": d.dimensions, "count": d.count, "id_base": d.id_base, "nlist": d.nlist,
+                "has_masks": bool(d.has_masks)}
+
+    # ``VectorIndex.export(format:) -> Data`` / ``import(data:format:)`` (``Core/Protocols.swift:157-160``); only the
+    # binary format exists here, any other raises as ``IVFIndex.export`` does (``Indexes/IVFIndex.swift:304-311``).
+    def export(self, format: str = "binary") -> bytes:
+        if format != "binary":
+            raise ExportFailed(f"unsupported export format {format}")
+        size = C.c_int64()
+        self.dev.check(self._lib.vsk_index_image_size(self._h, C.byref(size)))
+        buf = np.empty(size.value, np.uint8)
+        written = C.c_int64()
+        self.dev.check(self._lib.vsk_index_export(self._h, _ptr(buf), size.value, C.byref(written)))
+        return buf[: written.value].tobytes()
+
+    def save(self, path: str):
+        self.dev.check(self._lib.vsk_index_save(self._h, str(path).encode()))
+
     def _search(self, queries, k, qmasks=None):
         nq = queries.shape[0]
         if _is_dev(queries):
@@ -313,6 +347,44 @@ class _IndexBase:
         qm = _host(qmasks, np.uint64) if qmasks is not None else None
         self.dev.check(self._lib.vsk_search(self._h, _ptr(q), nq, k, _ptr(qm), _ptr(od), _ptr(oi)))
         return od, oi
+
+
+def _adopt(dev: "CUDAComputeDevice", h):
+    """Wrap a handle that came out of an index image in the class of its kind."""
+    probe = _IndexBase(dev)
+    probe._h = h
+    info = probe.info()
+    cls = {"flat_f32": FlatIndex, "flat_i8": QuantizedFlatIndex, "ivf": IVFIndex}[info["kind"]]
+    ix = cls.__new__(cls)
+    _IndexBase.__init__(ix, dev)
+    ix._h, probe._h = h, None
+    ix.dimensions = info["dimensions"]
+    if cls is IVFIndex:
+        ix.numberOfCentroids = info["nlist"]
+        ix.numberOfProbes = min(10, info["nlist"])      # IVFConfiguration default (IVFConfiguration.swift:32)
+        ix.clustering = KMeansClustering(dev)
+        cent = np.empty((info["nlist"], info["dimensions"]), np.float32)
+        dev.check(dev._lib.vsk_ivf_centroids(h, _ptr(cent)))
+        ix.centroids = cent
+        ix.trained = True
+    return ix
+
+
+def import_index(dev: "CUDAComputeDevice", data, format: str = "binary"):
+    """``import(data:format:)``: rebuild an index from the bytes ``export`` produced."""
+    if format != "binary":
+        raise ImportFailed(f"unsupported import format {format}")
+    buf = np.frombuffer(data, np.uint8)
+    h = C.c_void_p()
+    dev.check(dev._lib.vsk_index_import(dev._h, _ptr(buf), buf.size, C.byref(h)))
+    return _adopt(dev, h)
+
+
+def load_index(dev: "CUDAComputeDevice", path: str):
+    """Rebuild an index from the file ``save`` wrote."""
+    h = C.c_void_p()
+    dev.check(dev._lib.vsk_index_load(dev._h, str(path).encode(), C.byref(h)))
+    return _adopt(dev, h)
 
 
 class FlatIndex(_IndexBase):

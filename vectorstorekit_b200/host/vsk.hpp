@@ -37,6 +37,8 @@ struct EmptyInput : Error { using Error::Error; };
 struct Timeout : Error { using Error::Error; };
 struct NotTrained : Error { using Error::Error; };
 struct InsufficientTrainingData : Error { using Error::Error; };
+struct ImportFailed : Error { using Error::Error; };   // ImportError.decodingFailed (IVFIndex.swift:640-643)
+struct ExportFailed : Error { using Error::Error; };   // VectorStoreError.exportError (Errors.swift:661-680)
 
 inline void check(int32_t st, vsk_ctx* ctx) {
   if (st == VSK_OK) return;
@@ -52,6 +54,8 @@ inline void check(int32_t st, vsk_ctx* ctx) {
     case VSK_ERR_NOT_TRAINED: throw NotTrained(st, msg);
     case VSK_ERR_INSUFFICIENT_TRAINING_DATA: throw InsufficientTrainingData(st, msg);
     case VSK_ERR_INVALID_INPUT: case VSK_ERR_INVALID_BUFFER_SIZE: throw InvalidInput(st, msg);
+    case VSK_ERR_IMPORT_FAILED: throw ImportFailed(st, msg);
+    case VSK_ERR_EXPORT_FAILED: throw ExportFailed(st, msg);
     default: throw Error(st, msg);
   }
 }
@@ -91,12 +95,33 @@ struct SearchResults {            // one ascending row of k hits per query
   std::vector<int64_t> ids;       // [nq*k], -1 where fewer than k rows were eligible
 };
 
+// VectorIndex.export(format: .binary) -> Data (Core/Protocols.swift:157): the index image as bytes.
+inline std::vector<uint8_t> exportIndex(vsk_index* ix, vsk_ctx* ctx) {
+  int64_t bytes = 0, written = 0;
+  check(vsk_index_image_size(ix, &bytes), ctx);
+  std::vector<uint8_t> out((size_t)bytes);
+  check(vsk_index_export(ix, out.data(), bytes, &written), ctx);
+  out.resize((size_t)written);
+  return out;
+}
+
 class FlatIndex {
  public:
   FlatIndex(std::shared_ptr<CUDAComputeDevice> dev, int32_t dimensions, DistanceMetric metric)
       : dev_(std::move(dev)), dim_(dimensions) {
     check(vsk_flat_create(dev_->ctx(), metric_id(metric), dimensions, &ix_), dev_->ctx());
   }
+  // import(data:format: .binary) / a file written by save(): the image must hold a flat fp32 index
+  FlatIndex(std::shared_ptr<CUDAComputeDevice> dev, const void* image, int64_t bytes) : dev_(std::move(dev)) {
+    check(vsk_index_import(dev_->ctx(), image, bytes, &ix_), dev_->ctx());
+    adopt();
+  }
+  FlatIndex(std::shared_ptr<CUDAComputeDevice> dev, const std::string& path) : dev_(std::move(dev)) {
+    check(vsk_index_load(dev_->ctx(), path.c_str(), &ix_), dev_->ctx());
+    adopt();
+  }
+  std::vector<uint8_t> exportBinary() const { return exportIndex(ix_, dev_->ctx()); }
+  void save(const std::string& path) const { check(vsk_index_save(ix_, path.c_str()), dev_->ctx()); }
   ~FlatIndex() { if (ix_) vsk_index_destroy(ix_); }
   FlatIndex(const FlatIndex&) = delete;
   FlatIndex& operator=(const FlatIndex&) = delete;
@@ -110,9 +135,19 @@ class FlatIndex {
     return r;
   }
  private:
+  void adopt() {
+    vsk_index_info info{};
+    vsk_index_info_get(ix_, &info);
+    if (info.kind != VSK_INDEX_FLAT_F32) {
+      vsk_index_destroy(ix_);
+      ix_ = nullptr;
+      throw ImportFailed(VSK_ERR_IMPORT_FAILED, "the image does not hold a flat fp32 index");
+    }
+    dim_ = info.dimensions;
+  }
   std::shared_ptr<CUDAComputeDevice> dev_;
   vsk_index* ix_ = nullptr;
-  int32_t dim_;
+  int32_t dim_ = 0;
 };
 
 // MetalAccelerationEngine's distance surface.
