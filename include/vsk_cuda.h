@@ -108,7 +108,7 @@ typedef struct vsk_stats {
 } vsk_stats;
 
 /* What a handle holds (vsk_index_info_get); a loaded index image is described the same way. */
-typedef enum vsk_index_kind { VSK_INDEX_FLAT_F32 = 0, VSK_INDEX_FLAT_I8 = 1, VSK_INDEX_IVF = 2 } vsk_index_kind;
+typedef enum vsk_index_kind { VSK_INDEX_FLAT_F32 = 0, VSK_INDEX_FLAT_I8 = 1, VSK_INDEX_IVF = 2, VSK_INDEX_PQ = 3 } vsk_index_kind;
 typedef struct vsk_index_info {
   int32_t kind;        /* vsk_index_kind */
   int32_t metric;      /* vsk_metric */
@@ -117,6 +117,8 @@ typedef struct vsk_index_info {
   int64_t count;       /* rows */
   int64_t id_base;
   int32_t has_masks;   /* rows carry 64-bit filter masks */
+  int32_t pq_segments;       /* product-quantised index: segments, else 0 */
+  int32_t pq_codebook_size;  /* ... codewords per segment */
   int32_t reserved;
 } vsk_index_info;
 
@@ -271,6 +273,47 @@ int32_t vsk_sq8_index_create(vsk_ctx* ctx, int32_t metric, int32_t dim, const fl
                              const float* offset, vsk_index** out_index);
 int32_t vsk_sq8_index_add(vsk_index* index, const int8_t* codes, int64_t n);
 int32_t vsk_sq8_index_add_dev(vsk_index* index, const int8_t* codes, int64_t n);
+
+/* --- product quantisation ---------------------------------------------------------------------
+ * Replaces ProductQuantizer (Quantization/ProductQuantizer.swift) and the shaders productQuantize /
+ * productDequantize (Acceleration/Metal/Shaders/QuantizationShaders.metal:113-204).
+ *   codebooks   [segments][codebook_size][dim / segments] floats (Codebook.centroids,
+ *               ProductQuantizerCodebook.swift:8-11); dim % segments == 0, 2 <= codebook_size <= 256
+ *               (ProductQuantizationConfig.validate, Config/Quantization/ProductQuantizationConfig.swift:42-49;
+ *               a code is one byte, QuantizedVector.codes: [UInt8])
+ *   train       one k-means per segment (trainSegmentCodebook :266-312), `iterations` Lloyd steps from
+ *               init_codebooks (same layout; NULL = the segments of the first codebook_size rows).  The reference
+ *               seeds k-means++ / mini-batch k-means from Swift's random number generator, which cannot be
+ *               reproduced; callers that need the reference's codebooks pass them to the calls below.
+ *               Needs n >= codebook_size * segments rows (:34-41), else VSK_ERR_INSUFFICIENT_TRAINING_DATA.
+ *   encode      codes[n][segments]: per segment the nearest codeword by squared L2 accumulated in dimension
+ *               order, lowest code on ties (Codebook.encode :12-30)
+ *   decode      rows[n][dim]: the coded codewords side by side (:152-163); the per-vector norm rescale of
+ *               :165-180 uses a norm the Swift object stores beside the codes and is the caller's to apply
+ *   tables      tables[nq][segments][codebook_size]: squared L2 between each query segment and each codeword
+ *               (precomputeDistanceTables :205-233)
+ *   index       codes resident on the GPU; vsk_search / vsk_search_dev return per query the k rows with the
+ *               smallest asymmetric distance sqrt(sum over segments of table[segment][code])
+ *               (DistanceTables.computeDistance, ProductQuantizerTypes.swift:14-20; computeAsymmetricDistance
+ *               :341-356), ascending, ties by row.  The reference computes that distance one vector at a time and
+ *               has no scan over stored codes.  qmasks must be NULL. */
+int32_t vsk_pq_train(vsk_ctx* ctx, const float* rows, int64_t n, int32_t dim, int32_t segments,
+                     int32_t codebook_size, int32_t iterations, const float* init_codebooks, float* codebooks);
+int32_t vsk_pq_train_dev(vsk_ctx* ctx, const float* rows, int64_t n, int32_t dim, int32_t segments,
+                         int32_t codebook_size, int32_t iterations, const float* init_codebooks, float* codebooks);
+int32_t vsk_pq_encode(vsk_ctx* ctx, const float* codebooks, int32_t dim, int32_t segments, int32_t codebook_size,
+                      const float* rows, int64_t n, uint8_t* codes);
+int32_t vsk_pq_encode_dev(vsk_ctx* ctx, const float* codebooks, int32_t dim, int32_t segments, int32_t codebook_size,
+                          const float* rows, int64_t n, uint8_t* codes);
+int32_t vsk_pq_decode(vsk_ctx* ctx, const float* codebooks, int32_t dim, int32_t segments, int32_t codebook_size,
+                      const uint8_t* codes, int64_t n, float* rows);
+int32_t vsk_pq_distance_tables(vsk_ctx* ctx, const float* codebooks, int32_t dim, int32_t segments,
+                               int32_t codebook_size, const float* queries, int64_t nq, float* tables);
+/* codebooks: host or device memory, copied. */
+int32_t vsk_pq_index_create(vsk_ctx* ctx, int32_t dim, int32_t segments, int32_t codebook_size,
+                            const float* codebooks, vsk_index** out_index);
+int32_t vsk_pq_index_add(vsk_index* index, const uint8_t* codes, int64_t n);
+int32_t vsk_pq_index_add_dev(vsk_index* index, const uint8_t* codes, int64_t n);
 
 #ifdef __cplusplus
 }

@@ -170,6 +170,50 @@ class CpuOracle:
                                    _ptr(dist, _f32p), _ptr(ids, _i64p))
         return dist, ids
 
+    # ---- product quantisation (codebooks: [m][ksub][d/m]) ----
+    def pq_encode(self, x, codebooks):
+        x, cb = _f32(x), _f32(codebooks)
+        m, ksub, _ = cb.shape
+        codes = np.empty((x.shape[0], m), np.uint8)
+        self.lib.vskref_pq_encode(_ptr(x, _f32p), C.c_int64(x.shape[0]), x.shape[1], m, ksub, _ptr(cb, _f32p),
+                                  _ptr(codes, _u8p))
+        return codes
+
+    def pq_decode(self, codes, codebooks):
+        cb = _f32(codebooks)
+        codes = np.ascontiguousarray(codes, np.uint8)
+        m, ksub, ds = cb.shape
+        x = np.empty((codes.shape[0], m * ds), np.float32)
+        self.lib.vskref_pq_decode(_ptr(codes, _u8p), C.c_int64(codes.shape[0]), m * ds, m, ksub, _ptr(cb, _f32p),
+                                  _ptr(x, _f32p))
+        return x
+
+    def pq_tables(self, q, codebooks):
+        q, cb = _f32(q), _f32(codebooks)
+        m, ksub, _ = cb.shape
+        t = np.empty((q.shape[0], m, ksub), np.float32)
+        self.lib.vskref_pq_tables(_ptr(q, _f32p), C.c_int64(q.shape[0]), q.shape[1], m, ksub, _ptr(cb, _f32p),
+                                  _ptr(t, _f32p))
+        return t
+
+    def pq_search(self, q, codes, codebooks, k):
+        q, cb = _f32(q), _f32(codebooks)
+        codes = np.ascontiguousarray(codes, np.uint8)
+        m, ksub, _ = cb.shape
+        dist = np.empty((q.shape[0], k), np.float32)
+        ids = np.empty((q.shape[0], k), np.int64)
+        self.lib.vskref_pq_search(_ptr(q, _f32p), C.c_int64(q.shape[0]), _ptr(codes, _u8p), C.c_int64(codes.shape[0]),
+                                  q.shape[1], m, ksub, _ptr(cb, _f32p), k, _ptr(dist, _f32p), _ptr(ids, _i64p))
+        return dist, ids
+
+    def pq_train(self, x, init_codebooks, iters):
+        x, init = _f32(x), _f32(init_codebooks)
+        m, ksub, _ = init.shape
+        out = np.empty_like(init)
+        self.lib.vskref_pq_train(_ptr(x, _f32p), C.c_int64(x.shape[0]), x.shape[1], m, ksub, iters, _ptr(init, _f32p),
+                                 _ptr(out, _f32p))
+        return out
+
     def merge_topk(self, dist, ids):
         """dist/ids: [G, Q, k] per-shard lists with global ids -> merged [Q, k]."""
         dist = _f32(dist)
@@ -199,6 +243,29 @@ class MetalRef:
         L.metalref_min_distances.argtypes = [_f32p, C.c_uint, C.c_uint, _f32p, C.c_uint, _f32p]
         L.metalref_scalar_quantize.argtypes = [_f32p, _u8p, C.c_float, C.c_float, C.c_uint]
         L.metalref_scalar_dequantize.argtypes = [_u8p, _f32p, C.c_float, C.c_float, C.c_uint]
+        if hasattr(L, "metalref_product_quantize"):
+            L.metalref_product_quantize.argtypes = [_f32p, _f32p, _u8p, C.c_uint, C.c_uint, C.c_uint, C.c_uint, C.c_uint]
+            L.metalref_product_dequantize.argtypes = [_u8p, _f32p, _f32p, C.c_uint, C.c_uint, C.c_uint, C.c_uint]
+
+    def product_quantize(self, x, codebooks):
+        """Shader productQuantize (QuantizationShaders.metal:113-156); codebooks [m][ksub][d/m]."""
+        x, cb = _f32(x), _f32(codebooks)
+        m, ksub, ds = cb.shape
+        codes = np.empty((x.shape[0], m), np.uint8)
+        self.lib.metalref_product_quantize(_ptr(x, _f32p), _ptr(cb, _f32p), _ptr(codes, _u8p), x.shape[0], x.shape[1],
+                                           m, ds, ksub)
+        return codes
+
+    def product_dequantize(self, codes, codebooks):
+        """Shader productDequantize (:177-204); assumes 256 codes per subspace."""
+        cb = _f32(codebooks)
+        codes = np.ascontiguousarray(codes, np.uint8)
+        m, ksub, ds = cb.shape
+        assert ksub == 256
+        x = np.empty((codes.shape[0], m * ds), np.float32)
+        self.lib.metalref_product_dequantize(_ptr(codes, _u8p), _ptr(cb, _f32p), _ptr(x, _f32p), codes.shape[0],
+                                             m * ds, m, ds)
+        return x
 
     def distances(self, metric, q, x):
         q, x = _f32(q), _f32(x)

@@ -413,6 +413,105 @@ void vskref_sq8_search(int metric, const float* q, int64_t nq, const int8_t* cod
   }
 }
 
+// ---------------------------------------------------------------------------
+// Product quantisation, Quantization/ProductQuantizer.swift.
+//   codebooks  [m][ksub][ds] with ds = d / m (Codebook.centroids, ProductQuantizerCodebook.swift:8-11)
+//   encode     per segment the nearest codeword by squared L2 accumulated in dimension order, strict '<'
+//              so the lowest code wins ties (Codebook.encode :12-30; shader productQuantize,
+//              QuantizationShaders.metal:113-156)
+//   decode     concatenation of the coded codewords (:152-163).  The optional norm rescale of :165-180 needs
+//              the per-vector norm the Swift object carries in customData; it is not part of the code bytes
+//              and is left to the caller.
+//   tables     tables[s][c] = squared L2 between the query's segment and codeword c (:205-233)
+//   distance   sqrt of the sum over segments, in segment order, of tables[s][code[s]]
+//              (DistanceTables.computeDistance, ProductQuantizerTypes.swift:14-20; the same value as
+//              computeAsymmetricDistance :341-356)
+//   search     the reference has no scan over stored codes; defined here as exact ascending top-k of that
+//              distance, ties by row id.
+//   train      one k-means per segment (trainSegmentCodebook :266-312) with caller-supplied initial
+//              codewords: the reference's k-means++ / mini-batch draw from Swift's RNG and cannot be
+//              reproduced, so parity runs share the initial codebooks (as the IVF runs share centroids).
+// ---------------------------------------------------------------------------
+void vskref_pq_encode(const float* x, int64_t n, int d, int m, int ksub, const float* codebooks,
+                      uint8_t* codes) {
+  const int ds = d / m;
+#pragma omp parallel for schedule(static)
+  for (int64_t r = 0; r < n; ++r)
+    for (int s = 0; s < m; ++s) {
+      const float* seg = x + r * d + (size_t)s * ds;
+      float best = std::numeric_limits<float>::infinity();
+      int bc = 0;
+      for (int c = 0; c < ksub; ++c) {
+        const float* cw = codebooks + ((size_t)s * ksub + c) * ds;
+        float dist = 0.0f;
+        for (int i = 0; i < ds; ++i) { float diff = seg[i] - cw[i]; dist += diff * diff; }
+        if (dist < best) { best = dist; bc = c; }
+      }
+      codes[r * m + s] = (uint8_t)bc;
+    }
+}
+
+void vskref_pq_decode(const uint8_t* codes, int64_t n, int d, int m, int ksub, const float* codebooks,
+                      float* x) {
+  const int ds = d / m;
+  for (int64_t r = 0; r < n; ++r)
+    for (int s = 0; s < m; ++s)
+      std::memcpy(x + r * d + (size_t)s * ds, codebooks + ((size_t)s * ksub + codes[r * m + s]) * ds,
+                  sizeof(float) * (size_t)ds);
+}
+
+void vskref_pq_tables(const float* q, int64_t nq, int d, int m, int ksub, const float* codebooks,
+                      float* tables) {
+  const int ds = d / m;
+  for (int64_t a = 0; a < nq; ++a)
+    for (int s = 0; s < m; ++s)
+      for (int c = 0; c < ksub; ++c) {
+        const float* seg = q + a * d + (size_t)s * ds;
+        const float* cw = codebooks + ((size_t)s * ksub + c) * ds;
+        float sum = 0.0f;
+        for (int i = 0; i < ds; ++i) { float diff = seg[i] - cw[i]; sum += diff * diff; }
+        tables[((size_t)a * m + s) * ksub + c] = sum;
+      }
+}
+
+void vskref_pq_search(const float* q, int64_t nq, const uint8_t* codes, int64_t n, int d, int m, int ksub,
+                      const float* codebooks, int k, float* out_dist, int64_t* out_ids) {
+#pragma omp parallel
+  {
+    std::vector<float> table((size_t)m * ksub);
+    std::vector<std::pair<float, int64_t>> cand;
+#pragma omp for schedule(dynamic, 1)
+    for (int64_t a = 0; a < nq; ++a) {
+      vskref_pq_tables(q + a * d, 1, d, m, ksub, codebooks, table.data());
+      cand.clear();
+      for (int64_t r = 0; r < n; ++r) {
+        float dist = 0.0f;
+        for (int s = 0; s < m; ++s) dist += table[(size_t)s * ksub + codes[r * m + s]];
+        cand.emplace_back(std::sqrt(dist), r);
+      }
+      size_t kk = std::min<size_t>((size_t)k, cand.size());
+      std::partial_sort(cand.begin(), cand.begin() + kk, cand.end());
+      for (size_t j = 0; j < (size_t)k; ++j) {
+        out_dist[a * k + j] = j < kk ? cand[j].first : std::numeric_limits<float>::infinity();
+        out_ids[a * k + j] = j < kk ? cand[j].second : -1;
+      }
+    }
+  }
+}
+
+void vskref_pq_train(const float* x, int64_t n, int d, int m, int ksub, int iters, const float* init_codebooks,
+                     float* codebooks) {
+  const int ds = d / m;
+  std::vector<float> seg((size_t)n * ds);
+  std::vector<int32_t> asg((size_t)n);
+  for (int s = 0; s < m; ++s) {
+    for (int64_t r = 0; r < n; ++r)
+      std::memcpy(&seg[(size_t)r * ds], x + r * d + (size_t)s * ds, sizeof(float) * (size_t)ds);
+    vskref_kmeans(seg.data(), n, ds, ksub, iters, -1.0f, init_codebooks + (size_t)s * ksub * ds,
+                  codebooks + (size_t)s * ksub * ds, asg.data(), nullptr, nullptr);
+  }
+}
+
 // Merge of per-shard top-k lists: G lists of k (distance, global id) per query,
 // ascending by (distance, id) — what a single unsharded search would return.
 void vskref_merge_topk(const float* dist, const int64_t* ids, int g, int64_t nq, int k,

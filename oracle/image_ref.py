@@ -85,10 +85,12 @@ def parse_image(data: bytes):
     return meta, sections
 
 
-def build_image(kind: str, metric: str, dim: int, count: int, sections, id_base=0, has_masks=False, nlist=0) -> bytes:
+def build_image(kind: str, metric: str, dim: int, count: int, sections, id_base=0, has_masks=False, nlist=0,
+                pq_segments=0, pq_codebook_size=0) -> bytes:
     """An image as the library writes it, from (name, bytes) pairs."""
     meta = {"format": "vsk-b200-index-image", "format_version": 1, "kind": kind, "metric": metric, "dimensions": dim,
             "count": count, "id_base": id_base, "has_masks": has_masks, "nlist": nlist,
+            "pq_segments": pq_segments, "pq_codebook_size": pq_codebook_size,
             "sections": [{"name": n, "bytes": len(b), "checksum": "%016x" % checksum(b)} for n, b in sections]}
     text = json.dumps(meta, separators=(",", ":"))
     while (16 + len(text)) % ALIGN:

@@ -50,6 +50,17 @@ def main():
     out["q_in"] = v
     out["q_codes"] = m.scalar_quantize(v, 255.0, 0.0)
     out["q_back"] = m.scalar_dequantize(out["q_codes"], 255.0, 0.0)
+    # product quantisation shaders (productQuantize / productDequantize): 4 sub-spaces of 6 dimensions, 256
+    # codewords; codeword 200 duplicates codeword 17 in every sub-space (a tie: the lower code must win) and the
+    # first rows sit exactly on codewords
+    px = rng.standard_normal((200, 24)).astype(np.float32)
+    pcb = rng.standard_normal((4, 256, 6)).astype(np.float32)
+    pcb[:, 200] = pcb[:, 17]
+    for r in range(8):
+        px[r] = np.concatenate([pcb[s, (17, 200, 3, 255)[(r + s) % 4]] for s in range(4)])
+    out["pq_x"], out["pq_cb"] = px, pcb
+    out["pq_codes"] = m.product_quantize(px, pcb)
+    out["pq_back"] = m.product_dequantize(out["pq_codes"], pcb)
     np.savez_compressed(os.path.join(ROOT, "tests", "golden", "metal_shader_vectors.npz"), **out)
     print("wrote", len(out), "arrays")
 

@@ -215,3 +215,60 @@ def test_sq8_search_matches_decode_then_flat(cpu_oracle):
     d, ids = cpu_oracle.sq8_search(DOT, q, codes, s, o, 10)
     d2, ids2 = cpu_oracle.flat_search(DOT, q, xd, 10)
     assert np.array_equal(ids, ids2) and np.array_equal(d, d2)
+
+
+# ---- product quantisation ------------------------------------------------------------------------------------
+def test_pq_encode_decode_equal_reference_shaders(cpu_oracle):
+    """Golden outputs of the reference's productQuantize / productDequantize shaders
+    (QuantizationShaders.metal:113-204); codeword 200 duplicates 17, so ties resolve to the lower code."""
+    codes = cpu_oracle.pq_encode(GOLD["pq_x"], GOLD["pq_cb"])
+    assert np.array_equal(codes, GOLD["pq_codes"])
+    assert not np.any(codes == 200) and np.any(codes == 17)
+    assert np.array_equal(cpu_oracle.pq_decode(codes, GOLD["pq_cb"]), GOLD["pq_back"])
+
+
+def test_pq_shaders_live(cpu_oracle, metal_ref):
+    rng = np.random.default_rng(12)
+    x = rng.standard_normal((150, 32)).astype(np.float32)
+    cb = rng.standard_normal((8, 256, 4)).astype(np.float32)
+    codes = metal_ref.product_quantize(x, cb)
+    assert np.array_equal(cpu_oracle.pq_encode(x, cb), codes)
+    assert np.array_equal(cpu_oracle.pq_decode(codes, cb), metal_ref.product_dequantize(codes, cb))
+
+
+def test_pq_tables_and_distance_by_hand(cpu_oracle):
+    """ProductQuantizer.precomputeDistanceTables (:205-233) and DistanceTables.computeDistance
+    (ProductQuantizerTypes.swift:14-20) on numbers worked out by hand: 2 segments of 2 dimensions, 2 codewords."""
+    cb = np.array([[[0, 0], [1, 1]], [[2, 0], [0, 3]]], np.float32)
+    q = np.array([[1, 0, 0, 0]], np.float32)
+    t = cpu_oracle.pq_tables(q, cb)
+    assert np.array_equal(t[0], np.array([[1, 1], [4, 9]], np.float32))
+    codes = np.array([[0, 0], [1, 1], [0, 1], [1, 0]], np.uint8)
+    d, ids = cpu_oracle.pq_search(q, codes, cb, 4)
+    # sums 5, 10, 10, 5 -> sqrt; ties keep row order
+    assert np.array_equal(ids[0], [0, 3, 1, 2])
+    assert np.allclose(d[0], np.sqrt(np.array([5, 5, 10, 10], np.float32)))
+    # asymmetric distance == distance to the decoded row when the per-segment sums add exactly
+    back = cpu_oracle.pq_decode(codes, cb)
+    assert np.allclose(d[0], np.sort(np.sqrt(((q - back) ** 2).sum(1))))
+
+
+def test_pq_search_equals_table_sums(cpu_oracle):
+    rng = np.random.default_rng(13)
+    x = rng.standard_normal((500, 16)).astype(np.float32)
+    q = rng.standard_normal((6, 16)).astype(np.float32)
+    init = np.stack([x[:16, s * 4:(s + 1) * 4] for s in range(4)])
+    cb = cpu_oracle.pq_train(x, init, 4)
+    codes = cpu_oracle.pq_encode(x, cb)
+    t = cpu_oracle.pq_tables(q, cb)
+    d, ids = cpu_oracle.pq_search(q, codes, cb, 9)
+    for a in range(6):
+        s = np.zeros(500, np.float32)
+        for seg in range(4):
+            s = s + t[a, seg, codes[:, seg]]            # fp32 adds in segment order
+        full = np.sqrt(s)
+        order = np.lexsort((np.arange(500), full))[:9]
+        assert np.array_equal(ids[a], order) and np.array_equal(d[a], full[order])
+    # training moved the codewords to the means of their cells
+    asg = cpu_oracle.pq_encode(x, cb)
+    assert len(np.unique(asg[:, 0])) > 8

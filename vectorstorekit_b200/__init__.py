@@ -9,6 +9,6 @@ from .engine import (CUDAAccelerationEngine, CUDAAcceleratorStrategy, CUDAComput
                      InsufficientTrainingData, InvalidBufferSize, IVFIndex, KMeansClustering, QuantizedFlatIndex,
                      ScalarQuantizer, InvalidInput, NotTrained, SearchStrategy, Timeout,
                      UnsupportedOperation, VSKError, PATH_FP32_SCAN, PATH_TENSOR_RERANK, ImportFailed,
-                     ExportFailed, import_index, load_index)
+                     ExportFailed, import_index, load_index, ProductQuantizer, PQIndex)
 
 __all__ = [n for n in dir() if not n.startswith("_")]

@@ -35,7 +35,8 @@ class Stats(C.Structure):
 
 class IndexInfo(C.Structure):
     _fields_ = [("kind", C.c_int32), ("metric", C.c_int32), ("dimensions", C.c_int32), ("nlist", C.c_int32),
-                ("count", C.c_int64), ("id_base", C.c_int64), ("has_masks", C.c_int32), ("reserved", C.c_int32)]
+                ("count", C.c_int64), ("id_base", C.c_int64), ("has_masks", C.c_int32), ("pq_segments", C.c_int32),
+                ("pq_codebook_size", C.c_int32), ("reserved", C.c_int32)]
 
 
 # name -> (restype, argtypes).  Pointers that may be host or device memory are void*.
@@ -59,6 +60,15 @@ SIGNATURES = {
     "vsk_index_set_id_base": (C.c_int32, [vp, C.c_int64]),
     "vsk_index_info_get": (C.c_int32, [vp, C.POINTER(IndexInfo)]),
     "vsk_ivf_centroids": (C.c_int32, [vp, vp]),
+    "vsk_pq_train": (C.c_int32, [vp, vp, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32, vp, vp]),
+    "vsk_pq_train_dev": (C.c_int32, [vp, vp, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32, vp, vp]),
+    "vsk_pq_encode": (C.c_int32, [vp, vp, C.c_int32, C.c_int32, C.c_int32, vp, C.c_int64, vp]),
+    "vsk_pq_encode_dev": (C.c_int32, [vp, vp, C.c_int32, C.c_int32, C.c_int32, vp, C.c_int64, vp]),
+    "vsk_pq_decode": (C.c_int32, [vp, vp, C.c_int32, C.c_int32, C.c_int32, vp, C.c_int64, vp]),
+    "vsk_pq_distance_tables": (C.c_int32, [vp, vp, C.c_int32, C.c_int32, C.c_int32, vp, C.c_int64, vp]),
+    "vsk_pq_index_create": (C.c_int32, [vp, C.c_int32, C.c_int32, C.c_int32, vp, C.POINTER(vp)]),
+    "vsk_pq_index_add": (C.c_int32, [vp, vp, C.c_int64]),
+    "vsk_pq_index_add_dev": (C.c_int32, [vp, vp, C.c_int64]),
     "vsk_index_image_size": (C.c_int32, [vp, C.POINTER(C.c_int64)]),
     "vsk_index_export": (C.c_int32, [vp, vp, C.c_int64, C.POINTER(C.c_int64)]),
     "vsk_index_import": (C.c_int32, [vp, vp, C.c_int64, C.POINTER(vp)]),

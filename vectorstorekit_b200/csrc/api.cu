@@ -99,7 +99,6 @@ static int32_t cand_workspace(Ctx* ctx, int64_t nq, CandLists* c) {
 }
 
 // scan(mode, row_begin, row_end): appends to the lists.
-using ScanFn = std::function<int32_t(int mode, int64_t row_begin, int64_t row_end)>;
 
 // Rows per chunk after `seen` rows, for lists compacted to `keep` keys.  A chunk of g * seen rows appends
 // about keep * g keys to a list, with a relative spread of 1/sqrt(keep) (the threshold is the keep-th order
@@ -174,25 +173,14 @@ static int32_t flagged_queries(Ctx* ctx, const CandLists& cand, int64_t nq, std:
 // described by `proto` (metric, operands, norms, masks), with final output.
 static int pick_query_tile(int64_t g);
 
-int32_t fp32_topk(Ctx* ctx, const ExactScanArgs& proto, int64_t n, int64_t nq, const int32_t* sub_dev, int32_t k,
-                  int64_t id_base, float* out_dist, int64_t* out_ids, int level) {
+// Exact top-k of nq queries (optionally the subset `sub_dev` of a larger batch) over n rows with any scan that
+// follows the candidate-list protocol: `make_scan` binds the lists (and the subset) to a scan function; queries
+// whose list overflowed are re-run at the next level of the schedule.
+int32_t scan_topk(Ctx* ctx, const ScanBinder& make_scan, int64_t n, int64_t nq, const int32_t* sub_dev, int32_t k,
+                  int64_t id_base, int final_sqrt, float* out_dist, int64_t* out_ids, int level) {
   CandLists cand;
   VSK_TRY(cand_workspace(ctx, nq, &cand));
-  ExactScanArgs a = proto;
-  a.nq = nq;
-  // a small batch (a few queries, or the handful of queries a fallback re-runs): narrow query tiles
-  if (a.bm_hint == 0 && nq < 128) {
-    const int bm = pick_query_tile(nq);
-    if (bm < 128) a.bm_hint = bm;
-  }
-  a.q_subset = sub_dev;
-  a.cand = cand;
-  ScanFn scan = [&](int mode, int64_t b, int64_t e) {
-    a.mode = mode;
-    a.row_begin = b;
-    a.row_end = e;
-    return launch_exact_scan(ctx, a);
-  };
+  const ScanFn scan = make_scan(cand, nq, sub_dev);
   VSK_TRY(run_schedule(ctx, scan, n, nq, k, cand, level));
   SelectArgs fin{};
   fin.cand = cand;
@@ -202,10 +190,9 @@ int32_t fp32_topk(Ctx* ctx, const ExactScanArgs& proto, int64_t n, int64_t nq, c
   fin.out_dist = out_dist;
   fin.out_ids = out_ids;
   fin.k = k;
-  fin.metric = a.metric;
   fin.id_base = id_base;
   fin.q_subset = sub_dev;
-  fin.final_sqrt = a.metric == VSK_METRIC_EUCLIDEAN;
+  fin.final_sqrt = final_sqrt;
   fin.max_count = k;
   VSK_TRY(launch_select(ctx, fin));
   if (level < 2) {
@@ -223,10 +210,33 @@ int32_t fp32_topk(Ctx* ctx, const ExactScanArgs& proto, int64_t n, int64_t nq, c
       VSK_CUDA(ctx, cudaMemcpyAsync(p, bad.data(), bad.size() * sizeof(int32_t), cudaMemcpyHostToDevice, ctx->stream));
       VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
       ctx->stats.fallback_queries += (int64_t)bad.size();
-      VSK_TRY(fp32_topk(ctx, proto, n, (int64_t)bad.size(), (const int32_t*)p, k, id_base, out_dist, out_ids, level + 1));
+      VSK_TRY(scan_topk(ctx, make_scan, n, (int64_t)bad.size(), (const int32_t*)p, k, id_base, final_sqrt, out_dist,
+                        out_ids, level + 1));
     }
   }
   return VSK_OK;
+}
+
+int32_t fp32_topk(Ctx* ctx, const ExactScanArgs& proto, int64_t n, int64_t nq, const int32_t* sub_dev, int32_t k,
+                  int64_t id_base, float* out_dist, int64_t* out_ids, int level) {
+  const ScanBinder bind = [ctx, &proto](const CandLists& cand, int64_t bn, const int32_t* sub) -> ScanFn {
+    ExactScanArgs a = proto;
+    a.nq = bn;
+    // a small batch (a few queries, or the handful of queries a fallback re-runs): narrow query tiles
+    if (a.bm_hint == 0 && bn < 128) {
+      const int bm = pick_query_tile(bn);
+      if (bm < 128) a.bm_hint = bm;
+    }
+    a.q_subset = sub;
+    a.cand = cand;
+    return [ctx, a](int mode, int64_t b, int64_t e) mutable {
+      a.mode = mode;
+      a.row_begin = b;
+      a.row_end = e;
+      return launch_exact_scan(ctx, a);
+    };
+  };
+  return scan_topk(ctx, bind, n, nq, sub_dev, k, id_base, proto.metric == VSK_METRIC_EUCLIDEAN, out_dist, out_ids, level);
 }
 
 static int32_t fp32_search(Index* ix, const float* q, int64_t nq, const int32_t* sub_dev, int32_t k,
@@ -700,6 +710,8 @@ int32_t vsk_index_destroy(vsk_index* i) {
   dev_free(ix->list_offsets);
   dev_free(ix->list_rows);
   dev_free(ix->assign);
+  dev_free(ix->pq_codebooks);
+  dev_free(ix->pq_codes);
   delete ix;
   return VSK_OK;
 }
@@ -722,6 +734,10 @@ int32_t vsk_search_dev(vsk_index* i, const float* q, int64_t nq, int32_t k, cons
   if (!ix) return VSK_ERR_INVALID_INPUT;
   cudaSetDevice(ix->ctx->device);
   if (ix->kind == INDEX_FLAT_I8) return sq8_search_dev(ix, q, nq, k, out_dist, out_ids);
+  if (ix->kind == INDEX_PQ) {
+    if (qmasks) return fail(ix->ctx, VSK_ERR_UNSUPPORTED_OPERATION, "a product-quantised index carries no row masks");
+    return pq_search_dev(ix, q, nq, k, out_dist, out_ids);
+  }
   return flat_search_dev(ix, q, nq, k, qmasks, out_dist, out_ids);
 }
 

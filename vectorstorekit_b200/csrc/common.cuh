@@ -6,6 +6,7 @@
 #include <cuda_fp16.h>
 #include <stdint.h>
 
+#include <functional>
 #include <string>
 #include <vector>
 
@@ -104,6 +105,7 @@ enum Slot : int {
   SLOT_MISC2, SLOT_MISC3, SLOT_MISC4, SLOT_MISC5, SLOT_MISC6,
   SLOT_IVF_PROBE_D, SLOT_IVF_PROBE_I, SLOT_IVF_KEYS, SLOT_IVF_ORDER, SLOT_IVF_PAIR_OFF, SLOT_IVF_ITEM_CNT,
   SLOT_IVF_ITEM_OFF, SLOT_IVF_SUBSET, SLOT_IVF_STAGES, SLOT_KM_NSEG, SLOT_KM_SEGOFF, SLOT_KM_PARTIAL, SLOT_FILTER_PERM, SLOT_FILTER_ROWS, SLOT_FILTER_COUNT, SLOT_SQ_A, SLOT_SQ_B, SLOT_TC_A, SLOT_TC_B, SLOT_TC_C, SLOT_TC_D,
+  SLOT_PQ_TABLES,
   SLOT_COUNT
 };
 static_assert(SLOT_COUNT <= 64, "grow Ctx::scratch");
@@ -116,7 +118,7 @@ void prof_collect(Ctx* ctx);
 // Device pointer of at least `bytes` for the slot; contents are not preserved across growth.
 int32_t scratch(Ctx* ctx, int slot, size_t bytes, void** out);
 
-enum IndexKind : int { INDEX_FLAT_F32 = 0, INDEX_FLAT_I8 = 1, INDEX_IVF = 2 };
+enum IndexKind : int { INDEX_FLAT_F32 = 0, INDEX_FLAT_I8 = 1, INDEX_IVF = 2, INDEX_PQ = 3 };
 
 struct DevBuf {
   void* p = nullptr;
@@ -157,6 +159,10 @@ struct Index {
   std::vector<int64_t> list_offsets_h;
   int32_t* list_rows = nullptr;    // [n] original row of each stored row
   int32_t* assign = nullptr;       // [n] row -> list (original order)
+  // product quantisation
+  int32_t pq_m = 0, pq_ksub = 0;   // segments, codewords per segment
+  float* pq_codebooks = nullptr;   // [pq_m][pq_ksub][dim / pq_m]
+  uint8_t* pq_codes = nullptr;     // [capacity][pq_m]
 };
 
 // ---- exact_scan.cu -----------------------------------------------------------------------
@@ -222,6 +228,12 @@ int32_t launch_merge_topk(Ctx* ctx, const float* dist, const int64_t* ids, int32
 int32_t launch_init_cand(Ctx* ctx, const CandLists& c, int64_t nq);
 
 // ---- search schedule in api.cu -------------------------------------------------------------
+// A scan of rows [row_begin, row_end) in ScanMode `mode` that writes keys into candidate lists, and the function
+// that binds lists, batch size and query subset to such a scan.
+using ScanFn = std::function<int32_t(int mode, int64_t row_begin, int64_t row_end)>;
+using ScanBinder = std::function<ScanFn(const CandLists& cand, int64_t nq, const int32_t* sub_dev)>;
+int32_t scan_topk(Ctx* ctx, const ScanBinder& make_scan, int64_t n, int64_t nq, const int32_t* sub_dev, int32_t k,
+                  int64_t id_base, int final_sqrt, float* out_dist, int64_t* out_ids, int level);
 // Exact top-k of nq queries over n rows with the fp32 scan; `proto` carries metric, operands,
 // norms and masks.  Outputs are device pointers [nq][k] (indexed by sub_dev[pos] when given).
 int32_t fp32_topk(Ctx* ctx, const ExactScanArgs& proto, int64_t n, int64_t nq, const int32_t* sub_dev, int32_t k,
@@ -233,6 +245,10 @@ int64_t schedule_chunk(int64_t seen, int32_t keep, int level);
 int64_t schedule_dense_rows(int32_t keep);
 int64_t schedule_tuning(const char* name, int64_t dflt);
 int32_t schedule_max_count(int64_t seen, int64_t chunk, int32_t keep);
+
+// ---- pq.cu -------------------------------------------------------------------------------
+int32_t pq_search_dev(Index* ix, const float* q, int64_t nq, int32_t k, float* out_dist, int64_t* out_ids);
+int32_t pq_reserve(Index* ix, int64_t need);
 
 // ---- helpers in api.cu ---------------------------------------------------------------------
 int32_t dev_alloc(Ctx* ctx, void** p, size_t bytes);

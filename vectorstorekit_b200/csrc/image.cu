@@ -34,6 +34,7 @@ int32_t flat_reserve(Index* ix, int64_t need);
 int32_t flat_adopt_rows(Index* ix, int64_t n, bool has_masks);
 int32_t sq8_reserve(Index* ix, int64_t need);
 int32_t sq8_adopt_rows(Index* ix, int64_t n);
+int32_t pq_adopt_rows(Index* ix, int64_t n);
 
 namespace {
 
@@ -145,7 +146,7 @@ struct Section {
 };
 
 const char* kind_name(int kind) {
-  return kind == INDEX_FLAT_F32 ? "flat_f32" : kind == INDEX_FLAT_I8 ? "flat_i8" : kind == INDEX_IVF ? "ivf" : "?";
+  return kind == INDEX_FLAT_F32 ? "flat_f32" : kind == INDEX_FLAT_I8 ? "flat_i8" : kind == INDEX_IVF ? "ivf" : kind == INDEX_PQ ? "pq" : "?";
 }
 const char* metric_name(int m) {
   static const char* names[] = {"euclidean", "cosine", "dotProduct", "manhattan"};   // DistanceMetric raw values
@@ -175,6 +176,9 @@ std::vector<Section> sections_of(const Index* ix) {
     add("list_rows", ix->list_rows, n * 4);
     add("assignments", ix->assign, n * 4);
     add("rows", ix->rows, n * d * 4);   // in list order
+  } else if (ix->kind == INDEX_PQ) {
+    add("pq_codebooks", ix->pq_codebooks, (int64_t)ix->pq_ksub * d * 4);   // [m][ksub][d / m]
+    add("pq_codes", ix->pq_codes, n * ix->pq_m);
   }
   return s;
 }
@@ -186,9 +190,10 @@ std::string metadata_text(const Index* ix, const std::vector<Section>& secs) {
   std::string m;
   snprintf(buf, sizeof buf,
            "{\"format\":\"vsk-b200-index-image\",\"format_version\":1,\"kind\":\"%s\",\"metric\":\"%s\","
-           "\"dimensions\":%d,\"count\":%lld,\"id_base\":%lld,\"has_masks\":%s,\"nlist\":%d,\"sections\":[",
+           "\"dimensions\":%d,\"count\":%lld,\"id_base\":%lld,\"has_masks\":%s,\"nlist\":%d,\"pq_segments\":%d,"
+           "\"pq_codebook_size\":%d,\"sections\":[",
            kind_name(ix->kind), metric_name(ix->metric), ix->dim, (long long)ix->n, (long long)ix->id_base,
-           ix->has_masks ? "true" : "false", ix->nlist);
+           ix->has_masks ? "true" : "false", ix->nlist, ix->pq_m, ix->pq_ksub);
   m = buf;
   for (size_t i = 0; i < secs.size(); ++i) {
     snprintf(buf, sizeof buf, "%s{\"name\":\"%s\",\"bytes\":%lld,\"checksum\":\"%016llx\"}", i ? "," : "",
@@ -461,6 +466,17 @@ int32_t read_image(Ctx* ctx, Source& src, Index** out) {
         (st = dev_alloc(ctx, (void**)&ix->list_rows, (size_t)n * 4)) == VSK_OK &&
         (st = dev_alloc(ctx, (void**)&ix->assign, (size_t)n * 4)) == VSK_OK)
       st = dev_alloc(ctx, (void**)&ix->rows, (size_t)n * dim * 4);
+  } else if (kind == "pq") {
+    const long long pm = num("pq_segments", 0), pk = num("pq_codebook_size", 0);
+    if (pm <= 0 || dim % pm != 0 || pk < 2 || pk > 256) return fail(ctx, VSK_ERR_IMPORT_FAILED, "an impossible product quantiser");
+    ix = new Index();
+    ix->ctx = ctx;
+    ix->kind = INDEX_PQ;
+    ix->metric = VSK_METRIC_EUCLIDEAN;
+    ix->dim = (int32_t)dim;
+    ix->pq_m = (int32_t)pm;
+    ix->pq_ksub = (int32_t)pk;
+    if ((st = dev_alloc(ctx, (void**)&ix->pq_codebooks, (size_t)pk * dim * 4)) == VSK_OK) st = pq_reserve(ix, n);
   } else {
     return fail(ctx, VSK_ERR_IMPORT_FAILED, "unknown index kind '%s'", kind.c_str());
   }
@@ -489,6 +505,7 @@ int32_t read_image(Ctx* ctx, Source& src, Index** out) {
   // derived state
   if (ix->kind == INDEX_FLAT_F32) st = flat_adopt_rows(ix, n, has_masks);
   else if (ix->kind == INDEX_FLAT_I8) st = sq8_adopt_rows(ix, n);
+  else if (ix->kind == INDEX_PQ) st = pq_adopt_rows(ix, n);
   else {
     ix->n = n;
     ix->list_offsets_h.resize((size_t)nlist + 1);
@@ -518,7 +535,9 @@ extern "C" {
 int32_t vsk_index_info_get(vsk_index* i, vsk_index_info* info) {
   Index* ix = reinterpret_cast<Index*>(i);
   if (!ix || !info) return VSK_ERR_INVALID_INPUT;
-  info->kind = ix->kind == INDEX_FLAT_F32 ? VSK_INDEX_FLAT_F32 : ix->kind == INDEX_FLAT_I8 ? VSK_INDEX_FLAT_I8 : VSK_INDEX_IVF;
+  info->kind = ix->kind == INDEX_FLAT_F32 ? VSK_INDEX_FLAT_F32 : ix->kind == INDEX_FLAT_I8 ? VSK_INDEX_FLAT_I8 : ix->kind == INDEX_PQ ? VSK_INDEX_PQ : VSK_INDEX_IVF;
+  info->pq_segments = ix->pq_m;
+  info->pq_codebook_size = ix->pq_ksub;
   info->metric = ix->metric;
   info->dimensions = ix->dim;
   info->count = ix->n;

@@ -313,9 +313,9 @@ class _IndexBase:
     def info(self) -> dict:
         d = _lib.IndexInfo()
         self.dev.check(self._lib.vsk_index_info_get(self._h, C.byref(d)))
-        return {"kind": ("flat_f32", "flat_i8", "ivf")[d.kind], "metric": _METRIC_OF_ID[d.metric],
+        return {"kind": ("flat_f32", "flat_i8", "ivf", "pq")[d.kind], "metric": _METRIC_OF_ID[d.metric],
                 "dimensions": d.dimensions, "count": d.count, "id_base": d.id_base, "nlist": d.nlist,
-                "has_masks": bool(d.has_masks)}
+                "has_masks": bool(d.has_masks), "pq_segments": d.pq_segments, "pq_codebook_size": d.pq_codebook_size}
 
     # ``VectorIndex.export(format:) -> Data`` / ``import(data:format:)`` (``Core/Protocols.swift:157-160``); only the
     # binary format exists here, any other raises as ``IVFIndex.export`` does (``Indexes/IVFIndex.swift:304-311``).
@@ -354,11 +354,13 @@ def _adopt(dev: "CUDAComputeDevice", h):
     probe = _IndexBase(dev)
     probe._h = h
     info = probe.info()
-    cls = {"flat_f32": FlatIndex, "flat_i8": QuantizedFlatIndex, "ivf": IVFIndex}[info["kind"]]
+    cls = {"flat_f32": FlatIndex, "flat_i8": QuantizedFlatIndex, "ivf": IVFIndex, "pq": PQIndex}[info["kind"]]
     ix = cls.__new__(cls)
     _IndexBase.__init__(ix, dev)
     ix._h, probe._h = h, None
     ix.dimensions = info["dimensions"]
+    if cls is PQIndex:
+        ix.segments, ix.codebookSize = info["pq_segments"], info["pq_codebook_size"]
     if cls is IVFIndex:
         ix.numberOfCentroids = info["nlist"]
         ix.numberOfProbes = min(10, info["nlist"])      # IVFConfiguration default (IVFConfiguration.swift:32)
@@ -635,6 +637,137 @@ class QuantizedFlatIndex(_IndexBase):
         else:
             c = _host(codes, np.int8)
             self.dev.check(self._lib.vsk_sq8_index_add(self._h, _ptr(c), c.shape[0]))
+
+    def batchSearch(self, queries, k: int):
+        if queries.shape[1] != self.dimensions:
+            raise DimensionMismatch(f"expected {self.dimensions}, got {queries.shape[1]}")
+        return self._search(queries, int(k))
+
+
+class ProductQuantizer:
+    """``ProductQuantizer`` (``Quantization/ProductQuantizer.swift``) with ``ProductQuantizationConfig``'s fields
+    (``Config/Quantization/ProductQuantizationConfig.swift:8-50``): ``segments`` sub-spaces, ``codeSize`` bits per
+    code (at most 8: a code is one byte), ``codebookSize = 1 << codeSize`` codewords each.  ``codebooks`` is
+    ``[segments][codebookSize][dimensions / segments]``.  Training starts from caller-supplied codewords (default:
+    the segments of the first ``codebookSize`` vectors); the reference's k-means++ / mini-batch draws cannot be
+    reproduced."""
+
+    def __init__(self, dev: CUDAComputeDevice, dimensions: int, segments: int = 8, codeSize: int = 8,
+                 trainingIterations: int = 25):
+        if dimensions <= 0 or segments <= 0 or dimensions % segments != 0:
+            raise InvalidInput(f"invalid segmentation: {dimensions} dimensions into {segments} segments")
+        if not (4 <= codeSize <= 16):                       # ProductQuantizationConfig.validate :46-48
+            raise InvalidInput(f"invalid code size {codeSize}")
+        if codeSize > 8:
+            raise UnsupportedOperation("codes are stored as one byte per segment: codeSize must be at most 8")
+        self.dev, self._lib = dev, dev._lib
+        self.dimensions, self.segments, self.codeSize = int(dimensions), int(segments), int(codeSize)
+        self.codebookSize = 1 << codeSize
+        self.segmentDimensions = dimensions // segments
+        self.trainingIterations = int(trainingIterations)
+        self.codebooks = None
+        self.trained = False
+
+    def _shape(self):
+        return self.dimensions, self.segments, self.codebookSize
+
+    def _cb(self, like=None):
+        if not self.trained:
+            raise NotTrained("Quantizer must be trained before use")
+        if like is not None and _is_dev(like):
+            return self.codebooks if _is_dev(self.codebooks) else torch.as_tensor(self.codebooks, device=like.device)
+        return _host(self.codebooks, np.float32)
+
+    def set_codebooks(self, codebooks):
+        if tuple(codebooks.shape) != (self.segments, self.codebookSize, self.segmentDimensions):
+            raise DimensionMismatch("codebooks must be [segments][codebookSize][dimensions / segments]")
+        self.codebooks = codebooks.contiguous().float() if _is_dev(codebooks) else _host(codebooks, np.float32)
+        self.trained = True
+
+    def train(self, vectors, initialCodebooks=None):
+        n, d = vectors.shape
+        if d != self.dimensions:
+            raise DimensionMismatch(f"expected {self.dimensions}, got {d}")
+        dim, m, ks = self._shape()
+        if _is_dev(vectors):
+            x = vectors.contiguous().float()
+            init = None if initialCodebooks is None else torch.as_tensor(initialCodebooks, device=x.device).contiguous().float()
+            cb = torch.empty((m, ks, dim // m), dtype=torch.float32, device=x.device)
+            self.dev.check(self._lib.vsk_pq_train_dev(self.dev._h, _ptr(x), n, dim, m, ks, self.trainingIterations,
+                                                      _ptr(init), _ptr(cb)))
+        else:
+            x = _host(vectors, np.float32)
+            init = None if initialCodebooks is None else _host(initialCodebooks, np.float32)
+            cb = np.empty((m, ks, dim // m), np.float32)
+            self.dev.check(self._lib.vsk_pq_train(self.dev._h, _ptr(x), n, dim, m, ks, self.trainingIterations,
+                                                  _ptr(init), _ptr(cb)))
+        self.codebooks = cb
+        self.trained = True
+        return cb
+
+    def encodeBatch(self, vectors):
+        n, d = vectors.shape
+        if d != self.dimensions:
+            raise DimensionMismatch(f"expected {self.dimensions}, got {d}")
+        dim, m, ks = self._shape()
+        cb = self._cb(vectors)
+        if _is_dev(vectors):
+            x = vectors.contiguous().float()
+            codes = torch.empty((n, m), dtype=torch.uint8, device=x.device)
+            self.dev.check(self._lib.vsk_pq_encode_dev(self.dev._h, _ptr(cb), dim, m, ks, _ptr(x), n, _ptr(codes)))
+            return codes
+        x = _host(vectors, np.float32)
+        codes = np.empty((n, m), np.uint8)
+        self.dev.check(self._lib.vsk_pq_encode(self.dev._h, _ptr(cb), dim, m, ks, _ptr(x), n, _ptr(codes)))
+        return codes
+
+    def decodeBatch(self, codes):
+        dim, m, ks = self._shape()
+        c = _host(codes, np.uint8)
+        out = np.empty((c.shape[0], dim), np.float32)
+        self.dev.check(self._lib.vsk_pq_decode(self.dev._h, _ptr(self._cb()), dim, m, ks, _ptr(c), c.shape[0], _ptr(out)))
+        return out
+
+    # precomputeDistanceTables(query:) (:205-233), for a batch: [nq][segments][codebookSize]
+    def precomputeDistanceTables(self, queries):
+        dim, m, ks = self._shape()
+        q = _host(queries, np.float32)
+        if q.ndim == 1:
+            q = q[None]
+        if q.shape[1] != dim:
+            raise DimensionMismatch(f"expected {dim}, got {q.shape[1]}")
+        out = np.empty((q.shape[0], m, ks), np.float32)
+        self.dev.check(self._lib.vsk_pq_distance_tables(self.dev._h, _ptr(self._cb()), dim, m, ks, _ptr(q), q.shape[0],
+                                                        _ptr(out)))
+        return out
+
+    def index(self):
+        """A resident index of codes searched by asymmetric distance."""
+        return PQIndex(self.dev, self.dimensions, self.segments, self.codebookSize, self._cb())
+
+
+class PQIndex(_IndexBase):
+    """Codes resident on the GPU; ``batchSearch`` returns per query the ``k`` rows with the smallest asymmetric
+    distance (``DistanceTables.computeDistance``, ``ProductQuantizerTypes.swift:14-20``), ascending, ties by row."""
+
+    def __init__(self, dev: CUDAComputeDevice, dimensions: int, segments: int, codebookSize: int, codebooks):
+        super().__init__(dev)
+        h = C.c_void_p()
+        cb = codebooks.contiguous().float() if _is_dev(codebooks) else _host(codebooks, np.float32)
+        dev.check(self._lib.vsk_pq_index_create(dev._h, int(dimensions), int(segments), int(codebookSize), _ptr(cb),
+                                                C.byref(h)))
+        self._h = h
+        self.dimensions, self.segments, self.codebookSize = int(dimensions), int(segments), int(codebookSize)
+
+    def add(self, codes):
+        if codes.shape[1] != self.segments:
+            raise DimensionMismatch(f"expected {self.segments} codes per row, got {codes.shape[1]}")
+        if _is_dev(codes):
+            c = codes.contiguous()
+            self.dev.check(self._lib.vsk_pq_index_add_dev(self._h, _ptr(c), c.shape[0]))
+        else:
+            c = _host(codes, np.uint8)
+            self.dev.check(self._lib.vsk_pq_index_add(self._h, _ptr(c), c.shape[0]))
 
     def batchSearch(self, queries, k: int):
         if queries.shape[1] != self.dimensions:
