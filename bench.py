@@ -56,6 +56,11 @@ WORKLOADS = {
                name="filtered-manhattan-5M-d256-q10000-k50"),
     "c5s": dict(kind="filtered", metric="manhattan", rows=500_000, dim=256, queries=1_024, k=50, cfg=5,
                 name="filtered-manhattan-500k-d256-q1024-k50"),
+    # product-quantised codes searched by asymmetric distance (the storage-scan step after int8)
+    "pq": dict(kind="pq", metric="euclidean", rows=10_000_000, dim=128, queries=10_000, k=10, cfg=3, segments=16,
+               code_bits=8, train_rows=262_144, iters=10, nlist=4096, name="pq-adc-10M-d128-m16-q10000-k10"),
+    "pqs": dict(kind="pq", metric="euclidean", rows=2_000_000, dim=128, queries=2_048, k=10, cfg=3, segments=16,
+                code_bits=8, train_rows=131_072, iters=5, nlist=1024, name="pq-adc-2M-d128-m16-q2048-k10"),
 }
 
 
@@ -114,7 +119,7 @@ def _gen_slab(torch, wl, first_row, count, device, centres=None):
     if wl["kind"] == "filtered":
         return torch.rand((count, dim), generator=g, dtype=torch.float32, device=device) * 2 - 1
     t = torch.randn((count, dim), generator=g, dtype=torch.float32, device=device)
-    if wl["kind"] == "ivf":
+    if wl["kind"] in ("ivf", "pq"):
         c = torch.randint(0, centres.shape[0], (count,), generator=g, device=device)
         return centres[c] + 0.1 * t
     if wl["metric"] == "cosine":
@@ -289,6 +294,37 @@ class Bench:
         self.flops = 2.0 * self.nq * n * wl["dim"]
         self.bound = "tensor"
 
+    def _build_pq(self):
+        wl, t = self.wl, self.torch
+        g = t.Generator(device=self.device)
+        g.manual_seed(SEED + 31337)
+        centres = t.randn((wl["nlist"], wl["dim"]), generator=g, dtype=t.float32, device=self.device)
+        pq = self.vsk.ProductQuantizer(self.dev, wl["dim"], segments=wl["segments"], codeSize=wl["code_bits"],
+                                       trainingIterations=wl["iters"])
+        sample = gen_rows(t, wl, 0, wl["train_rows"], self.device, centres)     # every rank trains on the same rows
+        t.cuda.synchronize()
+        t0 = time.perf_counter()
+        pq.train(sample)
+        t.cuda.synchronize()
+        t1 = time.perf_counter()
+        self.index = pq.index()
+        step = 1 << 20
+        for b in range(self.lo, self.hi, step):
+            e = min(self.hi, b + step)
+            self.index.add(pq.encodeBatch(gen_rows(t, wl, b, e, self.device, centres)))
+        t.cuda.synchronize()
+        t2 = time.perf_counter()
+        self.index.set_id_base(self.lo)
+        self.queries = gen_queries(t, wl, self.device, centres)
+        self.pq, self.rows, self.centres = pq, None, centres
+        n = self.hi - self.lo
+        self.extra = {"segments": wl["segments"], "codebook_size": 1 << wl["code_bits"], "train_s": t1 - t0,
+                      "encode_rows_per_s": n / (t2 - t1), "code_bytes": n * wl["segments"]}
+        # one table look-up (a 4-byte word of shared memory) and one add per (query, row, segment)
+        self.flops = 1.0 * self.nq * n * wl["segments"]
+        self.bytes_per_query = float(n * wl["segments"])
+        self.bound = "smem"
+
     # ---- steps ----
     def local_search(self, queries, k):
         if self.wl["kind"] == "ivf":
@@ -332,6 +368,19 @@ class Bench:
         elif wl["kind"] == "ivf":
             x = self.rows.cpu().numpy()
             fn = lambda n: o.ivf_search(q[:n], x, self.centroids_host, self.assign_host, wl["nprobe"], self.k)
+        elif wl["kind"] == "pq":
+            n_all = self.hi - self.lo
+            n_cpu = min(n_all, 2_000_000)
+            xs = gen_rows(self.torch, wl, self.lo, self.lo + n_cpu, self.device, self.centres)
+            codes = self.pq.encodeBatch(xs).cpu().numpy()
+            del xs
+            cb = self.pq.codebooks.cpu().numpy() if hasattr(self.pq.codebooks, "cpu") else self.pq.codebooks
+            fn = lambda n: o.pq_search(q[:n], codes, cb, self.k)
+            v, nq, dt = cpu_rate(fn, self.nq, cores, seconds_target)
+            v *= n_cpu / n_all
+            return {"value": v, "unit": "queries/s", "cores": cores, "kind": "port",
+                    "sample": f"{nq} of {self.nq} queries over {n_cpu} of {n_all} rows, {dt:.1f} s"
+                              + (" (rate scaled by the row ratio: extrapolated)" if n_cpu < n_all else "")}
         else:
             # codes of a bounded prefix of the shard (regenerated and re-encoded on the GPU); the rate is scaled
             # by the row ratio and labelled as extrapolated
@@ -489,6 +538,13 @@ def main():
                     peak=pk["hbm_gbs"], peak_source=pk["source"] + " (copy)",
                     note="algorithmic bytes are query-major (each query reads its probed lists once); the list-major "
                          "kernel reuses a list across the queries that probe it, so achieved may exceed peak")
+    elif b.bound == "smem":
+        sm = dev.info()["sm_count"]
+        roof.update(unit="T look-ups/s", achieved=b.flops * args.steps / secs / 1e12 if secs > 0 else None,
+                    peak=sm * 32 * 1.965e9 / 1e12, peak_source="nominal: SMs x 32 shared-memory banks x 1965 MHz",
+                    algorithmic_codes_gbs=b.bytes_per_query * nq * args.steps / secs / 1e9 if secs > 0 else None,
+                    note="one 4-byte table word per (query, row, segment); query-major code bytes are given for "
+                         "the HBM view: a query tile re-reads the codes from L2")
     else:
         sm = dev.info()["sm_count"]
         roof.update(unit="T lane-instr/s", achieved=b.flops * args.steps / secs / 1e12 if secs > 0 else None,

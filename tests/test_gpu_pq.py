@@ -82,8 +82,8 @@ def test_adc_search_bit_exact(vsk, dev, cpu_oracle, shape):
 
 
 def test_adc_heavy_ties_and_device_pointers(vsk, dev, cpu_oracle):
-    """Four codewords per segment and two segments: 16 distinct code rows among 60 000, so thousands of rows tie
-    at every distance; the lists overflow and the schedule's fallback levels must still return rows in id order."""
+    """Quantised distances tie in bulk.  16 distinct code rows among 60 000: thousands of rows tie at every
+    distance, and the result must list the tied rows in row order."""
     import torch
     rng = np.random.default_rng(3)
     n, d, m = 60_000, 8, 2
@@ -96,7 +96,29 @@ def test_adc_heavy_ties_and_device_pointers(vsk, dev, cpu_oracle):
     dist, ids = ix.batchSearch(torch.as_tensor(q, device="cuda"), 100)
     rd, ri = cpu_oracle.pq_search(q, codes, cb, 100)
     assert np.array_equal(ids.cpu().numpy(), ri) and np.array_equal(dist.cpu().numpy(), rd)
-    assert dev.stats()["fallback_queries"] > 0
+
+
+def test_adc_late_block_of_identical_best_rows(vsk, dev, cpu_oracle):
+    """The nearest code row appears only in the second half of the database, 30 000 times in a row: a chunk
+    appends more keys than a candidate list holds, the overflow is detected and the queries are re-run with
+    smaller chunks (fallback_queries), and the answer is still the first 100 of those rows."""
+    rng = np.random.default_rng(33)
+    n, d, m = 60_000, 8, 2
+    cb = rng.standard_normal((m, 16, d // m)).astype(np.float32)
+    star = np.array([7, 11], np.uint8)
+    codes = rng.integers(0, 6, (n, m)).astype(np.uint8)           # codes 0..5: never the star row
+    codes[n // 2:] = star
+    target = np.concatenate([cb[0, 7], cb[1, 11]])
+    q = (target + 0.01 * rng.standard_normal((12, d))).astype(np.float32)
+    pq = _pq(vsk, dev, d, m, 4, cb)
+    ix = pq.index()
+    ix.add(codes)
+    before = dev.stats()["fallback_queries"]
+    dist, ids = ix.batchSearch(q, 100)
+    rd, ri = cpu_oracle.pq_search(q, codes, cb, 100)
+    assert np.array_equal(ids, ri) and np.array_equal(dist, rd)
+    assert np.array_equal(ids[0], np.arange(n // 2, n // 2 + 100))
+    assert dev.stats()["fallback_queries"] > before
 
 
 def test_train_against_oracle(vsk, dev, cpu_oracle):

@@ -118,7 +118,7 @@ struct PqScanArgs {
 template <int TQ, int MODE>
 __global__ void __launch_bounds__(PQ_THREADS) pq_scan_kernel(PqScanArgs a) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
-  float* tab = reinterpret_cast<float*>(smem_raw);                                   // [m][ksub][TQ]
+  float* tab = reinterpret_cast<float*>(smem_raw);                                   // m * ksub * TQ floats (layout below)
   uint8_t* cds = smem_raw + (size_t)a.m * a.ksub * TQ * sizeof(float);               // [m][PQ_THREADS]
   const int64_t parts = (a.row_end - a.row_begin + a.rows_per_cta - 1) / a.rows_per_cta;
   const int64_t qt = blockIdx.x / parts;
@@ -131,7 +131,17 @@ __global__ void __launch_bounds__(PQ_THREADS) pq_scan_kernel(PqScanArgs a) {
     const bool ok = pos < a.nq;
     const int64_t qi = ok ? (a.q_subset ? (int64_t)a.q_subset[pos] : pos) : 0;
     const float* src = a.tables + qi * entries;
-    for (int e = threadIdx.x; e < entries; e += PQ_THREADS) tab[(size_t)e * TQ + t] = ok ? __ldg(src + e) : CUDART_INF_F;
+    // TQ >= 4: [segment][group of 4 queries][code][4], so that the 32 lanes of one 16-byte load (one group, 32
+    // different codes) spread over all banks; a [segment][code][query] layout would put them on 8 of the 32
+    for (int e = threadIdx.x; e < entries; e += PQ_THREADS) {
+      const float v = ok ? __ldg(src + e) : CUDART_INF_F;
+      if (TQ % 4 == 0) {
+        const int sseg = e / a.ksub, c = e - sseg * a.ksub;
+        tab[(((size_t)sseg * (TQ / 4) + (t >> 2)) * a.ksub + c) * 4 + (t & 3)] = v;
+      } else {
+        tab[(size_t)e * TQ + t] = v;
+      }
+    }
   }
   float thr[TQ];
 #pragma unroll
@@ -154,17 +164,18 @@ __global__ void __launch_bounds__(PQ_THREADS) pq_scan_kernel(PqScanArgs a) {
     for (int t = 0; t < TQ; ++t) acc[t] = 0.f;
     for (int s = 0; s < a.m; ++s) {
       const int c = cds[s * PQ_THREADS + threadIdx.x];
-      const float* e = tab + ((size_t)s * a.ksub + c) * TQ;
       if (TQ % 4 == 0) {
+        const float* e = tab + ((size_t)s * (TQ / 4) * a.ksub + c) * 4;
 #pragma unroll
         for (int t = 0; t < TQ; t += 4) {
-          const float4 v = *reinterpret_cast<const float4*>(e + t);
+          const float4 v = *reinterpret_cast<const float4*>(e + (size_t)(t >> 2) * a.ksub * 4);
           acc[t] = __fadd_rn(acc[t], v.x);
           acc[t + 1] = __fadd_rn(acc[t + 1], v.y);
           acc[t + 2] = __fadd_rn(acc[t + 2], v.z);
           acc[t + 3] = __fadd_rn(acc[t + 3], v.w);
         }
       } else {
+        const float* e = tab + ((size_t)s * a.ksub + c) * TQ;
 #pragma unroll
         for (int t = 0; t < TQ; ++t) acc[t] = __fadd_rn(acc[t], e[t]);
       }
@@ -176,7 +187,9 @@ __global__ void __launch_bounds__(PQ_THREADS) pq_scan_kernel(PqScanArgs a) {
       const float v = __fsqrt_rn(acc[t]);
       if (MODE == SCAN_DENSE) {
         a.cand.keys[pos * kCandCap + (row - a.row_begin)] = make_key(v, (uint32_t)row);
-      } else if (v <= thr[t]) {
+      } else if (v < thr[t]) {
+        // strict: rows arrive in ascending order, so a later row that only ties the current k-th value has a
+        // larger row number than every kept key and cannot displace one (quantised distances tie in bulk)
         const int slot = atomicAdd(&a.cand.count[pos], 1);
         if (slot < kCandCap) a.cand.keys[pos * kCandCap + slot] = make_key(v, (uint32_t)row);
       }
