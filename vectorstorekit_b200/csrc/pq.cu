@@ -12,8 +12,8 @@
 // distances equal the CPU restatement bit for bit.  The scan is byte work: per (row, query) m table look-ups in
 // shared memory and m adds.  A CTA keeps the tables of TQ queries in shared memory, interleaved by query
 // ([segment][code][query]) so that one 16-byte shared-memory load serves four queries, streams blocks of 256
-// rows' codes (transposed to [segment][row] so a warp reads consecutive bytes), and appends keys to the
-// candidate lists of the search schedule (dense first chunk, thresholded later chunks).
+// rows (each thread reads its row's codes from global memory, four segments per 32-bit load) and appends keys to
+// the candidate lists of the search schedule (dense first chunk, thresholded later chunks).
 #include <math_constants.h>
 
 #include <algorithm>
@@ -28,7 +28,7 @@ int32_t kmeans_dev(Ctx* ctx, const float* rows, int64_t n, int32_t dim, int32_t 
 
 namespace {
 
-constexpr int PQ_THREADS = 256;
+constexpr int PQ_THREADS = 512;
 constexpr size_t PQ_SMEM_LIMIT = 200 * 1024;
 
 __device__ __forceinline__ float sqdiff_accum(float acc, float a, float b) {
@@ -114,18 +114,19 @@ struct PqScanArgs {
   CandLists cand;
 };
 
-// grid.x = query tiles * row parts.  Shared memory: tables of the tile's TQ queries + one block of codes.
+// grid.x = query tiles * row parts.  Shared memory holds the tables of the tile's TQ queries; a thread walks rows
+// and reads its row's codes straight from global memory, four segments per 32-bit load when the row length
+// allows (the 512 rows of a CTA's step are one contiguous block of m * 512 bytes).
 template <int TQ, int MODE>
 __global__ void __launch_bounds__(PQ_THREADS) pq_scan_kernel(PqScanArgs a) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
-  float* tab = reinterpret_cast<float*>(smem_raw);                                   // m * ksub * TQ floats (layout below)
-  uint8_t* cds = smem_raw + (size_t)a.m * a.ksub * TQ * sizeof(float);               // [m][PQ_THREADS]
+  float* tab = reinterpret_cast<float*>(smem_raw);   // m * ksub * TQ floats (layout below)
   const int64_t parts = (a.row_end - a.row_begin + a.rows_per_cta - 1) / a.rows_per_cta;
   const int64_t qt = blockIdx.x / parts;
   const int64_t part = blockIdx.x % parts;
   const int64_t p0 = qt * TQ;
   const int entries = a.m * a.ksub;
-  // tables of the tile, interleaved by query; a missing query of the last tile reads as +inf (never appended)
+  // tables of the tile; a missing query of the last tile reads as +inf (never appended)
   for (int t = 0; t < TQ; ++t) {
     const int64_t pos = p0 + t;
     const bool ok = pos < a.nq;
@@ -146,29 +147,22 @@ __global__ void __launch_bounds__(PQ_THREADS) pq_scan_kernel(PqScanArgs a) {
   float thr[TQ];
 #pragma unroll
   for (int t = 0; t < TQ; ++t) thr[t] = (MODE == SCAN_THRESHOLD && p0 + t < a.nq) ? a.cand.thr[p0 + t] : -CUDART_INF_F;
+  __syncthreads();
   const int64_t r_begin = a.row_begin + part * a.rows_per_cta;
   const int64_t r_end = min(a.row_end, r_begin + a.rows_per_cta);
-  for (int64_t r0 = r_begin; r0 < r_end; r0 += PQ_THREADS) {
-    __syncthreads();   // tables written / previous block of codes consumed
-    // this block's codes, transposed: thread t owns row r0 + t
-    const int64_t row = r0 + threadIdx.x;
-    const bool rok = row < r_end;
-    if (rok) {
-      const uint8_t* src = a.codes + row * a.m;
-      for (int s = 0; s < a.m; ++s) cds[s * PQ_THREADS + threadIdx.x] = __ldg(src + s);
-    }
-    __syncthreads();
-    if (!rok) continue;
+  const bool words = (a.m & 3) == 0 && (reinterpret_cast<uintptr_t>(a.codes) & 3) == 0;
+  const size_t group_stride = (size_t)a.ksub * 4;   // floats between the groups of 4 queries of one segment
+  for (int64_t row = r_begin + threadIdx.x; row < r_end; row += PQ_THREADS) {
     float acc[TQ];
 #pragma unroll
     for (int t = 0; t < TQ; ++t) acc[t] = 0.f;
-    for (int s = 0; s < a.m; ++s) {
-      const int c = cds[s * PQ_THREADS + threadIdx.x];
+    // adds one segment's table entries, in segment order (the reference's order of the sum)
+    auto add_segment = [&](int s, int c) {
       if (TQ % 4 == 0) {
         const float* e = tab + ((size_t)s * (TQ / 4) * a.ksub + c) * 4;
 #pragma unroll
         for (int t = 0; t < TQ; t += 4) {
-          const float4 v = *reinterpret_cast<const float4*>(e + (size_t)(t >> 2) * a.ksub * 4);
+          const float4 v = *reinterpret_cast<const float4*>(e + (size_t)(t >> 2) * group_stride);
           acc[t] = __fadd_rn(acc[t], v.x);
           acc[t + 1] = __fadd_rn(acc[t + 1], v.y);
           acc[t + 2] = __fadd_rn(acc[t + 2], v.z);
@@ -179,6 +173,17 @@ __global__ void __launch_bounds__(PQ_THREADS) pq_scan_kernel(PqScanArgs a) {
 #pragma unroll
         for (int t = 0; t < TQ; ++t) acc[t] = __fadd_rn(acc[t], e[t]);
       }
+    };
+    if (words) {
+      const uint32_t* src = reinterpret_cast<const uint32_t*>(a.codes + row * a.m);
+      for (int s4 = 0; s4 < (a.m >> 2); ++s4) {
+        const uint32_t w = __ldg(src + s4);
+#pragma unroll
+        for (int b = 0; b < 4; ++b) add_segment(s4 * 4 + b, (int)((w >> (8 * b)) & 0xffu));
+      }
+    } else {
+      const uint8_t* src = a.codes + row * a.m;
+      for (int s = 0; s < a.m; ++s) add_segment(s, (int)__ldg(src + s));
     }
 #pragma unroll
     for (int t = 0; t < TQ; ++t) {
@@ -213,7 +218,7 @@ int32_t launch_scan_tq(Ctx* ctx, const PqScanArgs& a, int mode, size_t smem, uns
 int pick_tq(int m, int ksub, int64_t nq) {
   const size_t per_query = (size_t)m * ksub * sizeof(float);
   int tq = 16;
-  while (tq > 1 && (tq * per_query + (size_t)m * PQ_THREADS > PQ_SMEM_LIMIT || tq / 2 >= nq)) tq >>= 1;
+  while (tq > 1 && (tq * per_query > PQ_SMEM_LIMIT || tq / 2 >= nq)) tq >>= 1;
   return tq;
 }
 
@@ -221,8 +226,8 @@ int32_t launch_pq_scan(Ctx* ctx, PqScanArgs a, int mode) {
   const int64_t rows = a.row_end - a.row_begin;
   if (rows <= 0 || a.nq <= 0) return VSK_OK;
   const int tq = pick_tq(a.m, a.ksub, a.nq);
-  const size_t smem = (size_t)tq * a.m * a.ksub * sizeof(float) + (size_t)a.m * PQ_THREADS;
-  if (smem > PQ_SMEM_LIMIT + 32 * 1024)
+  const size_t smem = (size_t)tq * a.m * a.ksub * sizeof(float);
+  if (smem > PQ_SMEM_LIMIT)
     return fail(ctx, VSK_ERR_INVALID_BUFFER_SIZE, "one query's distance table (%d x %d floats) does not fit in shared memory", a.m, a.ksub);
   const int64_t qtiles = ceil_div(a.nq, tq);
   // enough row parts to fill the GPU a few times over, each at least 4 096 rows so the table load is amortised
@@ -535,7 +540,7 @@ int32_t vsk_pq_index_create(vsk_ctx* c, int32_t dim, int32_t segments, int32_t c
   *out = nullptr;
   VSK_TRY(check_shape(ctx, dim, segments, codebook_size));
   if (!codebooks) return fail(ctx, VSK_ERR_NOT_TRAINED, "no codebooks: train the quantiser first");
-  if ((size_t)segments * codebook_size * sizeof(float) + (size_t)segments * PQ_THREADS > PQ_SMEM_LIMIT)
+  if ((size_t)segments * codebook_size * sizeof(float) > PQ_SMEM_LIMIT)
     return fail(ctx, VSK_ERR_INVALID_BUFFER_SIZE, "one query's distance table (%d x %d floats) does not fit in shared memory", segments, codebook_size);
   Index* ix = new Index();
   ix->ctx = ctx;
