@@ -44,6 +44,18 @@ int main() {
     return 8;
   } catch (const vsk::ImportFailed&) {
   }
+  // product quantiser: 2 segments of 2 dimensions, 16 codewords; row 1 sits on codewords (3, 5)
+  vsk::ProductQuantizer pq(dev, 4, 2, 4);
+  std::vector<float> cb(2 * 16 * 2);
+  for (size_t i = 0; i < cb.size(); ++i) cb[i] = (float)((i * 7) % 13) - 6.0f + 0.01f * (float)i;
+  pq.setCodebooks(cb);
+  const float pr[] = {cb[0], cb[1], cb[32], cb[33], cb[3 * 2], cb[3 * 2 + 1], cb[32 + 5 * 2], cb[32 + 5 * 2 + 1]};
+  auto codes = pq.encodeBatch(pr, 2);
+  if (codes[0] != 0 || codes[1] != 0 || codes[2] != 3 || codes[3] != 5) return 9;
+  vsk::PQIndex pix(dev, pq);
+  pix.add(codes.data(), 2);
+  auto pr2 = pix.batchSearch(pr + 4, 1, 2);
+  if (pr2.ids[0] != 1 || pr2.distances[0] != 0.0f || pr2.ids[1] != 0) return 10;
   std::puts("ok");
   return 0;
 }

@@ -241,4 +241,75 @@ class ScalarQuantizer {
   bool per_dim_;
 };
 
+// ProductQuantizer (Quantization/ProductQuantizer.swift) with ProductQuantizationConfig's fields; codes are one byte
+// per segment, so codeSize is at most 8.
+class ProductQuantizer {
+ public:
+  ProductQuantizer(std::shared_ptr<CUDAComputeDevice> dev, int32_t dimensions, int32_t segments = 8, int32_t codeSize = 8,
+                   int32_t trainingIterations = 25)
+      : dev_(std::move(dev)), dim_(dimensions), m_(segments), ksub_(1 << codeSize), iters_(trainingIterations) {
+    if (dimensions <= 0 || segments <= 0 || dimensions % segments != 0)
+      throw InvalidInput(VSK_ERR_INVALID_INPUT, "invalid segmentation");          // QuantizationError.invalidSegmentation
+    if (codeSize < 4 || codeSize > 8) throw InvalidInput(VSK_ERR_INVALID_INPUT, "invalid code size");
+  }
+  // train(on:) from initial codewords [segments][codebookSize][dimensions / segments] (nullptr: the first rows' segments)
+  void train(const float* rows, int64_t n, const float* initial = nullptr) {
+    codebooks.resize((size_t)ksub_ * dim_);
+    check(vsk_pq_train(dev_->ctx(), rows, n, dim_, m_, ksub_, iters_, initial, codebooks.data()), dev_->ctx());
+    trained_ = true;
+  }
+  void setCodebooks(std::vector<float> cb) { codebooks = std::move(cb); trained_ = true; }
+  std::vector<uint8_t> encodeBatch(const float* rows, int64_t n) const {
+    need();
+    std::vector<uint8_t> codes((size_t)n * m_);
+    check(vsk_pq_encode(dev_->ctx(), codebooks.data(), dim_, m_, ksub_, rows, n, codes.data()), dev_->ctx());
+    return codes;
+  }
+  std::vector<float> decodeBatch(const uint8_t* codes, int64_t n) const {
+    need();
+    std::vector<float> rows((size_t)n * dim_);
+    check(vsk_pq_decode(dev_->ctx(), codebooks.data(), dim_, m_, ksub_, codes, n, rows.data()), dev_->ctx());
+    return rows;
+  }
+  // precomputeDistanceTables(query:) for a batch: [nq][segments][codebookSize]
+  std::vector<float> precomputeDistanceTables(const float* queries, int64_t nq) const {
+    need();
+    std::vector<float> t((size_t)nq * m_ * ksub_);
+    check(vsk_pq_distance_tables(dev_->ctx(), codebooks.data(), dim_, m_, ksub_, queries, nq, t.data()), dev_->ctx());
+    return t;
+  }
+  int32_t segments() const { return m_; }
+  int32_t codebookSize() const { return ksub_; }
+  int32_t dimensions() const { return dim_; }
+  std::vector<float> codebooks;
+ private:
+  void need() const { if (!trained_) throw NotTrained(VSK_ERR_NOT_TRAINED, "Quantizer must be trained before use"); }
+  std::shared_ptr<CUDAComputeDevice> dev_;
+  int32_t dim_, m_, ksub_, iters_;
+  bool trained_ = false;
+};
+
+// Codes resident on the GPU, searched by asymmetric distance (DistanceTables.computeDistance,
+// ProductQuantizerTypes.swift:14-20): per query the k nearest rows, ascending, ties by row.
+class PQIndex {
+ public:
+  PQIndex(std::shared_ptr<CUDAComputeDevice> dev, const ProductQuantizer& pq) : dev_(std::move(dev)) {
+    check(vsk_pq_index_create(dev_->ctx(), pq.dimensions(), pq.segments(), pq.codebookSize(), pq.codebooks.data(), &ix_), dev_->ctx());
+  }
+  ~PQIndex() { if (ix_) vsk_index_destroy(ix_); }
+  PQIndex(const PQIndex&) = delete;
+  PQIndex& operator=(const PQIndex&) = delete;
+  void add(const uint8_t* codes, int64_t n) { check(vsk_pq_index_add(ix_, codes, n), dev_->ctx()); }
+  int64_t count() const { return vsk_index_size(ix_); }
+  SearchResults batchSearch(const float* queries, int64_t nq, int32_t k) const {
+    SearchResults r; r.nq = nq; r.k = k;
+    r.distances.resize((size_t)nq * k); r.ids.resize((size_t)nq * k);
+    check(vsk_search(ix_, queries, nq, k, nullptr, r.distances.data(), r.ids.data()), dev_->ctx());
+    return r;
+  }
+ private:
+  std::shared_ptr<CUDAComputeDevice> dev_;
+  vsk_index* ix_ = nullptr;
+};
+
 }  // namespace vsk
