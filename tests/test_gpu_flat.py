@@ -347,3 +347,25 @@ def test_cta_pair_kernel_in_subprocess():
     env = dict(os.environ, VSK_TC_PAIR="1")
     out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, timeout=300)
     assert out.returncode == 0 and "pair-ok" in out.stdout, out.stderr[-2000:]
+
+
+def test_distance_matrix_api(vsk, dev, cpu_oracle):
+    """MetalDistanceMatrix.computeDistanceMatrix (MetalDistanceMatrix.swift:49-119): A x B, and A x A with the
+    lower triangle mirrored from the upper one."""
+    import oracle as orc
+    rng = np.random.default_rng(77)
+    a = rng.standard_normal((37, 512)).astype(np.float32)       # the reference's type is Vector512
+    b = rng.standard_normal((53, 512)).astype(np.float32)
+    eng = vsk.CUDAAccelerationEngine(dev)
+    for metric in ("euclidean", "cosine", "manhattan", "dotProduct"):
+        mid = orc.METRIC_IDS[metric]
+        ab = eng.computeDistanceMatrix(a, b, metric)
+        ref = cpu_oracle.batch_distances(mid, a, b)
+        assert ab.shape == (37, 53) and np.allclose(ab, ref, rtol=1e-4, atol=1e-5)
+        aa = eng.computeDistanceMatrix(a, None, metric)
+        ref = cpu_oracle.batch_distances(mid, a, a)
+        assert np.array_equal(aa, aa.T)
+        assert np.allclose(np.triu(aa), np.triu(ref), rtol=1e-4, atol=2e-4)
+    import torch
+    aa = eng.computeDistanceMatrix(torch.as_tensor(a, device="cuda"), None, "euclidean")
+    assert torch.equal(aa, aa.T) and float(aa.diagonal().abs().max()) == 0.0

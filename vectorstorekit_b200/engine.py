@@ -275,6 +275,19 @@ class CUDAAccelerationEngine:
         self.dev.check(self._lib.vsk_batch_distances(self.dev._h, mid, _ptr(q), nq, _ptr(x), nx, d, _ptr(out)))
         return out
 
+    # MetalDistanceMatrix.computeDistanceMatrix(vectorsA:vectorsB:metric:) -> [[Float]]
+    # (Acceleration/Metal/MetalDistanceMatrix.swift:49-119).  With vectorsB omitted the matrix of vectorsA against
+    # itself is returned and, as the reference does (:352-381), the upper triangle (with the diagonal) is what is
+    # computed: the lower triangle is its mirror image.
+    def computeDistanceMatrix(self, vectorsA, vectorsB=None, metric=DistanceMetric.euclidean):
+        out = self.batchComputeDistances(vectorsA, vectorsA if vectorsB is None else vectorsB, metric)
+        if vectorsB is None:
+            if _is_dev(out):
+                out = torch.triu(out) + torch.triu(out, 1).T
+            else:
+                out = np.triu(out) + np.triu(out, 1).T
+        return out
+
     def mergeTopK(self, dist, ids):
         """[G, Q, k] per-shard results with global ids (CUDA tensors) -> merged [Q, k]."""
         g, nq, k = dist.shape
