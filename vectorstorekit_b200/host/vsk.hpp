@@ -162,6 +162,18 @@ class CUDAAccelerationEngine {
     check(vsk_batch_distances(dev_->ctx(), metric_id(metric), q, nq, x, nx, dim, out.data()), dev_->ctx());
     return out;
   }
+  // MetalDistanceMatrix.computeDistanceMatrix(vectorsA:vectorsB:metric:) (MetalDistanceMatrix.swift:49-119), row-major
+  // na x nb; with b == nullptr the matrix of a against itself, lower triangle mirrored from the upper (:352-381)
+  std::vector<float> computeDistanceMatrix(const float* a, int64_t na, const float* b, int64_t nb, int32_t dim,
+                                           DistanceMetric metric) const {
+    if (!b) {
+      std::vector<float> m = batchComputeDistances(a, na, a, na, dim, metric);
+      for (int64_t i = 0; i < na; ++i)
+        for (int64_t j = 0; j < i; ++j) m[(size_t)(i * na + j)] = m[(size_t)(j * na + i)];
+      return m;
+    }
+    return batchComputeDistances(a, na, b, nb, dim, metric);
+  }
   // computeDistances(query:candidates:metric:)
   std::vector<float> computeDistances(const float* query, const float* x, int64_t nx, int32_t dim, DistanceMetric m) const {
     return batchComputeDistances(query, 1, x, nx, dim, m);
