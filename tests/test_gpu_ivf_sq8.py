@@ -132,6 +132,44 @@ def test_ivf_search_vs_oracle(vsk, dev, cpu_oracle, cfg):
     ix.close()
 
 
+@pytest.mark.parametrize("cfg", [(200_000, 64, 512, 32, 10, 2000), (120_000, 128, 300, 20, 100, 1000),
+                                 (60_000, 40, 64, 64, 10, 700)])
+def test_ivf_tensor_list_scan(vsk, dev, cpu_oracle, cfg):
+    """The probed lists scanned on the tensor cores (coarse fp16 values, certificate, exact rerank) against the
+    oracle and against the fp32 list scan; lists are made very uneven (a few centres own most of the rows)."""
+    n, d, nlist, nprobe, k, nq = cfg
+    rng = np.random.default_rng(n + k)
+    centres = rng.standard_normal((nlist, d)).astype(np.float32)
+    w = rng.random(nlist) ** 4
+    w /= w.sum()
+    x = (centres[rng.choice(nlist, n, p=w)] + 0.15 * rng.standard_normal((n, d))).astype(np.float32)
+    q = (centres[rng.choice(nlist, nq, p=w)] + 0.15 * rng.standard_normal((nq, d))).astype(np.float32)
+    ix = vsk.IVFIndex(dev, d, numberOfCentroids=nlist, numberOfProbes=nprobe, maxIterations=4, tolerance=-1.0)
+    ix.train(x, x[:nlist])
+    ix.insert(x)
+    asg = ix.assignments()
+    sizes = np.bincount(asg, minlength=nlist)
+    assert sizes.max() > 3 * max(1, int(np.median(sizes)))            # uneven on purpose
+    before = dev.stats()
+    gd, gi = ix.batchSearch(q, k)
+    after = dev.stats()
+    assert after["tensor_tiles"] > before["tensor_tiles"]              # the tensor path ran
+    assert after["fallback_queries"] - before["fallback_queries"] <= nq // 10
+    rd, ri = cpu_oracle.ivf_search(q, x, ix.centroids, asg, nprobe, k)
+    assert_topk_parity(gd, gi, rd, ri)
+    dev.set_search_path(vsk.PATH_FP32_SCAN)
+    try:
+        fd, fi = ix.batchSearch(q, k)
+    finally:
+        dev.set_search_path(vsk.PATH_TENSOR_RERANK)
+    assert_topk_parity(gd, gi, fd, fi)
+    # device pointers
+    import torch
+    td, ti = ix.batchSearch(torch.as_tensor(q, device="cuda"), k)
+    assert np.array_equal(ti.cpu().numpy(), gi) and np.array_equal(td.cpu().numpy(), gd)
+    ix.close()
+
+
 def test_sq8_codes_bit_exact(vsk, dev, cpu_oracle):
     rng = np.random.default_rng(5)
     x = rng.standard_normal((5000, 37)).astype(np.float32)

@@ -14,6 +14,7 @@
 
 #include "common.cuh"
 #include "tile_core.cuh"
+#include "tensor_scan.cuh"
 
 namespace vsk {
 namespace {
@@ -340,6 +341,12 @@ int32_t ivf_search_positions(Ctx* ctx, Index* ix, const float* q, int64_t npos, 
     VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     for (int64_t i = 0; i < npos; ++i)
       if (flags[i]) bad.push_back((int32_t)i);
+    if (!bad.empty() && sub_dev) {
+      // list positions -> query indices of the caller's batch
+      std::vector<int32_t> sub_h((size_t)npos);
+      VSK_CUDA(ctx, cudaMemcpy(sub_h.data(), sub_dev, (size_t)npos * 4, cudaMemcpyDeviceToHost));
+      for (auto& b : bad) b = sub_h[(size_t)b];
+    }
     if (!bad.empty()) {
       void* p;
       VSK_TRY(scratch(ctx, SLOT_IVF_SUBSET, bad.size() * 4, &p));
@@ -422,6 +429,21 @@ int32_t ivf_search_dev(Index* ix, const float* q, int64_t nq, int32_t k, int32_t
     c.x = ix->centroids;
     c.dim = ix->dim;
     VSK_TRY(fp32_topk(ctx, c, ix->nlist, bn, nullptr, nprobe, 0, (float*)pd, (int64_t*)pi, 0));
+    if (ctx->search_path == VSK_PATH_TENSOR_RERANK && ivf_tensor_applicable(ix, bn, nprobe, k)) {
+      // coarse scan of the probed lists on the tensor cores + exact rerank; what it cannot certify is re-run below
+      std::vector<int32_t> redo;
+      VSK_TRY(ivf_tensor_search(ix, qb, bn, (const int64_t*)pi, nprobe, k, out_dist + b * k, out_ids + b * k, &redo));
+      if (!redo.empty()) {
+        void* p;
+        VSK_TRY(scratch(ctx, SLOT_MISC4, redo.size() * 4, &p));
+        VSK_CUDA(ctx, cudaMemcpyAsync(p, redo.data(), redo.size() * 4, cudaMemcpyHostToDevice, ctx->stream));
+        VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        ctx->stats.fallback_queries += (int64_t)redo.size();
+        VSK_TRY(ivf_search_positions(ctx, ix, qb, (int64_t)redo.size(), (const int32_t*)p, (const int64_t*)pi, nprobe, k,
+                                     out_dist + b * k, out_ids + b * k, false));
+      }
+      continue;
+    }
     VSK_TRY(ivf_search_positions(ctx, ix, qb, bn, nullptr, (const int64_t*)pi, nprobe, k, out_dist + b * k,
                                  out_ids + b * k, false));
   }

@@ -85,6 +85,14 @@ struct TcArgs {
   int32_t row_tile_fastest;   // tile order: 0 = query tile fastest (rows are the operand streamed once),
                               //             1 = row tile fastest (the "queries" are the operand streamed once)
   int32_t* err;               // device error word
+  // Tile-table mode (IVF list scan): the launch walks an explicit list of tiles instead of the full
+  // (query tile) x (row tile) grid, and the "query" operand holds one row per (query, probed list) pair, grouped
+  // by list.  tiles[t] = {first pair, first row, valid rows | in-pilot-window << 30, valid pairs};
+  // pair_info[p] = list position of the pair's query | remainder item << 31 (the rest of a query's nearest list
+  // after the pilot window: such a pair skips the tiles inside the window).
+  const int4* tiles;          // or null
+  int64_t num_tiles;
+  const uint32_t* pair_info;
 };
 
 // ---- PTX wrappers --------------------------------------------------------------------------
@@ -243,6 +251,13 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   // together read the same rows).  In row-tile-fastest order a unit OWNS whole query tiles and walks all their
   // row tiles in turn, so a query's running state (slot count, best key) stays in its thread's registers.
   auto tile_at = [&](int64_t i, int64_t& qt, int64_t& nt) -> bool {
+    if (a.tiles) {   // explicit tile list: nt is the tile's index in the table
+      const int64_t t = unit + i * units;
+      if (t >= a.num_tiles) return false;
+      nt = t;
+      qt = 0;
+      return true;
+    }
     if (a.row_tile_fastest) {
       const int64_t qi = i / ntiles;
       nt = i - qi * ntiles;
@@ -299,8 +314,9 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       for (int64_t i = 0; ok; ++i) {
         int64_t qt, nt;
         if (!tile_at(i, qt, nt)) break;
-        const int32_t qrow = (int32_t)(qt * QT + rank * TM);                       // this CTA's 128 queries
-        const int32_t xrow = (int32_t)(a.row_begin + nt * TN + rank * (TN / CTAS)); // its share of the 256 rows
+        const int32_t qrow = a.tiles ? __ldg(&a.tiles[nt].x) : (int32_t)(qt * QT + rank * TM);   // this CTA's 128 queries
+        const int32_t xrow = a.tiles ? __ldg(&a.tiles[nt].y)
+                                     : (int32_t)(a.row_begin + nt * TN + rank * (TN / CTAS)); // its share of the 256 rows
         for (int kb = 0; kb < a.kblocks; ++kb) {
           if (!mbar_wait(&sm->empty[s], ph ^ 1, sm, a.err, 1)) { ok = false; break; }
           uint8_t* st = sm->ring + s * STAGE_BYTES;
@@ -395,24 +411,51 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     int run_cnt = 0;                 // row-tile-fastest order: keys this thread has stored for its query so far
     float run_bv = CUDART_INF_F;     // ... and its best value / row so far (SCAN_ARGMIN)
     int64_t run_bn = 0;
+    // Tile-table mode: the tile's entry, this lane's pair and its threshold are a chain of three dependent global
+    // loads; they are fetched one tile ahead so the chain overlaps the current tile's work (with short contractions
+    // the epilogue, not the MMA, sets the pace).
+    struct Ahead { int4 e; uint32_t info; float thr; };
+    auto fetch_ahead = [&](int64_t i) {
+      Ahead h{make_int4(0, 0, 0, 0), 0u, -CUDART_INF_F};
+      const int64_t t = unit + i * units;
+      if (a.tiles && t < a.num_tiles) {
+        h.e = __ldg(&a.tiles[t]);
+        if (et < h.e.w) {
+          h.info = __ldg(a.pair_info + h.e.x + et);
+          const bool skip = (h.info >> 31) != 0u && ((h.e.z >> 30) & 1) != 0;
+          if (MODE == SCAN_THRESHOLD && !skip) h.thr = __ldg(a.cand.thr + (h.info & 0x7fffffffu));
+        }
+      }
+      return h;
+    };
+    Ahead ahead = fetch_ahead(0);
     for (;; ++local) {
       int64_t qt, nt;
       if (!ok || !tile_at(local, qt, nt)) break;
       const int acc = (int)(local & 1);
       const uint32_t aph = (uint32_t)((local >> 1) & 1);
-      const int64_t q = qt * QT + rank * TM + et;
+      const Ahead cur = ahead;
+      if (a.tiles) ahead = fetch_ahead(local + 1);
+      int64_t q = qt * QT + rank * TM + et;
       const bool owned = a.row_tile_fastest != 0;
       if (owned && nt == 0) { run_cnt = 0; run_bv = CUDART_INF_F; run_bn = 0; }
-      const int64_t n0 = a.row_begin + nt * TN;
-      const bool qok = q < a.nq;
+      int64_t n0 = a.row_begin + nt * TN;
+      int64_t row_end = a.row_end;
+      bool qok = q < a.nq;
+      if (a.tiles) {
+        n0 = cur.e.y;
+        row_end = (int64_t)cur.e.y + (cur.e.z & 0x3fffffff);
+        qok = et < cur.e.w;
+        q = cur.info & 0x7fffffffu;
+      }
       if (HAS_BETA) {
         // the tile's per-row terms; each warp stages its own copy, so no CTA-wide barrier is needed
         for (int i = lane; i < EPI_COLS; i += 32)
-          sm->beta[acc][ew][i] = (n0 + c0 * 32 + i < a.row_end) ? __ldg(a.beta + n0 + c0 * 32 + i) : 0.f;
+          sm->beta[acc][ew][i] = (n0 + c0 * 32 + i < row_end) ? __ldg(a.beta + n0 + c0 * 32 + i) : 0.f;
         __syncwarp();
       }
       float thr = CUDART_INF_F;
-      if (MODE == SCAN_THRESHOLD && qok) thr = a.cand.thr[q];
+      if (MODE == SCAN_THRESHOLD && qok) thr = a.tiles ? cur.thr : a.cand.thr[q];
       // every lane of the warp must take part in the wait result
       bool got = mbar_wait(&sm->tmem_full[acc], aph, sm, a.err, 4);
       got = __all_sync(0xffffffffu, got);
@@ -476,13 +519,25 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         for (int c = c0; c < c0 + EPI_GROUPS; ++c) {
           float v[32];
           tc_ld32(trow + (uint32_t)(c * 32), v);
-          const int64_t left = a.row_end - (n0 + c * 32);   // columns of this group inside the launch
+          const int64_t left = row_end - (n0 + c * 32);   // columns of this group inside the launch (tile)
+          // Cheap test first: the smallest of the group's 32 values against the threshold.  Most groups of a late
+          // chunk hold no hit for any of the warp's queries and then cost two instructions per value, not five.
+          float vmin = CUDART_INF_F;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            v[j] = HAS_BETA ? fmaf(v[j], alpha, sm->beta[acc][ew][(c - c0) * 32 + j]) : v[j] * alpha;
+            vmin = fminf(vmin, v[j]);
+          }
+          if (left >= 32 && !__any_sync(0xffffffffu, qok && vmin <= thr)) {
+            m[c - c0] = 0u;
+            continue;
+          }
           const uint32_t colmask = left >= 32 ? 0xffffffffu : (left > 0 ? ((1u << (int)left) - 1u) : 0u);
           uint32_t bits = 0;
           float hv = 0.f;   // the value of the (last) hit: all that pass 2 needs when a query has one hit in the group
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
-            const float val = HAS_BETA ? fmaf(v[j], alpha, sm->beta[acc][ew][(c - c0) * 32 + j]) : v[j] * alpha;
+            const float val = v[j];
             const bool hit = val <= thr;
             bits |= hit ? (1u << j) : 0u;
             hv = hit ? val : hv;
@@ -504,7 +559,7 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           const uint32_t bits = m[c - c0];
           const uint32_t colbits = __reduce_or_sync(0xffffffffu, bits);   // columns in which any query has a hit
           if (colbits == 0u) continue;
-          if (!__any_sync(0xffffffffu, (bits & (bits - 1u)) != 0u) && n0 + c * 32 + 32 <= a.row_end) {
+          if (!__any_sync(0xffffffffu, (bits & (bits - 1u)) != 0u) && n0 + c * 32 + 32 <= row_end) {
             // no query has more than one hit in this (whole) group: its value was kept by pass 1
             const uint32_t ok1 = (bits != 0u && base < cap_here) ? 1u : 0u;
             const uint64_t key1 = make_key(mv[c - c0], (uint32_t)(n0 + c * 32 + (__ffs((int)bits) - 1)));
@@ -956,7 +1011,7 @@ int32_t launch_tc(Ctx* ctx, const CUtensorMap& mq, const CUtensorMap& mx, const 
     attr_done[MODE][has_beta][pair] = true;
   }
   const int per_tile = pair ? 2 * TM : TM;
-  const int64_t tiles = ceil_div(a.nq, per_tile) * ceil_div(a.row_end - a.row_begin, TN);
+  const int64_t tiles = a.tiles ? a.num_tiles : ceil_div(a.nq, per_tile) * ceil_div(a.row_end - a.row_begin, TN);
   if (tiles <= 0) return VSK_OK;
   const int sms = ctx->prop.multiProcessorCount;
   unsigned grid = pair ? 2u * (unsigned)std::min<int64_t>(tiles, sms / 2) : (unsigned)std::min<int64_t>(tiles, sms);
@@ -1293,6 +1348,317 @@ int32_t tensor_search(Index* ix, const float* q, int64_t nq, int32_t k, const fl
   return VSK_OK;
 }
 
+
+// ---- IVF list scan on the tensor cores --------------------------------------------------------------
+// The probed lists of a batch, scanned with the same contraction kernel as the flat search.  Every (query, probed
+// list) pair is an item; items are grouped by (stage, list), and the fp16 query operand is gathered in that order,
+// so the queries that probe a list are consecutive rows of the "query" operand and a tile is 128 of them against
+// 256 rows of the list.  The tiles of a launch are listed list by list (a list's rows are read from HBM once).
+// Three launches: a pilot over the first rows of every query's nearest list with no threshold, then the remaining
+// probe ranks in two groups (the rest of the nearest list is an item of the first group).  The kernel filters on
+// the flat path's coarse values (|x|^2 - 2 q.x from fp16 operands); after every launch all listed rows are
+// re-scored exactly and the k best exact values are kept, so thresholds are exact and the filter only has to be
+// loose by the coarse values' error bound: no certificate is needed and the only queries handed back are those
+// whose list overflowed.
+constexpr int kIvfPilotTiles = 4;   // 1 024 rows of the nearest list set the first threshold
+
+// key of item (query, slot): stage * nlist + list, or null_key.  Slot p < nprobe is probe rank p (stage 0 for the
+// nearest list, 1 for ranks below r1, 2 above); slot nprobe is the rest of the nearest list beyond the pilot window.
+__global__ void ivf_item_keys_kernel(const int64_t* __restrict__ probes, int64_t nq, int nprobe, int nlist, int r1,
+                                     const int64_t* __restrict__ list_off, int64_t pilot_rows, int null_key,
+                                     int32_t* __restrict__ keys) {
+  const int slots = nprobe + 1;
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= nq * slots) return;
+  const int64_t pos = i / slots;
+  const int p = (int)(i - pos * slots);
+  int key = null_key;
+  if (p < nprobe) {
+    const int64_t l = probes[pos * nprobe + p];
+    if (l >= 0 && l < nlist) key = (p == 0 ? 0 : (p < r1 ? 1 : 2)) * nlist + (int)l;
+  } else {
+    const int64_t l = probes[pos * nprobe];
+    if (l >= 0 && l < nlist && list_off[l + 1] - list_off[l] > pilot_rows) key = nlist + (int)l;
+  }
+  keys[i] = key;
+}
+
+// per grouped item: its query and whether it is a remainder item; and the item's row of the gathered fp16 operand
+__global__ void ivf_gather_items_kernel(const int32_t* __restrict__ order, int64_t nitems, int slots,
+                                        const __half* __restrict__ q16, int dim16, uint32_t* __restrict__ pair_info,
+                                        __half* __restrict__ g16) {
+  const int64_t i = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (i >= nitems) return;
+  const int item = order[i];
+  const int pos = item / slots;
+  const int lane = threadIdx.x & 31;
+  if (lane == 0) pair_info[i] = (uint32_t)pos | ((item - pos * slots) == slots - 1 ? 0x80000000u : 0u);
+  const uint4* src = reinterpret_cast<const uint4*>(q16 + (int64_t)pos * dim16);
+  uint4* dst = reinterpret_cast<uint4*>(g16 + i * dim16);
+  for (int c = lane; c < dim16 / 8; c += 32) dst[c] = __ldg(src + c);
+}
+
+// tiles of (stage, list): ceil(pairs / 128) x row tiles (the pilot takes only the window)
+__device__ __forceinline__ int ivf_row_tiles(int64_t len, int stage) {
+  const int t = (int)((len + TN - 1) / TN);
+  return stage == 0 ? min(kIvfPilotTiles, t) : t;
+}
+
+__global__ void ivf_tile_count_kernel(const int64_t* __restrict__ pair_off, int stage, int nlist,
+                                      const int64_t* __restrict__ list_off, int64_t* __restrict__ counts) {
+  const int l = blockIdx.x * blockDim.x + threadIdx.x;
+  if (l >= nlist) return;
+  const int64_t pairs = pair_off[(int64_t)stage * nlist + l + 1] - pair_off[(int64_t)stage * nlist + l];
+  counts[l] = ((pairs + TM - 1) / TM) * ivf_row_tiles(list_off[l + 1] - list_off[l], stage);
+}
+
+__global__ void ivf_tile_fill_kernel(const int64_t* __restrict__ pair_off, int stage, int nlist,
+                                     const int64_t* __restrict__ list_off, const int64_t* __restrict__ offsets,
+                                     int4* __restrict__ tiles) {
+  const int l = blockIdx.x;
+  const int64_t pbeg = pair_off[(int64_t)stage * nlist + l], pairs = pair_off[(int64_t)stage * nlist + l + 1] - pbeg;
+  const int64_t beg = list_off[l], len = list_off[l + 1] - beg;
+  const int ptiles = (int)((pairs + TM - 1) / TM), rtiles = ivf_row_tiles(len, stage);
+  int4* out = tiles + offsets[l];
+  for (int i = threadIdx.x; i < ptiles * rtiles; i += blockDim.x) {
+    const int rt = i / ptiles, pt = i - rt * ptiles;
+    const int64_t r0 = (int64_t)rt * TN;
+    out[i] = make_int4((int)(pbeg + (int64_t)pt * TM), (int)(beg + r0),
+                       (int)min((int64_t)TN, len - r0) | ((rt < kIvfPilotTiles ? 1 : 0) << 30),
+                       (int)min((int64_t)TM, pairs - (int64_t)pt * TM));
+  }
+}
+
+// after the exact rerank: a key's row field goes from its storage position to the row's insertion index, so that
+// the final order breaks ties the way the fp32 list scan does
+__global__ void ivf_remap_keys_kernel(CandLists cand, int64_t nq, const int32_t* __restrict__ list_rows) {
+  const int64_t qi = blockIdx.x;
+  const int cnt = min(cand.count[qi], kCandCap);
+  uint64_t* keys = cand.keys + qi * kCandCap;
+  for (int c = threadIdx.x; c < cnt; c += blockDim.x) {
+    const uint64_t key = keys[c];
+    if (key != kEmptyKey) keys[c] = (key & 0xffffffff00000000ull) | (uint32_t)list_rows[(uint32_t)key];
+  }
+}
+
+// Coarse-domain threshold of a query from its exact one.  A row's exact squared distance is |q|^2 + c with
+// c = |x|^2 - 2 q.x, and its coarse value differs from c by at most eps, so every row with exact value <= T has
+// coarse value <= T - |q|^2 + eps; the last term covers fp32 rounding of the quantities being compared.
+// `dropped` (or null): the smallest coarse value the pilot's coarse pre-selection dropped for the query.  The pilot
+// keeps only its best rows by coarse value before the exact re-scoring; that is safe iff everything it dropped lies
+// above the coarse threshold, otherwise the query is flagged for the fp32 list scan.
+__global__ void ivf_coarse_threshold_kernel(const float* __restrict__ thr_exact, const float* __restrict__ qnorm,
+                                            const float* __restrict__ eps, float max_xnorm, int64_t nq,
+                                            float* __restrict__ thr_coarse, const float* __restrict__ dropped,
+                                            int32_t* __restrict__ flags) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= nq) return;
+  const float t = thr_exact[i];
+  float tc = CUDART_INF_F;
+  if (t < CUDART_INF_F) {
+    const float qn2 = qnorm[i] * qnorm[i];
+    tc = (t - qn2) + eps[i] + 2e-6f * (qn2 + max_xnorm * max_xnorm + t);
+  }
+  thr_coarse[i] = tc;
+  if (dropped && dropped[i] <= tc) atomicOr(&flags[i], 2);
+}
+
+// saved[i] = thr[i]; thr[i] = +inf (the next compaction works on exact values and must not inherit a coarse one)
+__global__ void ivf_save_threshold_kernel(float* __restrict__ thr, float* __restrict__ saved, int64_t nq) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= nq) return;
+  saved[i] = thr[i];
+  thr[i] = CUDART_INF_F;
+}
+
+bool ivf_tensor_applicable(const Index* ix, int64_t nq, int32_t nprobe, int32_t k) {
+  return ix->kind == INDEX_IVF && nq >= 2 * TM && k <= kCandCap / 4 && ix->n >= 8 * TN &&
+         (int64_t)nq * (nprobe + 1) < ((int64_t)1 << 30);
+}
+
+int32_t ivf_tensor_search(Index* ix, const float* q, int64_t nq, const int64_t* probes, int32_t nprobe, int32_t k,
+                          float* out_dist, int64_t* out_ids, std::vector<int32_t>* flagged) {
+  Ctx* ctx = ix->ctx;
+  flagged->clear();
+  VSK_TRY(tensor_prepare(ix));
+  const int dim = ix->dim, dim16 = ix->dim16, nlist = ix->nlist;
+  const int32_t keep = k;   // every compaction works on exact values, so no margin is needed
+  void* p;
+
+  // ---- query operands, bound, alpha (euclidean) ----
+  VSK_TRY(scratch(ctx, SLOT_Q16, (size_t)nq * dim16 * sizeof(__half), &p));
+  __half* q16 = (__half*)p;
+  VSK_TRY(scratch(ctx, SLOT_QAUX, (size_t)nq * 4 * sizeof(float) + 64, &p));
+  float* qn16 = (float*)p;
+  float* qe16 = qn16 + nq;
+  float* eps = qe16 + nq;
+  float* qn_tmp = eps + nq;
+  VSK_TRY(scratch(ctx, SLOT_TC_B, 64, &p));
+  unsigned* q_absmax = (unsigned*)p;
+  float* q_scale = (float*)p + 1;
+  float* alpha = (float*)p + 2;
+  int32_t* err = (int32_t*)p + 3;
+  unsigned long long* rr_total = (unsigned long long*)((char*)p + 16);
+  VSK_CUDA(ctx, cudaMemsetAsync(p, 0, 64, ctx->stream));
+  absmax_kernel<<<296, 256, 0, ctx->stream>>>(q, nq * (int64_t)dim, q_absmax);
+  choose_scale_kernel<<<1, 1, 0, ctx->stream>>>(q_absmax, 0, q_scale);
+  ctx->stats.kernel_launches += 2;
+  BoundConsts bc{ix->scale16, ix->max_xnorm16, ix->max_xerr16, ix->max_xnorm, ix->min_xnorm_nz, dim16};
+  launch_prep<VSK_METRIC_EUCLIDEAN>(ctx, q, nq, dim, dim16, q_scale, q16, nullptr, qn16, qe16, qn_tmp, nullptr);
+  bound_kernel<VSK_METRIC_EUCLIDEAN><<<(unsigned)ceil_div(nq, 256), 256, 0, ctx->stream>>>(qn16, qe16, qn_tmp, nq, q_scale, bc, eps, alpha);
+  ctx->stats.kernel_launches++;
+  VSK_CUDA(ctx, cudaGetLastError());
+
+  // ---- stage plan: which probe ranks go with the remainder of the nearest list ----
+  const double mean_len = std::max(1.0, (double)ix->n / (double)nlist);
+  const int64_t pilot_rows = (int64_t)kIvfPilotTiles * TN;
+  // rows one launch may add after the pilot's rows without (plausibly) overflowing a list: the flat schedule's rule.
+  // When all probed lists fit, one launch takes every remaining rank; otherwise the ranks are split in two groups.
+  const double chunk = (double)schedule_chunk(pilot_rows, keep, 0);
+  int r1 = mean_len * nprobe <= chunk ? (int)nprobe : (int)(chunk / 4.0 / mean_len);
+  r1 = std::max(1, std::min(r1, (int)nprobe));
+  const int nstages = r1 < nprobe ? 3 : 2;
+
+  // ---- items grouped by (stage, list); the query operand gathered in that order ----
+  const int slots = nprobe + 1;
+  const int64_t nitems = nq * slots;
+  const int nkeys = 3 * nlist + 1;
+  VSK_TRY(scratch(ctx, SLOT_IVF_KEYS, (size_t)nitems * 4, &p));
+  int32_t* keys = (int32_t*)p;
+  VSK_TRY(scratch(ctx, SLOT_IVF_ORDER, (size_t)nitems * 4, &p));
+  int32_t* order = (int32_t*)p;
+  VSK_TRY(scratch(ctx, SLOT_IVF_PAIR_OFF, (size_t)(nkeys + 1) * 8, &p));
+  int64_t* pair_off = (int64_t*)p;
+  ivf_item_keys_kernel<<<(unsigned)ceil_div(nitems, 256), 256, 0, ctx->stream>>>(probes, nq, nprobe, nlist, r1, ix->list_offsets,
+                                                                              pilot_rows, nkeys - 1, keys);
+  ctx->stats.kernel_launches++;
+  VSK_TRY(launch_stable_group(ctx, keys, nitems, nkeys, order, pair_off));
+  VSK_TRY(scratch(ctx, SLOT_IVF_SUBSET, (size_t)nitems * 4, &p));
+  uint32_t* pair_info = (uint32_t*)p;
+  VSK_TRY(scratch(ctx, SLOT_IVF_STAGES, (size_t)(nitems + TM) * dim16 * sizeof(__half), &p));
+  __half* g16 = (__half*)p;
+  ivf_gather_items_kernel<<<(unsigned)ceil_div(nitems, 8), 256, 0, ctx->stream>>>(order, nitems, slots, q16, dim16, pair_info, g16);
+  ctx->stats.kernel_launches++;
+
+  CUtensorMap mq, mx;
+  VSK_TRY(make_map(ctx, g16, nitems, dim16, TM, &mq));
+  VSK_TRY(make_map(ctx, ix->rows16, ix->n, dim16, TN, &mx));
+
+  CandLists cand;
+  VSK_TRY(scratch(ctx, SLOT_CAND_KEYS, (size_t)nq * kCandCap * sizeof(uint64_t), &p));
+  cand.keys = (uint64_t*)p;
+  VSK_TRY(scratch(ctx, SLOT_CAND_COUNT, (size_t)nq * 4, &p));
+  cand.count = (int32_t*)p;
+  VSK_TRY(scratch(ctx, SLOT_CAND_THR, (size_t)nq * 4, &p));
+  cand.thr = (float*)p;
+  VSK_TRY(scratch(ctx, SLOT_CAND_FLAGS, (size_t)nq * 4, &p));
+  cand.flags = (int32_t*)p;
+  cand.nq = nq;
+  VSK_TRY(launch_init_cand(ctx, cand, nq));
+
+  // the kernel filters on coarse values: it sees the lists with a coarse threshold derived from the exact one
+  VSK_TRY(scratch(ctx, SLOT_TC_D, (size_t)nq * sizeof(float), &p));
+  float* thr_coarse = (float*)p;
+  CandLists cand_coarse = cand;
+  cand_coarse.thr = thr_coarse;
+  VSK_TRY(scratch(ctx, SLOT_TC_C, (size_t)nq * sizeof(float), &p));
+  float* pilot_dropped = (float*)p;
+  const int32_t pilot_keep = std::min<int32_t>(1024, std::max(8 * k, 256));
+  TcArgs a{};
+  a.nq = nq;
+  a.kblocks = dim16 / TK;
+  a.mode = SCAN_THRESHOLD;
+  a.alpha = alpha;
+  a.beta = ix->row_aux;
+  a.cand = cand_coarse;
+  a.cap = kCandCap;
+  a.err = err;
+  a.pair_info = pair_info;
+  SelectArgs sel{};
+  sel.cand = cand;
+  sel.nq = nq;
+  sel.keep = keep;
+  sel.dense_count = -1;
+  sel.k = k;
+  const size_t qsm = (size_t)dim * sizeof(float);
+  if (qsm > 48 * 1024) return fail(ctx, VSK_ERR_INVALID_BUFFER_SIZE, "dimension %d is too large for the rerank kernel", dim);
+  const unsigned qgrid = (unsigned)ceil_div(nq, 256);
+
+  void *cnt_p, *off_p;
+  VSK_TRY(scratch(ctx, SLOT_IVF_ITEM_CNT, (size_t)(nlist + 1) * 8, &cnt_p));
+  VSK_TRY(scratch(ctx, SLOT_IVF_ITEM_OFF, (size_t)(nlist + 1) * 8, &off_p));
+  for (int stage = 0; stage < nstages; ++stage) {
+    ivf_tile_count_kernel<<<(unsigned)ceil_div(nlist, 256), 256, 0, ctx->stream>>>(pair_off, stage, nlist, ix->list_offsets, (int64_t*)cnt_p);
+    VSK_TRY(launch_scan_i64(ctx, (const int64_t*)cnt_p, nlist, (int64_t*)off_p));
+    int64_t total = 0;
+    VSK_CUDA(ctx, cudaMemcpyAsync(&total, (int64_t*)off_p + nlist, 8, cudaMemcpyDeviceToHost, ctx->stream));
+    VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    ctx->stats.kernel_launches += 2;
+    if (total <= 0) continue;
+    if (total > 0x7fffffffLL) return fail(ctx, VSK_ERR_INVALID_BUFFER_SIZE, "too many list tiles in one launch");
+    VSK_TRY(scratch(ctx, SLOT_X_TMP, (size_t)total * sizeof(int4), &p));
+    ivf_tile_fill_kernel<<<(unsigned)nlist, 128, 0, ctx->stream>>>(pair_off, stage, nlist, ix->list_offsets, (const int64_t*)off_p, (int4*)p);
+    ivf_coarse_threshold_kernel<<<qgrid, 256, 0, ctx->stream>>>(cand.thr, qn_tmp, eps, ix->max_xnorm, nq, thr_coarse,
+                                                                nullptr, cand.flags);
+    ctx->stats.kernel_launches += 2;
+    a.tiles = (const int4*)p;
+    a.num_tiles = total;
+    VSK_TRY(launch_tc<SCAN_THRESHOLD>(ctx, mq, mx, a, true, false));
+    if (stage == 0) {
+      // the pilot appended up to 1 024 rows per query: keep the best few by coarse value and re-score only those
+      SelectArgs pre = sel;
+      pre.keep = pilot_keep;
+      pre.max_count = (int32_t)pilot_rows;
+      VSK_TRY(launch_select(ctx, pre));
+      ivf_save_threshold_kernel<<<qgrid, 256, 0, ctx->stream>>>(cand.thr, pilot_dropped, nq);
+      ctx->stats.kernel_launches++;
+    }
+    // exact values for everything in the lists (the keys kept so far are re-scored too: at most k of them),
+    // then the k best exact values stay and the k-th becomes the query's exact threshold
+    rerank_kernel<VSK_METRIC_EUCLIDEAN><<<(unsigned)nq, 256, qsm, ctx->stream>>>(q, ix->rows, dim, nullptr, nullptr, cand, rr_total);
+    ctx->stats.kernel_launches++;
+    sel.max_count = stage == 0 ? pilot_keep : kCandCap;
+    VSK_TRY(launch_select(ctx, sel));
+    if (stage == 0) {
+      // was the coarse pre-selection safe?  (also refreshes the coarse thresholds, which the next launch recomputes)
+      ivf_coarse_threshold_kernel<<<qgrid, 256, 0, ctx->stream>>>(cand.thr, qn_tmp, eps, ix->max_xnorm, nq, thr_coarse,
+                                                                  pilot_dropped, cand.flags);
+      ctx->stats.kernel_launches++;
+    }
+  }
+
+  // ---- ids back to insertion order, final order ----
+  ivf_remap_keys_kernel<<<(unsigned)nq, 128, 0, ctx->stream>>>(cand, nq, ix->list_rows);
+  ctx->stats.kernel_launches++;
+  VSK_CUDA(ctx, cudaGetLastError());
+  SelectArgs fin{};
+  fin.cand = cand;
+  fin.nq = nq;
+  fin.dense_count = -1;
+  fin.keep = k;
+  fin.out_dist = out_dist;
+  fin.out_ids = out_ids;
+  fin.k = k;
+  fin.metric = VSK_METRIC_EUCLIDEAN;
+  fin.id_base = ix->id_base;
+  fin.final_sqrt = 1;
+  fin.max_count = keep;
+  VSK_TRY(launch_select(ctx, fin));
+
+  std::vector<int32_t> flags((size_t)nq);
+  int32_t herr = 0;
+  unsigned long long hrr = 0;
+  VSK_CUDA(ctx, cudaMemcpyAsync(flags.data(), cand.flags, nq * 4, cudaMemcpyDeviceToHost, ctx->stream));
+  VSK_CUDA(ctx, cudaMemcpyAsync(&herr, err, 4, cudaMemcpyDeviceToHost, ctx->stream));
+  VSK_CUDA(ctx, cudaMemcpyAsync(&hrr, rr_total, 8, cudaMemcpyDeviceToHost, ctx->stream));
+  VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  ctx->stats.reranked_rows += (int64_t)hrr;
+  if (herr != 0)
+    return fail(ctx, VSK_ERR_TIMEOUT, "tensor-core scan: a bounded pipeline wait ran out (role %d)", herr);
+  for (int64_t i = 0; i < nq; ++i)
+    if (flags[i]) flagged->push_back((int32_t)i);
+  return VSK_OK;
+}
 
 // ---- public: tensor-core nearest-centroid assignment (used by kmeans.cu) ---------------------------
 int32_t tensor_assign_prepare(Ctx* ctx, const float* rows, int64_t n, int32_t dim, TensorAssign* ta) {

@@ -11,6 +11,13 @@ namespace vsk {
 // q: [nq][dim] device; qnorm: |q| per query (cosine) or null; outputs device [nq][k].
 int32_t tensor_search(Index* ix, const float* q, int64_t nq, int32_t k, const float* qnorm,
                       float* out_dist, int64_t* out_ids);
+// The probed lists of an IVF index scanned on the tensor cores (coarse values, certificate, exact rerank).
+// probes: [nq][nprobe] device, nearest list first.  Results go to out_dist / out_ids for every query; the queries
+// whose result could not be certified (or whose candidate list overflowed) are returned in `flagged` for the
+// caller to re-run on the fp32 list scan.
+bool ivf_tensor_applicable(const Index* ix, int64_t nq, int32_t nprobe, int32_t k);
+int32_t ivf_tensor_search(Index* ix, const float* q, int64_t nq, const int64_t* probes, int32_t nprobe, int32_t k,
+                          float* out_dist, int64_t* out_ids, std::vector<int32_t>* flagged);
 // Drops the fp16 operand copy after rows were added.
 void tensor_invalidate(Index* ix);
 
