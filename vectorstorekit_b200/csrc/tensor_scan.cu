@@ -311,11 +311,17 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       uint32_t issued = 0;       // bit s: a copy into stage s was issued ...
       uint32_t issued_ph = 0;    // ... with this full-barrier parity
       bool ok = true;
+      // tile-table mode: the entry of the next tile is loaded while this tile's copies are issued, so that the
+      // table look-up (a global load) is not on the producer's critical path
+      int4 entry_next = make_int4(0, 0, 0, 0);
+      if (a.tiles && unit < a.num_tiles) entry_next = __ldg(&a.tiles[unit]);
       for (int64_t i = 0; ok; ++i) {
         int64_t qt, nt;
         if (!tile_at(i, qt, nt)) break;
-        const int32_t qrow = a.tiles ? __ldg(&a.tiles[nt].x) : (int32_t)(qt * QT + rank * TM);   // this CTA's 128 queries
-        const int32_t xrow = a.tiles ? __ldg(&a.tiles[nt].y)
+        const int4 entry = entry_next;
+        if (a.tiles && nt + units < a.num_tiles) entry_next = __ldg(&a.tiles[nt + units]);
+        const int32_t qrow = a.tiles ? entry.x : (int32_t)(qt * QT + rank * TM);   // this CTA's 128 queries
+        const int32_t xrow = a.tiles ? entry.y
                                      : (int32_t)(a.row_begin + nt * TN + rank * (TN / CTAS)); // its share of the 256 rows
         for (int kb = 0; kb < a.kblocks; ++kb) {
           if (!mbar_wait(&sm->empty[s], ph ^ 1, sm, a.err, 1)) { ok = false; break; }
@@ -448,11 +454,26 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         qok = et < cur.e.w;
         q = cur.info & 0x7fffffffu;
       }
+      // The tile's per-row terms; each warp stages its own copy, so no CTA-wide barrier is needed.  The first tile
+      // loads them directly; after that they are fetched one tile ahead into registers (the loads fly while this
+      // tile is processed) and stored to the other buffer at the end of the iteration.
+      float beta_next[EPI_COLS / 32];
       if (HAS_BETA) {
-        // the tile's per-row terms; each warp stages its own copy, so no CTA-wide barrier is needed
-        for (int i = lane; i < EPI_COLS; i += 32)
-          sm->beta[acc][ew][i] = (n0 + c0 * 32 + i < row_end) ? __ldg(a.beta + n0 + c0 * 32 + i) : 0.f;
-        __syncwarp();
+        if (local == 0) {
+          for (int i = lane; i < EPI_COLS; i += 32)
+            sm->beta[acc][ew][i] = (n0 + c0 * 32 + i < row_end) ? __ldg(a.beta + n0 + c0 * 32 + i) : 0.f;
+          __syncwarp();
+        }
+        int64_t nqt, nnt, nn0 = 0, nrow_end = 0;
+        if (tile_at(local + 1, nqt, nnt)) {
+          if (a.tiles) { nn0 = ahead.e.y; nrow_end = (int64_t)ahead.e.y + (ahead.e.z & 0x3fffffff); }
+          else { nn0 = a.row_begin + nnt * TN; nrow_end = a.row_end; }
+        }
+#pragma unroll
+        for (int i = 0; i < EPI_COLS / 32; ++i) {
+          const int64_t r = nn0 + c0 * 32 + lane + 32 * i;
+          beta_next[i] = r < nrow_end ? __ldg(a.beta + r) : 0.f;
+        }
       }
       float thr = CUDART_INF_F;
       if (MODE == SCAN_THRESHOLD && qok) thr = a.tiles ? cur.thr : a.cand.thr[q];
@@ -605,6 +626,10 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           if (nt == ntiles - 1 && qok)
             reinterpret_cast<unsigned short*>(a.cand.count)[q * 2 + (ew >> 2)] = (unsigned short)min(run_cnt, 65535);
         }
+      }
+      if (HAS_BETA) {
+#pragma unroll
+        for (int i = 0; i < EPI_COLS / 32; ++i) sm->beta[acc ^ 1][ew][lane + 32 * i] = beta_next[i];
       }
       tc_fence_before();
       __syncwarp();
@@ -874,27 +899,43 @@ __global__ void __launch_bounds__(256) rerank_kernel(const float* __restrict__ q
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
   const float qn = (METRIC == VSK_METRIC_COSINE) ? qnorm[qi] : 0.f;
-  for (int c = warp; c < cnt; c += nwarps) {
-    const uint32_t id = (uint32_t)keys[c];
-    const float* xr = x + (int64_t)id * dim;
-    float s = 0.f;
+  // four candidate rows per warp step: their key loads and row loads are independent chains, which is what keeps
+  // enough bytes in flight when a row is only a few hundred bytes
+  constexpr int RR = 4;
+  for (int c0 = warp * RR; c0 < cnt; c0 += nwarps * RR) {
+    uint32_t id[RR];
+    const float* xr[RR];
+    float s[RR];
+#pragma unroll
+    for (int r = 0; r < RR; ++r) {
+      id[r] = c0 + r < cnt ? (uint32_t)keys[c0 + r] : 0u;
+      xr[r] = x + (int64_t)id[r] * dim;
+      s[r] = 0.f;
+    }
     for (int i = lane; i < dim; i += 32) {
-      const float xv = __ldg(xr + i), qv = qs[i];
-      if (METRIC == VSK_METRIC_EUCLIDEAN) {
-        const float d = qv - xv;
-        s = fmaf(d, d, s);
-      } else {
-        s = fmaf(qv, xv, s);
+      const float qv = qs[i];
+#pragma unroll
+      for (int r = 0; r < RR; ++r) {
+        const float xv = __ldg(xr[r] + i);
+        if (METRIC == VSK_METRIC_EUCLIDEAN) {
+          const float d = qv - xv;
+          s[r] = fmaf(d, d, s[r]);
+        } else {
+          s[r] = fmaf(qv, xv, s[r]);
+        }
       }
     }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    if (lane == 0) {
-      float v;
-      if (METRIC == VSK_METRIC_COSINE) v = 1.0f - s / (qn * xnorm[id] + 1e-8f);
-      else if (METRIC == VSK_METRIC_DOT_PRODUCT) v = -s;
-      else v = s;
-      keys[c] = make_key(v, id);
+    for (int r = 0; r < RR; ++r) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) s[r] += __shfl_xor_sync(0xffffffffu, s[r], o);
+      if (lane == 0 && c0 + r < cnt) {
+        float v;
+        if (METRIC == VSK_METRIC_COSINE) v = 1.0f - s[r] / (qn * xnorm[id[r]] + 1e-8f);
+        else if (METRIC == VSK_METRIC_DOT_PRODUCT) v = -s[r];
+        else v = s[r];
+        keys[c0 + r] = make_key(v, id[r]);
+      }
     }
   }
 }
