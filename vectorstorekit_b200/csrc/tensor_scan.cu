@@ -49,19 +49,27 @@ template <int CTAS> struct Geo {
   static constexpr int STAGES = RING_BYTES / STAGE_BYTES;
   static constexpr int TX_BYTES = STAGE_BYTES * CTAS;   // bytes that complete a stage's full barrier
 };
-constexpr int TC_THREADS = 320;        // warp 0 producer, warp 1 MMA issuer, warps 2..9 epilogue
-constexpr int EPI_WARPS = 8;           // two per tensor-memory lane quarter: each takes half of the tile's columns
-constexpr int EPI_COLS = TN / 2;       // columns per epilogue warp
-constexpr int EPI_GROUPS = EPI_COLS / 32;
+// Warp 0 is the TMA producer, warp 1 the MMA issuer, then EW epilogue warps: EW / 4 per tensor-memory lane quarter,
+// each taking one of EW / 4 equal parts of the tile's columns.  EW = 8 for long contractions (the epilogue hides
+// behind the MMAs, and fewer warps cost less issue and power); EW = 16 for short ones (d <= 256), where a tile's
+// MMAs take about a microsecond and the epilogue warps' serial chain of tensor-memory loads sets the pace.
+template <int EW> struct Epi {
+  static constexpr int WARPS = EW;
+  static constexpr int PARTS = EW / 4;
+  static constexpr int COLS = TN / PARTS;      // columns per epilogue warp
+  static constexpr int GROUPS = COLS / 32;
+  static constexpr int THREADS = 64 + 32 * EW;
+};
 constexpr uint32_t WAIT_LIMIT = 1u << 23;
 constexpr int TMEM_COLS = 512;
 
-struct TcSmem {
+template <int EW>
+struct TcSmemT {
   // stage buffers first: each must start on a 1024-byte boundary for the 128B swizzle
   uint8_t ring[RING_BYTES];
-  float beta[2][EPI_WARPS][EPI_COLS];   // per accumulator buffer and epilogue warp: its columns' per-row terms
-  uint32_t masks[EPI_WARPS * 32][EPI_GROUPS + 1];  // per epilogue thread: pass bits of its 128 values (padded row)
-  float hitval[EPI_WARPS * 32][EPI_GROUPS + 1];    // ... and per group the value of its last hit
+  float beta[2][EW][Epi<EW>::COLS];   // per accumulator buffer and epilogue warp: its columns' per-row terms
+  uint32_t masks[EW * 32][Epi<EW>::GROUPS + 1];  // per epilogue thread: pass bits of its values (padded row)
+  float hitval[EW * 32][Epi<EW>::GROUPS + 1];    // ... and per group the value of its last hit
   uint64_t full[MAX_STAGES];
   uint64_t empty[MAX_STAGES];
   uint64_t tmem_full[2];
@@ -70,7 +78,7 @@ struct TcSmem {
   uint32_t tmem_base;
   volatile int abort_flag;
 };
-constexpr size_t TC_SMEM_BYTES = sizeof(TcSmem) + 1024;  // + alignment slack
+template <int EW> constexpr size_t tc_smem_bytes() { return sizeof(TcSmemT<EW>) + 1024; }   // + alignment slack
 
 struct TcArgs {
   int64_t nq;                 // queries (list positions)
@@ -93,6 +101,7 @@ struct TcArgs {
   const int4* tiles;          // or null
   int64_t num_tiles;
   const uint32_t* pair_info;
+  const float* pair_thr;      // [pairs] coarse threshold of the pair's query for this launch
 };
 
 // ---- PTX wrappers --------------------------------------------------------------------------
@@ -120,15 +129,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 // Bounded wait.  Returns false (and raises the abort flag and the error word) when the limit runs out
 // or another role has already aborted.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, TcSmem* sm, int32_t* err, int code) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int32_t* err, int code) {
   for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if (it > 64) {
-      if ((it & 63) == 0 && sm->abort_flag) return false;
+      if ((it & 63) == 0 && *abort_flag) return false;
       __nanosleep(64);
     }
   }
-  sm->abort_flag = 1;
+  *abort_flag = 1;
   atomicCAS(err, 0, code);
   return false;
 }
@@ -229,13 +238,15 @@ constexpr uint32_t kIdesc = (1u << 4) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t
 // the pair's instruction: M = 256 (128 rows in each CTA's tensor memory), N = 256
 constexpr uint32_t kIdescPair = (1u << 4) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)((2 * TM) >> 4) << 24);
 
-template <int MODE, bool HAS_BETA, int CTAS>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+template <int MODE, bool HAS_BETA, int CTAS, int EW>
+__global__ void __launch_bounds__(Epi<EW>::THREADS, 1)
 tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_x, TcArgs a) {
   using G = Geo<CTAS>;
   constexpr int STAGES = G::STAGES;
   constexpr int STAGE_BYTES = G::STAGE_BYTES;
   extern __shared__ uint8_t smem_raw[];
+  using TcSmem = TcSmemT<EW>;
+  constexpr int EPI_WARPS = EW, EPI_COLS = Epi<EW>::COLS, EPI_GROUPS = Epi<EW>::GROUPS, EPI_PARTS = Epi<EW>::PARTS;
   TcSmem* sm = reinterpret_cast<TcSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // a pair shares tiles: `unit` counts single CTAs (CTAS = 1) or pairs (CTAS = 2); `rank` is the CTA's place in its pair
@@ -324,7 +335,7 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         const int32_t xrow = a.tiles ? entry.y
                                      : (int32_t)(a.row_begin + nt * TN + rank * (TN / CTAS)); // its share of the 256 rows
         for (int kb = 0; kb < a.kblocks; ++kb) {
-          if (!mbar_wait(&sm->empty[s], ph ^ 1, sm, a.err, 1)) { ok = false; break; }
+          if (!mbar_wait(&sm->empty[s], ph ^ 1, &sm->abort_flag, a.err, 1)) { ok = false; break; }
           uint8_t* st = sm->ring + s * STAGE_BYTES;
           if (CTAS == 2) {
             // the leader's full barrier counts the bytes of both CTAs
@@ -365,11 +376,11 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         if (!ok || !tile_at(local, qt_unused, nt_unused)) break;
         const int acc = (int)(local & 1);
         const uint32_t aph = (uint32_t)((local >> 1) & 1);
-        if (!mbar_wait(&sm->tmem_empty[acc], aph ^ 1, sm, a.err, 2)) { ok = false; break; }
+        if (!mbar_wait(&sm->tmem_empty[acc], aph ^ 1, &sm->abort_flag, a.err, 2)) { ok = false; break; }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + (uint32_t)(acc * TN);
         for (int kb = 0; kb < a.kblocks; ++kb) {
-          if (!mbar_wait(&sm->full[s], ph, sm, a.err, 3)) { ok = false; break; }
+          if (!mbar_wait(&sm->full[s], ph, &sm->abort_flag, a.err, 3)) { ok = false; break; }
           tc_fence_after();
           const uint64_t adesc = make_desc(smem_u32(sm->ring + s * STAGE_BYTES));
           const uint64_t bdesc = make_desc(smem_u32(sm->ring + s * STAGE_BYTES + A_BYTES));
@@ -410,49 +421,58 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     const int quarter = warp & 3;                 // tensor-memory lanes this warp may read
     const int et = quarter * 32 + lane;           // row of the tile owned by this thread
     const int ew = warp - 2;                      // epilogue warp 0..7
-    const int c0 = (ew >> 2) * EPI_GROUPS;        // first 32-column group of this warp's half
+    const int part = ew >> 2;                     // which part of the tile's columns this warp takes
+    const int c0 = part * EPI_GROUPS;             // first 32-column group of that part
     const float alpha = __ldg(a.alpha);
     int64_t local = 0;
     bool ok = true;
     int run_cnt = 0;                 // row-tile-fastest order: keys this thread has stored for its query so far
     float run_bv = CUDART_INF_F;     // ... and its best value / row so far (SCAN_ARGMIN)
     int64_t run_bn = 0;
-    // Tile-table mode: the tile's entry, this lane's pair and its threshold are a chain of three dependent global
-    // loads; they are fetched one tile ahead so the chain overlaps the current tile's work (with short contractions
-    // the epilogue, not the MMA, sets the pace).
+    // Tile-table mode: the tile's entry, then this lane's pair and threshold (both indexed by the entry), are a
+    // chain of dependent global loads.  The chain is pipelined over the tiles: the entry is loaded two tiles ahead,
+    // the pair and threshold one tile ahead, so neither load is waited for (with short contractions the epilogue,
+    // not the MMA, sets the pace).  pair_info / pair_thr are padded by one tile, so the loads need no bounds test.
     struct Ahead { int4 e; uint32_t info; float thr; };
-    auto fetch_ahead = [&](int64_t i) {
-      Ahead h{make_int4(0, 0, 0, 0), 0u, -CUDART_INF_F};
+    auto entry_at = [&](int64_t i) {
       const int64_t t = unit + i * units;
-      if (a.tiles && t < a.num_tiles) {
-        h.e = __ldg(&a.tiles[t]);
-        if (et < h.e.w) {
-          h.info = __ldg(a.pair_info + h.e.x + et);
-          const bool skip = (h.info >> 31) != 0u && ((h.e.z >> 30) & 1) != 0;
-          if (MODE == SCAN_THRESHOLD && !skip) h.thr = __ldg(a.cand.thr + (h.info & 0x7fffffffu));
-        }
+      return (a.tiles && t < a.num_tiles) ? __ldg(&a.tiles[t]) : make_int4(0, 0, 0, 0);
+    };
+    auto pair_at = [&](const int4& e) {
+      Ahead h{e, 0u, -CUDART_INF_F};
+      if (a.tiles) {
+        h.info = __ldg(a.pair_info + e.x + et);
+        if (MODE == SCAN_THRESHOLD) h.thr = __ldg(a.pair_thr + e.x + et);
       }
       return h;
     };
-    Ahead ahead = fetch_ahead(0);
+    Ahead ahead = pair_at(entry_at(0));
+    int4 entry_next = entry_at(1);
     for (;; ++local) {
       int64_t qt, nt;
       if (!ok || !tile_at(local, qt, nt)) break;
       const int acc = (int)(local & 1);
       const uint32_t aph = (uint32_t)((local >> 1) & 1);
       const Ahead cur = ahead;
-      if (a.tiles) ahead = fetch_ahead(local + 1);
+      if (a.tiles) {
+        ahead = pair_at(entry_next);
+        entry_next = entry_at(local + 2);
+      }
       int64_t q = qt * QT + rank * TM + et;
       const bool owned = a.row_tile_fastest != 0;
       if (owned && nt == 0) { run_cnt = 0; run_bv = CUDART_INF_F; run_bn = 0; }
       int64_t n0 = a.row_begin + nt * TN;
       int64_t row_end = a.row_end;
       bool qok = q < a.nq;
+      float thr_tile = -CUDART_INF_F;
       if (a.tiles) {
         n0 = cur.e.y;
         row_end = (int64_t)cur.e.y + (cur.e.z & 0x3fffffff);
         qok = et < cur.e.w;
         q = cur.info & 0x7fffffffu;
+        // a remainder item (the rest of a query's nearest list) skips the tiles inside the pilot window
+        const bool skip = (cur.info >> 31) != 0u && ((cur.e.z >> 30) & 1) != 0;
+        if (qok && !skip) thr_tile = cur.thr;
       }
       // The tile's per-row terms; each warp stages its own copy, so no CTA-wide barrier is needed.  The first tile
       // loads them directly; after that they are fetched one tile ahead into registers (the loads fly while this
@@ -476,9 +496,9 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         }
       }
       float thr = CUDART_INF_F;
-      if (MODE == SCAN_THRESHOLD && qok) thr = a.tiles ? cur.thr : a.cand.thr[q];
+      if (MODE == SCAN_THRESHOLD && qok) thr = a.tiles ? thr_tile : a.cand.thr[q];
       // every lane of the warp must take part in the wait result
-      bool got = mbar_wait(&sm->tmem_full[acc], aph, sm, a.err, 4);
+      bool got = mbar_wait(&sm->tmem_full[acc], aph, &sm->abort_flag, a.err, 4);
       got = __all_sync(0xffffffffu, got);
       if (!got) { ok = false; break; }
       tc_fence_after();
@@ -572,7 +592,7 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         // columns appends to its own half of the query's list, counted in a register; the two 16-bit counts are
         // stored after the last row tile.
         int base = 0;
-        const int cap_here = owned ? a.cap / 2 : a.cap;
+        const int cap_here = owned ? a.cap / EPI_PARTS : a.cap;
         if (owned) base = run_cnt;
         else if (cnt) base = atomicAdd(&a.cand.count[q], cnt);
 #pragma unroll 1
@@ -584,7 +604,7 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             // no query has more than one hit in this (whole) group: its value was kept by pass 1
             const uint32_t ok1 = (bits != 0u && base < cap_here) ? 1u : 0u;
             const uint64_t key1 = make_key(mv[c - c0], (uint32_t)(n0 + c * 32 + (__ffs((int)bits) - 1)));
-            uint64_t* d1 = a.cand.keys + q * a.cap + (owned ? (ew >> 2) * cap_here : 0) + base;
+            uint64_t* d1 = a.cand.keys + q * a.cap + (owned ? part * cap_here : 0) + base;
             asm volatile(
                 "{\n\t.reg .pred p;\n\t"
                 "setp.ne.u32 p, %2, 0;\n\t"
@@ -597,7 +617,7 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           float v[32];
           tc_ld32(trow + (uint32_t)(c * 32), v);
           const int64_t nc = n0 + c * 32;
-          uint64_t* dst = a.cand.keys + q * a.cap + (owned ? (ew >> 2) * cap_here : 0) + base;
+          uint64_t* dst = a.cand.keys + q * a.cap + (owned ? part * cap_here : 0) + base;
           // Straight-line code with predicated stores: a branch around every store makes the warp wait out each
           // store's address chain in turn (measured: four times the cost of this form at 1 hit in 150 values).
           // Only whole octets of columns without any hit are skipped, on a warp-uniform test.
@@ -624,7 +644,7 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         if (owned) {
           run_cnt += cnt;
           if (nt == ntiles - 1 && qok)
-            reinterpret_cast<unsigned short*>(a.cand.count)[q * 2 + (ew >> 2)] = (unsigned short)min(run_cnt, 65535);
+            reinterpret_cast<unsigned char*>(a.cand.count)[q * 4 + part] = (unsigned char)min(run_cnt, 255);
         }
       }
       if (HAS_BETA) {
@@ -1041,15 +1061,16 @@ int32_t tensor_prepare(Index* ix) {
 
 // Launches the scan over tiles.  pair = true: clusters of two CTAs (tcgen05 cta_group::2); `mx` must then be a
 // tensor map with 128-row boxes (each CTA stages half of a 256-row tile).
-template <int MODE>
-int32_t launch_tc(Ctx* ctx, const CUtensorMap& mq, const CUtensorMap& mx, const TcArgs& a, bool has_beta, bool pair) {
-  static bool attr_done[4][2][2] = {};
+template <int MODE, int EW>
+int32_t launch_tc_ew(Ctx* ctx, const CUtensorMap& mq, const CUtensorMap& mx, const TcArgs& a, bool has_beta, bool pair) {
+  static bool attr_done[2][2] = {};
   void (*kern)(CUtensorMap, CUtensorMap, TcArgs) =
-      pair ? (has_beta ? tc_scan_kernel<MODE, true, 2> : tc_scan_kernel<MODE, false, 2>)
-           : (has_beta ? tc_scan_kernel<MODE, true, 1> : tc_scan_kernel<MODE, false, 1>);
-  if (!attr_done[MODE][has_beta][pair]) {
-    VSK_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_BYTES));
-    attr_done[MODE][has_beta][pair] = true;
+      pair ? (has_beta ? tc_scan_kernel<MODE, true, 2, EW> : tc_scan_kernel<MODE, false, 2, EW>)
+           : (has_beta ? tc_scan_kernel<MODE, true, 1, EW> : tc_scan_kernel<MODE, false, 1, EW>);
+  constexpr size_t smem = tc_smem_bytes<EW>();
+  if (!attr_done[has_beta][pair]) {
+    VSK_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    attr_done[has_beta][pair] = true;
   }
   const int per_tile = pair ? 2 * TM : TM;
   const int64_t tiles = a.tiles ? a.num_tiles : ceil_div(a.nq, per_tile) * ceil_div(a.row_end - a.row_begin, TN);
@@ -1060,8 +1081,8 @@ int32_t launch_tc(Ctx* ctx, const CUtensorMap& mq, const CUtensorMap& mx, const 
   if (pair) {
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(TC_THREADS);
-    cfg.dynamicSmemBytes = TC_SMEM_BYTES;
+    cfg.blockDim = dim3(Epi<EW>::THREADS);
+    cfg.dynamicSmemBytes = smem;
     cfg.stream = ctx->stream;
     cudaLaunchAttribute at[1];
     at[0].id = cudaLaunchAttributeClusterDimension;
@@ -1072,13 +1093,22 @@ int32_t launch_tc(Ctx* ctx, const CUtensorMap& mq, const CUtensorMap& mx, const 
     cfg.numAttrs = 1;
     VSK_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, mq, mx, a));
   } else {
-    kern<<<grid, TC_THREADS, TC_SMEM_BYTES, ctx->stream>>>(mq, mx, a);
+    kern<<<grid, Epi<EW>::THREADS, smem, ctx->stream>>>(mq, mx, a);
   }
   prof_end(ctx);
   ctx->stats.kernel_launches++;
   ctx->stats.tensor_tiles += tiles * (pair ? 2 : 1);
   VSK_CUDA(ctx, cudaGetLastError());
   return VSK_OK;
+}
+
+// Epilogue warps by contraction length (see Epi): 16 up to four K blocks (d <= 256), 8 beyond.
+inline int tc_epilogue_warps(int kblocks) { return kblocks <= 4 ? 16 : 8; }
+
+template <int MODE>
+int32_t launch_tc(Ctx* ctx, const CUtensorMap& mq, const CUtensorMap& mx, const TcArgs& a, bool has_beta, bool pair) {
+  if (tc_epilogue_warps(a.kblocks) == 16) return launch_tc_ew<MODE, 16>(ctx, mq, mx, a, has_beta, pair);
+  return launch_tc_ew<MODE, 8>(ctx, mq, mx, a, has_beta, pair);
 }
 
 // ---- k-means assignment on the tensor cores ----------------------------------------------------
@@ -1089,8 +1119,8 @@ int32_t launch_tc(Ctx* ctx, const CUtensorMap& mq, const CUtensorMap& mx, const 
 //           value of the coarse winner <= coarse minimum + eps, so its coarse value <= minimum + 2 eps)
 //   exact   the listed centroids are compared with the direct fp32 formula sum (x-c)^2; the smallest
 //           (value, index) wins, as the reference's strict '<' scan does (KMeansClustering.swift:283-288)
-// A row whose list overflows (more than kAssignCap near-ties) is re-done by the fp32 tile.
-constexpr int kAssignCap = 16;   // two sub-lists of 8: one per half of the centroid columns of a tile
+// A row whose list overflows (more near-ties than a sub-list holds) is re-done by the fp32 tile.
+constexpr int kAssignCap = 32;   // split into one sub-list per column part of a tile (2 parts of 16, or 4 of 8)
 
 // eps per data row against the current centroids; stats of the centroid operand are read on the device.
 __global__ void assign_bound_kernel(const float* __restrict__ xn16, const float* __restrict__ xe16,
@@ -1151,21 +1181,29 @@ __global__ void assign_prev_threshold_kernel(const float* __restrict__ x, int64_
 __global__ void assign_exact_kernel(const float* __restrict__ x, int64_t n, int dim, const float* __restrict__ cent,
                                     const uint64_t* __restrict__ keys, const int32_t* __restrict__ count,
                                     int32_t* __restrict__ assign, float* __restrict__ dist, int32_t* __restrict__ bad_rows,
-                                    int32_t* bad_count) {
+                                    int32_t* bad_count, int parts) {
   const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= n) return;
   const int lane = threadIdx.x & 31;
-  // two 16-bit counts: the sub-lists written by the two halves of the tile columns
+  // one 8-bit count per sub-list; the scan's column parts (2 or 4) each wrote one sub-list of kAssignCap / parts keys
   const unsigned packed = (unsigned)count[row];
-  const int cnt_a = (int)(packed & 0xffffu), cnt_b = (int)(packed >> 16);
-  if (cnt_a > kAssignCap / 2 || cnt_b > kAssignCap / 2 || cnt_a + cnt_b <= 0) {
+  const int sub = kAssignCap / parts;
+  int total = 0;
+  bool over = false;
+  for (int p = 0; p < parts; ++p) {
+    const int c = (int)((packed >> (8 * p)) & 0xffu);
+    over |= c > sub;
+    total += c;
+  }
+  if (over || total <= 0) {
     if (lane == 0) bad_rows[atomicAdd(bad_count, 1)] = (int32_t)row;
     return;
   }
   const float* xr = x + row * dim;
   uint64_t bestk = kEmptyKey;
-  for (int c = 0; c < cnt_a + cnt_b; ++c) {
-    const uint32_t id = (uint32_t)keys[row * kAssignCap + (c < cnt_a ? c : kAssignCap / 2 + (c - cnt_a))];
+  for (int p = 0; p < parts; ++p)
+  for (int c = 0; c < (int)((packed >> (8 * p)) & 0xffu); ++c) {
+    const uint32_t id = (uint32_t)keys[row * kAssignCap + p * sub + c];
     const float* cr = cent + (int64_t)id * dim;
     float s = 0.f;
     for (int i = lane; i < dim; i += 32) {
@@ -1512,6 +1550,13 @@ __global__ void ivf_save_threshold_kernel(float* __restrict__ thr, float* __rest
   thr[i] = CUDART_INF_F;
 }
 
+// threshold of every item's query, so that the scan reads it with the item's index
+__global__ void ivf_pair_threshold_kernel(const uint32_t* __restrict__ pair_info, int64_t nitems,
+                                          const float* __restrict__ thr_coarse, float* __restrict__ pair_thr) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < nitems) pair_thr[i] = thr_coarse[pair_info[i] & 0x7fffffffu];
+}
+
 bool ivf_tensor_applicable(const Index* ix, int64_t nq, int32_t nprobe, int32_t k) {
   return ix->kind == INDEX_IVF && nq >= 2 * TM && k <= kCandCap / 4 && ix->n >= 8 * TN &&
          (int64_t)nq * (nprobe + 1) < ((int64_t)1 << 30);
@@ -1574,8 +1619,10 @@ int32_t ivf_tensor_search(Index* ix, const float* q, int64_t nq, const int64_t* 
                                                                               pilot_rows, nkeys - 1, keys);
   ctx->stats.kernel_launches++;
   VSK_TRY(launch_stable_group(ctx, keys, nitems, nkeys, order, pair_off));
-  VSK_TRY(scratch(ctx, SLOT_IVF_SUBSET, (size_t)nitems * 4, &p));
+  VSK_TRY(scratch(ctx, SLOT_IVF_SUBSET, (size_t)(nitems + TM) * 8, &p));   // one tile of padding behind each array
   uint32_t* pair_info = (uint32_t*)p;
+  float* pair_thr = (float*)(pair_info + nitems + TM);
+  VSK_CUDA(ctx, cudaMemsetAsync(pair_info, 0, (size_t)(nitems + TM) * 8, ctx->stream));
   VSK_TRY(scratch(ctx, SLOT_IVF_STAGES, (size_t)(nitems + TM) * dim16 * sizeof(__half), &p));
   __half* g16 = (__half*)p;
   ivf_gather_items_kernel<<<(unsigned)ceil_div(nitems, 8), 256, 0, ctx->stream>>>(order, nitems, slots, q16, dim16, pair_info, g16);
@@ -1641,9 +1688,11 @@ int32_t ivf_tensor_search(Index* ix, const float* q, int64_t nq, const int64_t* 
     ivf_tile_fill_kernel<<<(unsigned)nlist, 128, 0, ctx->stream>>>(pair_off, stage, nlist, ix->list_offsets, (const int64_t*)off_p, (int4*)p);
     ivf_coarse_threshold_kernel<<<qgrid, 256, 0, ctx->stream>>>(cand.thr, qn_tmp, eps, ix->max_xnorm, nq, thr_coarse,
                                                                 nullptr, cand.flags);
-    ctx->stats.kernel_launches += 2;
+    ivf_pair_threshold_kernel<<<(unsigned)ceil_div(nitems, 256), 256, 0, ctx->stream>>>(pair_info, nitems, thr_coarse, pair_thr);
+    ctx->stats.kernel_launches += 3;
     a.tiles = (const int4*)p;
     a.num_tiles = total;
+    a.pair_thr = pair_thr;
     VSK_TRY(launch_tc<SCAN_THRESHOLD>(ctx, mq, mx, a, true, false));
     if (stage == 0) {
       // the pilot appended up to 1 024 rows per query: keep the best few by coarse value and re-score only those
@@ -1790,7 +1839,7 @@ int32_t tensor_assign(Ctx* ctx, TensorAssign* ta, const float* rows, const float
   a.mode = SCAN_THRESHOLD;
   VSK_TRY(launch_tc<SCAN_THRESHOLD>(ctx, mr, mc, a, true, false));
   assign_exact_kernel<<<(unsigned)ceil_div(n, 8), 256, 0, ctx->stream>>>(rows, n, dim, centroids, ta->keys, ta->count, assign, dist,
-                                                                         ta->bad_rows, (int32_t*)(sm + 6));
+                                                                         ta->bad_rows, (int32_t*)(sm + 6), tc_epilogue_warps(a.kblocks) / 4);
   ctx->stats.kernel_launches += 2;
   VSK_CUDA(ctx, cudaGetLastError());
   int32_t h[2] = {0, 0};
