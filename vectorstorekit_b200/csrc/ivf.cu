@@ -3,7 +3,11 @@
 // Replaces IVFIndex.insert / IVFIndex.search (Indexes/IVFIndex.swift:80-122,124-202), which walk
 // the probed lists one query at a time with scalar loops and a full sort.
 //
-// Search is LIST-major.  The (query, probe) pairs of a batch are grouped by list, so that the
+// With the tensor search path selected, a batch of at least 256 queries is scanned on the tensor cores
+// (ivf_tensor_search, tensor_scan.cu): coarse fp16 values filter the rows, every kept row is re-scored exactly, and
+// only queries whose candidate list overflowed come back to the fp32 scan below.
+//
+// The fp32 search is LIST-major.  The (query, probe) pairs of a batch are grouped by list, so that the
 // rows of a list are read once for all the queries that probe it: one CTA computes a block of
 // 128 probing queries x 128 list rows with the fp32 tile, and appends the rows at or below each
 // query's threshold to that query's candidate list.  Probes are processed in stages by probe rank

@@ -19,9 +19,12 @@
 // so that concurrently running CTAs share the same rows in L2):
 //   warp 0      TMA producer: 4-stage ring of {128 x 64 query, 256 x 64 row} fp16 tiles
 //   warp 1      tensor-memory allocation; one lane issues tcgen05.mma (M128 N256 K16 x 4 per stage)
-//   warps 2..9  epilogue: tcgen05.ld of the thread's accumulator row (one query per thread, two warps per
-//               lane quarter, 128 columns each), threshold filter, candidate append; double-buffered
-//               accumulators (2 x 256 columns)
+//   warps 2..   epilogue (8 warps for long contractions, 16 up to d = 256): tcgen05.ld of the thread's
+//               accumulator row (one query per thread; the warps of a lane quarter split the tile's columns),
+//               threshold filter, candidate append; double-buffered accumulators (2 x 256 columns)
+// The same kernel scans the probed lists of an IVF index (tile-table mode: an explicit list of tiles over a
+// query operand gathered per (query, list) pair) and assigns rows to centroids for k-means (argmin mode and a
+// threshold mode whose tiles walk the centroids for a fixed block of rows).
 // Every mbarrier wait is bounded: on expiry the kernel raises an error word, stops issuing work,
 // drains its copies and frees tensor memory, and the host call returns VSK_ERR_TIMEOUT.
 #include <cuda.h>
