@@ -712,6 +712,12 @@ int32_t vsk_index_destroy(vsk_index* i) {
   dev_free(ix->assign);
   dev_free(ix->pq_codebooks);
   dev_free(ix->pq_codes);
+  if (ix->coarse) {   // shares the centroids: only its derived buffers are its own
+    dev_free(ix->coarse->row_norm);
+    dev_free(ix->coarse->rows16);
+    dev_free(ix->coarse->row_aux);
+    delete ix->coarse;
+  }
   delete ix;
   return VSK_OK;
 }

@@ -159,6 +159,8 @@ struct Index {
   std::vector<int64_t> list_offsets_h;
   int32_t* list_rows = nullptr;    // [n] original row of each stored row
   int32_t* assign = nullptr;       // [n] row -> list (original order)
+  Index* coarse = nullptr;         // the centroids as a flat euclidean index (made at the first tensor-path search;
+                                   // shares `centroids`, owns only its derived buffers)
   // product quantisation
   int32_t pq_m = 0, pq_ksub = 0;   // segments, codewords per segment
   float* pq_codebooks = nullptr;   // [pq_m][pq_ksub][dim / pq_m]

@@ -427,13 +427,31 @@ int32_t ivf_search_dev(Index* ix, const float* q, int64_t nq, int32_t k, int32_t
     void *pd, *pi;
     VSK_TRY(scratch(ctx, SLOT_IVF_PROBE_D, (size_t)bn * nprobe * 4, &pd));
     VSK_TRY(scratch(ctx, SLOT_IVF_PROBE_I, (size_t)bn * nprobe * 8, &pi));
-    ExactScanArgs c{};
-    c.metric = VSK_METRIC_EUCLIDEAN;
-    c.q = qb;
-    c.x = ix->centroids;
-    c.dim = ix->dim;
-    VSK_TRY(fp32_topk(ctx, c, ix->nlist, bn, nullptr, nprobe, 0, (float*)pd, (int64_t*)pi, 0));
-    if (ctx->search_path == VSK_PATH_TENSOR_RERANK && ivf_tensor_applicable(ix, bn, nprobe, k)) {
+    const bool tensor = ctx->search_path == VSK_PATH_TENSOR_RERANK && ivf_tensor_applicable(ix, bn, nprobe, k);
+    if (tensor && ix->nlist >= 1024 && nprobe <= 1024) {
+      // the centroids are a flat euclidean index of their own: exact top-nprobe on the tensor path
+      if (!ix->coarse) {
+        Index* co = new Index();
+        co->ctx = ctx;
+        co->kind = INDEX_FLAT_F32;
+        co->metric = VSK_METRIC_EUCLIDEAN;
+        co->dim = ix->dim;
+        co->n = co->capacity = ix->nlist;
+        co->rows = ix->centroids;
+        ix->coarse = co;
+        VSK_TRY(dev_alloc(ctx, (void**)&co->row_norm, (size_t)ix->nlist * sizeof(float)));
+        VSK_TRY(launch_row_norms(ctx, co->rows, co->n, co->dim, 1, co->row_norm));
+      }
+      VSK_TRY(tensor_search(ix->coarse, qb, bn, nprobe, nullptr, (float*)pd, (int64_t*)pi));
+    } else {
+      ExactScanArgs c{};
+      c.metric = VSK_METRIC_EUCLIDEAN;
+      c.q = qb;
+      c.x = ix->centroids;
+      c.dim = ix->dim;
+      VSK_TRY(fp32_topk(ctx, c, ix->nlist, bn, nullptr, nprobe, 0, (float*)pd, (int64_t*)pi, 0));
+    }
+    if (tensor) {
       // coarse scan of the probed lists on the tensor cores + exact rerank; what it cannot certify is re-run below
       std::vector<int32_t> redo;
       VSK_TRY(ivf_tensor_search(ix, qb, bn, (const int64_t*)pi, nprobe, k, out_dist + b * k, out_ids + b * k, &redo));
