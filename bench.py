@@ -238,10 +238,23 @@ class Bench:
                                maxIterations=wl["iters"], tolerance=-1.0)
         t.cuda.synchronize()
         t0 = time.perf_counter()
-        ix.train(self.rows, self.rows[:wl["nlist"]].contiguous())
+        if self.world == 1:
+            ix.train(self.rows, self.rows[:wl["nlist"]].contiguous())
+        else:
+            # rows are sharded: every Lloyd iteration all-reduces the per-centroid sums and counts, so that all
+            # ranks hold the same centroids and every rank's lists are slices of the same lists
+            import torch.distributed as dist
+            from vectorstorekit_b200.sharded import ShardedKMeans
+            init = gen_rows(t, wl, 0, wl["nlist"], self.device, centres)        # the first rows of the whole database
+            trainer = self.vsk.KMeansTrainer(self.dev, self.rows, wl["nlist"])
+            cent, _, _ = ShardedKMeans(trainer.step, trainer.finish).cluster(init, wl["iters"], -1.0)
+            trainer.close()
+            ix.centroids, ix.trained = cent, True
         t.cuda.synchronize()
         t1 = time.perf_counter()
         ix.insert(self.rows)
+        if self.world > 1:
+            ix.set_id_base(self.lo)
         t.cuda.synchronize()
         t2 = time.perf_counter()
         self.index = ix

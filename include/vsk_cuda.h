@@ -208,6 +208,22 @@ int32_t vsk_kmeans(vsk_ctx* ctx, const float* rows, int64_t n, int32_t dim, int3
 int32_t vsk_kmeans_dev(vsk_ctx* ctx, const float* rows, int64_t n, int32_t dim, int32_t k,
                        int32_t max_iters, float tolerance, const float* init_centroids,
                        float* centroids, int32_t* assign, float* inertia, int32_t* iters_run);
+/* Lloyd iterations over rows that are spread over several GPUs (one shard per context; the reference has no
+ * multi-device training).  Each iteration every shard calls step with the current centroids and gets, for its own
+ * rows, the per-centroid sums [k][dim], the per-centroid row counts [k] (as floats) and the sum of its rows'
+ * un-squared distances (the reference's inertia, KMeansClustering.swift:97); the caller adds these up over the
+ * shards (ncclAllReduce) and calls vsk_kmeans_finish_dev, which forms the means (an empty cluster keeps its
+ * centroid, Shaders/ClusteringShaders.metal:171-176).  All pointers are device pointers; `rows` must stay valid
+ * while the trainer lives.  With one shard the result equals vsk_kmeans_dev's up to the order of the sums. */
+typedef struct vsk_kmeans_trainer vsk_kmeans_trainer;
+int32_t vsk_kmeans_trainer_create_dev(vsk_ctx* ctx, const float* rows, int64_t n, int32_t dim, int32_t k,
+                                      vsk_kmeans_trainer** out_trainer);
+int32_t vsk_kmeans_trainer_step_dev(vsk_kmeans_trainer* trainer, const float* centroids, float* sums, float* counts,
+                                    float* inertia);
+int32_t vsk_kmeans_trainer_assignments_dev(vsk_kmeans_trainer* trainer, int32_t* assign);
+int32_t vsk_kmeans_trainer_destroy(vsk_kmeans_trainer* trainer);
+int32_t vsk_kmeans_finish_dev(vsk_ctx* ctx, const float* sums, const float* counts, const float* prev_centroids,
+                              int32_t k, int32_t dim, float* centroids);
 /* Nearest centroid of every row (IVFIndex.findNearestCentroid, Indexes/IVFIndex.swift:514-527). */
 int32_t vsk_assign_dev(vsk_ctx* ctx, const float* rows, int64_t n, int32_t dim,
                        const float* centroids, int32_t k, int32_t* assign, float* dist);

@@ -88,6 +88,41 @@ def test_kmeans_convergence_and_errors(vsk, dev, cpu_oracle):
         km.cluster(x[:3], 5, x[:5])
 
 
+@pytest.mark.parametrize("shape", [(30_000, 32, 64, 4), (200_000, 128, 256, 3)])
+def test_kmeans_trainer_shards_equal_single_run(vsk, dev, cpu_oracle, shape):
+    """The step-wise trainer that multi-GPU training uses: two shards of the rows (here on one GPU), their sums,
+    counts and inertia added up by hand, give the centroids of vsk_kmeans on all rows."""
+    import torch
+    from vectorstorekit_b200.sharded import ShardedKMeans
+    n, d, k, iters = shape
+    rng = np.random.default_rng(n)
+    centres = rng.standard_normal((k, d)).astype(np.float32)
+    x = _mixture(rng, n, d, centres, 0.3)
+    init = x[:k].copy()
+    init[k - 1] = 1e3                                                     # attracts nothing: stays put
+    whole = vsk.KMeansClustering(dev, maxIterations=iters, tolerance=-1.0)
+    rc, ra, rit, rin = whole.cluster(x, k, init)
+    xt = torch.as_tensor(x, device="cuda")
+    cut = n // 3
+    shards = [vsk.KMeansTrainer(dev, xt[:cut], k), vsk.KMeansTrainer(dev, xt[cut:], k)]
+
+    def step(cent):
+        parts = [t.step(cent) for t in shards]
+        return tuple(sum(p[i] for p in parts) for i in range(3))           # what the all-reduce does across ranks
+
+    cent, it, inertia = ShardedKMeans(step, shards[0].finish).cluster(torch.as_tensor(init, device="cuda"), iters, -1.0)
+    assert it == rit == iters
+    assert np.max(np.abs(cent.cpu().numpy() - rc)) < 1e-3
+    assert abs(inertia - rin) <= 1e-3 * abs(rin)
+    assert np.array_equal(cent.cpu().numpy()[k - 1], init[k - 1])
+    asg = torch.cat([t.assignments() for t in shards]).cpu().numpy()
+    # the trainers hold the assignment to the centroids of the LAST step's input; compare with the oracle's
+    # assignment to those centroids (= the whole run's returned assignment)
+    assert np.mean(asg == ra) > 0.999
+    for t in shards:
+        t.close()
+
+
 def test_ivf_kat_and_errors(vsk, dev):
     """IVFIndexTests.swift:140-201: untrained use throws; basic search finds the inserted row."""
     ix = vsk.IVFIndex(dev, 4, numberOfCentroids=2, numberOfProbes=2, maxIterations=25)

@@ -56,3 +56,59 @@ def test_two_rank_sharded_search_equals_unsharded():
         p.join(120)
     assert all(p.exitcode == 0 for p in procs)
     assert ret.get(0) is True and ret.get(1) is True
+
+
+def _kmeans_worker(rank, world, port, ret):
+    """Sharded Lloyd iterations on CPU ranks: numpy stands in for the device step; the result must equal the CPU
+    oracle's k-means on the unsharded rows (up to the order of the fp32 sums)."""
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import oracle
+    from vectorstorekit_b200.sharded import ShardedKMeans, shard_range
+    o = oracle.CpuOracle()
+    rng = np.random.default_rng(11)
+    k, d = 7, 6
+    centres = rng.standard_normal((k, d)).astype(np.float32) * 3
+    x = (centres[rng.integers(0, k - 1, 901)] + 0.3 * rng.standard_normal((901, d))).astype(np.float32)
+    init = np.concatenate([x[:k - 1], np.full((1, d), 50.0, np.float32)])     # the last centroid attracts no row
+    lo, hi = shard_range(len(x), rank, world)
+    mine = x[lo:hi]
+
+    def step(cent):
+        c = cent.numpy()
+        asg, dist_ = o.assign(mine, c)
+        sums = np.zeros((k, d), np.float32)
+        np.add.at(sums, asg, mine)
+        counts = np.bincount(asg, minlength=k).astype(np.float32)
+        return torch.from_numpy(sums), torch.from_numpy(counts), torch.tensor([dist_.sum()], dtype=torch.float32)
+
+    def finish(sums, counts, cent):
+        s, c, old = sums.numpy(), counts.numpy(), cent.numpy()
+        out = np.where(c[:, None] > 0, s / np.maximum(c, 1)[:, None], old).astype(np.float32)
+        return torch.from_numpy(out)
+
+    cent, iters, inertia = ShardedKMeans(step, finish).cluster(torch.from_numpy(init), 5, -1.0)
+    rc, ra, rin, rit = o.kmeans(x, init, 5)
+    ok = iters == rit == 5 and np.allclose(cent.numpy(), rc, rtol=1e-4, atol=1e-5) and abs(inertia - rin) <= 1e-3 * abs(rin)
+    ok = ok and np.array_equal(cent.numpy()[k - 1], init[k - 1])             # the empty cluster kept its centroid
+    gathered = [torch.zeros_like(cent) for _ in range(world)]
+    dist.all_gather(gathered, cent)
+    ok = ok and all(torch.equal(g, cent) for g in gathered)                   # every rank holds the same centroids
+    ret[rank] = bool(ok)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_rank_sharded_kmeans_equals_unsharded():
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    port = 29950 + os.getpid() % 40
+    procs = [ctx.Process(target=_kmeans_worker, args=(r, 2, port, ret)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+    assert all(p.exitcode == 0 for p in procs)
+    assert ret.get(0) is True and ret.get(1) is True

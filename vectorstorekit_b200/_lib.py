@@ -60,6 +60,11 @@ SIGNATURES = {
     "vsk_index_set_id_base": (C.c_int32, [vp, C.c_int64]),
     "vsk_index_info_get": (C.c_int32, [vp, C.POINTER(IndexInfo)]),
     "vsk_ivf_centroids": (C.c_int32, [vp, vp]),
+    "vsk_kmeans_trainer_create_dev": (C.c_int32, [vp, vp, C.c_int64, C.c_int32, C.c_int32, C.POINTER(vp)]),
+    "vsk_kmeans_trainer_step_dev": (C.c_int32, [vp, vp, vp, vp, vp]),
+    "vsk_kmeans_trainer_assignments_dev": (C.c_int32, [vp, vp]),
+    "vsk_kmeans_trainer_destroy": (C.c_int32, [vp]),
+    "vsk_kmeans_finish_dev": (C.c_int32, [vp, vp, vp, vp, C.c_int32, C.c_int32, vp]),
     "vsk_pq_train": (C.c_int32, [vp, vp, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32, vp, vp]),
     "vsk_pq_train_dev": (C.c_int32, [vp, vp, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32, vp, vp]),
     "vsk_pq_encode": (C.c_int32, [vp, vp, C.c_int32, C.c_int32, C.c_int32, vp, C.c_int64, vp]),

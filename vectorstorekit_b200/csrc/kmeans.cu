@@ -87,6 +87,30 @@ __global__ void centroid_finish_kernel(const float* __restrict__ partial, int di
   }
 }
 
+// The same sum without the division, and the group's row count: one shard's contribution to a centroid when the
+// rows are spread over several GPUs (the means are formed after the shards' sums have been added up).
+__global__ void centroid_sum_kernel(const float* __restrict__ partial, int dim, const int64_t* __restrict__ offsets,
+                                    const int64_t* __restrict__ seg_off, float* __restrict__ sums,
+                                    float* __restrict__ counts) {
+  const int c = blockIdx.x;
+  const int64_t s0 = seg_off[c], s1 = seg_off[c + 1];
+  for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+    float s = 0.f;
+    for (int64_t g = s0; g < s1; ++g) s += partial[g * dim + d];
+    sums[(int64_t)c * dim + d] = s;
+  }
+  if (threadIdx.x == 0) counts[c] = (float)(offsets[c + 1] - offsets[c]);   // exact below 2^24 rows per centroid and shard
+}
+
+// centroids from summed contributions: sum / count, an empty cluster keeps its centroid
+__global__ void centroid_mean_kernel(const float* __restrict__ sums, const float* __restrict__ counts, int64_t total,
+                                     int dim, const float* __restrict__ old_c, float* __restrict__ new_c) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const float cnt = counts[i / dim];
+  new_c[i] = cnt > 0.f ? sums[i] / cnt : old_c[i];
+}
+
 // fixed-shape fp64 reduction: 1024 partial sums, then one block
 __global__ void sum_partial_kernel(const float* v, int64_t n, double* partial) {
   __shared__ double sh[256];
@@ -268,11 +292,131 @@ int32_t kmeans_dev(Ctx* ctx, const float* rows, int64_t n, int32_t dim, int32_t 
   return VSK_OK;
 }
 
+// ---- one Lloyd step over a shard of the rows (rows spread over several GPUs) -------------------------------
+struct KMeansTrainer {
+  Ctx* ctx = nullptr;
+  const float* rows = nullptr;
+  int64_t n = 0;
+  int32_t dim = 0, k = 0;
+  int32_t* assign = nullptr;   // [n]
+  float* dist = nullptr;       // [n]
+  int32_t* order = nullptr;    // [n]
+  bool tc = false;
+  TensorAssign ta;
+  int steps = 0;
+};
+
+int32_t trainer_step(KMeansTrainer* t, const float* centroids, float* sums, float* counts, float* inertia) {
+  Ctx* ctx = t->ctx;
+  const int64_t n = t->n;
+  const int dim = t->dim, k = t->k;
+  if (t->tc) VSK_TRY(tensor_assign(ctx, &t->ta, t->rows, centroids, k, t->assign, t->dist, t->steps > 0));
+  else VSK_TRY(assign_rows_fp32(ctx, t->rows, n, dim, centroids, k, t->assign, t->dist));
+  void *offsets, *nseg, *seg_off, *partial, *red;
+  VSK_TRY(scratch(ctx, SLOT_X_TMP, (size_t)(k + 1) * 8, &offsets));
+  VSK_TRY(launch_stable_group(ctx, t->assign, n, k, t->order, (int64_t*)offsets));
+  const int64_t max_segs = n / kSegRows + k + 1;
+  VSK_TRY(scratch(ctx, SLOT_KM_NSEG, (size_t)(k + 1) * 8, &nseg));
+  VSK_TRY(scratch(ctx, SLOT_KM_SEGOFF, (size_t)(k + 1) * 8, &seg_off));
+  VSK_TRY(scratch(ctx, SLOT_KM_PARTIAL, (size_t)max_segs * dim * 4, &partial));
+  VSK_TRY(scratch(ctx, SLOT_QAUX, 1024 * 8 + 16, &red));
+  segment_count_kernel<<<(unsigned)ceil_div(k, 256), 256, 0, ctx->stream>>>((const int64_t*)offsets, k, (int64_t*)nseg);
+  VSK_TRY(launch_scan_i64(ctx, (const int64_t*)nseg, k, (int64_t*)seg_off));
+  const int threads = std::min(256, (dim + 31) / 32 * 32);
+  segment_sum_kernel<<<(unsigned)max_segs, threads, 0, ctx->stream>>>(t->rows, dim, t->order, (const int64_t*)offsets,
+                                                                     (const int64_t*)seg_off, k, (float*)partial);
+  centroid_sum_kernel<<<k, threads, 0, ctx->stream>>>((const float*)partial, dim, (const int64_t*)offsets,
+                                                      (const int64_t*)seg_off, sums, counts);
+  sum_partial_kernel<<<1024, 256, 0, ctx->stream>>>(t->dist, n, (double*)red);
+  sum_final_kernel<<<1, 1024, 0, ctx->stream>>>((const double*)red, 1024, inertia);
+  ctx->stats.kernel_launches += 5;
+  VSK_CUDA(ctx, cudaGetLastError());
+  VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  t->steps++;
+  return VSK_OK;
+}
+
 }  // namespace vsk
 
 using namespace vsk;
 
 extern "C" {
+
+int32_t vsk_kmeans_trainer_create_dev(vsk_ctx* c, const float* rows, int64_t n, int32_t dim, int32_t k,
+                                      vsk_kmeans_trainer** out) {
+  Ctx* ctx = reinterpret_cast<Ctx*>(c);
+  if (!ctx || !out) return VSK_ERR_INVALID_INPUT;
+  cudaSetDevice(ctx->device);
+  *out = nullptr;
+  if (n <= 0 || !rows) return fail(ctx, VSK_ERR_EMPTY_INPUT, "empty dataset");
+  if (k <= 0) return fail(ctx, VSK_ERR_INVALID_INPUT, "k must be positive");
+  if (dim <= 0) return fail(ctx, VSK_ERR_DIMENSION_MISMATCH, "dimension must be positive");
+  if (n > 0x7fffffffLL) return fail(ctx, VSK_ERR_INVALID_BUFFER_SIZE, "at most 2^31-1 rows");
+  KMeansTrainer* t = new KMeansTrainer();
+  t->ctx = ctx;
+  t->rows = rows;
+  t->n = n;
+  t->dim = dim;
+  t->k = k;
+  t->tc = use_tensor_assign(ctx, n, k);
+  int32_t st;
+  if ((st = dev_alloc(ctx, (void**)&t->assign, (size_t)n * 4)) == VSK_OK &&
+      (st = dev_alloc(ctx, (void**)&t->dist, (size_t)n * 4)) == VSK_OK &&
+      (st = dev_alloc(ctx, (void**)&t->order, (size_t)n * 4)) == VSK_OK && t->tc)
+    st = tensor_assign_prepare(ctx, rows, n, dim, &t->ta);
+  if (st != VSK_OK) {
+    vsk_kmeans_trainer_destroy(reinterpret_cast<vsk_kmeans_trainer*>(t));
+    return st;
+  }
+  *out = reinterpret_cast<vsk_kmeans_trainer*>(t);
+  return VSK_OK;
+}
+
+int32_t vsk_kmeans_trainer_step_dev(vsk_kmeans_trainer* h, const float* centroids, float* sums, float* counts,
+                                    float* inertia) {
+  KMeansTrainer* t = reinterpret_cast<KMeansTrainer*>(h);
+  if (!t) return VSK_ERR_INVALID_INPUT;
+  cudaSetDevice(t->ctx->device);
+  if (!centroids || !sums || !counts || !inertia) return fail(t->ctx, VSK_ERR_INVALID_INPUT, "null pointer");
+  return trainer_step(t, centroids, sums, counts, inertia);
+}
+
+int32_t vsk_kmeans_trainer_assignments_dev(vsk_kmeans_trainer* h, int32_t* assign) {
+  KMeansTrainer* t = reinterpret_cast<KMeansTrainer*>(h);
+  if (!t || !assign) return VSK_ERR_INVALID_INPUT;
+  cudaSetDevice(t->ctx->device);
+  VSK_CUDA(t->ctx, cudaMemcpyAsync(assign, t->assign, (size_t)t->n * 4, cudaMemcpyDeviceToDevice, t->ctx->stream));
+  VSK_CUDA(t->ctx, cudaStreamSynchronize(t->ctx->stream));
+  return VSK_OK;
+}
+
+int32_t vsk_kmeans_trainer_destroy(vsk_kmeans_trainer* h) {
+  KMeansTrainer* t = reinterpret_cast<KMeansTrainer*>(h);
+  if (!t) return VSK_ERR_INVALID_INPUT;
+  cudaSetDevice(t->ctx->device);
+  cudaStreamSynchronize(t->ctx->stream);
+  if (t->tc) tensor_assign_release(&t->ta);
+  dev_free(t->assign);
+  dev_free(t->dist);
+  dev_free(t->order);
+  delete t;
+  return VSK_OK;
+}
+
+int32_t vsk_kmeans_finish_dev(vsk_ctx* c, const float* sums, const float* counts, const float* prev_centroids, int32_t k,
+                              int32_t dim, float* centroids) {
+  Ctx* ctx = reinterpret_cast<Ctx*>(c);
+  if (!ctx) return VSK_ERR_INVALID_INPUT;
+  cudaSetDevice(ctx->device);
+  if (k <= 0 || dim <= 0) return fail(ctx, VSK_ERR_EMPTY_INPUT, "no centroids");
+  if (!sums || !counts || !prev_centroids || !centroids) return fail(ctx, VSK_ERR_INVALID_INPUT, "null pointer");
+  const int64_t total = (int64_t)k * dim;
+  centroid_mean_kernel<<<(unsigned)ceil_div(total, 256), 256, 0, ctx->stream>>>(sums, counts, total, dim, prev_centroids, centroids);
+  ctx->stats.kernel_launches++;
+  VSK_CUDA(ctx, cudaGetLastError());
+  VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return VSK_OK;
+}
 
 int32_t vsk_kmeans_dev(vsk_ctx* c, const float* rows, int64_t n, int32_t dim, int32_t k, int32_t max_iters,
                        float tolerance, const float* init, float* centroids, int32_t* assign, float* inertia,

@@ -491,6 +491,53 @@ class KMeansClustering:
         return asg, dist
 
 
+class KMeansTrainer:
+    """One shard's side of a multi-GPU k-means run (``vectorstorekit_b200.sharded.ShardedKMeans`` drives it): the
+    shard's rows stay on the device, ``step`` assigns them to the given centroids and returns this shard's
+    per-centroid sums, counts and inertia as CUDA tensors, ``finish`` forms the means from summed contributions."""
+
+    def __init__(self, dev: CUDAComputeDevice, rows, k: int):
+        if not _is_dev(rows):
+            raise InvalidInput("KMeansTrainer takes a CUDA tensor of rows")
+        self.dev, self._lib = dev, dev._lib
+        self.rows = rows.contiguous().float()          # kept alive: the library reads it on every step
+        self.k = int(k)
+        self.n, self.dim = self.rows.shape
+        h = C.c_void_p()
+        dev.check(self._lib.vsk_kmeans_trainer_create_dev(dev._h, _ptr(self.rows), self.n, self.dim, self.k, C.byref(h)))
+        self._h = h
+
+    def step(self, centroids):
+        c = centroids.contiguous().float()
+        sums = torch.empty((self.k, self.dim), dtype=torch.float32, device=c.device)
+        counts = torch.empty((self.k,), dtype=torch.float32, device=c.device)
+        inertia = torch.empty((1,), dtype=torch.float32, device=c.device)
+        self.dev.check(self._lib.vsk_kmeans_trainer_step_dev(self._h, _ptr(c), _ptr(sums), _ptr(counts), _ptr(inertia)))
+        return sums, counts, inertia
+
+    def finish(self, sums, counts, centroids):
+        out = torch.empty_like(sums)
+        self.dev.check(self._lib.vsk_kmeans_finish_dev(self.dev._h, _ptr(sums.contiguous()), _ptr(counts.contiguous()),
+                                                       _ptr(centroids.contiguous().float()), self.k, self.dim, _ptr(out)))
+        return out
+
+    def assignments(self):
+        a = torch.empty((self.n,), dtype=torch.int32, device=self.rows.device)
+        self.dev.check(self._lib.vsk_kmeans_trainer_assignments_dev(self._h, _ptr(a)))
+        return a
+
+    def close(self):
+        if self._h:
+            self._lib.vsk_kmeans_trainer_destroy(self._h)
+            self._h = None
+
+    def __del__(self):  # pragma: no cover
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 class IVFIndex(_IndexBase):
     """``IVFIndex`` (``Indexes/IVFIndex.swift``): ``train(on:)`` runs k-means for the centroids,
     ``insert`` assigns rows to their nearest centroid's list, ``search`` probes ``numberOfProbes``

@@ -45,3 +45,38 @@ class ShardedSearch:
         if d.is_cuda:
             torch.cuda.current_stream().synchronize()
         return self.merge(gd, gi)
+
+
+class ShardedKMeans:
+    """Lloyd iterations over rows spread across the ranks of a group: every rank assigns its own rows to the
+    current centroids and sums them per centroid (``step``), the per-centroid sums, counts and the inertia are added
+    up over the ranks with one all-reduce each, and every rank forms the same new centroids (``finish``).  This is
+    ``KMeansClustering.cluster`` (``Clustering/KMeansClustering.swift:48-113``) with its update step split at the
+    point where shards have to talk; an empty cluster keeps its centroid.
+
+    ``step(centroids) -> (sums [k, d], counts [k], inertia [1])`` and ``finish(sums, counts, centroids) -> centroids``
+    are injected (on GPUs: ``KMeansTrainer.step`` / ``KMeansTrainer.finish``), so that the exchange can be exercised
+    on CPU ranks in tests."""
+
+    def __init__(self, step: Callable, finish: Callable, group=None):
+        import torch.distributed as dist
+        self._dist = dist
+        self.step, self.finish, self.group = step, finish, group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+
+    def cluster(self, initial_centroids, max_iterations: int, tolerance: float = 1e-4):
+        """-> (centroids, iterations, inertia).  tolerance < 0 runs exactly max_iterations."""
+        cent = initial_centroids
+        prev, inertia, it = float("inf"), float("inf"), 0
+        while it < max_iterations:
+            sums, counts, inert = self.step(cent)
+            if self.world > 1:
+                for t in (sums, counts, inert):
+                    self._dist.all_reduce(t, group=self.group)
+            cent = self.finish(sums, counts, cent)
+            inertia = float(inert.sum())
+            it += 1
+            if tolerance >= 0 and abs(inertia - prev) < tolerance:     # KMeansClustering.swift:98
+                break
+            prev = inertia
+        return cent, it, inertia
