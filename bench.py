@@ -571,6 +571,14 @@ def main():
         roof.update(unit="T lane-instr/s", achieved=b.flops * args.steps / secs / 1e12 if secs > 0 else None,
                     peak=sm * 128 * 1.965e9 / 1e12, peak_source="nominal: SMs x 128 FP32 lanes x 1965 MHz")
     roof["frac"] = roof["achieved"] / roof["peak"] if roof.get("achieved") else None
+    if wl["kind"] == "flat" and args.path == "tensor" and b.bound == "tensor":
+        # DRAM bytes per scan launch, from the ncu capture of the reduced workload (profiles/tc_scan_kernel__*):
+        # dram__bytes_read equals the fp16 rows of the launch read once plus the query operand, dram__bytes_write is
+        # the appended keys (about 6 MB); scaled to this workload by its rows (traffic grows in proportion)
+        d16 = (wl["dim"] + 63) // 64 * 64
+        per_step = (b.hi - b.lo) * d16 * 2 + (scan_n / args.steps) * (nq * d16 * 2 + 6.0e6)
+        roof["traffic"] = per_step / (scan_n / args.steps)
+        roof["traffic_source"] = "ncu capture of workload c2s, scaled by rows"
 
     line = {
         "metric": "queries/sec (k-NN, exact top-k match)", "value": nq * args.steps / (elapsed_ms * 1e-3),
