@@ -189,6 +189,24 @@ int32_t vsk_search(vsk_index* index, const float* queries, int64_t nq, int32_t k
 int32_t vsk_search_dev(vsk_index* index, const float* queries, int64_t nq, int32_t k,
                        const uint64_t* qmasks, float* out_dist, int64_t* out_ids);
 
+/* A shard's search in two halves, for a host that spreads the rows of one database over several GPUs
+ * (the multi-GPU form of VectorStore.batchSearch; the reference has no sharded search).
+ *   begin:  scans this shard.  bound[q] (device, nq floats) receives a value that this shard's ceil(k / shards)
+ *           best rows do not exceed, or +inf when nothing is known (shorter shards, index kinds and search paths
+ *           that have no split form).  The units depend on the query only, so the values of one query are
+ *           comparable between shards.
+ *   host:   element-wise MAXIMUM of `bound` over the shards (one all-reduce): at least k rows of the whole
+ *           database lie at or below it.
+ *   finish: with the reduced bound, returns this shard's rows among its k best that can still belong to the
+ *           overall k best (others are padded with +inf / -1), in the layout of vsk_search_dev.
+ * `begin` returns while its kernels still run on the context's stream (vsk_stream): do the reduction on that stream
+ * or synchronise it first; `finish` returns with the results complete.
+ * The queries, k and the bound buffer of `begin` must stay valid until `finish`, and no other call may be made on
+ * the index's context in between.  At most 16 384 queries per call.  Flat fp32 indexes without query masks. */
+int32_t vsk_search_shard_begin_dev(vsk_index* index, const float* queries, int64_t nq, int32_t k,
+                                   int32_t shards, float* bound);
+int32_t vsk_search_shard_finish_dev(vsk_index* index, const float* bound, float* out_dist, int64_t* out_ids);
+
 /* Merge of per-shard results: `g` lists of k (distance, global id) per query, laid out
  * [g][nq][k], into the k best per query by (distance, id) — what one unsharded search returns.
  * Device pointers.  The reference has no sharded search; this is the step after the NCCL gather. */

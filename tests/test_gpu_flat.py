@@ -291,6 +291,71 @@ def test_device_pointers_and_merge(vsk, dev, engine, cpu_oracle):
     assert np.array_equal(mi.cpu().numpy(), oi) and np.array_equal(md.cpu().numpy(), od)
 
 
+@pytest.mark.parametrize("metric,shards,k", [("euclidean", 3, 20), ("cosine", 4, 100), ("dotProduct", 2, 1),
+                                             ("euclidean", 8, 5)])
+def test_two_half_shard_search(vsk, engine, cpu_oracle, metric, shards, k):
+    """The search of a row shard in two halves (bound out, reduced bound in): shards emulated one after another on
+    one GPU, each on its own context; their merged result equals the unsharded search, and the reduced bound drops
+    most of each shard's rows before the exact re-scoring."""
+    import torch
+    rng = np.random.default_rng(29)
+    n, d, nq = 36_000, 64, 300
+    x = rng.standard_normal((n, d)).astype(np.float32)
+    q = rng.standard_normal((nq, d)).astype(np.float32)
+    x[20_000] = x[5]                       # an exact tie across two shards
+    xd, qd = torch.from_numpy(x).cuda(), torch.from_numpy(q).cuda()
+    devs, idx, bounds = [], [], []
+    try:
+        for s in range(shards):
+            dv = vsk.CUDAAcceleratorStrategy(0).initialize()
+            lo, hi = s * n // shards, (s + 1) * n // shards
+            ix = vsk.FlatIndex(dv, d, metric)
+            ix.add(xd[lo:hi])
+            ix.set_id_base(lo)
+            devs.append(dv); idx.append(ix)
+            bounds.append(ix.shardSearchBegin(qd, k, shards))
+        torch.cuda.synchronize()           # `begin` returns with its kernels still running on the library's stream
+        g = torch.stack(bounds).max(dim=0).values
+        assert bool(torch.isfinite(g).all())
+        parts = [ix.shardSearchFinish(g) for ix in idx]
+        reranked = sum(dv.stats()["reranked_rows"] for dv in devs)
+        fallbacks = sum(dv.stats()["fallback_queries"] for dv in devs)
+    finally:
+        for ix in idx:
+            ix.close()
+    pd, pi = torch.stack([p[0] for p in parts]), torch.stack([p[1] for p in parts])
+    md, mi = engine.mergeTopK(pd, pi)
+    rd, ri = cpu_oracle.flat_search(oracle.METRIC_IDS[metric], q, x, k)
+    assert_topk_parity(md.cpu().numpy(), mi.cpu().numpy(), rd, ri)
+    assert fallbacks <= nq // 20
+    if shards * 4 <= k:
+        # every shard alone would re-score more than k rows per query; with the bound, well under half of that
+        assert reranked < 0.5 * shards * nq * k
+
+
+def test_two_half_shard_search_without_split_form(vsk, cpu_oracle):
+    """fp32 search path and Manhattan have no split form: `begin` reports +inf, `finish` runs the whole search."""
+    import torch
+    rng = np.random.default_rng(31)
+    x = rng.standard_normal((5000, 32)).astype(np.float32)
+    q = rng.standard_normal((40, 32)).astype(np.float32)
+    dv = vsk.CUDAAcceleratorStrategy(0).initialize()
+    ix = vsk.FlatIndex(dv, 32, "manhattan")
+    try:
+        ix.add(torch.from_numpy(x).cuda())
+        with pytest.raises(vsk.InvalidInput):
+            ix._pending = (torch.from_numpy(q).cuda(), 6)
+            ix.shardSearchFinish(torch.zeros(40, device="cuda"))
+        b = ix.shardSearchBegin(torch.from_numpy(q).cuda(), 6, 4)
+        torch.cuda.synchronize()
+        assert bool(torch.isinf(b).all())
+        gd, gi = ix.shardSearchFinish(b)
+    finally:
+        ix.close()
+    rd, ri = cpu_oracle.flat_search(oracle.MANHATTAN, q, x, 6)
+    assert_topk_parity(gd.cpu().numpy(), gi.cpu().numpy(), rd, ri)
+
+
 def test_errors(vsk, dev, engine):
     x = np.zeros((4, 8), np.float32)
     with pytest.raises(vsk.EmptyInput):

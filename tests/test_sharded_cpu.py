@@ -1,5 +1,6 @@
-"""The N > 1 path on CPU: two gloo ranks, each searching its row shard (with the CPU oracle standing in
-for the GPU search), all-gather, merge — must equal the unsharded search exactly."""
+"""The N > 1 path on CPU: gloo ranks, each searching its row shard (with the CPU oracle standing in for the GPU
+search), the bound all-reduce, the all-to-all of the per-shard lists, the sliced merge and the all-gather — must
+equal the unsharded search exactly."""
 import os
 import sys
 
@@ -34,28 +35,48 @@ def _worker(rank, world, port, ret):
         d, i = o.merge_topk(gd.numpy(), gi.numpy())
         return torch.from_numpy(d), torch.from_numpy(i)
 
-    s = ShardedSearch(local, merge)
-    d, i = s.batchSearch(torch.from_numpy(q), 9)
+    # the two halves of the local search: `begin` reports the ceil(k / shards)-th best local distance, `finish`
+    # drops what lies above the maximum of those over the ranks (and counts what it kept)
+    state = {}
+
+    def begin(queries, k, shards):
+        d, i = local(queries, k)
+        state["res"] = (d, i)
+        j = -(-k // shards)
+        return d[:, j - 1].clone()
+
+    def finish(bound):
+        d, i = state.pop("res")
+        keep = d <= bound[:, None]
+        state["kept"] = int(keep.sum())
+        return torch.where(keep, d, torch.full_like(d, float("inf"))), torch.where(keep, i, torch.full_like(i, -1))
+
     rd, ri = o.flat_search(oracle.EUCLIDEAN, q, x, 9)
-    ok = np.array_equal(i.numpy(), ri) and np.array_equal(d.numpy(), rd)
+    ok = True
+    for s in (ShardedSearch(local, merge), ShardedSearch(local, merge, local_begin=begin, local_finish=finish),
+              ShardedSearch(local, merge, local_begin=begin, local_finish=finish, max_queries=5)):
+        d, i = s.batchSearch(torch.from_numpy(q), 9)
+        ok = ok and np.array_equal(i.numpy(), ri) and np.array_equal(d.numpy(), rd)
+    ok = ok and state["kept"] < 2 * 9          # the bound dropped rows (last batch: 2 queries of 9)
     ret[rank] = bool(ok)
     dist.barrier()
     dist.destroy_process_group()
 
 
-def test_two_rank_sharded_search_equals_unsharded():
+@pytest.mark.parametrize("world", [2, 3])
+def test_sharded_search_equals_unsharded(world):
     from vectorstorekit_b200.sharded import shard_range
     assert [shard_range(10, r, 3) for r in range(3)] == [(0, 3), (3, 6), (6, 10)]
     ctx = mp.get_context("spawn")
     ret = ctx.Manager().dict()
-    port = 29600 + os.getpid() % 300
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, ret)) for r in range(2)]
+    port = 29600 + os.getpid() % 300 + world
+    procs = [ctx.Process(target=_worker, args=(r, world, port, ret)) for r in range(world)]
     for p in procs:
         p.start()
     for p in procs:
         p.join(120)
     assert all(p.exitcode == 0 for p in procs)
-    assert ret.get(0) is True and ret.get(1) is True
+    assert all(ret.get(r) is True for r in range(world))
 
 
 def _kmeans_worker(rank, world, port, ret):

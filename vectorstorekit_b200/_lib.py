@@ -81,6 +81,8 @@ SIGNATURES = {
     "vsk_index_load": (C.c_int32, [vp, C.c_char_p, C.POINTER(vp)]),
     "vsk_search": (C.c_int32, [vp, vp, C.c_int64, C.c_int32, vp, vp, vp]),
     "vsk_search_dev": (C.c_int32, [vp, vp, C.c_int64, C.c_int32, vp, vp, vp]),
+    "vsk_search_shard_begin_dev": (C.c_int32, [vp, vp, C.c_int64, C.c_int32, C.c_int32, vp]),
+    "vsk_search_shard_finish_dev": (C.c_int32, [vp, vp, vp, vp]),
     "vsk_merge_topk_dev": (C.c_int32, [vp, vp, vp, C.c_int32, C.c_int64, C.c_int32, vp, vp]),
     "vsk_kmeans": (C.c_int32, [vp, vp, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_float, vp, vp, vp,
                                C.POINTER(C.c_float), C.POINTER(C.c_int32)]),

@@ -9,6 +9,7 @@
 #include <algorithm>
 #include <cstring>
 #include <functional>
+#include <math_constants.h>
 
 #include "common.cuh"
 #include "tensor_scan.cuh"
@@ -745,6 +746,66 @@ int32_t vsk_search_dev(vsk_index* i, const float* q, int64_t nq, int32_t k, cons
     return pq_search_dev(ix, q, nq, k, out_dist, out_ids);
   }
   return flat_search_dev(ix, q, nq, k, qmasks, out_dist, out_ids);
+}
+
+__global__ void fill_inf_kernel(float* p, int64_t n) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) p[i] = CUDART_INF_F;
+}
+
+int32_t vsk_search_shard_begin_dev(vsk_index* i, const float* q, int64_t nq, int32_t k, int32_t shards, float* bound) {
+  Index* ix = reinterpret_cast<Index*>(i);
+  if (!ix) return VSK_ERR_INVALID_INPUT;
+  Ctx* ctx = ix->ctx;
+  cudaSetDevice(ctx->device);
+  ctx->pending = ShardPending{};
+  if (ix->kind != INDEX_FLAT_F32) return fail(ctx, VSK_ERR_UNSUPPORTED_OPERATION, "the two-half search covers flat fp32 indexes");
+  if (nq <= 0 || ix->n <= 0) return fail(ctx, VSK_ERR_EMPTY_INPUT, "empty queries or empty index");
+  if (nq > kQueryBatch) return fail(ctx, VSK_ERR_INVALID_BUFFER_SIZE, "at most %lld queries per two-half search", (long long)kQueryBatch);
+  if (k <= 0 || k > kCandCap / 2) return fail(ctx, VSK_ERR_INVALID_INPUT, "k must be in [1, %d]", kCandCap / 2);
+  if (shards <= 0) return fail(ctx, VSK_ERR_INVALID_INPUT, "shards must be positive");
+  if (!q || !bound) return fail(ctx, VSK_ERR_INVALID_INPUT, "null pointer");
+  const bool tensor = ctx->search_path == VSK_PATH_TENSOR_RERANK && ix->metric != VSK_METRIC_MANHATTAN;
+  if (!tensor) {
+    // no split form: nothing is known yet, the second half runs the whole search
+    fill_inf_kernel<<<(unsigned)ceil_div(nq, 256), 256, 0, ctx->stream>>>(bound, nq);
+    ctx->stats.kernel_launches++;
+    VSK_CUDA(ctx, cudaGetLastError());
+    ctx->pending.active = true;
+    ctx->pending.ix = ix;
+    ctx->pending.q = q;
+    ctx->pending.nq = nq;
+    ctx->pending.k = k;
+    return VSK_OK;
+  }
+  ctx->stats.searches++;
+  ctx->stats.queries += nq;
+  float* qnorm = nullptr;
+  if (ix->metric == VSK_METRIC_COSINE) {
+    void* p;
+    VSK_TRY(scratch(ctx, SLOT_QNORM, nq * sizeof(float), &p));
+    qnorm = (float*)p;
+    VSK_TRY(launch_row_norms(ctx, q, nq, ix->dim, 0, qnorm));
+  }
+  return tensor_search_begin(ix, q, nq, k, qnorm, shards, bound);
+}
+
+int32_t vsk_search_shard_finish_dev(vsk_index* i, const float* bound, float* out_dist, int64_t* out_ids) {
+  Index* ix = reinterpret_cast<Index*>(i);
+  if (!ix) return VSK_ERR_INVALID_INPUT;
+  Ctx* ctx = ix->ctx;
+  cudaSetDevice(ctx->device);
+  if (!bound || !out_dist || !out_ids) return fail(ctx, VSK_ERR_INVALID_INPUT, "null pointer");
+  if (!ctx->pending.active || ctx->pending.ix != ix)
+    return fail(ctx, VSK_ERR_INVALID_INPUT, "no search is waiting for its second half on this index");
+  if (!ctx->pending.tensor) {
+    const ShardPending pd = ctx->pending;
+    ctx->pending = ShardPending{};
+    return flat_search_dev(ix, pd.q, pd.nq, pd.k, nullptr, out_dist, out_ids);
+  }
+  VSK_TRY(tensor_search_finish(ix, bound, out_dist, out_ids));
+  VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return VSK_OK;
 }
 
 int32_t vsk_search(vsk_index* i, const float* q, int64_t nq, int32_t k, const uint64_t* qmasks, float* out_dist,

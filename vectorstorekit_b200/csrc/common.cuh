@@ -83,6 +83,24 @@ struct CandLists {
 
 enum ScanMode : int { SCAN_DENSE = 0, SCAN_THRESHOLD = 1, SCAN_MATRIX = 2, SCAN_ARGMIN = 3 };
 
+struct Index;
+// What the second half of a search needs from the first (device pointers into the context's scratch, valid until
+// the next call on the context).
+struct ShardPending {
+  bool active = false;
+  bool tensor = false;        // false: the index kind or search path has no split form; `finish` runs the whole search
+  bool need_cert = false;     // the certifying compaction was left to the second half
+  Index* ix = nullptr;
+  const float* q = nullptr;
+  const float* qnorm = nullptr;
+  int64_t nq = 0;
+  int32_t k = 0, keep = 0, max_count = 0;
+  CandLists cand;
+  const float* eps = nullptr;
+  int32_t* err = nullptr;
+  unsigned long long* rr_total = nullptr;
+};
+
 struct Ctx {
   int device = 0;
   cudaStream_t stream = nullptr;
@@ -97,6 +115,7 @@ struct Ctx {
   // grow-only device scratch, one buffer per slot (see Slot)
   void* scratch[64] = {};
   size_t scratch_bytes[64] = {};
+  ShardPending pending;
 };
 
 enum Slot : int {
@@ -223,6 +242,12 @@ struct SelectArgs {
   int final_sqrt;           // 1: stored value is a squared L2 distance
   const float* cert_eps;    // non-null: last compaction of a coarse scan (see select.cu); uses k
   int32_t max_count;        // > 0: no list of this launch is expected to hold more keys (picks the kernel width)
+  // Row-sharded search (the two halves of a shard's search, see tensor_scan.cuh):
+  float* bound_out;         // non-null: measure only.  Writes the bound_rank-th smallest value of the list plus
+  int32_t bound_rank;       //   bound_eps[q] (+inf when the list is shorter) and leaves the list as it is.
+  const float* bound_eps;
+  const float* ext_bound;   // with cert_eps: per query, a value (same units, error bound included) that at least k
+                            //   rows over all shards do not exceed; rows above ext_bound + eps cannot matter
 };
 int32_t launch_select(Ctx* ctx, const SelectArgs& a);
 int32_t launch_merge_topk(Ctx* ctx, const float* dist, const int64_t* ids, int32_t g, int64_t nq,

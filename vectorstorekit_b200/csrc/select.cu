@@ -150,15 +150,41 @@ __global__ void __launch_bounds__(NT) select_kernel(SelectArgs a) {
   __syncthreads();
   const int valid = s_valid;
 
+  if (a.bound_out != nullptr) {
+    // Measure only (a shard's half-way point): c_j + eps bounds the exact value of this shard's j best rows from
+    // above.  The list stays as it is; a dense list gets its count written for the compaction that follows.
+    float b = CUDART_INF_F;
+    if (valid >= a.bound_rank) {
+      const uint64_t jth = block_radix_select(key, a.bound_rank, hist, &s_bin, &s_less, &s_in_bin);
+      b = ordered_to_float((uint32_t)(jth >> 32)) + a.bound_eps[q];
+    }
+    if (threadIdx.x == 0) {
+      a.bound_out[q] = b;
+      if (a.dense_count >= 0) a.cand.count[q] = c;
+    }
+    return;
+  }
+
   uint64_t pivot = kEmptyKey - 1;  // keep every real key
   if (a.cert_eps != nullptr) {
     // Last compaction of a coarse (bounded-error) scan.  Let c_k be the k-th smallest coarse value and
     // eps the query's error bound: a row of the true top-k has coarse value <= c_k + 2 eps, so those
     // rows are kept for the exact re-scoring.  The list is complete only below the threshold t that
     // filtered the scan, so the result can be certified only if c_k + 2 eps < t.
+    // A sharded search also knows a value g that at least k rows over all shards do not exceed (exactly): rows of
+    // the overall top-k then have coarse value <= g + eps, and only those are kept.
+    float bound = CUDART_INF_F;
+    bool have = false;
     if (valid >= a.k) {
       const uint64_t kth = block_radix_select(key, a.k, hist, &s_bin, &s_less, &s_in_bin);
-      const float bound = ordered_to_float((uint32_t)(kth >> 32)) + 2.0f * a.cert_eps[q];
+      bound = ordered_to_float((uint32_t)(kth >> 32)) + 2.0f * a.cert_eps[q];
+      have = true;
+    }
+    if (a.ext_bound != nullptr && a.ext_bound[q] < CUDART_INF_F) {
+      bound = fminf(bound, a.ext_bound[q] + a.cert_eps[q]);
+      have = true;
+    }
+    if (have) {
       pivot = ((uint64_t)float_to_ordered(bound) << 32) | 0xffffffffull;
       if (pivot == kEmptyKey) pivot = kEmptyKey - 1;
       if (threadIdx.x == 0 && !(bound < a.cand.thr[q])) atomicOr(&a.cand.flags[q], 2);

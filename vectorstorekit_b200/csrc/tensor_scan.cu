@@ -1236,9 +1236,15 @@ __global__ void scatter_best_kernel(const unsigned long long* __restrict__ best,
 
 void tensor_invalidate(Index* ix) { ix->n16 = -1; }
 
-int32_t tensor_search(Index* ix, const float* q, int64_t nq, int32_t k, const float* qnorm, float* out_dist,
-                      int64_t* out_ids) {
+// The search in two halves.  `begin` runs the scan and its compactions; `finish` certifies, re-scores and orders.
+// A plain search calls them back to back.  A shard of a row-sharded search passes `bound_out` (and the number of
+// shards): the last compaction is then left to `finish`, and bound_out[q] gets a value that this shard's
+// ceil(k / shards) best rows do not exceed; the host takes the maximum over the shards (at least k rows overall lie
+// below it) and hands it to `finish`, which keeps only rows that can still reach the overall top-k.
+int32_t tensor_search_begin(Index* ix, const float* q, int64_t nq, int32_t k, const float* qnorm, int32_t shards,
+                            float* bound_out) {
   Ctx* ctx = ix->ctx;
+  ctx->pending = ShardPending{};
   VSK_TRY(tensor_prepare(ix));
   const int metric = ix->metric;
   const int dim = ix->dim, dim16 = ix->dim16;
@@ -1351,8 +1357,18 @@ int32_t tensor_search(Index* ix, const float* q, int64_t nq, int32_t k, const fl
   sel.dense_count = (int32_t)seen;
   sel.max_count = (int32_t)seen;
   sel.k = k;
-  // the compaction after the last chunk keeps what the exact re-scoring needs and certifies the query
-  if (seen == n) sel.cert_eps = eps;
+  // the compaction after the last chunk keeps what the exact re-scoring needs and certifies the query; a shard
+  // only measures its bound there and leaves that compaction to the second half
+  auto last_select = [&]() {
+    if (bound_out == nullptr) {
+      sel.cert_eps = eps;
+    } else {
+      sel.bound_out = bound_out;
+      sel.bound_rank = (k + std::max(1, shards) - 1) / std::max(1, shards);
+      sel.bound_eps = eps;
+    }
+  };
+  if (seen == n) last_select();
   VSK_TRY(launch_select(ctx, sel));
   sel.dense_count = -1;
   a.mode = SCAN_THRESHOLD;
@@ -1370,7 +1386,53 @@ int32_t tensor_search(Index* ix, const float* q, int64_t nq, int32_t k, const fl
     VSK_TRY(launch_tc<SCAN_THRESHOLD>(ctx, mq, mx, a, has_beta, pair));
     sel.max_count = schedule_max_count(seen, chunk, keep);
     seen += chunk;
-    if (seen == n) sel.cert_eps = eps;
+    if (seen == n) last_select();
+    VSK_TRY(launch_select(ctx, sel));
+  }
+  ShardPending& pd = ctx->pending;
+  pd.active = true;
+  pd.tensor = true;
+  pd.ix = ix;
+  pd.q = q;
+  pd.nq = nq;
+  pd.k = k;
+  pd.qnorm = qnorm;
+  pd.cand = cand;
+  pd.eps = eps;
+  pd.err = err;
+  pd.rr_total = rr_total;
+  pd.keep = keep;
+  pd.max_count = sel.max_count;
+  pd.need_cert = bound_out != nullptr;
+  return VSK_OK;
+}
+
+int32_t tensor_search_finish(Index* ix, const float* ext_bound, float* out_dist, int64_t* out_ids) {
+  Ctx* ctx = ix->ctx;
+  const ShardPending pd = ctx->pending;
+  ctx->pending = ShardPending{};
+  if (!pd.active || !pd.tensor || pd.ix != ix)
+    return fail(ctx, VSK_ERR_INVALID_INPUT, "no search is waiting for its second half on this index");
+  const float* q = pd.q;
+  const float* qnorm = pd.qnorm;
+  const int64_t nq = pd.nq;
+  const int32_t k = pd.k, keep = pd.keep;
+  const CandLists cand = pd.cand;
+  int32_t* err = pd.err;
+  unsigned long long* rr_total = pd.rr_total;
+  const int metric = ix->metric;
+  const int dim = ix->dim;
+  const bool i8 = ix->kind == INDEX_FLAT_I8;
+  if (pd.need_cert) {
+    SelectArgs sel{};
+    sel.cand = cand;
+    sel.nq = nq;
+    sel.keep = keep;
+    sel.dense_count = -1;
+    sel.k = k;
+    sel.cert_eps = pd.eps;
+    sel.ext_bound = ext_bound;
+    sel.max_count = pd.max_count;
     VSK_TRY(launch_select(ctx, sel));
   }
 
@@ -1428,6 +1490,12 @@ int32_t tensor_search(Index* ix, const float* q, int64_t nq, int32_t k, const fl
     if (flags[i]) bad.push_back((int32_t)i);
   if (!bad.empty()) VSK_TRY(fp32_search_subset(ix, q, bad, k, qnorm, out_dist, out_ids));
   return VSK_OK;
+}
+
+int32_t tensor_search(Index* ix, const float* q, int64_t nq, int32_t k, const float* qnorm, float* out_dist,
+                      int64_t* out_ids) {
+  VSK_TRY(tensor_search_begin(ix, q, nq, k, qnorm, 1, nullptr));
+  return tensor_search_finish(ix, nullptr, out_dist, out_ids);
 }
 
 

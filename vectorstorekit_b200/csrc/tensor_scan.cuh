@@ -11,6 +11,14 @@ namespace vsk {
 // q: [nq][dim] device; qnorm: |q| per query (cosine) or null; outputs device [nq][k].
 int32_t tensor_search(Index* ix, const float* q, int64_t nq, int32_t k, const float* qnorm,
                       float* out_dist, int64_t* out_ids);
+// The same search in two halves, for a shard of a row-sharded search.  `begin` scans and, when bound_out is given,
+// writes per query a value that this shard's ceil(k / shards) best rows do not exceed (error bound included, in the
+// units of the scan's coarse values, which depend on the query only); the host takes the maximum over the shards and
+// passes it to `finish`, which then re-scores only rows that can reach the overall top-k.  No other call may use the
+// context in between.
+int32_t tensor_search_begin(Index* ix, const float* q, int64_t nq, int32_t k, const float* qnorm, int32_t shards,
+                            float* bound_out);
+int32_t tensor_search_finish(Index* ix, const float* ext_bound, float* out_dist, int64_t* out_ids);
 // The probed lists of an IVF index scanned on the tensor cores (coarse values, certificate, exact rerank).
 // probes: [nq][nprobe] device, nearest list first.  Results go to out_dist / out_ids for every query; the queries
 // whose result could not be certified (or whose candidate list overflowed) are returned in `flagged` for the

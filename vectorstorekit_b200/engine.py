@@ -446,6 +446,31 @@ class FlatIndex(_IndexBase):
             raise DimensionMismatch(f"expected {self.dimensions}, got {queries.shape[1]}")
         return self._search(queries, int(k), filter_masks)
 
+    # The search in two halves, for one shard of a row-sharded database (``sharded.ShardedSearch``): `begin` scans
+    # and returns, per query, a value that this shard's ceil(k / shards) best rows do not exceed; the caller takes the
+    # maximum over the shards and `finish` returns this shard's rows that can still be among the overall k best
+    # (others padded with +inf / -1).  Device tensors; no other call on the device object in between.  `begin`
+    # returns while its kernels still run on the library's stream (``dev.stream``): reduce the bound on that stream
+    # (``torch.cuda.ExternalStream``) or synchronise first.
+    def shardSearchBegin(self, queries, k: int, shards: int):
+        if queries.shape[1] != self.dimensions:
+            raise DimensionMismatch(f"expected {self.dimensions}, got {queries.shape[1]}")
+        if not _is_dev(queries):
+            raise InvalidInput("the two-half search takes device tensors")
+        q = queries.contiguous().float()
+        bound = torch.empty(q.shape[0], dtype=torch.float32, device=q.device)
+        self.dev.check(self._lib.vsk_search_shard_begin_dev(self._h, _ptr(q), q.shape[0], int(k), int(shards), _ptr(bound)))
+        self._pending = (q, int(k))
+        return bound
+
+    def shardSearchFinish(self, bound):
+        q, k = self._pending
+        od = torch.empty((q.shape[0], k), dtype=torch.float32, device=q.device)
+        oi = torch.empty((q.shape[0], k), dtype=torch.int64, device=q.device)
+        self.dev.check(self._lib.vsk_search_shard_finish_dev(self._h, _ptr(bound.contiguous()), _ptr(od), _ptr(oi)))
+        self._pending = None
+        return od, oi
+
 
 class KMeansClustering:
     """``KMeansClustering.cluster`` (``Clustering/KMeansClustering.swift:48-113``) with ``.custom``

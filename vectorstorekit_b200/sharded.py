@@ -1,16 +1,25 @@
 """Row-sharded search over the ranks of a ``torch.distributed`` group (one process per GPU).
 
-Rank g holds rows ``[g*N/G, (g+1)*N/G)`` of the database and answers every query on its shard; the
-per-rank ``[Q, k]`` (distance, global id) lists are exchanged with one all-gather and merged into the
-result an unsharded search would return (ties by global id).  The reference has no sharded search;
-this is the multi-GPU form of ``batchSearch``.
+Rank g holds rows ``[g*N/G, (g+1)*N/G)`` of the database and answers every query on its shard.  Two exchanges
+make the shards' answers into the result an unsharded search would return (ties by global id):
 
-The local search and the merge are injected, so that the exchange logic can be exercised on CPU ranks
-(``gloo``) in tests; on GPUs they are ``FlatIndex.batchSearch`` and ``CUDAAccelerationEngine.mergeTopK``.
+* half-way through the local search every rank knows a value that its ``ceil(k/G)`` best rows do not exceed; the
+  element-wise maximum over the ranks (one small all-reduce) is a value that at least k rows of the whole database
+  do not exceed, and the second half of the local search keeps only rows at or below it — about ``k/G`` per rank
+  instead of k, which is what makes the per-query work after the scan shrink with the shard;
+* the per-rank ``[Q, k]`` (distance, global id) lists are exchanged with an all-to-all so that rank g receives every
+  rank's lists for ITS slice of the queries, merges that slice, and an all-gather hands every rank the whole result.
+
+The reference has no sharded search; this is the multi-GPU form of ``batchSearch``.
+
+The local search, its two halves and the merge are injected, so that the exchange logic can be exercised on CPU
+ranks (``gloo``) in tests; on GPUs they are ``FlatIndex.batchSearch``, ``FlatIndex.shardSearchBegin`` /
+``shardSearchFinish`` and ``CUDAAccelerationEngine.mergeTopK``.
 """
 from __future__ import annotations
 
-from typing import Callable, Tuple
+import contextlib
+from typing import Callable, Optional, Tuple
 
 
 def shard_range(n_total: int, rank: int, world: int) -> Tuple[int, int]:
@@ -19,32 +28,69 @@ def shard_range(n_total: int, rank: int, world: int) -> Tuple[int, int]:
 
 
 class ShardedSearch:
-    def __init__(self, local_search: Callable, merge: Callable, group=None):
+    def __init__(self, local_search: Callable, merge: Callable, group=None, local_begin: Optional[Callable] = None,
+                 local_finish: Optional[Callable] = None, stream=None, max_queries: int = 16384):
         """local_search(queries, k) -> (dist [Q,k], ids [Q,k]) with GLOBAL ids (set the index's id base to
-        the shard's first row); merge(dist [G,Q,k], ids [G,Q,k]) -> (dist [Q,k], ids [Q,k])."""
+        the shard's first row); merge(dist [G,Q,k], ids [G,Q,k]) -> (dist [Q,k], ids [Q,k]).
+        local_begin(queries, k, shards) -> bound [Q] and local_finish(bound) -> (dist, ids) are the two halves of
+        local_search (optional).  `stream`: a ``torch.cuda.Stream`` on which the collectives are ordered (the
+        stream the injected functions launch on), so that nothing has to wait on the host in between."""
         import torch.distributed as dist
         self._dist = dist
         self.local_search = local_search
+        self.local_begin, self.local_finish = local_begin, local_finish
         self.merge = merge
         self.group = group
+        self.stream = stream
+        self.max_queries = max_queries
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+
+    def _host_order(self, t):
+        # without a common stream the injected functions and the collectives run on different streams:
+        # order them through the host
+        if self.stream is None and t.is_cuda:
+            import torch
+            torch.cuda.current_stream().synchronize()
+
+    def _local(self, queries, k):
+        if self.world == 1 or self.local_begin is None or self.local_finish is None or queries is None:
+            return self.local_search(queries, k)
+        import torch
+        nq = queries.shape[0]
+        if nq > self.max_queries:      # the two-half search takes a bounded batch
+            parts = [self._local(queries[b:b + self.max_queries], k) for b in range(0, nq, self.max_queries)]
+            return torch.cat([p[0] for p in parts]), torch.cat([p[1] for p in parts])
+        bound = self.local_begin(queries, k, self.world)
+        self._dist.all_reduce(bound, op=self._dist.ReduceOp.MAX, group=self.group)
+        self._host_order(bound)
+        return self.local_finish(bound)
 
     def batchSearch(self, queries, k: int):
         import torch
-        d, i = self.local_search(queries, k)
-        if self.world == 1:
-            return d, i
-        gd = torch.empty((self.world,) + tuple(d.shape), dtype=d.dtype, device=d.device)
-        gi = torch.empty((self.world,) + tuple(i.shape), dtype=i.dtype, device=i.device)
-        if d.is_cuda:   # NCCL: one collective straight into the stacked buffer
-            self._dist.all_gather_into_tensor(gd, d.contiguous(), group=self.group)
-            self._dist.all_gather_into_tensor(gi, i.contiguous(), group=self.group)
-        else:           # gloo (CPU tests)
-            self._dist.all_gather(list(gd.unbind(0)), d.contiguous(), group=self.group)
-            self._dist.all_gather(list(gi.unbind(0)), i.contiguous(), group=self.group)
-        if d.is_cuda:
-            torch.cuda.current_stream().synchronize()
-        return self.merge(gd, gi)
+        ctx = torch.cuda.stream(self.stream) if self.stream is not None else contextlib.nullcontext()
+        with ctx:
+            d, i = self._local(queries, k)
+            if self.world == 1:
+                return d, i
+            world, nq = self.world, d.shape[0]
+            per = -(-nq // world)              # queries merged by each rank
+            if per * world != nq:              # pad to whole slices (padding rows merge to nothing)
+                dp = torch.full((per * world, k), float("inf"), dtype=d.dtype, device=d.device)
+                ip = torch.full((per * world, k), -1, dtype=i.dtype, device=i.device)
+                dp[:nq], ip[:nq] = d, i
+                d, i = dp, ip
+            d, i = d.contiguous(), i.contiguous()
+            rd, ri = torch.empty_like(d), torch.empty_like(i)     # [world][per][k]: slice of rank r's lists
+            self._dist.all_to_all_single(rd, d, group=self.group)
+            self._dist.all_to_all_single(ri, i, group=self.group)
+            self._host_order(rd)
+            md, mi = self.merge(rd.view(world, per, k), ri.view(world, per, k))
+            od, oi = torch.empty_like(d), torch.empty_like(i)
+            self._dist.all_gather_into_tensor(od, md.contiguous(), group=self.group)
+            self._dist.all_gather_into_tensor(oi, mi.contiguous(), group=self.group)
+            if d.is_cuda:
+                (self.stream or torch.cuda.current_stream()).synchronize()
+            return od[:nq], oi[:nq]
 
 
 class ShardedKMeans:
