@@ -47,12 +47,24 @@ __global__ void seg_scatter_kernel(const int32_t* keys, int64_t n, int64_t seg_l
   seg_walk(keys, begin, min(n, begin + seg_len), table + seg * nkeys, offsets, order);
 }
 
-// per key: exclusive scan of the segment counts; totals[key] = items with that key
+// per key: exclusive scan of the segment counts; totals[key] = items with that key.  Eight segments per step so
+// that the loads of a step are independent (the walk is otherwise one memory latency per segment).
 __global__ void seg_scan_kernel(int32_t* table, int64_t nseg, int32_t nkeys, int64_t* totals) {
   const int key = blockIdx.x * blockDim.x + threadIdx.x;
   if (key >= nkeys) return;
   int64_t run = 0;
-  for (int64_t s = 0; s < nseg; ++s) {
+  int64_t s = 0;
+  for (; s + 8 <= nseg; s += 8) {
+    int32_t t[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) t[u] = table[(s + u) * nkeys + key];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      table[(s + u) * nkeys + key] = (int32_t)run;
+      run += t[u];
+    }
+  }
+  for (; s < nseg; ++s) {
     const int32_t t = table[s * nkeys + key];
     table[s * nkeys + key] = (int32_t)run;
     run += t;
@@ -97,8 +109,12 @@ int32_t launch_scan_i64(Ctx* ctx, const int64_t* totals, int32_t n, int64_t* off
 int32_t launch_stable_group(Ctx* ctx, const int32_t* keys, int64_t n, int32_t nkeys, int32_t* order,
                             int64_t* offsets) {
   if (n <= 0 || nkeys <= 0) return fail(ctx, VSK_ERR_EMPTY_INPUT, "nothing to group");
-  // segment length: at least 4096 items, and long enough that the count table stays below 64 M entries
-  int64_t seg_len = std::max<int64_t>(4096, ceil_div(n * (int64_t)nkeys, 64ll << 20));
+  // Segment length: a warp walks its segment 32 items per step, each step one dependent read-modify-write of its
+  // counters, so short segments (many warps) are what makes a small grouping fast; the count table (segments x keys)
+  // bounds them from below: at most 8 M entries for the sake of the scan over it, 1 024 to 4 096 items otherwise
+  // (about 1 000 segments when there are enough items).
+  int64_t seg_len = std::min<int64_t>(4096, std::max<int64_t>(1024, ceil_div(n, 1024)));
+  seg_len = std::max<int64_t>(seg_len, ceil_div(n * (int64_t)nkeys, 8ll << 20));
   seg_len = ceil_div(seg_len, 32) * 32;
   const int64_t nseg = ceil_div(n, seg_len);
   void *table, *totals;
