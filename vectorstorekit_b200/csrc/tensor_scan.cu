@@ -567,14 +567,30 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           // Cheap test first: the smallest of the group's 32 values against the threshold.  Most groups of a late
           // chunk hold no hit for any of the warp's queries and then cost two instructions per value, not five.
           float vmin = CUDART_INF_F;
+          if (!HAS_BETA && alpha < 0.f) {
+            // value = alpha * accumulator with alpha < 0: the smallest value is alpha times the largest accumulator
+            // (the multiplication is monotone, so this is the same number), one instruction per value; the values
+            // themselves are only formed for a group that has a hit
+            float amax = v[0];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            v[j] = HAS_BETA ? fmaf(v[j], alpha, sm->beta[acc][ew][(c - c0) * 32 + j]) : v[j] * alpha;
-            vmin = fminf(vmin, v[j]);
-          }
-          if (left >= 32 && !__any_sync(0xffffffffu, qok && vmin <= thr)) {
-            m[c - c0] = 0u;
-            continue;
+            for (int j = 1; j < 32; ++j) amax = fmaxf(amax, v[j]);
+            vmin = amax * alpha;
+            if (left >= 32 && !__any_sync(0xffffffffu, qok && vmin <= thr)) {
+              m[c - c0] = 0u;
+              continue;
+            }
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] *= alpha;
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              v[j] = HAS_BETA ? fmaf(v[j], alpha, sm->beta[acc][ew][(c - c0) * 32 + j]) : v[j] * alpha;
+              vmin = fminf(vmin, v[j]);
+            }
+            if (left >= 32 && !__any_sync(0xffffffffu, qok && vmin <= thr)) {
+              m[c - c0] = 0u;
+              continue;
+            }
           }
           const uint32_t colmask = left >= 32 ? 0xffffffffu : (left > 0 ? ((1u << (int)left) - 1u) : 0u);
           uint32_t bits = 0;
