@@ -30,6 +30,8 @@
 #include <cuda.h>
 #include <math_constants.h>
 
+#include <cmath>
+
 #include "common.cuh"
 #include "tensor_scan.cuh"
 
@@ -710,7 +712,9 @@ __global__ void absmax_kernel(const float* __restrict__ x, int64_t total, unsign
 }
 
 // scale = 2^e with 2^13 < absmax * scale <= 2^14 (1 when absmax is 0 or not finite); cosine: 2^14
-__global__ void choose_scale_kernel(const unsigned* absmax, int cosine, float* scale) {
+// fold != 0 (queries against folded rows, see FoldArgs): the scale is also kept where the folded constant
+// s 2^-exp is a normal fp16 number.
+__global__ void choose_scale_kernel(const unsigned* absmax, int cosine, float* scale, int fold = 0, int fold_exp = 0) {
   float s = 16384.f;
   if (!cosine) {
     const float m = __uint_as_float(*absmax);
@@ -721,6 +725,7 @@ __global__ void choose_scale_kernel(const unsigned* absmax, int cosine, float* s
       s = ldexpf(1.f, 14 - e);
     }
   }
+  if (fold) s = fmaxf(fminf(s, ldexpf(1.f, fold_exp + 15)), ldexpf(1.f, fold_exp - 14));
   *scale = s;
 }
 
@@ -728,10 +733,22 @@ __global__ void choose_scale_kernel(const unsigned* absmax, int cosine, float* s
 // zeros to dim16, and the measured quantities the error bound needs.
 //   aux[row]   = |x|^2 (euclidean), unused otherwise
 //   nrm16[row] = |x'|, err16[row] = |s*x^ - x'|   (optional per-row outputs, used for queries)
+// Euclidean operands can carry the per-row term of the value inside the contraction.  The last 48 columns of the
+// padded width then hold, on the row side, -(s_x |x|^2 / 2) 2^exp split into three fp16 pieces (each piece stored 16
+// times as piece / 16, which keeps it in range), and on the query side the constant u = s_q 2^-exp (a power of two,
+// exact in fp16): their products add up to -s_q s_x |x|^2 / 2, so the accumulator is s_q s_x (q.x - |x|^2 / 2) and
+// the value alpha * accumulator needs no per-row term in the epilogue.
+constexpr int kFoldCols = 48;
+struct FoldArgs {
+  int side;   // 0: none, 1: rows (pieces of the term), 2: queries (the constant)
+  int col0;   // first of the kFoldCols columns
+  int exp;
+};
+
 template <int METRIC>
 __global__ void prep_rows_kernel(const float* __restrict__ x, int64_t n, int dim, int dim16, const float* scale_p,
                                  __half* __restrict__ out, float* __restrict__ aux, float* __restrict__ nrm16,
-                                 float* __restrict__ err16, float* __restrict__ nrm, PrepStats* stats) {
+                                 float* __restrict__ err16, float* __restrict__ nrm, PrepStats* stats, FoldArgs fold) {
   const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= n) return;
   const int lane = threadIdx.x & 31;
@@ -751,11 +768,28 @@ __global__ void prep_rows_kernel(const float* __restrict__ x, int64_t n, int dim
     float t = 0.f;
     if (i < dim) t = (METRIC == VSK_METRIC_COSINE) ? (__ldg(p + i) * inv) * s : __ldg(p + i) * s;
     const __half h = __float2half_rn(t);
-    out[row * dim16 + i] = h;
+    if (fold.side == 0 || i < fold.col0) out[row * dim16 + i] = h;
     const float back = __half2float(h);
     n2 = fmaf(back, back, n2);
     const float e = t - back;
     e2 = fmaf(e, e, e2);
+  }
+  if (fold.side == 1) {
+    // pieces of R = s_x (|x|^2 / 2) 2^exp: p0 = fp16(R/16), then the same of what is left, twice (the remainders are
+    // exact in fp32); what is left after three pieces is below 2^-33 R
+    const float R = ldexpf(0.5f * ss * s, fold.exp);
+    const __half p0 = __float2half_rn(R * 0.0625f);
+    const float r1 = R - 16.0f * __half2float(p0);
+    const __half p1 = __float2half_rn(r1 * 0.0625f);
+    const float r2 = r1 - 16.0f * __half2float(p1);
+    const __half p2 = __float2half_rn(r2 * 0.0625f);
+    for (int i = lane; i < kFoldCols; i += 32) {
+      const __half p = i < 16 ? p0 : (i < 32 ? p1 : p2);
+      out[row * dim16 + fold.col0 + i] = __hneg(p);
+    }
+  } else if (fold.side == 2) {
+    const __half u = __float2half_rn(ldexpf(s, -fold.exp));
+    for (int i = lane; i < kFoldCols; i += 32) out[row * dim16 + fold.col0 + i] = u;
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
@@ -786,6 +820,7 @@ struct BoundConsts {
   float max_norm;      // max |x|
   float min_norm_nz;   // min nonzero |x|
   int dim16;
+  float fold_bmax;     // folded rows: max |x|^2 / 2 (0 otherwise)
 };
 
 // eps[q]: |coarse - exact| <= eps for every row, in the units of the stored coarse value.
@@ -805,6 +840,9 @@ __global__ void bound_kernel(const float* __restrict__ qn16, const float* __rest
   const float a = qn16[q], e = qe16[q];
   float dot_err = (a * c.max_err16 + e * c.max_norm16 + e * c.max_err16) + (float)c.dim16 * 2.3841858e-7f * a * c.max_norm16;
   dot_err *= inv;
+  // folded per-row term (true units): its products pass through the same fp32 accumulation, and three fp16 pieces
+  // leave less than 2^-30 of it unrepresented
+  dot_err += ((float)c.dim16 * 2.3841858e-7f + 9.3132257e-10f) * c.fold_bmax;
   float r;
   if (METRIC == VSK_METRIC_EUCLIDEAN) {
     // + fp32 rounding of the stored |x|^2 (a sum of dim squares) and of the final multiply-add
@@ -1013,10 +1051,26 @@ int32_t make_map(Ctx* ctx, const __half* base, int64_t rows, int32_t dim16, int 
 
 template <int METRIC>
 void launch_prep(Ctx* ctx, const float* x, int64_t n, int dim, int dim16, const float* scale, __half* out, float* aux,
-                 float* nrm16, float* err16, float* nrm, PrepStats* stats) {
+                 float* nrm16, float* err16, float* nrm, PrepStats* stats, FoldArgs fold = FoldArgs{0, 0, 0}) {
   prep_rows_kernel<METRIC><<<(unsigned)ceil_div(n, 8), 256, 0, ctx->stream>>>(x, n, dim, dim16, scale, out, aux, nrm16,
-                                                                               err16, nrm, stats);
+                                                                               err16, nrm, stats, fold);
   ctx->stats.kernel_launches++;
+}
+
+// max over rows of |x|^2, summed as prep_rows_kernel sums it (one warp per row)
+__global__ void max_sq_kernel(const float* __restrict__ x, int64_t n, int dim, unsigned* out) {
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= n) return;
+  const int lane = threadIdx.x & 31;
+  const float* p = x + row * dim;
+  float ss = 0.f;
+  for (int i = lane; i < dim; i += 32) {
+    const float v = __ldg(p + i);
+    ss = fmaf(v, v, ss);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if (lane == 0) atomicMax(out, __float_as_uint(ss));
 }
 
 // fp16 operand copy of the index rows + the constants of the error bound (once per index state)
@@ -1028,12 +1082,19 @@ int32_t tensor_prepare(Index* ix) {
   ix->rows16 = nullptr;
   ix->row_aux = nullptr;
   ix->dim16 = (int32_t)(ceil_div(ix->dim, TK) * TK);
+  // Folding the per-row term into the operands (FoldArgs) pays where the epilogue, not the MMAs, sets the pace
+  // (up to four K blocks), and is free where the padding already has room for it.
+  static const int64_t fold_mode = schedule_tuning("VSK_FOLD", 1);
+  ix->fold16 = fold_mode != 0 && ix->kind != INDEX_FLAT_I8 && ix->metric == VSK_METRIC_EUCLIDEAN &&
+               (ix->dim16 / TK <= 4 || ix->dim16 - ix->dim >= kFoldCols);
+  if (ix->fold16 && ix->dim16 - ix->dim < kFoldCols) ix->dim16 += TK;
   VSK_TRY(dev_alloc(ctx, (void**)&ix->rows16, (size_t)ix->n * ix->dim16 * sizeof(__half)));
   VSK_TRY(dev_alloc(ctx, (void**)&ix->row_aux, (size_t)ix->n * sizeof(float)));
   void* p;
-  VSK_TRY(scratch(ctx, SLOT_TC_A, sizeof(PrepStats) + 16, &p));
+  VSK_TRY(scratch(ctx, SLOT_TC_A, sizeof(PrepStats) + 32, &p));
   PrepStats* st = (PrepStats*)p;
   float* scale = (float*)((char*)p + sizeof(PrepStats));
+  unsigned* max_sq = (unsigned*)((char*)p + sizeof(PrepStats) + 16);
   PrepStats init{0u, 0u, 0u, 0u, 0x7f800000u};
   VSK_CUDA(ctx, cudaMemcpyAsync(st, &init, sizeof(init), cudaMemcpyHostToDevice, ctx->stream));
   const bool cosine = ix->metric == VSK_METRIC_COSINE;
@@ -1050,9 +1111,29 @@ int32_t tensor_prepare(Index* ix) {
   }
   choose_scale_kernel<<<1, 1, 0, ctx->stream>>>(&st->absmax, cosine ? 1 : 0, scale);
   ctx->stats.kernel_launches++;
+  FoldArgs fold{0, 0, 0};
+  ix->fold_exp = 0;
+  ix->fold_bmax = 0.f;
+  if (ix->fold16) {
+    // the exponent that brings the largest piece, s_x (|x|^2 / 2) 2^exp / 16, just below 2^14
+    VSK_CUDA(ctx, cudaMemsetAsync(max_sq, 0, 4, ctx->stream));
+    max_sq_kernel<<<(unsigned)ceil_div(ix->n, 8), 256, 0, ctx->stream>>>(ix->rows, ix->n, ix->dim, max_sq);
+    ctx->stats.kernel_launches++;
+    float hmax = 0.f, hscale = 1.f;
+    VSK_CUDA(ctx, cudaMemcpyAsync(&hmax, max_sq, 4, cudaMemcpyDeviceToHost, ctx->stream));
+    VSK_CUDA(ctx, cudaMemcpyAsync(&hscale, scale, 4, cudaMemcpyDeviceToHost, ctx->stream));
+    VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    const double top = 0.5 * (double)hmax * (double)hscale / 16.0;
+    int e = 0;
+    if (top > 0.0 && std::isfinite(top)) e = 14 - (int)std::ceil(std::log2(top));
+    ix->fold_exp = std::max(-100, std::min(100, e));
+    ix->fold_bmax = 0.5f * hmax;
+    if (!std::isfinite(top)) ix->fold16 = false;   // the plain form copes with what overflows here no better, but is the known path
+    fold = FoldArgs{ix->fold16 ? 1 : 0, ix->dim16 - kFoldCols, ix->fold_exp};
+  }
   switch (ix->metric) {
     case VSK_METRIC_EUCLIDEAN:
-      launch_prep<VSK_METRIC_EUCLIDEAN>(ctx, ix->rows, ix->n, ix->dim, ix->dim16, scale, ix->rows16, ix->row_aux, nullptr, nullptr, nullptr, st);
+      launch_prep<VSK_METRIC_EUCLIDEAN>(ctx, ix->rows, ix->n, ix->dim, ix->dim16, scale, ix->rows16, ix->row_aux, nullptr, nullptr, nullptr, st, fold);
       break;
     case VSK_METRIC_COSINE:
       launch_prep<VSK_METRIC_COSINE>(ctx, ix->rows, ix->n, ix->dim, ix->dim16, scale, ix->rows16, ix->row_aux, nullptr, nullptr, nullptr, st);
@@ -1302,9 +1383,11 @@ int32_t tensor_search_begin(Index* ix, const float* q, int64_t nq, int32_t k, co
     absmax_kernel<<<296, 256, 0, ctx->stream>>>(qsrc, nq * (int64_t)dim, q_absmax);
     ctx->stats.kernel_launches++;
   }
-  choose_scale_kernel<<<1, 1, 0, ctx->stream>>>(q_absmax, cosine ? 1 : 0, q_scale);
+  const bool fold = ix->fold16;
+  const FoldArgs qfold{fold ? 2 : 0, dim16 - kFoldCols, ix->fold_exp};
+  choose_scale_kernel<<<1, 1, 0, ctx->stream>>>(q_absmax, cosine ? 1 : 0, q_scale, fold ? 1 : 0, ix->fold_exp);
   ctx->stats.kernel_launches++;
-  BoundConsts bc{ix->scale16, ix->max_xnorm16, ix->max_xerr16, ix->max_xnorm, ix->min_xnorm_nz, dim16};
+  BoundConsts bc{ix->scale16, ix->max_xnorm16, ix->max_xerr16, ix->max_xnorm, ix->min_xnorm_nz, dim16, fold ? ix->fold_bmax : 0.f};
   const unsigned bgrid = (unsigned)ceil_div(nq, 256);
   if (i8) {
     launch_prep<VSK_METRIC_DOT_PRODUCT>(ctx, qsrc, nq, dim, dim16, q_scale, q16, nullptr, qn16, qe16, qn_tmp, nullptr);
@@ -1315,7 +1398,7 @@ int32_t tensor_search_begin(Index* ix, const float* q, int64_t nq, int32_t k, co
   } else
   switch (metric) {
     case VSK_METRIC_EUCLIDEAN:
-      launch_prep<VSK_METRIC_EUCLIDEAN>(ctx, q, nq, dim, dim16, q_scale, q16, nullptr, qn16, qe16, qn_tmp, nullptr);
+      launch_prep<VSK_METRIC_EUCLIDEAN>(ctx, q, nq, dim, dim16, q_scale, q16, nullptr, qn16, qe16, qn_tmp, nullptr, qfold);
       bound_kernel<VSK_METRIC_EUCLIDEAN><<<bgrid, 256, 0, ctx->stream>>>(qn16, qe16, qn_tmp, nq, q_scale, bc, eps, alpha);
       break;
     case VSK_METRIC_COSINE:
@@ -1354,7 +1437,7 @@ int32_t tensor_search_begin(Index* ix, const float* q, int64_t nq, int32_t k, co
   a.nq = nq;
   a.kblocks = dim16 / TK;
   a.alpha = alpha;
-  a.beta = metric == VSK_METRIC_EUCLIDEAN ? ix->row_aux : nullptr;
+  a.beta = (metric == VSK_METRIC_EUCLIDEAN && !fold) ? ix->row_aux : nullptr;
   a.cand = cand;
   a.cap = kCandCap;
   a.err = err;
@@ -1674,10 +1757,12 @@ int32_t ivf_tensor_search(Index* ix, const float* q, int64_t nq, const int64_t* 
   unsigned long long* rr_total = (unsigned long long*)((char*)p + 16);
   VSK_CUDA(ctx, cudaMemsetAsync(p, 0, 64, ctx->stream));
   absmax_kernel<<<296, 256, 0, ctx->stream>>>(q, nq * (int64_t)dim, q_absmax);
-  choose_scale_kernel<<<1, 1, 0, ctx->stream>>>(q_absmax, 0, q_scale);
+  const bool fold = ix->fold16;
+  const FoldArgs qfold{fold ? 2 : 0, dim16 - kFoldCols, ix->fold_exp};
+  choose_scale_kernel<<<1, 1, 0, ctx->stream>>>(q_absmax, 0, q_scale, fold ? 1 : 0, ix->fold_exp);
   ctx->stats.kernel_launches += 2;
-  BoundConsts bc{ix->scale16, ix->max_xnorm16, ix->max_xerr16, ix->max_xnorm, ix->min_xnorm_nz, dim16};
-  launch_prep<VSK_METRIC_EUCLIDEAN>(ctx, q, nq, dim, dim16, q_scale, q16, nullptr, qn16, qe16, qn_tmp, nullptr);
+  BoundConsts bc{ix->scale16, ix->max_xnorm16, ix->max_xerr16, ix->max_xnorm, ix->min_xnorm_nz, dim16, fold ? ix->fold_bmax : 0.f};
+  launch_prep<VSK_METRIC_EUCLIDEAN>(ctx, q, nq, dim, dim16, q_scale, q16, nullptr, qn16, qe16, qn_tmp, nullptr, qfold);
   bound_kernel<VSK_METRIC_EUCLIDEAN><<<(unsigned)ceil_div(nq, 256), 256, 0, ctx->stream>>>(qn16, qe16, qn_tmp, nq, q_scale, bc, eps, alpha);
   ctx->stats.kernel_launches++;
   VSK_CUDA(ctx, cudaGetLastError());
@@ -1744,7 +1829,7 @@ int32_t ivf_tensor_search(Index* ix, const float* q, int64_t nq, const int64_t* 
   a.kblocks = dim16 / TK;
   a.mode = SCAN_THRESHOLD;
   a.alpha = alpha;
-  a.beta = ix->row_aux;
+  a.beta = fold ? nullptr : ix->row_aux;
   a.cand = cand_coarse;
   a.cap = kCandCap;
   a.err = err;
@@ -1780,7 +1865,7 @@ int32_t ivf_tensor_search(Index* ix, const float* q, int64_t nq, const int64_t* 
     a.tiles = (const int4*)p;
     a.num_tiles = total;
     a.pair_thr = pair_thr;
-    VSK_TRY(launch_tc<SCAN_THRESHOLD>(ctx, mq, mx, a, true, false));
+    VSK_TRY(launch_tc<SCAN_THRESHOLD>(ctx, mq, mx, a, !fold, false));
     if (stage == 0) {
       // the pilot appended up to 1 024 rows per query: keep the best few by coarse value and re-score only those
       SelectArgs pre = sel;
