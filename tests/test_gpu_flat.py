@@ -356,6 +356,37 @@ def test_two_half_shard_search_without_split_form(vsk, cpu_oracle):
     assert_topk_parity(gd.cpu().numpy(), gi.cpu().numpy(), rd, ri)
 
 
+@pytest.mark.parametrize("d", [96, 128, 200, 320])
+@pytest.mark.parametrize("case", ["unit", "tiny", "huge", "offset", "query_scale", "zero_rows"])
+def test_euclidean_row_term_inside_contraction(vsk, dev, cpu_oracle, d, case):
+    """Euclidean search over operand layouts with and without the |x|^2 term folded into the contraction (d <= 256
+    folds, d = 320 does not), on value ranges that stress the folded term: tiny and huge norms, a common offset (|x|^2
+    much larger than the differences that rank the rows), queries on another scale than the rows, zero rows."""
+    rng = np.random.default_rng(1000 + d)
+    n, nq, k = 20_000, 200, 10
+    x = rng.standard_normal((n, d)).astype(np.float32)
+    q = rng.standard_normal((nq, d)).astype(np.float32)
+    if case == "tiny":
+        x *= 1e-3; q *= 1e-3
+    elif case == "huge":
+        x *= 1e3; q *= 1e3
+    elif case == "offset":
+        x += 5.0; q += 5.0
+    elif case == "query_scale":
+        q *= 100.0
+    elif case == "zero_rows":
+        x[::7] = 0.0
+        q[0] = 0.0
+    ix = vsk.FlatIndex(dev, d, "euclidean")
+    try:
+        ix.add(x)
+        gd, gi = ix.batchSearch(q, k)
+    finally:
+        ix.close()
+    rd, ri = cpu_oracle.flat_search(oracle.EUCLIDEAN, q, x, k)
+    assert_topk_parity(gd, gi, rd, ri)
+
+
 def test_errors(vsk, dev, engine):
     x = np.zeros((4, 8), np.float32)
     with pytest.raises(vsk.EmptyInput):
