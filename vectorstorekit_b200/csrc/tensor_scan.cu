@@ -1648,32 +1648,33 @@ __global__ void ivf_gather_items_kernel(const int32_t* __restrict__ order, int64
 }
 
 // tiles of (stage, list): ceil(pairs / 128) x row tiles (the pilot takes only the window)
-__device__ __forceinline__ int ivf_row_tiles(int64_t len, int stage) {
+__device__ __forceinline__ int ivf_row_tiles(int64_t len, int stage, int pilot_tiles) {
   const int t = (int)((len + TN - 1) / TN);
-  return stage == 0 ? min(kIvfPilotTiles, t) : t;
+  return stage == 0 ? min(pilot_tiles, t) : t;
 }
 
 __global__ void ivf_tile_count_kernel(const int64_t* __restrict__ pair_off, int stage, int nlist,
-                                      const int64_t* __restrict__ list_off, int64_t* __restrict__ counts) {
+                                      const int64_t* __restrict__ list_off, int64_t* __restrict__ counts,
+                                      int pilot_tiles) {
   const int l = blockIdx.x * blockDim.x + threadIdx.x;
   if (l >= nlist) return;
   const int64_t pairs = pair_off[(int64_t)stage * nlist + l + 1] - pair_off[(int64_t)stage * nlist + l];
-  counts[l] = ((pairs + TM - 1) / TM) * ivf_row_tiles(list_off[l + 1] - list_off[l], stage);
+  counts[l] = ((pairs + TM - 1) / TM) * ivf_row_tiles(list_off[l + 1] - list_off[l], stage, pilot_tiles);
 }
 
 __global__ void ivf_tile_fill_kernel(const int64_t* __restrict__ pair_off, int stage, int nlist,
                                      const int64_t* __restrict__ list_off, const int64_t* __restrict__ offsets,
-                                     int4* __restrict__ tiles) {
+                                     int4* __restrict__ tiles, int pilot_tiles) {
   const int l = blockIdx.x;
   const int64_t pbeg = pair_off[(int64_t)stage * nlist + l], pairs = pair_off[(int64_t)stage * nlist + l + 1] - pbeg;
   const int64_t beg = list_off[l], len = list_off[l + 1] - beg;
-  const int ptiles = (int)((pairs + TM - 1) / TM), rtiles = ivf_row_tiles(len, stage);
+  const int ptiles = (int)((pairs + TM - 1) / TM), rtiles = ivf_row_tiles(len, stage, pilot_tiles);
   int4* out = tiles + offsets[l];
   for (int i = threadIdx.x; i < ptiles * rtiles; i += blockDim.x) {
     const int rt = i / ptiles, pt = i - rt * ptiles;
     const int64_t r0 = (int64_t)rt * TN;
     out[i] = make_int4((int)(pbeg + (int64_t)pt * TM), (int)(beg + r0),
-                       (int)min((int64_t)TN, len - r0) | ((rt < kIvfPilotTiles ? 1 : 0) << 30),
+                       (int)min((int64_t)TN, len - r0) | ((rt < pilot_tiles ? 1 : 0) << 30),
                        (int)min((int64_t)TM, pairs - (int64_t)pt * TM));
   }
 }
@@ -1769,7 +1770,8 @@ int32_t ivf_tensor_search(Index* ix, const float* q, int64_t nq, const int64_t* 
 
   // ---- stage plan: which probe ranks go with the remainder of the nearest list ----
   const double mean_len = std::max(1.0, (double)ix->n / (double)nlist);
-  const int64_t pilot_rows = (int64_t)kIvfPilotTiles * TN;
+  static const int pilot_tiles = (int)schedule_tuning("VSK_IVF_PILOT_TILES", kIvfPilotTiles);
+  const int64_t pilot_rows = (int64_t)pilot_tiles * TN;
   // rows one launch may add after the pilot's rows without (plausibly) overflowing a list: the flat schedule's rule.
   // When all probed lists fit, one launch takes every remaining rank; otherwise the ranks are split in two groups.
   const double chunk = (double)schedule_chunk(pilot_rows, keep, 0);
@@ -1848,7 +1850,7 @@ int32_t ivf_tensor_search(Index* ix, const float* q, int64_t nq, const int64_t* 
   VSK_TRY(scratch(ctx, SLOT_IVF_ITEM_CNT, (size_t)(nlist + 1) * 8, &cnt_p));
   VSK_TRY(scratch(ctx, SLOT_IVF_ITEM_OFF, (size_t)(nlist + 1) * 8, &off_p));
   for (int stage = 0; stage < nstages; ++stage) {
-    ivf_tile_count_kernel<<<(unsigned)ceil_div(nlist, 256), 256, 0, ctx->stream>>>(pair_off, stage, nlist, ix->list_offsets, (int64_t*)cnt_p);
+    ivf_tile_count_kernel<<<(unsigned)ceil_div(nlist, 256), 256, 0, ctx->stream>>>(pair_off, stage, nlist, ix->list_offsets, (int64_t*)cnt_p, pilot_tiles);
     VSK_TRY(launch_scan_i64(ctx, (const int64_t*)cnt_p, nlist, (int64_t*)off_p));
     int64_t total = 0;
     VSK_CUDA(ctx, cudaMemcpyAsync(&total, (int64_t*)off_p + nlist, 8, cudaMemcpyDeviceToHost, ctx->stream));
@@ -1857,7 +1859,7 @@ int32_t ivf_tensor_search(Index* ix, const float* q, int64_t nq, const int64_t* 
     if (total <= 0) continue;
     if (total > 0x7fffffffLL) return fail(ctx, VSK_ERR_INVALID_BUFFER_SIZE, "too many list tiles in one launch");
     VSK_TRY(scratch(ctx, SLOT_X_TMP, (size_t)total * sizeof(int4), &p));
-    ivf_tile_fill_kernel<<<(unsigned)nlist, 128, 0, ctx->stream>>>(pair_off, stage, nlist, ix->list_offsets, (const int64_t*)off_p, (int4*)p);
+    ivf_tile_fill_kernel<<<(unsigned)nlist, 128, 0, ctx->stream>>>(pair_off, stage, nlist, ix->list_offsets, (const int64_t*)off_p, (int4*)p, pilot_tiles);
     ivf_coarse_threshold_kernel<<<qgrid, 256, 0, ctx->stream>>>(cand.thr, qn_tmp, eps, ix->max_xnorm, nq, thr_coarse,
                                                                 nullptr, cand.flags);
     ivf_pair_threshold_kernel<<<(unsigned)ceil_div(nitems, 256), 256, 0, ctx->stream>>>(pair_info, nitems, thr_coarse, pair_thr);
