@@ -50,6 +50,9 @@ WORKLOADS = {
                 nprobe=32, iters=5, name="ivf-euclidean-1M-d128-nlist1024-nprobe32-q2048-k10"),
     "c4": dict(kind="sq8", metric="dotProduct", rows=50_000_000, dim=384, queries=10_000, k=10, cfg=4,
                name="int8-dot-50M-d384-q10000-k10"),
+    # one eighth of c4's rows with all of its queries: what one rank of the 8-GPU run searches
+    "c4e": dict(kind="sq8", metric="dotProduct", rows=6_250_000, dim=384, queries=10_000, k=10, cfg=4,
+                name="int8-dot-6.25M-d384-q10000-k10"),
     "c4s": dict(kind="sq8", metric="dotProduct", rows=2_000_000, dim=384, queries=2_048, k=10, cfg=4,
                 name="int8-dot-2M-d384-q2048-k10"),
     "c5": dict(kind="filtered", metric="manhattan", rows=5_000_000, dim=256, queries=10_000, k=50, cfg=5,
@@ -251,6 +254,11 @@ class Bench:
             import torch.distributed as dist
             from vectorstorekit_b200.sharded import ShardedKMeans
             init = gen_rows(t, wl, 0, wl["nlist"], self.device, centres)        # the first rows of the whole database
+            # the first collective of a process sets up NCCL's channels (hundreds of ms): not part of an iteration
+            warm = t.zeros(1, device=self.device)
+            dist.all_reduce(warm)
+            t.cuda.synchronize()
+            t0 = time.perf_counter()
             trainer = self.vsk.KMeansTrainer(self.dev, self.rows, wl["nlist"])
             cent, _, _ = ShardedKMeans(trainer.step, trainer.finish).cluster(init, wl["iters"], -1.0)
             trainer.close()

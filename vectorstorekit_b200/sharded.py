@@ -120,9 +120,13 @@ class ShardedKMeans:
                 for t in (sums, counts, inert):
                     self._dist.all_reduce(t, group=self.group)
             cent = self.finish(sums, counts, cent)
-            inertia = float(inert.sum())
             it += 1
-            if tolerance >= 0 and abs(inertia - prev) < tolerance:     # KMeansClustering.swift:98
+            if tolerance < 0:          # a fixed number of iterations: nothing to decide, nothing to read back
+                continue
+            inertia = float(inert.sum())
+            if abs(inertia - prev) < tolerance:     # KMeansClustering.swift:98
                 break
             prev = inertia
+        if tolerance < 0 and it > 0:
+            inertia = float(inert.sum())
         return cent, it, inertia
