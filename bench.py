@@ -476,8 +476,13 @@ def main():
     ap.add_argument("--path", default="tensor", choices=["tensor", "fp32"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--queries", type=int, default=0,
+                    help="override the workload's batch size (a few queries show the HBM-bound regime of a scan)")
     args = ap.parse_args()
-    wl = WORKLOADS[args.workload]
+    wl = dict(WORKLOADS[args.workload])
+    if args.queries > 0:
+        wl["queries"] = args.queries
+        wl["name"] = wl["name"] + f"-batch{args.queries}"
     if args.impl == "reference":
         return run_reference(args, wl)
 
@@ -587,6 +592,21 @@ def main():
         roof.update(unit="T lane-instr/s", achieved=b.flops * args.steps / secs / 1e12 if secs > 0 else None,
                     peak=sm * 128 * 1.965e9 / 1e12, peak_source="nominal: SMs x 128 FP32 lanes x 1965 MHz")
     roof["frac"] = roof["achieved"] / roof["peak"] if roof.get("achieved") else None
+    if wl["kind"] in ("flat", "sq8", "filtered") and secs > 0:
+        # the HBM view of the same launches: the stored operand the scan reads (fp16 images on the tensor path, else
+        # fp32 rows or int8 codes) crossing HBM once per batch; this is what bounds a batch of a few queries
+        if args.path == "tensor" and b.bound == "tensor":
+            per_row = (wl["dim"] + 63) // 64 * 64 * 2
+        else:
+            per_row = wl["dim"] * (1 if wl["kind"] == "sq8" else 4)
+            if wl["kind"] == "filtered":
+                # every row's 8-byte mask, and the rows some query of the batch may see: half of them under one
+                # one-hot mask, 1 - 2^-g of them under g distinct ones
+                distinct = len(set(b.qmasks.cpu().tolist())) if b.qmasks is not None else 64
+                per_row = per_row * (1.0 - 0.5 ** min(distinct, 64)) + 8
+        gbs = (b.hi - b.lo) * per_row * args.steps / secs / 1e9
+        roof["hbm_view"] = {"bytes_per_row": per_row, "achieved_gbs": gbs, "peak_gbs": pk["hbm_gbs"],
+                            "frac": gbs / pk["hbm_gbs"]}
     if wl["kind"] == "flat" and args.path == "tensor" and b.bound == "tensor":
         # DRAM bytes per scan launch, from the ncu capture of the reduced workload (profiles/tc_scan_kernel__*):
         # dram__bytes_read equals the fp16 rows of the launch read once plus the query operand, dram__bytes_write is

@@ -327,6 +327,10 @@ static int32_t filtered_grouped_search(Index* ix, const float* q, int64_t nq, in
     padded += ceil_div(sz, pick_query_tile(sz)) * pick_query_tile(sz);
   }
   if (groups > 256 || (double)padded * 0.6 > (double)(ceil_div(nq, 128) * 128)) return VSK_OK;
+  // A batch small enough for the streaming scan is bound by the bytes it reads: one pass over all rows (rows that
+  // no query may see are skipped there too) beats one pass over the eligible rows per group, unless there is
+  // only one group.
+  if (nq <= kStreamScanMaxQueries && groups > 1) return VSK_OK;
   *handled = true;
   void *dperm, *drows, *dcount;
   VSK_TRY(scratch(ctx, SLOT_FILTER_PERM, (size_t)nq * 4, &dperm));

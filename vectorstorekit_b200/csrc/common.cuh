@@ -214,6 +214,12 @@ struct ExactScanArgs {
   unsigned long long* best; // SCAN_ARGMIN: [nq] smallest (value, row) key, pre-set to all ones
 };
 int32_t launch_exact_scan(Ctx* ctx, const ExactScanArgs& a);
+// ---- stream_scan.cu ------------------------------------------------------------------------
+// The same scan for a batch of at most kStreamScanMaxQueries queries over fp32 rows, candidate modes only: queries
+// in shared memory, every row streamed from HBM once.  launch_exact_scan hands such launches over.
+constexpr int kStreamScanMaxQueries = 8;
+bool stream_scan_applies(const ExactScanArgs& a);
+int32_t launch_stream_scan(Ctx* ctx, const ExactScanArgs& a);
 int32_t launch_row_norms(Ctx* ctx, const float* x, int64_t n, int32_t dim, int squared, float* out);
 
 // ---- group.cu ----------------------------------------------------------------------------
