@@ -89,3 +89,84 @@ def test_filter_that_matches_almost_nothing(vsk, dev, cpu_oracle):
     rd, ri = cpu_oracle.flat_search(oracle.EUCLIDEAN, q, x, 5, rm, qm)
     assert_topk_parity(gd, gi, rd, ri)
     assert sorted(gi[0][gi[0] >= 0].tolist()) == [11, 4_999] and np.all(gi[1] == -1)
+
+
+def _mixture(rng, n, d, centres, sigma=0.1):
+    c = rng.integers(0, centres.shape[0], n)
+    return (centres[c] + sigma * rng.standard_normal((n, d))).astype(np.float32)
+
+
+@pytest.mark.parametrize("cfg", [(60_000, 128, 256, 16, 10), (20_000, 32, 64, 8, 10), (3_000, 17, 10, 10, 25),
+                                 (40_000, 130, 40, 3, 100)])
+@pytest.mark.parametrize("nq", [1, 2, 7, 16, 17])
+def test_ivf_search_of_a_few_queries(vsk, dev, cpu_oracle, cfg, nq):
+    """``IVFIndex.search`` is a one-query call: a handful of queries stream the rows of their own probed lists
+    (per-query slices of one row list) instead of going through the list-major tiles.  Parity on shared state,
+    as for the batch search: the GPU's centroids and list membership are handed to the oracle."""
+    n, d, nlist, nprobe, k = cfg
+    rng = np.random.default_rng(n + nlist)
+    centres = rng.standard_normal((max(nlist, 4), d)).astype(np.float32)
+    x = _mixture(rng, n, d, centres)
+    q = _mixture(rng, nq, d, centres)
+    ix = vsk.IVFIndex(dev, d, numberOfCentroids=nlist, numberOfProbes=nprobe, maxIterations=4, tolerance=-1.0)
+    try:
+        ix.train(x)
+        ix.insert(x)
+        asg = ix.assignments()
+        gd, gi = ix.batchSearch(q, k)
+        rd, ri = cpu_oracle.ivf_search(q, x, ix.centroids, asg, nprobe, k)
+        assert_topk_parity(gd, gi, rd, ri)
+        if nq <= 7:
+            # `.exact` probes every list and equals the flat search (IVFIndexTests.swift:203-260)
+            ed, ei = ix.batchSearch(q, k, vsk.SearchStrategy.exact)
+            fd, fi = cpu_oracle.flat_search(oracle.EUCLIDEAN, q, x, k)
+            assert_topk_parity(ed, ei, fd, fi)
+    finally:
+        ix.close()
+
+
+def test_ivf_few_queries_with_id_base_and_short_lists(vsk, dev, cpu_oracle):
+    """Fewer rows in the probed lists than k: the tail of a result row is (+inf, -1); ids carry the index's
+    id base (a shard's first global row)."""
+    rng = np.random.default_rng(8)
+    centres = (10.0 * rng.standard_normal((50, 8))).astype(np.float32)
+    x = _mixture(rng, 400, 8, centres)
+    q = _mixture(rng, 3, 8, centres)
+    ix = vsk.IVFIndex(dev, 8, numberOfCentroids=50, numberOfProbes=2, maxIterations=3, tolerance=-1.0)
+    try:
+        ix.train(x)
+        ix.insert(x)
+        ix.set_id_base(1_000_000)
+        asg = ix.assignments()
+        gd, gi = ix.batchSearch(q, 40)
+        rd, ri = cpu_oracle.ivf_search(q, x, ix.centroids, asg, 2, 40)
+        ri = np.where(ri >= 0, ri + 1_000_000, ri)
+        assert_topk_parity(gd, gi, rd, ri)
+        assert np.any(gi < 0)
+    finally:
+        ix.close()
+
+
+def test_ivf_few_queries_adversarial_row_order(vsk, dev, cpu_oracle):
+    """Rows stored so that, inside a list, every next row is nearer to queries 0 and 2 than all rows before it: the
+    threshold never filters, their candidate lists overflow and the two are re-run with smaller chunks (a subset
+    of the batch whose list positions differ from its query numbers), while query 1 finishes at the first try."""
+    n, d = 60_000, 8
+    rng = np.random.default_rng(12)
+    x = (1e-3 * rng.standard_normal((n, d))).astype(np.float32)
+    x[:, 0] += (2.0 - np.arange(n) / n).astype(np.float32)
+    q = np.zeros((3, d), np.float32)
+    q[1] = x[n // 3] + 0.01
+    q[2, 1] = 1e-3
+    ix = vsk.IVFIndex(dev, d, numberOfCentroids=4, numberOfProbes=4, maxIterations=5, tolerance=-1.0)
+    try:
+        ix.train(x)
+        ix.insert(x)
+        asg = ix.assignments()
+        before = dev.stats()["fallback_queries"]
+        gd, gi = ix.batchSearch(q, 10)
+        assert dev.stats()["fallback_queries"] - before >= 2
+        rd, ri = cpu_oracle.ivf_search(q, x, ix.centroids, asg, 4, 10)
+        assert_topk_parity(gd, gi, rd, ri)
+    finally:
+        ix.close()

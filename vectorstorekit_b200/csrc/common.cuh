@@ -212,12 +212,19 @@ struct ExactScanArgs {
   float* out;               // SCAN_MATRIX: [nq][ld_out]
   int64_t ld_out;
   unsigned long long* best; // SCAN_ARGMIN: [nq] smallest (value, row) key, pre-set to all ones
+  // Per-query row lists (streaming scan only; the probed lists of an IVF search for a few queries): query i
+  // (q_subset[m] for list position m) scans entries [seg_begin[i], seg_begin[i] + seg_count[i]) of x_rows, and
+  // row_begin / row_end index positions inside each query's own slice.  Null otherwise.
+  const int64_t* seg_begin;
+  const int32_t* seg_count;
 };
 int32_t launch_exact_scan(Ctx* ctx, const ExactScanArgs& a);
 // ---- stream_scan.cu ------------------------------------------------------------------------
 // The same scan for a batch of at most kStreamScanMaxQueries queries over fp32 rows, candidate modes only: queries
 // in shared memory, every row streamed from HBM once.  launch_exact_scan hands such launches over.
 constexpr int kStreamScanMaxQueries = 8;
+constexpr int kStreamScanMaxSegQueries = 16;   // with per-query row lists (one grid row per query): beyond this the
+                                               // list-major tiles, which read a list once for all its queries, win
 bool stream_scan_applies(const ExactScanArgs& a);
 int32_t launch_stream_scan(Ctx* ctx, const ExactScanArgs& a);
 int32_t launch_row_norms(Ctx* ctx, const float* x, int64_t n, int32_t dim, int squared, float* out);

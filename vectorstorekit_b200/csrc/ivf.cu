@@ -408,6 +408,91 @@ int32_t ivf_build_dev(Ctx* ctx, const float* centroids, int32_t nlist, const flo
   return VSK_OK;
 }
 
+// ---- a few queries: each streams its own probed lists ------------------------------------------------------
+// IVFIndex.search is a one-query call (IVFIndex.swift:124-202).  For a handful of queries the list-major tiles
+// above pad every (list, query) pair to 32 query rows; here every query gets the row numbers of its probed
+// lists as a slice of one row list and the streaming scan reads each of those rows once (for one query over
+// 32 of 4 096 lists of a 10 M x 128 index: 40 MB).  Keys carry stored-row numbers; the original row ids are put in
+// at the end.
+
+// Entry (query, probe) -> positions [dst, dst + len) of the row list hold stored rows lbeg .. lbeg + len.
+__global__ void ivf_expand_lists_kernel(const int64_t* __restrict__ triples, int32_t* __restrict__ rows) {
+  const int64_t dst = triples[3 * blockIdx.x], lbeg = triples[3 * blockIdx.x + 1], len = triples[3 * blockIdx.x + 2];
+  for (int64_t t = threadIdx.x; t < len; t += blockDim.x) rows[dst + t] = (int32_t)(lbeg + t);
+}
+
+__global__ void ivf_stored_to_ids_kernel(int64_t* ids, int64_t count, const int32_t* __restrict__ list_rows,
+                                         int64_t id_base) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < count && ids[i] >= 0) ids[i] = (int64_t)list_rows[ids[i]] + id_base;
+}
+
+constexpr int64_t kIvfFewMaxEntries = 32ll << 20;   // row-list entries (128 MB) the few-query path may use
+
+// *handled = false (nothing done) when the batch does not fit this path.
+int32_t ivf_search_few(Ctx* ctx, Index* ix, const float* q, int64_t nq, const int64_t* probes, int32_t nprobe,
+                       int32_t k, float* out_dist, int64_t* out_ids, bool* handled) {
+  *handled = false;
+  ExactScanArgs a{};
+  a.metric = VSK_METRIC_EUCLIDEAN;
+  a.mode = SCAN_DENSE;
+  a.q = q;
+  a.x = ix->rows;
+  a.dim = ix->dim;
+  a.nq = nq;
+  std::vector<int64_t> ph((size_t)nq * nprobe);
+  VSK_CUDA(ctx, cudaMemcpyAsync(ph.data(), probes, ph.size() * 8, cudaMemcpyDeviceToHost, ctx->stream));
+  VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  std::vector<int64_t> triples, seg_begin((size_t)nq);
+  std::vector<int32_t> seg_count((size_t)nq);
+  triples.reserve(ph.size() * 3);
+  int64_t total = 0, longest = 0;
+  for (int64_t i = 0; i < nq; ++i) {
+    seg_begin[(size_t)i] = total;
+    int64_t cnt = 0;
+    for (int p = 0; p < nprobe; ++p) {
+      const int64_t l = ph[(size_t)(i * nprobe + p)];
+      if (l < 0 || l >= ix->nlist) continue;
+      const int64_t lbeg = ix->list_offsets_h[(size_t)l], len = ix->list_offsets_h[(size_t)l + 1] - lbeg;
+      if (len <= 0) continue;
+      triples.push_back(total + cnt);
+      triples.push_back(lbeg);
+      triples.push_back(len);
+      cnt += len;
+    }
+    if (cnt > 0x7fffffffLL) return VSK_OK;
+    seg_count[(size_t)i] = (int32_t)cnt;
+    total += cnt;
+    longest = std::max(longest, cnt);
+  }
+  if (total > kIvfFewMaxEntries) return VSK_OK;
+  void *drows, *dtri, *dbeg, *dcnt;
+  VSK_TRY(scratch(ctx, SLOT_IVF_ORDER, (size_t)std::max<int64_t>(total, 1) * 4, &drows));
+  VSK_TRY(scratch(ctx, SLOT_IVF_PAIR_OFF, std::max<size_t>(triples.size(), 3) * 8, &dtri));
+  VSK_TRY(scratch(ctx, SLOT_IVF_ITEM_OFF, (size_t)nq * 8, &dbeg));
+  VSK_TRY(scratch(ctx, SLOT_IVF_ITEM_CNT, (size_t)nq * 4, &dcnt));
+  a.x_rows = (const int32_t*)drows;
+  a.seg_begin = (const int64_t*)dbeg;
+  a.seg_count = (const int32_t*)dcnt;
+  if (!stream_scan_applies(a)) return VSK_OK;
+  *handled = true;
+  if (!triples.empty())
+    VSK_CUDA(ctx, cudaMemcpyAsync(dtri, triples.data(), triples.size() * 8, cudaMemcpyHostToDevice, ctx->stream));
+  VSK_CUDA(ctx, cudaMemcpyAsync(dbeg, seg_begin.data(), (size_t)nq * 8, cudaMemcpyHostToDevice, ctx->stream));
+  VSK_CUDA(ctx, cudaMemcpyAsync(dcnt, seg_count.data(), (size_t)nq * 4, cudaMemcpyHostToDevice, ctx->stream));
+  if (!triples.empty()) {
+    ivf_expand_lists_kernel<<<(unsigned)(triples.size() / 3), 256, 0, ctx->stream>>>((const int64_t*)dtri, (int32_t*)drows);
+    ctx->stats.kernel_launches++;
+    VSK_CUDA(ctx, cudaGetLastError());
+  }
+  VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));   // the host vectors are locals
+  VSK_TRY(fp32_topk(ctx, a, longest, nq, nullptr, k, 0, out_dist, out_ids, 0));
+  ivf_stored_to_ids_kernel<<<(unsigned)ceil_div(nq * k, 256), 256, 0, ctx->stream>>>(out_ids, nq * k, ix->list_rows, ix->id_base);
+  ctx->stats.kernel_launches++;
+  VSK_CUDA(ctx, cudaGetLastError());
+  return VSK_OK;
+}
+
 int32_t ivf_search_dev(Index* ix, const float* q, int64_t nq, int32_t k, int32_t nprobe, float* out_dist,
                        int64_t* out_ids) {
   Ctx* ctx = ix->ctx;
@@ -465,6 +550,11 @@ int32_t ivf_search_dev(Index* ix, const float* q, int64_t nq, int32_t k, int32_t
                                      out_dist + b * k, out_ids + b * k, false));
       }
       continue;
+    }
+    if (bn <= kStreamScanMaxSegQueries) {
+      bool few = false;
+      VSK_TRY(ivf_search_few(ctx, ix, qb, bn, (const int64_t*)pi, nprobe, k, out_dist + b * k, out_ids + b * k, &few));
+      if (few) continue;
     }
     VSK_TRY(ivf_search_positions(ctx, ix, qb, bn, nullptr, (const int64_t*)pi, nprobe, k, out_dist + b * k,
                                  out_ids + b * k, false));

@@ -20,7 +20,8 @@ namespace vsk {
 namespace {
 
 constexpr int SS_THREADS = 256;
-constexpr int SS_ROWS = 2;   // rows per warp step: a staged query value is used for both
+// Rows per warp step (template parameter ROWS): a staged query value is used for all of them.  Two by default;
+// four for one or two queries over rows of at most 1 KB, where two rows leave too few loads in flight per lane.
 
 // v[0..V) per lane -> the total over the warp of v[j] on the lanes with (lane >> (5 - log2 V)) == j, in v[0].
 // Each stage halves the values a lane still carries: a lane keeps the half its lane bit selects and hands the
@@ -46,8 +47,17 @@ __device__ __forceinline__ void warp_reduce_scatter(float (&v)[V], int lane) {
 template <int V> struct Log2 { static constexpr int value = 1 + Log2<V / 2>::value; };
 template <> struct Log2<1> { static constexpr int value = 0; };
 
-template <int METRIC, int MODE, int NQ, bool VEC>
+// SEG: every query scans its own slice of the row list (NQ = 1; blockIdx.y is the query's position).
+template <int METRIC, int MODE, int NQ, bool VEC, bool SEG, int SS_ROWS>
 __global__ void __launch_bounds__(SS_THREADS, NQ > 4 ? 3 : 4) stream_scan_kernel(ExactScanArgs a) {
+  static_assert(!SEG || NQ == 1, "per-query row lists are scanned one query per grid row");
+  const int qb = SEG ? (int)blockIdx.y : 0;            // first query position of this CTA
+  const int nq_here = SEG ? 1 : (int)a.nq;             // queries of this CTA
+  // slices belong to queries, not to list positions (a re-run of some queries keeps their slices)
+  const int qseg = SEG ? (a.q_subset ? a.q_subset[qb] : qb) : 0;
+  const int32_t* x_rows = SEG ? a.x_rows + a.seg_begin[qseg] : a.x_rows;
+  // positions at or beyond the slice's length hold no row (a dense chunk still owns their slots)
+  const int64_t live_end = SEG ? min(a.row_end, (int64_t)a.seg_count[qseg]) : a.row_end;
   extern __shared__ __align__(16) float sq[];   // [NQ][dim]; rows of queries beyond nq are zero
   __shared__ float s_thr[NQ], s_qn[NQ];
   __shared__ uint64_t s_qm[NQ];
@@ -57,17 +67,17 @@ __global__ void __launch_bounds__(SS_THREADS, NQ > 4 ? 3 : 4) stream_scan_kernel
   for (int idx = threadIdx.x; idx < NQ * dim; idx += SS_THREADS) {
     const int i = idx / dim, k = idx - i * dim;
     float v = 0.f;
-    if (i < a.nq) {
-      const int64_t qi = a.q_subset ? (int64_t)a.q_subset[i] : i;
+    if (i < nq_here) {
+      const int64_t qi = a.q_subset ? (int64_t)a.q_subset[qb + i] : qb + i;
       v = a.q[qi * dim + k];
     }
     sq[idx] = v;
   }
   if (threadIdx.x < NQ) {
     const int i = threadIdx.x;
-    const bool mok = i < a.nq;
-    const int64_t qi = mok ? (a.q_subset ? (int64_t)a.q_subset[i] : i) : 0;
-    s_thr[i] = (MODE == SCAN_THRESHOLD && mok) ? a.cand.thr[i] : 0.f;
+    const bool mok = i < nq_here;
+    const int64_t qi = mok ? (a.q_subset ? (int64_t)a.q_subset[qb + i] : qb + i) : 0;
+    s_thr[i] = (MODE == SCAN_THRESHOLD && mok) ? a.cand.thr[qb + i] : 0.f;
     s_qn[i] = (METRIC == VSK_METRIC_COSINE && mok) ? a.qnorm[qi] : 0.f;
     s_qm[i] = mok ? (a.q_masks ? a.q_masks[qi] : ~0ull) : 0ull;
   }
@@ -93,9 +103,10 @@ __global__ void __launch_bounds__(SS_THREADS, NQ > 4 ? 3 : 4) stream_scan_kernel
     for (int r = 0; r < SS_ROWS; ++r) {
       const int64_t n = n0 + r;
       ok[r] = n < a.row_end;
-      rid[r] = ok[r] ? (a.x_rows ? (uint32_t)a.x_rows[n] : (uint32_t)n) : 0u;
-      rmask[r] = (a.row_masks && ok[r]) ? a.row_masks[rid[r]] : ~0ull;
-      live[r] = ok[r] && (rmask[r] & any_mask) != 0;   // a row no query may see is not read
+      const bool has = n < live_end;
+      rid[r] = has ? (x_rows ? (uint32_t)x_rows[n] : (uint32_t)n) : 0u;
+      rmask[r] = (a.row_masks && has) ? a.row_masks[rid[r]] : ~0ull;
+      live[r] = has && (rmask[r] & any_mask) != 0;     // a row no query may see is not read
     }
     float acc[V];
 #pragma unroll
@@ -167,41 +178,59 @@ __global__ void __launch_bounds__(SS_THREADS, NQ > 4 ? 3 : 4) stream_scan_kernel
 #pragma unroll
     for (int t = 1; t < SS_ROWS; ++t)
       if (r == t) { okr = ok[t]; liver = live[t]; ridr = rid[t]; rmaskr = rmask[t]; }
-    if (!okr || i >= a.nq) continue;
+    if (!okr || i >= nq_here) continue;
     float v = acc[0];
     if (METRIC == VSK_METRIC_COSINE) v = 1.0f - v / (s_qn[i] * (liver ? a.xnorm[ridr] : 0.f) + 1e-8f);
     else if (METRIC == VSK_METRIC_DOT_PRODUCT) v = -v;
     const bool elig = liver && (rmaskr & s_qm[i]) != 0;
     if (MODE == SCAN_DENSE) {
-      a.cand.keys[(int64_t)i * kCandCap + (n0 + r - a.row_begin)] = elig ? make_key(v, ridr) : kEmptyKey;
+      a.cand.keys[(int64_t)(qb + i) * kCandCap + (n0 + r - a.row_begin)] = elig ? make_key(v, ridr) : kEmptyKey;
     } else {
       if (elig && v <= s_thr[i]) {
-        const int pos = atomicAdd(&a.cand.count[i], 1);
-        if (pos < kCandCap) a.cand.keys[(int64_t)i * kCandCap + pos] = make_key(v, ridr);
+        const int pos = atomicAdd(&a.cand.count[qb + i], 1);
+        if (pos < kCandCap) a.cand.keys[(int64_t)(qb + i) * kCandCap + pos] = make_key(v, ridr);
       }
     }
   }
 }
 
-template <int METRIC, int MODE, int NQ>
-int32_t launch_nq(Ctx* ctx, const ExactScanArgs& a, bool vec) {
+template <int METRIC, int MODE, int NQ, int ROWS>
+int32_t launch_rows(Ctx* ctx, const ExactScanArgs& a, bool vec) {
   const int64_t rows = a.row_end - a.row_begin;
   const int warps = SS_THREADS / 32;
-  const int64_t want = ceil_div(rows, (int64_t)warps * SS_ROWS);
-  const int64_t cap = (int64_t)ctx->prop.multiProcessorCount * (NQ > 4 ? 3 : 4);
-  const unsigned grid = (unsigned)std::max<int64_t>(1, std::min(want, cap));
+  const int64_t want = ceil_div(rows, (int64_t)warps * ROWS);
+  const int nseg = a.seg_begin ? (int)a.nq : 1;   // per-query row lists: grid (CTAs over the chunk's positions, queries)
+  const int64_t cap = std::max<int64_t>(1, (int64_t)ctx->prop.multiProcessorCount * (NQ > 4 ? 3 : 4) / nseg);
+  dim3 grid((unsigned)std::max<int64_t>(1, std::min(want, cap)), (unsigned)nseg);
   const size_t smem = (size_t)NQ * a.dim * sizeof(float);
   prof_begin(ctx);
-  if (vec) stream_scan_kernel<METRIC, MODE, NQ, true><<<grid, SS_THREADS, smem, ctx->stream>>>(a);
-  else stream_scan_kernel<METRIC, MODE, NQ, false><<<grid, SS_THREADS, smem, ctx->stream>>>(a);
+  if constexpr (NQ == 1) {
+    if (a.seg_begin) {
+      if (vec) stream_scan_kernel<METRIC, MODE, 1, true, true, ROWS><<<grid, SS_THREADS, smem, ctx->stream>>>(a);
+      else stream_scan_kernel<METRIC, MODE, 1, false, true, ROWS><<<grid, SS_THREADS, smem, ctx->stream>>>(a);
+    }
+  }
+  if (!a.seg_begin) {
+    if (vec) stream_scan_kernel<METRIC, MODE, NQ, true, false, ROWS><<<grid, SS_THREADS, smem, ctx->stream>>>(a);
+    else stream_scan_kernel<METRIC, MODE, NQ, false, false, ROWS><<<grid, SS_THREADS, smem, ctx->stream>>>(a);
+  }
   prof_end(ctx);
   ctx->stats.kernel_launches++;
   VSK_CUDA(ctx, cudaGetLastError());
   return VSK_OK;
 }
 
+template <int METRIC, int MODE, int NQ>
+int32_t launch_nq(Ctx* ctx, const ExactScanArgs& a, bool vec) {
+  if constexpr (NQ <= 2) {
+    if (a.dim <= 256) return launch_rows<METRIC, MODE, NQ, 4>(ctx, a, vec);
+  }
+  return launch_rows<METRIC, MODE, NQ, 2>(ctx, a, vec);
+}
+
 template <int METRIC, int MODE>
 int32_t launch_mode(Ctx* ctx, const ExactScanArgs& a, bool vec) {
+  if (a.seg_begin) return launch_nq<METRIC, MODE, 1>(ctx, a, vec);   // one query per grid row
   if (a.nq <= 1) return launch_nq<METRIC, MODE, 1>(ctx, a, vec);
   if (a.nq <= 2) return launch_nq<METRIC, MODE, 2>(ctx, a, vec);
   if (a.nq <= 4) return launch_nq<METRIC, MODE, 4>(ctx, a, vec);
@@ -221,6 +250,10 @@ bool stream_scan_applies(const ExactScanArgs& a) {
   if (off) return false;
   if (a.x_codes != nullptr || a.x == nullptr) return false;                 // fp32 rows only
   if (a.mode != SCAN_DENSE && a.mode != SCAN_THRESHOLD) return false;       // candidate modes only
+  if (a.seg_begin) {
+    return a.x_rows != nullptr && a.seg_count != nullptr && a.nq >= 1 && a.nq <= kStreamScanMaxSegQueries &&
+           (size_t)a.dim * sizeof(float) <= 48 * 1024;
+  }
   if (a.nq < 1 || a.nq > kStreamScanMaxQueries) return false;
   if ((size_t)kStreamScanMaxQueries * a.dim * sizeof(float) > 48 * 1024) return false;   // queries stay in shared memory
   return true;
