@@ -551,7 +551,9 @@ int32_t vsk_pq_index_create(vsk_ctx* c, int32_t dim, int32_t segments, int32_t c
   ix->pq_ksub = codebook_size;
   const size_t cb_bytes = (size_t)codebook_size * dim * 4;
   int32_t st = dev_alloc(ctx, (void**)&ix->pq_codebooks, cb_bytes);
-  if (st == VSK_OK && cudaMemcpy(ix->pq_codebooks, codebooks, cb_bytes, cudaMemcpyDefault) != cudaSuccess)
+  // on the context's stream, which the kernels that read the codebooks run on (it does not wait for the legacy stream)
+  if (st == VSK_OK && (cudaMemcpyAsync(ix->pq_codebooks, codebooks, cb_bytes, cudaMemcpyDefault, ctx->stream) != cudaSuccess ||
+                       cudaStreamSynchronize(ctx->stream) != cudaSuccess))
     st = fail(ctx, VSK_ERR_EXECUTION_FAILED, "copy of the codebooks failed");
   if (st != VSK_OK) {
     vsk_index_destroy(reinterpret_cast<vsk_index*>(ix));

@@ -299,7 +299,9 @@ int32_t vsk_sq8_encode_dev(vsk_ctx* c, const float* rows, int64_t n, int32_t dim
 
 static int32_t sq8_host_call(Ctx* ctx, const float* rows, int64_t n, int32_t dim, int32_t mode, float* scale,
                              float* offset, bool train, int8_t* codes_out, const int8_t* codes_in, float* rows_out) {
-  // one helper for the three host-pointer entry points: stage in, run the device call, stage out
+  // one helper for the three host-pointer entry points: stage in, run the device call, stage out.  The copies in go
+  // through the context's stream, like the kernels that read them: that stream does not wait for the legacy default
+  // stream, and a plain cudaMemcpy from pageable memory may return before its last bytes have landed.
   float *dx = nullptr, *dscale = nullptr, *doffset = nullptr, *dmm = nullptr;
   int8_t* dcodes = nullptr;
   int32_t st = VSK_OK;
@@ -311,7 +313,7 @@ static int32_t sq8_host_call(Ctx* ctx, const float* rows, int64_t n, int32_t dim
       (st = dev_alloc(ctx, (void**)&dmm, (size_t)dim * 8)) == VSK_OK &&
       (st = dev_alloc(ctx, (void**)&dcodes, elems)) == VSK_OK) {
     if (train) {
-      cudaMemcpy(dx, rows, elems * 4, cudaMemcpyHostToDevice);
+      cudaMemcpyAsync(dx, rows, elems * 4, cudaMemcpyHostToDevice, ctx->stream);
       st = vsk_sq8_minmax_dev(c, dx, n, dim, dmm, dmm + dim);
       if (st == VSK_OK) st = vsk_sq8_params_dev(c, dmm, dmm + dim, dim, mode, dscale, doffset);
       if (st == VSK_OK) {
@@ -319,14 +321,14 @@ static int32_t sq8_host_call(Ctx* ctx, const float* rows, int64_t n, int32_t dim
         cudaMemcpy(offset, doffset, (size_t)dim * 4, cudaMemcpyDeviceToHost);
       }
     } else {
-      cudaMemcpy(dscale, scale, (size_t)dim * 4, cudaMemcpyHostToDevice);
-      cudaMemcpy(doffset, offset, (size_t)dim * 4, cudaMemcpyHostToDevice);
+      cudaMemcpyAsync(dscale, scale, (size_t)dim * 4, cudaMemcpyHostToDevice, ctx->stream);
+      cudaMemcpyAsync(doffset, offset, (size_t)dim * 4, cudaMemcpyHostToDevice, ctx->stream);
       if (codes_out) {
-        cudaMemcpy(dx, rows, elems * 4, cudaMemcpyHostToDevice);
+        cudaMemcpyAsync(dx, rows, elems * 4, cudaMemcpyHostToDevice, ctx->stream);
         st = vsk_sq8_encode_dev(c, dx, n, dim, dscale, doffset, dcodes);
         if (st == VSK_OK) cudaMemcpy(codes_out, dcodes, elems, cudaMemcpyDeviceToHost);
       } else {
-        cudaMemcpy(dcodes, codes_in, elems, cudaMemcpyHostToDevice);
+        cudaMemcpyAsync(dcodes, codes_in, elems, cudaMemcpyHostToDevice, ctx->stream);
         sq8_decode_kernel<<<(unsigned)ceil_div((int64_t)elems, 256), 256, 0, ctx->stream>>>(dcodes, (int64_t)elems, dim, dscale, doffset, dx);
         ctx->stats.kernel_launches++;
         cudaError_t e = cudaStreamSynchronize(ctx->stream);
@@ -392,8 +394,9 @@ int32_t vsk_sq8_index_create(vsk_ctx* c, int32_t metric, int32_t dim, const floa
     return st;
   }
   // scale/offset are host arrays (a few hundred floats the host computed or received)
-  cudaMemcpy(ix->sq_scale, scale, (size_t)dim * 4, cudaMemcpyDefault);
-  cudaMemcpy(ix->sq_offset, offset, (size_t)dim * 4, cudaMemcpyDefault);
+  cudaMemcpyAsync(ix->sq_scale, scale, (size_t)dim * 4, cudaMemcpyDefault, ctx->stream);
+  cudaMemcpyAsync(ix->sq_offset, offset, (size_t)dim * 4, cudaMemcpyDefault, ctx->stream);
+  cudaStreamSynchronize(ctx->stream);
   *out = reinterpret_cast<vsk_index*>(ix);
   return VSK_OK;
 }

@@ -20,8 +20,7 @@ namespace vsk {
 namespace {
 
 constexpr int SS_THREADS = 256;
-// Rows per warp step (template parameter ROWS): a staged query value is used for all of them.  Two by default;
-// four for one or two queries over rows of at most 1 KB, where two rows leave too few loads in flight per lane.
+// Rows per warp step (template parameter): a staged query value is used for all of them.
 
 // v[0..V) per lane -> the total over the warp of v[j] on the lanes with (lane >> (5 - log2 V)) == j, in v[0].
 // Each stage halves the values a lane still carries: a lane keeps the half its lane bit selects and hands the
@@ -222,9 +221,8 @@ int32_t launch_rows(Ctx* ctx, const ExactScanArgs& a, bool vec) {
 
 template <int METRIC, int MODE, int NQ>
 int32_t launch_nq(Ctx* ctx, const ExactScanArgs& a, bool vec) {
-  if constexpr (NQ <= 2) {
-    if (a.dim <= 256) return launch_rows<METRIC, MODE, NQ, 4>(ctx, a, vec);
-  }
+  // four rows per step were measured for one and two queries over rows of at most 1 KB: slower than two (one query
+  // over 5 M x 256: 0.47 against 0.43 ms), so every launch takes two
   return launch_rows<METRIC, MODE, NQ, 2>(ctx, a, vec);
 }
 
