@@ -366,6 +366,12 @@ class Bench:
 
     def step_host(self):
         lib, t = self.dev._lib, self.torch
+        if self.world > 1 and self.qm_pinned is None:
+            # rows are sharded: pinned queries to the device, the sharded search, merged result to pinned host memory
+            if not hasattr(self, "q_staging"):
+                self.q_staging = t.empty_like(self.queries)
+            self.sharded.batchSearchHost(self.q_pinned, self.k, self.out_d_host, self.out_i_host, self.q_staging)
+            return
         qp, od, oi = (C.c_void_p(x.data_ptr()) for x in (self.q_pinned, self.out_d_host, self.out_i_host))
         if self.wl["kind"] == "ivf":
             self.dev.check(lib.vsk_ivf_search(self.index._h, qp, self.nq, self.k, self.wl["nprobe"], od, oi))
@@ -592,7 +598,7 @@ def main():
         roof.update(unit="T lane-instr/s", achieved=b.flops * args.steps / secs / 1e12 if secs > 0 else None,
                     peak=sm * 128 * 1.965e9 / 1e12, peak_source="nominal: SMs x 128 FP32 lanes x 1965 MHz")
     roof["frac"] = roof["achieved"] / roof["peak"] if roof.get("achieved") else None
-    if wl["kind"] in ("flat", "sq8", "filtered") and secs > 0:
+    if args.queries > 0 and wl["kind"] in ("flat", "sq8", "filtered") and secs > 0:
         # the HBM view of the same launches: the stored operand the scan reads (fp16 images on the tensor path, else
         # fp32 rows or int8 codes) crossing HBM once per batch; this is what bounds a batch of a few queries
         if args.path == "tensor" and b.bound == "tensor":

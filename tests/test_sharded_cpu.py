@@ -58,6 +58,10 @@ def _worker(rank, world, port, ret):
         d, i = s.batchSearch(torch.from_numpy(q), 9)
         ok = ok and np.array_equal(i.numpy(), ri) and np.array_equal(d.numpy(), rd)
     ok = ok and state["kept"] < 2 * 9          # the bound dropped rows (last batch: 2 queries of 9)
+    # host buffers in, host buffers out
+    hd, hi_ = torch.empty((17, 9), dtype=torch.float32), torch.empty((17, 9), dtype=torch.int64)
+    ShardedSearch(local, merge).batchSearchHost(torch.from_numpy(q), 9, hd, hi_)
+    ok = ok and np.array_equal(hi_.numpy(), ri) and np.array_equal(hd.numpy(), rd)
     ret[rank] = bool(ok)
     dist.barrier()
     dist.destroy_process_group()

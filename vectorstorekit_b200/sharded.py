@@ -92,6 +92,25 @@ class ShardedSearch:
                 (self.stream or torch.cuda.current_stream()).synchronize()
             return od[:nq], oi[:nq]
 
+    def batchSearchHost(self, queries_host, k: int, out_dist_host, out_ids_host, staging=None):
+        """Host buffers in, host buffers out: the queries go to `staging` (a device tensor of their shape; CPU ranks
+        pass none and search the host tensor itself), the sharded search runs on them, and the merged result is
+        copied into the two host tensors.  Everything is ordered on the search's stream; the call returns when the
+        results are in host memory.  The copies are torch's blocking kind on purpose: a non-blocking copy makes
+        torch's pinned-memory allocator keep an event of the stream, and the search's stream belongs to the library
+        and may be gone when the host buffers are freed."""
+        import torch
+        ctx = torch.cuda.stream(self.stream) if self.stream is not None else contextlib.nullcontext()
+        with ctx:
+            q = queries_host
+            if staging is not None:
+                staging.copy_(queries_host)
+                q = staging
+            d, i = self.batchSearch(q, k)
+            out_dist_host.copy_(d)
+            out_ids_host.copy_(i)
+        return out_dist_host, out_ids_host
+
 
 class ShardedKMeans:
     """Lloyd iterations over rows spread across the ranks of a group: every rank assigns its own rows to the
