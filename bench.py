@@ -368,9 +368,13 @@ class Bench:
         lib, t = self.dev._lib, self.torch
         if self.world > 1 and self.qm_pinned is None:
             # rows are sharded: pinned queries to the device, the sharded search, merged result to pinned host memory
+            # (every rank holds the same queries: each copies its 1/N of them, an all-gather does the rest)
             if not hasattr(self, "q_staging"):
-                self.q_staging = t.empty_like(self.queries)
-            self.sharded.batchSearchHost(self.q_pinned, self.k, self.out_d_host, self.out_i_host, self.q_staging)
+                per = -(-self.nq // self.world)
+                self.q_staging = t.empty((per * self.world, self.queries.shape[1]), dtype=self.queries.dtype,
+                                         device=self.device)
+            self.sharded.batchSearchHost(self.q_pinned, self.k, self.out_d_host, self.out_i_host, self.q_staging,
+                                         gather_queries=True)
             return
         qp, od, oi = (C.c_void_p(x.data_ptr()) for x in (self.q_pinned, self.out_d_host, self.out_i_host))
         if self.wl["kind"] == "ivf":
@@ -635,6 +639,7 @@ def main():
                         if (b.hi - b.lo) * wl["dim"] * 2 > 126e6 else "L2 flushed by the candidate-list traffic only"},
                        **b.extra),
         "roofline": roof,
+        # host -> device bytes of the whole job per step: at N > 1 each rank sends its 1/N of the queries
         "e2e": {"value": e2e, "unit": "queries/s", "h2d_bytes_per_step": nq * wl["dim"] * 4 + (nq * 8 if b.qmasks is not None else 0),
                 "d2h_bytes_per_step": nq * k * 12},
         "gpu_launches": int(launches),

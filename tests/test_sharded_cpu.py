@@ -62,6 +62,13 @@ def _worker(rank, world, port, ret):
     hd, hi_ = torch.empty((17, 9), dtype=torch.float32), torch.empty((17, 9), dtype=torch.int64)
     ShardedSearch(local, merge).batchSearchHost(torch.from_numpy(q), 9, hd, hi_)
     ok = ok and np.array_equal(hi_.numpy(), ri) and np.array_equal(hd.numpy(), rd)
+    # ... with every rank sending only its share of the queries to the "device" (17 queries: uneven shares)
+    per = -(-17 // world)
+    stage = torch.full((per * world, 24), float("nan"))
+    hd.fill_(0), hi_.fill_(0)
+    ShardedSearch(local, merge).batchSearchHost(torch.from_numpy(q), 9, hd, hi_, staging=stage, gather_queries=True)
+    ok = ok and np.array_equal(hi_.numpy(), ri) and np.array_equal(hd.numpy(), rd)
+    ok = ok and np.array_equal(stage[:17].numpy(), q)
     ret[rank] = bool(ok)
     dist.barrier()
     dist.destroy_process_group()

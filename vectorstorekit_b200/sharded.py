@@ -92,18 +92,34 @@ class ShardedSearch:
                 (self.stream or torch.cuda.current_stream()).synchronize()
             return od[:nq], oi[:nq]
 
-    def batchSearchHost(self, queries_host, k: int, out_dist_host, out_ids_host, staging=None):
+    def batchSearchHost(self, queries_host, k: int, out_dist_host, out_ids_host, staging=None,
+                        gather_queries: bool = False):
         """Host buffers in, host buffers out: the queries go to `staging` (a device tensor of their shape; CPU ranks
         pass none and search the host tensor itself), the sharded search runs on them, and the merged result is
         copied into the two host tensors.  Everything is ordered on the search's stream; the call returns when the
-        results are in host memory.  The copies are torch's blocking kind on purpose: a non-blocking copy makes
+        results are in host memory.  With `gather_queries` (all ranks were handed the same host queries) a rank copies
+        only its share of them to the device and an all-gather hands every rank the rest.  The copies are torch's
+        blocking kind on purpose: a non-blocking copy makes
         torch's pinned-memory allocator keep an event of the stream, and the search's stream belongs to the library
         and may be gone when the host buffers are freed."""
         import torch
         ctx = torch.cuda.stream(self.stream) if self.stream is not None else contextlib.nullcontext()
         with ctx:
             q = queries_host
-            if staging is not None:
+            nq = queries_host.shape[0]
+            if staging is not None and gather_queries and self.world > 1:
+                # every rank holds the same host queries: each sends only its 1/G of them over PCIe and the ranks
+                # exchange the parts over NVLink (`staging` has ceil(Q / G) * G rows; the padding is never read)
+                per = -(-nq // self.world)
+                r = self._dist.get_rank(self.group)
+                lo = min(r * per, nq)
+                hi = min(lo + per, nq)
+                part = torch.empty((per,) + tuple(staging.shape[1:]), dtype=staging.dtype, device=staging.device)
+                if hi > lo:
+                    part[:hi - lo].copy_(queries_host[lo:hi])
+                self._dist.all_gather_into_tensor(staging, part, group=self.group)
+                q = staging[:nq]
+            elif staging is not None:
                 staging.copy_(queries_host)
                 q = staging
             d, i = self.batchSearch(q, k)
