@@ -445,6 +445,10 @@ def run_reference(args, wl):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    # torch.distributed.run sets OMP_NUM_THREADS=1 for its workers unless it is set: this arm is the one process that
+    # works, and it is meant to use every host thread (the OpenMP runtime reads the variable when it is first loaded)
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1 and os.environ.get("OMP_NUM_THREADS") == "1":
+        os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
     oracle, o = get_oracle()
     n, dim, nq, k = wl["rows"], wl["dim"], wl["queries"], wl["k"]
     if wl["kind"] != "flat":
