@@ -465,7 +465,7 @@ int32_t ivf_search_few(Ctx* ctx, Index* ix, const float* q, int64_t nq, const in
     total += cnt;
     longest = std::max(longest, cnt);
   }
-  if (total > kIvfFewMaxEntries) return VSK_OK;
+  if (total > kIvfFewMaxEntries || total == 0) return VSK_OK;   // too many rows, or nothing to scan: the general path
   void *drows, *dtri, *dbeg, *dcnt;
   VSK_TRY(scratch(ctx, SLOT_IVF_ORDER, (size_t)std::max<int64_t>(total, 1) * 4, &drows));
   VSK_TRY(scratch(ctx, SLOT_IVF_PAIR_OFF, std::max<size_t>(triples.size(), 3) * 8, &dtri));
