@@ -170,3 +170,15 @@ def test_ivf_few_queries_adversarial_row_order(vsk, dev, cpu_oracle):
         assert_topk_parity(gd, gi, rd, ri)
     finally:
         ix.close()
+
+
+@pytest.mark.parametrize("nq,d", [(1, 1536), (4, 1536), (8, 1536), (8, 1500), (3, 3000)])
+def test_few_queries_at_the_shared_memory_limit(vsk, dev, cpu_oracle, nq, d):
+    """The staged queries must fit 48 KB of shared memory next to the kernel's static words: eight queries of
+    1 536 dimensions are exactly 48 KB and go to the tile instead; four of them, or eight of 1 500, stream."""
+    rng = np.random.default_rng(nq + d)
+    x = rng.standard_normal((3_000, d)).astype(np.float32)
+    q = rng.standard_normal((nq, d)).astype(np.float32)
+    gd, gi = _search(vsk, dev, "cosine", x, q, 10, path=1)
+    rd, ri = cpu_oracle.flat_search(oracle.COSINE, q, x, 10)
+    assert_topk_parity(gd, gi, rd, ri)

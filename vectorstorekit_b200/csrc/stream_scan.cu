@@ -250,13 +250,16 @@ bool stream_scan_applies(const ExactScanArgs& a) {
   if (off) return false;
   if (a.x_codes != nullptr || a.x == nullptr) return false;                 // fp32 rows only
   if (a.mode != SCAN_DENSE && a.mode != SCAN_THRESHOLD) return false;       // candidate modes only
+  // the queries stay in shared memory: the staged rows (1, 2, 4 or 8 of them) plus the kernel's few static words
+  // must fit the 48 KB a launch gets without opting in to more
+  constexpr size_t kSmemBudget = 48 * 1024 - 512;
   if (a.seg_begin) {
     return a.x_rows != nullptr && a.seg_count != nullptr && a.nq >= 1 && a.nq <= kStreamScanMaxSegQueries &&
-           (size_t)a.dim * sizeof(float) <= 48 * 1024;
+           (size_t)a.dim * sizeof(float) <= kSmemBudget;
   }
   if (a.nq < 1 || a.nq > kStreamScanMaxQueries) return false;
-  if ((size_t)kStreamScanMaxQueries * a.dim * sizeof(float) > 48 * 1024) return false;   // queries stay in shared memory
-  return true;
+  const size_t staged = a.nq <= 1 ? 1 : (a.nq <= 2 ? 2 : (a.nq <= 4 ? 4 : 8));
+  return staged * a.dim * sizeof(float) <= kSmemBudget;
 }
 
 int32_t launch_stream_scan(Ctx* ctx, const ExactScanArgs& a) {
