@@ -183,7 +183,8 @@ int32_t vsk_index_import(vsk_ctx* ctx, const void* src, int64_t bytes, vsk_index
 int32_t vsk_index_save(vsk_index* index, const char* path);
 int32_t vsk_index_load(vsk_ctx* ctx, const char* path, vsk_index** out_index);
 
-/* out_dist[nq*k], out_ids[nq*k].  qmasks may be NULL. */
+/* out_dist[nq*k], out_ids[nq*k].  qmasks may be NULL.  nq = 1 is VectorStore.search (one query): batches of one
+ * to eight queries over fp32 rows stream every row they may see from HBM once instead of padding a query tile. */
 int32_t vsk_search(vsk_index* index, const float* queries, int64_t nq, int32_t k,
                    const uint64_t* qmasks, float* out_dist, int64_t* out_ids);
 int32_t vsk_search_dev(vsk_index* index, const float* queries, int64_t nq, int32_t k,
@@ -273,7 +274,8 @@ int32_t vsk_ivf_assignments(vsk_index* index, int32_t* assign);
 /* The index's centroids, [nlist][dim] floats to host memory (what IVFIndex.export keeps, IVFIndex.swift:297-302). */
 int32_t vsk_ivf_centroids(vsk_index* index, float* centroids);
 /* Probe the nprobe nearest lists, rooted L2, ascending top-k.  Replaces IVFIndex.search
- * (Indexes/IVFIndex.swift:124-202); nprobe == nlist is its `.exact` strategy (:551-560). */
+ * (Indexes/IVFIndex.swift:124-202); nprobe == nlist is its `.exact` strategy (:551-560).  The reference's call is
+ * the nq = 1 case; up to sixteen queries each stream the rows of their own probed lists. */
 int32_t vsk_ivf_search(vsk_index* index, const float* queries, int64_t nq, int32_t k,
                        int32_t nprobe, float* out_dist, int64_t* out_ids);
 int32_t vsk_ivf_search_dev(vsk_index* index, const float* queries, int64_t nq, int32_t k,
