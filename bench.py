@@ -5,8 +5,10 @@
 Metric: queries/sec of exact top-k search (BASELINE.json).  The default workload (c2) is the
 configuration the metric is quoted on: flat cosine, 1 000 000 x 768 fp32 rows (N(0,1), L2-normalised),
 10 000 queries, k = 100.  A step is one batch search of all queries over the resident database.
-With N > 1 (one process per GPU under torchrun) the rows are sharded across ranks, each rank searches
-its shard, the per-shard top-k lists are all-gathered over NCCL and merged ("scaling": "strong").
+With N > 1 (one process per GPU under torchrun) the rows are sharded across ranks and a step is one
+vsk_search_sharded call per rank: each rank scans its shard, the shards agree on a per-query bound (one
+all-reduce), the per-shard top-k lists travel as packed keys in one all-to-all, and every rank merges and
+returns its 1/N of the queries ("scaling": "strong").
 
 Other workloads (not the default line): c1 flat euclidean 100k x 128; c3 IVF (10M x 128, nlist 4096,
 20 Lloyd iterations, nprobe 32); c4 int8 dot product 50M x 384; c5 filtered Manhattan 5M x 256; and
@@ -14,7 +16,9 @@ reduced copies (suffix s) for profiler captures.
 
 value     queries/s with queries already in HBM (CUDA events on the library's stream, max over ranks)
 e2e       queries/s through the host-pointer C-ABI call: pinned host queries in, host results out
-roofline  the scan kernels' device time from CUDA events recorded around each launch
+roofline  the scan kernels' device time from CUDA events recorded around each launch, in a second timed region
+          with the library's profiling on (profiling runs a batch on one stream, so that an event pair brackets
+          one kernel alone; the first region runs large batches as two halves on two streams)
 cpu_baseline / --impl reference: the CPU restatement of the reference's search on the host cores
 """
 import argparse
@@ -200,13 +204,19 @@ class Bench:
         self.out_d_host = torch.empty((self.nq, self.k), dtype=torch.float32).pin_memory()
         self.out_i_host = torch.empty((self.nq, self.k), dtype=torch.int64).pin_memory()
         self.qm_pinned = self.qmasks.cpu().pin_memory() if self.qmasks is not None else None
-        from vectorstorekit_b200.sharded import ShardedSearch
+        from vectorstorekit_b200.sharded import ShardedSearch, join_communicator
         # every injected function launches on the library's stream; the collectives are ordered on it too
         self.stream = torch.cuda.ExternalStream(dev.stream, device=device)
-        halves = {}
-        if wl["kind"] == "flat" and path == "tensor":
-            halves = dict(local_begin=self.index.shardSearchBegin, local_finish=self.index.shardSearchFinish)
-        self.sharded = ShardedSearch(self.local_search, engine.mergeTopK, stream=self.stream, **halves)
+        # flat fp32 (filtered or not) and int8 indexes: the whole sharded search is one C-ABI call
+        # (vsk_search_sharded over the library's own NCCL communicator); IVF and PQ go through the injected form
+        self.abi_sharded = world > 1 and wl["kind"] in ("flat", "filtered", "sq8")
+        if self.abi_sharded:
+            join_communicator(dev)
+            first, count = vsk.sharded_slice(self.nq, world, rank)
+            self.slice = (first, count)
+            self.dev_out = (torch.empty((max(count, 1), self.k), dtype=torch.float32, device=device),
+                            torch.empty((max(count, 1), self.k), dtype=torch.int64, device=device))
+        self.sharded = ShardedSearch(self.local_search, engine.mergeTopK, stream=self.stream)
 
     # ---- builders ----
     def _build_flat(self):
@@ -362,13 +372,22 @@ class Bench:
         return self.index.batchSearch(queries, k)
 
     def step_device(self):
+        if self.abi_sharded:
+            # every rank ends the step holding the merged top-k of its 1/N of the queries
+            return self.index.shardedSearch(self.queries, self.k, filter_masks=self.qmasks, out=self.dev_out)
         return self.sharded.batchSearch(self.queries, self.k)
 
     def step_host(self):
         lib, t = self.dev._lib, self.torch
+        if self.abi_sharded:
+            # pinned host queries in (every rank holds them; each sends its 1/N over PCIe, NVLink does the rest),
+            # this rank's slice of the merged result out to pinned host memory: one vsk_search_sharded call
+            first, count = self.slice
+            self.index.shardedSearch(self.q_pinned, self.k, filter_masks=self.qm_pinned, split_queries=True,
+                                     out=(self.out_d_host[first:first + max(count, 1)],
+                                          self.out_i_host[first:first + max(count, 1)]))
+            return
         if self.world > 1 and self.qm_pinned is None:
-            # rows are sharded: pinned queries to the device, the sharded search, merged result to pinned host memory
-            # (every rank holds the same queries: each copies its 1/N of them, an all-gather does the rest)
             if not hasattr(self, "q_staging"):
                 per = -(-self.nq // self.world)
                 self.q_staging = t.empty((per * self.world, self.queries.shape[1]), dtype=self.queries.dtype,
@@ -439,6 +458,15 @@ class Bench:
                 "sample": f"{nq} of {self.nq} queries over all {self.hi - self.lo} rows, {dt:.1f} s"}
 
 
+def config_of(wl, world, path):
+    """The `config` object of a line: the same for this arm and for the reference arm."""
+    shard_rows = wl["rows"] // max(world, 1)
+    return {"workload": wl["name"], "rows": wl["rows"], "dim": wl["dim"], "queries": wl["queries"], "k": wl["k"],
+            "metric": wl["metric"], "sharding": f"rows/{world}", "search_path": path,
+            "l2": "the database read by every pass is larger than L2 (126 MB)"
+            if shard_rows * wl["dim"] * 2 > 126e6 else "L2 flushed by the candidate-list traffic only"}
+
+
 def run_reference(args, wl):
     """--impl reference: the reference's CPU search path (C++ restatement of AccelerateOptimizer /
     UnifiedDistanceComputation; its Swift sources cannot be built on Linux) on all host threads."""
@@ -451,30 +479,67 @@ def run_reference(args, wl):
         os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
     oracle, o = get_oracle()
     n, dim, nq, k = wl["rows"], wl["dim"], wl["queries"], wl["k"]
-    if wl["kind"] != "flat":
-        print(json.dumps({"impl": "reference", "unavailable": "the reference arm is defined for the flat workloads (c1, c2)"}))
-        return
     rng = np.random.default_rng(SEED)
-    x = rng.standard_normal((n, dim), dtype=np.float32)
-    q = rng.standard_normal((nq, dim), dtype=np.float32)
-    if wl["metric"] == "cosine":
-        x /= np.linalg.norm(x, axis=1, keepdims=True)
-        q /= np.linalg.norm(q, axis=1, keepdims=True)
-    mid = oracle.METRIC_IDS[wl["metric"]]
     cores = o.num_threads()
+    mid = oracle.METRIC_IDS[wl["metric"]]
+    scale_rows = 1.0        # rate multiplier when only a prefix of the rows is searched on the CPU (extrapolation)
+    note = ""
+    if wl["kind"] == "flat":
+        x = rng.standard_normal((n, dim), dtype=np.float32)
+        q = rng.standard_normal((nq, dim), dtype=np.float32)
+        if wl["metric"] == "cosine":
+            x /= np.linalg.norm(x, axis=1, keepdims=True)
+            q /= np.linalg.norm(q, axis=1, keepdims=True)
+        fn = lambda c: o.flat_search(mid, q[:c], x, k, fast=True)
+    elif wl["kind"] == "filtered":
+        x = rng.random((n, dim), dtype=np.float32) * 2 - 1
+        q = rng.random((nq, dim), dtype=np.float32) * 2 - 1
+        rm = rng.integers(0, 2 ** 64, n, dtype=np.uint64)
+        qm = np.uint64(1) << rng.integers(0, 64, nq).astype(np.uint64)
+        fn = lambda c: o.flat_search(mid, q[:c], x, k, rm, qm[:c], fast=True)
+    elif wl["kind"] == "ivf":
+        # IVFIndex.search on the host.  Training 10 M rows on the CPU would take hours, so the index the CPU arm
+        # searches has the mixture's own centres as centroids and every row filed under the centre it was drawn
+        # from: lists of the same number and mean length as a trained index.  Only the search is timed.
+        nlist = wl["nlist"]
+        centres = rng.standard_normal((nlist, dim), dtype=np.float32)
+        comp = rng.integers(0, nlist, n).astype(np.int32)
+        x = np.empty((n, dim), np.float32)
+        for lo in range(0, n, 1 << 20):
+            hi = min(n, lo + (1 << 20))
+            x[lo:hi] = centres[comp[lo:hi]] + np.float32(0.1) * rng.standard_normal((hi - lo, dim), dtype=np.float32)
+        qc = rng.integers(0, nlist, nq)
+        q = centres[qc] + np.float32(0.1) * rng.standard_normal((nq, dim), dtype=np.float32)
+        fn = lambda c: o.ivf_search(q[:c], x, centres, comp, wl["nprobe"], k)
+        note = "; lists = mixture components (training is not part of the timed search)"
+    elif wl["kind"] == "sq8":
+        # a bounded prefix of the rows (generating and encoding 50 M x 384 on the host alone takes minutes);
+        # the rate is scaled by the row ratio and labelled as extrapolated
+        n_cpu = min(n, 2_000_000)
+        x = rng.standard_normal((n_cpu, dim), dtype=np.float32)
+        q = rng.standard_normal((nq, dim), dtype=np.float32)
+        sc, of = o.sq8_train(x, True)
+        codes = o.sq8_encode(x, sc, of)
+        del x
+        fn = lambda c: o.sq8_search(mid, q[:c], codes, sc, of, k)
+        scale_rows = n_cpu / n
+        note = f"; {n_cpu} of {n} rows, rate scaled by the row ratio: extrapolated"
+    else:
+        print(json.dumps({"impl": "reference", "unavailable": f"no CPU arm for workload kind {wl['kind']}"}))
+        return
     per_step = max(5.0, min(30.0, 120.0 / max(1, args.steps + args.warmup)))
     rates, desc = [], ""
-    for s in range(args.warmup + args.steps):
-        r, m, dt = cpu_rate(lambda c: o.flat_search(mid, q[:c], x, k, fast=True), nq, cores, per_step)
-        desc = f"{m} of {nq} queries over all {n} rows, {dt:.1f} s"
-        if s >= args.warmup:
-            rates.append(r)
+    for s_ in range(args.warmup + args.steps):
+        r, m, dt = cpu_rate(fn, nq, cores, per_step)
+        desc = f"{m} of {nq} queries, {dt:.1f} s, per-query time x {nq} = the batch time (extrapolated)" + note
+        if s_ >= args.warmup:
+            rates.append(r * scale_rows)
     v = float(np.mean(rates))
     print(json.dumps({
         "impl": "reference", "metric": "queries/sec (k-NN, exact top-k match)", "value": v, "unit": "queries/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * nq / v,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": wl["name"], "rows": n, "dim": dim, "queries": nq, "k": k, "metric": wl["metric"]},
+        "config": config_of(wl, max(1, args.gpus), args.path),
         "cpu_baseline": {"value": v, "unit": "queries/s", "cores": cores, "kind": "port", "sample": desc},
         "e2e": {"value": v, "unit": "queries/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0}))
@@ -490,6 +555,8 @@ def main():
     ap.add_argument("--path", default="tensor", choices=["tensor", "fp32"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--tuning", action="append", default=[], metavar="FIELD=VALUE",
+                    help="a field of the library's vsk_tuning (e.g. overlap_min_queries=0, chunk_growth=4)")
     ap.add_argument("--queries", type=int, default=0,
                     help="override the workload's batch size (a few queries show the HBM-bound regime of a scan)")
     args = ap.parse_args()
@@ -513,6 +580,8 @@ def main():
         dist.init_process_group("nccl", device_id=device)
     dev = vsk.CUDAComputeDevice(local)
     dev.set_search_path(vsk.PATH_TENSOR_RERANK if args.path == "tensor" else vsk.PATH_FP32_SCAN)
+    if args.tuning:
+        dev.set_tuning(**{kv.split("=")[0]: int(kv.split("=")[1]) for kv in args.tuning})
     engine = vsk.CUDAAccelerationEngine(dev)
     b = Bench(torch, vsk, dev, engine, wl, rank, world, device, args.path)
     nq, k = b.nq, b.k
@@ -529,8 +598,7 @@ def main():
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    dev.profile(True)
-    st0 = dev.stats()
+    st_a = dev.stats()
     barrier()
     t0 = time.perf_counter()
     e0 = torch.cuda.Event(enable_timing=True)
@@ -542,8 +610,26 @@ def main():
     barrier()
     wall = time.perf_counter() - t0
     dev_ms = e0.elapsed_time(e1)
+    st_b = dev.stats()
+    # second region, profiling on: an event pair around every scan launch (and, at N > 1, around every phase of the
+    # sharded call).  Not part of `value`.
+    prof_steps = max(1, min(args.steps, 5))
+    dev.profile(True)
+    b.step_device()
+    st0 = dev.stats()
+    phases = None
+    for _ in range(prof_steps):
+        b.step_device()
+        if b.abi_sharded:
+            ph = dev.sharded_phase_ms()
+            phases = ph if phases is None else {k_: phases[k_] + v for k_, v in ph.items()}
     st1 = dev.stats()
     dev.profile(False)
+    if phases is not None:
+        names = list(phases)
+        pt = torch.tensor([phases[n_] / prof_steps for n_ in names], dtype=torch.float64, device=device)
+        dist.all_reduce(pt, op=dist.ReduceOp.MAX)
+        phases = {n_: round(float(v), 4) for n_, v in zip(names, pt.tolist())}
     # CUDA events on the library's stream, on which the collectives of a sharded step are ordered as well;
     # the wall clock between the two barriers is reported beside it
     elapsed_ms = dev_ms
@@ -573,13 +659,14 @@ def main():
         sampler.stop_flag = True
         sampler.join(timeout=2)
 
-    launches = st1["kernel_launches"] - st0["kernel_launches"]
+    launches = st_b["kernel_launches"] - st_a["kernel_launches"]
     scan_ms = st1["scan_kernel_ms"] - st0["scan_kernel_ms"]
     scan_n = max(1, st1["scan_kernel_launches"] - st0["scan_kernel_launches"])
     pk = peaks()
     roof = {"bound": b.bound, "kernel": "scan kernels (distance computation + fused candidate filter)",
-            "kernel_ms_per_step": scan_ms / args.steps, "kernel_launches_per_step": scan_n / args.steps, "traffic": None}
-    secs = scan_ms * 1e-3
+            "kernel_ms_per_step": scan_ms / prof_steps, "kernel_launches_per_step": scan_n / prof_steps, "traffic": None,
+            "timed_steps": prof_steps}
+    secs = scan_ms * 1e-3 * args.steps / prof_steps     # the formulas below are written per `args.steps` steps
     if b.bound == "tensor":
         roof.update(unit="TFLOP/s", achieved=b.flops * args.steps / secs / 1e12 if secs > 0 else None,
                     peak=pk["bf16_tflops"], peak_source=pk["source"] + " (cuBLAS bf16, sustained)")
@@ -597,14 +684,18 @@ def main():
     elif b.bound == "smem":
         sm = dev.info()["sm_count"]
         roof.update(unit="T look-ups/s", achieved=b.flops * args.steps / secs / 1e12 if secs > 0 else None,
-                    peak=sm * 32 * 1.965e9 / 1e12, peak_source="nominal: SMs x 32 shared-memory banks x 1965 MHz",
+                    peak=dev.measure_peak("smem_gather") / 1e12,
+                    peak_source="measured in this run: 4-byte shared-memory loads at random addresses (vsk_measure_peak)",
+                    nominal_peak=sm * 32 * 1.965e9 / 1e12,
                     algorithmic_codes_gbs=b.bytes_per_query * nq * args.steps / secs / 1e9 if secs > 0 else None,
                     note="one 4-byte table word per (query, row, segment); query-major code bytes are given for "
                          "the HBM view: a query tile re-reads the codes from L2")
     else:
         sm = dev.info()["sm_count"]
         roof.update(unit="T lane-instr/s", achieved=b.flops * args.steps / secs / 1e12 if secs > 0 else None,
-                    peak=sm * 128 * 1.965e9 / 1e12, peak_source="nominal: SMs x 128 FP32 lanes x 1965 MHz")
+                    peak=dev.measure_peak("fp32_issue") / 1e12,
+                    peak_source="measured in this run: FADD/FFMA chains on every warp slot (vsk_measure_peak)",
+                    nominal_peak=sm * 128 * 1.965e9 / 1e12)
     roof["frac"] = roof["achieved"] / roof["peak"] if roof.get("achieved") else None
     if args.queries > 0 and wl["kind"] in ("flat", "sq8", "filtered") and secs > 0:
         # the HBM view of the same launches: the stored operand the scan reads (fp16 images on the tensor path, else
@@ -622,12 +713,12 @@ def main():
         roof["hbm_view"] = {"bytes_per_row": per_row, "achieved_gbs": gbs, "peak_gbs": pk["hbm_gbs"],
                             "frac": gbs / pk["hbm_gbs"]}
     if wl["kind"] == "flat" and args.path == "tensor" and b.bound == "tensor":
-        # DRAM bytes per scan launch, from the ncu capture of the reduced workload (profiles/tc_scan_kernel__*):
+        # DRAM bytes per scan launch, from the ncu capture of the reduced workload c2s:
         # dram__bytes_read equals the fp16 rows of the launch read once plus the query operand, dram__bytes_write is
         # the appended keys (about 6 MB); scaled to this workload by its rows (traffic grows in proportion)
         d16 = (wl["dim"] + 63) // 64 * 64
-        per_step = (b.hi - b.lo) * d16 * 2 + (scan_n / args.steps) * (nq * d16 * 2 + 6.0e6)
-        roof["traffic"] = per_step / (scan_n / args.steps)
+        per_step = (b.hi - b.lo) * d16 * 2 + (scan_n / prof_steps) * (nq * d16 * 2 + 6.0e6)
+        roof["traffic"] = per_step / (scan_n / prof_steps)
         roof["traffic_source"] = "ncu capture of workload c2s, scaled by rows"
 
     line = {
@@ -637,20 +728,23 @@ def main():
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": ("f16 operands, f32 accumulate, f32 rerank" if args.path == "tensor" and b.bound == "tensor" else "f32"),
         "data": "synthetic",
-        "config": dict({"workload": wl["name"], "rows": wl["rows"], "dim": wl["dim"], "queries": nq, "k": k,
-                        "metric": wl["metric"], "sharding": f"rows/{world}", "search_path": args.path,
-                        "l2": "the database read by every pass is larger than L2 (126 MB)"
-                        if (b.hi - b.lo) * wl["dim"] * 2 > 126e6 else "L2 flushed by the candidate-list traffic only"},
-                       **b.extra),
+        "config": config_of(wl, world, args.path),
+        "workload_detail": b.extra,
+        "tuning": dev.tuning(),
         "roofline": roof,
         # host -> device bytes of the whole job per step: at N > 1 each rank sends its 1/N of the queries
         "e2e": {"value": e2e, "unit": "queries/s", "h2d_bytes_per_step": nq * wl["dim"] * 4 + (nq * 8 if b.qmasks is not None else 0),
                 "d2h_bytes_per_step": nq * k * 12},
         "gpu_launches": int(launches),
-        "stats": {"fallback_queries": st1["fallback_queries"] - st0["fallback_queries"],
-                  "reranked_rows": st1["reranked_rows"] - st0["reranked_rows"],
-                  "tensor_tiles": st1["tensor_tiles"] - st0["tensor_tiles"]},
+        "stats": {"fallback_queries": st_b["fallback_queries"] - st_a["fallback_queries"],
+                  "reranked_rows": st_b["reranked_rows"] - st_a["reranked_rows"],
+                  "tensor_tiles": st_b["tensor_tiles"] - st_a["tensor_tiles"]},
     }
+    if phases is not None:
+        line["phases_ms"] = dict(phases, note="one sharded call with profiling on (one stream), max over ranks")
+    if world > 1:
+        line["result_layout"] = ("every rank holds the merged top-k of its 1/N of the queries"
+                                 if b.abi_sharded else "every rank holds all results")
     if rank == 0:
         line["clocks"] = sampler.summary()
         if world == 1 and not args.no_cpu_baseline:

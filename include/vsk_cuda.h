@@ -122,6 +122,21 @@ typedef struct vsk_index_info {
   int32_t reserved;
 } vsk_index_info;
 
+/* Tuning of the search schedule, per context (vsk_tuning_get / vsk_tuning_set).  The defaults are what the
+ * library was measured with; the fields exist for experiments and for hosts that know their workload.  Stands in
+ * for the reference's AccelerationConfiguration (Acceleration/MetalAccelerationEngine.swift:1025-1049). */
+typedef struct vsk_tuning {
+  int32_t fold_row_term;        /* 1: euclidean contractions up to d = 256 carry |x|^2 inside the operands */
+  int32_t chunk_growth;         /* 3: a chunk of the flat tensor-path scan is at most this multiple of the rows seen */
+  int32_t dense_rows;           /* 0 = automatic; rows of the first (unfiltered) chunk otherwise */
+  int32_t ivf_pilot_tiles;      /* 4: 256-row tiles of the nearest list that set an IVF query's first threshold */
+  int32_t stream_scan;          /* 1: batches of up to eight queries stream the rows instead of padding a tile */
+  int32_t overlap_min_queries;  /* 2048: tensor-path batches of at least this many queries run as two halves on two
+                                   streams (one half's selection and re-scoring under the other's contraction);
+                                   0 = never */
+  int32_t reserved[10];
+} vsk_tuning;
+
 /* --- context ------------------------------------------------------------------------------
  * Replaces ComputeAccelerator.initialize()/capabilities() (Core/Protocols.swift:11-20) and the
  * process-wide MetalAccelerationEngine.shared (MetalAccelerationEngine.swift:25-30). */
@@ -139,6 +154,20 @@ int32_t vsk_set_search_path(vsk_ctx* ctx, int32_t path);
 int32_t vsk_profile(vsk_ctx* ctx, int32_t enable);
 /* The CUDA stream (cudaStream_t) every call on this context is enqueued on. */
 void* vsk_stream(vsk_ctx* ctx);
+/* Rows of the next chunk of the search schedule after `seen` rows, for candidate lists compacted to `keep` keys
+ * (1 <= keep <= 2048), at re-run level 0 - 2; -1 for arguments outside that range.  Host arithmetic only (needs no
+ * device): the schedule advances by this many rows, so it is positive for every valid input. */
+int64_t vsk_schedule_chunk(int64_t seen, int32_t keep, int32_t level);
+/* Measured ceilings of this GPU for the scans that neither HBM nor the tensor cores bound (a few milliseconds of
+ * a synthetic kernel on the context's stream, best of five, CUDA events):
+ *   VSK_PEAK_FP32_ISSUE   FP32 instructions per second, counted per thread (the Manhattan scan's bound)
+ *   VSK_PEAK_SMEM_GATHER  4-byte shared-memory words per second at random addresses (the product-quantised scan's)
+ * The reference has no counterpart; its thread-configuration benchmark is the nearest relative
+ * (Acceleration/Metal/MetalThreadConfigurationOptimizer.swift:430-440). */
+typedef enum vsk_peak { VSK_PEAK_FP32_ISSUE = 0, VSK_PEAK_SMEM_GATHER = 1 } vsk_peak;
+int32_t vsk_measure_peak(vsk_ctx* ctx, int32_t what, double* per_second);
+int32_t vsk_tuning_get(vsk_ctx* ctx, vsk_tuning* out);
+int32_t vsk_tuning_set(vsk_ctx* ctx, const vsk_tuning* in);
 
 /* --- stateless distances -------------------------------------------------------------------
  * Full nq x nx matrix, out[q*nx + c].  Replaces MetalAccelerationEngine.batchComputeDistances
@@ -183,8 +212,10 @@ int32_t vsk_index_import(vsk_ctx* ctx, const void* src, int64_t bytes, vsk_index
 int32_t vsk_index_save(vsk_index* index, const char* path);
 int32_t vsk_index_load(vsk_ctx* ctx, const char* path, vsk_index** out_index);
 
-/* out_dist[nq*k], out_ids[nq*k].  qmasks may be NULL.  nq = 1 is VectorStore.search (one query): batches of one
- * to eight queries over fp32 rows stream every row they may see from HBM once instead of padding a query tile. */
+/* out_dist[nq*k], out_ids[nq*k].  qmasks may be NULL.  nq = 1 is VectorStore.search (one query).  Routing of a
+ * flat fp32 index: euclidean, cosine and dot-product batches (with or without masks) take the tensor-core path
+ * on the default search path; Manhattan batches and VSK_PATH_FP32_SCAN take the fp32 tile, where a batch of one to
+ * eight queries streams every row it may see from HBM once instead of padding a query tile. */
 int32_t vsk_search(vsk_index* index, const float* queries, int64_t nq, int32_t k,
                    const uint64_t* qmasks, float* out_dist, int64_t* out_ids);
 int32_t vsk_search_dev(vsk_index* index, const float* queries, int64_t nq, int32_t k,
@@ -210,9 +241,63 @@ int32_t vsk_search_shard_finish_dev(vsk_index* index, const float* bound, float*
 
 /* Merge of per-shard results: `g` lists of k (distance, global id) per query, laid out
  * [g][nq][k], into the k best per query by (distance, id) — what one unsharded search returns.
+ * Equal distances are ordered by (list, position): give the lists in ascending order of their shards' first
+ * global row, each ascending by (distance, id), and that is the (distance, id) order.
  * Device pointers.  The reference has no sharded search; this is the step after the NCCL gather. */
 int32_t vsk_merge_topk_dev(vsk_ctx* ctx, const float* dist, const int64_t* ids, int32_t g,
                            int64_t nq, int32_t k, float* out_dist, int64_t* out_ids);
+
+/* --- row-sharded search over several GPUs (one process and one context per GPU) -------------------
+ * The database's rows are spread over `nranks` GPUs: rank g's index holds rows [g*N/G, (g+1)*N/G) and its id base
+ * (vsk_index_set_id_base) is its first global row.  The reference has no multi-device search; its hosts await one
+ * call (MetalAccelerationEngine.batchComputeDistances, Acceleration/MetalAccelerationEngine.swift:139-204,444-449),
+ * and so do these.  Collectives are NCCL (libnccl.so.2, loaded when vsk_comm_init is first called; the library has
+ * no link-time dependency on it), enqueued on the context's streams; no kernel of this library reads another GPU's
+ * memory.
+ *   vsk_comm_unique_id  fills 128 bytes (an ncclUniqueId) on ONE rank; the host hands the same bytes to every rank
+ *   vsk_comm_init       joins the communicator (every rank calls it, same id, its own rank); collective
+ *   vsk_comm_destroy    leaves it (vsk_close does this too)
+ *   vsk_search_sharded_dev
+ *       Every rank passes the SAME queries (device, [nq][dim]) and k.  Each rank scans its shard; the shards agree on a
+ *       per-query bound (one all-reduce of nq floats) so that a shard re-scores only rows that can reach the overall
+ *       top-k; the per-shard lists travel as packed 64-bit (distance, global row) keys in ONE all-to-all, so that
+ *       rank g receives every shard's lists for its slice of the queries and merges them: ties by global row, what
+ *       an unsharded search returns.  Global rows must fit 32 bits (id base + rows <= 2^32 - 1).
+ *       layout VSK_SHARDED_SLICE: rank g gets the merged results of queries [first, first + count) (vsk_sharded_slice)
+ *                                 at the start of out_dist / out_ids (count * k entries).  No further exchange.
+ *       layout VSK_SHARDED_ALL:   an all-gather hands every rank all nq * k results.
+ *   vsk_search_sharded  the same with host pointers.  With VSK_SHARDED_QUERIES_SPLIT (flag, or-ed into layout) a
+ *       rank copies only its 1/nranks of the host queries to its GPU and an all-gather over NVLink distributes
+ *       them (all ranks hold the same host queries; saves PCIe traffic).  Results land in host memory in the
+ *       chosen layout.
+ * Flat fp32 and int8 indexes; query masks may be NULL. */
+enum { VSK_COMM_ID_BYTES = 128 };
+typedef enum vsk_sharded_layout { VSK_SHARDED_SLICE = 0, VSK_SHARDED_ALL = 1, VSK_SHARDED_QUERIES_SPLIT = 16 } vsk_sharded_layout;
+int32_t vsk_comm_unique_id(void* id_bytes);
+int32_t vsk_comm_init(vsk_ctx* ctx, int32_t nranks, int32_t rank, const void* id_bytes);
+int32_t vsk_comm_destroy(vsk_ctx* ctx);
+/* ranks and this rank of the context's communicator (1, 0 without one) */
+int32_t vsk_comm_info(vsk_ctx* ctx, int32_t* nranks, int32_t* rank);
+/* the queries whose merged results rank `rank` of `nranks` returns under VSK_SHARDED_SLICE */
+void vsk_sharded_slice(int64_t nq, int32_t nranks, int32_t rank, int64_t* first, int64_t* count);
+int32_t vsk_search_sharded_dev(vsk_index* index, const float* queries, int64_t nq, int32_t k, const uint64_t* qmasks,
+                               int32_t layout, float* out_dist, int64_t* out_ids);
+int32_t vsk_search_sharded(vsk_index* index, const float* queries, int64_t nq, int32_t k, const uint64_t* qmasks,
+                           int32_t layout, float* out_dist, int64_t* out_ids);
+/* Timing of the phases of the last vsk_search_sharded(_dev) call on this context, in milliseconds, from CUDA
+ * events on the context's streams (recorded when vsk_profile is on; zeros otherwise):
+ *   [0] query copy and exchange  [1] scan and compactions up to the bound  [2] bound all-reduce
+ *   [3] certificate, re-scoring, final order, key packing  [4] all-to-all  [5] merge  [6] all-gather / copy out
+ * A batch that ran as two halves reports the first half. */
+enum { VSK_SHARDED_PHASES = 7 };
+int32_t vsk_sharded_phase_ms(vsk_ctx* ctx, float* ms);
+
+/* The tensor path's coarse values, for auditing its error bound (no counterpart in the reference).  For the first
+ * `rows` rows of a flat fp32 index (rows <= 4096) and nq queries: coarse[q * rows + r] is the value the
+ * contraction's filter sees (fp16 operands, fp32 accumulation on the tensor cores; the squared form for euclidean,
+ * without the row-independent |q|^2), eps[q] the bound the certificate assumes on |coarse - exact|.  Device pointers. */
+int32_t vsk_coarse_values_dev(vsk_index* index, const float* queries, int64_t nq, int64_t rows, float* coarse,
+                              float* eps);
 
 /* --- k-means / IVF -------------------------------------------------------------------------
  * Lloyd iterations from caller-supplied initial centroids.  Replaces KMeansClustering.cluster

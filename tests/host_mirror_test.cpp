@@ -44,6 +44,13 @@ int main() {
     return 8;
   } catch (const vsk::ImportFailed&) {
   }
+  // a communicator of one rank: the sharded call is the plain search, in both layouts
+  dev->joinCommunicator(1, 0, {});
+  int64_t first = -1;
+  auto s1 = ix.shardedSearch(q, 1, 2, nullptr, false, &first);
+  auto s2 = ix.shardedSearch(q, 1, 2, nullptr, true);
+  if (first != 0 || s1.ids != r.ids || s1.distances != r.distances || s2.ids != r.ids) return 11;
+  dev->leaveCommunicator();
   // product quantiser: 2 segments of 2 dimensions, 16 codewords; row 1 sits on codewords (3, 5)
   vsk::ProductQuantizer pq(dev, 4, 2, 4);
   std::vector<float> cb(2 * 16 * 2);

@@ -419,30 +419,90 @@ def test_cpp_host_mirror_on_gpu(tmp_path):
     assert out.returncode == 0 and out.stdout.strip() == "ok", out
 
 
-def test_cta_pair_kernel_in_subprocess():
-    """The cta_group::2 variant of the tensor scan (opt-in through VSK_TC_PAIR, read once per process)."""
-    import subprocess, sys, textwrap
-    code = textwrap.dedent("""
-        import sys, numpy as np
-        sys.path.insert(0, %r); sys.path.insert(0, %r)
-        import vectorstorekit_b200 as vsk, oracle
-        from parity import assert_topk_parity
-        dev = vsk.CUDAComputeDevice(0)
-        rng = np.random.default_rng(5)
-        for metric, mid in (("cosine", oracle.COSINE), ("euclidean", oracle.EUCLIDEAN)):
-            x = rng.standard_normal((30000, 200)).astype(np.float32)
-            q = rng.standard_normal((300, 200)).astype(np.float32)
-            ix = vsk.FlatIndex(dev, 200, metric); ix.add(x)
-            d, i = ix.batchSearch(q, 25)
-            rd, ri = oracle.CpuOracle().flat_search(mid, q, x, 25)
-            assert_topk_parity(d, i, rd, ri)
-        st = dev.stats()
-        assert st["tensor_tiles"] > 0 and st["fallback_queries"] == 0
-        print("pair-ok")
-    """) % (ROOT, os.path.join(ROOT, "tests"))
-    env = dict(os.environ, VSK_TC_PAIR="1")
-    out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, timeout=300)
-    assert out.returncode == 0 and "pair-ok" in out.stdout, out.stderr[-2000:]
+def test_two_lanes_equal_one_lane(vsk, cpu_oracle):
+    """A batch large enough for the two-lane schedule (two halves on two streams) returns what the one-lane schedule
+    returns, bit for bit, and both match the oracle; uneven halves and a batch just above the switch included."""
+    import torch
+    dev = vsk.CUDAComputeDevice(0)
+    rng = np.random.default_rng(77)
+    try:
+        for metric, d, nq in (("cosine", 256, 2048 + 37), ("euclidean", 96, 4096), ("dotProduct", 320, 3000)):
+            x = rng.standard_normal((60_000, d)).astype(np.float32)
+            q = rng.standard_normal((nq, d)).astype(np.float32)
+            ix = vsk.FlatIndex(dev, d, metric)
+            ix.add(x)
+            qd = torch.as_tensor(q, device="cuda")
+            dev.set_tuning(overlap_min_queries=2048)
+            d2, i2 = ix.batchSearch(qd, 20)
+            dev.set_tuning(overlap_min_queries=0)
+            d1, i1 = ix.batchSearch(qd, 20)
+            assert torch.equal(i1, i2) and torch.equal(d1, d2)
+            sub = np.arange(0, nq, 16)
+            rd, ri = cpu_oracle.flat_search(oracle.METRIC_IDS[metric], q[sub], x, 20)
+            assert_topk_parity(d2.cpu().numpy()[sub], i2.cpu().numpy()[sub], rd, ri)
+            ix.close()
+        assert dev.tuning()["overlap_min_queries"] == 0
+    finally:
+        dev.close()
+
+
+@pytest.mark.parametrize("metric", ["euclidean", "cosine", "dotProduct"])
+def test_filtered_batch_stays_on_the_tensor_path(vsk, cpu_oracle, metric):
+    """A filtered batch of a tensor-path metric is filtered in the contraction's epilogue: tensor tiles are computed,
+    the result equals the oracle's pre-filter + search.  One-hot masks over Bernoulli(0.5) row masks, a mask that
+    matches nothing, one that matches everything, and a rare bit (1 % of the rows) that leaves fewer than k rows in
+    the first chunk."""
+    dev = vsk.CUDAComputeDevice(0)
+    try:
+        rng = np.random.default_rng(5150)
+        n, d, nq, k = 50_000, 200, 700, 30
+        x = rng.standard_normal((n, d)).astype(np.float32)
+        q = rng.standard_normal((nq, d)).astype(np.float32)
+        rm = rng.integers(0, 2 ** 62, n, dtype=np.uint64)
+        rare = rng.random(n) < 0.01
+        rm = (rm & ~np.uint64(1 << 62)) | (rare.astype(np.uint64) << np.uint64(62))
+        qm = (np.uint64(1) << rng.integers(0, 62, nq).astype(np.uint64))
+        qm[0:40] = np.uint64(1 << 63)                     # no row has bit 63
+        qm[40:80] = np.uint64(2 ** 64 - 1)                # every row with any bit
+        qm[80:140] = np.uint64(1 << 62)                   # the rare bit
+        ix = vsk.FlatIndex(dev, d, metric)
+        ix.add(x, rm)
+        before = dev.stats()
+        gd, gi = ix.batchSearch(q, k, qm)
+        after = dev.stats()
+        ix.close()
+        assert after["tensor_tiles"] > before["tensor_tiles"]
+        rd, ri = cpu_oracle.flat_search(oracle.METRIC_IDS[metric], q, x, k, rm, qm)
+        assert_topk_parity(gd, gi, rd, ri)
+        assert np.all(gi[:40] == -1)
+        ok = gi >= 0
+        assert np.all(((rm[np.clip(gi, 0, None)] & qm[:, None]) != 0) | ~ok)
+    finally:
+        dev.close()
+
+
+def test_selective_filters_take_the_row_list_path(vsk, cpu_oracle):
+    """When the filters leave only a few percent of the pairs eligible, scanning the eligible rows beats filtering
+    the full contraction: the batch goes to the grouped fp32 scan (no tensor tiles) and is exact all the same."""
+    dev = vsk.CUDAComputeDevice(0)
+    try:
+        rng = np.random.default_rng(61)
+        n, d, nq, k = 40_000, 64, 300, 10
+        x = rng.standard_normal((n, d)).astype(np.float32)
+        q = rng.standard_normal((nq, d)).astype(np.float32)
+        rm = (rng.random(n) < 0.01).astype(np.uint64) | ((rng.random(n) < 0.02).astype(np.uint64) << np.uint64(1))
+        qm = np.where(np.arange(nq) % 2 == 0, np.uint64(1), np.uint64(2)).astype(np.uint64)
+        ix = vsk.FlatIndex(dev, d, "euclidean")
+        ix.add(x, rm)
+        before = dev.stats()
+        gd, gi = ix.batchSearch(q, k, qm)
+        after = dev.stats()
+        ix.close()
+        assert after["tensor_tiles"] == before["tensor_tiles"]
+        rd, ri = cpu_oracle.flat_search(oracle.EUCLIDEAN, q, x, k, rm, qm)
+        assert_topk_parity(gd, gi, rd, ri)
+    finally:
+        dev.close()
 
 
 def test_distance_matrix_api(vsk, dev, cpu_oracle):

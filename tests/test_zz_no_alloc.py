@@ -48,6 +48,22 @@ def test_static_scratch_assign_matches_allocating_entry_point_twice():
             assert np.mean(a1 == a0) > 0.999
             assert np.allclose(d1, d0, rtol=1e-4, atol=1e-4)
             assert a1.min() >= 0 and a1.max() < k
+        # the property the entry point exists for: after its first call on the device it allocates nothing.  Free
+        # device memory (cudaMemGetInfo) must not move across further calls - also right after the allocating entry
+        # point grew its own scratch for a larger batch.
+        x = torch.randn((200_000, 64), generator=g, device="cuda")
+        c = torch.randn((300, 64), generator=g, device="cuda")
+        xs = x[:50_000].contiguous()
+        st, _, _ = _call(lib, lib.vsk_assign_dev, ctx, x, c)
+        assert st == 0
+        outs = [torch.empty(50_000, dtype=torch.int32, device="cuda"), torch.empty(50_000, dtype=torch.float32, device="cuda")]
+        torch.cuda.synchronize()
+        free0 = torch.cuda.mem_get_info()[0]
+        for _ in range(3):
+            st = lib.vsk_assign_static_dev(ctx, C.c_void_p(xs.data_ptr()), 50_000, 64, C.c_void_p(c.data_ptr()), 300,
+                                           C.c_void_p(outs[0].data_ptr()), C.c_void_p(outs[1].data_ptr()))
+            assert st == 0
+            assert torch.cuda.mem_get_info()[0] == free0
         # beyond the fixed capacity: refused with a clear message, nothing launched
         big = (1 << 20) + 1
         x = torch.zeros((big, 4), device="cuda")

@@ -9,7 +9,7 @@ from .engine import (CUDAAccelerationEngine, CUDAAcceleratorStrategy, CUDAComput
                      InsufficientTrainingData, InvalidBufferSize, IVFIndex, KMeansClustering, QuantizedFlatIndex,
                      ScalarQuantizer, InvalidInput, NotTrained, SearchStrategy, Timeout,
                      UnsupportedOperation, VSKError, PATH_FP32_SCAN, PATH_TENSOR_RERANK, ImportFailed,
-                     ExportFailed, import_index, load_index, ProductQuantizer, PQIndex, KMeansTrainer)
+                     ExportFailed, import_index, load_index, ProductQuantizer, PQIndex, KMeansTrainer, sharded_slice)
 from .filters import (CompositeFilter, FilterBitmaskCompiler, FilterOperation, LogicalOperation, MetadataFilter,
                       VectorFilter)
 

@@ -39,6 +39,16 @@ class IndexInfo(C.Structure):
                 ("pq_codebook_size", C.c_int32), ("reserved", C.c_int32)]
 
 
+class Tuning(C.Structure):
+    _fields_ = [("fold_row_term", C.c_int32), ("chunk_growth", C.c_int32), ("dense_rows", C.c_int32),
+                ("ivf_pilot_tiles", C.c_int32), ("stream_scan", C.c_int32), ("overlap_min_queries", C.c_int32),
+                ("reserved", C.c_int32 * 10)]
+
+
+COMM_ID_BYTES = 128
+SHARDED_SLICE, SHARDED_ALL, SHARDED_QUERIES_SPLIT = 0, 1, 16
+SHARDED_PHASES = 7
+
 # name -> (restype, argtypes).  Pointers that may be host or device memory are void*.
 SIGNATURES = {
     "vsk_open": (C.c_int32, [C.c_int32, C.POINTER(vp)]),
@@ -50,6 +60,19 @@ SIGNATURES = {
     "vsk_set_search_path": (C.c_int32, [vp, C.c_int32]),
     "vsk_stream": (vp, [vp]),
     "vsk_profile": (C.c_int32, [vp, C.c_int32]),
+    "vsk_schedule_chunk": (C.c_int64, [C.c_int64, C.c_int32, C.c_int32]),
+    "vsk_measure_peak": (C.c_int32, [vp, C.c_int32, C.POINTER(C.c_double)]),
+    "vsk_tuning_get": (C.c_int32, [vp, C.POINTER(Tuning)]),
+    "vsk_tuning_set": (C.c_int32, [vp, C.POINTER(Tuning)]),
+    "vsk_comm_unique_id": (C.c_int32, [vp]),
+    "vsk_comm_init": (C.c_int32, [vp, C.c_int32, C.c_int32, vp]),
+    "vsk_comm_destroy": (C.c_int32, [vp]),
+    "vsk_comm_info": (C.c_int32, [vp, C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
+    "vsk_sharded_slice": (None, [C.c_int64, C.c_int32, C.c_int32, C.POINTER(C.c_int64), C.POINTER(C.c_int64)]),
+    "vsk_search_sharded_dev": (C.c_int32, [vp, vp, C.c_int64, C.c_int32, vp, C.c_int32, vp, vp]),
+    "vsk_search_sharded": (C.c_int32, [vp, vp, C.c_int64, C.c_int32, vp, C.c_int32, vp, vp]),
+    "vsk_sharded_phase_ms": (C.c_int32, [vp, C.POINTER(C.c_float)]),
+    "vsk_coarse_values_dev": (C.c_int32, [vp, vp, C.c_int64, C.c_int64, vp, vp]),
     "vsk_batch_distances": (C.c_int32, [vp, C.c_int32, vp, C.c_int64, vp, C.c_int64, C.c_int32, vp]),
     "vsk_batch_distances_dev": (C.c_int32, [vp, C.c_int32, vp, C.c_int64, vp, C.c_int64, C.c_int32, vp]),
     "vsk_flat_create": (C.c_int32, [vp, C.c_int32, C.c_int32, C.POINTER(vp)]),

@@ -69,6 +69,7 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
         for _, log in results:
             sys.stderr.write(log)
     objs = [o for o, _ in results]
+    # NCCL is looked up with dlopen when a communicator is first asked for: no -lnccl here
     cmd = [nvcc, "-shared", "-cudart", "static", "-o", LIB] + objs + ["-lpthread", "-ldl"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:

@@ -42,7 +42,37 @@ void dev_free(void* p) {
   if (p) cudaFree(p);
 }
 
+int32_t lanes_fork(Ctx* ctx) {
+  VSK_CUDA(ctx, cudaEventRecord(ctx->ev_fork, ctx->stream_main));
+  VSK_CUDA(ctx, cudaStreamWaitEvent(ctx->stream_aux, ctx->ev_fork, 0));
+  return VSK_OK;
+}
+int32_t lanes_join(Ctx* ctx) {
+  VSK_CUDA(ctx, cudaEventRecord(ctx->ev_join, ctx->stream_aux));
+  VSK_CUDA(ctx, cudaStreamWaitEvent(ctx->stream_main, ctx->ev_join, 0));
+  return VSK_OK;
+}
+
+int32_t pinned_reserve(Ctx* ctx, PinnedBuf* b, size_t bytes) {
+  if (b->bytes >= bytes) return VSK_OK;
+  // the old buffer may still be the target of a copy in flight
+  VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream_main));
+  VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream_aux));
+  if (b->p) cudaFreeHost(b->p);
+  b->p = nullptr;
+  b->bytes = 0;
+  const size_t want = bytes + bytes / 4 + 4096;
+  if (cudaHostAlloc(&b->p, want, cudaHostAllocDefault) != cudaSuccess) {
+    cudaGetLastError();
+    b->p = nullptr;
+    return fail(ctx, VSK_ERR_OUT_OF_MEMORY, "pinned host memory: %zu bytes not available", want);
+  }
+  b->bytes = want;
+  return VSK_OK;
+}
+
 int32_t scratch(Ctx* ctx, int slot, size_t bytes, void** out) {
+  slot += ctx->lane * 64;   // each lane has its own set of buffers
   if (ctx->scratch_bytes[slot] < bytes) {
     // in-flight work may still use the old buffer
     VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
@@ -82,6 +112,17 @@ void prof_collect(Ctx* ctx) {
   ctx->prof_used = 0;
 }
 
+vsk_tuning default_tuning() {
+  vsk_tuning t{};
+  t.fold_row_term = 1;
+  t.chunk_growth = 3;
+  t.dense_rows = 0;
+  t.ivf_pilot_tiles = 4;
+  t.stream_scan = 1;
+  t.overlap_min_queries = 2048;
+  return t;
+}
+
 static bool metric_ok(int32_t m) { return m >= VSK_METRIC_EUCLIDEAN && m <= VSK_METRIC_MANHATTAN; }
 
 // Candidate-list workspace for `nq` queries.
@@ -114,15 +155,8 @@ int64_t schedule_chunk(int64_t seen, int32_t keep, int level) {
   return std::max<int64_t>(room, (int64_t)(g * (double)seen));
 }
 
-// Tuning overrides for experiments (unset in normal use): VSK_DENSE_ROWS, VSK_GROWTH.
-int64_t schedule_tuning(const char* name, int64_t dflt) {
-  const char* v = getenv(name);
-  return v && *v ? atoll(v) : dflt;
-}
-
-int64_t schedule_dense_rows(int32_t keep) {
-  static const int64_t forced = schedule_tuning("VSK_DENSE_ROWS", 0);
-  if (forced > 0) return std::min<int64_t>(kCandCap, forced);
+int64_t schedule_dense_rows(const Ctx* ctx, int32_t keep) {
+  if (ctx->tuning.dense_rows > 0) return std::min<int64_t>(kCandCap, ctx->tuning.dense_rows);
   return std::min<int64_t>(kCandCap, std::max<int64_t>(1024, ceil_div(8 * (int64_t)keep, 256) * 256));
 }
 
@@ -138,12 +172,15 @@ int32_t schedule_max_count(int64_t seen, int64_t chunk, int32_t keep) {
 // and its query is re-run at the next level.
 static int32_t run_schedule(Ctx* ctx, const ScanFn& scan, int64_t n, int64_t nq, int32_t keep,
                             const CandLists& cand, int level) {
+  // a list must have room beyond the keys it keeps, or the walk below would never advance
+  if (keep <= 0 || keep > kCandCap / 2)
+    return fail(ctx, VSK_ERR_INVALID_INPUT, "a search keeps between 1 and %d rows per query (asked for %d)", kCandCap / 2, keep);
   VSK_TRY(launch_init_cand(ctx, cand, nq));
   SelectArgs sel{};
   sel.cand = cand;
   sel.nq = nq;
   sel.keep = keep;
-  int64_t seen = std::min<int64_t>(n, schedule_dense_rows(keep));
+  int64_t seen = std::min<int64_t>(n, schedule_dense_rows(ctx, keep));
   VSK_TRY(scan(SCAN_DENSE, 0, seen));
   sel.dense_count = (int32_t)seen;
   sel.max_count = (int32_t)seen;
@@ -151,6 +188,7 @@ static int32_t run_schedule(Ctx* ctx, const ScanFn& scan, int64_t n, int64_t nq,
   sel.dense_count = -1;
   while (seen < n) {
     const int64_t chunk = std::min(schedule_chunk(seen, keep, level), n - seen);
+    if (chunk <= 0) return fail(ctx, VSK_ERR_EXECUTION_FAILED, "search schedule: empty chunk after %lld rows", (long long)seen);
     VSK_TRY(scan(SCAN_THRESHOLD, seen, seen + chunk));
     sel.max_count = level >= 2 ? kCandCap : schedule_max_count(seen, chunk, keep);
     VSK_TRY(launch_select(ctx, sel));
@@ -285,6 +323,25 @@ __global__ void mask_compact_kernel(const uint64_t* __restrict__ masks, int64_t 
   if (pass) rows[block_base + warp_base[warp] + __popc(bal & ((1u << lane) - 1u))] = (int32_t)i;
 }
 
+// counts[g] = rows eligible under group mask g (at most 64 groups; one pass over the row masks)
+__global__ void mask_count_kernel(const uint64_t* __restrict__ masks, int64_t n, const uint64_t* __restrict__ gmasks,
+                                  int groups, unsigned long long* __restrict__ counts) {
+  __shared__ uint64_t gm[64];
+  __shared__ unsigned int local[64];
+  if (threadIdx.x < 64) {
+    gm[threadIdx.x] = threadIdx.x < groups ? gmasks[threadIdx.x] : 0ull;
+    local[threadIdx.x] = 0u;
+  }
+  __syncthreads();
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const uint64_t m = masks[i];
+    for (int g = 0; g < groups; ++g)
+      if ((m & gm[g]) != 0ull) atomicAdd(&local[g], 1u);
+  }
+  __syncthreads();
+  if (threadIdx.x < groups && local[threadIdx.x]) atomicAdd(&counts[threadIdx.x], (unsigned long long)local[threadIdx.x]);
+}
+
 __global__ void fill_empty_results_kernel(const int32_t* __restrict__ qpos, int64_t m, int k, float* out_dist,
                                           int64_t* out_ids) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -303,8 +360,12 @@ static int pick_query_tile(int64_t g) {
 }
 
 // Returns *handled = false (and does nothing) when the batch has too many distinct masks to profit.
+// max_fraction >= 0: the caller has a faster scan for the unfiltered pairs (the tensor path, about thirty times the
+// fp32 tile's rate) and this path is taken only when the filters leave less than that share of the (query, row)
+// pairs eligible - then scanning only eligible rows wins all the same.
 static int32_t filtered_grouped_search(Index* ix, const float* q, int64_t nq, int32_t k, const float* qnorm,
-                                       const uint64_t* qmasks, float* out_dist, int64_t* out_ids, bool* handled) {
+                                       const uint64_t* qmasks, float* out_dist, int64_t* out_ids, bool* handled,
+                                       double max_fraction = -1.0) {
   Ctx* ctx = ix->ctx;
   *handled = false;
   std::vector<uint64_t> hm((size_t)nq);
@@ -331,8 +392,26 @@ static int32_t filtered_grouped_search(Index* ix, const float* q, int64_t nq, in
   // no query may see are skipped there too) beats one pass over the eligible rows per group, unless there is
   // only one group.
   if (nq <= kStreamScanMaxQueries && groups > 1) return VSK_OK;
-  *handled = true;
   void *dperm, *drows, *dcount;
+  if (max_fraction >= 0.0) {
+    if (groups > 64) return VSK_OK;
+    std::vector<uint64_t> gm((size_t)groups);
+    for (int64_t g = 0; g < groups; ++g) gm[(size_t)g] = hm[(size_t)perm[(size_t)starts[(size_t)g]]];
+    VSK_TRY(scratch(ctx, SLOT_FILTER_COUNT, 64 * 16, &dcount));
+    unsigned long long* dcnt = (unsigned long long*)dcount;
+    uint64_t* dgm = (uint64_t*)dcount + 64;
+    VSK_CUDA(ctx, cudaMemsetAsync(dcnt, 0, 64 * 8, ctx->stream));
+    VSK_CUDA(ctx, cudaMemcpyAsync(dgm, gm.data(), (size_t)groups * 8, cudaMemcpyHostToDevice, ctx->stream));
+    mask_count_kernel<<<(unsigned)std::min<int64_t>(ceil_div(ix->n, 256), 1184), 256, 0, ctx->stream>>>(ix->masks, ix->n, dgm, (int)groups, dcnt);
+    ctx->stats.kernel_launches++;
+    std::vector<unsigned long long> cnt((size_t)groups);
+    VSK_CUDA(ctx, cudaMemcpyAsync(cnt.data(), dcnt, (size_t)groups * 8, cudaMemcpyDeviceToHost, ctx->stream));
+    VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    double pairs = 0.0;
+    for (int64_t g = 0; g < groups; ++g) pairs += (double)(starts[(size_t)g + 1] - starts[(size_t)g]) * (double)cnt[(size_t)g];
+    if (pairs >= max_fraction * (double)nq * (double)ix->n) return VSK_OK;
+  }
+  *handled = true;
   VSK_TRY(scratch(ctx, SLOT_FILTER_PERM, (size_t)nq * 4, &dperm));
   VSK_TRY(scratch(ctx, SLOT_FILTER_ROWS, (size_t)ix->n * 4, &drows));
   VSK_TRY(scratch(ctx, SLOT_FILTER_COUNT, 16, &dcount));
@@ -391,15 +470,19 @@ static int32_t flat_search_dev(Index* ix, const float* q, int64_t nq, int32_t k,
       qnorm = (float*)p;
       VSK_TRY(launch_row_norms(ctx, qb, bn, ix->dim, 0, qnorm));
     }
+    // Euclidean, cosine and dot-product batches take the tensor path, filtered or not (the filter is applied to the
+    // hits in the contraction's epilogue).  A batch of a few queries is bound by the bytes it reads, not by the
+    // contraction: the fp32 streaming scan reads each eligible fp32 row once.
     const bool tensor = ctx->search_path == VSK_PATH_TENSOR_RERANK && ix->metric != VSK_METRIC_MANHATTAN &&
-                        !qmasks;
+                        !(mb && bn <= kStreamScanMaxQueries);
     bool grouped = false;
     if (mb && ix->has_masks)
-      VSK_TRY(filtered_grouped_search(ix, qb, bn, k, qnorm, mb, out_dist + b * k, out_ids + b * k, &grouped));
+      VSK_TRY(filtered_grouped_search(ix, qb, bn, k, qnorm, mb, out_dist + b * k, out_ids + b * k, &grouped,
+                                      tensor ? 0.03 : -1.0));
     if (grouped) {
       // done: every group of equal masks was scanned against its own eligible rows
     } else if (tensor) {
-      VSK_TRY(tensor_search(ix, qb, bn, k, qnorm, out_dist + b * k, out_ids + b * k));
+      VSK_TRY(tensor_search(ix, qb, bn, k, qnorm, mb, out_dist + b * k, out_ids + b * k));
     } else {
       VSK_TRY(fp32_search(ix, qb, bn, nullptr, k, qnorm, mb, out_dist + b * k, out_ids + b * k, 0));
     }
@@ -410,7 +493,7 @@ static int32_t flat_search_dev(Index* ix, const float* q, int64_t nq, int32_t k,
 
 // Entry used by the tensor path for queries whose certificate failed.
 int32_t fp32_search_subset(Index* ix, const float* q, const std::vector<int32_t>& subset, int32_t k,
-                           const float* qnorm, float* out_dist, int64_t* out_ids) {
+                           const float* qnorm, const uint64_t* qmasks, float* out_dist, int64_t* out_ids) {
   Ctx* ctx = ix->ctx;
   if (subset.empty()) return VSK_OK;
   void* p;
@@ -418,7 +501,7 @@ int32_t fp32_search_subset(Index* ix, const float* q, const std::vector<int32_t>
   VSK_CUDA(ctx, cudaMemcpyAsync(p, subset.data(), subset.size() * sizeof(int32_t), cudaMemcpyHostToDevice, ctx->stream));
   VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   ctx->stats.fallback_queries += (int64_t)subset.size();
-  return fp32_search(ix, q, (int64_t)subset.size(), (const int32_t*)p, k, qnorm, nullptr, out_dist, out_ids, 0);
+  return fp32_search(ix, q, (int64_t)subset.size(), (const int32_t*)p, k, qnorm, qmasks, out_dist, out_ids, 0);
 }
 
 int32_t flat_reserve(Index* ix, int64_t need) {
@@ -428,9 +511,15 @@ int32_t flat_reserve(Index* ix, int64_t need) {
   float* rows = nullptr;
   float* norm = nullptr;
   uint64_t* masks = nullptr;
-  VSK_TRY(dev_alloc(ctx, (void**)&rows, (size_t)cap * ix->dim * sizeof(float)));
-  VSK_TRY(dev_alloc(ctx, (void**)&norm, (size_t)cap * sizeof(float)));
-  VSK_TRY(dev_alloc(ctx, (void**)&masks, (size_t)cap * sizeof(uint64_t)));
+  int32_t st;
+  if ((st = dev_alloc(ctx, (void**)&rows, (size_t)cap * ix->dim * sizeof(float))) != VSK_OK ||
+      (st = dev_alloc(ctx, (void**)&norm, (size_t)cap * sizeof(float))) != VSK_OK ||
+      (st = dev_alloc(ctx, (void**)&masks, (size_t)cap * sizeof(uint64_t))) != VSK_OK) {
+    dev_free(rows);   // out of memory part-way: the index keeps what it had
+    dev_free(norm);
+    dev_free(masks);
+    return st;
+  }
   if (ix->n > 0) {
     VSK_CUDA(ctx, cudaMemcpyAsync(rows, ix->rows, (size_t)ix->n * ix->dim * sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream));
     VSK_CUDA(ctx, cudaMemcpyAsync(norm, ix->row_norm, (size_t)ix->n * sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream));
@@ -531,10 +620,19 @@ int32_t vsk_open(int32_t device, vsk_ctx** out_ctx) {
     delete ctx;
     return VSK_ERR_DEVICE_NOT_AVAILABLE;
   }
-  if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess) {
+  if (cudaStreamCreateWithFlags(&ctx->stream_main, cudaStreamNonBlocking) != cudaSuccess ||
+      cudaStreamCreateWithFlags(&ctx->stream_aux, cudaStreamNonBlocking) != cudaSuccess ||
+      cudaEventCreateWithFlags(&ctx->ev_fork, cudaEventDisableTiming) != cudaSuccess ||
+      cudaEventCreateWithFlags(&ctx->ev_join, cudaEventDisableTiming) != cudaSuccess) {
+    if (ctx->stream_main) cudaStreamDestroy(ctx->stream_main);
+    if (ctx->stream_aux) cudaStreamDestroy(ctx->stream_aux);
+    if (ctx->ev_fork) cudaEventDestroy(ctx->ev_fork);
+    cudaGetLastError();
     delete ctx;
     return VSK_ERR_DEVICE_NOT_AVAILABLE;
   }
+  ctx->stream = ctx->stream_main;
+  ctx->tuning = default_tuning();
   *out_ctx = reinterpret_cast<vsk_ctx*>(ctx);
   return VSK_OK;
 }
@@ -543,10 +641,17 @@ int32_t vsk_close(vsk_ctx* c) {
   Ctx* ctx = reinterpret_cast<Ctx*>(c);
   if (!ctx) return VSK_ERR_INVALID_INPUT;
   cudaSetDevice(ctx->device);
-  cudaStreamSynchronize(ctx->stream);
+  cudaStreamSynchronize(ctx->stream_main);
+  cudaStreamSynchronize(ctx->stream_aux);
+  comm_release(ctx);
   for (auto& p : ctx->scratch) dev_free(p);
+  for (auto& b : ctx->host_flags)
+    if (b.p) cudaFreeHost(b.p);
   for (auto& e : ctx->prof_events) cudaEventDestroy(e);
-  cudaStreamDestroy(ctx->stream);
+  cudaEventDestroy(ctx->ev_fork);
+  cudaEventDestroy(ctx->ev_join);
+  cudaStreamDestroy(ctx->stream_main);
+  cudaStreamDestroy(ctx->stream_aux);
   delete ctx;
   return VSK_OK;
 }
@@ -591,6 +696,11 @@ int32_t vsk_set_search_path(vsk_ctx* c, int32_t path) {
   return VSK_OK;
 }
 
+int64_t vsk_schedule_chunk(int64_t seen, int32_t keep, int32_t level) {
+  if (seen < 0 || keep <= 0 || keep > kCandCap / 2) return -1;
+  return schedule_chunk(seen, keep, level);
+}
+
 int32_t vsk_profile(vsk_ctx* c, int32_t enable) {
   Ctx* ctx = reinterpret_cast<Ctx*>(c);
   if (!ctx) return VSK_ERR_INVALID_INPUT;
@@ -602,7 +712,24 @@ int32_t vsk_profile(vsk_ctx* c, int32_t enable) {
 
 void* vsk_stream(vsk_ctx* c) {
   Ctx* ctx = reinterpret_cast<Ctx*>(c);
-  return ctx ? (void*)ctx->stream : nullptr;
+  return ctx ? (void*)ctx->stream_main : nullptr;
+}
+
+int32_t vsk_tuning_get(vsk_ctx* c, vsk_tuning* out) {
+  Ctx* ctx = reinterpret_cast<Ctx*>(c);
+  if (!ctx || !out) return VSK_ERR_INVALID_INPUT;
+  *out = ctx->tuning;
+  return VSK_OK;
+}
+
+int32_t vsk_tuning_set(vsk_ctx* c, const vsk_tuning* in) {
+  Ctx* ctx = reinterpret_cast<Ctx*>(c);
+  if (!ctx || !in) return VSK_ERR_INVALID_INPUT;
+  if (in->chunk_growth < 1 || in->ivf_pilot_tiles < 1 || in->ivf_pilot_tiles > 16 || in->dense_rows < 0 ||
+      in->dense_rows > kCandCap || in->overlap_min_queries < 0)
+    return fail(ctx, VSK_ERR_INVALID_INPUT, "tuning value out of range");
+  ctx->tuning = *in;
+  return VSK_OK;
 }
 
 int32_t vsk_batch_distances_dev(vsk_ctx* c, int32_t metric, const float* q, int64_t nq, const float* x,
@@ -752,6 +879,32 @@ int32_t vsk_search_dev(vsk_index* i, const float* q, int64_t nq, int32_t k, cons
   return flat_search_dev(ix, q, nq, k, qmasks, out_dist, out_ids);
 }
 
+}  // extern "C"
+
+namespace vsk {
+// vsk_search_dev for callers inside the library (the device is already selected)
+int32_t flat_search_dev_entry(Index* ix, const float* q, int64_t nq, int32_t k, const uint64_t* qmasks, float* out_dist,
+                              int64_t* out_ids) {
+  if (ix->kind == INDEX_FLAT_I8) return sq8_search_dev(ix, q, nq, k, out_dist, out_ids);
+  return flat_search_dev(ix, q, nq, k, qmasks, out_dist, out_ids);
+}
+}  // namespace vsk
+
+extern "C" {
+
+int32_t vsk_coarse_values_dev(vsk_index* i, const float* q, int64_t nq, int64_t rows, float* coarse, float* eps) {
+  Index* ix = reinterpret_cast<Index*>(i);
+  if (!ix) return VSK_ERR_INVALID_INPUT;
+  Ctx* ctx = ix->ctx;
+  cudaSetDevice(ctx->device);
+  if (ix->kind != INDEX_FLAT_F32) return fail(ctx, VSK_ERR_INVALID_INPUT, "not a flat fp32 index");
+  if (ix->metric == VSK_METRIC_MANHATTAN) return fail(ctx, VSK_ERR_UNSUPPORTED_OPERATION, "manhattan has no tensor path");
+  if (nq <= 0 || ix->n <= 0) return fail(ctx, VSK_ERR_EMPTY_INPUT, "empty queries or empty index");
+  if (nq > kQueryBatch) return fail(ctx, VSK_ERR_INVALID_BUFFER_SIZE, "at most %lld queries per call", (long long)kQueryBatch);
+  if (!q || !coarse) return fail(ctx, VSK_ERR_INVALID_INPUT, "null pointer");
+  return tensor_coarse_values(ix, q, nq, rows, coarse, eps);
+}
+
 __global__ void fill_inf_kernel(float* p, int64_t n) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) p[i] = CUDART_INF_F;
@@ -762,7 +915,7 @@ int32_t vsk_search_shard_begin_dev(vsk_index* i, const float* q, int64_t nq, int
   if (!ix) return VSK_ERR_INVALID_INPUT;
   Ctx* ctx = ix->ctx;
   cudaSetDevice(ctx->device);
-  ctx->pending = ShardPending{};
+  ctx->pending[ctx->lane] = ShardPending{};
   if (ix->kind != INDEX_FLAT_F32) return fail(ctx, VSK_ERR_UNSUPPORTED_OPERATION, "the two-half search covers flat fp32 indexes");
   if (nq <= 0 || ix->n <= 0) return fail(ctx, VSK_ERR_EMPTY_INPUT, "empty queries or empty index");
   if (nq > kQueryBatch) return fail(ctx, VSK_ERR_INVALID_BUFFER_SIZE, "at most %lld queries per two-half search", (long long)kQueryBatch);
@@ -775,11 +928,11 @@ int32_t vsk_search_shard_begin_dev(vsk_index* i, const float* q, int64_t nq, int
     fill_inf_kernel<<<(unsigned)ceil_div(nq, 256), 256, 0, ctx->stream>>>(bound, nq);
     ctx->stats.kernel_launches++;
     VSK_CUDA(ctx, cudaGetLastError());
-    ctx->pending.active = true;
-    ctx->pending.ix = ix;
-    ctx->pending.q = q;
-    ctx->pending.nq = nq;
-    ctx->pending.k = k;
+    ctx->pending[ctx->lane].active = true;
+    ctx->pending[ctx->lane].ix = ix;
+    ctx->pending[ctx->lane].q = q;
+    ctx->pending[ctx->lane].nq = nq;
+    ctx->pending[ctx->lane].k = k;
     return VSK_OK;
   }
   ctx->stats.searches++;
@@ -791,7 +944,7 @@ int32_t vsk_search_shard_begin_dev(vsk_index* i, const float* q, int64_t nq, int
     qnorm = (float*)p;
     VSK_TRY(launch_row_norms(ctx, q, nq, ix->dim, 0, qnorm));
   }
-  return tensor_search_begin(ix, q, nq, k, qnorm, shards, bound);
+  return tensor_search_begin(ix, q, nq, k, qnorm, nullptr, shards, bound);
 }
 
 int32_t vsk_search_shard_finish_dev(vsk_index* i, const float* bound, float* out_dist, int64_t* out_ids) {
@@ -800,11 +953,11 @@ int32_t vsk_search_shard_finish_dev(vsk_index* i, const float* bound, float* out
   Ctx* ctx = ix->ctx;
   cudaSetDevice(ctx->device);
   if (!bound || !out_dist || !out_ids) return fail(ctx, VSK_ERR_INVALID_INPUT, "null pointer");
-  if (!ctx->pending.active || ctx->pending.ix != ix)
+  if (!ctx->pending[ctx->lane].active || ctx->pending[ctx->lane].ix != ix)
     return fail(ctx, VSK_ERR_INVALID_INPUT, "no search is waiting for its second half on this index");
-  if (!ctx->pending.tensor) {
-    const ShardPending pd = ctx->pending;
-    ctx->pending = ShardPending{};
+  if (!ctx->pending[ctx->lane].tensor) {
+    const ShardPending pd = ctx->pending[ctx->lane];
+    ctx->pending[ctx->lane] = ShardPending{};
     return flat_search_dev(ix, pd.q, pd.nq, pd.k, nullptr, out_dist, out_ids);
   }
   VSK_TRY(tensor_search_finish(ix, bound, out_dist, out_ids));

@@ -93,30 +93,72 @@ struct ShardPending {
   Index* ix = nullptr;
   const float* q = nullptr;
   const float* qnorm = nullptr;
+  const uint64_t* qmasks = nullptr;
   int64_t nq = 0;
   int32_t k = 0, keep = 0, max_count = 0;
   CandLists cand;
   const float* eps = nullptr;
   int32_t* err = nullptr;
   unsigned long long* rr_total = nullptr;
+  // second half issued, results not yet looked at by the host
+  bool issued = false;
+  float* out_dist = nullptr;
+  int64_t* out_ids = nullptr;
 };
 
+struct Comm;   // NCCL communicator of a row-sharded search (comm.cu)
+
+// Pinned host memory that grows on demand (results the host reads back right after a stream drains).
+struct PinnedBuf {
+  void* p = nullptr;
+  size_t bytes = 0;
+};
+
+// A context issues work on one of two LANES.  Lane 0 is the context's stream (`stream_main`, the one vsk_stream
+// returns).  A large tensor-path batch is split in two halves; the second half is issued on lane 1 (`stream_aux`),
+// so that one half's compactions, re-scoring and exchanges run under the other half's contraction.  `stream` and
+// `lane` say where launches and scratch requests go right now (LaneGuard switches them); each lane has its own
+// scratch slots and its own pending half-search, so the halves never share a work buffer.
 struct Ctx {
   int device = 0;
-  cudaStream_t stream = nullptr;
+  cudaStream_t stream = nullptr;        // where launches go now: stream_main, or stream_aux while lane 1 is issued
+  cudaStream_t stream_main = nullptr;
+  cudaStream_t stream_aux = nullptr;
+  cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+  int lane = 0;
   cudaDeviceProp prop{};
   std::string err;
   int32_t search_path = VSK_PATH_TENSOR_RERANK;
+  vsk_tuning tuning{};
   vsk_stats stats{};
   // optional timing of the dominant (scan) kernels with CUDA events on `stream`
   bool profile = false;
   std::vector<cudaEvent_t> prof_events;  // begin/end pairs
   size_t prof_used = 0;
-  // grow-only device scratch, one buffer per slot (see Slot)
-  void* scratch[64] = {};
-  size_t scratch_bytes[64] = {};
-  ShardPending pending;
+  // grow-only device scratch, one buffer per (lane, slot) (see Slot)
+  void* scratch[2 * 64] = {};
+  size_t scratch_bytes[2 * 64] = {};
+  ShardPending pending[2];
+  PinnedBuf host_flags[2];   // per lane: the flag words a finished half-search hands to the host
+  Comm* comm = nullptr;
 };
+
+// Issues on lane `lane` until it goes out of scope.
+struct LaneGuard {
+  Ctx* c;
+  LaneGuard(Ctx* ctx, int lane) : c(ctx) {
+    c->lane = lane;
+    c->stream = lane ? c->stream_aux : c->stream_main;
+  }
+  ~LaneGuard() {
+    c->lane = 0;
+    c->stream = c->stream_main;
+  }
+};
+// lane 1 starts after everything issued on lane 0 so far; lane 0 continues after everything issued on lane 1
+int32_t lanes_fork(Ctx* ctx);
+int32_t lanes_join(Ctx* ctx);
+int32_t pinned_reserve(Ctx* ctx, PinnedBuf* b, size_t bytes);
 
 enum Slot : int {
   SLOT_Q = 0, SLOT_OUT_D, SLOT_OUT_I, SLOT_QMASK, SLOT_CAND_KEYS, SLOT_CAND_COUNT, SLOT_CAND_THR,
@@ -124,7 +166,7 @@ enum Slot : int {
   SLOT_MISC2, SLOT_MISC3, SLOT_MISC4, SLOT_MISC5, SLOT_MISC6,
   SLOT_IVF_PROBE_D, SLOT_IVF_PROBE_I, SLOT_IVF_KEYS, SLOT_IVF_ORDER, SLOT_IVF_PAIR_OFF, SLOT_IVF_ITEM_CNT,
   SLOT_IVF_ITEM_OFF, SLOT_IVF_SUBSET, SLOT_IVF_STAGES, SLOT_KM_NSEG, SLOT_KM_SEGOFF, SLOT_KM_PARTIAL, SLOT_FILTER_PERM, SLOT_FILTER_ROWS, SLOT_FILTER_COUNT, SLOT_SQ_A, SLOT_SQ_B, SLOT_TC_A, SLOT_TC_B, SLOT_TC_C, SLOT_TC_D,
-  SLOT_PQ_TABLES,
+  SLOT_PQ_TABLES, SLOT_SH_D, SLOT_SH_I, SLOT_SH_SEND, SLOT_SH_RECV, SLOT_SH_BOUND, SLOT_SH_MERGED, SLOT_SH_ALL,
   SLOT_COUNT
 };
 static_assert(SLOT_COUNT <= 64, "grow Ctx::scratch");
@@ -225,7 +267,7 @@ int32_t launch_exact_scan(Ctx* ctx, const ExactScanArgs& a);
 constexpr int kStreamScanMaxQueries = 8;
 constexpr int kStreamScanMaxSegQueries = 16;   // with per-query row lists (one grid row per query): beyond this the
                                                // list-major tiles, which read a list once for all its queries, win
-bool stream_scan_applies(const ExactScanArgs& a);
+bool stream_scan_applies(const Ctx* ctx, const ExactScanArgs& a);
 int32_t launch_stream_scan(Ctx* ctx, const ExactScanArgs& a);
 int32_t launch_row_norms(Ctx* ctx, const float* x, int64_t n, int32_t dim, int squared, float* out);
 
@@ -269,6 +311,12 @@ int32_t launch_select(Ctx* ctx, const SelectArgs& a);
 int32_t launch_merge_topk(Ctx* ctx, const float* dist, const int64_t* ids, int32_t g, int64_t nq,
                           int32_t k, float* out_dist, int64_t* out_ids);
 int32_t launch_init_cand(Ctx* ctx, const CandLists& c, int64_t nq);
+// Packed (distance, global row) keys for the exchange between shards (select.cu): pack [nq][k] results into
+// [rows][k] keys (rows >= nq: padding is filled with missing entries), merge g lists per query, unpack.
+int32_t launch_pack_keys(Ctx* ctx, const float* dist, const int64_t* ids, int64_t nq, int64_t rows, int32_t k,
+                         uint64_t* keys);
+int32_t launch_unpack_keys(Ctx* ctx, const uint64_t* keys, int64_t count, float* dist, int64_t* ids);
+int32_t launch_merge_keys(Ctx* ctx, const uint64_t* in, int32_t g, int64_t stride_q, int64_t nq, int32_t k, uint64_t* out);
 
 // ---- search schedule in api.cu -------------------------------------------------------------
 // A scan of rows [row_begin, row_end) in ScanMode `mode` that writes keys into candidate lists, and the function
@@ -285,8 +333,7 @@ int32_t fp32_topk(Ctx* ctx, const ExactScanArgs& proto, int64_t n, int64_t nq, c
 int64_t schedule_chunk(int64_t seen, int32_t keep, int level);
 // Rows of the dense first chunk, and an upper bound (mean + 8 deviations) on the keys a list holds after a
 // thresholded chunk of `chunk` rows that followed `seen` rows.
-int64_t schedule_dense_rows(int32_t keep);
-int64_t schedule_tuning(const char* name, int64_t dflt);
+int64_t schedule_dense_rows(const Ctx* ctx, int32_t keep);
 int32_t schedule_max_count(int64_t seen, int64_t chunk, int32_t keep);
 
 // ---- pq.cu -------------------------------------------------------------------------------
@@ -294,6 +341,9 @@ int32_t pq_search_dev(Index* ix, const float* q, int64_t nq, int32_t k, float* o
 int32_t pq_reserve(Index* ix, int64_t need);
 
 // ---- helpers in api.cu ---------------------------------------------------------------------
+vsk_tuning default_tuning();
+// comm.cu: leaves the context's communicator, if any
+void comm_release(Ctx* ctx);
 int32_t dev_alloc(Ctx* ctx, void** p, size_t bytes);
 void dev_free(void* p);
 

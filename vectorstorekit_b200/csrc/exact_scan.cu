@@ -175,7 +175,7 @@ __global__ void row_norm_kernel(const float* __restrict__ x, int64_t n, int dim,
 }  // namespace
 
 int32_t launch_exact_scan(Ctx* ctx, const ExactScanArgs& a) {
-  if (stream_scan_applies(a)) return launch_stream_scan(ctx, a);   // a few queries: HBM-bound streaming kernel
+  if (stream_scan_applies(ctx, a)) return launch_stream_scan(ctx, a);   // a few queries: HBM-bound streaming kernel
   if (a.seg_begin) return fail(ctx, VSK_ERR_UNSUPPORTED_OPERATION, "per-query row lists need the streaming scan");
   switch (a.metric) {
     case VSK_METRIC_EUCLIDEAN: return launch_metric<VSK_METRIC_EUCLIDEAN>(ctx, a);

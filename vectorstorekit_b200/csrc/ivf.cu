@@ -427,6 +427,12 @@ __global__ void ivf_stored_to_ids_kernel(int64_t* ids, int64_t count, const int3
   if (i < count && ids[i] >= 0) ids[i] = (int64_t)list_rows[ids[i]] + id_base;
 }
 
+// every list, in index order, as each query's probe list
+__global__ void ivf_probe_all_kernel(int64_t* __restrict__ probes, int64_t nq, int nprobe) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < nq * nprobe) probes[i] = i % nprobe;
+}
+
 constexpr int64_t kIvfFewMaxEntries = 32ll << 20;   // row-list entries (128 MB) the few-query path may use
 
 // *handled = false (nothing done) when the batch does not fit this path.
@@ -474,7 +480,7 @@ int32_t ivf_search_few(Ctx* ctx, Index* ix, const float* q, int64_t nq, const in
   a.x_rows = (const int32_t*)drows;
   a.seg_begin = (const int64_t*)dbeg;
   a.seg_count = (const int32_t*)dcnt;
-  if (!stream_scan_applies(a)) return VSK_OK;
+  if (!stream_scan_applies(ctx, a)) return VSK_OK;
   *handled = true;
   if (!triples.empty())
     VSK_CUDA(ctx, cudaMemcpyAsync(dtri, triples.data(), triples.size() * 8, cudaMemcpyHostToDevice, ctx->stream));
@@ -502,6 +508,12 @@ int32_t ivf_search_dev(Index* ix, const float* q, int64_t nq, int32_t k, int32_t
   if (nprobe <= 0) return fail(ctx, VSK_ERR_INVALID_INPUT, "nprobe must be positive");
   if (!q || !out_dist || !out_ids) return fail(ctx, VSK_ERR_INVALID_INPUT, "null pointer");
   nprobe = std::min(nprobe, ix->nlist);
+  // The probe selection is a top-nprobe over the centroids and shares the candidate lists' limit on k.  Probing
+  // every list (the reference's `.exact` strategy, IVFIndex.swift:551-560) needs no selection at all.
+  const bool probe_all = nprobe == ix->nlist && nprobe > kCandCap / 2;
+  if (nprobe > kCandCap / 2 && !probe_all)
+    return fail(ctx, VSK_ERR_INVALID_INPUT, "nprobe must be at most %d, or equal to the number of lists (%d)", kCandCap / 2,
+                ix->nlist);
   ctx->stats.searches++;
   ctx->stats.queries += nq;
   constexpr int64_t kBatch = 16384;
@@ -513,7 +525,11 @@ int32_t ivf_search_dev(Index* ix, const float* q, int64_t nq, int32_t k, int32_t
     VSK_TRY(scratch(ctx, SLOT_IVF_PROBE_D, (size_t)bn * nprobe * 4, &pd));
     VSK_TRY(scratch(ctx, SLOT_IVF_PROBE_I, (size_t)bn * nprobe * 8, &pi));
     const bool tensor = ctx->search_path == VSK_PATH_TENSOR_RERANK && ivf_tensor_applicable(ix, bn, nprobe, k);
-    if (tensor && ix->nlist >= 1024 && nprobe <= 1024) {
+    if (probe_all) {
+      ivf_probe_all_kernel<<<(unsigned)ceil_div(bn * (int64_t)nprobe, 256), 256, 0, ctx->stream>>>((int64_t*)pi, bn, nprobe);
+      ctx->stats.kernel_launches++;
+      VSK_CUDA(ctx, cudaGetLastError());
+    } else if (tensor && ix->nlist >= 1024 && nprobe <= 1024) {
       // the centroids are a flat euclidean index of their own: exact top-nprobe on the tensor path
       if (!ix->coarse) {
         Index* co = new Index();
@@ -523,11 +539,16 @@ int32_t ivf_search_dev(Index* ix, const float* q, int64_t nq, int32_t k, int32_t
         co->dim = ix->dim;
         co->n = co->capacity = ix->nlist;
         co->rows = ix->centroids;
+        int32_t cst = dev_alloc(ctx, (void**)&co->row_norm, (size_t)ix->nlist * sizeof(float));
+        if (cst == VSK_OK) cst = launch_row_norms(ctx, co->rows, co->n, co->dim, 1, co->row_norm);
+        if (cst != VSK_OK) {   // the shadow index exists only once it is complete
+          dev_free(co->row_norm);
+          delete co;
+          return cst;
+        }
         ix->coarse = co;
-        VSK_TRY(dev_alloc(ctx, (void**)&co->row_norm, (size_t)ix->nlist * sizeof(float)));
-        VSK_TRY(launch_row_norms(ctx, co->rows, co->n, co->dim, 1, co->row_norm));
       }
-      VSK_TRY(tensor_search(ix->coarse, qb, bn, nprobe, nullptr, (float*)pd, (int64_t*)pi));
+      VSK_TRY(tensor_search(ix->coarse, qb, bn, nprobe, nullptr, nullptr, (float*)pd, (int64_t*)pi));
     } else {
       ExactScanArgs c{};
       c.metric = VSK_METRIC_EUCLIDEAN;

@@ -312,7 +312,109 @@ __global__ void __launch_bounds__(128) merge_select_kernel(const float* __restri
   }
 }
 
+// ---- packed (distance, global row) keys: what shards exchange -----------------------------------------------
+// A result entry as one 64-bit word, ordered(distance) << 32 | global row, so that unsigned order is (distance,
+// global row) order - the order an unsharded search returns - whatever shard an entry came from.  A missing entry
+// (id -1) is the all-ones key.  Rows beyond `nq` (padding to whole slices) are filled with missing entries.
+__global__ void pack_keys_kernel(const float* __restrict__ dist, const int64_t* __restrict__ ids, int64_t nq, int64_t rows,
+                                 int k, uint64_t* __restrict__ keys) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows * k) return;
+  uint64_t key = kEmptyKey;
+  if (i < nq * k) {
+    const int64_t id = ids[i];
+    if (id >= 0) key = make_key(dist[i], (uint32_t)id);
+  }
+  keys[i] = key;
+}
+
+__global__ void unpack_keys_kernel(const uint64_t* __restrict__ keys, int64_t count, float* __restrict__ dist,
+                                   int64_t* __restrict__ ids) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= count) return;
+  const uint64_t key = keys[i];
+  dist[i] = key == kEmptyKey ? CUDART_INF_F : ordered_to_float((uint32_t)(key >> 32));
+  ids[i] = key == kEmptyKey ? -1 : (int64_t)(uint32_t)key;
+}
+
+// Merge of g lists of k keys per query ([g][stride_q][k], query q of this launch at row q): the k smallest keys,
+// ascending, to out[q][k].  One CTA per query: the keys stay in registers, a radix select finds the k-th, only the
+// survivors are sorted.
+template <int NT>
+__global__ void __launch_bounds__(NT) merge_keys_kernel(const uint64_t* __restrict__ in, int g, int64_t stride_q, int k,
+                                                        uint64_t* __restrict__ out) {
+  __shared__ __align__(16) uint64_t s[NT * SEL_ITEMS];
+  __shared__ int hist[256];
+  __shared__ int s_valid, s_bin, s_less, s_in_bin, s_out;
+  const int64_t q = blockIdx.x;
+  const int c = g * k;
+  uint64_t key[SEL_ITEMS];
+  int nvalid = 0;
+#pragma unroll
+  for (int i = 0; i < SEL_ITEMS; ++i) {
+    const int idx = threadIdx.x + i * NT;
+    key[i] = kEmptyKey;
+    if (idx < c) {
+      const int sh = idx / k, j = idx - sh * k;
+      key[i] = in[((int64_t)sh * stride_q + q) * k + j];
+    }
+    nvalid += key[i] != kEmptyKey;
+  }
+  if (threadIdx.x == 0) { s_valid = 0; s_out = 0; }
+  __syncthreads();
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) nvalid += __shfl_xor_sync(0xffffffffu, nvalid, o);
+  if ((threadIdx.x & 31) == 0) atomicAdd(&s_valid, nvalid);
+  __syncthreads();
+  const int valid = s_valid;
+  uint64_t pivot = kEmptyKey - 1;
+  // keys are distinct (a global row appears once), so the select resolves all 64 bits and exactly k survive
+  if (valid > k) pivot = block_radix_select(key, k, hist, &s_bin, &s_less, &s_in_bin);
+  const int P = next_pow2(max(min(valid, k), 1));
+  for (int i = threadIdx.x; i < P; i += blockDim.x) s[i] = kEmptyKey;
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < SEL_ITEMS; ++i)
+    if (key[i] <= pivot && key[i] != kEmptyKey) {
+      const int pos = atomicAdd(&s_out, 1);
+      if (pos < P) s[pos] = key[i];
+    }
+  __syncthreads();
+  bitonic_sort(s, P);
+  for (int j = threadIdx.x; j < k; j += blockDim.x) out[q * k + j] = j < P ? s[j] : kEmptyKey;
+}
+
 }  // namespace
+
+int32_t launch_pack_keys(Ctx* ctx, const float* dist, const int64_t* ids, int64_t nq, int64_t rows, int32_t k,
+                         uint64_t* keys) {
+  if (rows <= 0) return VSK_OK;
+  pack_keys_kernel<<<(unsigned)ceil_div(rows * k, 256), 256, 0, ctx->stream>>>(dist, ids, nq, rows, k, keys);
+  ctx->stats.kernel_launches++;
+  VSK_CUDA(ctx, cudaGetLastError());
+  return VSK_OK;
+}
+
+int32_t launch_unpack_keys(Ctx* ctx, const uint64_t* keys, int64_t count, float* dist, int64_t* ids) {
+  if (count <= 0) return VSK_OK;
+  unpack_keys_kernel<<<(unsigned)ceil_div(count, 256), 256, 0, ctx->stream>>>(keys, count, dist, ids);
+  ctx->stats.kernel_launches++;
+  VSK_CUDA(ctx, cudaGetLastError());
+  return VSK_OK;
+}
+
+int32_t launch_merge_keys(Ctx* ctx, const uint64_t* in, int32_t g, int64_t stride_q, int64_t nq, int32_t k, uint64_t* out) {
+  if (nq <= 0) return VSK_OK;
+  if ((int64_t)g * k > kCandCap)
+    return fail(ctx, VSK_ERR_INVALID_BUFFER_SIZE, "merge of %d lists of %d exceeds %d keys", g, k, kCandCap);
+  if (g * k <= 128 * SEL_ITEMS)
+    merge_keys_kernel<128><<<(unsigned)nq, 128, 0, ctx->stream>>>(in, g, stride_q, k, out);
+  else
+    merge_keys_kernel<SEL_THREADS><<<(unsigned)nq, SEL_THREADS, 0, ctx->stream>>>(in, g, stride_q, k, out);
+  ctx->stats.kernel_launches++;
+  VSK_CUDA(ctx, cudaGetLastError());
+  return VSK_OK;
+}
 
 int32_t launch_select(Ctx* ctx, const SelectArgs& a) {
   if (a.nq <= 0) return VSK_OK;

@@ -82,7 +82,9 @@ __global__ void sq8_encode_kernel(const float* __restrict__ x, int64_t total, in
   // 4 elements per thread when the row length allows aligned 16-byte loads
   const int64_t i4 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
   if (i4 >= total) return;
-  if ((dim & 3) == 0 && i4 + 3 < total) {
+  // (a caller's view may start at any 4-byte offset: the wide path also needs both pointers aligned)
+  const bool wide = (dim & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(codes) & 3) == 0;
+  if (wide && i4 + 3 < total) {
     const float4 v = __ldg(reinterpret_cast<const float4*>(x + i4));
     const int d = (int)(i4 % dim);
     const float in[4] = {v.x, v.y, v.z, v.w};
@@ -217,7 +219,7 @@ int32_t sq8_search_dev(Index* ix, const float* q, int64_t nq, int32_t k, float* 
   for (int64_t b = 0; b < nq; b += kBatch) {
     const int64_t bn = std::min(kBatch, nq - b);
     if (tensor) {
-      VSK_TRY(tensor_search(ix, q + b * ix->dim, bn, k, nullptr, out_dist + b * k, out_ids + b * k));
+      VSK_TRY(tensor_search(ix, q + b * ix->dim, bn, k, nullptr, nullptr, out_dist + b * k, out_ids + b * k));
       continue;
     }
     ExactScanArgs a{};

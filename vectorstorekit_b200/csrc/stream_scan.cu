@@ -245,9 +245,8 @@ int32_t launch_stream_metric(Ctx* ctx, const ExactScanArgs& a, bool vec) {
 
 }  // namespace
 
-bool stream_scan_applies(const ExactScanArgs& a) {
-  static const int64_t off = schedule_tuning("VSK_NO_STREAM_SCAN", 0);
-  if (off) return false;
+bool stream_scan_applies(const Ctx* ctx, const ExactScanArgs& a) {
+  if (!ctx->tuning.stream_scan) return false;
   if (a.x_codes != nullptr || a.x == nullptr) return false;                 // fp32 rows only
   if (a.mode != SCAN_DENSE && a.mode != SCAN_THRESHOLD) return false;       // candidate modes only
   // the queries stay in shared memory: the staged rows (1, 2, 4 or 8 of them) plus the kernel's few static words

@@ -42,18 +42,13 @@ constexpr int TM = 128;        // queries per tile (UMMA M)
 constexpr int TN = 256;        // rows per tile (UMMA N)
 constexpr int TK = 64;         // fp16 elements per k-block (128 bytes: one swizzle atom)
 constexpr int A_BYTES = TM * TK * 2;   // 16 KB: 128 query rows x 64 fp16
-constexpr int RING_BYTES = 192 * 1024; // operand ring: 4 stages of 48 KB (one CTA per tile) or 6 of 32 KB (CTA pair)
-constexpr int MAX_STAGES = 6;
-// CTAS = 1: a CTA computes a 128-query x 256-row tile from a 16 KB query box and a 32 KB row box per stage.
-// CTAS = 2: a pair of CTAs (a cluster of two SMs) computes a 256-query x 256-row tile with one
-//           tcgen05.mma.cta_group::2; each CTA stages its 128 queries and HALF of the rows (16 KB + 16 KB),
-//           so every CTA moves a third fewer operand bytes from L2 per flop and the ring holds six stages.
-template <int CTAS> struct Geo {
-  static constexpr int B_BYTES = (TN / CTAS) * TK * 2;
-  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = RING_BYTES / STAGE_BYTES;
-  static constexpr int TX_BYTES = STAGE_BYTES * CTAS;   // bytes that complete a stage's full barrier
-};
+constexpr int B_BYTES = TN * TK * 2;   // 32 KB: 256 database rows x 64 fp16
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int STAGES = 4;              // operand ring: 4 stages of 48 KB
+constexpr int RING_BYTES = STAGES * STAGE_BYTES;
+// (A variant on pairs of CTAs - tcgen05.mma.cta_group::2, a 256-query tile, each CTA staging half of the rows -
+// was built and measured 2 - 3 % slower on the headline workload: the kernel is bound by the power cap, not by
+// operand traffic from L2.  It was removed.)
 // Warp 0 is the TMA producer, warp 1 the MMA issuer, then EW epilogue warps: EW / 4 per tensor-memory lane quarter,
 // each taking one of EW / 4 equal parts of the tile's columns.  EW = 8 for long contractions (the epilogue hides
 // behind the MMAs, and fewer warps cost less issue and power); EW = 16 for short ones (d <= 256), where a tile's
@@ -75,8 +70,8 @@ struct TcSmemT {
   float beta[2][EW][Epi<EW>::COLS];   // per accumulator buffer and epilogue warp: its columns' per-row terms
   uint32_t masks[EW * 32][Epi<EW>::GROUPS + 1];  // per epilogue thread: pass bits of its values (padded row)
   float hitval[EW * 32][Epi<EW>::GROUPS + 1];    // ... and per group the value of its last hit
-  uint64_t full[MAX_STAGES];
-  uint64_t empty[MAX_STAGES];
+  uint64_t full[STAGES];
+  uint64_t empty[STAGES];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
   uint64_t drain;
@@ -107,6 +102,9 @@ struct TcArgs {
   int64_t num_tiles;
   const uint32_t* pair_info;
   const float* pair_thr;      // [pairs] coarse threshold of the pair's query for this launch
+  // Filter (HAS_MASK kernels): operand row r may be appended for query q iff (row_masks[r] & q_masks[q]) != 0.
+  const uint64_t* row_masks;  // [rows of the row operand]
+  const uint64_t* q_masks;    // [nq] by list position
 };
 
 // ---- PTX wrappers --------------------------------------------------------------------------
@@ -152,42 +150,6 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, u
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
           smem_u32(dst)),
       "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
-      : "memory");
-}
-
-// ---- helpers for a pair of CTAs (cluster of two) ---------------------------------------------
-// shared::cluster address of the same shared-memory location in CTA `rank` of the cluster
-__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
-  return r;
-}
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-__device__ __forceinline__ void cluster_sync() {
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// TMA load issued by either CTA of the pair; the bytes are counted on the barrier at `bar_cluster_addr`
-// (the leader's full barrier).  No multicast: each CTA fetches only its own boxes.
-__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int32_t c0, int32_t c1) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
-          smem_u32(dst)),
-      "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
-      : "memory");
-}
-// completion of all MMAs issued so far by this thread -> one arrival on the barrier at a shared::cluster address
-__device__ __forceinline__ void tc_commit_pair(uint32_t bar_cluster_addr) {
-  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr) : "memory");
-}
-__device__ __forceinline__ void tc_mma_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
-      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 
@@ -240,25 +202,18 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
 
 // Instruction descriptor: fp32 accumulate, fp16 A and B, both K-major, N = 256, M = 128.
 constexpr uint32_t kIdesc = (1u << 4) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(TM >> 4) << 24);
-// the pair's instruction: M = 256 (128 rows in each CTA's tensor memory), N = 256
-constexpr uint32_t kIdescPair = (1u << 4) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)((2 * TM) >> 4) << 24);
 
-template <int MODE, bool HAS_BETA, int CTAS, int EW>
+template <int MODE, bool HAS_BETA, bool HAS_MASK, int EW>
 __global__ void __launch_bounds__(Epi<EW>::THREADS, 1)
 tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_x, TcArgs a) {
-  using G = Geo<CTAS>;
-  constexpr int STAGES = G::STAGES;
-  constexpr int STAGE_BYTES = G::STAGE_BYTES;
   extern __shared__ uint8_t smem_raw[];
   using TcSmem = TcSmemT<EW>;
   constexpr int EPI_WARPS = EW, EPI_COLS = Epi<EW>::COLS, EPI_GROUPS = Epi<EW>::GROUPS, EPI_PARTS = Epi<EW>::PARTS;
   TcSmem* sm = reinterpret_cast<TcSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // a pair shares tiles: `unit` counts single CTAs (CTAS = 1) or pairs (CTAS = 2); `rank` is the CTA's place in its pair
-  const uint32_t rank = CTAS == 2 ? (blockIdx.x & 1u) : 0u;
-  const int64_t unit = CTAS == 2 ? (blockIdx.x >> 1) : blockIdx.x;
-  const int64_t units = CTAS == 2 ? (gridDim.x >> 1) : gridDim.x;
-  constexpr int QT = TM * CTAS;  // queries per tile
+  const int64_t unit = blockIdx.x;
+  const int64_t units = gridDim.x;
+  constexpr int QT = TM;  // queries per tile
 
   const int64_t qtiles = (a.nq + QT - 1) / QT;
   const int64_t ntiles = (a.row_end - a.row_begin + TN - 1) / TN;
@@ -294,28 +249,20 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&sm->tmem_full[b], 1);
-      mbar_init(&sm->tmem_empty[b], EPI_WARPS * CTAS);   // the leader's copy collects both CTAs' epilogue warps
+      mbar_init(&sm->tmem_empty[b], EPI_WARPS);
     }
     mbar_init(&sm->drain, 1);
     sm->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    if (CTAS == 2) {
-      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm->tmem_base)),
-                   "r"(TMEM_COLS)
-                   : "memory");
-      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-    } else {
-      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm->tmem_base)),
-                   "r"(TMEM_COLS)
-                   : "memory");
-      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm->tmem_base)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
   __syncthreads();
-  if (CTAS == 2) cluster_sync();   // both CTAs' barriers exist before anything arrives on them remotely
   tc_fence_after();
   const uint32_t tmem_base = sm->tmem_base;
 
@@ -336,32 +283,21 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         if (!tile_at(i, qt, nt)) break;
         const int4 entry = entry_next;
         if (a.tiles && nt + units < a.num_tiles) entry_next = __ldg(&a.tiles[nt + units]);
-        const int32_t qrow = a.tiles ? entry.x : (int32_t)(qt * QT + rank * TM);   // this CTA's 128 queries
-        const int32_t xrow = a.tiles ? entry.y
-                                     : (int32_t)(a.row_begin + nt * TN + rank * (TN / CTAS)); // its share of the 256 rows
+        const int32_t qrow = a.tiles ? entry.x : (int32_t)(qt * QT);
+        const int32_t xrow = a.tiles ? entry.y : (int32_t)(a.row_begin + nt * TN);
         for (int kb = 0; kb < a.kblocks; ++kb) {
           if (!mbar_wait(&sm->empty[s], ph ^ 1, &sm->abort_flag, a.err, 1)) { ok = false; break; }
           uint8_t* st = sm->ring + s * STAGE_BYTES;
-          if (CTAS == 2) {
-            // the leader's full barrier counts the bytes of both CTAs
-            if (rank == 0) mbar_expect_tx(&sm->full[s], G::TX_BYTES);
-            const uint32_t bar = map_to_cta(smem_u32(&sm->full[s]), 0);
-            tma_load_2d_pair(st, &map_q, bar, kb * TK, qrow);
-            tma_load_2d_pair(st + A_BYTES, &map_x, bar, kb * TK, xrow);
-          } else {
-            mbar_expect_tx(&sm->full[s], G::TX_BYTES);
-            tma_load_2d(st, &map_q, &sm->full[s], kb * TK, qrow);
-            tma_load_2d(st + A_BYTES, &map_x, &sm->full[s], kb * TK, xrow);
-          }
+          mbar_expect_tx(&sm->full[s], STAGE_BYTES);
+          tma_load_2d(st, &map_q, &sm->full[s], kb * TK, qrow);
+          tma_load_2d(st + A_BYTES, &map_x, &sm->full[s], kb * TK, xrow);
           issued |= 1u << s;
           issued_ph = (issued_ph & ~(1u << s)) | (ph << s);
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
       }
-      // copies still in flight must land before the CTA's shared memory is released (the second CTA of a pair
-      // cannot poll the leader's barrier: the cluster barrier at the end covers it, since the leader consumes
-      // every stage it was told to expect)
-      for (int i = 0; i < STAGES && rank == 0; ++i)
+      // copies still in flight must land before the CTA's shared memory is released
+      for (int i = 0; i < STAGES; ++i)
         if (issued & (1u << i)) {
           for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
             if (mbar_try_wait(&sm->full[i], (issued_ph >> i) & 1)) break;
@@ -370,8 +306,8 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         }
     }
   } else if (warp == 1) {
-    // ---------------- MMA issuer (the leader of a pair issues for both CTAs) ----------------
-    if (lane == 0 && rank == 0) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
       int s = 0;
       uint32_t ph = 0;
       int64_t local = 0;
@@ -392,30 +328,15 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 #pragma unroll
           for (int k4 = 0; k4 < TK / 16; ++k4) {
             // 16 fp16 = 32 bytes further along K inside the swizzle atom: +2 in 16-byte units
-            if (CTAS == 2) tc_mma_pair(tmem_d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), kIdescPair, (kb | k4) ? 1u : 0u);
-            else tc_mma(tmem_d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), kIdesc, (kb | k4) ? 1u : 0u);
+            tc_mma(tmem_d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), kIdesc, (kb | k4) ? 1u : 0u);
           }
-          // the stage is free, in both CTAs, once these MMAs have read it
-          if (CTAS == 2) {
-            tc_commit_pair(map_to_cta(smem_u32(&sm->empty[s]), 0));
-            tc_commit_pair(map_to_cta(smem_u32(&sm->empty[s]), 1));
-          } else {
-            tc_commit(&sm->empty[s]);
-          }
+          tc_commit(&sm->empty[s]);   // the stage is free once these MMAs have read it
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
-        if (ok) {
-          if (CTAS == 2) {
-            tc_commit_pair(map_to_cta(smem_u32(&sm->tmem_full[acc]), 0));
-            tc_commit_pair(map_to_cta(smem_u32(&sm->tmem_full[acc]), 1));
-          } else {
-            tc_commit(&sm->tmem_full[acc]);
-          }
-        }
+        if (ok) tc_commit(&sm->tmem_full[acc]);
       }
       // all issued MMAs must retire before tensor memory is freed
-      if (CTAS == 2) tc_commit_pair(map_to_cta(smem_u32(&sm->drain), 0));
-      else tc_commit(&sm->drain);
+      tc_commit(&sm->drain);
       for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
         if (mbar_try_wait(&sm->drain, 0)) break;
         __nanosleep(64);
@@ -463,7 +384,7 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         ahead = pair_at(entry_next);
         entry_next = entry_at(local + 2);
       }
-      int64_t q = qt * QT + rank * TM + et;
+      int64_t q = qt * QT + et;
       const bool owned = a.row_tile_fastest != 0;
       if (owned && nt == 0) { run_cnt = 0; run_bv = CUDART_INF_F; run_bn = 0; }
       int64_t n0 = a.row_begin + nt * TN;
@@ -502,6 +423,8 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       }
       float thr = CUDART_INF_F;
       if (MODE == SCAN_THRESHOLD && qok) thr = a.tiles ? thr_tile : a.cand.thr[q];
+      uint64_t qm = 0ull;   // this query's filter mask: a row is eligible iff (row mask & qm) != 0
+      if (HAS_MASK && qok) qm = __ldg(a.q_masks + q);
       // every lane of the warp must take part in the wait result
       bool got = mbar_wait(&sm->tmem_full[acc], aph, &sm->abort_flag, a.err, 4);
       got = __all_sync(0xffffffffu, got);
@@ -522,11 +445,16 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           for (int j = 0; j < 32; j += 2) {
             const float v0 = HAS_BETA ? fmaf(v[j], alpha, sm->beta[acc][ew][(c - c0) * 32 + j]) : v[j] * alpha;
             const float v1 = HAS_BETA ? fmaf(v[j + 1], alpha, sm->beta[acc][ew][(c - c0) * 32 + j + 1]) : v[j + 1] * alpha;
+            uint64_t k0 = make_key(v0, (uint32_t)(nc + j)), k1 = make_key(v1, (uint32_t)(nc + j + 1));
+            if (HAS_MASK) {
+              // the same row mask for every lane (a broadcast load); an ineligible row leaves an empty slot
+              if (nc + j < a.row_end && (__ldg(a.row_masks + nc + j) & qm) == 0ull) k0 = kEmptyKey;
+              if (nc + j + 1 < a.row_end && (__ldg(a.row_masks + nc + j + 1) & qm) == 0ull) k1 = kEmptyKey;
+            }
             if (nc + j + 1 < a.row_end)
-              *reinterpret_cast<ulonglong2*>(dst + j) =
-                  make_ulonglong2(make_key(v0, (uint32_t)(nc + j)), make_key(v1, (uint32_t)(nc + j + 1)));
+              *reinterpret_cast<ulonglong2*>(dst + j) = make_ulonglong2(k0, k1);
             else if (nc + j < a.row_end)
-              dst[j] = make_key(v0, (uint32_t)(nc + j));
+              dst[j] = k0;
           }
         }
       } else if (MODE == SCAN_ARGMIN) {
@@ -605,6 +533,16 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             hv = hit ? val : hv;
           }
           bits = qok ? (bits & colmask) : 0u;
+          if (HAS_MASK) {
+            // Only hits are tested against the filter (a few per query and tile once the threshold is tight): the
+            // row masks of a tile are 2 KB and stay in L1 for the CTA's 128 queries.
+            uint32_t b = bits;
+            while (b) {
+              const int j = __ffs((int)b) - 1;
+              b &= b - 1u;
+              if ((__ldg(a.row_masks + n0 + c * 32 + j) & qm) == 0ull) bits &= ~(1u << j);
+            }
+          }
           m[c - c0] = bits;
           mv[c - c0] = hv;
           cnt += __popc(bits);
@@ -621,7 +559,7 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           const uint32_t bits = m[c - c0];
           const uint32_t colbits = __reduce_or_sync(0xffffffffu, bits);   // columns in which any query has a hit
           if (colbits == 0u) continue;
-          if (!__any_sync(0xffffffffu, (bits & (bits - 1u)) != 0u) && n0 + c * 32 + 32 <= row_end) {
+          if (!HAS_MASK && !__any_sync(0xffffffffu, (bits & (bits - 1u)) != 0u) && n0 + c * 32 + 32 <= row_end) {
             // no query has more than one hit in this (whole) group: its value was kept by pass 1
             const uint32_t ok1 = (bits != 0u && base < cap_here) ? 1u : 0u;
             const uint64_t key1 = make_key(mv[c - c0], (uint32_t)(n0 + c * 32 + (__ffs((int)bits) - 1)));
@@ -674,21 +612,16 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) {
-        if (CTAS == 2) mbar_arrive_cluster(map_to_cta(smem_u32(&sm->tmem_empty[acc]), 0));
-        else mbar_arrive(&sm->tmem_empty[acc]);
-      }
+      if (lane == 0) mbar_arrive(&sm->tmem_empty[acc]);
     }
   }
 
   // ---------------- teardown ----------------
   tc_fence_before();
   __syncthreads();
-  if (CTAS == 2) cluster_sync();   // neither CTA leaves (or frees tensor memory) while its partner may still reach it
   if (warp == 1) {
     tc_fence_after();
-    if (CTAS == 2) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
-    else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
 }
 
@@ -1084,8 +1017,7 @@ int32_t tensor_prepare(Index* ix) {
   ix->dim16 = (int32_t)(ceil_div(ix->dim, TK) * TK);
   // Folding the per-row term into the operands (FoldArgs) pays where the epilogue, not the MMAs, sets the pace
   // (up to four K blocks), and is free where the padding already has room for it.
-  static const int64_t fold_mode = schedule_tuning("VSK_FOLD", 1);
-  ix->fold16 = fold_mode != 0 && ix->kind != INDEX_FLAT_I8 && ix->metric == VSK_METRIC_EUCLIDEAN &&
+  ix->fold16 = ctx->tuning.fold_row_term != 0 && ix->kind != INDEX_FLAT_I8 && ix->metric == VSK_METRIC_EUCLIDEAN &&
                (ix->dim16 / TK <= 4 || ix->dim16 - ix->dim >= kFoldCols);
   if (ix->fold16 && ix->dim16 - ix->dim < kFoldCols) ix->dim16 += TK;
   VSK_TRY(dev_alloc(ctx, (void**)&ix->rows16, (size_t)ix->n * ix->dim16 * sizeof(__half)));
@@ -1159,45 +1091,32 @@ int32_t tensor_prepare(Index* ix) {
   return VSK_OK;
 }
 
-// Launches the scan over tiles.  pair = true: clusters of two CTAs (tcgen05 cta_group::2); `mx` must then be a
-// tensor map with 128-row boxes (each CTA stages half of a 256-row tile).
+// Launches the scan over tiles (persistent: one CTA per SM, or per tile when there are fewer tiles).
 template <int MODE, int EW>
-int32_t launch_tc_ew(Ctx* ctx, const CUtensorMap& mq, const CUtensorMap& mx, const TcArgs& a, bool has_beta, bool pair) {
+int32_t launch_tc_ew(Ctx* ctx, const CUtensorMap& mq, const CUtensorMap& mx, const TcArgs& a, bool has_beta) {
   static bool attr_done[2][2] = {};
-  void (*kern)(CUtensorMap, CUtensorMap, TcArgs) =
-      pair ? (has_beta ? tc_scan_kernel<MODE, true, 2, EW> : tc_scan_kernel<MODE, false, 2, EW>)
-           : (has_beta ? tc_scan_kernel<MODE, true, 1, EW> : tc_scan_kernel<MODE, false, 1, EW>);
-  constexpr size_t smem = tc_smem_bytes<EW>();
-  if (!attr_done[has_beta][pair]) {
-    VSK_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    attr_done[has_beta][pair] = true;
+  const bool has_mask = MODE != SCAN_ARGMIN && a.row_masks != nullptr && a.q_masks != nullptr;
+  void (*kern)(CUtensorMap, CUtensorMap, TcArgs);
+  if constexpr (MODE == SCAN_ARGMIN) {
+    kern = has_beta ? tc_scan_kernel<MODE, true, false, EW> : tc_scan_kernel<MODE, false, false, EW>;
+  } else {
+    kern = has_mask ? (has_beta ? tc_scan_kernel<MODE, true, true, EW> : tc_scan_kernel<MODE, false, true, EW>)
+                    : (has_beta ? tc_scan_kernel<MODE, true, false, EW> : tc_scan_kernel<MODE, false, false, EW>);
   }
-  const int per_tile = pair ? 2 * TM : TM;
-  const int64_t tiles = a.tiles ? a.num_tiles : ceil_div(a.nq, per_tile) * ceil_div(a.row_end - a.row_begin, TN);
+  constexpr size_t smem = tc_smem_bytes<EW>();
+  if (!attr_done[has_beta][has_mask]) {
+    VSK_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    attr_done[has_beta][has_mask] = true;
+  }
+  const int64_t tiles = a.tiles ? a.num_tiles : ceil_div(a.nq, TM) * ceil_div(a.row_end - a.row_begin, TN);
   if (tiles <= 0) return VSK_OK;
   const int sms = ctx->prop.multiProcessorCount;
-  unsigned grid = pair ? 2u * (unsigned)std::min<int64_t>(tiles, sms / 2) : (unsigned)std::min<int64_t>(tiles, sms);
+  const unsigned grid = (unsigned)std::min<int64_t>(tiles, sms);
   prof_begin(ctx);
-  if (pair) {
-    cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(Epi<EW>::THREADS);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = ctx->stream;
-    cudaLaunchAttribute at[1];
-    at[0].id = cudaLaunchAttributeClusterDimension;
-    at[0].val.clusterDim.x = 2;
-    at[0].val.clusterDim.y = 1;
-    at[0].val.clusterDim.z = 1;
-    cfg.attrs = at;
-    cfg.numAttrs = 1;
-    VSK_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, mq, mx, a));
-  } else {
-    kern<<<grid, Epi<EW>::THREADS, smem, ctx->stream>>>(mq, mx, a);
-  }
+  kern<<<grid, Epi<EW>::THREADS, smem, ctx->stream>>>(mq, mx, a);
   prof_end(ctx);
   ctx->stats.kernel_launches++;
-  ctx->stats.tensor_tiles += tiles * (pair ? 2 : 1);
+  ctx->stats.tensor_tiles += tiles;
   VSK_CUDA(ctx, cudaGetLastError());
   return VSK_OK;
 }
@@ -1206,9 +1125,9 @@ int32_t launch_tc_ew(Ctx* ctx, const CUtensorMap& mq, const CUtensorMap& mx, con
 inline int tc_epilogue_warps(int kblocks) { return kblocks <= 4 ? 16 : 8; }
 
 template <int MODE>
-int32_t launch_tc(Ctx* ctx, const CUtensorMap& mq, const CUtensorMap& mx, const TcArgs& a, bool has_beta, bool pair) {
-  if (tc_epilogue_warps(a.kblocks) == 16) return launch_tc_ew<MODE, 16>(ctx, mq, mx, a, has_beta, pair);
-  return launch_tc_ew<MODE, 8>(ctx, mq, mx, a, has_beta, pair);
+int32_t launch_tc(Ctx* ctx, const CUtensorMap& mq, const CUtensorMap& mx, const TcArgs& a, bool has_beta) {
+  if (tc_epilogue_warps(a.kblocks) == 16) return launch_tc_ew<MODE, 16>(ctx, mq, mx, a, has_beta);
+  return launch_tc_ew<MODE, 8>(ctx, mq, mx, a, has_beta);
 }
 
 // ---- k-means assignment on the tensor cores ----------------------------------------------------
@@ -1332,22 +1251,23 @@ __global__ void scatter_best_kernel(const unsigned long long* __restrict__ best,
 }  // namespace
 
 void tensor_invalidate(Index* ix) { ix->n16 = -1; }
+int32_t tensor_prepare_index(Index* ix) { return tensor_prepare(ix); }
 
-// The search in two halves.  `begin` runs the scan and its compactions; `finish` certifies, re-scores and orders.
-// A plain search calls them back to back.  A shard of a row-sharded search passes `bound_out` (and the number of
-// shards): the last compaction is then left to `finish`, and bound_out[q] gets a value that this shard's
-// ceil(k / shards) best rows do not exceed; the host takes the maximum over the shards (at least k rows overall lie
-// below it) and hands it to `finish`, which keeps only rows that can still reach the overall top-k.
-int32_t tensor_search_begin(Index* ix, const float* q, int64_t nq, int32_t k, const float* qnorm, int32_t shards,
-                            float* bound_out) {
+// ---- query operands of a flat search ------------------------------------------------------------------
+// fp16 operand rows of the queries, their error bound eps[q], the output coefficient alpha, and the small words a
+// search needs (device error word, re-scored row counter), all in the current lane's scratch.
+struct QueryOperands {
+  __half* q16 = nullptr;
+  float* eps = nullptr;
+  float* alpha = nullptr;
+  int32_t* err = nullptr;
+  unsigned long long* rr_total = nullptr;
+};
+
+int32_t prepare_query_operands(Index* ix, const float* q, int64_t nq, QueryOperands* out) {
   Ctx* ctx = ix->ctx;
-  ctx->pending = ShardPending{};
-  VSK_TRY(tensor_prepare(ix));
   const int metric = ix->metric;
   const int dim = ix->dim, dim16 = ix->dim16;
-  const int32_t keep = std::min<int32_t>(kCandCap / 2, k + std::max(8, k / 8));
-
-  // ---- query operands, bound, alpha ----
   void* p;
   VSK_TRY(scratch(ctx, SLOT_Q16, (size_t)nq * dim16 * sizeof(__half), &p));
   __half* q16 = (__half*)p;
@@ -1412,35 +1332,67 @@ int32_t tensor_search_begin(Index* ix, const float* q, int64_t nq, int32_t k, co
   }
   ctx->stats.kernel_launches++;
   VSK_CUDA(ctx, cudaGetLastError());
+  out->q16 = q16;
+  out->eps = eps;
+  out->alpha = alpha;
+  out->err = err;
+  out->rr_total = rr_total;
+  return VSK_OK;
+}
 
-  // CTA pairs (cta_group::2) when there are at least two query tiles to pair up
-  static const int64_t pair_mode = schedule_tuning("VSK_TC_PAIR", 0);
-  const bool pair = pair_mode != 0 && nq > TM;
+int32_t cand_lists(Ctx* ctx, int64_t nq, CandLists* cand) {
+  void* p;
+  VSK_TRY(scratch(ctx, SLOT_CAND_KEYS, (size_t)nq * kCandCap * sizeof(uint64_t), &p));
+  cand->keys = (uint64_t*)p;
+  VSK_TRY(scratch(ctx, SLOT_CAND_COUNT, (size_t)nq * 4, &p));
+  cand->count = (int32_t*)p;
+  VSK_TRY(scratch(ctx, SLOT_CAND_THR, (size_t)nq * 4, &p));
+  cand->thr = (float*)p;
+  VSK_TRY(scratch(ctx, SLOT_CAND_FLAGS, (size_t)nq * 4, &p));
+  cand->flags = (int32_t*)p;
+  cand->nq = nq;
+  return VSK_OK;
+}
+
+// The search in two halves.  `begin` runs the scan and its compactions; `finish` certifies, re-scores and orders.
+// A plain search calls them back to back.  A shard of a row-sharded search passes `bound_out` (and the number of
+// shards): the last compaction is then left to `finish`, and bound_out[q] gets a value that this shard's
+// ceil(k / shards) best rows do not exceed; the host takes the maximum over the shards (at least k rows overall lie
+// below it) and hands it to `finish`, which keeps only rows that can still reach the overall top-k.
+// qmasks (or null): per-query filter masks; rows are then filtered in the contraction's epilogue.
+int32_t tensor_search_begin(Index* ix, const float* q, int64_t nq, int32_t k, const float* qnorm, const uint64_t* qmasks,
+                            int32_t shards, float* bound_out) {
+  Ctx* ctx = ix->ctx;
+  ctx->pending[ctx->lane] = ShardPending{};
+  VSK_TRY(tensor_prepare(ix));
+  const int metric = ix->metric;
+  const int dim16 = ix->dim16;
+  const int32_t keep = std::min<int32_t>(kCandCap / 2, k + std::max(8, k / 8));
+  QueryOperands qo;
+  VSK_TRY(prepare_query_operands(ix, q, nq, &qo));
+  const bool fold = ix->fold16;
+
   CUtensorMap mq, mx;
-  VSK_TRY(make_map(ctx, q16, nq, dim16, TM, &mq));
-  VSK_TRY(make_map(ctx, ix->rows16, ix->n, dim16, pair ? TN / 2 : TN, &mx));
+  VSK_TRY(make_map(ctx, qo.q16, nq, dim16, TM, &mq));
+  VSK_TRY(make_map(ctx, ix->rows16, ix->n, dim16, TN, &mx));
 
   // ---- candidate lists and the chunk schedule ----
   CandLists cand;
-  VSK_TRY(scratch(ctx, SLOT_CAND_KEYS, (size_t)nq * kCandCap * sizeof(uint64_t), &p));
-  cand.keys = (uint64_t*)p;
-  VSK_TRY(scratch(ctx, SLOT_CAND_COUNT, (size_t)nq * 4, &p));
-  cand.count = (int32_t*)p;
-  VSK_TRY(scratch(ctx, SLOT_CAND_THR, (size_t)nq * 4, &p));
-  cand.thr = (float*)p;
-  VSK_TRY(scratch(ctx, SLOT_CAND_FLAGS, (size_t)nq * 4, &p));
-  cand.flags = (int32_t*)p;
-  cand.nq = nq;
+  VSK_TRY(cand_lists(ctx, nq, &cand));
   VSK_TRY(launch_init_cand(ctx, cand, nq));
 
   TcArgs a{};
   a.nq = nq;
   a.kblocks = dim16 / TK;
-  a.alpha = alpha;
+  a.alpha = qo.alpha;
   a.beta = (metric == VSK_METRIC_EUCLIDEAN && !fold) ? ix->row_aux : nullptr;
   a.cand = cand;
   a.cap = kCandCap;
-  a.err = err;
+  a.err = qo.err;
+  if (qmasks && ix->has_masks) {
+    a.row_masks = ix->masks;
+    a.q_masks = qmasks;
+  }
   const bool has_beta = a.beta != nullptr;
   SelectArgs sel{};
   sel.cand = cand;
@@ -1448,11 +1400,11 @@ int32_t tensor_search_begin(Index* ix, const float* q, int64_t nq, int32_t k, co
   sel.keep = keep;
   const int64_t n = ix->n;
   const int64_t room = kCandCap - keep;
-  int64_t seen = std::min<int64_t>(n, schedule_dense_rows(keep));
+  int64_t seen = std::min<int64_t>(n, schedule_dense_rows(ctx, keep));
   a.mode = SCAN_DENSE;
   a.row_begin = 0;
   a.row_end = seen;
-  VSK_TRY(launch_tc<SCAN_DENSE>(ctx, mq, mx, a, has_beta, pair));
+  VSK_TRY(launch_tc<SCAN_DENSE>(ctx, mq, mx, a, has_beta));
   sel.dense_count = (int32_t)seen;
   sel.max_count = (int32_t)seen;
   sel.k = k;
@@ -1460,35 +1412,35 @@ int32_t tensor_search_begin(Index* ix, const float* q, int64_t nq, int32_t k, co
   // only measures its bound there and leaves that compaction to the second half
   auto last_select = [&]() {
     if (bound_out == nullptr) {
-      sel.cert_eps = eps;
+      sel.cert_eps = qo.eps;
     } else {
       sel.bound_out = bound_out;
       sel.bound_rank = (k + std::max(1, shards) - 1) / std::max(1, shards);
-      sel.bound_eps = eps;
+      sel.bound_eps = qo.eps;
     }
   };
   if (seen == n) last_select();
   VSK_TRY(launch_select(ctx, sel));
   sel.dense_count = -1;
   a.mode = SCAN_THRESHOLD;
+  const int64_t growth = std::max(1, ctx->tuning.chunk_growth);
   while (seen < n) {
     // schedule_chunk bounds the chunk so that a list cannot plausibly overflow; below that bound chunks
     // grow geometrically (each no larger than three times the rows seen so far), which keeps the share of
     // rows scanned under a loose threshold small: the epilogue's append path costs far more than its filter.
     int64_t chunk = schedule_chunk(seen, keep, 0);
-    static const int64_t growth = schedule_tuning("VSK_GROWTH", 3);
     chunk = std::min<int64_t>(chunk, std::max<int64_t>(growth >= 100 ? room : 1024, growth * seen));
     chunk = std::max<int64_t>(TN, chunk / TN * TN);   // whole row tiles
     chunk = std::min(chunk, n - seen);
     a.row_begin = seen;
     a.row_end = seen + chunk;
-    VSK_TRY(launch_tc<SCAN_THRESHOLD>(ctx, mq, mx, a, has_beta, pair));
+    VSK_TRY(launch_tc<SCAN_THRESHOLD>(ctx, mq, mx, a, has_beta));
     sel.max_count = schedule_max_count(seen, chunk, keep);
     seen += chunk;
     if (seen == n) last_select();
     VSK_TRY(launch_select(ctx, sel));
   }
-  ShardPending& pd = ctx->pending;
+  ShardPending& pd = ctx->pending[ctx->lane];
   pd.active = true;
   pd.tensor = true;
   pd.ix = ix;
@@ -1496,29 +1448,29 @@ int32_t tensor_search_begin(Index* ix, const float* q, int64_t nq, int32_t k, co
   pd.nq = nq;
   pd.k = k;
   pd.qnorm = qnorm;
+  pd.qmasks = a.q_masks;
   pd.cand = cand;
-  pd.eps = eps;
-  pd.err = err;
-  pd.rr_total = rr_total;
+  pd.eps = qo.eps;
+  pd.err = qo.err;
+  pd.rr_total = qo.rr_total;
   pd.keep = keep;
   pd.max_count = sel.max_count;
   pd.need_cert = bound_out != nullptr;
   return VSK_OK;
 }
 
-int32_t tensor_search_finish(Index* ix, const float* ext_bound, float* out_dist, int64_t* out_ids) {
+// Second half, part one: everything that can be enqueued without looking at results - the certifying compaction
+// (a shard's), the exact re-scoring, the final order, and the copy of the flag words to pinned host memory.
+int32_t tensor_search_finish_issue(Index* ix, const float* ext_bound, float* out_dist, int64_t* out_ids) {
   Ctx* ctx = ix->ctx;
-  const ShardPending pd = ctx->pending;
-  ctx->pending = ShardPending{};
-  if (!pd.active || !pd.tensor || pd.ix != ix)
+  ShardPending& pd = ctx->pending[ctx->lane];
+  if (!pd.active || !pd.tensor || pd.ix != ix || pd.issued)
     return fail(ctx, VSK_ERR_INVALID_INPUT, "no search is waiting for its second half on this index");
   const float* q = pd.q;
   const float* qnorm = pd.qnorm;
   const int64_t nq = pd.nq;
   const int32_t k = pd.k, keep = pd.keep;
   const CandLists cand = pd.cand;
-  int32_t* err = pd.err;
-  unsigned long long* rr_total = pd.rr_total;
   const int metric = ix->metric;
   const int dim = ix->dim;
   const bool i8 = ix->kind == INDEX_FLAT_I8;
@@ -1535,21 +1487,21 @@ int32_t tensor_search_finish(Index* ix, const float* ext_bound, float* out_dist,
     VSK_TRY(launch_select(ctx, sel));
   }
 
-  // ---- certificate + exact rerank + final order ----
+  // ---- exact rerank + final order ----
   const size_t qsm = (size_t)dim * sizeof(float);
   if (qsm > 200 * 1024) return fail(ctx, VSK_ERR_INVALID_BUFFER_SIZE, "dimension %d is too large for the rerank kernel", dim);
 #define VSK_RERANK(M_)                                                                                          \
   do {                                                                                                          \
     if (qsm > 48 * 1024)                                                                                        \
       VSK_CUDA(ctx, cudaFuncSetAttribute(rerank_kernel<M_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)qsm)); \
-    rerank_kernel<M_><<<(unsigned)nq, 256, qsm, ctx->stream>>>(q, ix->rows, dim, qnorm, ix->row_norm, cand, rr_total); \
+    rerank_kernel<M_><<<(unsigned)nq, 256, qsm, ctx->stream>>>(q, ix->rows, dim, qnorm, ix->row_norm, cand, pd.rr_total); \
   } while (0)
   if (i8) {
     if (qsm > 48 * 1024) return fail(ctx, VSK_ERR_INVALID_BUFFER_SIZE, "dimension %d is too large for the int8 rerank kernel", dim);
     if (metric == VSK_METRIC_EUCLIDEAN)
-      rerank_i8_kernel<VSK_METRIC_EUCLIDEAN><<<(unsigned)nq, 256, qsm, ctx->stream>>>(q, ix->codes, dim, ix->sq_scale, ix->sq_offset, cand, rr_total);
+      rerank_i8_kernel<VSK_METRIC_EUCLIDEAN><<<(unsigned)nq, 256, qsm, ctx->stream>>>(q, ix->codes, dim, ix->sq_scale, ix->sq_offset, cand, pd.rr_total);
     else
-      rerank_i8_kernel<VSK_METRIC_DOT_PRODUCT><<<(unsigned)nq, 256, qsm, ctx->stream>>>(q, ix->codes, dim, ix->sq_scale, ix->sq_offset, cand, rr_total);
+      rerank_i8_kernel<VSK_METRIC_DOT_PRODUCT><<<(unsigned)nq, 256, qsm, ctx->stream>>>(q, ix->codes, dim, ix->sq_scale, ix->sq_offset, cand, pd.rr_total);
   } else
   switch (metric) {
     case VSK_METRIC_EUCLIDEAN: VSK_RERANK(VSK_METRIC_EUCLIDEAN); break;
@@ -1573,28 +1525,145 @@ int32_t tensor_search_finish(Index* ix, const float* ext_bound, float* out_dist,
   fin.max_count = keep;
   VSK_TRY(launch_select(ctx, fin));
 
-  // ---- flags: bounded-wait expiry, overflowed lists, failed certificates ----
-  std::vector<int32_t> flags((size_t)nq);
-  int32_t herr = 0;
-  VSK_CUDA(ctx, cudaMemcpyAsync(flags.data(), cand.flags, nq * 4, cudaMemcpyDeviceToHost, ctx->stream));
-  VSK_CUDA(ctx, cudaMemcpyAsync(&herr, err, 4, cudaMemcpyDeviceToHost, ctx->stream));
-  unsigned long long hrr = 0;
-  VSK_CUDA(ctx, cudaMemcpyAsync(&hrr, rr_total, 8, cudaMemcpyDeviceToHost, ctx->stream));
-  VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  // ---- flag words to the host: bounded-wait expiry, overflowed lists, failed certificates ----
+  PinnedBuf& hb = ctx->host_flags[ctx->lane];
+  VSK_TRY(pinned_reserve(ctx, &hb, (size_t)nq * 4 + 16));
+  char* h = (char*)hb.p;
+  VSK_CUDA(ctx, cudaMemcpyAsync(h, pd.err, 4, cudaMemcpyDeviceToHost, ctx->stream));
+  VSK_CUDA(ctx, cudaMemcpyAsync(h + 8, pd.rr_total, 8, cudaMemcpyDeviceToHost, ctx->stream));
+  VSK_CUDA(ctx, cudaMemcpyAsync(h + 16, cand.flags, (size_t)nq * 4, cudaMemcpyDeviceToHost, ctx->stream));
+  pd.issued = true;
+  pd.out_dist = out_dist;
+  pd.out_ids = out_ids;
+  return VSK_OK;
+}
+
+// Second half, part two, after the stream of lane `from_lane` has drained: reads that lane's flag words and re-runs
+// on the fp32 scan (on the CURRENT lane) the queries whose candidate list overflowed or whose result could not be
+// certified.
+int32_t tensor_search_finish_collect(Index* ix, int from_lane) {
+  Ctx* ctx = ix->ctx;
+  if (from_lane < 0) from_lane = ctx->lane;
+  const ShardPending pd = ctx->pending[from_lane];
+  ctx->pending[from_lane] = ShardPending{};
+  if (!pd.active || !pd.issued || pd.ix != ix)
+    return fail(ctx, VSK_ERR_INVALID_INPUT, "no search is waiting to be collected on this index");
+  const char* h = (const char*)ctx->host_flags[from_lane].p;
+  int32_t herr;
+  unsigned long long hrr;
+  memcpy(&herr, h, 4);
+  memcpy(&hrr, h + 8, 8);
+  const int32_t* flags = (const int32_t*)(h + 16);
   ctx->stats.reranked_rows += (int64_t)hrr;
   if (herr != 0)
     return fail(ctx, VSK_ERR_TIMEOUT, "tensor-core scan: a bounded pipeline wait ran out (role %d)", herr);
   std::vector<int32_t> bad;
-  for (int64_t i = 0; i < nq; ++i)
+  for (int64_t i = 0; i < pd.nq; ++i)
     if (flags[i]) bad.push_back((int32_t)i);
-  if (!bad.empty()) VSK_TRY(fp32_search_subset(ix, q, bad, k, qnorm, out_dist, out_ids));
+  if (!bad.empty()) VSK_TRY(fp32_search_subset(ix, pd.q, bad, pd.k, pd.qnorm, pd.qmasks, pd.out_dist, pd.out_ids));
   return VSK_OK;
 }
 
-int32_t tensor_search(Index* ix, const float* q, int64_t nq, int32_t k, const float* qnorm, float* out_dist,
-                      int64_t* out_ids) {
-  VSK_TRY(tensor_search_begin(ix, q, nq, k, qnorm, 1, nullptr));
-  return tensor_search_finish(ix, nullptr, out_dist, out_ids);
+int32_t tensor_search_finish(Index* ix, const float* ext_bound, float* out_dist, int64_t* out_ids) {
+  Ctx* ctx = ix->ctx;
+  VSK_TRY(tensor_search_finish_issue(ix, ext_bound, out_dist, out_ids));
+  VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return tensor_search_finish_collect(ix, -1);
+}
+
+// How a batch of nq queries is split over the two lanes: the first half's size (a whole number of query tiles), or 0
+// for one lane.  Two lanes need enough queries that each half still fills the machine, and timing the scan kernels
+// with events (vsk_profile) needs them alone on the device.
+int64_t tensor_lane_split(const Ctx* ctx, int64_t nq) {
+  const int64_t min_q = ctx->tuning.overlap_min_queries;
+  if (min_q <= 0 || nq < min_q || nq < 4 * TM || ctx->profile) return 0;
+  return ceil_div(ceil_div(nq, 2), TM) * TM;
+}
+
+int32_t tensor_search(Index* ix, const float* q, int64_t nq, int32_t k, const float* qnorm, const uint64_t* qmasks,
+                      float* out_dist, int64_t* out_ids) {
+  Ctx* ctx = ix->ctx;
+  const int64_t na = ctx->lane == 0 ? tensor_lane_split(ctx, nq) : 0;
+  if (na == 0) {
+    VSK_TRY(tensor_search_begin(ix, q, nq, k, qnorm, qmasks, 1, nullptr));
+    return tensor_search_finish(ix, nullptr, out_dist, out_ids);
+  }
+  // Two halves on two streams.  Each half is a complete search of its own queries (own candidate lists, own
+  // operands); the device runs one half's compactions, re-scoring and final order while the other half's
+  // contraction holds the tensor cores.
+  VSK_TRY(tensor_prepare(ix));   // the shared operand copy is made before the lanes part
+  const int64_t nb = nq - na;
+  const float* qb = q + na * ix->dim;
+  const float* qnb = qnorm ? qnorm + na : nullptr;
+  const uint64_t* qmb = qmasks ? qmasks + na : nullptr;
+  VSK_TRY(lanes_fork(ctx));
+  int32_t st = VSK_OK;
+  auto on_lane = [&](int lane, auto&& fn) {
+    if (st != VSK_OK) return;
+    LaneGuard g(ctx, lane);
+    st = fn();
+  };
+  on_lane(0, [&] { return tensor_search_begin(ix, q, na, k, qnorm, qmasks, 1, nullptr); });
+  on_lane(1, [&] { return tensor_search_begin(ix, qb, nb, k, qnb, qmb, 1, nullptr); });
+  on_lane(0, [&] { return tensor_search_finish_issue(ix, nullptr, out_dist, out_ids); });
+  on_lane(1, [&] { return tensor_search_finish_issue(ix, nullptr, out_dist + na * k, out_ids + na * k); });
+  const int32_t jst = lanes_join(ctx);
+  cudaStreamSynchronize(ctx->stream_main);   // lane 1 has joined: both halves are complete (or failed)
+  if (st != VSK_OK || jst != VSK_OK) {
+    cudaStreamSynchronize(ctx->stream_aux);
+    ctx->pending[0] = ShardPending{};
+    ctx->pending[1] = ShardPending{};
+    return st != VSK_OK ? st : jst;
+  }
+  // flagged queries of either half are re-run on lane 0, whose own work is over
+  const int32_t sa = tensor_search_finish_collect(ix, 0);
+  const int32_t sb = tensor_search_finish_collect(ix, 1);
+  return sa != VSK_OK ? sa : sb;
+}
+
+// keys of a dense chunk -> their values, row-major [nq][rows]
+__global__ void keys_to_values_kernel(const uint64_t* __restrict__ keys, int64_t nq, int64_t rows, float* __restrict__ out) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= nq * rows) return;
+  const int64_t q = i / rows, r = i - q * rows;
+  out[i] = ordered_to_float((uint32_t)(keys[q * kCandCap + r] >> 32));
+}
+
+// The coarse values of the first `rows` rows (one dense chunk of the scan) and the bound the certificate assumes.
+int32_t tensor_coarse_values(Index* ix, const float* q, int64_t nq, int64_t rows, float* coarse, float* eps_out) {
+  Ctx* ctx = ix->ctx;
+  if (rows <= 0 || rows > kCandCap || rows > ix->n)
+    return fail(ctx, VSK_ERR_INVALID_BUFFER_SIZE, "rows must be in [1, min(%d, index size)]", kCandCap);
+  VSK_TRY(tensor_prepare(ix));
+  QueryOperands qo;
+  VSK_TRY(prepare_query_operands(ix, q, nq, &qo));
+  CUtensorMap mq, mx;
+  VSK_TRY(make_map(ctx, qo.q16, nq, ix->dim16, TM, &mq));
+  VSK_TRY(make_map(ctx, ix->rows16, ix->n, ix->dim16, TN, &mx));
+  CandLists cand;
+  VSK_TRY(cand_lists(ctx, nq, &cand));
+  VSK_TRY(launch_init_cand(ctx, cand, nq));
+  TcArgs a{};
+  a.nq = nq;
+  a.kblocks = ix->dim16 / TK;
+  a.alpha = qo.alpha;
+  a.beta = (ix->metric == VSK_METRIC_EUCLIDEAN && !ix->fold16) ? ix->row_aux : nullptr;
+  a.cand = cand;
+  a.cap = kCandCap;
+  a.err = qo.err;
+  a.mode = SCAN_DENSE;
+  a.row_begin = 0;
+  a.row_end = rows;
+  VSK_TRY(launch_tc<SCAN_DENSE>(ctx, mq, mx, a, a.beta != nullptr));
+  keys_to_values_kernel<<<(unsigned)ceil_div(nq * rows, 256), 256, 0, ctx->stream>>>(cand.keys, nq, rows, coarse);
+  ctx->stats.kernel_launches++;
+  VSK_CUDA(ctx, cudaGetLastError());
+  if (eps_out) VSK_CUDA(ctx, cudaMemcpyAsync(eps_out, qo.eps, (size_t)nq * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+  int32_t herr = 0;
+  VSK_CUDA(ctx, cudaMemcpyAsync(&herr, qo.err, 4, cudaMemcpyDeviceToHost, ctx->stream));
+  VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  if (herr != 0) return fail(ctx, VSK_ERR_TIMEOUT, "tensor-core scan: a bounded pipeline wait ran out (role %d)", herr);
+  return VSK_OK;
 }
 
 
@@ -1770,7 +1839,7 @@ int32_t ivf_tensor_search(Index* ix, const float* q, int64_t nq, const int64_t* 
 
   // ---- stage plan: which probe ranks go with the remainder of the nearest list ----
   const double mean_len = std::max(1.0, (double)ix->n / (double)nlist);
-  static const int pilot_tiles = (int)schedule_tuning("VSK_IVF_PILOT_TILES", kIvfPilotTiles);
+  const int pilot_tiles = ctx->tuning.ivf_pilot_tiles > 0 ? ctx->tuning.ivf_pilot_tiles : kIvfPilotTiles;
   const int64_t pilot_rows = (int64_t)pilot_tiles * TN;
   // rows one launch may add after the pilot's rows without (plausibly) overflowing a list: the flat schedule's rule.
   // When all probed lists fit, one launch takes every remaining rank; otherwise the ranks are split in two groups.
@@ -1867,7 +1936,7 @@ int32_t ivf_tensor_search(Index* ix, const float* q, int64_t nq, const int64_t* 
     a.tiles = (const int4*)p;
     a.num_tiles = total;
     a.pair_thr = pair_thr;
-    VSK_TRY(launch_tc<SCAN_THRESHOLD>(ctx, mq, mx, a, !fold, false));
+    VSK_TRY(launch_tc<SCAN_THRESHOLD>(ctx, mq, mx, a, !fold));
     if (stage == 0) {
       // the pilot appended up to 1 024 rows per query: keep the best few by coarse value and re-score only those
       SelectArgs pre = sel;
@@ -2007,11 +2076,11 @@ int32_t tensor_assign(Ctx* ctx, TensorAssign* ta, const float* rows, const float
   } else {
     VSK_CUDA(ctx, cudaMemsetAsync(ta->best, 0xff, (size_t)n * sizeof(unsigned long long), ctx->stream));
     a.mode = SCAN_ARGMIN;
-    VSK_TRY(launch_tc<SCAN_ARGMIN>(ctx, mr, mc, a, true, false));
+    VSK_TRY(launch_tc<SCAN_ARGMIN>(ctx, mr, mc, a, true));
     assign_threshold_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, ctx->stream>>>(ta->best, eps, n, ta->thr, ta->count);
   }
   a.mode = SCAN_THRESHOLD;
-  VSK_TRY(launch_tc<SCAN_THRESHOLD>(ctx, mr, mc, a, true, false));
+  VSK_TRY(launch_tc<SCAN_THRESHOLD>(ctx, mr, mc, a, true));
   assign_exact_kernel<<<(unsigned)ceil_div(n, 8), 256, 0, ctx->stream>>>(rows, n, dim, centroids, ta->keys, ta->count, assign, dist,
                                                                          ta->bad_rows, (int32_t*)(sm + 6), tc_epilogue_warps(a.kblocks) / 4);
   ctx->stats.kernel_launches += 2;

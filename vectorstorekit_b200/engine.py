@@ -207,6 +207,54 @@ class CUDAComputeDevice:
     def stream(self) -> int:
         return int(self._lib.vsk_stream(self._h) or 0)
 
+    def measure_peak(self, what: str) -> float:
+        """``vsk_measure_peak``: "fp32_issue" (FP32 instructions/s per thread) or "smem_gather" (4-byte words/s)."""
+        v = C.c_double()
+        self.check(self._lib.vsk_measure_peak(self._h, {"fp32_issue": 0, "smem_gather": 1}[what], C.byref(v)))
+        return float(v.value)
+
+    # ---- tuning of the search schedule (``vsk_tuning``) ----
+    def tuning(self) -> dict:
+        t = _lib.Tuning()
+        self.check(self._lib.vsk_tuning_get(self._h, C.byref(t)))
+        return {f: getattr(t, f) for f, _ in t._fields_ if f != "reserved"}
+
+    def set_tuning(self, **fields):
+        t = _lib.Tuning()
+        self.check(self._lib.vsk_tuning_get(self._h, C.byref(t)))
+        for name, value in fields.items():
+            if name == "reserved" or not hasattr(t, name):
+                raise InvalidInput(f"unknown tuning field {name}")
+            setattr(t, name, int(value))
+        self.check(self._lib.vsk_tuning_set(self._h, C.byref(t)))
+
+    # ---- communicator of a row-sharded search: one process and one device object per GPU ----
+    def comm_unique_id(self) -> bytes:
+        """128 bytes made on ONE rank; hand the same bytes to ``comm_init`` on every rank."""
+        buf = (C.c_ubyte * _lib.COMM_ID_BYTES)()
+        st = self._lib.vsk_comm_unique_id(buf)
+        if st != 0:
+            raise ExecutionFailed("NCCL is not available (libnccl.so.2 could not be loaded)")
+        return bytes(buf)
+
+    def comm_init(self, nranks: int, rank: int, unique_id: Optional[bytes]):
+        buf = (C.c_ubyte * _lib.COMM_ID_BYTES).from_buffer_copy(unique_id) if unique_id is not None else None
+        self.check(self._lib.vsk_comm_init(self._h, int(nranks), int(rank), buf))
+
+    def comm_destroy(self):
+        self.check(self._lib.vsk_comm_destroy(self._h))
+
+    def comm_info(self):
+        n, r = C.c_int32(), C.c_int32()
+        self.check(self._lib.vsk_comm_info(self._h, C.byref(n), C.byref(r)))
+        return n.value, r.value
+
+    def sharded_phase_ms(self):
+        ms = (C.c_float * _lib.SHARDED_PHASES)()
+        self.check(self._lib.vsk_sharded_phase_ms(self._h, ms))
+        names = ("queries", "scan", "bound_allreduce", "finish", "all_to_all", "merge", "gather")
+        return dict(zip(names, (float(x) for x in ms)))
+
 
 class CUDAAcceleratorStrategy:
     """``ComputeAccelerator`` conformance for a B200 (``Core/Protocols.swift:11-20``)."""
@@ -362,6 +410,52 @@ class _IndexBase:
         return od, oi
 
 
+def sharded_slice(nq: int, nranks: int, rank: int):
+    """Queries [first, first + count) whose merged results rank `rank` returns under the SLICE layout."""
+    per = -(-nq // max(nranks, 1))
+    lo = min(rank * per, nq)
+    return lo, min(per, nq - lo)
+
+
+class _ShardedSearchMixin:
+    """``vsk_search_sharded``: the row-sharded form of ``batchSearch`` for a flat fp32 or int8 index whose device
+    object has joined a communicator (``CUDAComputeDevice.comm_init``).  Every rank passes the same queries."""
+
+    def shardedSearch(self, queries, k: int, filter_masks=None, gather: bool = False, split_queries: bool = False,
+                      out=None):
+        """-> (dist, ids).  gather=False: this rank's slice of the queries (``sharded_slice``), merged over all
+        shards; gather=True: all queries on every rank.  Device tensors in -> device tensors out; host arrays (numpy,
+        or pinned torch CPU tensors) in -> host out, copies inside the call.  `out` = (dist, ids) buffers to fill."""
+        nq, k = int(queries.shape[0]), int(k)
+        if nq == 0:
+            raise EmptyInput("no queries")
+        if queries.shape[1] != self.dimensions:
+            raise DimensionMismatch(f"expected {self.dimensions}, got {queries.shape[1]}")
+        nranks, rank = self.dev.comm_info()
+        rows = nq if (gather or nranks == 1) else sharded_slice(nq, nranks, rank)[1]
+        layout = (_lib.SHARDED_ALL if gather else _lib.SHARDED_SLICE) | (_lib.SHARDED_QUERIES_SPLIT if split_queries else 0)
+        if _is_dev(queries):
+            q = queries.contiguous().float()
+            od, oi = out if out is not None else (torch.empty((max(rows, 1), k), dtype=torch.float32, device=q.device),
+                                                  torch.empty((max(rows, 1), k), dtype=torch.int64, device=q.device))
+            qm = filter_masks.contiguous() if filter_masks is not None else None
+            self.dev.check(self._lib.vsk_search_sharded_dev(self._h, _ptr(q), nq, k, _ptr(qm), layout, _ptr(od), _ptr(oi)))
+            return od[:rows], oi[:rows]
+        if torch is not None and isinstance(queries, torch.Tensor):      # a (pinned) CPU tensor
+            q = queries.contiguous()
+            od, oi = out if out is not None else (torch.empty((max(rows, 1), k), dtype=torch.float32),
+                                                  torch.empty((max(rows, 1), k), dtype=torch.int64))
+            qm = filter_masks.contiguous() if filter_masks is not None else None
+            ptr = lambda t: C.c_void_p(t.data_ptr()) if t is not None else None
+            self.dev.check(self._lib.vsk_search_sharded(self._h, ptr(q), nq, k, ptr(qm), layout, ptr(od), ptr(oi)))
+            return od[:rows], oi[:rows]
+        q = _host(queries, np.float32)
+        od, oi = out if out is not None else (np.empty((max(rows, 1), k), np.float32), np.empty((max(rows, 1), k), np.int64))
+        qm = _host(filter_masks, np.uint64) if filter_masks is not None else None
+        self.dev.check(self._lib.vsk_search_sharded(self._h, _ptr(q), nq, k, _ptr(qm), layout, _ptr(od), _ptr(oi)))
+        return od[:rows], oi[:rows]
+
+
 def _adopt(dev: "CUDAComputeDevice", h):
     """Wrap a handle that came out of an index image in the class of its kind."""
     probe = _IndexBase(dev)
@@ -402,7 +496,7 @@ def load_index(dev: "CUDAComputeDevice", path: str):
     return _adopt(dev, h)
 
 
-class FlatIndex(_IndexBase):
+class FlatIndex(_IndexBase, _ShardedSearchMixin):
     """Resident database + exact k-NN.  ``masks`` are per-row uint64 metadata bitmasks; a search
     with ``filter_masks`` keeps row r for query q iff ``masks[r] & filter_masks[q] != 0`` — the
     bitmask form of the reference's pre-filter (``Indexes/IVFIndex.swift:163-172``)."""
@@ -445,6 +539,15 @@ class FlatIndex(_IndexBase):
         if queries.shape[1] != self.dimensions:
             raise DimensionMismatch(f"expected {self.dimensions}, got {queries.shape[1]}")
         return self._search(queries, int(k), filter_masks)
+
+    def coarseValues(self, queries, rows: int):
+        """``vsk_coarse_values_dev``: the tensor path's coarse values of the first `rows` rows and the per-query
+        bound the certificate assumes on |coarse - exact| (device tensors), for auditing that bound."""
+        q = queries.contiguous().float()
+        coarse = torch.empty((q.shape[0], int(rows)), dtype=torch.float32, device=q.device)
+        eps = torch.empty(q.shape[0], dtype=torch.float32, device=q.device)
+        self.dev.check(self._lib.vsk_coarse_values_dev(self._h, _ptr(q), q.shape[0], int(rows), _ptr(coarse), _ptr(eps)))
+        return coarse, eps
 
     # The search in two halves, for one shard of a row-sharded database (``sharded.ShardedSearch``): `begin` scans
     # and returns, per query, a value that this shard's ceil(k / shards) best rows do not exceed; the caller takes the
@@ -702,7 +805,7 @@ class ScalarQuantizer:
         return out
 
 
-class QuantizedFlatIndex(_IndexBase):
+class QuantizedFlatIndex(_IndexBase, _ShardedSearchMixin):
     """Flat index over int8 codes; distances are taken against the dequantised rows."""
 
     def __init__(self, dev: CUDAComputeDevice, dimensions: int, metric, scale, offset):

@@ -10,6 +10,7 @@
 //   ScalarQuantizer                Quantization/ScalarQuantizer.swift (int8)
 // Errors are thrown as exceptions named after MetalComputeError / IVFError cases.
 #pragma once
+#include <algorithm>
 #include <cstdint>
 #include <memory>
 #include <stdexcept>
@@ -79,6 +80,23 @@ class CUDAComputeDevice {
   vsk_ctx* ctx() const { return ctx_; }
   vsk_device_info capabilities() const { vsk_device_info i{}; check(vsk_device_info_get(ctx_, &i), ctx_); return i; }
   vsk_stats statistics() const { vsk_stats s{}; check(vsk_stats_get(ctx_, &s), ctx_); return s; }
+  // Row-sharded search: one process and one device object per GPU.  ONE rank makes the id, the host hands the same
+  // bytes to every rank, every rank joins with its own rank number.
+  static std::vector<uint8_t> communicatorId() {
+    std::vector<uint8_t> id(VSK_COMM_ID_BYTES);
+    const int32_t st = vsk_comm_unique_id(id.data());
+    if (st != VSK_OK) throw Error(st, "NCCL is not available");
+    return id;
+  }
+  void joinCommunicator(int32_t nranks, int32_t rank, const std::vector<uint8_t>& id) {
+    check(vsk_comm_init(ctx_, nranks, rank, id.empty() ? nullptr : id.data()), ctx_);
+  }
+  void leaveCommunicator() { check(vsk_comm_destroy(ctx_), ctx_); }
+  std::pair<int32_t, int32_t> communicator() const {   // (ranks, this rank)
+    int32_t n = 1, r = 0;
+    check(vsk_comm_info(ctx_, &n, &r), ctx_);
+    return {n, r};
+  }
  private:
   vsk_ctx* ctx_ = nullptr;
 };
@@ -132,6 +150,24 @@ class FlatIndex {
     if (nq <= 0) throw EmptyInput(VSK_ERR_EMPTY_INPUT, "no queries");
     r.distances.resize((size_t)nq * k); r.ids.resize((size_t)nq * k);
     check(vsk_search(ix_, queries, nq, k, filter_masks, r.distances.data(), r.ids.data()), dev_->ctx());
+    return r;
+  }
+  // This index holds rows [idBase, idBase + count) of a database spread over the ranks of the device's communicator.
+  void setIdBase(int64_t base) { check(vsk_index_set_id_base(ix_, base), dev_->ctx()); }
+  // The sharded form of batchSearch: every rank passes the same queries.  gather = false: the merged results of this
+  // rank's slice of the queries (firstQuery says where the slice starts); gather = true: all queries on every rank.
+  SearchResults shardedSearch(const float* queries, int64_t nq, int32_t k, const uint64_t* filter_masks = nullptr,
+                              bool gather = false, int64_t* firstQuery = nullptr) const {
+    if (nq <= 0) throw EmptyInput(VSK_ERR_EMPTY_INPUT, "no queries");
+    const auto cm = dev_->communicator();
+    int64_t first = 0, count = nq;
+    if (!gather) vsk_sharded_slice(nq, cm.first, cm.second, &first, &count);
+    SearchResults r; r.nq = count; r.k = k;
+    r.distances.resize((size_t)std::max<int64_t>(count, 1) * k); r.ids.resize((size_t)std::max<int64_t>(count, 1) * k);
+    check(vsk_search_sharded(ix_, queries, nq, k, filter_masks, gather ? VSK_SHARDED_ALL : VSK_SHARDED_SLICE,
+                             r.distances.data(), r.ids.data()), dev_->ctx());
+    r.distances.resize((size_t)count * k); r.ids.resize((size_t)count * k);
+    if (firstQuery) *firstQuery = first;
     return r;
   }
  private:

@@ -22,6 +22,20 @@ import contextlib
 from typing import Callable, Optional, Tuple
 
 
+def join_communicator(dev, group=None):
+    """Joins `dev` (a ``CUDAComputeDevice``) to a communicator over the ranks of a ``torch.distributed`` group: rank 0
+    makes the id (``vsk_comm_unique_id``), the group broadcasts the 128 bytes, every rank calls ``vsk_comm_init``.
+    After this, ``FlatIndex.shardedSearch`` / ``QuantizedFlatIndex.shardedSearch`` (``vsk_search_sharded``) do the
+    whole sharded search inside the library - scan, bound all-reduce, one all-to-all of packed keys, merge - and
+    this module's ``ShardedSearch`` is needed only for index kinds without that entry point and for CPU tests."""
+    import torch.distributed as dist
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    box = [dev.comm_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(box, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+    dev.comm_init(world, rank, box[0])
+    return world, rank
+
+
 def shard_range(n_total: int, rank: int, world: int) -> Tuple[int, int]:
     """Rows [lo, hi) of rank `rank`; the union over ranks is [0, n_total) with no overlap."""
     return rank * n_total // world, (rank + 1) * n_total // world
