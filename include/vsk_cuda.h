@@ -131,9 +131,10 @@ typedef struct vsk_tuning {
   int32_t dense_rows;           /* 0 = automatic; rows of the first (unfiltered) chunk otherwise */
   int32_t ivf_pilot_tiles;      /* 4: 256-row tiles of the nearest list that set an IVF query's first threshold */
   int32_t stream_scan;          /* 1: batches of up to eight queries stream the rows instead of padding a tile */
-  int32_t overlap_min_queries;  /* 2048: tensor-path batches of at least this many queries run as two halves on two
-                                   streams (one half's selection and re-scoring under the other's contraction);
-                                   0 = never */
+  int32_t overlap_min_queries;  /* 0 = never; otherwise tensor-path batches of at least this many queries run as
+                                   two halves on two streams (one half's selection, re-scoring and exchange under
+                                   the other's contraction).  Off by default: on one power-capped GPU the two
+                                   halves were measured to slow each other down by what the overlap gains. */
   int32_t reserved[10];
 } vsk_tuning;
 
@@ -152,6 +153,13 @@ int32_t vsk_set_search_path(vsk_ctx* ctx, int32_t path);
  * context's stream; totals appear in vsk_stats.  Stands in for MetalProfiler's per-operation timing
  * (Acceleration/Metal/MetalProfiler.swift:74-110). */
 int32_t vsk_profile(vsk_ctx* ctx, int32_t enable);
+/* Event log of the next calls on this context: one CUDA event after each scan, selection, re-scoring and exchange,
+ * on the stream it was enqueued on.  vsk_timeline_read drains both streams, writes one line per event - "<lane>
+ * <what> <milliseconds since the log was switched on or last read>" - into `text` (at most `capacity` bytes,
+ * NUL-terminated), clears the log and returns the bytes written (-1 on bad arguments).  Shows how the two halves of
+ * a large batch overlap.  Stands in for MetalProfiler's event log (Acceleration/Metal/MetalProfiler.swift:74-110). */
+int32_t vsk_timeline(vsk_ctx* ctx, int32_t enable);
+int64_t vsk_timeline_read(vsk_ctx* ctx, char* text, int64_t capacity);
 /* The CUDA stream (cudaStream_t) every call on this context is enqueued on. */
 void* vsk_stream(vsk_ctx* ctx);
 /* Rows of the next chunk of the search schedule after `seen` rows, for candidate lists compacted to `keep` keys

@@ -212,9 +212,10 @@ def test_tensor_accumulation_error_is_inside_the_certificate_term(vsk, dev, d):
     import torch
     n, nq = 4096, 512
     g = torch.Generator(device="cuda").manual_seed(900 + d)
-    # multiples of 1/64 in [-4, 4]: exact in fp16 at any power-of-two operand scale the library may choose
-    x = (torch.randint(-256, 257, (n, d), generator=g, device="cuda").float() / 64.0).contiguous()
-    q = (torch.randint(-256, 257, (nq, d), generator=g, device="cuda").float() / 64.0).contiguous()
+    # N(0,1) rounded to fp16: full 11-bit significands, and still fp16 numbers after any power-of-two operand scale
+    # the library may choose (|values| stay far inside fp16's range), so the operands carry no rounding of their own
+    x = torch.randn((n, d), generator=g, device="cuda").half().float().contiguous()
+    q = torch.randn((nq, d), generator=g, device="cuda").half().float().contiguous()
     ix = vsk.FlatIndex(dev, d, "dotProduct")
     try:
         ix.add(x)
@@ -236,7 +237,7 @@ def test_tensor_accumulation_error_is_inside_the_certificate_term(vsk, dev, d):
 @pytest.mark.parametrize("metric", ["euclidean", "cosine", "dotProduct"])
 def test_coarse_values_stay_within_eps_of_the_exact_values(vsk, dev, metric):
     """On ordinary fp32 data the coarse value of every (query, row) pair lies within the query's eps of the exact
-    value (fp64 of the reference's formula; squared form for euclidean, without |q|^2): the inequality the
+    value (fp64 of the reference's formula; squared form for euclidean, without |q|^2; cosine without its 1): the inequality the
     certificate rests on."""
     import torch
     rng = np.random.default_rng(31)
@@ -255,7 +256,8 @@ def test_coarse_values_stay_within_eps_of_the_exact_values(vsk, dev, metric):
     if metric == "euclidean":
         ref = (x64 ** 2).sum(1)[None, :] - 2.0 * dot                     # |x|^2 - 2 q.x
     elif metric == "cosine":
-        ref = 1.0 - dot / (np.linalg.norm(q64, axis=1)[:, None] * np.linalg.norm(x64, axis=1)[None, :] + 1e-8)
+        # the scan ranks by -cos; the row-independent "1 +" is added when the distance is formed
+        ref = -dot / (np.linalg.norm(q64, axis=1)[:, None] * np.linalg.norm(x64, axis=1)[None, :] + 1e-8)
     else:
         ref = -dot
     excess = np.abs(coarse - ref) - eps[:, None]

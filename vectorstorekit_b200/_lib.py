@@ -62,6 +62,8 @@ SIGNATURES = {
     "vsk_profile": (C.c_int32, [vp, C.c_int32]),
     "vsk_schedule_chunk": (C.c_int64, [C.c_int64, C.c_int32, C.c_int32]),
     "vsk_measure_peak": (C.c_int32, [vp, C.c_int32, C.POINTER(C.c_double)]),
+    "vsk_timeline": (C.c_int32, [vp, C.c_int32]),
+    "vsk_timeline_read": (C.c_int64, [vp, C.c_char_p, C.c_int64]),
     "vsk_tuning_get": (C.c_int32, [vp, C.POINTER(Tuning)]),
     "vsk_tuning_set": (C.c_int32, [vp, C.POINTER(Tuning)]),
     "vsk_comm_unique_id": (C.c_int32, [vp]),

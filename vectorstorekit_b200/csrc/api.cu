@@ -87,6 +87,19 @@ int32_t scratch(Ctx* ctx, int slot, size_t bytes, void** out) {
   return VSK_OK;
 }
 
+void tl_mark(Ctx* ctx, const char* name) {
+  if (!ctx->timeline) return;
+  if (ctx->marks_used == ctx->marks.size()) {
+    cudaEvent_t e;
+    if (cudaEventCreate(&e) != cudaSuccess) { cudaGetLastError(); return; }
+    ctx->marks.push_back(Ctx::Mark{name, ctx->lane, e});
+  }
+  Ctx::Mark& m = ctx->marks[ctx->marks_used++];
+  m.name = name;
+  m.lane = ctx->lane;
+  cudaEventRecord(m.ev, ctx->stream);
+}
+
 void prof_begin(Ctx* ctx) {
   if (!ctx->profile) return;
   if (ctx->prof_used + 2 > ctx->prof_events.size()) {
@@ -119,7 +132,7 @@ vsk_tuning default_tuning() {
   t.dense_rows = 0;
   t.ivf_pilot_tiles = 4;
   t.stream_scan = 1;
-  t.overlap_min_queries = 2048;
+  t.overlap_min_queries = 0;   // measured: on one GPU the halves take turns at a power-capped device, no gain
   return t;
 }
 
@@ -648,6 +661,8 @@ int32_t vsk_close(vsk_ctx* c) {
   for (auto& b : ctx->host_flags)
     if (b.p) cudaFreeHost(b.p);
   for (auto& e : ctx->prof_events) cudaEventDestroy(e);
+  for (auto& m : ctx->marks) cudaEventDestroy(m.ev);
+  if (ctx->tl_origin) cudaEventDestroy(ctx->tl_origin);
   cudaEventDestroy(ctx->ev_fork);
   cudaEventDestroy(ctx->ev_join);
   cudaStreamDestroy(ctx->stream_main);
@@ -699,6 +714,45 @@ int32_t vsk_set_search_path(vsk_ctx* c, int32_t path) {
 int64_t vsk_schedule_chunk(int64_t seen, int32_t keep, int32_t level) {
   if (seen < 0 || keep <= 0 || keep > kCandCap / 2) return -1;
   return schedule_chunk(seen, keep, level);
+}
+
+int32_t vsk_timeline(vsk_ctx* c, int32_t enable) {
+  Ctx* ctx = reinterpret_cast<Ctx*>(c);
+  if (!ctx) return VSK_ERR_INVALID_INPUT;
+  cudaSetDevice(ctx->device);
+  cudaStreamSynchronize(ctx->stream_main);
+  cudaStreamSynchronize(ctx->stream_aux);
+  ctx->marks_used = 0;
+  ctx->timeline = enable != 0;
+  if (ctx->timeline) {
+    if (!ctx->tl_origin && cudaEventCreate(&ctx->tl_origin) != cudaSuccess) {
+      cudaGetLastError();
+      ctx->timeline = false;
+      return fail(ctx, VSK_ERR_EXECUTION_FAILED, "could not create the origin event");
+    }
+    cudaEventRecord(ctx->tl_origin, ctx->stream_main);
+  }
+  return VSK_OK;
+}
+
+int64_t vsk_timeline_read(vsk_ctx* c, char* text, int64_t capacity) {
+  Ctx* ctx = reinterpret_cast<Ctx*>(c);
+  if (!ctx || !text || capacity <= 0) return -1;
+  cudaSetDevice(ctx->device);
+  cudaStreamSynchronize(ctx->stream_main);
+  cudaStreamSynchronize(ctx->stream_aux);
+  int64_t used = 0;
+  text[0] = 0;
+  for (size_t i = 0; i < ctx->marks_used; ++i) {
+    float ms = 0.f;
+    if (cudaEventElapsedTime(&ms, ctx->tl_origin, ctx->marks[i].ev) != cudaSuccess) { cudaGetLastError(); continue; }
+    const int w = snprintf(text + used, (size_t)(capacity - used), "%d %s %.4f\n", ctx->marks[i].lane, ctx->marks[i].name, ms);
+    if (w < 0 || used + w >= capacity) break;
+    used += w;
+  }
+  ctx->marks_used = 0;
+  if (ctx->timeline) cudaEventRecord(ctx->tl_origin, ctx->stream_main);
+  return used;
 }
 
 int32_t vsk_profile(vsk_ctx* c, int32_t enable) {

@@ -124,6 +124,7 @@ static int32_t exchange_keys(Ctx* ctx, const NcclApi* api, Comm* cm, const uint6
     }
   }
   VSK_NCCL(ctx, api, api->GroupEnd());
+  tl_mark(ctx, "all_to_all");
   return VSK_OK;
 }
 
@@ -191,6 +192,7 @@ static int32_t search_sharded_dev(Index* ix, const float* q, int64_t nq, int32_t
       VSK_TRY(tensor_search_begin(ix, q, nq, k, qnorm, qmasks, G, bound));
       phase_mark(ctx, cm, 2);
       VSK_NCCL(ctx, api, api->AllReduce(bound, bound, (size_t)nq, ncclFloat32, ncclMax, cm->comm, ctx->stream));
+      tl_mark(ctx, "bound_allreduce");
       phase_mark(ctx, cm, 3);
       VSK_TRY(tensor_search_finish(ix, bound, loc_d, loc_i));
     } else {
@@ -207,6 +209,7 @@ static int32_t search_sharded_dev(Index* ix, const float* q, int64_t nq, int32_t
       };
       auto reduce = [&](float* b, int64_t n) -> int32_t {
         VSK_NCCL(ctx, api, api->AllReduce(b, b, (size_t)n, ncclFloat32, ncclMax, cm->comm, ctx->stream));
+        tl_mark(ctx, "bound_allreduce");
         return VSK_OK;
       };
       on_lane(0, [&] { return tensor_search_begin(ix, q, na, k, qnorm, qmasks, G, bound); });

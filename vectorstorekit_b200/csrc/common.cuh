@@ -141,7 +141,25 @@ struct Ctx {
   ShardPending pending[2];
   PinnedBuf host_flags[2];   // per lane: the flag words a finished half-search hands to the host
   Comm* comm = nullptr;
+  // optional event log (vsk_timeline): one event after each marked launch, on the stream it went to
+  bool timeline = false;
+  struct Mark { const char* name; int lane; cudaEvent_t ev; };
+  std::vector<Mark> marks;
+  size_t marks_used = 0;
+  cudaEvent_t tl_origin = nullptr;
 };
+// Records "the work issued so far on the current lane, up to `name`, is done" when the event log is on.
+void tl_mark(Ctx* ctx, const char* name);
+
+// Small kernels (selection, re-scoring, operand preparation, key packing) ask for the largest shared-memory
+// carve-out, the configuration the contraction kernel runs under: an SM does not switch its L1 / shared-memory split
+// while it holds a CTA, so a kernel that preferred another split could not join the contraction's CTAs on an SM and
+// the two lanes of a context would take turns instead of overlapping.
+template <typename K>
+inline void prefer_shared_carveout(K kernel) {
+  cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+  cudaGetLastError();
+}
 
 // Issues on lane `lane` until it goes out of scope.
 struct LaneGuard {

@@ -189,6 +189,11 @@ int32_t launch_exact_scan(Ctx* ctx, const ExactScanArgs& a) {
 int32_t launch_row_norms(Ctx* ctx, const float* x, int64_t n, int32_t dim, int squared, float* out) {
   if (n <= 0) return VSK_OK;
   const int warps = 8;
+  static bool carveout_done = false;
+  if (!carveout_done) {
+    prefer_shared_carveout(row_norm_kernel);
+    carveout_done = true;
+  }
   row_norm_kernel<<<(unsigned)ceil_div(n, warps), warps * 32, 0, ctx->stream>>>(x, n, dim, squared, out);
   ctx->stats.kernel_launches++;
   VSK_CUDA(ctx, cudaGetLastError());

@@ -390,6 +390,7 @@ int32_t launch_pack_keys(Ctx* ctx, const float* dist, const int64_t* ids, int64_
                          uint64_t* keys) {
   if (rows <= 0) return VSK_OK;
   pack_keys_kernel<<<(unsigned)ceil_div(rows * k, 256), 256, 0, ctx->stream>>>(dist, ids, nq, rows, k, keys);
+  tl_mark(ctx, "pack_keys");
   ctx->stats.kernel_launches++;
   VSK_CUDA(ctx, cudaGetLastError());
   return VSK_OK;
@@ -411,6 +412,7 @@ int32_t launch_merge_keys(Ctx* ctx, const uint64_t* in, int32_t g, int64_t strid
     merge_keys_kernel<128><<<(unsigned)nq, 128, 0, ctx->stream>>>(in, g, stride_q, k, out);
   else
     merge_keys_kernel<SEL_THREADS><<<(unsigned)nq, SEL_THREADS, 0, ctx->stream>>>(in, g, stride_q, k, out);
+  tl_mark(ctx, "merge_keys");
   ctx->stats.kernel_launches++;
   VSK_CUDA(ctx, cudaGetLastError());
   return VSK_OK;
@@ -421,6 +423,17 @@ int32_t launch_select(Ctx* ctx, const SelectArgs& a) {
   // lists known to hold at most 1024 keys take the 128-thread variant (four times as many CTAs per SM);
   // only the final ordering sorts in shared memory
   const bool small = a.max_count > 0 && a.max_count <= 128 * SEL_ITEMS && (a.dense_count < 0 || a.dense_count <= 128 * SEL_ITEMS);
+  static bool carveout_done = false;
+  if (!carveout_done) {
+    prefer_shared_carveout(select_kernel<128>);
+    prefer_shared_carveout(select_kernel<SEL_THREADS>);
+    prefer_shared_carveout(init_cand_kernel);
+    prefer_shared_carveout(pack_keys_kernel);
+    prefer_shared_carveout(unpack_keys_kernel);
+    prefer_shared_carveout(merge_keys_kernel<128>);
+    prefer_shared_carveout(merge_keys_kernel<SEL_THREADS>);
+    carveout_done = true;
+  }
   if (small) {
     const size_t smem = a.out_ids ? 128 * SEL_ITEMS * sizeof(uint64_t) : 0;
     select_kernel<128><<<(unsigned)a.nq, 128, smem, ctx->stream>>>(a);
@@ -428,6 +441,7 @@ int32_t launch_select(Ctx* ctx, const SelectArgs& a) {
     const size_t smem = a.out_ids ? kCandCap * sizeof(uint64_t) : 0;
     select_kernel<SEL_THREADS><<<(unsigned)a.nq, SEL_THREADS, smem, ctx->stream>>>(a);
   }
+  tl_mark(ctx, a.out_ids ? "final_order" : (a.bound_out ? "bound_select" : (a.cert_eps ? "certify_select" : "select")));
   ctx->stats.kernel_launches++;
   VSK_CUDA(ctx, cudaGetLastError());
   return VSK_OK;

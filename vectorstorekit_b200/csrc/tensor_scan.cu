@@ -1115,6 +1115,7 @@ int32_t launch_tc_ew(Ctx* ctx, const CUtensorMap& mq, const CUtensorMap& mx, con
   prof_begin(ctx);
   kern<<<grid, Epi<EW>::THREADS, smem, ctx->stream>>>(mq, mx, a);
   prof_end(ctx);
+  tl_mark(ctx, MODE == SCAN_DENSE ? "scan_dense" : (MODE == SCAN_ARGMIN ? "scan_argmin" : "scan"));
   ctx->stats.kernel_launches++;
   ctx->stats.tensor_tiles += tiles;
   VSK_CUDA(ctx, cudaGetLastError());
@@ -1266,6 +1267,26 @@ struct QueryOperands {
 
 int32_t prepare_query_operands(Index* ix, const float* q, int64_t nq, QueryOperands* out) {
   Ctx* ctx = ix->ctx;
+  static bool carveout_done = false;
+  if (!carveout_done) {
+    prefer_shared_carveout(absmax_kernel);
+    prefer_shared_carveout(choose_scale_kernel);
+    prefer_shared_carveout(scale_queries_kernel);
+    prefer_shared_carveout(prep_rows_kernel<VSK_METRIC_EUCLIDEAN>);
+    prefer_shared_carveout(prep_rows_kernel<VSK_METRIC_COSINE>);
+    prefer_shared_carveout(prep_rows_kernel<VSK_METRIC_DOT_PRODUCT>);
+    prefer_shared_carveout(bound_kernel<VSK_METRIC_EUCLIDEAN>);
+    prefer_shared_carveout(bound_kernel<VSK_METRIC_COSINE>);
+    prefer_shared_carveout(bound_kernel<VSK_METRIC_DOT_PRODUCT>);
+    prefer_shared_carveout(bound_i8_kernel<VSK_METRIC_EUCLIDEAN>);
+    prefer_shared_carveout(bound_i8_kernel<VSK_METRIC_DOT_PRODUCT>);
+    prefer_shared_carveout(rerank_kernel<VSK_METRIC_EUCLIDEAN>);
+    prefer_shared_carveout(rerank_kernel<VSK_METRIC_COSINE>);
+    prefer_shared_carveout(rerank_kernel<VSK_METRIC_DOT_PRODUCT>);
+    prefer_shared_carveout(rerank_i8_kernel<VSK_METRIC_EUCLIDEAN>);
+    prefer_shared_carveout(rerank_i8_kernel<VSK_METRIC_DOT_PRODUCT>);
+    carveout_done = true;
+  }
   const int metric = ix->metric;
   const int dim = ix->dim, dim16 = ix->dim16;
   void* p;
@@ -1332,6 +1353,7 @@ int32_t prepare_query_operands(Index* ix, const float* q, int64_t nq, QueryOpera
   }
   ctx->stats.kernel_launches++;
   VSK_CUDA(ctx, cudaGetLastError());
+  tl_mark(ctx, "query_operands");
   out->q16 = q16;
   out->eps = eps;
   out->alpha = alpha;
@@ -1509,6 +1531,7 @@ int32_t tensor_search_finish_issue(Index* ix, const float* ext_bound, float* out
     default: VSK_RERANK(VSK_METRIC_DOT_PRODUCT); break;
   }
 #undef VSK_RERANK
+  tl_mark(ctx, "rerank");
   ctx->stats.kernel_launches++;
   VSK_CUDA(ctx, cudaGetLastError());
   SelectArgs fin{};

@@ -207,6 +207,19 @@ class CUDAComputeDevice:
     def stream(self) -> int:
         return int(self._lib.vsk_stream(self._h) or 0)
 
+    def timeline(self, enable: bool):
+        self.check(self._lib.vsk_timeline(self._h, 1 if enable else 0))
+
+    def timeline_read(self):
+        """-> [(lane, what, ms)] of the calls since the log was switched on or last read."""
+        buf = C.create_string_buffer(1 << 20)
+        n = self._lib.vsk_timeline_read(self._h, buf, len(buf))
+        out = []
+        for line in buf.raw[:max(n, 0)].decode().splitlines():
+            lane, what, ms = line.split()
+            out.append((int(lane), what, float(ms)))
+        return out
+
     def measure_peak(self, what: str) -> float:
         """``vsk_measure_peak``: "fp32_issue" (FP32 instructions/s per thread) or "smem_gather" (4-byte words/s)."""
         v = C.c_double()
