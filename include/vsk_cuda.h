@@ -320,6 +320,19 @@ int32_t vsk_kmeans(vsk_ctx* ctx, const float* rows, int64_t n, int32_t dim, int3
 int32_t vsk_kmeans_dev(vsk_ctx* ctx, const float* rows, int64_t n, int32_t dim, int32_t k,
                        int32_t max_iters, float tolerance, const float* init_centroids,
                        float* centroids, int32_t* assign, float* inertia, int32_t* iters_run);
+/* k-means++ initial centroids, the reference's default initialisation (KMeansClustering.initializeKMeansPlusPlus,
+ * Clustering/KMeansClustering.swift:209-260; shader compute_min_distances, Shaders/ClusteringShaders.metal:205-238).
+ * The first centroid is a row drawn uniformly; each next one is drawn with the reference's weights - a row's squared
+ * distance to its nearest chosen centroid divided by the SUM OF UN-SQUARED distances (:236-239; the weights do not
+ * sum to one, which is kept) - the first row whose running sum exceeds a uniform draw in [0, 1), else the last row.
+ * Draws come from the reference's seeded generator (a 64-bit LCG re-seeded with seed + number of centroids so far,
+ * :244,480-491) mapped as Swift's standard library maps it.  centroids: [k][dim]; picked (may be NULL): the k chosen
+ * row indices, host memory.  Running sums are taken in double precision by a parallel scan where the reference adds
+ * floats in sequence, so a draw that lands within rounding of a row boundary may pick the neighbouring row. */
+int32_t vsk_kmeans_init_plusplus(vsk_ctx* ctx, const float* rows, int64_t n, int32_t dim, int32_t k, uint64_t seed,
+                                 float* centroids, int64_t* picked);
+int32_t vsk_kmeans_init_plusplus_dev(vsk_ctx* ctx, const float* rows, int64_t n, int32_t dim, int32_t k, uint64_t seed,
+                                     float* centroids, int64_t* picked);
 /* Lloyd iterations over rows that are spread over several GPUs (one shard per context; the reference has no
  * multi-device training).  Each iteration every shard calls step with the current centroids and gets, for its own
  * rows, the per-centroid sums [k][dim], the per-centroid row counts [k] (as floats) and the sum of its rows'
@@ -373,6 +386,24 @@ int32_t vsk_ivf_search(vsk_index* index, const float* queries, int64_t nq, int32
                        int32_t nprobe, float* out_dist, int64_t* out_ids);
 int32_t vsk_ivf_search_dev(vsk_index* index, const float* queries, int64_t nq, int32_t k,
                            int32_t nprobe, float* out_dist, int64_t* out_ids);
+/* Metadata filter on the IVF path.  Replaces the `filter:` argument of IVFIndex.search
+ * (Indexes/IVFIndex.swift:128,162-165,564-570): the rows of the probed lists are filtered first, then ranked.
+ * vsk_ivf_set_masks gives every row of a built index a 64-bit mask, masks[i] for the i-th row in insertion order
+ * (n = vsk_index_size masks); a search keeps row r for query q iff (masks[r] & qmasks[q]) != 0.  qmasks NULL = no
+ * filter.  Results with fewer than k eligible rows in the probed lists are padded with id -1, distance +inf. */
+int32_t vsk_ivf_set_masks(vsk_index* index, const uint64_t* masks);
+int32_t vsk_ivf_set_masks_dev(vsk_index* index, const uint64_t* masks);
+int32_t vsk_ivf_search_filtered(vsk_index* index, const float* queries, int64_t nq, int32_t k, int32_t nprobe,
+                                const uint64_t* qmasks, float* out_dist, int64_t* out_ids);
+int32_t vsk_ivf_search_filtered_dev(vsk_index* index, const float* queries, int64_t nq, int32_t k, int32_t nprobe,
+                                    const uint64_t* qmasks, float* out_dist, int64_t* out_ids);
+/* Appends n rows to a built index: each goes to the list of its nearest centroid, behind the rows that list already
+ * holds, and gets the next insertion indices (vsk_index_size before the call, onward).  Replaces IVFIndex.insert
+ * (Indexes/IVFIndex.swift:80-122), which appends one entry at a time; here only the new rows are assigned, the
+ * stored rows are regrouped in one pass at copy speed, and nothing is re-trained.  masks: NULL, or one per new row
+ * when the index carries masks.  A host that inserts single entries should collect them and add them in blocks. */
+int32_t vsk_ivf_add(vsk_index* index, const float* rows, int64_t n, const uint64_t* masks);
+int32_t vsk_ivf_add_dev(vsk_index* index, const float* rows, int64_t n, const uint64_t* masks);
 
 /* --- int8 scalar quantiser -----------------------------------------------------------------
  * Replaces ScalarQuantizer.quantizeBatch for `.int8` (Quantization/ScalarQuantizer.swift:129-164):

@@ -67,6 +67,9 @@ class CpuOracle:
         L.vskref_assign.argtypes = [_f32p, C.c_int64, C.c_int, _f32p, C.c_int, _i32p, _f32p]
         L.vskref_ivf_search.argtypes = [_f32p, C.c_int64, _f32p, C.c_int64, C.c_int, _f32p, C.c_int, _i32p,
                                         C.c_int, C.c_int, _f32p, _i64p]
+        L.vskref_ivf_search_filtered.argtypes = [_f32p, C.c_int64, _f32p, C.c_int64, C.c_int, _f32p, C.c_int, _i32p,
+                                                 C.c_int, C.c_int, _u64p, _u64p, _f32p, _i64p]
+        L.vskref_kmeans_plusplus.argtypes = [_f32p, C.c_int64, C.c_int, C.c_int, C.c_uint64, _f32p, _i64p]
         L.vskref_sq8_train.argtypes = [_f32p, C.c_int64, C.c_int, C.c_int, _f32p, _f32p]
         L.vskref_sq8_encode.argtypes = [_f32p, C.c_int64, C.c_int, _f32p, _f32p, _i8p]
         L.vskref_sq8_decode.argtypes = [_i8p, C.c_int64, C.c_int, _f32p, _f32p, _f32p]
@@ -135,6 +138,26 @@ class CpuOracle:
                                    _ptr(centroids, _f32p), centroids.shape[0], _ptr(assign, _i32p), nprobe, k,
                                    _ptr(dist, _f32p), _ptr(ids, _i64p))
         return dist, ids
+
+    def ivf_search_filtered(self, q, x, centroids, assign, nprobe, k, row_masks, query_masks):
+        q, x, centroids = _f32(q), _f32(x), _f32(centroids)
+        assign = np.ascontiguousarray(assign, np.int32)
+        rm = np.ascontiguousarray(row_masks, np.uint64) if row_masks is not None else None
+        qm = np.ascontiguousarray(query_masks, np.uint64) if query_masks is not None else None
+        dist = np.empty((q.shape[0], k), np.float32)
+        ids = np.empty((q.shape[0], k), np.int64)
+        self.lib.vskref_ivf_search_filtered(_ptr(q, _f32p), q.shape[0], _ptr(x, _f32p), x.shape[0], x.shape[1],
+                                            _ptr(centroids, _f32p), centroids.shape[0], _ptr(assign, _i32p), nprobe, k,
+                                            _ptr(rm, _u64p), _ptr(qm, _u64p), _ptr(dist, _f32p), _ptr(ids, _i64p))
+        return dist, ids
+
+    def kmeans_plusplus(self, x, k, seed):
+        x = _f32(x)
+        cent = np.empty((k, x.shape[1]), np.float32)
+        picked = np.empty(k, np.int64)
+        self.lib.vskref_kmeans_plusplus(_ptr(x, _f32p), x.shape[0], x.shape[1], k, C.c_uint64(seed), _ptr(cent, _f32p),
+                                        _ptr(picked, _i64p))
+        return cent, picked
 
     def sq8_train(self, x, per_dim):
         x = _f32(x)

@@ -325,6 +325,103 @@ void vskref_ivf_search(const float* q, int64_t nq, const float* x, int64_t n, in
   }
 }
 
+// IVFIndex.search with a metadata filter (Indexes/IVFIndex.swift:128,162-172): the rows of the probed lists are
+// collected, the filter drops the ineligible ones (FilterEvaluator.filterVectors, :564-570), distances are computed
+// for what is left and sorted.  The filter here is the bitmask form: row r passes for query a iff
+// (row_masks[r] & query_masks[a]) != 0.
+void vskref_ivf_search_filtered(const float* q, int64_t nq, const float* x, int64_t n, int d,
+                                const float* centroids, int nlist, const int32_t* assign, int nprobe, int k,
+                                const uint64_t* row_masks, const uint64_t* query_masks,
+                                float* out_dist, int64_t* out_ids) {
+  std::vector<std::vector<int64_t>> lists((size_t)nlist);
+  for (int64_t r = 0; r < n; ++r) lists[assign[r]].push_back(r);
+#pragma omp parallel for schedule(dynamic, 4)
+  for (int64_t a = 0; a < nq; ++a) {
+    const float* qa = q + a * d;
+    std::vector<std::pair<float, int>> cd((size_t)nlist);
+    for (int c = 0; c < nlist; ++c)
+      cd[c] = {vskref_distance(VSKREF_EUCLIDEAN, qa, centroids + (size_t)c * d, d), c};
+    int np = std::min(nprobe, nlist);
+    std::partial_sort(cd.begin(), cd.begin() + np, cd.end());
+    std::vector<std::pair<float, int64_t>> cand;
+    for (int p = 0; p < np; ++p)
+      for (int64_t r : lists[cd[p].second]) {
+        if (row_masks && query_masks && (row_masks[r] & query_masks[a]) == 0) continue;   // filtered before distances
+        cand.emplace_back(vskref_distance(VSKREF_EUCLIDEAN, qa, x + r * d, d), r);
+      }
+    size_t kk = std::min<size_t>((size_t)k, cand.size());
+    std::partial_sort(cand.begin(), cand.begin() + kk, cand.end());
+    for (size_t j = 0; j < (size_t)k; ++j) {
+      out_dist[a * k + j] = j < kk ? cand[j].first : std::numeric_limits<float>::infinity();
+      out_ids[a * k + j] = j < kk ? cand[j].second : -1;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// k-means++ initialisation, Clustering/KMeansClustering.swift:209-260:
+//   first centroid  vectors[Int.random(in: 0..<n, using: SeedableRNG(seed))]
+//   then, k-1 times: distances[i] = min over the chosen centroids of the un-squared euclidean distance (:397-428,
+//                    a float sum in dimension order, sqrt); sumDistances = distances.reduce(0, +);
+//                    probabilities[i] = distances[i] * distances[i] / sumDistances   (squared over the sum of
+//                    UN-squared ones: they do not sum to one; kept as written);
+//                    weightedSample with Float.random(in: 0..<1, using: SeedableRNG(seed + centroids.count)):
+//                    the first index whose float running sum exceeds the draw, else the last index (:435-447).
+// SeedableRNG is the 64-bit LCG of :480-491.  Swift's standard library maps a generator's output to
+// Int.random(in: 0..<n) by multiply-high with rejection, and to Float.random(in: 0..<1) as 24 random bits * 2^-24
+// (stdlib/public/core/Integers.swift, FloatingPointRandom.swift); those two mappings are restated from the published
+// source of the standard library, which is not part of the reference tree: parity unpinned for them.
+// ---------------------------------------------------------------------------
+namespace {
+struct SwiftLcg {
+  uint64_t state;
+  uint64_t next() { state = state * 2862933555777941757ull + 3037000493ull; return state; }
+};
+uint64_t swift_int_below(SwiftLcg& g, uint64_t n) {
+  unsigned __int128 m = (unsigned __int128)g.next() * n;
+  if ((uint64_t)m < n) {
+    const uint64_t t = (0 - n) % n;
+    while ((uint64_t)m < t) m = (unsigned __int128)g.next() * n;
+  }
+  return (uint64_t)(m >> 64);
+}
+float swift_unit_float(SwiftLcg& g) { return (float)((uint32_t)g.next() & 0xffffffu) * 5.9604645e-8f; }
+}  // namespace
+
+void vskref_kmeans_plusplus(const float* x, int64_t n, int d, int k, uint64_t seed, float* centroids, int64_t* picked) {
+  SwiftLcg g0{seed};
+  std::vector<int64_t> chosen;
+  chosen.push_back((int64_t)swift_int_below(g0, (uint64_t)n));
+  std::vector<float> dist((size_t)n, std::numeric_limits<float>::infinity());
+  while ((int)chosen.size() < k) {
+    const float* c = x + chosen.back() * d;   // min over all chosen = running min with the newest
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < n; ++r) {
+      float s = 0.f;
+      for (int i = 0; i < d; ++i) {
+        const float diff = x[r * d + i] - c[i];
+        s += diff * diff;
+      }
+      dist[r] = std::min(dist[r], std::sqrt(s));
+    }
+    float sum = 0.f;
+    for (int64_t r = 0; r < n; ++r) sum += dist[r];
+    SwiftLcg g{seed + (uint64_t)chosen.size()};
+    const float u = swift_unit_float(g);
+    int64_t next = n - 1;
+    float cumulative = 0.f;
+    for (int64_t r = 0; r < n; ++r) {
+      cumulative += dist[r] * dist[r] / sum;
+      if (u < cumulative) { next = r; break; }
+    }
+    chosen.push_back(next);
+  }
+  for (int j = 0; j < k; ++j) {
+    std::memcpy(centroids + (size_t)j * d, x + chosen[j] * d, sizeof(float) * (size_t)d);
+    if (picked) picked[j] = chosen[j];
+  }
+}
+
 // ---------------------------------------------------------------------------
 // Scalar int8 quantiser, Quantization/ScalarQuantizer.swift:
 //   statistics  :389-418   min / max over the values

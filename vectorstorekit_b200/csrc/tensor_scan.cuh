@@ -35,7 +35,7 @@ int32_t tensor_coarse_values(Index* ix, const float* q, int64_t nq, int64_t rows
 // caller to re-run on the fp32 list scan.
 bool ivf_tensor_applicable(const Index* ix, int64_t nq, int32_t nprobe, int32_t k);
 int32_t ivf_tensor_search(Index* ix, const float* q, int64_t nq, const int64_t* probes, int32_t nprobe, int32_t k,
-                          float* out_dist, int64_t* out_ids, std::vector<int32_t>* flagged);
+                          const uint64_t* qmasks, float* out_dist, int64_t* out_ids, std::vector<int32_t>* flagged);
 // Drops the fp16 operand copy after rows were added; makes it (once per index state).
 void tensor_invalidate(Index* ix);
 int32_t tensor_prepare_index(Index* ix);

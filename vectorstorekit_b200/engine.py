@@ -20,6 +20,7 @@ Arrays may be numpy arrays (host memory: copied in and out by the library) or to
 from __future__ import annotations
 
 import ctypes as C
+import os
 import enum
 from typing import Optional, Sequence
 
@@ -482,6 +483,9 @@ def _adopt(dev: "CUDAComputeDevice", h):
     if cls is PQIndex:
         ix.segments, ix.codebookSize = info["pq_segments"], info["pq_codebook_size"]
     if cls is IVFIndex:
+        ix._has_masks = info["has_masks"]
+        ix._pending_rows, ix._pending_masks = [], []
+        ix.trainingSampleSize, ix.seed = 100_000, None
         ix.numberOfCentroids = info["nlist"]
         ix.numberOfProbes = min(10, info["nlist"])      # IVFConfiguration default (IVFConfiguration.swift:32)
         ix.clustering = KMeansClustering(dev)
@@ -592,16 +596,41 @@ class KMeansClustering:
     """``KMeansClustering.cluster`` (``Clustering/KMeansClustering.swift:48-113``) with ``.custom``
     initial centroids (:189-193).  Returns (centroids, assignments, iterations, inertia)."""
 
-    def __init__(self, dev: CUDAComputeDevice, maxIterations: int = 100, tolerance: float = 1e-4):
+    def __init__(self, dev: CUDAComputeDevice, maxIterations: int = 100, tolerance: float = 1e-4,
+                 seed: Optional[int] = None):
         self.dev = dev
         self._lib = dev._lib
         self.maxIterations = maxIterations
         self.tolerance = tolerance
+        self.seed = seed          # KMeansClusteringConfiguration.seed; None = drawn from the system, as SystemRNG is
 
-    def cluster(self, vectors, k: int, initialCentroids):
+    def initializeKMeansPlusPlus(self, vectors, k: int, seed: Optional[int] = None):
+        """``initializeKMeansPlusPlus`` (``KMeansClustering.swift:209-260``) -> (centroids, picked row indices)."""
+        n, d = vectors.shape
+        if seed is None:
+            seed = self.seed
+        if seed is None:
+            seed = int.from_bytes(os.urandom(8), "little")
+        picked = np.empty(k, np.int64)
+        if _is_dev(vectors):
+            x = vectors.contiguous().float()
+            cent = torch.empty((k, d), dtype=torch.float32, device=x.device)
+            self.dev.check(self._lib.vsk_kmeans_init_plusplus_dev(self.dev._h, _ptr(x), n, d, k, C.c_uint64(seed), _ptr(cent),
+                                                                  _ptr(picked)))
+        else:
+            x = _host(vectors, np.float32)
+            cent = np.empty((k, d), np.float32)
+            self.dev.check(self._lib.vsk_kmeans_init_plusplus(self.dev._h, _ptr(x), n, d, k, C.c_uint64(seed), _ptr(cent),
+                                                              _ptr(picked)))
+        return cent, picked
+
+    def cluster(self, vectors, k: int, initialCentroids=None):
+        """initialCentroids=None: k-means++ (the reference's default ``initMethod``); else ``.custom``."""
         if len(vectors) == 0:
             raise EmptyInput("emptyDataset")
         n, d = vectors.shape
+        if initialCentroids is None:
+            initialCentroids, _ = self.initializeKMeansPlusPlus(vectors, k)
         inertia = C.c_float()
         iters = C.c_int32()
         if _is_dev(vectors):
@@ -680,58 +709,126 @@ class KMeansTrainer:
 
 
 class IVFIndex(_IndexBase):
-    """``IVFIndex`` (``Indexes/IVFIndex.swift``): ``train(on:)`` runs k-means for the centroids,
-    ``insert`` assigns rows to their nearest centroid's list, ``search`` probes ``numberOfProbes``
-    lists (all of them for ``SearchStrategy.exact``) with rooted L2.  Rows are inserted in one
-    batch; ids are insertion indices."""
+    """``IVFIndex`` (``Indexes/IVFIndex.swift``): ``train(on:)`` runs k-means for the centroids, ``insert`` files rows
+    under their nearest centroid's list, ``search`` probes ``numberOfProbes`` lists (all of them for
+    ``SearchStrategy.exact``) with rooted L2, after the metadata filter when one is given.  Ids are insertion
+    indices.  The first ``insert`` builds the lists; later ones append to them (``vsk_ivf_add``) without touching the
+    assignment of the rows already stored.  ``insertEntry`` is the reference's one-entry ``insert``: entries are
+    collected on the host and appended as one block before the next search."""
 
     def __init__(self, dev: CUDAComputeDevice, dimensions: int, numberOfCentroids: int = 1024,
-                 numberOfProbes: int = 10, maxIterations: int = 100, tolerance: float = 1e-4):
+                 numberOfProbes: int = 10, maxIterations: int = 100, tolerance: float = 1e-4,
+                 trainingSampleSize: int = 100_000, seed: Optional[int] = None):
         super().__init__(dev)
-        if dimensions <= 0 or numberOfCentroids <= 0 or not (0 < numberOfProbes <= numberOfCentroids):
+        if dimensions <= 0 or numberOfCentroids <= 0 or not (0 < numberOfProbes <= numberOfCentroids) \
+                or trainingSampleSize < numberOfCentroids:
             raise InvalidInput("IVFConfiguration.validate failed")  # IVFConfiguration.swift:49-59
         self.dimensions = dimensions
         self.numberOfCentroids = numberOfCentroids
         self.numberOfProbes = numberOfProbes
-        self.clustering = KMeansClustering(dev, maxIterations, tolerance)
+        self.trainingSampleSize = trainingSampleSize            # IVFConfiguration.swift:12,33
+        self.seed = seed
+        self.clustering = KMeansClustering(dev, maxIterations, tolerance, seed=seed)
         self.centroids = None
         self.trained = False
+        self._has_masks = False
+        self._pending_rows, self._pending_masks = [], []
 
     def train(self, samples, initialCentroids=None):
+        """``train(on:)`` (``IVFIndex.swift:397-446``).  initialCentroids=None is the reference's default
+        initialisation, k-means++ (``KMeansClustering.swift:209-260``), seeded by ``seed``."""
         if len(samples) < self.numberOfCentroids:
             raise InsufficientTrainingData(f"provided {len(samples)}, required {self.numberOfCentroids}")
-        if initialCentroids is None:
-            initialCentroids = samples[: self.numberOfCentroids]
         self.centroids, _, iters, inertia = self.clustering.cluster(samples, self.numberOfCentroids, initialCentroids)
         self.trained = True
         self.close()
+        self._has_masks = False
+        self._pending_rows, self._pending_masks = [], []
         return iters, inertia
 
-    def insert(self, rows):
+    def trainOnSample(self, allVectors, initialCentroids=None):
+        """What ``optimize`` / re-training do with a large store (``IVFIndex.swift:462-468``): train on
+        ``trainingSampleSize`` rows drawn without replacement (seeded permutation) when there are more."""
+        n = len(allVectors)
+        if n > self.trainingSampleSize:
+            rng = np.random.default_rng(self.seed)
+            pick = np.sort(rng.permutation(n)[: self.trainingSampleSize])
+            if _is_dev(allVectors):
+                allVectors = allVectors[torch.as_tensor(pick, device=allVectors.device)]
+            else:
+                allVectors = np.asarray(allVectors)[pick]
+        return self.train(allVectors, initialCentroids)
+
+    def insert(self, rows, masks=None):
+        """A block of rows (and their filter masks); ids continue from ``count``."""
         if not self.trained:
             raise NotTrained("Index must be trained before use")
-        self.close()
-        h = C.c_void_p()
         n, d = rows.shape
-        if _is_dev(rows):
+        if d != self.dimensions:
+            raise DimensionMismatch(f"expected {self.dimensions}, got {d}")
+        self._flush()
+        on_dev = _is_dev(rows)
+        if on_dev:
             r = rows.contiguous().float()
+            m = masks.contiguous() if masks is not None else None
+        else:
+            r = _host(rows, np.float32)
+            m = _host(masks, np.uint64) if masks is not None else None
+        if self._h:   # append to the lists
+            fn = self._lib.vsk_ivf_add_dev if on_dev else self._lib.vsk_ivf_add
+            self.dev.check(fn(self._h, _ptr(r), n, _ptr(m)))
+            return
+        h = C.c_void_p()
+        if on_dev:
             c = self.centroids if _is_dev(self.centroids) else torch.as_tensor(self.centroids, device=r.device)
             self.dev.check(self._lib.vsk_ivf_build_dev(self.dev._h, _ptr(c.contiguous()), self.numberOfCentroids,
                                                        _ptr(r), n, d, C.byref(h)))
         else:
-            r = _host(rows, np.float32)
             c = _host(self.centroids, np.float32)
             self.dev.check(self._lib.vsk_ivf_build(self.dev._h, _ptr(c), self.numberOfCentroids, _ptr(r), n, d,
                                                    C.byref(h)))
         self._h = h
+        if m is not None:
+            fn = self._lib.vsk_ivf_set_masks_dev if on_dev else self._lib.vsk_ivf_set_masks
+            self.dev.check(fn(self._h, _ptr(m)))
+            self._has_masks = True
+
+    def insertEntry(self, vector, mask: Optional[int] = None) -> int:
+        """``insert(_ entry:)`` (``IVFIndex.swift:80-122``): one vector; returns its id."""
+        if not self.trained:
+            raise NotTrained("Index must be trained before use")
+        v = _host(vector, np.float32).reshape(-1)
+        if v.size != self.dimensions:
+            raise DimensionMismatch(f"expected {self.dimensions}, got {v.size}")
+        self._pending_rows.append(v)
+        self._pending_masks.append(mask)
+        return self.count - 1
+
+    def _flush(self):
+        if not self._pending_rows:
+            return
+        rows = np.stack(self._pending_rows)
+        masks = None
+        if any(m is not None for m in self._pending_masks):
+            masks = np.array([0 if m is None else m for m in self._pending_masks], np.uint64)
+        self._pending_rows, self._pending_masks = [], []
+        self.insert(rows, masks)
+
+    @property
+    def count(self) -> int:
+        return (int(self._lib.vsk_index_size(self._h)) if self._h else 0) + len(self._pending_rows)
 
     def assignments(self):
+        self._flush()
         out = np.empty(self.count, np.int32)
         self.dev.check(self._lib.vsk_ivf_assignments(self._h, _ptr(out)))
         return out
 
-    def batchSearch(self, queries, k: int, strategy: SearchStrategy = SearchStrategy.adaptive):
-        if not self.trained or not self._h:
+    def batchSearch(self, queries, k: int, strategy: SearchStrategy = SearchStrategy.adaptive, filter_masks=None):
+        if not self.trained:
+            raise NotTrained("Index must be trained before use")
+        self._flush()
+        if not self._h:
             raise NotTrained("Index must be trained before use")
         nprobe = self.numberOfCentroids if strategy == SearchStrategy.exact else self.numberOfProbes
         nq = queries.shape[0]
@@ -739,16 +836,21 @@ class IVFIndex(_IndexBase):
             q = queries.contiguous().float()
             od = torch.empty((nq, k), dtype=torch.float32, device=q.device)
             oi = torch.empty((nq, k), dtype=torch.int64, device=q.device)
-            self.dev.check(self._lib.vsk_ivf_search_dev(self._h, _ptr(q), nq, k, nprobe, _ptr(od), _ptr(oi)))
+            qm = filter_masks.contiguous() if filter_masks is not None else None
+            self.dev.check(self._lib.vsk_ivf_search_filtered_dev(self._h, _ptr(q), nq, k, nprobe, _ptr(qm), _ptr(od), _ptr(oi)))
             return od, oi
         q = _host(queries, np.float32)
         od = np.empty((nq, k), np.float32)
         oi = np.empty((nq, k), np.int64)
-        self.dev.check(self._lib.vsk_ivf_search(self._h, _ptr(q), nq, k, nprobe, _ptr(od), _ptr(oi)))
+        qm = _host(filter_masks, np.uint64) if filter_masks is not None else None
+        self.dev.check(self._lib.vsk_ivf_search_filtered(self._h, _ptr(q), nq, k, nprobe, _ptr(qm), _ptr(od), _ptr(oi)))
         return od, oi
 
-    def search(self, query, k: int, strategy: SearchStrategy = SearchStrategy.adaptive):
-        d, i = self.batchSearch(query.reshape(1, -1), k, strategy)
+    def search(self, query, k: int, strategy: SearchStrategy = SearchStrategy.adaptive, filter_mask: Optional[int] = None):
+        fm = None if filter_mask is None else np.array([filter_mask], np.uint64)
+        if fm is not None and _is_dev(query):
+            fm = torch.as_tensor(fm.view(np.int64), device=query.device)
+        d, i = self.batchSearch(query.reshape(1, -1), k, strategy, fm)
         return d[0], i[0]
 
 
