@@ -135,7 +135,12 @@ typedef struct vsk_tuning {
                                    two halves on two streams (one half's selection, re-scoring and exchange under
                                    the other's contraction).  Off by default: on one power-capped GPU the two
                                    halves were measured to slow each other down by what the overlap gains. */
-  int32_t reserved[10];
+  int32_t wait_limit_log2;      /* 0 = default (23): a pipeline wait inside the contraction kernel gives up after
+                                   2^this polls (tens of nanoseconds each) and the call returns VSK_ERR_TIMEOUT,
+                                   the counterpart of commandBufferTimeout (Acceleration/Metal/MetalErrors.swift:30) */
+  int32_t test_stall_scan;      /* testing only: 1 makes the next contraction launch leave one operand stage
+                                   unfilled, so that a bounded wait runs out; resets itself to 0 */
+  int32_t reserved[8];
 } vsk_tuning;
 
 /* --- context ------------------------------------------------------------------------------

@@ -32,11 +32,19 @@ _u8p = C.POINTER(C.c_uint8)
 _u32p = C.POINTER(C.c_uint32)
 
 
+def reference_tree():
+    """The reference checkout, if this machine has one: $VSK_REFERENCE_TREE, else a folder named `reference` beside the
+    repository.  Only the build of the shader checker reads it."""
+    cand = os.environ.get("VSK_REFERENCE_TREE") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+    return cand if os.path.isdir(os.path.join(cand, "Sources", "VectorStoreKit")) else None
+
+
 def build(native: bool = False) -> None:
     """Run the Makefile (compiles cpu_ref.cpp; compiles the reference shaders when the
     reference checkout is present)."""
-    subprocess.run(["make", "-C", _HERE, "all"] + (["native"] if native else []), check=True,
-                   stdout=subprocess.DEVNULL)
+    ref = reference_tree()
+    subprocess.run(["make", "-C", _HERE, "all"] + (["native"] if native else []) + ([f"REF={ref}"] if ref else []),
+                   check=True, stdout=subprocess.DEVNULL)
 
 
 def _f32(a):

@@ -505,6 +505,33 @@ def test_selective_filters_take_the_row_list_path(vsk, cpu_oracle):
         dev.close()
 
 
+def test_bounded_wait_expiry_returns_timeout_and_the_context_survives(vsk, cpu_oracle):
+    """The contraction kernel's pipeline waits are bounded.  The testing switch makes CTA 0 leave one operand stage
+    unfilled: the consumer's wait for it runs out (a short limit is set so that this takes milliseconds), every role
+    leaves its loop, copies in flight are drained, tensor memory is released and the call returns the counterpart of
+    commandBufferTimeout (MetalErrors.swift:30) - no trap, no fault.  The next search on the same context is exact."""
+    dev = vsk.CUDAComputeDevice(0)
+    try:
+        rng = np.random.default_rng(404)
+        x = rng.standard_normal((20_000, 128)).astype(np.float32)
+        q = rng.standard_normal((300, 128)).astype(np.float32)
+        ix = vsk.FlatIndex(dev, 128, "cosine")
+        ix.add(x)
+        d0, i0 = ix.batchSearch(q, 10)
+        dev.set_tuning(wait_limit_log2=16, test_stall_scan=1)
+        with pytest.raises(vsk.Timeout):
+            ix.batchSearch(q, 10)
+        assert dev.tuning()["test_stall_scan"] == 0          # one shot
+        dev.set_tuning(wait_limit_log2=0)
+        d1, i1 = ix.batchSearch(q, 10)
+        assert np.array_equal(i1, i0) and np.array_equal(d1, d0)
+        rd, ri = cpu_oracle.flat_search(oracle.COSINE, q, x, 10)
+        assert_topk_parity(d1, i1, rd, ri)
+        ix.close()
+    finally:
+        dev.close()
+
+
 def test_distance_matrix_api(vsk, dev, cpu_oracle):
     """MetalDistanceMatrix.computeDistanceMatrix (MetalDistanceMatrix.swift:49-119): A x B, and A x A with the
     lower triangle mirrored from the upper one."""

@@ -144,3 +144,66 @@ def test_two_rank_sharded_kmeans_equals_unsharded():
         p.join(120)
     assert all(p.exitcode == 0 for p in procs)
     assert ret.get(0) is True and ret.get(1) is True
+
+
+def _leaving_worker(rank, world, port, ret):
+    """Three ranks run sharded searches; after the first step rank 2 leaves (between steps: none of its collectives is
+    in flight).  The others must get an error from their next exchange within the group's timeout instead of waiting
+    for ever, and the failed call must leave them able to report it."""
+    import datetime
+    import time
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
+    import oracle
+    from vectorstorekit_b200.sharded import ShardedSearch, shard_range
+    o = oracle.CpuOracle()
+    rng = np.random.default_rng(8)
+    x = rng.standard_normal((600, 8)).astype(np.float32)
+    q = rng.standard_normal((9, 8)).astype(np.float32)
+    lo, hi = shard_range(len(x), rank, world)
+
+    def local(queries, k):
+        d, i = o.flat_search(oracle.EUCLIDEAN, queries.numpy(), x[lo:hi], k)
+        return torch.from_numpy(d), torch.from_numpy(np.where(i >= 0, i + lo, -1))
+
+    def merge(gd, gi):
+        d, i = o.merge_topk(gd.numpy(), gi.numpy())
+        return torch.from_numpy(d), torch.from_numpy(i)
+
+    s = ShardedSearch(local, merge)
+    d, i = s.batchSearch(torch.from_numpy(q), 4)          # step 1: everybody is here
+    rd, ri = o.flat_search(oracle.EUCLIDEAN, q, x, 4)
+    first_ok = np.array_equal(i.numpy(), ri)
+    if rank == world - 1:
+        ret[rank] = ("left", first_ok)
+        os._exit(0)                                       # leaves without a word; the host-side failure of the test
+    t0 = time.time()
+    try:
+        s.batchSearch(torch.from_numpy(q), 4)             # step 2: one rank is gone
+        ret[rank] = ("no error", first_ok, time.time() - t0)
+    except Exception as e:                                # gloo: connection closed by peer / timed out
+        ret[rank] = ("error", first_ok, time.time() - t0, type(e).__name__)
+    os._exit(0)                                           # the group is broken: no barrier, no clean shutdown
+
+
+def test_a_rank_that_leaves_between_steps_fails_the_others_quickly():
+    world = 3
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    port = 29700 + os.getpid() % 200
+    procs = [ctx.Process(target=_leaving_worker, args=(r, world, port, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(90)
+    for p in procs:
+        if p.is_alive():
+            p.kill()
+            pytest.fail("a rank was still blocked after 90 s")
+    assert ret.get(world - 1) == ("left", True)
+    for r in range(world - 1):
+        state = ret.get(r)
+        assert state is not None and state[0] == "error" and state[1] is True, state
+        assert state[2] < 60, state

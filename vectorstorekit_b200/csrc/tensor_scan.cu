@@ -105,6 +105,11 @@ struct TcArgs {
   // Filter (HAS_MASK kernels): operand row r may be appended for query q iff (row_masks[r] & q_masks[q]) != 0.
   const uint64_t* row_masks;  // [rows of the row operand]
   const uint64_t* q_masks;    // [nq] by list position
+  // Bounded waits: polls before a wait gives up (0 = WAIT_LIMIT).  stall_kblock >= 0 (testing only): the producer of
+  // CTA 0 leaves out the copies of that k-block of its first tile, so that the consumer's wait for them runs out and
+  // the time-out path (error word, abort flag, drain, tensor-memory release, VSK_ERR_TIMEOUT) can be exercised.
+  uint32_t wait_limit;
+  int32_t stall_kblock;
 };
 
 // ---- PTX wrappers --------------------------------------------------------------------------
@@ -132,8 +137,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 // Bounded wait.  Returns false (and raises the abort flag and the error word) when the limit runs out
 // or another role has already aborted.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int32_t* err, int code) {
-  for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int32_t* err, int code,
+                                          uint32_t limit) {
+  for (uint32_t it = 0; it < limit; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if (it > 64) {
       if ((it & 63) == 0 && *abort_flag) return false;
@@ -214,6 +220,7 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   const int64_t unit = blockIdx.x;
   const int64_t units = gridDim.x;
   constexpr int QT = TM;  // queries per tile
+  const uint32_t wait_limit = a.wait_limit ? a.wait_limit : WAIT_LIMIT;
 
   const int64_t qtiles = (a.nq + QT - 1) / QT;
   const int64_t ntiles = (a.row_end - a.row_begin + TN - 1) / TN;
@@ -286,20 +293,24 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         const int32_t qrow = a.tiles ? entry.x : (int32_t)(qt * QT);
         const int32_t xrow = a.tiles ? entry.y : (int32_t)(a.row_begin + nt * TN);
         for (int kb = 0; kb < a.kblocks; ++kb) {
-          if (!mbar_wait(&sm->empty[s], ph ^ 1, &sm->abort_flag, a.err, 1)) { ok = false; break; }
+          if (!mbar_wait(&sm->empty[s], ph ^ 1, &sm->abort_flag, a.err, 1, wait_limit)) { ok = false; break; }
           uint8_t* st = sm->ring + s * STAGE_BYTES;
-          mbar_expect_tx(&sm->full[s], STAGE_BYTES);
-          tma_load_2d(st, &map_q, &sm->full[s], kb * TK, qrow);
-          tma_load_2d(st + A_BYTES, &map_x, &sm->full[s], kb * TK, xrow);
-          issued |= 1u << s;
-          issued_ph = (issued_ph & ~(1u << s)) | (ph << s);
+          if (a.stall_kblock >= 0 && unit == 0 && i == 0 && kb == a.stall_kblock) {
+            // testing only: this stage is never filled, the consumer's bounded wait for it runs out
+          } else {
+            mbar_expect_tx(&sm->full[s], STAGE_BYTES);
+            tma_load_2d(st, &map_q, &sm->full[s], kb * TK, qrow);
+            tma_load_2d(st + A_BYTES, &map_x, &sm->full[s], kb * TK, xrow);
+            issued |= 1u << s;
+            issued_ph = (issued_ph & ~(1u << s)) | (ph << s);
+          }
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
       }
       // copies still in flight must land before the CTA's shared memory is released
       for (int i = 0; i < STAGES; ++i)
         if (issued & (1u << i)) {
-          for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
+          for (uint32_t it = 0; it < wait_limit; ++it) {
             if (mbar_try_wait(&sm->full[i], (issued_ph >> i) & 1)) break;
             __nanosleep(64);
           }
@@ -317,11 +328,11 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         if (!ok || !tile_at(local, qt_unused, nt_unused)) break;
         const int acc = (int)(local & 1);
         const uint32_t aph = (uint32_t)((local >> 1) & 1);
-        if (!mbar_wait(&sm->tmem_empty[acc], aph ^ 1, &sm->abort_flag, a.err, 2)) { ok = false; break; }
+        if (!mbar_wait(&sm->tmem_empty[acc], aph ^ 1, &sm->abort_flag, a.err, 2, wait_limit)) { ok = false; break; }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + (uint32_t)(acc * TN);
         for (int kb = 0; kb < a.kblocks; ++kb) {
-          if (!mbar_wait(&sm->full[s], ph, &sm->abort_flag, a.err, 3)) { ok = false; break; }
+          if (!mbar_wait(&sm->full[s], ph, &sm->abort_flag, a.err, 3, wait_limit)) { ok = false; break; }
           tc_fence_after();
           const uint64_t adesc = make_desc(smem_u32(sm->ring + s * STAGE_BYTES));
           const uint64_t bdesc = make_desc(smem_u32(sm->ring + s * STAGE_BYTES + A_BYTES));
@@ -337,7 +348,7 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       }
       // all issued MMAs must retire before tensor memory is freed
       tc_commit(&sm->drain);
-      for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
+      for (uint32_t it = 0; it < wait_limit; ++it) {
         if (mbar_try_wait(&sm->drain, 0)) break;
         __nanosleep(64);
       }
@@ -426,7 +437,7 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       uint64_t qm = 0ull;   // this query's filter mask: a row is eligible iff (row mask & qm) != 0
       if (HAS_MASK && qok) qm = __ldg(a.q_masks + q);
       // every lane of the warp must take part in the wait result
-      bool got = mbar_wait(&sm->tmem_full[acc], aph, &sm->abort_flag, a.err, 4);
+      bool got = mbar_wait(&sm->tmem_full[acc], aph, &sm->abort_flag, a.err, 4, wait_limit);
       got = __all_sync(0xffffffffu, got);
       if (!got) { ok = false; break; }
       tc_fence_after();
@@ -1112,8 +1123,15 @@ int32_t launch_tc_ew(Ctx* ctx, const CUtensorMap& mq, const CUtensorMap& mx, con
   if (tiles <= 0) return VSK_OK;
   const int sms = ctx->prop.multiProcessorCount;
   const unsigned grid = (unsigned)std::min<int64_t>(tiles, sms);
+  TcArgs la = a;
+  la.wait_limit = ctx->tuning.wait_limit_log2 > 0 ? (1u << std::min(ctx->tuning.wait_limit_log2, 30)) : 0u;
+  la.stall_kblock = -1;
+  if (ctx->tuning.test_stall_scan > 0) {   // testing only, one shot
+    la.stall_kblock = 0;
+    ctx->tuning.test_stall_scan = 0;
+  }
   prof_begin(ctx);
-  kern<<<grid, Epi<EW>::THREADS, smem, ctx->stream>>>(mq, mx, a);
+  kern<<<grid, Epi<EW>::THREADS, smem, ctx->stream>>>(mq, mx, la);
   prof_end(ctx);
   tl_mark(ctx, MODE == SCAN_DENSE ? "scan_dense" : (MODE == SCAN_ARGMIN ? "scan_argmin" : "scan"));
   ctx->stats.kernel_launches++;
