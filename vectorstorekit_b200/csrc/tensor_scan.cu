@@ -34,15 +34,12 @@
 
 #include "common.cuh"
 #include "tensor_scan.cuh"
+#include "tc_ptx.cuh"
 
 namespace vsk {
 namespace {
 
-constexpr int TM = 128;        // queries per tile (UMMA M)
-constexpr int TN = 256;        // rows per tile (UMMA N)
-constexpr int TK = 64;         // fp16 elements per k-block (128 bytes: one swizzle atom)
-constexpr int A_BYTES = TM * TK * 2;   // 16 KB: 128 query rows x 64 fp16
-constexpr int B_BYTES = TN * TK * 2;   // 32 KB: 256 database rows x 64 fp16
+using namespace tc;   // tile geometry and the tcgen05 / TMA / mbarrier wrappers (tc_ptx.cuh)
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int STAGES = 4;              // operand ring: 4 stages of 48 KB
 constexpr int RING_BYTES = STAGES * STAGE_BYTES;
@@ -60,8 +57,6 @@ template <int EW> struct Epi {
   static constexpr int GROUPS = COLS / 32;
   static constexpr int THREADS = 64 + 32 * EW;
 };
-constexpr uint32_t WAIT_LIMIT = 1u << 23;
-constexpr int TMEM_COLS = 512;
 
 template <int EW>
 struct TcSmemT {
@@ -112,102 +107,6 @@ struct TcArgs {
   int32_t stall_kblock;
 };
 
-// ---- PTX wrappers --------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait.  Returns false (and raises the abort flag and the error word) when the limit runs out
-// or another role has already aborted.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int32_t* err, int code,
-                                          uint32_t limit) {
-  for (uint32_t it = 0; it < limit; ++it) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (it > 64) {
-      if ((it & 63) == 0 && *abort_flag) return false;
-      __nanosleep(64);
-    }
-  }
-  *abort_flag = 1;
-  atomicCAS(err, 0, code);
-  return false;
-}
-
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int32_t c0, int32_t c1) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
-          smem_u32(dst)),
-      "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
-      : "memory");
-}
-
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void tc_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-
-// D[tmem] (+)= A[smem desc] * B[smem desc]; M = 128, N = 256, K = 16, fp16 x fp16 -> fp32
-__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
-      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-
-// 32 consecutive fp32 columns of this thread's tensor-memory lane
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32]) {
-  uint32_t r[32];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-}
-
-// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 fp16), 128-byte
-// swizzled, rows packed: 8-row groups 1024 bytes apart.
-__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((smem_addr >> 4) & 0x3fff);  // start address, 16-byte units
-  d |= (uint64_t)1 << 16;                      // leading-dimension byte offset (unused with swizzle): 1
-  d |= (uint64_t)(1024 >> 4) << 32;            // stride between 8-row groups: 1024 bytes
-  d |= (uint64_t)1 << 46;                      // descriptor version of this architecture
-  d |= (uint64_t)2 << 61;                      // 128-byte swizzle
-  return d;
-}
-
-// Instruction descriptor: fp32 accumulate, fp16 A and B, both K-major, N = 256, M = 128.
-constexpr uint32_t kIdesc = (1u << 4) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(TM >> 4) << 24);
 
 template <int MODE, bool HAS_BETA, bool HAS_MASK, int EW>
 __global__ void __launch_bounds__(Epi<EW>::THREADS, 1)
@@ -636,6 +535,328 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   }
 }
 
+// ---- nearest-centroid assignment with a STATIONARY centroid block ---------------------------------------
+// k-means assignment is a contraction of 10^7 data rows against a few thousand centroids with a short inner
+// dimension (d = 128: two or three 64-wide k-blocks).  In the general kernel every 128 x 256 tile re-fetches both
+// operands from L2 - 96 KB for 8 Mflop - and at that ratio the L2 -> shared-memory fill, not the tensor pipe, sets the
+// pace (measured: 1.44 us per tile against 0.53 us of MMAs).  Here a CTA keeps one block of 256 centroids (all its
+// k-blocks, up to 128 KB) resident in shared memory and streams 128-row data tiles past it: 16 KB per k-block and
+// tile, a third of the traffic (a sixth with the row term folded in), so the MMAs set the pace again.
+//   grid      blocks of 256 centroids x groups of CTAs; CTA (b, g) holds centroid block b and takes data tiles
+//             g, g + groups, ...  (more blocks than SMs: a CTA takes several blocks in turn)
+//   warp 0    TMA producer: the centroid block once, then the data tiles through a ring of 16 KB stages
+//   warp 1    tcgen05.mma issuer: per data tile and k-block one M128 N256 K16 x 4 against the resident block
+//   warps 2.. epilogue (16 warps): the centroid's |c|^2 / 2 rides inside the contraction (fold columns), so a value
+//             is alpha * accumulator and the test for "no hit in these 32 columns" is one max per value.
+//             Threshold mode: a hit (rare: the threshold is the row's previous assignment plus the error band)
+//             is appended to the row's short list with an atomic slot; arg-min mode (first iteration): one
+//             atomicMin per row, centroid block and column part.
+// Every mbarrier wait is bounded like the general kernel's.
+constexpr int AS_EW = 16;
+constexpr int AS_THREADS = 64 + 32 * AS_EW;
+constexpr int AS_MAX_KB = 4;                       // k-blocks of the resident block (d + 48 fold columns <= 256)
+constexpr int AS_RING_BYTES = 192 * 1024;          // resident block + data-tile stages
+constexpr int AS_MAX_STAGES = 8;
+
+struct AsSmem {
+  uint8_t ring[AS_RING_BYTES];   // [kblocks x 32 KB centroid block][stages x 16 KB data k-blocks]
+  uint64_t a_full[AS_MAX_STAGES];
+  uint64_t a_empty[AS_MAX_STAGES];
+  uint64_t b_full, b_empty;
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint64_t drain;
+  uint32_t tmem_base;
+  volatile int abort_flag;
+  int log_n;                     // hits this CTA has logged so far
+};
+constexpr size_t kAsSmemBytes = sizeof(AsSmem) + 1024;
+
+struct AsArgs {
+  int64_t n;                  // data rows
+  int32_t k;                  // centroids
+  int32_t kblocks;            // dim16 / 64, <= AS_MAX_KB
+  int32_t groups;             // CTAs per centroid block (1 when there are more blocks than CTAs)
+  const float* alpha;         // value = alpha * accumulator = |c|^2 - 2 x.c
+  const float* thr;           // [n] SCAN_THRESHOLD: a centroid is listed for a row iff value <= thr[row]
+  // SCAN_THRESHOLD: every hit is logged as {row, centroid} in this CTA's own stretch of the log; the slot comes from a
+  // shared-memory counter, so an append never waits for a round trip to L2 (with 32 rows x 64 columns per warp and
+  // step, half of the steps hold a hit somewhere: a global atomic per hit made the epilogue wait out its latency)
+  uint2* log;                 // [gridDim.x][log_cap]
+  int32_t* log_count;         // [gridDim.x] entries written (capped); a CTA that ran out of room raises err = 9
+  int64_t log_cap;            // entries per CTA = log_total / gridDim.x (set at launch)
+  int64_t log_total;
+  unsigned long long* best;   // [n] SCAN_ARGMIN: smallest (value, centroid) key, pre-set to all ones
+  int32_t* err;
+  uint32_t wait_limit;
+};
+
+template <int MODE>
+__global__ void __launch_bounds__(AS_THREADS, 1)
+assign_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_c, AsArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  AsSmem* sm = reinterpret_cast<AsSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t wait_limit = a.wait_limit ? a.wait_limit : WAIT_LIMIT;
+  const int nb = (a.k + TN - 1) / TN;                       // centroid blocks
+  const int64_t qtiles = (a.n + TM - 1) / TM;               // data tiles
+  const int bres_bytes = a.kblocks * B_BYTES;
+  const int stages = min(AS_MAX_STAGES, (AS_RING_BYTES - bres_bytes) / A_BYTES);
+  // this CTA's centroid blocks and its share of the data tiles
+  const bool one_block = a.groups >= 1 && nb <= (int)gridDim.x;
+  const int b_first = one_block ? (int)(blockIdx.x % nb) : (int)blockIdx.x;
+  const int b_step = one_block ? (1 << 30) : (int)gridDim.x;
+  const int64_t t_first = one_block ? (int64_t)(blockIdx.x / nb) : 0;
+  const int64_t t_step = one_block ? a.groups : 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < AS_MAX_STAGES; ++s) {
+      mbar_init(&sm->a_full[s], 1);
+      mbar_init(&sm->a_empty[s], 1);
+    }
+    mbar_init(&sm->b_full, 1);
+    mbar_init(&sm->b_empty, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&sm->tmem_full[b], 1);
+      mbar_init(&sm->tmem_empty[b], AS_EW);
+    }
+    mbar_init(&sm->drain, 1);
+    sm->abort_flag = 0;
+    sm->log_n = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm->tmem_base)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = sm->tmem_base;
+  uint8_t* a_ring = sm->ring + bres_bytes;
+  uint2* my_log = MODE == SCAN_THRESHOLD ? a.log + (int64_t)blockIdx.x * a.log_cap : nullptr;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0, bph = 0;
+      uint32_t issued = 0, issued_ph = 0;
+      bool b_issued = false;
+      uint32_t b_issued_ph = 0;
+      bool ok = true;
+      for (int b = b_first; ok && b < nb; b += b_step) {
+        // the resident block may be replaced once every MMA that read the previous one has retired
+        if (!mbar_wait(&sm->b_empty, bph ^ 1, &sm->abort_flag, a.err, 5, wait_limit)) { ok = false; break; }
+        mbar_expect_tx(&sm->b_full, (uint32_t)bres_bytes);
+        for (int kb = 0; kb < a.kblocks; ++kb) tma_load_2d(sm->ring + kb * B_BYTES, &map_c, &sm->b_full, kb * TK, b * TN);
+        b_issued = true;
+        b_issued_ph = bph;
+        bph ^= 1;
+        for (int64_t t = t_first; ok && t < qtiles; t += t_step) {
+          for (int kb = 0; kb < a.kblocks; ++kb) {
+            if (!mbar_wait(&sm->a_empty[s], ph ^ 1, &sm->abort_flag, a.err, 1, wait_limit)) { ok = false; break; }
+            mbar_expect_tx(&sm->a_full[s], A_BYTES);
+            tma_load_2d(a_ring + s * A_BYTES, &map_x, &sm->a_full[s], kb * TK, (int32_t)(t * TM));
+            issued |= 1u << s;
+            issued_ph = (issued_ph & ~(1u << s)) | (ph << s);
+            if (++s == stages) { s = 0; ph ^= 1; }
+          }
+        }
+      }
+      // copies still in flight must land before the CTA's shared memory is released
+      if (b_issued)
+        for (uint32_t it = 0; it < wait_limit; ++it) {
+          if (mbar_try_wait(&sm->b_full, b_issued_ph)) break;
+          __nanosleep(64);
+        }
+      for (int i = 0; i < stages; ++i)
+        if (issued & (1u << i))
+          for (uint32_t it = 0; it < wait_limit; ++it) {
+            if (mbar_try_wait(&sm->a_full[i], (issued_ph >> i) & 1)) break;
+            __nanosleep(64);
+          }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0, bph = 0;
+      int64_t local = 0;
+      bool ok = true;
+      for (int b = b_first; ok && b < nb; b += b_step) {
+        if (!mbar_wait(&sm->b_full, bph, &sm->abort_flag, a.err, 6, wait_limit)) { ok = false; break; }
+        bph ^= 1;
+        tc_fence_after();
+        for (int64_t t = t_first; ok && t < qtiles; t += t_step, ++local) {
+          const int acc = (int)(local & 1);
+          const uint32_t aph = (uint32_t)((local >> 1) & 1);
+          if (!mbar_wait(&sm->tmem_empty[acc], aph ^ 1, &sm->abort_flag, a.err, 2, wait_limit)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t tmem_d = tmem_base + (uint32_t)(acc * TN);
+          for (int kb = 0; kb < a.kblocks; ++kb) {
+            if (!mbar_wait(&sm->a_full[s], ph, &sm->abort_flag, a.err, 3, wait_limit)) { ok = false; break; }
+            tc_fence_after();
+            const uint64_t adesc = make_desc(smem_u32(a_ring + s * A_BYTES));
+            const uint64_t bdesc = make_desc(smem_u32(sm->ring + kb * B_BYTES));
+#pragma unroll
+            for (int k4 = 0; k4 < TK / 16; ++k4)
+              tc_mma(tmem_d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), kIdesc, (kb | k4) ? 1u : 0u);
+            tc_commit(&sm->a_empty[s]);
+            if (++s == stages) { s = 0; ph ^= 1; }
+          }
+          if (ok) tc_commit(&sm->tmem_full[acc]);
+        }
+        if (ok) tc_commit(&sm->b_empty);   // arrives when every MMA issued so far (all readers of this block) has retired
+      }
+      tc_commit(&sm->drain);
+      for (uint32_t it = 0; it < wait_limit; ++it) {
+        if (mbar_try_wait(&sm->drain, 0)) break;
+        __nanosleep(64);
+      }
+    }
+  } else {
+    // ---------------- epilogue: one data row per thread, a quarter of the block's columns per warp ----------------
+    constexpr int PARTS = AS_EW / 4, GROUPS = TN / PARTS / 32;
+    const int quarter = warp & 3;
+    const int et = quarter * 32 + lane;
+    const int ew = warp - 2;
+    const int part = ew >> 2;
+    const int c0 = part * GROUPS;
+    const float alpha = __ldg(a.alpha);
+    int64_t local = 0;
+    bool ok = true;
+    for (int b = b_first; ok && b < nb; b += b_step) {
+      const int col_base = b * TN;
+      float thr_next = CUDART_INF_F;
+      if (MODE == SCAN_THRESHOLD && t_first < qtiles && t_first * TM + et < a.n) thr_next = __ldg(a.thr + t_first * TM + et);
+      for (int64_t t = t_first; t < qtiles; t += t_step, ++local) {
+        const int acc = (int)(local & 1);
+        const uint32_t aph = (uint32_t)((local >> 1) & 1);
+        const int64_t q = t * TM + et;
+        const bool qok = q < a.n;
+        const float thr = thr_next;
+        if (MODE == SCAN_THRESHOLD) {   // the next tile's threshold is in flight while this tile is processed
+          const int64_t qn = (t + t_step) * TM + et;
+          thr_next = (t + t_step < qtiles && qn < a.n) ? __ldg(a.thr + qn) : CUDART_INF_F;
+        }
+        bool got = mbar_wait(&sm->tmem_full[acc], aph, &sm->abort_flag, a.err, 4, wait_limit);
+        got = __all_sync(0xffffffffu, got);
+        if (!got) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t trow = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * TN);
+        float bv = CUDART_INF_F;   // SCAN_ARGMIN: this thread's best over its columns of the block
+        int bj = 0;
+#pragma unroll 1
+        for (int c = c0; c < c0 + GROUPS; ++c) {
+          float v[32];
+          tc_ld32(trow + (uint32_t)(c * 32), v);
+          const int left = a.k - (col_base + c * 32);   // valid centroids from this group's first column on
+          if (left <= 0) continue;
+          if (MODE == SCAN_ARGMIN) {
+            // alpha < 0: the smallest value of the group is alpha times its largest accumulator - one max per value;
+            // the column is looked for only when the group beats the best so far (ever more rarely as groups go by)
+            float amax = -CUDART_INF_F;
+            if (left >= 32) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) amax = fmaxf(amax, v[j]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) amax = j < left ? fmaxf(amax, v[j]) : amax;
+            }
+            const float gmin = amax * alpha;
+            if (gmin < bv) {   // strict '<': an earlier (lower) centroid keeps a tie
+              bv = gmin;
+              int jj = 31;
+#pragma unroll
+              for (int j = 31; j >= 0; --j) jj = (j < left && v[j] == amax) ? j : jj;   // the lowest column holding the max
+              bj = c * 32 + jj;
+            }
+          } else {
+            // value = alpha * accumulator with alpha < 0: the smallest value is alpha times the largest accumulator
+            float amax = v[0];
+#pragma unroll
+            for (int j = 1; j < 32; ++j) amax = fmaxf(amax, v[j]);
+            const bool mine = qok && amax * alpha <= thr;   // this row has a hit among the 32 columns
+            if (left >= 32 && !__any_sync(0xffffffffu, mine)) continue;
+            if (mine || left < 32) {
+              const uint32_t colmask = left >= 32 ? 0xffffffffu : ((1u << left) - 1u);
+              uint32_t bits = 0;
+#pragma unroll
+              for (int j = 0; j < 32; ++j) bits |= (v[j] * alpha <= thr) ? (1u << j) : 0u;
+              bits = qok ? (bits & colmask) : 0u;
+              while (bits) {   // one or two hits as a rule
+                const int j = __ffs((int)bits) - 1;
+                bits &= bits - 1u;
+                const int slot = atomicAdd(&sm->log_n, 1);
+                if (slot < a.log_cap) my_log[slot] = make_uint2((uint32_t)q, (uint32_t)(col_base + c * 32 + j));
+              }
+            }
+          }
+        }
+        if (MODE == SCAN_ARGMIN && qok && bv < CUDART_INF_F)
+          atomicMin(a.best + q, (unsigned long long)make_key(bv, (uint32_t)(col_base + bj)));
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm->tmem_empty[acc]);
+      }
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before();
+  __syncthreads();
+  if (MODE == SCAN_THRESHOLD && threadIdx.x == 0) {
+    const int logged = sm->log_n;
+    a.log_count[blockIdx.x] = (int32_t)min((int64_t)logged, a.log_cap);
+    if (logged > a.log_cap) atomicCAS(a.err, 0, 9);
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// One warp per logged hit: the exact squared distance of the row to the listed centroid, direct fp32 formula, merged
+// into best[row] - smallest (value, centroid), the reference's strict '<' scan (KMeansClustering.swift:283-288).
+__global__ void assign_log_exact_kernel(const float* __restrict__ x, int dim, const float* __restrict__ cent,
+                                        const uint2* __restrict__ log, const int32_t* __restrict__ log_count, int64_t log_cap,
+                                        unsigned long long* __restrict__ best) {
+  const int cta = blockIdx.y;
+  const int cnt = log_count[cta];
+  const uint2* mine = log + (int64_t)cta * log_cap;
+  const int lane = threadIdx.x & 31;
+  for (int e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); e < cnt; e += gridDim.x * (blockDim.x >> 5)) {
+    const uint2 h = mine[e];
+    const float* xr = x + (int64_t)h.x * dim;
+    const float* cr = cent + (int64_t)h.y * dim;
+    float s = 0.f;
+    for (int i = lane; i < dim; i += 32) {
+      const float d = __ldg(xr + i) - __ldg(cr + i);
+      s = fmaf(d, d, s);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) atomicMin(best + h.x, (unsigned long long)make_key(s, h.y));
+  }
+}
+
+// best[row] -> assignment and rooted distance; a row without any logged hit is handed to the exact scan
+__global__ void assign_log_decode_kernel(const unsigned long long* __restrict__ best, int64_t n, int32_t* __restrict__ assign,
+                                         float* __restrict__ dist, int32_t* __restrict__ bad_rows, int32_t* bad_count) {
+  const int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= n) return;
+  const unsigned long long b = best[r];
+  if (b == ~0ull) {
+    bad_rows[atomicAdd(bad_count, 1)] = (int32_t)r;
+    return;
+  }
+  assign[r] = (int32_t)(uint32_t)b;
+  if (dist) dist[r] = sqrtf(ordered_to_float((uint32_t)(b >> 32)));
+}
+
 // ---- operand preparation --------------------------------------------------------------------
 // Statistics accumulated with atomics on order-preserving integer images of non-negative floats.
 struct PrepStats {
@@ -687,6 +908,7 @@ struct FoldArgs {
   int side;   // 0: none, 1: rows (pieces of the term), 2: queries (the constant)
   int col0;   // first of the kFoldCols columns
   int exp;
+  const int* exp_dev = nullptr;   // when given, the exponent is read from device memory instead
 };
 
 template <int METRIC>
@@ -718,10 +940,11 @@ __global__ void prep_rows_kernel(const float* __restrict__ x, int64_t n, int dim
     const float e = t - back;
     e2 = fmaf(e, e, e2);
   }
+  const int fold_exp = fold.exp_dev ? *fold.exp_dev : fold.exp;
   if (fold.side == 1) {
     // pieces of R = s_x (|x|^2 / 2) 2^exp: p0 = fp16(R/16), then the same of what is left, twice (the remainders are
     // exact in fp32); what is left after three pieces is below 2^-33 R
-    const float R = ldexpf(0.5f * ss * s, fold.exp);
+    const float R = ldexpf(0.5f * ss * s, fold_exp);
     const __half p0 = __float2half_rn(R * 0.0625f);
     const float r1 = R - 16.0f * __half2float(p0);
     const __half p1 = __float2half_rn(r1 * 0.0625f);
@@ -732,7 +955,7 @@ __global__ void prep_rows_kernel(const float* __restrict__ x, int64_t n, int dim
       out[row * dim16 + fold.col0 + i] = __hneg(p);
     }
   } else if (fold.side == 2) {
-    const __half u = __float2half_rn(ldexpf(s, -fold.exp));
+    const __half u = __float2half_rn(ldexpf(s, -fold_exp));
     for (int i = lane; i < kFoldCols; i += 32) out[row * dim16 + fold.col0 + i] = u;
   }
 #pragma unroll
@@ -1164,7 +1387,7 @@ constexpr int kAssignCap = 32;   // split into one sub-list per column part of a
 __global__ void assign_bound_kernel(const float* __restrict__ xn16, const float* __restrict__ xe16,
                                     const float* __restrict__ xnorm, int64_t n, const float* scale_x,
                                     const float* scale_c, const PrepStats* cs, int dim16, float* __restrict__ eps,
-                                    float* alpha) {
+                                    float* alpha, int folded) {
   const int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const float inv = 1.0f / ((*scale_x) * (*scale_c));
   if (r == 0) *alpha = -2.0f * inv;
@@ -1172,7 +1395,10 @@ __global__ void assign_bound_kernel(const float* __restrict__ xn16, const float*
   const float C16 = __uint_as_float(cs->max_norm16), E16 = __uint_as_float(cs->max_err16);
   const float Cn = __uint_as_float(cs->max_norm);
   const float a = xn16[r], e = xe16[r];
-  const float dot_err = ((a * E16 + e * C16 + e * E16) + (float)dim16 * 2.3841858e-7f * a * C16) * inv;
+  float dot_err = ((a * E16 + e * C16 + e * E16) + (float)dim16 * 2.3841858e-7f * a * C16) * inv;
+  // |c|^2 / 2 carried inside the contraction: its products pass through the same fp32 accumulation, and three fp16
+  // pieces leave less than 2^-30 of it unrepresented
+  if (folded) dot_err += ((float)dim16 * 2.3841858e-7f + 9.3132257e-10f) * 0.5f * Cn * Cn;
   const float v = 2.0f * dot_err + 4.0f * 5.9604645e-8f * (float)dim16 * Cn * Cn +
                   2.0f * 5.9604645e-8f * (Cn * Cn + 2.0f * xnorm[r] * Cn);
   eps[r] = v * 1.0001f + 1e-30f;
@@ -1224,14 +1450,23 @@ __global__ void assign_exact_kernel(const float* __restrict__ x, int64_t n, int 
   if (row >= n) return;
   const int lane = threadIdx.x & 31;
   // one 8-bit count per sub-list; the scan's column parts (2 or 4) each wrote one sub-list of kAssignCap / parts keys
-  const unsigned packed = (unsigned)count[row];
-  const int sub = kAssignCap / parts;
+  // parts == 0: one list of up to kAssignCap keys with a plain count (the stationary-block kernel)
+  unsigned packed = (unsigned)count[row];
+  int sub = kAssignCap;
   int total = 0;
   bool over = false;
-  for (int p = 0; p < parts; ++p) {
-    const int c = (int)((packed >> (8 * p)) & 0xffu);
-    over |= c > sub;
-    total += c;
+  if (parts == 0) {
+    total = (int)packed;
+    over = total > kAssignCap;
+    packed = (unsigned)min(total, 255);
+    parts = 1;
+  } else {
+    sub = kAssignCap / parts;
+    for (int p = 0; p < parts; ++p) {
+      const int c = (int)((packed >> (8 * p)) & 0xffu);
+      over |= c > sub;
+      total += c;
+    }
   }
   if (over || total <= 0) {
     if (lane == 0) bad_rows[atomicAdd(bad_count, 1)] = (int32_t)row;
@@ -1265,6 +1500,83 @@ __global__ void scatter_best_kernel(const unsigned long long* __restrict__ best,
   const unsigned long long b = best[i];
   assign[rows[i]] = (int32_t)(uint32_t)b;
   if (dist) dist[rows[i]] = sqrtf(ordered_to_float((uint32_t)(b >> 32)));
+}
+
+// Scale of the centroid operand and exponent of the folded term for one Lloyd iteration (device-side, nothing is
+// read back).  With M = max |c|^2 / 2: the largest of the three fp16 pieces of s_c M 2^e / 16 should sit just below
+// 2^14, and the constant on the data side, u = s_x 2^-e, must be a normal fp16 number no larger than 2^15.  When u
+// would be too large the centroid scale is lowered by the excess (the pieces shrink, e grows, u shrinks); the error
+// bound is computed from the measured residuals of whatever scale is used, so it stays valid.
+__global__ void assign_fold_setup_kernel(const unsigned* max_sq, float* scale_c, const float* scale_x, int* exp_out, float* u_out) {
+  const float M = 0.5f * __uint_as_float(*max_sq);
+  float sc = *scale_c;
+  const float sx = *scale_x;
+  int e = 0;
+  if (M > 0.f && M < CUDART_INF_F) {
+    int m2;
+    frexpf(sc * M * 0.0625f, &m2);   // sc M / 16 = f 2^m2, f in [0.5, 1)
+    e = 14 - m2;                     // brings it to [2^13, 2^14)
+    int ex;
+    frexpf(sx, &ex);                 // sx = 2^(ex-1)
+    const int lu = (ex - 1) - e;     // log2 of u
+    if (lu > 15) {
+      const int shift = lu - 15;
+      sc = ldexpf(sc, -shift);
+      e += shift;
+    } else if (lu < -14) {
+      e -= (-14 - lu);               // u up to the smallest normal; the pieces only get smaller
+    }
+  }
+  *scale_c = sc;
+  *exp_out = e;
+  *u_out = ldexpf(sx, -e);
+}
+
+// the data operand's fold columns hold the constant u (one 16-byte store of eight copies per thread)
+__global__ void assign_fill_fold_kernel(__half* __restrict__ rows16, int64_t n, int dim16, int col0, const float* __restrict__ u) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  constexpr int chunks = kFoldCols / 8;
+  if (i >= n * chunks) return;
+  const int64_t row = i / chunks;
+  const int c = (int)(i - row * chunks);
+  const __half h = __float2half_rn(*u);
+  const __half2 h2 = __halves2half2(h, h);
+  uint4 v;
+  v.x = v.y = v.z = v.w = *reinterpret_cast<const unsigned*>(&h2);
+  *reinterpret_cast<uint4*>(rows16 + row * dim16 + col0 + c * 8) = v;
+}
+
+template <int MODE>
+int32_t launch_assign_scan(Ctx* ctx, const CUtensorMap& mx, const CUtensorMap& mc, AsArgs a, unsigned* grid_out = nullptr,
+                           int64_t* log_cap_out = nullptr) {
+  static bool attr_done = false;
+  if (!attr_done) {
+    VSK_CUDA(ctx, cudaFuncSetAttribute(assign_scan_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAsSmemBytes));
+    attr_done = true;
+  }
+  const int sms = ctx->prop.multiProcessorCount;
+  const int nb = (int)ceil_div(a.k, TN);
+  const int64_t qtiles = ceil_div(a.n, TM);
+  unsigned grid;
+  if (nb <= sms) {
+    a.groups = (int)std::max<int64_t>(1, std::min<int64_t>(sms / nb, qtiles));
+    grid = (unsigned)(nb * a.groups);
+  } else {
+    a.groups = 1;
+    grid = (unsigned)sms;
+  }
+  a.wait_limit = ctx->tuning.wait_limit_log2 > 0 ? (1u << std::min(ctx->tuning.wait_limit_log2, 30)) : 0u;
+  a.log_cap = std::min<int64_t>(a.log_total / grid, 0x7fffffff);
+  if (grid_out) *grid_out = grid;
+  if (log_cap_out) *log_cap_out = a.log_cap;
+  prof_begin(ctx);
+  assign_scan_kernel<MODE><<<grid, AS_THREADS, kAsSmemBytes, ctx->stream>>>(mx, mc, a);
+  prof_end(ctx);
+  tl_mark(ctx, MODE == SCAN_ARGMIN ? "assign_argmin" : "assign_scan");
+  ctx->stats.kernel_launches++;
+  ctx->stats.tensor_tiles += (int64_t)nb * qtiles;
+  VSK_CUDA(ctx, cudaGetLastError());
+  return VSK_OK;
 }
 
 }  // namespace
@@ -2042,7 +2354,10 @@ int32_t ivf_tensor_search(Index* ix, const float* q, int64_t nq, const int64_t* 
 int32_t tensor_assign_prepare(Ctx* ctx, const float* rows, int64_t n, int32_t dim, TensorAssign* ta) {
   ta->n = n;
   ta->dim = dim;
-  ta->dim16 = (int32_t)(ceil_div(dim, TK) * TK);
+  // Short contractions keep a block of centroids resident (assign_scan_kernel): the operands then carry 48 more
+  // columns for the folded |c|^2 / 2 term.  Longer ones (more than four k-blocks with those columns) take the general kernel.
+  ta->stationary = dim + kFoldCols <= AS_MAX_KB * TK;
+  ta->dim16 = (int32_t)(ceil_div(dim + (ta->stationary ? kFoldCols : 0), TK) * TK);
   VSK_TRY(dev_alloc(ctx, (void**)&ta->rows16, (size_t)n * ta->dim16 * sizeof(__half)));
   VSK_TRY(dev_alloc(ctx, (void**)&ta->stats, (size_t)n * 4 * sizeof(float)));
   VSK_TRY(dev_alloc(ctx, (void**)&ta->keys, (size_t)n * kAssignCap * sizeof(uint64_t)));
@@ -2092,13 +2407,53 @@ int32_t tensor_assign(Ctx* ctx, TensorAssign* ta, const float* rows, const float
   VSK_CUDA(ctx, cudaMemsetAsync(sm + 5, 0, 8, ctx->stream));
   absmax_kernel<<<64, 256, 0, ctx->stream>>>(centroids, (int64_t)k * dim, sm + 2);
   choose_scale_kernel<<<1, 1, 0, ctx->stream>>>(sm + 2, 0, fsm + 3);
-  launch_prep<VSK_METRIC_EUCLIDEAN>(ctx, centroids, k, dim, dim16, fsm + 3, c16, caux, nullptr, nullptr, nullptr, cs);
-  assign_bound_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, ctx->stream>>>(st, st + n, st + 2 * n, n, fsm + 1, fsm + 3, cs, dim16, eps, fsm + 4);
+  FoldArgs cfold{0, 0, 0};
+  if (ta->stationary) {
+    // words 24..27 of `small`: max |c|^2, the fold exponent, (unused), the data side's constant
+    VSK_CUDA(ctx, cudaMemsetAsync(sm + 24, 0, 16, ctx->stream));
+    max_sq_kernel<<<(unsigned)ceil_div(k, 8), 256, 0, ctx->stream>>>(centroids, k, dim, sm + 24);
+    assign_fold_setup_kernel<<<1, 1, 0, ctx->stream>>>(sm + 24, fsm + 3, fsm + 1, (int*)sm + 25, fsm + 27);
+    assign_fill_fold_kernel<<<(unsigned)ceil_div(n * (kFoldCols / 8), 256), 256, 0, ctx->stream>>>(ta->rows16, n, dim16, dim16 - kFoldCols, fsm + 27);
+    ctx->stats.kernel_launches += 3;
+    cfold = FoldArgs{1, dim16 - kFoldCols, 0, (const int*)sm + 25};
+  }
+  launch_prep<VSK_METRIC_EUCLIDEAN>(ctx, centroids, k, dim, dim16, fsm + 3, c16, caux, nullptr, nullptr, nullptr, cs, cfold);
+  assign_bound_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, ctx->stream>>>(st, st + n, st + 2 * n, n, fsm + 1, fsm + 3, cs, dim16, eps, fsm + 4,
+                                                                         ta->stationary ? 1 : 0);
   ctx->stats.kernel_launches += 3;
   VSK_CUDA(ctx, cudaGetLastError());
   CUtensorMap mc;
   VSK_TRY(make_map(ctx, c16, k, dim16, TN, &mc));
   const CUtensorMap& mr = *(const CUtensorMap*)ta->map_rows;
+  if (ta->stationary) {
+    AsArgs sa{};
+    sa.n = n;
+    sa.k = k;
+    sa.kblocks = dim16 / TK;
+    sa.alpha = fsm + 4;
+    sa.thr = ta->thr;
+    // the hit log lives in the rows' key lists (n x kAssignCap words of 8 bytes), its per-CTA counts in `count`
+    sa.log = reinterpret_cast<uint2*>(ta->keys);
+    sa.log_total = n * (int64_t)kAssignCap;
+    sa.log_count = ta->count;
+    sa.best = ta->best;
+    sa.err = (int32_t*)(sm + 5);
+    if (assign_holds_previous) {
+      assign_prev_threshold_kernel<<<(unsigned)ceil_div(n, 8), 256, 0, ctx->stream>>>(rows, n, dim, centroids, assign, eps, ta->thr, ta->count);
+    } else {
+      VSK_CUDA(ctx, cudaMemsetAsync(ta->best, 0xff, (size_t)n * sizeof(unsigned long long), ctx->stream));
+      VSK_TRY(launch_assign_scan<SCAN_ARGMIN>(ctx, mr, mc, sa));
+      assign_threshold_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, ctx->stream>>>(ta->best, eps, n, ta->thr, ta->count);
+    }
+    VSK_CUDA(ctx, cudaMemsetAsync(ta->best, 0xff, (size_t)n * sizeof(unsigned long long), ctx->stream));
+    unsigned sgrid = 0;
+    int64_t log_cap = 0;
+    VSK_TRY(launch_assign_scan<SCAN_THRESHOLD>(ctx, mr, mc, sa, &sgrid, &log_cap));
+    assign_log_exact_kernel<<<dim3(64, sgrid), 256, 0, ctx->stream>>>(rows, dim, centroids, sa.log, sa.log_count, log_cap, ta->best);
+    assign_log_decode_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, ctx->stream>>>(ta->best, n, assign, dist, ta->bad_rows, (int32_t*)(sm + 6));
+    ctx->stats.kernel_launches += 3;
+    VSK_CUDA(ctx, cudaGetLastError());
+  } else {
 
   TcArgs a{};
   a.nq = n;
@@ -2130,9 +2485,32 @@ int32_t tensor_assign(Ctx* ctx, TensorAssign* ta, const float* rows, const float
                                                                          ta->bad_rows, (int32_t*)(sm + 6), tc_epilogue_warps(a.kblocks) / 4);
   ctx->stats.kernel_launches += 2;
   VSK_CUDA(ctx, cudaGetLastError());
+  }
   int32_t h[2] = {0, 0};
   VSK_CUDA(ctx, cudaMemcpyAsync(h, sm + 5, 8, cudaMemcpyDeviceToHost, ctx->stream));
   VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  if (h[0] == 9) {
+    // a CTA's hit log ran full (rows with very many near-ties): the fp32 tile decides for every row
+    ctx->stats.fallback_queries += n;
+    ExactScanArgs e{};
+    e.metric = VSK_METRIC_EUCLIDEAN;
+    e.mode = SCAN_ARGMIN;
+    e.q = rows;
+    e.nq = n;
+    e.x = centroids;
+    e.dim = dim;
+    e.row_begin = 0;
+    e.row_end = k;
+    e.best = ta->best;
+    VSK_CUDA(ctx, cudaMemsetAsync(ta->best, 0xff, (size_t)n * sizeof(unsigned long long), ctx->stream));
+    VSK_TRY(launch_exact_scan(ctx, e));
+    VSK_CUDA(ctx, cudaMemsetAsync(sm + 6, 0, 4, ctx->stream));
+    assign_log_decode_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, ctx->stream>>>(ta->best, n, assign, dist, ta->bad_rows, (int32_t*)(sm + 6));
+    ctx->stats.kernel_launches++;
+    VSK_CUDA(ctx, cudaGetLastError());
+    VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return VSK_OK;
+  }
   if (h[0] != 0) return fail(ctx, VSK_ERR_TIMEOUT, "tensor-core assignment: a bounded pipeline wait ran out (role %d)", h[0]);
   if (h[1] > 0) {
     // rows with too many near-ties (or none listed): the fp32 tile decides

@@ -58,6 +58,7 @@ struct TensorAssign {
   float* thr = nullptr;               // [n]
   int32_t* bad_rows = nullptr;        // [n] rows handed to the fp32 tile
   void* small = nullptr;              // scalars and centroid-operand statistics
+  bool stationary = false;            // short contraction: resident centroid block, |c|^2 / 2 folded into the operands
   alignas(64) unsigned char map_rows[128] = {};  // TMA tensor map of rows16
 };
 int32_t tensor_assign_prepare(Ctx* ctx, const float* rows, int64_t n, int32_t dim, TensorAssign* ta);
