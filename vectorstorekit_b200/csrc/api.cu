@@ -880,6 +880,7 @@ int32_t vsk_flat_add_f32(vsk_index* i, const float* rows, int64_t n, const uint6
   Index* ix = reinterpret_cast<Index*>(i);
   if (!ix) return VSK_ERR_INVALID_INPUT;
   cudaSetDevice(ix->ctx->device);
+  drain_stale_error("vsk_flat_add");
   return flat_add(ix, rows, n, masks, false);
 }
 
@@ -887,6 +888,7 @@ int32_t vsk_flat_add_f32_dev(vsk_index* i, const float* rows, int64_t n, const u
   Index* ix = reinterpret_cast<Index*>(i);
   if (!ix) return VSK_ERR_INVALID_INPUT;
   cudaSetDevice(ix->ctx->device);
+  drain_stale_error("vsk_flat_add");
   return flat_add(ix, rows, n, masks, true);
 }
 
@@ -936,6 +938,7 @@ int32_t vsk_search_dev(vsk_index* i, const float* q, int64_t nq, int32_t k, cons
   Index* ix = reinterpret_cast<Index*>(i);
   if (!ix) return VSK_ERR_INVALID_INPUT;
   cudaSetDevice(ix->ctx->device);
+  drain_stale_error("vsk_search_dev");
   if (ix->kind == INDEX_FLAT_I8) return sq8_search_dev(ix, q, nq, k, out_dist, out_ids);
   if (ix->kind == INDEX_PQ) {
     if (qmasks) return fail(ix->ctx, VSK_ERR_UNSUPPORTED_OPERATION, "a product-quantised index carries no row masks");

@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 #include <cuda_fp16.h>
 #include <stdint.h>
+#include <cstdio>
 
 #include <functional>
 #include <string>
@@ -148,6 +149,17 @@ struct Ctx {
   size_t marks_used = 0;
   cudaEvent_t tl_origin = nullptr;
 };
+// A CUDA runtime error that is not sticky stays in the thread's "last error" slot until somebody reads it; a launch
+// check that reads the slot would then blame its own kernel for a failure of an earlier, unrelated call.  Entry points
+// drain the slot first and say once on stderr what they found.
+inline void drain_stale_error(const char* where) {
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    static int told = 0;
+    if (told++ < 4) fprintf(stderr, "vsk: stale CUDA error before %s: %s\n", where, cudaGetErrorString(e));
+  }
+}
+
 // Records "the work issued so far on the current lane, up to `name`, is done" when the event log is on.
 void tl_mark(Ctx* ctx, const char* name);
 

@@ -1381,6 +1381,7 @@ int32_t launch_tc(Ctx* ctx, const CUtensorMap& mq, const CUtensorMap& mx, const 
 //   exact   the listed centroids are compared with the direct fp32 formula sum (x-c)^2; the smallest
 //           (value, index) wins, as the reference's strict '<' scan does (KMeansClustering.swift:283-288)
 // A row whose list overflows (more near-ties than a sub-list holds) is re-done by the fp32 tile.
+constexpr int kAssignLogPerRow = 6;
 constexpr int kAssignCap = 32;   // split into one sub-list per column part of a tile (2 parts of 16, or 4 of 8)
 
 // eps per data row against the current centroids; stats of the centroid operand are read on the device.
@@ -2360,7 +2361,8 @@ int32_t tensor_assign_prepare(Ctx* ctx, const float* rows, int64_t n, int32_t di
   ta->dim16 = (int32_t)(ceil_div(dim + (ta->stationary ? kFoldCols : 0), TK) * TK);
   VSK_TRY(dev_alloc(ctx, (void**)&ta->rows16, (size_t)n * ta->dim16 * sizeof(__half)));
   VSK_TRY(dev_alloc(ctx, (void**)&ta->stats, (size_t)n * 4 * sizeof(float)));
-  VSK_TRY(dev_alloc(ctx, (void**)&ta->keys, (size_t)n * kAssignCap * sizeof(uint64_t)));
+  // stationary kernel: `keys` is the hit log (a hit or two per row as a rule; six entries per row of room)
+  VSK_TRY(dev_alloc(ctx, (void**)&ta->keys, (size_t)n * (ta->stationary ? kAssignLogPerRow : kAssignCap) * sizeof(uint64_t)));
   VSK_TRY(dev_alloc(ctx, (void**)&ta->best, (size_t)n * sizeof(unsigned long long)));
   VSK_TRY(dev_alloc(ctx, (void**)&ta->count, (size_t)n * sizeof(int32_t)));
   VSK_TRY(dev_alloc(ctx, (void**)&ta->thr, (size_t)n * sizeof(float)));
@@ -2434,7 +2436,7 @@ int32_t tensor_assign(Ctx* ctx, TensorAssign* ta, const float* rows, const float
     sa.thr = ta->thr;
     // the hit log lives in the rows' key lists (n x kAssignCap words of 8 bytes), its per-CTA counts in `count`
     sa.log = reinterpret_cast<uint2*>(ta->keys);
-    sa.log_total = n * (int64_t)kAssignCap;
+    sa.log_total = n * (int64_t)kAssignLogPerRow;
     sa.log_count = ta->count;
     sa.best = ta->best;
     sa.err = (int32_t*)(sm + 5);
