@@ -234,6 +234,23 @@ int32_t vsk_search(vsk_index* index, const float* queries, int64_t nq, int32_t k
 int32_t vsk_search_dev(vsk_index* index, const float* queries, int64_t nq, int32_t k,
                        const uint64_t* qmasks, float* out_dist, int64_t* out_ids);
 
+/* The asynchronous form.  The reference's batch call commits a command buffer and resumes its caller from the
+ * buffer's completion handler (MetalAccelerationEngine.swift:139-204, :444-449; MetalDistanceCompute.swift:365-375).
+ * These calls return at once; the search runs on the context's worker thread, in submission order, and
+ * done(user, status) is then called FROM THAT THREAD with the results complete in out_dist / out_ids (host memory for
+ * vsk_search_async, device memory with the stream drained for vsk_search_dev_async).  Every buffer stays valid until
+ * the callback.  Between a submission and its callback the context belongs to the worker: no other call on the
+ * context or its indices except further *_async submissions and vsk_wait.  A status other than VSK_OK from the
+ * submission itself means nothing was queued and `done` will not be called.
+ * vsk_wait blocks until nothing is queued or running and returns the first failing status since the previous
+ * vsk_wait (VSK_OK if none); vsk_last_error then holds its message.  vsk_close waits for queued work too. */
+typedef void (*vsk_done_fn)(void* user, int32_t status);
+int32_t vsk_search_async(vsk_index* index, const float* queries, int64_t nq, int32_t k, const uint64_t* qmasks,
+                         float* out_dist, int64_t* out_ids, vsk_done_fn done, void* user);
+int32_t vsk_search_dev_async(vsk_index* index, const float* queries, int64_t nq, int32_t k, const uint64_t* qmasks,
+                             float* out_dist, int64_t* out_ids, vsk_done_fn done, void* user);
+int32_t vsk_wait(vsk_ctx* ctx);
+
 /* A shard's search in two halves, for a host that spreads the rows of one database over several GPUs
  * (the multi-GPU form of VectorStore.batchSearch; the reference has no sharded search).
  *   begin:  scans this shard.  bound[q] (device, nq floats) receives a value that this shard's ceil(k / shards)

@@ -44,6 +44,26 @@ int main() {
     return 8;
   } catch (const vsk::ImportFailed&) {
   }
+  // the awaited form: two submissions queue behind one another, both futures resolve to the blocking call's result
+  {
+    auto f1 = ix.batchSearchAsync(q, 1, 2);
+    auto f2 = ix.batchSearchAsync(q, 1, 2);
+    auto a1 = f1.get();
+    auto a2 = f2.get();
+    dev->wait();
+    if (a1.ids != r.ids || a1.distances != r.distances || a2.ids != r.ids) return 12;
+    auto bad = ix.batchSearchAsync(q, 1, 0);   // k = 0: the failure arrives through the future
+    try {
+      bad.get();
+      return 13;
+    } catch (const vsk::Error&) {
+    }
+    try {
+      dev->wait();                              // ...and once more as the first failure since the last wait
+      return 14;
+    } catch (const vsk::Error&) {
+    }
+  }
   // a communicator of one rank: the sharded call is the plain search, in both layouts
   dev->joinCommunicator(1, 0, {});
   int64_t first = -1;

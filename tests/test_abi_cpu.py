@@ -130,7 +130,7 @@ def test_unsupported_metric_raises():
 def _build_host_mirror(tmp):
     import subprocess
     exe = os.path.join(tmp, "host_mirror_test")
-    subprocess.run(["g++", "-std=c++17", "-O1", os.path.join(ROOT, "tests", "host_mirror_test.cpp"), "-o", exe,
+    subprocess.run(["g++", "-std=c++17", "-O1", "-pthread", os.path.join(ROOT, "tests", "host_mirror_test.cpp"), "-o", exe,
                     "-L", os.path.join(ROOT, "vectorstorekit_b200"), "-lvsk_cuda",
                     "-Wl,-rpath," + os.path.join(ROOT, "vectorstorekit_b200")], check=True)
     return exe

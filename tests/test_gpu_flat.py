@@ -552,3 +552,39 @@ def test_distance_matrix_api(vsk, dev, cpu_oracle):
     import torch
     aa = eng.computeDistanceMatrix(torch.as_tensor(a, device="cuda"), None, "euclidean")
     assert torch.equal(aa, aa.T) and float(aa.diagonal().abs().max()) == 0.0
+
+
+def test_async_search_is_the_blocking_search(vsk, cpu_oracle):
+    """vsk_search_async / vsk_search_dev_async (the completion-handler form, MetalAccelerationEngine.swift:444-449):
+    submissions queue on the context's worker and resolve, in order, to what the blocking call returns; a failing
+    call fails its future and is reported once more by wait()."""
+    import torch
+    dev = vsk.CUDAComputeDevice(0)
+    try:
+        rng = np.random.default_rng(909)
+        x = rng.standard_normal((30_000, 96)).astype(np.float32)
+        qs = [rng.standard_normal((n, 96)).astype(np.float32) for n in (1, 200, 1500)]
+        ix = vsk.FlatIndex(dev, 96, "euclidean")
+        ix.add(x)
+        want = [ix.batchSearch(q, 10) for q in qs]
+        futs = [ix.batchSearchAsync(q, 10) for q in qs]                  # three in the queue at once
+        fdev = ix.batchSearchAsync(torch.as_tensor(qs[1], device="cuda"), 10)
+        for f, (wd, wi) in zip(futs, want):
+            gd, gi = f.result(timeout=120)
+            assert np.array_equal(gi, wi) and np.array_equal(gd, wd)
+        dd, di = fdev.result(timeout=120)                                # stream drained before the callback
+        assert np.array_equal(di.cpu().numpy(), want[1][1])
+        dev.wait()
+        rd, ri = cpu_oracle.flat_search(oracle.EUCLIDEAN, qs[2], x, 10)
+        assert_topk_parity(*futs[2].result(), rd, ri)
+        bad = ix.batchSearchAsync(qs[0], 40_000)                         # k > rows of the index
+        with pytest.raises(vsk.VSKError):
+            bad.result(timeout=120)
+        with pytest.raises(vsk.VSKError):
+            dev.wait()
+        dev.wait()                                                       # reported once
+        gd, gi = ix.batchSearchAsync(qs[0], 10).result(timeout=120)      # the context still works
+        assert np.array_equal(gi, want[0][1])
+        ix.close()
+    finally:
+        dev.close()

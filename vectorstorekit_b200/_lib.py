@@ -18,6 +18,7 @@ c_i32p = C.POINTER(C.c_int32)
 c_u64p = C.POINTER(C.c_uint64)
 c_i8p = C.POINTER(C.c_int8)
 vp = C.c_void_p
+DONE_FN = C.CFUNCTYPE(None, C.c_void_p, C.c_int32)   # vsk_done_fn
 
 
 class DeviceInfo(C.Structure):
@@ -106,6 +107,9 @@ SIGNATURES = {
     "vsk_index_load": (C.c_int32, [vp, C.c_char_p, C.POINTER(vp)]),
     "vsk_search": (C.c_int32, [vp, vp, C.c_int64, C.c_int32, vp, vp, vp]),
     "vsk_search_dev": (C.c_int32, [vp, vp, C.c_int64, C.c_int32, vp, vp, vp]),
+    "vsk_search_async": (C.c_int32, [vp, vp, C.c_int64, C.c_int32, vp, vp, vp, DONE_FN, vp]),
+    "vsk_search_dev_async": (C.c_int32, [vp, vp, C.c_int64, C.c_int32, vp, vp, vp, DONE_FN, vp]),
+    "vsk_wait": (C.c_int32, [vp]),
     "vsk_search_shard_begin_dev": (C.c_int32, [vp, vp, C.c_int64, C.c_int32, C.c_int32, vp]),
     "vsk_search_shard_finish_dev": (C.c_int32, [vp, vp, vp, vp]),
     "vsk_merge_topk_dev": (C.c_int32, [vp, vp, vp, C.c_int32, C.c_int64, C.c_int32, vp, vp]),

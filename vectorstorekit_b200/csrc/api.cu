@@ -664,6 +664,7 @@ int32_t vsk_open(int32_t device, vsk_ctx** out_ctx) {
 int32_t vsk_close(vsk_ctx* c) {
   Ctx* ctx = reinterpret_cast<Ctx*>(c);
   if (!ctx) return VSK_ERR_INVALID_INPUT;
+  worker_release(ctx);   // runs what is still queued, then joins
   cudaSetDevice(ctx->device);
   cudaStreamSynchronize(ctx->stream_main);
   cudaStreamSynchronize(ctx->stream_aux);

@@ -108,6 +108,7 @@ struct ShardPending {
 };
 
 struct Comm;   // NCCL communicator of a row-sharded search (comm.cu)
+struct Worker; // thread and queue behind the *_async entry points (async.cu)
 
 // Pinned host memory that grows on demand (results the host reads back right after a stream drains).
 struct PinnedBuf {
@@ -142,6 +143,7 @@ struct Ctx {
   ShardPending pending[2];
   PinnedBuf host_flags[2];   // per lane: the flag words a finished half-search hands to the host
   Comm* comm = nullptr;
+  Worker* worker = nullptr;
   // optional event log (vsk_timeline): one event after each marked launch, on the stream it went to
   bool timeline = false;
   struct Mark { const char* name; int lane; cudaEvent_t ev; };
@@ -380,6 +382,7 @@ int32_t pq_reserve(Index* ix, int64_t need);
 vsk_tuning default_tuning();
 // comm.cu: leaves the context's communicator, if any
 void comm_release(Ctx* ctx);
+void worker_release(Ctx* ctx);
 int32_t dev_alloc(Ctx* ctx, void** p, size_t bytes);
 void dev_free(void* p);
 

@@ -169,11 +169,20 @@ class CUDAComputeDevice:
                 f"cannot open CUDA device {device}: {self._lib.vsk_status_string(st).decode()}")
         self._h = h
         self.device = device
+        self._inflight = set()          # asynchronous calls whose callback has not run
+        self._inflight_keep = {}        # their buffers and callback objects
+
+    def wait(self):
+        """``vsk_wait``: blocks until every asynchronous call has completed; raises the first failure."""
+        st = self._lib.vsk_wait(self._h)
+        self._inflight_keep = {k: v for k, v in self._inflight_keep.items() if k in self._inflight}
+        self.check(st)
 
     def close(self):
         if getattr(self, "_h", None):
             self._lib.vsk_close(self._h)
             self._h = None
+            self._inflight_keep = {}
 
     def __del__(self):  # pragma: no cover
         try:
@@ -423,6 +432,49 @@ class _IndexBase:
         self.dev.check(self._lib.vsk_search(self._h, _ptr(q), nq, k, _ptr(qm), _ptr(od), _ptr(oi)))
         return od, oi
 
+    def _searchAsync(self, queries, k, qmasks=None):
+        """``vsk_search_async`` / ``vsk_search_dev_async``: returns a ``concurrent.futures.Future`` that the library's
+        worker thread resolves to (dist, ids), or fails with the error class of the status.  Until the future is
+        done the device object takes only further ``*Async`` calls and ``wait()``."""
+        import concurrent.futures
+        fut = concurrent.futures.Future()
+        nq = queries.shape[0]
+        dev_side = _is_dev(queries)
+        if dev_side:
+            q = queries.contiguous().float()
+            od = torch.empty((nq, k), dtype=torch.float32, device=q.device)
+            oi = torch.empty((nq, k), dtype=torch.int64, device=q.device)
+            qm = qmasks.contiguous() if qmasks is not None else None
+            call = self._lib.vsk_search_dev_async
+        else:
+            q = _host(queries, np.float32)
+            od = np.empty((nq, k), np.float32)
+            oi = np.empty((nq, k), np.int64)
+            qm = _host(qmasks, np.uint64) if qmasks is not None else None
+            call = self._lib.vsk_search_async
+        keep = []                                   # buffers and the callback object live until the callback ran
+
+        def done(_user, st):
+            try:
+                if st == 0:
+                    fut.set_result((od, oi))
+                else:
+                    msg = self._lib.vsk_last_error(self.dev._h).decode()
+                    fut.set_exception(_ERRORS.get(st, VSKError)(msg or self._lib.vsk_status_string(st).decode()))
+            finally:
+                self.dev._inflight.discard(id(keep))
+
+        cb = _lib.DONE_FN(done)
+        keep.extend((q, qm, od, oi, cb, keep))
+        self.dev._inflight_keep[id(keep)] = keep
+        self.dev._inflight.add(id(keep))
+        st = call(self._h, _ptr(q), nq, k, _ptr(qm), _ptr(od), _ptr(oi), cb, None)
+        if st != 0:
+            self.dev._inflight.discard(id(keep))
+            self.dev._inflight_keep.pop(id(keep), None)
+            self.dev.check(st)
+        return fut
+
 
 def sharded_slice(nq: int, nranks: int, rank: int):
     """Queries [first, first + count) whose merged results rank `rank` returns under the SLICE layout."""
@@ -556,6 +608,15 @@ class FlatIndex(_IndexBase, _ShardedSearchMixin):
         if queries.shape[1] != self.dimensions:
             raise DimensionMismatch(f"expected {self.dimensions}, got {queries.shape[1]}")
         return self._search(queries, int(k), filter_masks)
+
+    # The awaited form (``MetalAccelerationEngine.batchComputeDistances`` is ``async``, :139-204): a future of
+    # batchSearch's result.
+    def batchSearchAsync(self, queries, k: int, filter_masks=None):
+        if len(queries) == 0:
+            raise EmptyInput("no queries")
+        if queries.shape[1] != self.dimensions:
+            raise DimensionMismatch(f"expected {self.dimensions}, got {queries.shape[1]}")
+        return self._searchAsync(queries, int(k), filter_masks)
 
     def coarseValues(self, queries, rows: int):
         """``vsk_coarse_values_dev``: the tensor path's coarse values of the first `rows` rows and the per-query

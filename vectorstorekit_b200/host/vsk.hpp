@@ -12,6 +12,7 @@
 #pragma once
 #include <algorithm>
 #include <cstdint>
+#include <future>
 #include <memory>
 #include <stdexcept>
 #include <string>
@@ -92,6 +93,8 @@ class CUDAComputeDevice {
     check(vsk_comm_init(ctx_, nranks, rank, id.empty() ? nullptr : id.data()), ctx_);
   }
   void leaveCommunicator() { check(vsk_comm_destroy(ctx_), ctx_); }
+  // Blocks until every asynchronous call has completed; throws the first failure.
+  void wait() { check(vsk_wait(ctx_), ctx_); }
   std::pair<int32_t, int32_t> communicator() const {   // (ranks, this rank)
     int32_t n = 1, r = 0;
     check(vsk_comm_info(ctx_, &n, &r), ctx_);
@@ -151,6 +154,27 @@ class FlatIndex {
     r.distances.resize((size_t)nq * k); r.ids.resize((size_t)nq * k);
     check(vsk_search(ix_, queries, nq, k, filter_masks, r.distances.data(), r.ids.data()), dev_->ctx());
     return r;
+  }
+  // The awaited form (MetalAccelerationEngine.batchComputeDistances is `async`, :139-204): the library's worker thread
+  // fulfils the future.  `queries` (and filter_masks) stay valid until then; until the future is ready the device
+  // object takes only further *Async calls and wait().
+  std::future<SearchResults> batchSearchAsync(const float* queries, int64_t nq, int32_t k,
+                                              const uint64_t* filter_masks = nullptr) const {
+    if (nq <= 0) throw EmptyInput(VSK_ERR_EMPTY_INPUT, "no queries");
+    struct Pending { std::promise<SearchResults> p; SearchResults r; vsk_ctx* ctx; };
+    auto* pend = new Pending();
+    pend->ctx = dev_->ctx();
+    pend->r.nq = nq; pend->r.k = k;
+    pend->r.distances.resize((size_t)nq * k); pend->r.ids.resize((size_t)nq * k);
+    auto fut = pend->p.get_future();
+    const int32_t st = vsk_search_async(ix_, queries, nq, k, filter_masks, pend->r.distances.data(), pend->r.ids.data(),
+        [](void* user, int32_t status) {
+          std::unique_ptr<Pending> p(static_cast<Pending*>(user));
+          if (status == VSK_OK) { p->p.set_value(std::move(p->r)); return; }
+          try { check(status, p->ctx); } catch (...) { p->p.set_exception(std::current_exception()); }
+        }, pend);
+    if (st != VSK_OK) { delete pend; check(st, dev_->ctx()); }
+    return fut;
   }
   // This index holds rows [idBase, idBase + count) of a database spread over the ranks of the device's communicator.
   void setIdBase(int64_t base) { check(vsk_index_set_id_base(ix_, base), dev_->ctx()); }
