@@ -12,7 +12,7 @@
 // This is the path of VectorStore.search (one query), of small filtered or Manhattan batches, and
 // of the few queries a tensor-path search re-runs when their certificate fails.  With per-query row
 // lists (ExactScanArgs::seg_begin) it is also the IVF search of a few queries: one grid row per query,
-// each over the rows of its own probed lists.  VSK_NO_STREAM_SCAN=1 (read once) switches it off.  A lane sums its
+// each over the rows of its own probed lists.  vsk_tuning.stream_scan = 0 switches it off.  A lane sums its
 // own dimensions first and the lanes are added afterwards, so a value can differ from the tile's
 // (dimension-order) sum in the last bits.
 #include "common.cuh"
