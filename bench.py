@@ -758,7 +758,11 @@ def main():
         line["clocks"] = sampler.summary()
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = b.cpu_baseline()
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
+    # release the library's objects in order (the context closes the indices created on it first); left to the
+    # interpreter's shutdown, finalisers of the Bench object's reference cycle run in no particular order
+    torch.cuda.synchronize()
+    dev.close()
     if world > 1:
         dist.destroy_process_group()
 

@@ -179,6 +179,23 @@ int64_t vsk_schedule_chunk(int64_t seen, int32_t keep, int32_t level);
  * (Acceleration/Metal/MetalThreadConfigurationOptimizer.swift:430-440). */
 typedef enum vsk_peak { VSK_PEAK_FP32_ISSUE = 0, VSK_PEAK_SMEM_GATHER = 1 } vsk_peak;
 int32_t vsk_measure_peak(vsk_ctx* ctx, int32_t what, double* per_second);
+/* The checked build variant (libvsk_cuda_checked.so, `python -m vectorstorekit_b200.build --checked`): every global
+ * load, store and atomic of every kernel is range-tested against the device buffers the library allocated (with the
+ * sizes the calls asked for) and the buffers the caller announced; an access outside them, or one not aligned to its
+ * own size, is diverted to a sink and counted instead of being executed - no trap, the context stays usable.  It is
+ * what Metal's shader validation layer is to the reference and what compute-sanitizer is to CUDA where that tool can
+ * run.  In the normal library these calls exist and do nothing (vsk_checked_build returns 0).
+ *   vsk_checked_register    announce a caller-owned device buffer that `_dev` entry points will be given
+ *   vsk_checked_faults      out3 = {refused accesses since the last call, first refused address,
+ *                           its size in bytes | write << 8 | misaligned << 9}; waits for the context's streams
+ *   vsk_checked_selftest    reads one word past the announced end of a buffer of the library's own (the memory behind
+ *                           it is valid): an instrumented build records exactly one refused access */
+int32_t vsk_checked_build(void);
+int32_t vsk_checked_register(const void* device_ptr, int64_t bytes);
+int32_t vsk_checked_unregister(const void* device_ptr);
+int32_t vsk_checked_faults(vsk_ctx* ctx, uint64_t* out3);
+int32_t vsk_checked_selftest(vsk_ctx* ctx);
+
 int32_t vsk_tuning_get(vsk_ctx* ctx, vsk_tuning* out);
 int32_t vsk_tuning_set(vsk_ctx* ctx, const vsk_tuning* in);
 

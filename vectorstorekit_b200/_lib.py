@@ -10,7 +10,10 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libvsk_cuda.so")
+# VSK_CHECKED=1 selects the checked build variant (every global access of every kernel range-tested; see
+# ``build.py --checked``).  It is a testing aid: same entry points, several times slower.
+CHECKED = os.environ.get("VSK_CHECKED", "0") not in ("", "0")
+LIB_PATH = os.path.join(HERE, "libvsk_cuda_checked.so" if CHECKED else "libvsk_cuda.so")
 
 c_f32p = C.POINTER(C.c_float)
 c_i64p = C.POINTER(C.c_int64)
@@ -110,6 +113,11 @@ SIGNATURES = {
     "vsk_search_async": (C.c_int32, [vp, vp, C.c_int64, C.c_int32, vp, vp, vp, DONE_FN, vp]),
     "vsk_search_dev_async": (C.c_int32, [vp, vp, C.c_int64, C.c_int32, vp, vp, vp, DONE_FN, vp]),
     "vsk_wait": (C.c_int32, [vp]),
+    "vsk_checked_build": (C.c_int32, []),
+    "vsk_checked_register": (C.c_int32, [vp, C.c_int64]),
+    "vsk_checked_unregister": (C.c_int32, [vp]),
+    "vsk_checked_faults": (C.c_int32, [vp, vp]),
+    "vsk_checked_selftest": (C.c_int32, [vp]),
     "vsk_search_shard_begin_dev": (C.c_int32, [vp, vp, C.c_int64, C.c_int32, C.c_int32, vp]),
     "vsk_search_shard_finish_dev": (C.c_int32, [vp, vp, vp, vp]),
     "vsk_merge_topk_dev": (C.c_int32, [vp, vp, vp, C.c_int32, C.c_int64, C.c_int32, vp, vp]),
@@ -153,7 +161,7 @@ def load() -> C.CDLL:
         return _lib
     if not os.path.exists(LIB_PATH):
         raise ImportError(
-            f"{LIB_PATH} is missing: build it with `python -m vectorstorekit_b200.build` "
+            f"{LIB_PATH} is missing: build it with `python -m vectorstorekit_b200.build{' --checked' if CHECKED else ''}` "
             "(there is no CPU implementation to fall back on)")
     lib = C.CDLL(LIB_PATH)
     for name, (res, args) in SIGNATURES.items():

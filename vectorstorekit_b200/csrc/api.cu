@@ -36,10 +36,12 @@ int32_t dev_alloc(Ctx* ctx, void** p, size_t bytes) {
     cudaGetLastError();
     return fail(ctx, VSK_ERR_OUT_OF_MEMORY, "device out of memory: required %zu bytes, available %zu", bytes, fr);
   }
+  chk_add(*p, bytes);
   return VSK_OK;
 }
 void dev_free(void* p) {
   if (!p) return;
+  chk_remove(p);
   const cudaError_t e = cudaFree(p);
   if (e != cudaSuccess) {
     // nothing to hand the error to (frees happen on clean-up paths): say so once, and do not leave it behind for the
@@ -88,7 +90,11 @@ int32_t scratch(Ctx* ctx, int slot, size_t bytes, void** out) {
     dev_free(ctx->scratch[slot]);
     ctx->scratch[slot] = nullptr;
     ctx->scratch_bytes[slot] = 0;
+#ifdef VSK_CHECKED
+    size_t want = (bytes + 15) & ~(size_t)15;   // no slack: the announced range is the largest request so far
+#else
     size_t want = bytes + bytes / 8 + 256;
+#endif
     VSK_TRY(dev_alloc(ctx, &ctx->scratch[slot], want));
     ctx->scratch_bytes[slot] = want;
   }
@@ -657,6 +663,15 @@ int32_t vsk_open(int32_t device, vsk_ctx** out_ctx) {
   }
   ctx->stream = ctx->stream_main;
   ctx->tuning = default_tuning();
+  if (chk_open(ctx) != VSK_OK) {   // checked build: the range table of this GPU
+    cudaStreamDestroy(ctx->stream_main);
+    cudaStreamDestroy(ctx->stream_aux);
+    cudaEventDestroy(ctx->ev_fork);
+    cudaEventDestroy(ctx->ev_join);
+    cudaGetLastError();
+    delete ctx;
+    return VSK_ERR_DEVICE_NOT_AVAILABLE;
+  }
   *out_ctx = reinterpret_cast<vsk_ctx*>(ctx);
   return VSK_OK;
 }

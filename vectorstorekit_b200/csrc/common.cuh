@@ -12,6 +12,7 @@
 #include <vector>
 
 #include "../../include/vsk_cuda.h"
+#include "checked.cuh"   // empty unless VSK_CHECKED
 
 namespace vsk {
 
@@ -382,6 +383,10 @@ int32_t pq_reserve(Index* ix, int64_t need);
 vsk_tuning default_tuning();
 // comm.cu: leaves the context's communicator, if any
 void comm_release(Ctx* ctx);
+// Range table of the checked build (checked.cu); no-ops otherwise.
+int32_t chk_open(Ctx* ctx);
+void chk_add(const void* p, size_t bytes);
+void chk_remove(const void* p);
 void worker_release(Ctx* ctx);
 int32_t dev_alloc(Ctx* ctx, void** p, size_t bytes);
 void dev_free(void* p);

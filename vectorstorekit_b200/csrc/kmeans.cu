@@ -201,6 +201,7 @@ int32_t assign_rows_static(Ctx* ctx, const float* rows, int64_t n, int32_t dim, 
     void* p = nullptr;
     VSK_CUDA(ctx, cudaGetSymbolAddress(&p, g_assign_static_keys));
     keys = g_assign_static_ptr[ctx->device] = static_cast<unsigned long long*>(p);
+    chk_add(p, sizeof(g_assign_static_keys));   // checked build: the array is a legal target
   }
   // The array still holds the previous call's keys: every key this call reads must start as all ones.
   VSK_CUDA(ctx, cudaMemsetAsync(keys, 0xff, (size_t)n * sizeof(unsigned long long), ctx->stream));

@@ -22,6 +22,7 @@ from __future__ import annotations
 import ctypes as C
 import os
 import enum
+import weakref
 from typing import Optional, Sequence
 
 import numpy as np
@@ -153,6 +154,9 @@ def _ptr(a):
         return None
     if _is_dev(a):
         torch.cuda.current_stream(a.device).synchronize()
+        if _lib.CHECKED and a.numel():
+            # the checked build tests every kernel access against the buffers it knows: announce this one
+            _lib.load().vsk_checked_register(C.c_void_p(a.data_ptr()), a.numel() * a.element_size())
         return C.c_void_p(a.data_ptr())
     return C.c_void_p(a.ctypes.data)
 
@@ -169,8 +173,19 @@ class CUDAComputeDevice:
                 f"cannot open CUDA device {device}: {self._lib.vsk_status_string(st).decode()}")
         self._h = h
         self.device = device
+        self._children = weakref.WeakSet()   # indices and trainers created on this context: closed before it
         self._inflight = set()          # asynchronous calls whose callback has not run
         self._inflight_keep = {}        # their buffers and callback objects
+
+    # The checked build variant (``VSK_CHECKED=1``; ``vsk_checked_*``): refused accesses since the last call as
+    # (count, first address, size | write << 8 | misaligned << 9); always (0, 0, 0) in the normal library.
+    def checked_faults(self):
+        out = (C.c_uint64 * 3)()
+        self.check(self._lib.vsk_checked_faults(self._h, out))
+        return int(out[0]), int(out[1]), int(out[2])
+
+    def checked_selftest(self):
+        self.check(self._lib.vsk_checked_selftest(self._h))
 
     def wait(self):
         """``vsk_wait``: blocks until every asynchronous call has completed; raises the first failure."""
@@ -180,6 +195,11 @@ class CUDAComputeDevice:
 
     def close(self):
         if getattr(self, "_h", None):
+            for child in list(self._children):
+                try:
+                    child.close()
+                except Exception:
+                    pass
             self._lib.vsk_close(self._h)
             self._h = None
             self._inflight_keep = {}
@@ -375,11 +395,14 @@ class _IndexBase:
         self.dev = dev
         self._lib = dev._lib
         self._h = None
+        dev._children.add(self)
 
     def close(self):
-        if self._h:
+        # An index lives inside its context: once the device object is closed (it closes its indices first) the
+        # handle is gone too.  At interpreter shutdown finalisers run in no particular order, hence the check.
+        if self._h and getattr(self.dev, "_h", None):
             self._lib.vsk_index_destroy(self._h)
-            self._h = None
+        self._h = None
 
     def __del__(self):  # pragma: no cover
         try:
@@ -737,6 +760,7 @@ class KMeansTrainer:
         h = C.c_void_p()
         dev.check(self._lib.vsk_kmeans_trainer_create_dev(dev._h, _ptr(self.rows), self.n, self.dim, self.k, C.byref(h)))
         self._h = h
+        dev._children.add(self)
 
     def step(self, centroids):
         c = centroids.contiguous().float()
@@ -758,9 +782,9 @@ class KMeansTrainer:
         return a
 
     def close(self):
-        if self._h:
+        if self._h and getattr(self.dev, "_h", None):
             self._lib.vsk_kmeans_trainer_destroy(self._h)
-            self._h = None
+        self._h = None
 
     def __del__(self):  # pragma: no cover
         try:
