@@ -92,23 +92,23 @@ int32_t chk_open(Ctx* ctx) {
 
 static void chk_add_to(chk::DeviceTable* t, const void* p, size_t bytes) {
   const unsigned long long lo = (unsigned long long)(uintptr_t)p, hi = lo + bytes;
-  auto it = t->ranges.find(lo);
-  if (it != t->ranges.end() && it->second == hi) return;   // unchanged
-  {
-    // a part of a buffer that is already known (a slice of a tensor the caller announced whole): nothing to add
-    auto up = t->ranges.upper_bound(lo);
-    if (up != t->ranges.begin()) {
-      auto prev = std::prev(up);
-      if (prev->first <= lo && prev->second >= hi) return;
-    }
+  // Ranges that overlap the new one are leftovers of buffers the caller's allocator has since reused (live buffers
+  // do not overlap).  A leftover that contains the new range whole may equally be a live buffer of which this is a
+  // slice: it stays.  Others lose the part that overlaps - not more: the rest may still cover a live buffer that
+  // was announced while it lay inside the leftover.
+  auto it = t->ranges.upper_bound(lo);
+  if (it != t->ranges.begin()) {
+    auto prev = std::prev(it);
+    if (prev->first <= lo && prev->second >= hi) return;   // already covered
+    if (prev->second > lo) it = prev;
   }
-  // whatever overlaps the new range is stale (the caller's allocator has reused the memory)
-  auto first = t->ranges.lower_bound(lo);
-  if (first != t->ranges.begin()) {
-    auto prev = std::prev(first);
-    if (prev->second > lo) first = prev;
+  std::vector<std::pair<unsigned long long, unsigned long long>> keep;
+  while (it != t->ranges.end() && it->first < hi) {
+    if (it->first < lo) keep.emplace_back(it->first, lo);
+    if (it->second > hi) keep.emplace_back(hi, it->second);
+    it = t->ranges.erase(it);
   }
-  while (first != t->ranges.end() && first->first < hi) first = t->ranges.erase(first);
+  for (auto& r : keep) t->ranges[r.first] = r.second;
   t->ranges[lo] = hi;
   chk::upload(*t);
 }

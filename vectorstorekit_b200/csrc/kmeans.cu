@@ -256,7 +256,9 @@ int32_t kmeans_dev(Ctx* ctx, const float* rows, int64_t n, int32_t dim, int32_t 
   while (it < max_iters && !converged) {
     if (tc) VSK_TRY(tensor_assign(ctx, &ta, rows, (const float*)cur, k, assign, (float*)dist, it > 0));
     else VSK_TRY(assign_rows_fp32(ctx, rows, n, dim, (const float*)cur, k, assign, (float*)dist));
+    tl_mark(ctx, "assign_done");
     VSK_TRY(launch_stable_group(ctx, assign, n, k, (int32_t*)order, (int64_t*)offsets));
+    tl_mark(ctx, "group_rows");
     {
       // segments per centroid -> first segment of each centroid -> partial sums -> means
       const int64_t max_segs = n / kSegRows + k + 1;
@@ -275,6 +277,7 @@ int32_t kmeans_dev(Ctx* ctx, const float* rows, int64_t n, int32_t dim, int32_t 
     }
     sum_partial_kernel<<<1024, 256, 0, ctx->stream>>>((const float*)dist, n, (double*)partial);
     sum_final_kernel<<<1, 1024, 0, ctx->stream>>>((const double*)partial, 1024, (float*)inert);
+    tl_mark(ctx, "update_done");
     ctx->stats.kernel_launches += 3;
     VSK_CUDA(ctx, cudaGetLastError());
     std::swap(cur, nxt);

@@ -41,8 +41,103 @@ constexpr int SEL_ITEMS = 8;  // keys per thread, held in registers
 // (1-based, ascending).  One pass per byte from the top; a pass histograms the byte among the keys that
 // still match the decided prefix.  After the four value bytes, if the rest of the rank is made up of ALL
 // keys with exactly that value, the id bytes need not be resolved and the pivot is (value, max id).
+//
+// Fast path first.  The values of one list sit in a narrow band (everything at or below the query's threshold), so the
+// top bytes of the keys are the same for all of them and byte-wise passes from the top spend two of their four rounds
+// learning nothing.  The fast path takes the smallest value v0 of the list, histograms the 8 most significant bits in
+// which (value - v0) varies, and descends 8 bits at a time inside the bin that holds the rank until that bin has at
+// most 32 keys; those go to shared memory and one warp finds the wanted one by counting, for every key, the keys
+// below it.  Typical lists (a few hundred keys) need one histogram.  A bin of more than 32 keys that share their
+// whole 32-bit value (bulk ties) falls back to the byte-wise passes below, which also resolve the row bits.
 __device__ __forceinline__ uint64_t block_radix_select(const uint64_t (&key)[SEL_ITEMS], int rank, int* hist,
                                                        int* s_bin, int* s_less, int* s_in_bin) {
+  __shared__ unsigned f_min, f_max;
+  __shared__ int f_n;
+  __shared__ unsigned long long f_small[32];
+  __shared__ unsigned long long f_pivot;
+  {
+    unsigned lo = 0xffffffffu, hi = 0u;
+#pragma unroll
+    for (int i = 0; i < SEL_ITEMS; ++i)
+      if (key[i] != kEmptyKey) {
+        const unsigned v = (unsigned)(key[i] >> 32);
+        lo = min(lo, v);
+        hi = max(hi, v);
+      }
+    lo = __reduce_min_sync(0xffffffffu, lo);
+    hi = __reduce_max_sync(0xffffffffu, hi);
+    if (threadIdx.x == 0) { f_min = 0xffffffffu; f_max = 0u; f_n = 0; }
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0;
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) { atomicMin(&f_min, lo); atomicMax(&f_max, hi); }
+    __syncthreads();
+    const unsigned v0 = f_min, range = f_max - v0;
+    if (f_max >= v0 && range != 0u) {
+      int shift = max(0, 32 - __clz(range) - 8);   // the digit of the first level: (u >> shift), at most 8 bits
+      int width = 32 - __clz(range) - shift;
+      unsigned prefix = 0u;                        // u >> (shift + width) of the keys still in play
+      int r = rank;
+      for (int level = 0;; ++level) {
+        const unsigned dmask = (1u << width) - 1u;
+#pragma unroll
+        for (int i = 0; i < SEL_ITEMS; ++i)
+          if (key[i] != kEmptyKey) {
+            const unsigned u = (unsigned)(key[i] >> 32) - v0;
+            if (level == 0 || (u >> (shift + width)) == prefix) atomicAdd(&hist[(u >> shift) & dmask], 1);
+          }
+        __syncthreads();
+        if (threadIdx.x < 32) {
+          int local[8], sum = 0;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) { local[j] = hist[threadIdx.x * 8 + j]; sum += local[j]; }
+          int incl = sum;
+#pragma unroll
+          for (int o = 1; o < 32; o <<= 1) {
+            const int t = __shfl_up_sync(0xffffffffu, incl, o);
+            if ((int)threadIdx.x >= o) incl += t;
+          }
+          int before = incl - sum;
+          if (before < r && r <= incl) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              if (before < r && r <= before + local[j]) {
+                *s_bin = threadIdx.x * 8 + j;
+                *s_less = before;
+                *s_in_bin = local[j];
+              }
+              before += local[j];
+            }
+          }
+        }
+        __syncthreads();
+        const int bin = *s_bin, less = *s_less, in_bin = *s_in_bin;
+        r -= less;
+        const unsigned want = (level == 0 ? 0u : (prefix << width)) | (unsigned)bin;   // u >> shift of the bin's keys
+        if (in_bin <= 32) {
+#pragma unroll
+          for (int i = 0; i < SEL_ITEMS; ++i)
+            if (key[i] != kEmptyKey && (((unsigned)(key[i] >> 32) - v0) >> shift) == want)
+              f_small[atomicAdd(&f_n, 1)] = key[i];
+          __syncthreads();
+          if (threadIdx.x < 32) {
+            const unsigned long long mine = (int)threadIdx.x < in_bin ? f_small[threadIdx.x] : kEmptyKey;
+            int below = 0;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) below += __shfl_sync(0xffffffffu, mine, j) < mine;
+            if ((int)threadIdx.x < in_bin && below == r - 1) f_pivot = mine;
+          }
+          __syncthreads();
+          return f_pivot;
+        }
+        if (shift == 0) break;   // more than 32 keys with one and the same value: the byte-wise passes resolve the rows
+        prefix = want;
+        width = min(8, shift);
+        shift -= width;
+        for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0;
+        __syncthreads();
+      }
+    }
+  }
   uint64_t prefix = 0, mask = 0;
   for (int shift = 56; shift >= 0; shift -= 8) {
     for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0;
@@ -90,7 +185,7 @@ __device__ __forceinline__ uint64_t block_radix_select(const uint64_t (&key)[SEL
 // lengths of the launch (SelectArgs::max_count); a list that is longer all the same is flagged like an
 // overflowed list and its query is re-run.
 template <int NT>
-__global__ void __launch_bounds__(NT) select_kernel(SelectArgs a) {
+__global__ void __launch_bounds__(NT, NT == 128 ? 10 : 2) select_kernel(SelectArgs a) {
   extern __shared__ __align__(16) uint64_t s[];
   constexpr int CAPACITY = NT * SEL_ITEMS;
   __shared__ int hist[256];

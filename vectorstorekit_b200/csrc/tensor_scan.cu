@@ -549,8 +549,8 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 //   warps 2.. epilogue (16 warps): the centroid's |c|^2 / 2 rides inside the contraction (fold columns), so a value
 //             is alpha * accumulator and the test for "no hit in these 32 columns" is one max per value.
 //             Threshold mode: a hit (rare: the threshold is the row's previous assignment plus the error band)
-//             is appended to the row's short list with an atomic slot; arg-min mode (first iteration): one
-//             atomicMin per row, centroid block and column part.
+//             is logged as {row, centroid} in the CTA's own stretch of a log, its slot taken from a shared-memory
+//             counter; arg-min mode (first iteration): one atomicMin per row, centroid block and column part.
 // Every mbarrier wait is bounded like the general kernel's.
 constexpr int AS_EW = 16;
 constexpr int AS_THREADS = 64 + 32 * AS_EW;
@@ -821,6 +821,7 @@ assign_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
 
 // One warp per logged hit: the exact squared distance of the row to the listed centroid, direct fp32 formula, merged
 // into best[row] - smallest (value, centroid), the reference's strict '<' scan (KMeansClustering.swift:283-288).
+template <bool VEC>
 __global__ void assign_log_exact_kernel(const float* __restrict__ x, int dim, const float* __restrict__ cent,
                                         const uint2* __restrict__ log, const int32_t* __restrict__ log_count, int64_t log_cap,
                                         unsigned long long* __restrict__ best) {
@@ -828,7 +829,44 @@ __global__ void assign_log_exact_kernel(const float* __restrict__ x, int dim, co
   const int cnt = log_count[cta];
   const uint2* mine = log + (int64_t)cta * log_cap;
   const int lane = threadIdx.x & 31;
-  for (int e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); e < cnt; e += gridDim.x * (blockDim.x >> 5)) {
+  const int warps = gridDim.x * (blockDim.x >> 5);
+  const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (VEC) {
+    // 16-byte loads (dim a multiple of 4, aligned rows), two hits per step: four independent loads in flight per lane
+    const int nv = dim >> 2;
+    for (int e = 2 * w; e < cnt; e += 2 * warps) {
+      const bool two = e + 1 < cnt;
+      const uint2 h0 = mine[e], h1 = two ? mine[e + 1] : h0;
+      const float4* x0 = reinterpret_cast<const float4*>(x + (int64_t)h0.x * dim);
+      const float4* c0 = reinterpret_cast<const float4*>(cent + (int64_t)h0.y * dim);
+      const float4* x1 = reinterpret_cast<const float4*>(x + (int64_t)h1.x * dim);
+      const float4* c1 = reinterpret_cast<const float4*>(cent + (int64_t)h1.y * dim);
+      float s0 = 0.f, s1 = 0.f;
+      for (int i = lane; i < nv; i += 32) {
+        const float4 a0 = __ldg(x0 + i), b0 = __ldg(c0 + i), a1 = __ldg(x1 + i), b1 = __ldg(c1 + i);
+        float d;
+        d = a0.x - b0.x; s0 = fmaf(d, d, s0);
+        d = a0.y - b0.y; s0 = fmaf(d, d, s0);
+        d = a0.z - b0.z; s0 = fmaf(d, d, s0);
+        d = a0.w - b0.w; s0 = fmaf(d, d, s0);
+        d = a1.x - b1.x; s1 = fmaf(d, d, s1);
+        d = a1.y - b1.y; s1 = fmaf(d, d, s1);
+        d = a1.z - b1.z; s1 = fmaf(d, d, s1);
+        d = a1.w - b1.w; s1 = fmaf(d, d, s1);
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        s0 += __shfl_xor_sync(0xffffffffu, s0, o);
+        s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+      }
+      if (lane == 0) {
+        atomicMin(best + h0.x, (unsigned long long)make_key(s0, h0.y));
+        if (two) atomicMin(best + h1.x, (unsigned long long)make_key(s1, h1.y));
+      }
+    }
+    return;
+  }
+  for (int e = w; e < cnt; e += warps) {
     const uint2 h = mine[e];
     const float* xr = x + (int64_t)h.x * dim;
     const float* cr = cent + (int64_t)h.y * dim;
@@ -1417,12 +1455,56 @@ __global__ void assign_threshold_kernel(const unsigned long long* __restrict__ b
 // |c_p|^2 - 2 x.c_p of the centroid the row was assigned to last time, the nearest centroid c* has exact value
 // <= u, hence coarse value <= u + eps.  One warp per row computes u = sum (x-c_p)^2 - |x|^2 in fp32; the
 // threshold is u + 2 eps (the second eps covers the fp32 rounding of u itself).  This replaces pass 1.
+template <bool VEC>
 __global__ void assign_prev_threshold_kernel(const float* __restrict__ x, int64_t n, int dim, const float* __restrict__ cent,
                                              const int32_t* __restrict__ prev, const float* __restrict__ eps,
                                              float* __restrict__ thr, int32_t* __restrict__ count) {
+  const int lane = threadIdx.x & 31;
+  if (VEC) {
+    // four rows per warp, 16-byte loads (dim a multiple of 4, aligned rows): eight independent loads in flight per lane
+    const int64_t row0 = ((int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * 4;
+    if (row0 >= n) return;
+    const int nv = dim >> 2;
+    const float4* xr[4];
+    const float4* cr[4];
+    float d2[4], x2[4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const int64_t row = min(row0 + r, n - 1);
+      xr[r] = reinterpret_cast<const float4*>(x + row * dim);
+      cr[r] = reinterpret_cast<const float4*>(cent + (int64_t)prev[row] * dim);
+      d2[r] = 0.f;
+      x2[r] = 0.f;
+    }
+    for (int i = lane; i < nv; i += 32) {
+      float4 a[4], b[4];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) { a[r] = __ldg(xr[r] + i); b[r] = __ldg(cr[r] + i); }
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        float d;
+        d = a[r].x - b[r].x; d2[r] = fmaf(d, d, d2[r]); x2[r] = fmaf(a[r].x, a[r].x, x2[r]);
+        d = a[r].y - b[r].y; d2[r] = fmaf(d, d, d2[r]); x2[r] = fmaf(a[r].y, a[r].y, x2[r]);
+        d = a[r].z - b[r].z; d2[r] = fmaf(d, d, d2[r]); x2[r] = fmaf(a[r].z, a[r].z, x2[r]);
+        d = a[r].w - b[r].w; d2[r] = fmaf(d, d, d2[r]); x2[r] = fmaf(a[r].w, a[r].w, x2[r]);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        d2[r] += __shfl_xor_sync(0xffffffffu, d2[r], o);
+        x2[r] += __shfl_xor_sync(0xffffffffu, x2[r], o);
+      }
+      if (lane == 0 && row0 + r < n) {
+        thr[row0 + r] = (d2[r] - x2[r]) + 2.0f * eps[row0 + r] + 4.0f * 5.9604645e-8f * (d2[r] + x2[r]);
+        count[row0 + r] = 0;
+      }
+    }
+    return;
+  }
   const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= n) return;
-  const int lane = threadIdx.x & 31;
   const float* xr = x + row * dim;
   const float* cr = cent + (int64_t)prev[row] * dim;
   float d2 = 0.f, x2 = 0.f;
@@ -1440,6 +1522,16 @@ __global__ void assign_prev_threshold_kernel(const float* __restrict__ x, int64_
     thr[row] = (d2 - x2) + 2.0f * eps[row] + 4.0f * 5.9604645e-8f * (d2 + x2);
     count[row] = 0;
   }
+}
+
+// launches the vector form when the rows allow 16-byte loads
+static void launch_prev_threshold(Ctx* ctx, const float* rows, int64_t n, int dim, const float* centroids, const int32_t* assign,
+                                  const float* eps, float* thr, int32_t* count) {
+  const bool vec = dim % 4 == 0 && ((uintptr_t)rows & 15) == 0 && ((uintptr_t)centroids & 15) == 0;
+  if (vec)
+    assign_prev_threshold_kernel<true><<<(unsigned)ceil_div(n, 32), 256, 0, ctx->stream>>>(rows, n, dim, centroids, assign, eps, thr, count);
+  else
+    assign_prev_threshold_kernel<false><<<(unsigned)ceil_div(n, 8), 256, 0, ctx->stream>>>(rows, n, dim, centroids, assign, eps, thr, count);
 }
 
 // one warp per data row: exact squared distances to the listed centroids
@@ -2441,7 +2533,7 @@ int32_t tensor_assign(Ctx* ctx, TensorAssign* ta, const float* rows, const float
     sa.best = ta->best;
     sa.err = (int32_t*)(sm + 5);
     if (assign_holds_previous) {
-      assign_prev_threshold_kernel<<<(unsigned)ceil_div(n, 8), 256, 0, ctx->stream>>>(rows, n, dim, centroids, assign, eps, ta->thr, ta->count);
+      launch_prev_threshold(ctx, rows, n, dim, centroids, assign, eps, ta->thr, ta->count);
     } else {
       VSK_CUDA(ctx, cudaMemsetAsync(ta->best, 0xff, (size_t)n * sizeof(unsigned long long), ctx->stream));
       VSK_TRY(launch_assign_scan<SCAN_ARGMIN>(ctx, mr, mc, sa));
@@ -2450,8 +2542,13 @@ int32_t tensor_assign(Ctx* ctx, TensorAssign* ta, const float* rows, const float
     VSK_CUDA(ctx, cudaMemsetAsync(ta->best, 0xff, (size_t)n * sizeof(unsigned long long), ctx->stream));
     unsigned sgrid = 0;
     int64_t log_cap = 0;
+    tl_mark(ctx, "assign_thresholds");
     VSK_TRY(launch_assign_scan<SCAN_THRESHOLD>(ctx, mr, mc, sa, &sgrid, &log_cap));
-    assign_log_exact_kernel<<<dim3(64, sgrid), 256, 0, ctx->stream>>>(rows, dim, centroids, sa.log, sa.log_count, log_cap, ta->best);
+    if (dim % 4 == 0 && ((uintptr_t)rows & 15) == 0 && ((uintptr_t)centroids & 15) == 0)
+      assign_log_exact_kernel<true><<<dim3(64, sgrid), 256, 0, ctx->stream>>>(rows, dim, centroids, sa.log, sa.log_count, log_cap, ta->best);
+    else
+      assign_log_exact_kernel<false><<<dim3(64, sgrid), 256, 0, ctx->stream>>>(rows, dim, centroids, sa.log, sa.log_count, log_cap, ta->best);
+    tl_mark(ctx, "assign_exact");
     assign_log_decode_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, ctx->stream>>>(ta->best, n, assign, dist, ta->bad_rows, (int32_t*)(sm + 6));
     ctx->stats.kernel_launches += 3;
     VSK_CUDA(ctx, cudaGetLastError());
@@ -2474,7 +2571,7 @@ int32_t tensor_assign(Ctx* ctx, TensorAssign* ta, const float* rows, const float
   a.cand.flags = nullptr;
   a.cand.nq = n;
   if (assign_holds_previous) {
-    assign_prev_threshold_kernel<<<(unsigned)ceil_div(n, 8), 256, 0, ctx->stream>>>(rows, n, dim, centroids, assign, eps, ta->thr, ta->count);
+    launch_prev_threshold(ctx, rows, n, dim, centroids, assign, eps, ta->thr, ta->count);
   } else {
     VSK_CUDA(ctx, cudaMemsetAsync(ta->best, 0xff, (size_t)n * sizeof(unsigned long long), ctx->stream));
     a.mode = SCAN_ARGMIN;
