@@ -680,6 +680,12 @@ def main():
         roof.update(unit="TFLOP/s", achieved=b.flops * args.steps / secs / 1e12 if secs > 0 else None,
                     peak=pk["bf16_tflops"], peak_source=pk["source"] + " (cuBLAS bf16, sustained)")
         if wl["kind"] == "ivf":
+            # second view: a contraction this short (two or three K blocks) is paced by reading its accumulators out
+            # of tensor memory, 4 bytes per (query, row) pair, against the measured tcgen05.ld rate
+            pairs = b.flops / (2.0 * wl["dim"])
+            roof.update(tmem_readout={"unit": "TB/s", "achieved": 4.0 * pairs * args.steps / secs / 1e12 if secs > 0 else None,
+                                      "peak": dev.measure_peak("tmem_read") / 1e12,
+                                      "peak_source": "measured in this run: tcgen05.ld by 16 warps per SM (vsk_measure_peak)"})
             roof.update(algorithmic_query_major_gbs=b.bytes_per_query * nq * args.steps / secs / 1e9 if secs > 0 else None,
                         note="flops count the rows of the probed lists only (2 x queries x scanned rows x dim); with "
                              "d = 128 a tile's MMAs take 0.5 us and the epilogue sets the pace, so the fraction of the "

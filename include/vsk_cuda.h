@@ -140,7 +140,9 @@ typedef struct vsk_tuning {
                                    the counterpart of commandBufferTimeout (Acceleration/Metal/MetalErrors.swift:30) */
   int32_t test_stall_scan;      /* testing only: 1 makes the next contraction launch leave one operand stage
                                    unfilled, so that a bounded wait runs out; resets itself to 0 */
-  int32_t reserved[8];
+  int32_t assign_stages;        /* measurement only: caps the data-tile stages of the k-means assignment kernel's operand
+                                   ring (0 = as many as fit) */
+  int32_t reserved[7];
 } vsk_tuning;
 
 /* --- context ------------------------------------------------------------------------------
@@ -175,9 +177,11 @@ int64_t vsk_schedule_chunk(int64_t seen, int32_t keep, int32_t level);
  * a synthetic kernel on the context's stream, best of five, CUDA events):
  *   VSK_PEAK_FP32_ISSUE   FP32 instructions per second, counted per thread (the Manhattan scan's bound)
  *   VSK_PEAK_SMEM_GATHER  4-byte shared-memory words per second at random addresses (the product-quantised scan's)
+ *   VSK_PEAK_TMEM_READ    bytes per second read out of tensor memory by tcgen05.ld (the bound of contractions with a
+ *                         short inner dimension: every accumulator is read once, 4 bytes per (row, centroid) pair)
  * The reference has no counterpart; its thread-configuration benchmark is the nearest relative
  * (Acceleration/Metal/MetalThreadConfigurationOptimizer.swift:430-440). */
-typedef enum vsk_peak { VSK_PEAK_FP32_ISSUE = 0, VSK_PEAK_SMEM_GATHER = 1 } vsk_peak;
+typedef enum vsk_peak { VSK_PEAK_FP32_ISSUE = 0, VSK_PEAK_SMEM_GATHER = 1, VSK_PEAK_TMEM_READ = 2 } vsk_peak;
 int32_t vsk_measure_peak(vsk_ctx* ctx, int32_t what, double* per_second);
 /* The checked build variant (libvsk_cuda_checked.so, `python -m vectorstorekit_b200.build --checked`): every global
  * load, store and atomic of every kernel is range-tested against the device buffers the library allocated (with the

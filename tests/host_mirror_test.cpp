@@ -64,6 +64,21 @@ int main() {
     } catch (const vsk::Error&) {
     }
   }
+  // the caller's layer: string ids and metadata back, the filter as a bit (the reference's filter test:
+  // category == "A" keeps v1 and v3, Tests/VectorStoreKitTests/IVFIndexTests.swift:536-590)
+  {
+    vsk::VectorStore store(dev, 4, vsk::DistanceMetric::euclidean, true);
+    const uint64_t categoryA = 1;
+    store.add({{"v1", {1, 0, 0, 0}, "{\"category\":\"A\"}", categoryA},
+               {"v2", {0.9f, 0.1f, 0, 0}, "{\"category\":\"B\"}", 0},
+               {"v3", {0, 1, 0, 0}, "{\"category\":\"A\"}", categoryA}});
+    auto all = store.search(q, 3);
+    if (all.size() != 3 || all[0].id != "v1" || all[1].id != "v2" || all[2].id != "v3") return 15;
+    auto onlyA = store.search(q, 3, categoryA);
+    if (onlyA.size() != 2 || onlyA[0].id != "v1" || onlyA[1].id != "v3" ||
+        onlyA[1].metadata.find("\"A\"") == std::string::npos) return 16;
+    if (std::fabs(onlyA[1].distance - std::sqrt(2.0f)) > 1e-4f) return 17;
+  }
   // a communicator of one rank: the sharded call is the plain search, in both layouts
   dev->joinCommunicator(1, 0, {});
   int64_t first = -1;

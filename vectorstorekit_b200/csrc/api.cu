@@ -807,7 +807,8 @@ int32_t vsk_tuning_set(vsk_ctx* c, const vsk_tuning* in) {
   Ctx* ctx = reinterpret_cast<Ctx*>(c);
   if (!ctx || !in) return VSK_ERR_INVALID_INPUT;
   if (in->chunk_growth < 1 || in->ivf_pilot_tiles < 1 || in->ivf_pilot_tiles > 16 || in->dense_rows < 0 ||
-      in->dense_rows > kCandCap || in->overlap_min_queries < 0 || in->wait_limit_log2 < 0 || in->wait_limit_log2 > 30)
+      in->dense_rows > kCandCap || in->overlap_min_queries < 0 || in->wait_limit_log2 < 0 || in->wait_limit_log2 > 30 ||
+      in->assign_stages < 0 || in->assign_stages > 8)
     return fail(ctx, VSK_ERR_INVALID_INPUT, "tuning value out of range");
   ctx->tuning = *in;
   return VSK_OK;

@@ -97,6 +97,33 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32]) {
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// The same load without the wait: several loads can be in flight before one tc_ld_wait.
+__device__ __forceinline__ void tc_ld32_issue(uint32_t taddr, float (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]), "=f"(v[4]), "=f"(v[5]), "=f"(v[6]), "=f"(v[7]), "=f"(v[8]),
+        "=f"(v[9]), "=f"(v[10]), "=f"(v[11]), "=f"(v[12]), "=f"(v[13]), "=f"(v[14]), "=f"(v[15]), "=f"(v[16]),
+        "=f"(v[17]), "=f"(v[18]), "=f"(v[19]), "=f"(v[20]), "=f"(v[21]), "=f"(v[22]), "=f"(v[23]), "=f"(v[24]),
+        "=f"(v[25]), "=f"(v[26]), "=f"(v[27]), "=f"(v[28]), "=f"(v[29]), "=f"(v[30]), "=f"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// largest of 32 values by a tree (depth 5) instead of a chain of 31 dependent operations
+__device__ __forceinline__ float max32(const float (&v)[32]) {
+  float m[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) m[i] = fmaxf(v[2 * i], v[2 * i + 1]);
+#pragma unroll
+  for (int w = 8; w > 0; w >>= 1)
+#pragma unroll
+    for (int i = 0; i < w; ++i) m[i] = fmaxf(m[i], m[i + w]);
+  return m[0];
+}
+
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 fp16), 128-byte
 // swizzled, rows packed: 8-row groups 1024 bytes apart.
 __device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {

@@ -79,6 +79,7 @@ struct TcArgs {
   int64_t nq;                 // queries (list positions)
   int64_t row_begin, row_end; // rows of this launch
   int32_t kblocks;            // dim16 / 64
+  int32_t k16_last;           // K16 steps of the last K block that hold operand columns (the rest is padding); 0 = all 4
   int mode;                   // SCAN_DENSE or SCAN_THRESHOLD
   const float* alpha;         // device scalar: value = alpha * acc + beta[row]
   const float* beta;          // [n] or null (treated as 0)
@@ -235,10 +236,11 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           tc_fence_after();
           const uint64_t adesc = make_desc(smem_u32(sm->ring + s * STAGE_BYTES));
           const uint64_t bdesc = make_desc(smem_u32(sm->ring + s * STAGE_BYTES + A_BYTES));
+          const int nk4 = (kb == a.kblocks - 1 && a.k16_last > 0) ? a.k16_last : TK / 16;
 #pragma unroll
           for (int k4 = 0; k4 < TK / 16; ++k4) {
             // 16 fp16 = 32 bytes further along K inside the swizzle atom: +2 in 16-byte units
-            tc_mma(tmem_d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), kIdesc, (kb | k4) ? 1u : 0u);
+            if (k4 < nk4) tc_mma(tmem_d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), kIdesc, (kb | k4) ? 1u : 0u);
           }
           tc_commit(&sm->empty[s]);   // the stage is free once these MMAs have read it
           if (++s == STAGES) { s = 0; ph ^= 1; }
@@ -576,6 +578,8 @@ struct AsArgs {
   int64_t n;                  // data rows
   int32_t k;                  // centroids
   int32_t kblocks;            // dim16 / 64, <= AS_MAX_KB
+  int32_t k16_last;           // K16 steps of the last K block that hold operand columns; 0 = all 4
+  int32_t max_stages;         // measurement: cap on the data-tile stages (0 = as many as fit)
   int32_t groups;             // CTAs per centroid block (1 when there are more blocks than CTAs)
   const float* alpha;         // value = alpha * accumulator = |c|^2 - 2 x.c
   const float* thr;           // [n] SCAN_THRESHOLD: a centroid is listed for a row iff value <= thr[row]
@@ -601,7 +605,12 @@ assign_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
   const int nb = (a.k + TN - 1) / TN;                       // centroid blocks
   const int64_t qtiles = (a.n + TM - 1) / TM;               // data tiles
   const int bres_bytes = a.kblocks * B_BYTES;
-  const int stages = min(AS_MAX_STAGES, (AS_RING_BYTES - bres_bytes) / A_BYTES);
+  // A stage of the data ring holds ALL K blocks of a data tile when two such stages fit (one wait, one batch of MMAs
+  // and one commit per tile instead of per K block); otherwise, or when max_stages asks for it, one K block.
+  const int skb = (a.max_stages == 0 && 2 * a.kblocks * A_BYTES <= AS_RING_BYTES - bres_bytes) ? a.kblocks : 1;
+  const int stage_bytes = skb * A_BYTES;
+  int stages = min(AS_MAX_STAGES, (AS_RING_BYTES - bres_bytes) / stage_bytes);
+  if (a.max_stages > 0) stages = max(2, min(stages, a.max_stages));
   // this CTA's centroid blocks and its share of the data tiles
   const bool one_block = a.groups >= 1 && nb <= (int)gridDim.x;
   const int b_first = one_block ? (int)(blockIdx.x % nb) : (int)blockIdx.x;
@@ -656,10 +665,11 @@ assign_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
         b_issued_ph = bph;
         bph ^= 1;
         for (int64_t t = t_first; ok && t < qtiles; t += t_step) {
-          for (int kb = 0; kb < a.kblocks; ++kb) {
+          for (int kb = 0; kb < a.kblocks; kb += skb) {
             if (!mbar_wait(&sm->a_empty[s], ph ^ 1, &sm->abort_flag, a.err, 1, wait_limit)) { ok = false; break; }
-            mbar_expect_tx(&sm->a_full[s], A_BYTES);
-            tma_load_2d(a_ring + s * A_BYTES, &map_x, &sm->a_full[s], kb * TK, (int32_t)(t * TM));
+            mbar_expect_tx(&sm->a_full[s], (uint32_t)stage_bytes);
+            for (int j = 0; j < skb; ++j)
+              tma_load_2d(a_ring + s * stage_bytes + j * A_BYTES, &map_x, &sm->a_full[s], (kb + j) * TK, (int32_t)(t * TM));
             issued |= 1u << s;
             issued_ph = (issued_ph & ~(1u << s)) | (ph << s);
             if (++s == stages) { s = 0; ph ^= 1; }
@@ -696,14 +706,18 @@ assign_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
           if (!mbar_wait(&sm->tmem_empty[acc], aph ^ 1, &sm->abort_flag, a.err, 2, wait_limit)) { ok = false; break; }
           tc_fence_after();
           const uint32_t tmem_d = tmem_base + (uint32_t)(acc * TN);
-          for (int kb = 0; kb < a.kblocks; ++kb) {
+          for (int kb0 = 0; kb0 < a.kblocks; kb0 += skb) {
             if (!mbar_wait(&sm->a_full[s], ph, &sm->abort_flag, a.err, 3, wait_limit)) { ok = false; break; }
             tc_fence_after();
-            const uint64_t adesc = make_desc(smem_u32(a_ring + s * A_BYTES));
-            const uint64_t bdesc = make_desc(smem_u32(sm->ring + kb * B_BYTES));
+            for (int j = 0; j < skb; ++j) {
+              const int kb = kb0 + j;
+              const uint64_t adesc = make_desc(smem_u32(a_ring + s * stage_bytes + j * A_BYTES));
+              const uint64_t bdesc = make_desc(smem_u32(sm->ring + kb * B_BYTES));
+              const int nk4 = (kb == a.kblocks - 1 && a.k16_last > 0) ? a.k16_last : TK / 16;
 #pragma unroll
-            for (int k4 = 0; k4 < TK / 16; ++k4)
-              tc_mma(tmem_d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), kIdesc, (kb | k4) ? 1u : 0u);
+              for (int k4 = 0; k4 < TK / 16; ++k4)
+                if (k4 < nk4) tc_mma(tmem_d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), kIdesc, (kb | k4) ? 1u : 0u);
+            }
             tc_commit(&sm->a_empty[s]);
             if (++s == stages) { s = 0; ph ^= 1; }
           }
@@ -747,6 +761,42 @@ assign_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
         if (!got) { ok = false; break; }
         tc_fence_after();
         const uint32_t trow = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * TN);
+        if (MODE == SCAN_THRESHOLD) {
+          // Both 32-column groups of this warp are read at once and the accumulator is handed back BEFORE the values
+          // are looked at: the next tile's MMAs never wait for the tests below (with a short contraction the
+          // epilogue's own latency, not the MMAs and not the operand fill, sets the pace of this kernel).
+          static_assert(GROUPS == 2, "two groups per warp");
+          float v0[32], v1[32];
+          tc_ld32_issue(trow + (uint32_t)(c0 * 32), v0);
+          tc_ld32_issue(trow + (uint32_t)((c0 + 1) * 32), v1);
+          tc_ld_wait();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&sm->tmem_empty[acc]);
+          const int left0 = a.k - (col_base + c0 * 32), left1 = left0 - 32;
+          // value = alpha * accumulator with alpha < 0: the smallest value is alpha times the largest accumulator
+          const bool mine0 = qok && left0 > 0 && max32(v0) * alpha <= thr;
+          const bool mine1 = qok && left1 > 0 && max32(v1) * alpha <= thr;
+          const bool partial = (left0 > 0 && left0 < 32) || (left1 > 0 && left1 < 32);   // the block's last, short group
+          if (!partial && !__any_sync(0xffffffffu, mine0 || mine1)) continue;
+#pragma unroll
+          for (int g = 0; g < 2; ++g) {
+            const int left = g == 0 ? left0 : left1;
+            if (left <= 0 || !(g == 0 ? mine0 : mine1)) continue;
+            const uint32_t colmask = left >= 32 ? 0xffffffffu : ((1u << left) - 1u);
+            uint32_t bits = 0;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) bits |= ((g == 0 ? v0[j] : v1[j]) * alpha <= thr) ? (1u << j) : 0u;
+            bits &= colmask;
+            while (bits) {   // one or two hits as a rule
+              const int j = __ffs((int)bits) - 1;
+              bits &= bits - 1u;
+              const int slot = atomicAdd(&sm->log_n, 1);
+              if (slot < a.log_cap) my_log[slot] = make_uint2((uint32_t)q, (uint32_t)(col_base + (c0 + g) * 32 + j));
+            }
+          }
+          continue;
+        }
         float bv = CUDART_INF_F;   // SCAN_ARGMIN: this thread's best over its columns of the block
         int bj = 0;
 #pragma unroll 1
@@ -928,7 +978,7 @@ __global__ void choose_scale_kernel(const unsigned* absmax, int cosine, float* s
       s = ldexpf(1.f, 14 - e);
     }
   }
-  if (fold) s = fmaxf(fminf(s, ldexpf(1.f, fold_exp + 15)), ldexpf(1.f, fold_exp - 14));
+  if (fold) s = fmaxf(fminf(s, ldexpf(1.f, fold_exp + 13)), ldexpf(1.f, fold_exp - 14));   // 4u <= 2^15, 2u normal
   *scale = s;
 }
 
@@ -936,15 +986,23 @@ __global__ void choose_scale_kernel(const unsigned* absmax, int cosine, float* s
 // zeros to dim16, and the measured quantities the error bound needs.
 //   aux[row]   = |x|^2 (euclidean), unused otherwise
 //   nrm16[row] = |x'|, err16[row] = |s*x^ - x'|   (optional per-row outputs, used for queries)
-// Euclidean operands can carry the per-row term of the value inside the contraction.  The last 48 columns of the
-// padded width then hold, on the row side, -(s_x |x|^2 / 2) 2^exp split into three fp16 pieces (each piece stored 16
-// times as piece / 16, which keeps it in range), and on the query side the constant u = s_q 2^-exp (a power of two,
-// exact in fp16): their products add up to -s_q s_x |x|^2 / 2, so the accumulator is s_q s_x (q.x - |x|^2 / 2) and
-// the value alpha * accumulator needs no per-row term in the epilogue.
-constexpr int kFoldCols = 48;
+// Euclidean operands can carry the per-row term of the value inside the contraction.  Sixteen columns - one K16
+// step of the MMA, placed right behind the data columns (fold_col0) - hold, on the row side, R = -(s_x |x|^2 / 2) 2^exp
+// split into three fp16 pieces p0 + p1 + p2 = R / 16 (p0 in columns 0-3, p1 in 4-7, p2 in 8-15), and on the query
+// side the constants 4u (columns 0-7) and 2u (columns 8-15), u = s_q 2^-exp a power of two: the sixteen products add
+// up to 16 u (p0 + p1 + p2) = -s_q s_x |x|^2 / 2, so the accumulator is s_q s_x (q.x - |x|^2 / 2) and the value
+// alpha * accumulator needs no per-row term in the epilogue.  Columns behind the sixteen are zero and the MMA issuer
+// skips K16 steps that hold nothing but padding (kvalid), so the term costs one K16 step, not a K block.
+constexpr int kFoldCols = 16;
+__host__ __device__ inline int fold_col0(int dim) { return (dim + 15) / 16 * 16; }
+// K16 steps of the last 64-column K block that hold operand columns, for `kvalid` columns in a width of dim16
+inline int k16_last_of(int kvalid, int dim16) {
+  const int steps = (kvalid + 15) / 16, before = 4 * (dim16 / 64 - 1);
+  return std::max(1, std::min(4, steps - before));
+}
 struct FoldArgs {
-  int side;   // 0: none, 1: rows (pieces of the term), 2: queries (the constant)
-  int col0;   // first of the kFoldCols columns
+  int side;   // 0: none, 1: rows (pieces of the term), 2: queries (the constants)
+  int col0;   // first of the kFoldCols columns (fold_col0(dim))
   int exp;
   const int* exp_dev = nullptr;   // when given, the exponent is read from device memory instead
 };
@@ -972,7 +1030,7 @@ __global__ void prep_rows_kernel(const float* __restrict__ x, int64_t n, int dim
     float t = 0.f;
     if (i < dim) t = (METRIC == VSK_METRIC_COSINE) ? (__ldg(p + i) * inv) * s : __ldg(p + i) * s;
     const __half h = __float2half_rn(t);
-    if (fold.side == 0 || i < fold.col0) out[row * dim16 + i] = h;
+    if (fold.side == 0 || i < fold.col0 || i >= fold.col0 + kFoldCols) out[row * dim16 + i] = h;
     const float back = __half2float(h);
     n2 = fmaf(back, back, n2);
     const float e = t - back;
@@ -988,13 +1046,13 @@ __global__ void prep_rows_kernel(const float* __restrict__ x, int64_t n, int dim
     const __half p1 = __float2half_rn(r1 * 0.0625f);
     const float r2 = r1 - 16.0f * __half2float(p1);
     const __half p2 = __float2half_rn(r2 * 0.0625f);
-    for (int i = lane; i < kFoldCols; i += 32) {
-      const __half p = i < 16 ? p0 : (i < 32 ? p1 : p2);
-      out[row * dim16 + fold.col0 + i] = __hneg(p);
+    if (lane < kFoldCols) {
+      const __half p = lane < 4 ? p0 : (lane < 8 ? p1 : p2);
+      out[row * dim16 + fold.col0 + lane] = __hneg(p);
     }
   } else if (fold.side == 2) {
-    const __half u = __float2half_rn(ldexpf(s, -fold_exp));
-    for (int i = lane; i < kFoldCols; i += 32) out[row * dim16 + fold.col0 + i] = u;
+    // 4u against the four copies of p0 and of p1, 2u against the eight copies of p2
+    if (lane < kFoldCols) out[row * dim16 + fold.col0 + lane] = __float2half_rn(ldexpf(s, (lane < 8 ? 2 : 1) - fold_exp));
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
@@ -1290,8 +1348,8 @@ int32_t tensor_prepare(Index* ix) {
   // Folding the per-row term into the operands (FoldArgs) pays where the epilogue, not the MMAs, sets the pace
   // (up to four K blocks), and is free where the padding already has room for it.
   ix->fold16 = ctx->tuning.fold_row_term != 0 && ix->kind != INDEX_FLAT_I8 && ix->metric == VSK_METRIC_EUCLIDEAN &&
-               (ix->dim16 / TK <= 4 || ix->dim16 - ix->dim >= kFoldCols);
-  if (ix->fold16 && ix->dim16 - ix->dim < kFoldCols) ix->dim16 += TK;
+               (ix->dim16 / TK <= 4 || ix->dim16 - fold_col0(ix->dim) >= kFoldCols);
+  if (ix->fold16 && ix->dim16 - fold_col0(ix->dim) < kFoldCols) ix->dim16 += TK;
   VSK_TRY(dev_alloc(ctx, (void**)&ix->rows16, (size_t)ix->n * ix->dim16 * sizeof(__half)));
   VSK_TRY(dev_alloc(ctx, (void**)&ix->row_aux, (size_t)ix->n * sizeof(float)));
   void* p;
@@ -1333,7 +1391,7 @@ int32_t tensor_prepare(Index* ix) {
     ix->fold_exp = std::max(-100, std::min(100, e));
     ix->fold_bmax = 0.5f * hmax;
     if (!std::isfinite(top)) ix->fold16 = false;   // the plain form copes with what overflows here no better, but is the known path
-    fold = FoldArgs{ix->fold16 ? 1 : 0, ix->dim16 - kFoldCols, ix->fold_exp};
+    fold = FoldArgs{ix->fold16 ? 1 : 0, fold_col0(ix->dim), ix->fold_exp};
   }
   switch (ix->metric) {
     case VSK_METRIC_EUCLIDEAN:
@@ -1597,7 +1655,7 @@ __global__ void scatter_best_kernel(const unsigned long long* __restrict__ best,
 
 // Scale of the centroid operand and exponent of the folded term for one Lloyd iteration (device-side, nothing is
 // read back).  With M = max |c|^2 / 2: the largest of the three fp16 pieces of s_c M 2^e / 16 should sit just below
-// 2^14, and the constant on the data side, u = s_x 2^-e, must be a normal fp16 number no larger than 2^15.  When u
+// 2^14, and the constants on the data side, 4u and 2u with u = s_x 2^-e, must be normal fp16 numbers: u <= 2^13.  When u
 // would be too large the centroid scale is lowered by the excess (the pieces shrink, e grows, u shrinks); the error
 // bound is computed from the measured residuals of whatever scale is used, so it stays valid.
 __global__ void assign_fold_setup_kernel(const unsigned* max_sq, float* scale_c, const float* scale_x, int* exp_out, float* u_out) {
@@ -1612,8 +1670,8 @@ __global__ void assign_fold_setup_kernel(const unsigned* max_sq, float* scale_c,
     int ex;
     frexpf(sx, &ex);                 // sx = 2^(ex-1)
     const int lu = (ex - 1) - e;     // log2 of u
-    if (lu > 15) {
-      const int shift = lu - 15;
+    if (lu > 13) {
+      const int shift = lu - 13;
       sc = ldexpf(sc, -shift);
       e += shift;
     } else if (lu < -14) {
@@ -1632,7 +1690,7 @@ __global__ void assign_fill_fold_kernel(__half* __restrict__ rows16, int64_t n, 
   if (i >= n * chunks) return;
   const int64_t row = i / chunks;
   const int c = (int)(i - row * chunks);
-  const __half h = __float2half_rn(*u);
+  const __half h = __float2half_rn(*u * (c == 0 ? 4.0f : 2.0f));   // columns 0-7: 4u, columns 8-15: 2u
   const __half2 h2 = __halves2half2(h, h);
   uint4 v;
   v.x = v.y = v.z = v.w = *reinterpret_cast<const unsigned*>(&h2);
@@ -1748,7 +1806,7 @@ int32_t prepare_query_operands(Index* ix, const float* q, int64_t nq, QueryOpera
     ctx->stats.kernel_launches++;
   }
   const bool fold = ix->fold16;
-  const FoldArgs qfold{fold ? 2 : 0, dim16 - kFoldCols, ix->fold_exp};
+  const FoldArgs qfold{fold ? 2 : 0, fold_col0(ix->dim), ix->fold_exp};
   choose_scale_kernel<<<1, 1, 0, ctx->stream>>>(q_absmax, cosine ? 1 : 0, q_scale, fold ? 1 : 0, ix->fold_exp);
   ctx->stats.kernel_launches++;
   BoundConsts bc{ix->scale16, ix->max_xnorm16, ix->max_xerr16, ix->max_xnorm, ix->min_xnorm_nz, dim16, fold ? ix->fold_bmax : 0.f};
@@ -1829,6 +1887,7 @@ int32_t tensor_search_begin(Index* ix, const float* q, int64_t nq, int32_t k, co
   TcArgs a{};
   a.nq = nq;
   a.kblocks = dim16 / TK;
+  a.k16_last = k16_last_of(fold ? fold_col0(ix->dim) + kFoldCols : ix->dim, dim16);
   a.alpha = qo.alpha;
   a.beta = (metric == VSK_METRIC_EUCLIDEAN && !fold) ? ix->row_aux : nullptr;
   a.cand = cand;
@@ -2092,6 +2151,7 @@ int32_t tensor_coarse_values(Index* ix, const float* q, int64_t nq, int64_t rows
   TcArgs a{};
   a.nq = nq;
   a.kblocks = ix->dim16 / TK;
+  a.k16_last = k16_last_of(ix->fold16 ? fold_col0(ix->dim) + kFoldCols : ix->dim, ix->dim16);
   a.alpha = qo.alpha;
   a.beta = (ix->metric == VSK_METRIC_EUCLIDEAN && !ix->fold16) ? ix->row_aux : nullptr;
   a.cand = cand;
@@ -2274,7 +2334,7 @@ int32_t ivf_tensor_search(Index* ix, const float* q, int64_t nq, const int64_t* 
   VSK_CUDA(ctx, cudaMemsetAsync(p, 0, 64, ctx->stream));
   absmax_kernel<<<296, 256, 0, ctx->stream>>>(q, nq * (int64_t)dim, q_absmax);
   const bool fold = ix->fold16;
-  const FoldArgs qfold{fold ? 2 : 0, dim16 - kFoldCols, ix->fold_exp};
+  const FoldArgs qfold{fold ? 2 : 0, fold_col0(ix->dim), ix->fold_exp};
   choose_scale_kernel<<<1, 1, 0, ctx->stream>>>(q_absmax, 0, q_scale, fold ? 1 : 0, ix->fold_exp);
   ctx->stats.kernel_launches += 2;
   BoundConsts bc{ix->scale16, ix->max_xnorm16, ix->max_xerr16, ix->max_xnorm, ix->min_xnorm_nz, dim16, fold ? ix->fold_bmax : 0.f};
@@ -2344,6 +2404,7 @@ int32_t ivf_tensor_search(Index* ix, const float* q, int64_t nq, const int64_t* 
   TcArgs a{};
   a.nq = nq;
   a.kblocks = dim16 / TK;
+  a.k16_last = k16_last_of(fold ? fold_col0(ix->dim) + kFoldCols : ix->dim, dim16);
   a.mode = SCAN_THRESHOLD;
   a.alpha = alpha;
   a.beta = fold ? nullptr : ix->row_aux;
@@ -2449,8 +2510,8 @@ int32_t tensor_assign_prepare(Ctx* ctx, const float* rows, int64_t n, int32_t di
   ta->dim = dim;
   // Short contractions keep a block of centroids resident (assign_scan_kernel): the operands then carry 48 more
   // columns for the folded |c|^2 / 2 term.  Longer ones (more than four k-blocks with those columns) take the general kernel.
-  ta->stationary = dim + kFoldCols <= AS_MAX_KB * TK;
-  ta->dim16 = (int32_t)(ceil_div(dim + (ta->stationary ? kFoldCols : 0), TK) * TK);
+  ta->stationary = fold_col0(dim) + kFoldCols <= AS_MAX_KB * TK;
+  ta->dim16 = (int32_t)(ceil_div(ta->stationary ? fold_col0(dim) + kFoldCols : dim, TK) * TK);
   VSK_TRY(dev_alloc(ctx, (void**)&ta->rows16, (size_t)n * ta->dim16 * sizeof(__half)));
   VSK_TRY(dev_alloc(ctx, (void**)&ta->stats, (size_t)n * 4 * sizeof(float)));
   // stationary kernel: `keys` is the hit log (a hit or two per row as a rule; six entries per row of room)
@@ -2507,9 +2568,9 @@ int32_t tensor_assign(Ctx* ctx, TensorAssign* ta, const float* rows, const float
     VSK_CUDA(ctx, cudaMemsetAsync(sm + 24, 0, 16, ctx->stream));
     max_sq_kernel<<<(unsigned)ceil_div(k, 8), 256, 0, ctx->stream>>>(centroids, k, dim, sm + 24);
     assign_fold_setup_kernel<<<1, 1, 0, ctx->stream>>>(sm + 24, fsm + 3, fsm + 1, (int*)sm + 25, fsm + 27);
-    assign_fill_fold_kernel<<<(unsigned)ceil_div(n * (kFoldCols / 8), 256), 256, 0, ctx->stream>>>(ta->rows16, n, dim16, dim16 - kFoldCols, fsm + 27);
+    assign_fill_fold_kernel<<<(unsigned)ceil_div(n * (kFoldCols / 8), 256), 256, 0, ctx->stream>>>(ta->rows16, n, dim16, fold_col0(dim), fsm + 27);
     ctx->stats.kernel_launches += 3;
-    cfold = FoldArgs{1, dim16 - kFoldCols, 0, (const int*)sm + 25};
+    cfold = FoldArgs{1, fold_col0(dim), 0, (const int*)sm + 25};
   }
   launch_prep<VSK_METRIC_EUCLIDEAN>(ctx, centroids, k, dim, dim16, fsm + 3, c16, caux, nullptr, nullptr, nullptr, cs, cfold);
   assign_bound_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, ctx->stream>>>(st, st + n, st + 2 * n, n, fsm + 1, fsm + 3, cs, dim16, eps, fsm + 4,
@@ -2524,6 +2585,8 @@ int32_t tensor_assign(Ctx* ctx, TensorAssign* ta, const float* rows, const float
     sa.n = n;
     sa.k = k;
     sa.kblocks = dim16 / TK;
+    sa.k16_last = k16_last_of(fold_col0(dim) + kFoldCols, dim16);
+    sa.max_stages = ctx->tuning.assign_stages;
     sa.alpha = fsm + 4;
     sa.thr = ta->thr;
     // the hit log lives in the rows' key lists (n x kAssignCap words of 8 bytes), its per-CTA counts in `count`
@@ -2559,6 +2622,7 @@ int32_t tensor_assign(Ctx* ctx, TensorAssign* ta, const float* rows, const float
   a.row_begin = 0;
   a.row_end = k;
   a.kblocks = dim16 / TK;
+  a.k16_last = k16_last_of(dim, dim16);
   a.alpha = fsm + 4;
   a.beta = caux;
   a.row_tile_fastest = 1;

@@ -251,9 +251,10 @@ class CUDAComputeDevice:
         return out
 
     def measure_peak(self, what: str) -> float:
-        """``vsk_measure_peak``: "fp32_issue" (FP32 instructions/s per thread) or "smem_gather" (4-byte words/s)."""
+        """``vsk_measure_peak``: "fp32_issue" (FP32 instructions/s per thread), "smem_gather" (4-byte words/s) or
+        "tmem_read" (bytes/s read out of tensor memory)."""
         v = C.c_double()
-        self.check(self._lib.vsk_measure_peak(self._h, {"fp32_issue": 0, "smem_gather": 1}[what], C.byref(v)))
+        self.check(self._lib.vsk_measure_peak(self._h, {"fp32_issue": 0, "smem_gather": 1, "tmem_read": 2}[what], C.byref(v)))
         return float(v.value)
 
     # ---- tuning of the search schedule (``vsk_tuning``) ----

@@ -384,4 +384,74 @@ class PQIndex {
   vsk_index* ix_ = nullptr;
 };
 
+// ---- the caller's layer: VectorEntry in, [SearchResult] out -----------------------------------------------------
+// VectorEntry(id:vector:metadata:) (Core/VectorTypes.swift:23-45) and SearchResult (Core/SearchTypes.swift:11-55) with
+// VectorID = String.  The library works on insertion indices; this class keeps the index -> (VectorID, metadata)
+// table on the host, as IVFIndex does (Indexes/IVFIndex.swift:104-111).  A filter is a 64-bit mask here: the caller
+// assigns bits to its filters and tags every entry with the bits of the filters it passes (the Python mirror's
+// FilterBitmaskCompiler derives them from SearchFilter values); a query passes the bit of its filter.
+struct VectorEntry {
+  std::string id;
+  std::vector<float> vector;
+  std::string metadata;        // the entry's metadata as the caller encodes it (JSON in the reference)
+  uint64_t filterBits = 0;     // filters this entry passes
+};
+
+struct SearchResult {
+  std::string id;
+  float distance = 0.f;
+  std::string metadata;
+  const char* tier = "hot";
+  float confidence = 1.0f;
+};
+
+class VectorStore {   // a flat exact store: VectorStore.search(query:k:strategy:filter:) (API/VectorStore.swift:271-318)
+ public:
+  VectorStore(std::shared_ptr<CUDAComputeDevice> dev, int32_t dimensions, DistanceMetric metric, bool filtered = false)
+      : index_(std::move(dev), dimensions, metric), dim_(dimensions), filtered_(filtered) {}
+  int64_t count() const { return (int64_t)ids_.size(); }
+  void add(const std::vector<VectorEntry>& entries) {
+    if (entries.empty()) return;
+    std::vector<float> rows;
+    std::vector<uint64_t> masks;
+    rows.reserve(entries.size() * (size_t)dim_);
+    for (const auto& e : entries) {
+      if ((int32_t)e.vector.size() != dim_)
+        throw DimensionMismatch(VSK_ERR_DIMENSION_MISMATCH, "expected " + std::to_string(dim_) + ", got " +
+                                                                std::to_string(e.vector.size()));
+      rows.insert(rows.end(), e.vector.begin(), e.vector.end());
+      masks.push_back(e.filterBits);
+      ids_.push_back(e.id);
+      metadata_.push_back(e.metadata);
+    }
+    index_.add(rows.data(), (int64_t)entries.size(), filtered_ ? masks.data() : nullptr);
+  }
+  // one ascending list per query; a list is shorter than k when fewer rows pass the filter
+  std::vector<std::vector<SearchResult>> batchSearch(const float* queries, int64_t nq, int32_t k,
+                                                     const uint64_t* filterBits = nullptr) const {
+    if (filterBits && !filtered_) throw InvalidInput(VSK_ERR_INVALID_INPUT, "the store was created without filters");
+    const SearchResults r = index_.batchSearch(queries, nq, k, filterBits);
+    std::vector<std::vector<SearchResult>> out((size_t)nq);
+    for (int64_t q = 0; q < nq; ++q)
+      for (int32_t j = 0; j < k; ++j) {
+        const int64_t id = r.ids[(size_t)(q * k + j)];
+        if (id < 0) break;
+        SearchResult s;
+        s.id = ids_[(size_t)id];
+        s.distance = r.distances[(size_t)(q * k + j)];
+        s.metadata = metadata_[(size_t)id];
+        out[(size_t)q].push_back(std::move(s));
+      }
+    return out;
+  }
+  std::vector<SearchResult> search(const float* query, int32_t k, uint64_t filterBit = 0) const {
+    return batchSearch(query, 1, k, filterBit ? &filterBit : nullptr)[0];
+  }
+ private:
+  FlatIndex index_;
+  int32_t dim_;
+  bool filtered_;
+  std::vector<std::string> ids_, metadata_;
+};
+
 }  // namespace vsk
