@@ -142,7 +142,9 @@ typedef struct vsk_tuning {
                                    unfilled, so that a bounded wait runs out; resets itself to 0 */
   int32_t assign_stages;        /* measurement only: caps the data-tile stages of the k-means assignment kernel's operand
                                    ring (0 = as many as fit) */
-  int32_t reserved[7];
+  int32_t stage_kblocks;        /* K blocks (64 operand columns) per stage of the contraction kernel's operand ring: 1 =
+                                   four stages of 48 KB, 2 = two stages of 96 KB (half the hand-overs per tile) */
+  int32_t reserved[6];
 } vsk_tuning;
 
 /* --- context ------------------------------------------------------------------------------

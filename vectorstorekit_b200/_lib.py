@@ -47,7 +47,7 @@ class Tuning(C.Structure):
     _fields_ = [("fold_row_term", C.c_int32), ("chunk_growth", C.c_int32), ("dense_rows", C.c_int32),
                 ("ivf_pilot_tiles", C.c_int32), ("stream_scan", C.c_int32), ("overlap_min_queries", C.c_int32),
                 ("wait_limit_log2", C.c_int32), ("test_stall_scan", C.c_int32), ("assign_stages", C.c_int32),
-                ("reserved", C.c_int32 * 7)]
+                ("stage_kblocks", C.c_int32), ("reserved", C.c_int32 * 6)]
 
 
 COMM_ID_BYTES = 128

@@ -148,6 +148,7 @@ vsk_tuning default_tuning() {
   t.ivf_pilot_tiles = 4;
   t.stream_scan = 1;
   t.overlap_min_queries = 0;   // measured: on one GPU the halves take turns at a power-capped device, no gain
+  t.stage_kblocks = 2;   // measured: C2 -3 %, int8 shard -7 %, IVF and the 100 k flat case unchanged
   return t;
 }
 
@@ -808,7 +809,7 @@ int32_t vsk_tuning_set(vsk_ctx* c, const vsk_tuning* in) {
   if (!ctx || !in) return VSK_ERR_INVALID_INPUT;
   if (in->chunk_growth < 1 || in->ivf_pilot_tiles < 1 || in->ivf_pilot_tiles > 16 || in->dense_rows < 0 ||
       in->dense_rows > kCandCap || in->overlap_min_queries < 0 || in->wait_limit_log2 < 0 || in->wait_limit_log2 > 30 ||
-      in->assign_stages < 0 || in->assign_stages > 8)
+      in->assign_stages < 0 || in->assign_stages > 8 || in->stage_kblocks < 0 || in->stage_kblocks > 2)
     return fail(ctx, VSK_ERR_INVALID_INPUT, "tuning value out of range");
   ctx->tuning = *in;
   return VSK_OK;

@@ -80,6 +80,8 @@ struct TcArgs {
   int64_t row_begin, row_end; // rows of this launch
   int32_t kblocks;            // dim16 / 64
   int32_t k16_last;           // K16 steps of the last K block that hold operand columns (the rest is padding); 0 = all 4
+  int32_t stage_kblocks;      // K blocks per ring stage: 1 (four stages of 48 KB) or 2 (two stages of 96 KB: half the
+                              // hand-overs between producer, MMA issuer and ring)
   int mode;                   // SCAN_DENSE or SCAN_THRESHOLD
   const float* alpha;         // device scalar: value = alpha * acc + beta[row]
   const float* beta;          // [n] or null (treated as 0)
@@ -121,6 +123,8 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   const int64_t units = gridDim.x;
   constexpr int QT = TM;  // queries per tile
   const uint32_t wait_limit = a.wait_limit ? a.wait_limit : WAIT_LIMIT;
+  const int kps = a.stage_kblocks == 2 ? 2 : 1;   // K blocks per ring stage
+  const int nstages = STAGES / kps;
 
   const int64_t qtiles = (a.nq + QT - 1) / QT;
   const int64_t ntiles = (a.row_end - a.row_begin + TN - 1) / TN;
@@ -192,19 +196,22 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         if (a.tiles && nt + units < a.num_tiles) entry_next = __ldg(&a.tiles[nt + units]);
         const int32_t qrow = a.tiles ? entry.x : (int32_t)(qt * QT);
         const int32_t xrow = a.tiles ? entry.y : (int32_t)(a.row_begin + nt * TN);
-        for (int kb = 0; kb < a.kblocks; ++kb) {
+        for (int kb = 0; kb < a.kblocks; kb += kps) {
           if (!mbar_wait(&sm->empty[s], ph ^ 1, &sm->abort_flag, a.err, 1, wait_limit)) { ok = false; break; }
-          uint8_t* st = sm->ring + s * STAGE_BYTES;
+          uint8_t* st = sm->ring + s * kps * STAGE_BYTES;
+          const int nkb = min(kps, a.kblocks - kb);
           if (a.stall_kblock >= 0 && unit == 0 && i == 0 && kb == a.stall_kblock) {
             // testing only: this stage is never filled, the consumer's bounded wait for it runs out
           } else {
-            mbar_expect_tx(&sm->full[s], STAGE_BYTES);
-            tma_load_2d(st, &map_q, &sm->full[s], kb * TK, qrow);
-            tma_load_2d(st + A_BYTES, &map_x, &sm->full[s], kb * TK, xrow);
+            mbar_expect_tx(&sm->full[s], (uint32_t)(nkb * STAGE_BYTES));
+            for (int j = 0; j < nkb; ++j) {
+              tma_load_2d(st + j * STAGE_BYTES, &map_q, &sm->full[s], (kb + j) * TK, qrow);
+              tma_load_2d(st + j * STAGE_BYTES + A_BYTES, &map_x, &sm->full[s], (kb + j) * TK, xrow);
+            }
             issued |= 1u << s;
             issued_ph = (issued_ph & ~(1u << s)) | (ph << s);
           }
-          if (++s == STAGES) { s = 0; ph ^= 1; }
+          if (++s == nstages) { s = 0; ph ^= 1; }
         }
       }
       // copies still in flight must land before the CTA's shared memory is released
@@ -231,19 +238,23 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         if (!mbar_wait(&sm->tmem_empty[acc], aph ^ 1, &sm->abort_flag, a.err, 2, wait_limit)) { ok = false; break; }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + (uint32_t)(acc * TN);
-        for (int kb = 0; kb < a.kblocks; ++kb) {
+        for (int kb0 = 0; kb0 < a.kblocks; kb0 += kps) {
           if (!mbar_wait(&sm->full[s], ph, &sm->abort_flag, a.err, 3, wait_limit)) { ok = false; break; }
           tc_fence_after();
-          const uint64_t adesc = make_desc(smem_u32(sm->ring + s * STAGE_BYTES));
-          const uint64_t bdesc = make_desc(smem_u32(sm->ring + s * STAGE_BYTES + A_BYTES));
-          const int nk4 = (kb == a.kblocks - 1 && a.k16_last > 0) ? a.k16_last : TK / 16;
+          const int nkb = min(kps, a.kblocks - kb0);
+          for (int j = 0; j < nkb; ++j) {
+            const int kb = kb0 + j;
+            const uint64_t adesc = make_desc(smem_u32(sm->ring + (s * kps + j) * STAGE_BYTES));
+            const uint64_t bdesc = make_desc(smem_u32(sm->ring + (s * kps + j) * STAGE_BYTES + A_BYTES));
+            const int nk4 = (kb == a.kblocks - 1 && a.k16_last > 0) ? a.k16_last : TK / 16;
 #pragma unroll
-          for (int k4 = 0; k4 < TK / 16; ++k4) {
-            // 16 fp16 = 32 bytes further along K inside the swizzle atom: +2 in 16-byte units
-            if (k4 < nk4) tc_mma(tmem_d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), kIdesc, (kb | k4) ? 1u : 0u);
+            for (int k4 = 0; k4 < TK / 16; ++k4) {
+              // 16 fp16 = 32 bytes further along K inside the swizzle atom: +2 in 16-byte units
+              if (k4 < nk4) tc_mma(tmem_d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), kIdesc, (kb | k4) ? 1u : 0u);
+            }
           }
           tc_commit(&sm->empty[s]);   // the stage is free once these MMAs have read it
-          if (++s == STAGES) { s = 0; ph ^= 1; }
+          if (++s == nstages) { s = 0; ph ^= 1; }
         }
         if (ok) tc_commit(&sm->tmem_full[acc]);
       }
@@ -1445,6 +1456,7 @@ int32_t launch_tc_ew(Ctx* ctx, const CUtensorMap& mq, const CUtensorMap& mx, con
   TcArgs la = a;
   la.wait_limit = ctx->tuning.wait_limit_log2 > 0 ? (1u << std::min(ctx->tuning.wait_limit_log2, 30)) : 0u;
   la.stall_kblock = -1;
+  la.stage_kblocks = ctx->tuning.stage_kblocks == 2 ? 2 : 1;
   if (ctx->tuning.test_stall_scan > 0) {   // testing only, one shot
     la.stall_kblock = 0;
     ctx->tuning.test_stall_scan = 0;
