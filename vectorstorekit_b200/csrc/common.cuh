@@ -242,7 +242,7 @@ struct Index {
   float max_xerr16 = 0.f;      // max |x*s - x'| over rows
   float min_xnorm_nz = 0.f;    // min nonzero |x|
   float max_xnorm = 0.f;       // max |x|
-  bool fold16 = false;         // euclidean: the per-row term |x|^2 rides in the last 48 operand columns (tensor_scan.cu)
+  bool fold16 = false;         // euclidean: the per-row term |x|^2 rides in sixteen operand columns behind the data (tensor_scan.cu)
   int32_t fold_exp = 0;        // ... scaled by 2^fold_exp
   float fold_bmax = 0.f;       // ... max |x|^2 / 2
   // int8

@@ -567,7 +567,7 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 // Every mbarrier wait is bounded like the general kernel's.
 constexpr int AS_EW = 16;
 constexpr int AS_THREADS = 64 + 32 * AS_EW;
-constexpr int AS_MAX_KB = 4;                       // k-blocks of the resident block (d + 48 fold columns <= 256)
+constexpr int AS_MAX_KB = 4;                       // k-blocks of the resident block (d + 16 fold columns <= 256)
 constexpr int AS_RING_BYTES = 192 * 1024;          // resident block + data-tile stages
 constexpr int AS_MAX_STAGES = 8;
 
@@ -1939,7 +1939,9 @@ int32_t tensor_search_begin(Index* ix, const float* q, int64_t nq, int32_t k, co
   VSK_TRY(launch_select(ctx, sel));
   sel.dense_count = -1;
   a.mode = SCAN_THRESHOLD;
-  const int64_t growth = std::max(1, ctx->tuning.chunk_growth);
+  // A small batch is bound by its launches, not by its hits: fewer, faster-growing chunks (each still within what a
+  // list can take, schedule_chunk) save a contraction and a compaction launch per step they skip.
+  const int64_t growth = nq <= 2048 ? std::max(16, ctx->tuning.chunk_growth) : std::max(1, ctx->tuning.chunk_growth);
   while (seen < n) {
     // schedule_chunk bounds the chunk so that a list cannot plausibly overflow; below that bound chunks
     // grow geometrically (each no larger than three times the rows seen so far), which keeps the share of
