@@ -127,7 +127,8 @@ typedef struct vsk_index_info {
  * for the reference's AccelerationConfiguration (Acceleration/MetalAccelerationEngine.swift:1025-1049). */
 typedef struct vsk_tuning {
   int32_t fold_row_term;        /* 1: euclidean contractions up to d = 256 carry |x|^2 inside the operands */
-  int32_t chunk_growth;         /* 3: a chunk of the flat tensor-path scan is at most this multiple of the rows seen */
+  int32_t chunk_growth;         /* 3: a chunk of the flat tensor-path scan is at most this multiple of the rows seen
+                                   (batches of up to 2 048 queries, which are bound by their launches, use at least 16) */
   int32_t dense_rows;           /* 0 = automatic; rows of the first (unfiltered) chunk otherwise */
   int32_t ivf_pilot_tiles;      /* 4: 256-row tiles of the nearest list that set an IVF query's first threshold */
   int32_t stream_scan;          /* 1: batches of up to eight queries stream the rows instead of padding a tile */
