@@ -77,6 +77,63 @@ def test_tensor_assign_equals_fp32_assign(vsk, dev):
     assert a1[7] == 3 and a1[3] == 3 and np.array_equal(a1[:500][np.arange(500) != 7], np.arange(500)[np.arange(500) != 7])
 
 
+def test_lloyd_iterations_on_the_tensor_path_equal_the_fp32_path(vsk, dev):
+    """Several Lloyd iterations on clustered data, where the thresholds of the next scan come from the previous
+    assignment (per row the exact value of its centroid at the new position or, where the centroid has hardly moved,
+    the triangle inequality): the run ends where the fp32 tile's run ends."""
+    import torch
+    g = torch.Generator(device="cuda").manual_seed(17)
+    n, d, k, iters = 300_000, 64, 1024, 8
+    centres = torch.randn((k, d), generator=g, device="cuda")
+    x = centres[torch.randint(0, k, (n,), generator=g, device="cuda")] + 0.05 * torch.randn((n, d), generator=g, device="cuda")
+    init = x[:k].contiguous()
+    out = []
+    for path in (vsk.PATH_FP32_SCAN, vsk.PATH_TENSOR_RERANK):
+        dev.set_search_path(path)
+        km = vsk.KMeansClustering(dev, maxIterations=iters, tolerance=-1.0)
+        before = dev.stats()
+        cent, asg, it, inertia = km.cluster(x, k, init)
+        after = dev.stats()
+        out.append((cent.cpu().numpy(), asg.cpu().numpy(), float(inertia), after["fallback_queries"] - before["fallback_queries"]))
+    dev.set_search_path(vsk.PATH_TENSOR_RERANK)
+    (c0, a0, i0, _), (c1, a1, i1, fb) = out
+    assert fb < n                                        # never the whole-batch fp32 fallback
+    assert np.mean(a0 == a1) > 0.999, np.mean(a0 == a1)
+    assert abs(i0 - i1) <= 1e-3 * abs(i0)
+    assert np.max(np.abs(c0 - c1)) < 5e-2
+
+
+@pytest.mark.parametrize("data", ["unstructured", "clustered"])
+def test_every_lloyd_step_assigns_each_row_to_a_nearest_centroid(vsk, dev, data):
+    """Step by step through the trainer (the caller hands in the centroids of each step): after every step each row's
+    centroid must be a nearest one under the direct formula - checked in fp64 - whichever way the step's thresholds
+    were formed.  On unstructured data (no gaps between clusters) many centroids sit inside the looser triangle
+    bound; the hit log may fill, in which case the step repeats itself with exact thresholds."""
+    import torch
+    g = torch.Generator(device="cuda").manual_seed(23)
+    n, d, k = 200_000, 64, 1024
+    if data == "unstructured":
+        x = torch.randn((n, d), generator=g, device="cuda")
+    else:
+        centres = torch.randn((k, d), generator=g, device="cuda")
+        x = centres[torch.randint(0, k, (n,), generator=g, device="cuda")] + 0.05 * torch.randn((n, d), generator=g, device="cuda")
+    c = x[:k].clone()
+    tr = vsk.KMeansTrainer(dev, x, k)
+    sample = torch.randperm(n, generator=g, device="cuda")[:20_000]
+    xs = x[sample].double()
+    try:
+        for step in range(7):
+            sums, counts, inertia = tr.step(c)
+            a = tr.assignments()[sample].long()
+            dd = torch.cdist(xs, c.double())                       # [sample][k], fp64
+            best = dd.min(dim=1).values
+            got = dd.gather(1, a[:, None])[:, 0]
+            assert bool((got <= best * (1 + 1e-5) + 1e-6).all()), (step, float((got - best).max()))
+            c = tr.finish(sums, counts, c)
+    finally:
+        tr.close()
+
+
 def test_kmeans_convergence_and_errors(vsk, dev, cpu_oracle):
     rng = np.random.default_rng(4)
     x = np.concatenate([rng.standard_normal((200, 4)) * 0.01 + 5, rng.standard_normal((200, 4)) * 0.01 - 5]).astype(np.float32)

@@ -943,10 +943,14 @@ __global__ void assign_log_exact_kernel(const float* __restrict__ x, int dim, co
 }
 
 // best[row] -> assignment and rooted distance; a row without any logged hit is handed to the exact scan
+// (`err` given and raised: the scan's log is incomplete - nothing is written, so that the previous assignment and its
+// distances survive for the repeat)
 __global__ void assign_log_decode_kernel(const unsigned long long* __restrict__ best, int64_t n, int32_t* __restrict__ assign,
-                                         float* __restrict__ dist, int32_t* __restrict__ bad_rows, int32_t* bad_count) {
+                                         float* __restrict__ dist, int32_t* __restrict__ bad_rows, int32_t* bad_count,
+                                         const int32_t* __restrict__ err) {
   const int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (r >= n) return;
+  if (err != nullptr && *err != 0) return;
   const unsigned long long b = best[r];
   if (b == ~0ull) {
     bad_rows[atomicAdd(bad_count, 1)] = (int32_t)r;
@@ -1521,42 +1525,87 @@ __global__ void assign_threshold_kernel(const unsigned long long* __restrict__ b
   count[r] = 0;
 }
 
-// Threshold from the previous assignment (Lloyd iterations after the first): with u the exact value
-// |c_p|^2 - 2 x.c_p of the centroid the row was assigned to last time, the nearest centroid c* has exact value
-// <= u, hence coarse value <= u + eps.  One warp per row computes u = sum (x-c_p)^2 - |x|^2 in fp32; the
-// threshold is u + 2 eps (the second eps covers the fp32 rounding of u itself).  This replaces pass 1.
+// Thresholds of the next scan from the previous assignment (Lloyd iterations after the first).  With u the exact value
+// |c_p|^2 - 2 x.c_p = |x - c_p|^2 - |x|^2 of the centroid the row was assigned to last time, the nearest centroid c* has
+// exact value <= u, hence coarse value <= u + eps; the threshold is u + 2 eps (the second eps covers the fp32 rounding
+// of u itself).  Two ways to u, chosen per row:
+//   exact   one read of the row: sum (x - c_p)^2 and sum x^2 in fp32 (a warp per row, four rows in flight);
+//   bound   no read at all, when the centroid has moved by no more than `ratio` of the row's distance to it: the
+//           triangle inequality, |x - c_new| <= |x - c_old| + |c_new - c_old|, with the distance the last iteration
+//           left in `dist_old`, the shifts in `shift` and the row norms measured when the operand was made.  The bound
+//           is looser than the exact value by at most (2 ratio + ratio^2) of the squared distance, which lists a few
+//           more centroids for the exact decision and costs nothing in correctness.
+// A lane takes one of 32 consecutive rows; the rows that need the exact form are then done by the whole warp.
 template <bool VEC>
-__global__ void assign_prev_threshold_kernel(const float* __restrict__ x, int64_t n, int dim, const float* __restrict__ cent,
-                                             const int32_t* __restrict__ prev, const float* __restrict__ eps,
-                                             float* __restrict__ thr, int32_t* __restrict__ count) {
+__global__ void __launch_bounds__(256) assign_prev_threshold_kernel(
+    const float* __restrict__ x, int64_t n, int dim, const float* __restrict__ cent, const int32_t* __restrict__ prev,
+    const float* __restrict__ eps, float* __restrict__ thr, int32_t* __restrict__ count, const float* __restrict__ dist_old,
+    const float* __restrict__ shift, const float* __restrict__ xnorm, float ratio) {
   const int lane = threadIdx.x & 31;
-  if (VEC) {
-    // four rows per warp, 16-byte loads (dim a multiple of 4, aligned rows): eight independent loads in flight per lane
-    const int64_t row0 = ((int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * 4;
-    if (row0 >= n) return;
-    const int nv = dim >> 2;
-    const float4* xr[4];
-    const float4* cr[4];
-    float d2[4], x2[4];
+  const int64_t row0 = ((int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * 32;
+  if (row0 >= n) return;
+  const int64_t mine = row0 + lane;
+  const bool have = mine < n;
+  bool need = have;
+  if (have && dist_old != nullptr) {
+    const float d = dist_old[mine], sft = shift[prev[mine]];
+    if (d > 0.f && d < CUDART_INF_F && sft <= ratio * d) {
+      const float xn = xnorm[mine], x2 = xn * xn;
+      const float ub = (d + sft) * (1.0f + 1e-5f);
+      const float ub2 = ub * ub;
+      thr[mine] = (ub2 - x2) + 2.0f * eps[mine] + 1e-5f * (ub2 + x2);
+      count[mine] = 0;
+      need = false;
+    }
+  }
+  unsigned todo = __ballot_sync(0xffffffffu, need);
+  while (todo) {
+    // up to four rows per step, each read by the whole warp
+    int64_t rr[4];
+    int nr = 0;
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
-      const int64_t row = min(row0 + r, n - 1);
-      xr[r] = reinterpret_cast<const float4*>(x + row * dim);
-      cr[r] = reinterpret_cast<const float4*>(cent + (int64_t)prev[row] * dim);
-      d2[r] = 0.f;
-      x2[r] = 0.f;
+      rr[r] = row0;
+      if (todo) {
+        const int l = __ffs((int)todo) - 1;
+        todo &= todo - 1u;
+        rr[r] = row0 + l;
+        nr = r + 1;
+      }
     }
-    for (int i = lane; i < nv; i += 32) {
-      float4 a[4], b[4];
-#pragma unroll
-      for (int r = 0; r < 4; ++r) { a[r] = __ldg(xr[r] + i); b[r] = __ldg(cr[r] + i); }
+    float d2[4] = {0.f, 0.f, 0.f, 0.f}, x2[4] = {0.f, 0.f, 0.f, 0.f};
+    if (VEC) {
+      const int nv = dim >> 2;
+      const float4* xr[4];
+      const float4* cr[4];
 #pragma unroll
       for (int r = 0; r < 4; ++r) {
-        float d;
-        d = a[r].x - b[r].x; d2[r] = fmaf(d, d, d2[r]); x2[r] = fmaf(a[r].x, a[r].x, x2[r]);
-        d = a[r].y - b[r].y; d2[r] = fmaf(d, d, d2[r]); x2[r] = fmaf(a[r].y, a[r].y, x2[r]);
-        d = a[r].z - b[r].z; d2[r] = fmaf(d, d, d2[r]); x2[r] = fmaf(a[r].z, a[r].z, x2[r]);
-        d = a[r].w - b[r].w; d2[r] = fmaf(d, d, d2[r]); x2[r] = fmaf(a[r].w, a[r].w, x2[r]);
+        xr[r] = reinterpret_cast<const float4*>(x + rr[r] * dim);
+        cr[r] = reinterpret_cast<const float4*>(cent + (int64_t)prev[rr[r]] * dim);
+      }
+      for (int i = lane; i < nv; i += 32) {
+        float4 a[4], b[4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) { a[r] = __ldg(xr[r] + i); b[r] = __ldg(cr[r] + i); }
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          float d;
+          d = a[r].x - b[r].x; d2[r] = fmaf(d, d, d2[r]); x2[r] = fmaf(a[r].x, a[r].x, x2[r]);
+          d = a[r].y - b[r].y; d2[r] = fmaf(d, d, d2[r]); x2[r] = fmaf(a[r].y, a[r].y, x2[r]);
+          d = a[r].z - b[r].z; d2[r] = fmaf(d, d, d2[r]); x2[r] = fmaf(a[r].z, a[r].z, x2[r]);
+          d = a[r].w - b[r].w; d2[r] = fmaf(d, d, d2[r]); x2[r] = fmaf(a[r].w, a[r].w, x2[r]);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const float* xr = x + rr[r] * dim;
+        const float* cr = cent + (int64_t)prev[rr[r]] * dim;
+        for (int i = lane; i < dim; i += 32) {
+          const float xv = __ldg(xr + i), d = xv - __ldg(cr + i);
+          d2[r] = fmaf(d, d, d2[r]);
+          x2[r] = fmaf(xv, xv, x2[r]);
+        }
       }
     }
 #pragma unroll
@@ -1566,42 +1615,40 @@ __global__ void assign_prev_threshold_kernel(const float* __restrict__ x, int64_
         d2[r] += __shfl_xor_sync(0xffffffffu, d2[r], o);
         x2[r] += __shfl_xor_sync(0xffffffffu, x2[r], o);
       }
-      if (lane == 0 && row0 + r < n) {
-        thr[row0 + r] = (d2[r] - x2[r]) + 2.0f * eps[row0 + r] + 4.0f * 5.9604645e-8f * (d2[r] + x2[r]);
-        count[row0 + r] = 0;
+      if (lane == 0 && r < nr) {
+        thr[rr[r]] = (d2[r] - x2[r]) + 2.0f * eps[rr[r]] + 4.0f * 5.9604645e-8f * (d2[r] + x2[r]);
+        count[rr[r]] = 0;
       }
     }
-    return;
-  }
-  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (row >= n) return;
-  const float* xr = x + row * dim;
-  const float* cr = cent + (int64_t)prev[row] * dim;
-  float d2 = 0.f, x2 = 0.f;
-  for (int i = lane; i < dim; i += 32) {
-    const float xv = __ldg(xr + i), d = xv - __ldg(cr + i);
-    d2 = fmaf(d, d, d2);
-    x2 = fmaf(xv, xv, x2);
-  }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    d2 += __shfl_xor_sync(0xffffffffu, d2, o);
-    x2 += __shfl_xor_sync(0xffffffffu, x2, o);
-  }
-  if (lane == 0) {
-    thr[row] = (d2 - x2) + 2.0f * eps[row] + 4.0f * 5.9604645e-8f * (d2 + x2);
-    count[row] = 0;
   }
 }
 
-// launches the vector form when the rows allow 16-byte loads
+// |c_new - c_old| per centroid (one warp each), a hair above its fp32 value
+__global__ void assign_shift_kernel(const float* __restrict__ cent, const float* __restrict__ old, int k, int dim,
+                                    float* __restrict__ shift) {
+  const int c = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (c >= k) return;
+  const int lane = threadIdx.x & 31;
+  float s = 0.f;
+  for (int i = lane; i < dim; i += 32) {
+    const float d = cent[(int64_t)c * dim + i] - old[(int64_t)c * dim + i];
+    s = fmaf(d, d, s);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if (lane == 0) shift[c] = sqrtf(s) * (1.0f + 1e-5f);
+}
+
+// launches the vector form when the rows allow 16-byte loads; dist_old == nullptr: every row takes the exact form
 static void launch_prev_threshold(Ctx* ctx, const float* rows, int64_t n, int dim, const float* centroids, const int32_t* assign,
-                                  const float* eps, float* thr, int32_t* count) {
+                                  const float* eps, float* thr, int32_t* count, const float* dist_old, const float* shift,
+                                  const float* xnorm, float ratio) {
   const bool vec = dim % 4 == 0 && ((uintptr_t)rows & 15) == 0 && ((uintptr_t)centroids & 15) == 0;
+  const unsigned grid = (unsigned)ceil_div(n, 256);
   if (vec)
-    assign_prev_threshold_kernel<true><<<(unsigned)ceil_div(n, 32), 256, 0, ctx->stream>>>(rows, n, dim, centroids, assign, eps, thr, count);
+    assign_prev_threshold_kernel<true><<<grid, 256, 0, ctx->stream>>>(rows, n, dim, centroids, assign, eps, thr, count, dist_old, shift, xnorm, ratio);
   else
-    assign_prev_threshold_kernel<false><<<(unsigned)ceil_div(n, 8), 256, 0, ctx->stream>>>(rows, n, dim, centroids, assign, eps, thr, count);
+    assign_prev_threshold_kernel<false><<<grid, 256, 0, ctx->stream>>>(rows, n, dim, centroids, assign, eps, thr, count, dist_old, shift, xnorm, ratio);
 }
 
 // one warp per data row: exact squared distances to the listed centroids
@@ -2522,7 +2569,7 @@ int32_t ivf_tensor_search(Index* ix, const float* q, int64_t nq, const int64_t* 
 int32_t tensor_assign_prepare(Ctx* ctx, const float* rows, int64_t n, int32_t dim, TensorAssign* ta) {
   ta->n = n;
   ta->dim = dim;
-  // Short contractions keep a block of centroids resident (assign_scan_kernel): the operands then carry 48 more
+  // Short contractions keep a block of centroids resident (assign_scan_kernel): the operands then carry 16 more
   // columns for the folded |c|^2 / 2 term.  Longer ones (more than four k-blocks with those columns) take the general kernel.
   ta->stationary = fold_col0(dim) + kFoldCols <= AS_MAX_KB * TK;
   ta->dim16 = (int32_t)(ceil_div(ta->stationary ? fold_col0(dim) + kFoldCols : dim, TK) * TK);
@@ -2550,7 +2597,7 @@ int32_t tensor_assign_prepare(Ctx* ctx, const float* rows, int64_t n, int32_t di
 
 void tensor_assign_release(TensorAssign* ta) {
   dev_free(ta->rows16); dev_free(ta->stats); dev_free(ta->keys); dev_free(ta->best); dev_free(ta->count);
-  dev_free(ta->thr); dev_free(ta->bad_rows); dev_free(ta->small);
+  dev_free(ta->thr); dev_free(ta->bad_rows); dev_free(ta->small); dev_free(ta->prev_cent); dev_free(ta->shift);
   *ta = TensorAssign{};
 }
 
@@ -2609,26 +2656,67 @@ int32_t tensor_assign(Ctx* ctx, TensorAssign* ta, const float* rows, const float
     sa.log_count = ta->count;
     sa.best = ta->best;
     sa.err = (int32_t*)(sm + 5);
-    if (assign_holds_previous) {
-      launch_prev_threshold(ctx, rows, n, dim, centroids, assign, eps, ta->thr, ta->count);
-    } else {
-      VSK_CUDA(ctx, cudaMemsetAsync(ta->best, 0xff, (size_t)n * sizeof(unsigned long long), ctx->stream));
-      VSK_TRY(launch_assign_scan<SCAN_ARGMIN>(ctx, mr, mc, sa));
-      assign_threshold_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, ctx->stream>>>(ta->best, eps, n, ta->thr, ta->count);
+    // The centroids of the previous call and how far each has moved since: rows whose centroid has hardly moved take
+    // their threshold from the triangle inequality instead of a read of the row (assign_prev_threshold_kernel).
+    if (ta->prev_k != k) {
+      dev_free(ta->prev_cent);
+      dev_free(ta->shift);
+      ta->prev_cent = nullptr;
+      ta->shift = nullptr;
+      ta->prev_k = 0;
+      VSK_TRY(dev_alloc(ctx, (void**)&ta->prev_cent, (size_t)k * dim * sizeof(float)));
+      VSK_TRY(dev_alloc(ctx, (void**)&ta->shift, (size_t)k * sizeof(float)));
+      ta->prev_k = k;
+      ta->have_prev = false;
     }
-    VSK_CUDA(ctx, cudaMemsetAsync(ta->best, 0xff, (size_t)n * sizeof(unsigned long long), ctx->stream));
+    const bool bound_ok = assign_holds_previous && ta->have_prev && ta->bound_allowed && dist != nullptr;
+    if (bound_ok) {
+      assign_shift_kernel<<<(unsigned)ceil_div(k, 8), 256, 0, ctx->stream>>>(centroids, ta->prev_cent, k, dim, ta->shift);
+      ctx->stats.kernel_launches++;
+    }
     unsigned sgrid = 0;
     int64_t log_cap = 0;
-    tl_mark(ctx, "assign_thresholds");
-    VSK_TRY(launch_assign_scan<SCAN_THRESHOLD>(ctx, mr, mc, sa, &sgrid, &log_cap));
-    if (dim % 4 == 0 && ((uintptr_t)rows & 15) == 0 && ((uintptr_t)centroids & 15) == 0)
-      assign_log_exact_kernel<true><<<dim3(64, sgrid), 256, 0, ctx->stream>>>(rows, dim, centroids, sa.log, sa.log_count, log_cap, ta->best);
-    else
-      assign_log_exact_kernel<false><<<dim3(64, sgrid), 256, 0, ctx->stream>>>(rows, dim, centroids, sa.log, sa.log_count, log_cap, ta->best);
-    tl_mark(ctx, "assign_exact");
-    assign_log_decode_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, ctx->stream>>>(ta->best, n, assign, dist, ta->bad_rows, (int32_t*)(sm + 6));
-    ctx->stats.kernel_launches += 3;
-    VSK_CUDA(ctx, cudaGetLastError());
+    // one pass: thresholds (or the coarse arg-min of a first iteration), threshold scan, exact decisions
+    auto pass = [&](bool with_bound) -> int32_t {
+      VSK_CUDA(ctx, cudaMemsetAsync(sm + 5, 0, 8, ctx->stream));
+      if (assign_holds_previous) {
+        launch_prev_threshold(ctx, rows, n, dim, centroids, assign, eps, ta->thr, ta->count, with_bound ? dist : nullptr,
+                              ta->shift, st + 2 * n, 0.02f);
+      } else {
+        VSK_CUDA(ctx, cudaMemsetAsync(ta->best, 0xff, (size_t)n * sizeof(unsigned long long), ctx->stream));
+        VSK_TRY(launch_assign_scan<SCAN_ARGMIN>(ctx, mr, mc, sa));
+        assign_threshold_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, ctx->stream>>>(ta->best, eps, n, ta->thr, ta->count);
+      }
+      VSK_CUDA(ctx, cudaMemsetAsync(ta->best, 0xff, (size_t)n * sizeof(unsigned long long), ctx->stream));
+      tl_mark(ctx, "assign_thresholds");
+      VSK_TRY(launch_assign_scan<SCAN_THRESHOLD>(ctx, mr, mc, sa, &sgrid, &log_cap));
+      if (dim % 4 == 0 && ((uintptr_t)rows & 15) == 0 && ((uintptr_t)centroids & 15) == 0)
+        assign_log_exact_kernel<true><<<dim3(64, sgrid), 256, 0, ctx->stream>>>(rows, dim, centroids, sa.log, sa.log_count, log_cap, ta->best);
+      else
+        assign_log_exact_kernel<false><<<dim3(64, sgrid), 256, 0, ctx->stream>>>(rows, dim, centroids, sa.log, sa.log_count, log_cap, ta->best);
+      tl_mark(ctx, "assign_exact");
+      // writes nothing when the scan raised an error: the previous assignment survives for a repeat
+      assign_log_decode_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, ctx->stream>>>(ta->best, n, assign, dist, ta->bad_rows, (int32_t*)(sm + 6),
+                                                                                (const int32_t*)(sm + 5));
+      ctx->stats.kernel_launches += 4;
+      VSK_CUDA(ctx, cudaGetLastError());
+      return VSK_OK;
+    };
+    VSK_TRY(pass(bound_ok));
+    if (bound_ok) {
+      // The looser thresholds list more centroids per row; data without gaps between its clusters can fill the hit
+      // log.  Then the pass is repeated once with exact thresholds, and the bound is not tried again on this data.
+      int32_t e0 = 0;
+      VSK_CUDA(ctx, cudaMemcpyAsync(&e0, sm + 5, 4, cudaMemcpyDeviceToHost, ctx->stream));
+      VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+      if (e0 == 9) {
+        ta->bound_allowed = false;
+        VSK_TRY(pass(false));
+      }
+    }
+    // remember these centroids for the next call's shifts
+    VSK_CUDA(ctx, cudaMemcpyAsync(ta->prev_cent, centroids, (size_t)k * dim * sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream));
+    ta->have_prev = true;
   } else {
 
   TcArgs a{};
@@ -2649,7 +2737,7 @@ int32_t tensor_assign(Ctx* ctx, TensorAssign* ta, const float* rows, const float
   a.cand.flags = nullptr;
   a.cand.nq = n;
   if (assign_holds_previous) {
-    launch_prev_threshold(ctx, rows, n, dim, centroids, assign, eps, ta->thr, ta->count);
+    launch_prev_threshold(ctx, rows, n, dim, centroids, assign, eps, ta->thr, ta->count, nullptr, nullptr, nullptr, 0.f);
   } else {
     VSK_CUDA(ctx, cudaMemsetAsync(ta->best, 0xff, (size_t)n * sizeof(unsigned long long), ctx->stream));
     a.mode = SCAN_ARGMIN;
@@ -2682,7 +2770,8 @@ int32_t tensor_assign(Ctx* ctx, TensorAssign* ta, const float* rows, const float
     VSK_CUDA(ctx, cudaMemsetAsync(ta->best, 0xff, (size_t)n * sizeof(unsigned long long), ctx->stream));
     VSK_TRY(launch_exact_scan(ctx, e));
     VSK_CUDA(ctx, cudaMemsetAsync(sm + 6, 0, 4, ctx->stream));
-    assign_log_decode_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, ctx->stream>>>(ta->best, n, assign, dist, ta->bad_rows, (int32_t*)(sm + 6));
+    assign_log_decode_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, ctx->stream>>>(ta->best, n, assign, dist, ta->bad_rows, (int32_t*)(sm + 6),
+                                                                              nullptr);
     ctx->stats.kernel_launches++;
     VSK_CUDA(ctx, cudaGetLastError());
     VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));

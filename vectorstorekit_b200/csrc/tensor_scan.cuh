@@ -59,6 +59,11 @@ struct TensorAssign {
   int32_t* bad_rows = nullptr;        // [n] rows handed to the fp32 tile
   void* small = nullptr;              // scalars and centroid-operand statistics
   bool stationary = false;            // short contraction: resident centroid block, |c|^2 / 2 folded into the operands
+  float* prev_cent = nullptr;         // [prev_k][dim] the centroids of the previous call (stationary path) ...
+  float* shift = nullptr;             // [prev_k] ... and how far each has moved since
+  int32_t prev_k = 0;
+  bool have_prev = false;
+  bool bound_allowed = true;          // thresholds from the triangle inequality where a centroid has hardly moved
   alignas(64) unsigned char map_rows[128] = {};  // TMA tensor map of rows16
 };
 int32_t tensor_assign_prepare(Ctx* ctx, const float* rows, int64_t n, int32_t dim, TensorAssign* ta);
