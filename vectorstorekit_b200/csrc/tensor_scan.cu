@@ -1743,7 +1743,10 @@ __global__ void assign_fold_setup_kernel(const unsigned* max_sq, float* scale_c,
 }
 
 // the data operand's fold columns hold the constant u (one 16-byte store of eight copies per thread)
-__global__ void assign_fill_fold_kernel(__half* __restrict__ rows16, int64_t n, int dim16, int col0, const float* __restrict__ u) {
+// (u_done: the constant the columns hold already - a Lloyd iteration whose exponent has not changed writes nothing)
+__global__ void assign_fill_fold_kernel(__half* __restrict__ rows16, int64_t n, int dim16, int col0, const float* __restrict__ u,
+                                        const float* __restrict__ u_done) {
+  if (*u == *u_done) return;
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   constexpr int chunks = kFoldCols / 8;
   if (i >= n * chunks) return;
@@ -2629,7 +2632,9 @@ int32_t tensor_assign(Ctx* ctx, TensorAssign* ta, const float* rows, const float
     VSK_CUDA(ctx, cudaMemsetAsync(sm + 24, 0, 16, ctx->stream));
     max_sq_kernel<<<(unsigned)ceil_div(k, 8), 256, 0, ctx->stream>>>(centroids, k, dim, sm + 24);
     assign_fold_setup_kernel<<<1, 1, 0, ctx->stream>>>(sm + 24, fsm + 3, fsm + 1, (int*)sm + 25, fsm + 27);
-    assign_fill_fold_kernel<<<(unsigned)ceil_div(n * (kFoldCols / 8), 256), 256, 0, ctx->stream>>>(ta->rows16, n, dim16, fold_col0(dim), fsm + 27);
+    // word 30: the constant the data operand's fold columns hold (0 = none yet; a real constant is a power of two)
+    assign_fill_fold_kernel<<<(unsigned)ceil_div(n * (kFoldCols / 8), 256), 256, 0, ctx->stream>>>(ta->rows16, n, dim16, fold_col0(dim), fsm + 27, fsm + 30);
+    VSK_CUDA(ctx, cudaMemcpyAsync(fsm + 30, fsm + 27, sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream));
     ctx->stats.kernel_launches += 3;
     cfold = FoldArgs{1, fold_col0(dim), 0, (const int*)sm + 25};
   }
