@@ -18,7 +18,8 @@ the sizes the call asked for, plus buffers the caller announced) or is not a glo
 windows are bounded by the hardware); otherwise it records the first offending address and instruction size in the
 device-side state and returns the address of a small sink buffer, so the access itself never leaves valid memory: no
 trap, no fault, and the host reads the violation after the call.  Tensor-map (TMA) copies are bounds-checked by the
-hardware against the extents in their descriptor and are not touched.
+hardware against the extents in their descriptor and are not touched; the global side of an asynchronous
+``cp.async`` copy is checked like a load.
 """
 from __future__ import annotations
 
@@ -29,6 +30,9 @@ _TYPE_BYTES = {"b8": 1, "u8": 1, "s8": 1, "b16": 2, "u16": 2, "s16": 2, "f16": 2
                "s32": 4, "f32": 4, "f16x2": 4, "bf16x2": 4, "b64": 8, "u64": 8, "s64": 8, "f64": 8, "b128": 16}
 _OTHER_SPACES = ("shared", "local", "param", "const")
 _INSTR = re.compile(r"^(?P<indent>\s*)(?:@(?P<neg>!?)(?P<pred>%p\d+)\s+)?(?P<op>(?:ld|st|atom|red)\.[A-Za-z0-9_.:]+)(?P<rest>\s.*;.*)$")
+# cp.async.{ca,cg}.shared.global [dst], [src], cp-size{, src-size};  - the global side is the SECOND address
+_CPASYNC = re.compile(r"^(?P<indent>\s*)(?:@(?P<neg>!?)(?P<pred>%p\d+)\s+)?(?P<op>cp\.async\.c[ag]\.shared(?:::cta)?\.global[A-Za-z0-9_.:]*)"
+                      r"(?P<head>\s+\[[^\]]+\]\s*,\s*)\[\s*(?P<base>%rd\d+)\s*(?:\+\s*(?P<imm>-?\d+))?\s*\](?P<tail>\s*,\s*(?P<size>\d+).*;.*)$")
 _ADDR = re.compile(r"\[\s*(?P<base>%rd\d+)\s*(?:\+\s*(?P<imm>-?\d+))?\s*\]")
 _CHECKER = re.compile(r"\.func\s*\(\.param\s+\.b64\s+\w+\)\s+(?P<name>_ZN\w*vsk_chk_access\w*)\s*\(")
 
@@ -63,6 +67,31 @@ def instrument(ptx: str) -> tuple[str, int]:
             ends_body = depth == 0 and "}" in line
             if ends_decl or ends_body:
                 in_checker = False
+            continue
+        mc = _CPASYNC.match(line)
+        if mc:
+            # asynchronous global -> shared copy: the source address goes through the checker (as a read of cp-size
+            # bytes; a refused copy reads the sink instead)
+            sites += 1
+            ind, base, imm = mc.group("indent"), mc.group("base"), mc.group("imm") or "0"
+            info = int(mc.group("size"))
+            label = f"$L_vskc_{sites}"
+            if mc.group("pred"):
+                out.append(f"{ind}@{'' if mc.group('neg') else '!'}{mc.group('pred')} bra {label};")
+            out.append(f"{ind}{{")
+            out.append(f"{ind}.reg .b64 %vskc_a;")
+            out.append(f"{ind}.param .b64 vskc_in;")
+            out.append(f"{ind}.param .b32 vskc_sz;")
+            out.append(f"{ind}.param .b64 vskc_out;")
+            out.append(f"{ind}add.s64 %vskc_a, {base}, {imm};")
+            out.append(f"{ind}st.param.b64 [vskc_in], %vskc_a;")
+            out.append(f"{ind}st.param.b32 [vskc_sz], {info};")
+            out.append(f"{ind}call.uni (vskc_out), {checker}, (vskc_in, vskc_sz);")
+            out.append(f"{ind}ld.param.b64 %vskc_a, [vskc_out];")
+            out.append(f"{ind}{mc.group('op')}{mc.group('head')}[%vskc_a]{mc.group('tail')}")
+            out.append(f"{ind}}}")
+            if mc.group("pred"):
+                out.append(f"{label}:")
             continue
         mi = _INSTR.match(line)
         if not mi:
