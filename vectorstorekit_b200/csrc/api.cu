@@ -817,6 +817,7 @@ int32_t vsk_tuning_set(vsk_ctx* c, const vsk_tuning* in) {
 
 int32_t vsk_batch_distances_dev(vsk_ctx* c, int32_t metric, const float* q, int64_t nq, const float* x,
                                 int64_t nx, int32_t dim, float* out) {
+  VSK_TRACE("vsk_batch_distances_dev");
   Ctx* ctx = reinterpret_cast<Ctx*>(c);
   if (!ctx) return VSK_ERR_INVALID_INPUT;
   cudaSetDevice(ctx->device);
@@ -851,6 +852,7 @@ int32_t vsk_batch_distances_dev(vsk_ctx* c, int32_t metric, const float* q, int6
 
 int32_t vsk_batch_distances(vsk_ctx* c, int32_t metric, const float* q, int64_t nq, const float* x, int64_t nx,
                             int32_t dim, float* out) {
+  VSK_TRACE("vsk_batch_distances");
   Ctx* ctx = reinterpret_cast<Ctx*>(c);
   if (!ctx) return VSK_ERR_INVALID_INPUT;
   cudaSetDevice(ctx->device);
@@ -895,6 +897,7 @@ int32_t vsk_flat_create(vsk_ctx* c, int32_t metric, int32_t dim, vsk_index** out
 }
 
 int32_t vsk_flat_add_f32(vsk_index* i, const float* rows, int64_t n, const uint64_t* masks) {
+  VSK_TRACE("vsk_flat_add_f32");
   Index* ix = reinterpret_cast<Index*>(i);
   if (!ix) return VSK_ERR_INVALID_INPUT;
   cudaSetDevice(ix->ctx->device);
@@ -903,6 +906,7 @@ int32_t vsk_flat_add_f32(vsk_index* i, const float* rows, int64_t n, const uint6
 }
 
 int32_t vsk_flat_add_f32_dev(vsk_index* i, const float* rows, int64_t n, const uint64_t* masks) {
+  VSK_TRACE("vsk_flat_add_f32_dev");
   Index* ix = reinterpret_cast<Index*>(i);
   if (!ix) return VSK_ERR_INVALID_INPUT;
   cudaSetDevice(ix->ctx->device);
@@ -953,6 +957,7 @@ int32_t vsk_index_set_id_base(vsk_index* i, int64_t id_base) {
 
 int32_t vsk_search_dev(vsk_index* i, const float* q, int64_t nq, int32_t k, const uint64_t* qmasks,
                        float* out_dist, int64_t* out_ids) {
+  VSK_TRACE("vsk_search_dev");
   Index* ix = reinterpret_cast<Index*>(i);
   if (!ix) return VSK_ERR_INVALID_INPUT;
   cudaSetDevice(ix->ctx->device);
@@ -1053,6 +1058,7 @@ int32_t vsk_search_shard_finish_dev(vsk_index* i, const float* bound, float* out
 
 int32_t vsk_search(vsk_index* i, const float* q, int64_t nq, int32_t k, const uint64_t* qmasks, float* out_dist,
                    int64_t* out_ids) {
+  VSK_TRACE("vsk_search");
   Index* ix = reinterpret_cast<Index*>(i);
   if (!ix) return VSK_ERR_INVALID_INPUT;
   Ctx* ctx = ix->ctx;

@@ -358,6 +358,7 @@ void vsk_sharded_slice(int64_t nq, int32_t nranks, int32_t rank, int64_t* first,
 
 int32_t vsk_search_sharded_dev(vsk_index* i, const float* q, int64_t nq, int32_t k, const uint64_t* qmasks, int32_t layout,
                                float* out_dist, int64_t* out_ids) {
+  VSK_TRACE("vsk_search_sharded_dev");
   Index* ix = reinterpret_cast<Index*>(i);
   if (!ix) return VSK_ERR_INVALID_INPUT;
   Ctx* ctx = ix->ctx;
@@ -376,6 +377,7 @@ int32_t vsk_search_sharded_dev(vsk_index* i, const float* q, int64_t nq, int32_t
 
 int32_t vsk_search_sharded(vsk_index* i, const float* q, int64_t nq, int32_t k, const uint64_t* qmasks, int32_t layout,
                            float* out_dist, int64_t* out_ids) {
+  VSK_TRACE("vsk_search_sharded");
   Index* ix = reinterpret_cast<Index*>(i);
   if (!ix) return VSK_ERR_INVALID_INPUT;
   Ctx* ctx = ix->ctx;

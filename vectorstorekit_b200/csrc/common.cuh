@@ -11,6 +11,8 @@
 #include <string>
 #include <vector>
 
+#include <nvtx3/nvToolsExt.h>   // header-only; ranges cost nothing unless a profiler is attached
+
 #include "../../include/vsk_cuda.h"
 #include "checked.cuh"   // empty unless VSK_CHECKED
 
@@ -22,6 +24,18 @@ namespace vsk {
 // ------------------------------------------------------------------------------------------
 struct Ctx;
 int32_t fail(Ctx* ctx, int32_t status, const char* fmt, ...);
+
+// NVTX range over a scope: entry points and the phases of a search show up by name on a profiler's timeline (the
+// reference marks the same spans with os_signpost, Acceleration/Metal/MetalPerformanceProfiler.swift:10-43).
+struct TraceRange {
+  explicit TraceRange(const char* name) { nvtxRangePushA(name); }
+  ~TraceRange() { nvtxRangePop(); }
+  TraceRange(const TraceRange&) = delete;
+  TraceRange& operator=(const TraceRange&) = delete;
+};
+#define VSK_TRACE_CAT2(a, b) a##b
+#define VSK_TRACE_CAT(a, b) VSK_TRACE_CAT2(a, b)
+#define VSK_TRACE(name) ::vsk::TraceRange VSK_TRACE_CAT(vsk_trace_range_, __LINE__)(name)
 
 #define VSK_CUDA(ctx, expr)                                                                   \
   do {                                                                                        \

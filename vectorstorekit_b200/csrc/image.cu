@@ -561,6 +561,7 @@ int32_t vsk_index_image_size(vsk_index* i, int64_t* bytes) {
 }
 
 int32_t vsk_index_export(vsk_index* i, void* dst, int64_t capacity, int64_t* written) {
+  VSK_TRACE("vsk_index_export");
   Index* ix = reinterpret_cast<Index*>(i);
   if (!ix) return VSK_ERR_INVALID_INPUT;
   cudaSetDevice(ix->ctx->device);
@@ -570,6 +571,7 @@ int32_t vsk_index_export(vsk_index* i, void* dst, int64_t capacity, int64_t* wri
 }
 
 int32_t vsk_index_import(vsk_ctx* c, const void* src, int64_t bytes, vsk_index** out) {
+  VSK_TRACE("vsk_index_import");
   Ctx* ctx = reinterpret_cast<Ctx*>(c);
   if (!ctx || !out) return VSK_ERR_INVALID_INPUT;
   cudaSetDevice(ctx->device);
@@ -580,6 +582,7 @@ int32_t vsk_index_import(vsk_ctx* c, const void* src, int64_t bytes, vsk_index**
 }
 
 int32_t vsk_index_save(vsk_index* i, const char* path) {
+  VSK_TRACE("vsk_index_save");
   Index* ix = reinterpret_cast<Index*>(i);
   if (!ix) return VSK_ERR_INVALID_INPUT;
   cudaSetDevice(ix->ctx->device);
@@ -594,6 +597,7 @@ int32_t vsk_index_save(vsk_index* i, const char* path) {
 }
 
 int32_t vsk_index_load(vsk_ctx* c, const char* path, vsk_index** out) {
+  VSK_TRACE("vsk_index_load");
   Ctx* ctx = reinterpret_cast<Ctx*>(c);
   if (!ctx || !out) return VSK_ERR_INVALID_INPUT;
   cudaSetDevice(ctx->device);

@@ -730,6 +730,7 @@ extern "C" {
 
 int32_t vsk_ivf_build_dev(vsk_ctx* c, const float* centroids, int32_t nlist, const float* rows, int64_t n, int32_t dim,
                           vsk_index** out) {
+  VSK_TRACE("vsk_ivf_build_dev");
   Ctx* ctx = reinterpret_cast<Ctx*>(c);
   if (!ctx || !out) return VSK_ERR_INVALID_INPUT;
   cudaSetDevice(ctx->device);
@@ -738,6 +739,7 @@ int32_t vsk_ivf_build_dev(vsk_ctx* c, const float* centroids, int32_t nlist, con
 
 int32_t vsk_ivf_build(vsk_ctx* c, const float* centroids, int32_t nlist, const float* rows, int64_t n, int32_t dim,
                       vsk_index** out) {
+  VSK_TRACE("vsk_ivf_build");
   Ctx* ctx = reinterpret_cast<Ctx*>(c);
   if (!ctx || !out) return VSK_ERR_INVALID_INPUT;
   cudaSetDevice(ctx->device);
@@ -781,6 +783,7 @@ int32_t vsk_ivf_centroids(vsk_index* i, float* centroids) {
 
 int32_t vsk_ivf_search_filtered_dev(vsk_index* i, const float* q, int64_t nq, int32_t k, int32_t nprobe,
                                     const uint64_t* qmasks, float* out_dist, int64_t* out_ids) {
+  VSK_TRACE("vsk_ivf_search_filtered_dev");
   Index* ix = reinterpret_cast<Index*>(i);
   if (!ix) return VSK_ERR_INVALID_INPUT;
   cudaSetDevice(ix->ctx->device);
@@ -789,6 +792,7 @@ int32_t vsk_ivf_search_filtered_dev(vsk_index* i, const float* q, int64_t nq, in
 
 int32_t vsk_ivf_search_dev(vsk_index* i, const float* q, int64_t nq, int32_t k, int32_t nprobe, float* out_dist,
                            int64_t* out_ids) {
+  VSK_TRACE("vsk_ivf_search_dev");
   return vsk_ivf_search_filtered_dev(i, q, nq, k, nprobe, nullptr, out_dist, out_ids);
 }
 
@@ -815,6 +819,7 @@ int32_t vsk_ivf_set_masks(vsk_index* i, const uint64_t* masks) {
 }
 
 int32_t vsk_ivf_add_dev(vsk_index* i, const float* rows, int64_t n, const uint64_t* masks) {
+  VSK_TRACE("vsk_ivf_add_dev");
   Index* ix = reinterpret_cast<Index*>(i);
   if (!ix) return VSK_ERR_INVALID_INPUT;
   cudaSetDevice(ix->ctx->device);
@@ -822,6 +827,7 @@ int32_t vsk_ivf_add_dev(vsk_index* i, const float* rows, int64_t n, const uint64
 }
 
 int32_t vsk_ivf_add(vsk_index* i, const float* rows, int64_t n, const uint64_t* masks) {
+  VSK_TRACE("vsk_ivf_add");
   Index* ix = reinterpret_cast<Index*>(i);
   if (!ix) return VSK_ERR_INVALID_INPUT;
   Ctx* ctx = ix->ctx;
@@ -844,11 +850,13 @@ int32_t vsk_ivf_add(vsk_index* i, const float* rows, int64_t n, const uint64_t* 
 
 int32_t vsk_ivf_search(vsk_index* i, const float* q, int64_t nq, int32_t k, int32_t nprobe, float* out_dist,
                        int64_t* out_ids) {
+  VSK_TRACE("vsk_ivf_search");
   return vsk_ivf_search_filtered(i, q, nq, k, nprobe, nullptr, out_dist, out_ids);
 }
 
 int32_t vsk_ivf_search_filtered(vsk_index* i, const float* q, int64_t nq, int32_t k, int32_t nprobe, const uint64_t* qmasks,
                                 float* out_dist, int64_t* out_ids) {
+  VSK_TRACE("vsk_ivf_search_filtered");
   Index* ix = reinterpret_cast<Index*>(i);
   if (!ix) return VSK_ERR_INVALID_INPUT;
   Ctx* ctx = ix->ctx;

@@ -378,6 +378,7 @@ int32_t vsk_kmeans_trainer_create_dev(vsk_ctx* c, const float* rows, int64_t n, 
 
 int32_t vsk_kmeans_trainer_step_dev(vsk_kmeans_trainer* h, const float* centroids, float* sums, float* counts,
                                     float* inertia) {
+  VSK_TRACE("vsk_kmeans_trainer_step_dev");
   KMeansTrainer* t = reinterpret_cast<KMeansTrainer*>(h);
   if (!t) return VSK_ERR_INVALID_INPUT;
   cudaSetDevice(t->ctx->device);
@@ -425,6 +426,7 @@ int32_t vsk_kmeans_finish_dev(vsk_ctx* c, const float* sums, const float* counts
 int32_t vsk_kmeans_dev(vsk_ctx* c, const float* rows, int64_t n, int32_t dim, int32_t k, int32_t max_iters,
                        float tolerance, const float* init, float* centroids, int32_t* assign, float* inertia,
                        int32_t* iters_run) {
+  VSK_TRACE("vsk_kmeans_dev");
   Ctx* ctx = reinterpret_cast<Ctx*>(c);
   if (!ctx) return VSK_ERR_INVALID_INPUT;
   cudaSetDevice(ctx->device);
@@ -434,6 +436,7 @@ int32_t vsk_kmeans_dev(vsk_ctx* c, const float* rows, int64_t n, int32_t dim, in
 int32_t vsk_kmeans(vsk_ctx* c, const float* rows, int64_t n, int32_t dim, int32_t k, int32_t max_iters,
                    float tolerance, const float* init, float* centroids, int32_t* assign, float* inertia,
                    int32_t* iters_run) {
+  VSK_TRACE("vsk_kmeans");
   Ctx* ctx = reinterpret_cast<Ctx*>(c);
   if (!ctx) return VSK_ERR_INVALID_INPUT;
   cudaSetDevice(ctx->device);
@@ -466,6 +469,7 @@ int32_t vsk_kmeans(vsk_ctx* c, const float* rows, int64_t n, int32_t dim, int32_
 
 int32_t vsk_assign_dev(vsk_ctx* c, const float* rows, int64_t n, int32_t dim, const float* centroids, int32_t k,
                        int32_t* assign, float* dist) {
+  VSK_TRACE("vsk_assign_dev");
   Ctx* ctx = reinterpret_cast<Ctx*>(c);
   if (!ctx) return VSK_ERR_INVALID_INPUT;
   cudaSetDevice(ctx->device);

@@ -250,6 +250,7 @@ extern "C" {
 
 int32_t vsk_kmeans_init_plusplus_dev(vsk_ctx* c, const float* rows, int64_t n, int32_t dim, int32_t k, uint64_t seed,
                                      float* centroids, int64_t* picked) {
+  VSK_TRACE("vsk_kmeans_init_plusplus_dev");
   Ctx* ctx = reinterpret_cast<Ctx*>(c);
   if (!ctx) return VSK_ERR_INVALID_INPUT;
   cudaSetDevice(ctx->device);
@@ -258,6 +259,7 @@ int32_t vsk_kmeans_init_plusplus_dev(vsk_ctx* c, const float* rows, int64_t n, i
 
 int32_t vsk_kmeans_init_plusplus(vsk_ctx* c, const float* rows, int64_t n, int32_t dim, int32_t k, uint64_t seed,
                                  float* centroids, int64_t* picked) {
+  VSK_TRACE("vsk_kmeans_init_plusplus");
   Ctx* ctx = reinterpret_cast<Ctx*>(c);
   if (!ctx) return VSK_ERR_INVALID_INPUT;
   cudaSetDevice(ctx->device);

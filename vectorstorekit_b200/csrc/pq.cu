@@ -455,6 +455,7 @@ int32_t vsk_pq_train_dev(vsk_ctx* c, const float* rows, int64_t n, int32_t dim, 
 
 int32_t vsk_pq_encode_dev(vsk_ctx* c, const float* codebooks, int32_t dim, int32_t segments, int32_t codebook_size,
                           const float* rows, int64_t n, uint8_t* codes) {
+  VSK_TRACE("vsk_pq_encode_dev");
   Ctx* ctx = reinterpret_cast<Ctx*>(c);
   if (!ctx) return VSK_ERR_INVALID_INPUT;
   cudaSetDevice(ctx->device);
@@ -468,6 +469,7 @@ int32_t vsk_pq_encode_dev(vsk_ctx* c, const float* codebooks, int32_t dim, int32
 
 int32_t vsk_pq_encode(vsk_ctx* c, const float* codebooks, int32_t dim, int32_t segments, int32_t codebook_size,
                       const float* rows, int64_t n, uint8_t* codes) {
+  VSK_TRACE("vsk_pq_encode");
   Ctx* ctx = reinterpret_cast<Ctx*>(c);
   if (!ctx) return VSK_ERR_INVALID_INPUT;
   cudaSetDevice(ctx->device);

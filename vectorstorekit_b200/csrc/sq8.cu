@@ -286,6 +286,7 @@ int32_t vsk_sq8_params_dev(vsk_ctx* c, const float* minv, const float* maxv, int
 
 int32_t vsk_sq8_encode_dev(vsk_ctx* c, const float* rows, int64_t n, int32_t dim, const float* scale,
                            const float* offset, int8_t* codes) {
+  VSK_TRACE("vsk_sq8_encode_dev");
   Ctx* ctx;
   VSK_TRY(check_ctx(c, &ctx));
   if (n <= 0) return fail(ctx, VSK_ERR_EMPTY_INPUT, "no rows");
@@ -356,6 +357,7 @@ int32_t vsk_sq8_train(vsk_ctx* c, const float* rows, int64_t n, int32_t dim, int
 
 int32_t vsk_sq8_encode(vsk_ctx* c, const float* rows, int64_t n, int32_t dim, const float* scale, const float* offset,
                        int8_t* codes) {
+  VSK_TRACE("vsk_sq8_encode");
   Ctx* ctx;
   VSK_TRY(check_ctx(c, &ctx));
   if (n <= 0) return fail(ctx, VSK_ERR_EMPTY_INPUT, "no rows");
@@ -404,6 +406,7 @@ int32_t vsk_sq8_index_create(vsk_ctx* c, int32_t metric, int32_t dim, const floa
 }
 
 int32_t vsk_sq8_index_add(vsk_index* i, const int8_t* codes, int64_t n) {
+  VSK_TRACE("vsk_sq8_index_add");
   Index* ix = reinterpret_cast<Index*>(i);
   if (!ix) return VSK_ERR_INVALID_INPUT;
   cudaSetDevice(ix->ctx->device);
@@ -411,6 +414,7 @@ int32_t vsk_sq8_index_add(vsk_index* i, const int8_t* codes, int64_t n) {
 }
 
 int32_t vsk_sq8_index_add_dev(vsk_index* i, const int8_t* codes, int64_t n) {
+  VSK_TRACE("vsk_sq8_index_add_dev");
   Index* ix = reinterpret_cast<Index*>(i);
   if (!ix) return VSK_ERR_INVALID_INPUT;
   cudaSetDevice(ix->ctx->device);

@@ -1809,6 +1809,7 @@ struct QueryOperands {
 };
 
 int32_t prepare_query_operands(Index* ix, const float* q, int64_t nq, QueryOperands* out) {
+  VSK_TRACE("vsk:query_operands");
   Ctx* ctx = ix->ctx;
   static bool carveout_done = false;
   if (!carveout_done) {
@@ -1927,6 +1928,7 @@ int32_t cand_lists(Ctx* ctx, int64_t nq, CandLists* cand) {
 // qmasks (or null): per-query filter masks; rows are then filtered in the contraction's epilogue.
 int32_t tensor_search_begin(Index* ix, const float* q, int64_t nq, int32_t k, const float* qnorm, const uint64_t* qmasks,
                             int32_t shards, float* bound_out) {
+  VSK_TRACE("vsk:scan");
   Ctx* ctx = ix->ctx;
   ctx->pending[ctx->lane] = ShardPending{};
   VSK_TRY(tensor_prepare(ix));
@@ -2030,6 +2032,7 @@ int32_t tensor_search_begin(Index* ix, const float* q, int64_t nq, int32_t k, co
 // Second half, part one: everything that can be enqueued without looking at results - the certifying compaction
 // (a shard's), the exact re-scoring, the final order, and the copy of the flag words to pinned host memory.
 int32_t tensor_search_finish_issue(Index* ix, const float* ext_bound, float* out_dist, int64_t* out_ids) {
+  VSK_TRACE("vsk:finish");
   Ctx* ctx = ix->ctx;
   ShardPending& pd = ctx->pending[ctx->lane];
   if (!pd.active || !pd.tensor || pd.ix != ix || pd.issued)
@@ -2374,6 +2377,7 @@ bool ivf_tensor_applicable(const Index* ix, int64_t nq, int32_t nprobe, int32_t 
 
 int32_t ivf_tensor_search(Index* ix, const float* q, int64_t nq, const int64_t* probes, int32_t nprobe, int32_t k,
                           const uint64_t* qmasks, float* out_dist, int64_t* out_ids, std::vector<int32_t>* flagged) {
+  VSK_TRACE("vsk:ivf_list_scan");
   Ctx* ctx = ix->ctx;
   flagged->clear();
   VSK_TRY(tensor_prepare(ix));
@@ -2606,6 +2610,7 @@ void tensor_assign_release(TensorAssign* ta) {
 
 int32_t tensor_assign(Ctx* ctx, TensorAssign* ta, const float* rows, const float* centroids, int32_t k,
                       int32_t* assign, float* dist, bool assign_holds_previous) {
+  VSK_TRACE("vsk:assign");
   static_assert(sizeof(CUtensorMap) <= sizeof(ta->map_rows), "tensor map storage too small");
   const int64_t n = ta->n;
   const int dim = ta->dim, dim16 = ta->dim16;
