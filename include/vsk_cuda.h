@@ -338,6 +338,14 @@ int32_t vsk_search_sharded_dev(vsk_index* index, const float* queries, int64_t n
                                int32_t layout, float* out_dist, int64_t* out_ids);
 int32_t vsk_search_sharded(vsk_index* index, const float* queries, int64_t nq, int32_t k, const uint64_t* qmasks,
                            int32_t layout, float* out_dist, int64_t* out_ids);
+/* The same for an IVF index whose rows are sharded: every rank holds a slice of every list (same centroids on all
+ * ranks - train with vsk_kmeans_trainer_* and all-reduced sums - and vsk_index_set_id_base = the shard's first global
+ * row).  Each rank probes `nprobe` lists of its shard (IVFIndex.search, Indexes/IVFIndex.swift:124-202), then the
+ * exchange and the merge of vsk_search_sharded.  qmasks may be NULL. */
+int32_t vsk_ivf_search_sharded_dev(vsk_index* index, const float* queries, int64_t nq, int32_t k, int32_t nprobe,
+                                   const uint64_t* qmasks, int32_t layout, float* out_dist, int64_t* out_ids);
+int32_t vsk_ivf_search_sharded(vsk_index* index, const float* queries, int64_t nq, int32_t k, int32_t nprobe,
+                               const uint64_t* qmasks, int32_t layout, float* out_dist, int64_t* out_ids);
 /* Timing of the phases of the last vsk_search_sharded(_dev) call on this context, in milliseconds, from CUDA
  * events on the context's streams (recorded when vsk_profile is on; zeros otherwise):
  *   [0] query copy and exchange  [1] scan and compactions up to the bound  [2] bound all-reduce

@@ -588,3 +588,26 @@ def test_async_search_is_the_blocking_search(vsk, cpu_oracle):
         ix.close()
     finally:
         dev.close()
+
+
+@pytest.mark.parametrize("d", [96, 200, 768])
+def test_ring_stage_granularity_does_not_change_results(vsk, cpu_oracle, d):
+    """The contraction kernel's operand ring holds one or two K blocks per stage (vsk_tuning.stage_kblocks): the same
+    MMAs in the same order either way, so the results are identical bit for bit (odd numbers of K blocks included)."""
+    dev = vsk.CUDAComputeDevice(0)
+    try:
+        rng = np.random.default_rng(1000 + d)
+        x = rng.standard_normal((30_000, d)).astype(np.float32)
+        q = rng.standard_normal((600, d)).astype(np.float32)
+        ix = vsk.FlatIndex(dev, d, "euclidean")
+        ix.add(x)
+        out = []
+        for kblocks in (1, 2):
+            dev.set_tuning(stage_kblocks=kblocks)
+            out.append(ix.batchSearch(q, 20))
+        assert np.array_equal(out[0][1], out[1][1]) and np.array_equal(out[0][0], out[1][0])
+        rd, ri = cpu_oracle.flat_search(oracle.EUCLIDEAN, q, x, 20)
+        assert_topk_parity(out[1][0], out[1][1], rd, ri)
+        ix.close()
+    finally:
+        dev.close()

@@ -3,8 +3,9 @@
 One GPU: a communicator of one rank must return exactly what the plain search returns, in every layout and through
 both the host-pointer and the device-pointer form.  Two or more GPUs (skipped on a one-GPU box): one child process per
 GPU, each holding a row shard, joined through vsk_comm_unique_id / vsk_comm_init; the merged result must equal the CPU
-oracle's search over the whole database (ties by global row), for fp32 cosine / euclidean, a filtered batch and an
-int8 index, with slice and gathered layouts, uneven query slices and a batch large enough for the two-lane schedule.
+oracle's search over the whole database (ties by global row), for fp32 cosine / euclidean, a filtered batch, an int8
+index and an IVF index (vsk_ivf_search_sharded: every shard holds a slice of every list), with slice and gathered
+layouts, uneven query slices and a batch large enough for the two-lane schedule.
 """
 import os
 import subprocess
@@ -47,6 +48,17 @@ def test_one_rank_communicator_equals_plain_search(vsk, cpu_oracle):
         rd, ri = cpu_oracle.flat_search(oracle.COSINE, q, x, 12)
         assert_topk_parity(pd, pi, rd, ri)
         ix.close()
+        # an IVF index through vsk_ivf_search_sharded
+        iv = vsk.IVFIndex(dev, 96, numberOfCentroids=64, numberOfProbes=8, maxIterations=2, tolerance=-1.0)
+        iv.train(x, x[:64].copy())
+        iv.insert(x)
+        pd, pi = iv.batchSearch(q, 12)
+        for gather in (False, True):
+            sd, si = iv.shardedSearch(q, 12, gather=gather)
+            assert np.array_equal(si, pi) and np.array_equal(sd, pd)
+            dd, di = iv.shardedSearch(torch.as_tensor(q, device="cuda"), 12, gather=gather)
+            assert np.array_equal(di.cpu().numpy(), pi) and np.array_equal(dd.cpu().numpy(), pd)
+        iv.close()
         dev.comm_destroy()
         assert dev.comm_info() == (1, 0)
     finally:
@@ -95,7 +107,14 @@ CHILD = textwrap.dedent("""
         if c.get("masked"):
             masks = rng.integers(0, 2 ** 63, n, dtype=np.uint64)
             qm = (np.uint64(1) << rng.integers(0, 63, nq).astype(np.uint64))
-        if c["kind"] == "sq8":
+        if c["kind"] == "ivf":
+            # every rank trains on the same rows from the same start (the update is deterministic: same centroids
+            # everywhere), then files only its own shard: a slice of every list
+            ix = vsk.IVFIndex(dev, d, numberOfCentroids=c["nlist"], numberOfProbes=c["nprobe"], maxIterations=3, tolerance=-1.0)
+            ix.train(x, x[:c["nlist"]].copy())
+            ix.insert(x[lo:hi])
+            np.savez(os.path.join(outdir, name + f"_rank{rank}.npz"), assign=ix.assignments(), centroids=ix.centroids)
+        elif c["kind"] == "sq8":
             mn, mx = x.min(0), x.max(0)
             sq = vsk.ScalarQuantizer(dev, per_dim=True)
             scale, offset = sq.set_range(torch.as_tensor(mn, device="cuda"), torch.as_tensor(mx, device="cuda"))
@@ -131,6 +150,7 @@ CASES = {
     "masked_dot": dict(kind="flat", metric="dotProduct", n=50_000, d=200, nq=600, k=16, seed=3, masked=True),
     "manhattan": dict(kind="flat", metric="manhattan", n=20_000, d=64, nq=130, k=8, seed=4),
     "int8_dot": dict(kind="sq8", metric="dotProduct", n=80_000, d=96, nq=700, k=10, seed=5),
+    "ivf_euclid": dict(kind="ivf", metric="euclidean", n=60_000, d=64, nq=900, k=10, seed=6, nlist=96, nprobe=12),
 }
 
 
@@ -175,7 +195,14 @@ def test_sharded_search_over_ranks_equals_unsharded_oracle(cpu_oracle, tmp_path,
             qm = (np.uint64(1) << rng.integers(0, 63, nq).astype(np.uint64))
         got = np.load(tmp_path / (name + ".npz"))
         mid = oracle.METRIC_IDS[c["metric"]]
-        if c["kind"] == "sq8":
+        if c["kind"] == "ivf":
+            # shared state, as in the single-GPU IVF tests: the GPU-trained centroids and the shards' list membership
+            parts = [np.load(tmp_path / f"{name}_rank{r}.npz") for r in range(world)]
+            for part in parts[1:]:
+                assert np.array_equal(part["centroids"], parts[0]["centroids"])     # same centroids on every rank
+            asg = np.concatenate([part["assign"] for part in parts])
+            rd, ri = cpu_oracle.ivf_search(q, x, parts[0]["centroids"], asg, c["nprobe"], k)
+        elif c["kind"] == "sq8":
             scale = (np.float32(255.0) / (x.max(0) - x.min(0))).astype(np.float32)
             offset = (-x.min(0) * scale - np.float32(128.0)).astype(np.float32)
             codes = cpu_oracle.sq8_encode(x, scale, offset)

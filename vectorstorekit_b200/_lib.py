@@ -78,6 +78,8 @@ SIGNATURES = {
     "vsk_sharded_slice": (None, [C.c_int64, C.c_int32, C.c_int32, C.POINTER(C.c_int64), C.POINTER(C.c_int64)]),
     "vsk_search_sharded_dev": (C.c_int32, [vp, vp, C.c_int64, C.c_int32, vp, C.c_int32, vp, vp]),
     "vsk_search_sharded": (C.c_int32, [vp, vp, C.c_int64, C.c_int32, vp, C.c_int32, vp, vp]),
+    "vsk_ivf_search_sharded_dev": (C.c_int32, [vp, vp, C.c_int64, C.c_int32, C.c_int32, vp, C.c_int32, vp, vp]),
+    "vsk_ivf_search_sharded": (C.c_int32, [vp, vp, C.c_int64, C.c_int32, C.c_int32, vp, C.c_int32, vp, vp]),
     "vsk_sharded_phase_ms": (C.c_int32, [vp, C.POINTER(C.c_float)]),
     "vsk_coarse_values_dev": (C.c_int32, [vp, vp, C.c_int64, C.c_int64, vp, vp]),
     "vsk_batch_distances": (C.c_int32, [vp, C.c_int32, vp, C.c_int64, vp, C.c_int64, C.c_int32, vp]),

@@ -130,23 +130,32 @@ static int32_t exchange_keys(Ctx* ctx, const NcclApi* api, Comm* cm, const uint6
 
 int32_t flat_search_dev_entry(Index* ix, const float* q, int64_t nq, int32_t k, const uint64_t* qmasks, float* out_dist,
                               int64_t* out_ids);   // api.cu: vsk_search_dev without the device selection
+int32_t ivf_search_dev_entry(Index* ix, const float* q, int64_t nq, int32_t k, int32_t nprobe, const uint64_t* qmasks,
+                             float* out_dist, int64_t* out_ids);   // ivf.cu
 
+// nprobe > 0: an IVF index whose every shard holds a slice of every list (the centroids are the same on all ranks:
+// vsk_kmeans_trainer_* with all-reduced sums), probed with that many lists; nprobe == 0: flat fp32 / int8.
 static int32_t search_sharded_dev(Index* ix, const float* q, int64_t nq, int32_t k, const uint64_t* qmasks, int32_t layout,
-                                  float* out_dist, int64_t* out_ids) {
+                                  float* out_dist, int64_t* out_ids, int32_t nprobe = 0) {
   Ctx* ctx = ix->ctx;
   Comm* cm = ctx->comm;
   if (nq <= 0 || ix->n <= 0) return fail(ctx, VSK_ERR_EMPTY_INPUT, "empty queries or empty index");
   if (k <= 0 || k > kCandCap / 2) return fail(ctx, VSK_ERR_INVALID_INPUT, "k must be in [1, %d]", kCandCap / 2);
   if (!q || !out_dist || !out_ids) return fail(ctx, VSK_ERR_INVALID_INPUT, "null pointer");
-  if (ix->kind != INDEX_FLAT_F32 && ix->kind != INDEX_FLAT_I8)
-    return fail(ctx, VSK_ERR_UNSUPPORTED_OPERATION, "the sharded search covers flat fp32 and int8 indexes");
-  if (qmasks && !(ix->kind == INDEX_FLAT_F32 && ix->has_masks))
+  const bool ivf = nprobe > 0;
+  if (ivf ? ix->kind != INDEX_IVF : (ix->kind != INDEX_FLAT_F32 && ix->kind != INDEX_FLAT_I8))
+    return fail(ctx, VSK_ERR_UNSUPPORTED_OPERATION,
+                "the sharded search covers flat fp32 and int8 indexes (vsk_search_sharded) and IVF indexes (vsk_ivf_search_sharded)");
+  if (qmasks && !((ix->kind == INDEX_FLAT_F32 || ix->kind == INDEX_IVF) && ix->has_masks))
     return fail(ctx, VSK_ERR_INVALID_INPUT, "query masks given but the index has no row masks");
+  auto whole_local_search = [&](float* d, int64_t* i) -> int32_t {
+    return ivf ? ivf_search_dev_entry(ix, q, nq, k, nprobe, qmasks, d, i) : flat_search_dev_entry(ix, q, nq, k, qmasks, d, i);
+  };
   const int what = layout & 15;
   if (what != VSK_SHARDED_SLICE && what != VSK_SHARDED_ALL) return fail(ctx, VSK_ERR_INVALID_INPUT, "unknown result layout %d", what);
   if (!cm || cm->nranks == 1) {
     // one shard: the plain search is the whole answer, and every layout is the same
-    return flat_search_dev_entry(ix, q, nq, k, qmasks, out_dist, out_ids);
+    return whole_local_search(out_dist, out_ids);
   }
   const NcclApi* api = nccl_api();
   if (!api) return fail(ctx, VSK_ERR_EXECUTION_FAILED, "NCCL is not available");
@@ -237,7 +246,7 @@ static int32_t search_sharded_dev(Index* ix, const float* q, int64_t nq, int32_t
   } else {
     phase_mark(ctx, cm, 2);
     phase_mark(ctx, cm, 3);
-    VSK_TRY(flat_search_dev_entry(ix, q, nq, k, qmasks, loc_d, loc_i));
+    VSK_TRY(whole_local_search(loc_d, loc_i));
   }
 
   // ---- exchange and merge: this rank's slice of the queries ----
@@ -356,9 +365,8 @@ void vsk_sharded_slice(int64_t nq, int32_t nranks, int32_t rank, int64_t* first,
   if (count) *count = c;
 }
 
-int32_t vsk_search_sharded_dev(vsk_index* i, const float* q, int64_t nq, int32_t k, const uint64_t* qmasks, int32_t layout,
-                               float* out_dist, int64_t* out_ids) {
-  VSK_TRACE("vsk_search_sharded_dev");
+static int32_t sharded_dev_entry(vsk_index* i, const float* q, int64_t nq, int32_t k, const uint64_t* qmasks, int32_t layout,
+                                 float* out_dist, int64_t* out_ids, int32_t nprobe) {
   Index* ix = reinterpret_cast<Index*>(i);
   if (!ix) return VSK_ERR_INVALID_INPUT;
   Ctx* ctx = ix->ctx;
@@ -369,15 +377,14 @@ int32_t vsk_search_sharded_dev(vsk_index* i, const float* q, int64_t nq, int32_t
       cudaEventRecord(ctx->comm->ev[0], ctx->stream_main);
     }
   }
-  VSK_TRY(search_sharded_dev(ix, q, nq, k, qmasks, layout, out_dist, out_ids));
+  VSK_TRY(search_sharded_dev(ix, q, nq, k, qmasks, layout, out_dist, out_ids, nprobe));
   VSK_CUDA(ctx, cudaStreamSynchronize(ctx->stream_main));
   collect_phases(ctx->comm);
   return VSK_OK;
 }
 
-int32_t vsk_search_sharded(vsk_index* i, const float* q, int64_t nq, int32_t k, const uint64_t* qmasks, int32_t layout,
-                           float* out_dist, int64_t* out_ids) {
-  VSK_TRACE("vsk_search_sharded");
+static int32_t sharded_host_entry(vsk_index* i, const float* q, int64_t nq, int32_t k, const uint64_t* qmasks, int32_t layout,
+                                  float* out_dist, int64_t* out_ids, int32_t nprobe) {
   Index* ix = reinterpret_cast<Index*>(i);
   if (!ix) return VSK_ERR_INVALID_INPUT;
   Ctx* ctx = ix->ctx;
@@ -417,7 +424,7 @@ int32_t vsk_search_sharded(vsk_index* i, const float* q, int64_t nq, int32_t k, 
     VSK_CUDA(ctx, cudaMemcpyAsync(dm, qmasks, (size_t)nq * 8, cudaMemcpyHostToDevice, ctx->stream));
     ctx->stats.h2d_bytes += nq * 8;
   }
-  VSK_TRY(search_sharded_dev(ix, (const float*)dq, nq, k, (const uint64_t*)dm, layout, (float*)dd, (int64_t*)di));
+  VSK_TRY(search_sharded_dev(ix, (const float*)dq, nq, k, (const uint64_t*)dm, layout, (float*)dd, (int64_t*)di, nprobe));
   const int64_t outn = ((layout & 15) == VSK_SHARDED_SLICE && G > 1) ? count : nq;
   if (outn > 0) {
     VSK_CUDA(ctx, cudaMemcpyAsync(out_dist, dd, (size_t)outn * k * 4, cudaMemcpyDeviceToHost, ctx->stream));
@@ -427,6 +434,36 @@ int32_t vsk_search_sharded(vsk_index* i, const float* q, int64_t nq, int32_t k, 
   ctx->stats.d2h_bytes += outn * k * 12;
   collect_phases(cm);
   return VSK_OK;
+}
+
+int32_t vsk_search_sharded_dev(vsk_index* i, const float* q, int64_t nq, int32_t k, const uint64_t* qmasks, int32_t layout,
+                               float* out_dist, int64_t* out_ids) {
+  VSK_TRACE("vsk_search_sharded_dev");
+  return sharded_dev_entry(i, q, nq, k, qmasks, layout, out_dist, out_ids, 0);
+}
+
+int32_t vsk_search_sharded(vsk_index* i, const float* q, int64_t nq, int32_t k, const uint64_t* qmasks, int32_t layout,
+                           float* out_dist, int64_t* out_ids) {
+  VSK_TRACE("vsk_search_sharded");
+  return sharded_host_entry(i, q, nq, k, qmasks, layout, out_dist, out_ids, 0);
+}
+
+int32_t vsk_ivf_search_sharded_dev(vsk_index* i, const float* q, int64_t nq, int32_t k, int32_t nprobe, const uint64_t* qmasks,
+                                   int32_t layout, float* out_dist, int64_t* out_ids) {
+  VSK_TRACE("vsk_ivf_search_sharded_dev");
+  Index* ix = reinterpret_cast<Index*>(i);
+  if (!ix) return VSK_ERR_INVALID_INPUT;
+  if (nprobe <= 0) return fail(ix->ctx, VSK_ERR_INVALID_INPUT, "nprobe must be positive");
+  return sharded_dev_entry(i, q, nq, k, qmasks, layout, out_dist, out_ids, nprobe);
+}
+
+int32_t vsk_ivf_search_sharded(vsk_index* i, const float* q, int64_t nq, int32_t k, int32_t nprobe, const uint64_t* qmasks,
+                               int32_t layout, float* out_dist, int64_t* out_ids) {
+  VSK_TRACE("vsk_ivf_search_sharded");
+  Index* ix = reinterpret_cast<Index*>(i);
+  if (!ix) return VSK_ERR_INVALID_INPUT;
+  if (nprobe <= 0) return fail(ix->ctx, VSK_ERR_INVALID_INPUT, "nprobe must be positive");
+  return sharded_host_entry(i, q, nq, k, qmasks, layout, out_dist, out_ids, nprobe);
 }
 
 int32_t vsk_sharded_phase_ms(vsk_ctx* c, float* ms) {

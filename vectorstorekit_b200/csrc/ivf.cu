@@ -722,6 +722,12 @@ int32_t ivf_search_dev(Index* ix, const float* q, int64_t nq, int32_t k, int32_t
 }
 
 }  // namespace
+
+// the IVF search for callers inside the library (the sharded search, comm.cu); the device is already selected
+int32_t ivf_search_dev_entry(Index* ix, const float* q, int64_t nq, int32_t k, int32_t nprobe, const uint64_t* qmasks,
+                             float* out_dist, int64_t* out_ids) {
+  return ivf_search_dev(ix, q, nq, k, nprobe, qmasks, out_dist, out_ids);
+}
 }  // namespace vsk
 
 using namespace vsk;

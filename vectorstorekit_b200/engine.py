@@ -508,8 +508,14 @@ def sharded_slice(nq: int, nranks: int, rank: int):
 
 
 class _ShardedSearchMixin:
-    """``vsk_search_sharded``: the row-sharded form of ``batchSearch`` for a flat fp32 or int8 index whose device
-    object has joined a communicator (``CUDAComputeDevice.comm_init``).  Every rank passes the same queries."""
+    """``vsk_search_sharded`` (``vsk_ivf_search_sharded`` for an IVF index): the row-sharded form of ``batchSearch``
+    for an index whose device object has joined a communicator (``CUDAComputeDevice.comm_init``).  Every rank passes
+    the same queries."""
+    _sharded_names = ("vsk_search_sharded_dev", "vsk_search_sharded")
+
+    def _sharded_extra(self):
+        """Arguments between k and the query masks (the IVF form's nprobe)."""
+        return ()
 
     def shardedSearch(self, queries, k: int, filter_masks=None, gather: bool = False, split_queries: bool = False,
                       out=None):
@@ -529,7 +535,8 @@ class _ShardedSearchMixin:
             od, oi = out if out is not None else (torch.empty((max(rows, 1), k), dtype=torch.float32, device=q.device),
                                                   torch.empty((max(rows, 1), k), dtype=torch.int64, device=q.device))
             qm = filter_masks.contiguous() if filter_masks is not None else None
-            self.dev.check(self._lib.vsk_search_sharded_dev(self._h, _ptr(q), nq, k, _ptr(qm), layout, _ptr(od), _ptr(oi)))
+            fn = getattr(self._lib, self._sharded_names[0])
+            self.dev.check(fn(self._h, _ptr(q), nq, k, *self._sharded_extra(), _ptr(qm), layout, _ptr(od), _ptr(oi)))
             return od[:rows], oi[:rows]
         if torch is not None and isinstance(queries, torch.Tensor):      # a (pinned) CPU tensor
             q = queries.contiguous()
@@ -537,12 +544,14 @@ class _ShardedSearchMixin:
                                                   torch.empty((max(rows, 1), k), dtype=torch.int64))
             qm = filter_masks.contiguous() if filter_masks is not None else None
             ptr = lambda t: C.c_void_p(t.data_ptr()) if t is not None else None
-            self.dev.check(self._lib.vsk_search_sharded(self._h, ptr(q), nq, k, ptr(qm), layout, ptr(od), ptr(oi)))
+            fn = getattr(self._lib, self._sharded_names[1])
+            self.dev.check(fn(self._h, ptr(q), nq, k, *self._sharded_extra(), ptr(qm), layout, ptr(od), ptr(oi)))
             return od[:rows], oi[:rows]
         q = _host(queries, np.float32)
         od, oi = out if out is not None else (np.empty((max(rows, 1), k), np.float32), np.empty((max(rows, 1), k), np.int64))
         qm = _host(filter_masks, np.uint64) if filter_masks is not None else None
-        self.dev.check(self._lib.vsk_search_sharded(self._h, _ptr(q), nq, k, _ptr(qm), layout, _ptr(od), _ptr(oi)))
+        fn = getattr(self._lib, self._sharded_names[1])
+        self.dev.check(fn(self._h, _ptr(q), nq, k, *self._sharded_extra(), _ptr(qm), layout, _ptr(od), _ptr(oi)))
         return od[:rows], oi[:rows]
 
 
@@ -794,7 +803,7 @@ class KMeansTrainer:
             pass
 
 
-class IVFIndex(_IndexBase):
+class IVFIndex(_IndexBase, _ShardedSearchMixin):
     """``IVFIndex`` (``Indexes/IVFIndex.swift``): ``train(on:)`` runs k-means for the centroids, ``insert`` files rows
     under their nearest centroid's list, ``search`` probes ``numberOfProbes`` lists (all of them for
     ``SearchStrategy.exact``) with rooted L2, after the metadata filter when one is given.  Ids are insertion
@@ -931,6 +940,19 @@ class IVFIndex(_IndexBase):
         qm = _host(filter_masks, np.uint64) if filter_masks is not None else None
         self.dev.check(self._lib.vsk_ivf_search_filtered(self._h, _ptr(q), nq, k, nprobe, _ptr(qm), _ptr(od), _ptr(oi)))
         return od, oi
+
+    # the row-sharded form (``vsk_ivf_search_sharded``): every rank holds a slice of every list and probes
+    # ``numberOfProbes`` of them; see ``_ShardedSearchMixin.shardedSearch``
+    _sharded_names = ("vsk_ivf_search_sharded_dev", "vsk_ivf_search_sharded")
+
+    def _sharded_extra(self):
+        return (int(self.numberOfProbes),)
+
+    def shardedSearch(self, queries, k: int, filter_masks=None, gather: bool = False, split_queries: bool = False, out=None):
+        if not self.trained:
+            raise NotTrained("Index must be trained before use")
+        self._flush()
+        return _ShardedSearchMixin.shardedSearch(self, queries, k, filter_masks, gather, split_queries, out)
 
     def search(self, query, k: int, strategy: SearchStrategy = SearchStrategy.adaptive, filter_mask: Optional[int] = None):
         fm = None if filter_mask is None else np.array([filter_mask], np.uint64)

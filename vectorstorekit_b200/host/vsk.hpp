@@ -268,16 +268,42 @@ class IVFIndex {
                      assign.data(), &inertia, &iters), dev_->ctx());
     trained_ = true;
   }
-  void insert(const float* rows, int64_t n) {
+  // IVFIndex.insert (Indexes/IVFIndex.swift:80-122): the first rows build the lists, later ones are filed behind the
+  // rows their lists already hold (no rebuild).  `masks` (one 64-bit filter mask per row) either on every call or on none.
+  void insert(const float* rows, int64_t n, const uint64_t* masks = nullptr) {
     if (!trained_) throw NotTrained(VSK_ERR_NOT_TRAINED, "Index must be trained before use");
-    if (ix_) { vsk_index_destroy(ix_); ix_ = nullptr; }
-    check(vsk_ivf_build(dev_->ctx(), centroids_.data(), nlist_, rows, n, dim_, &ix_), dev_->ctx());
+    if (!ix_) {
+      check(vsk_ivf_build(dev_->ctx(), centroids_.data(), nlist_, rows, n, dim_, &ix_), dev_->ctx());
+      if (masks) check(vsk_ivf_set_masks(ix_, masks), dev_->ctx());
+    } else {
+      check(vsk_ivf_add(ix_, rows, n, masks), dev_->ctx());
+    }
   }
-  SearchResults batchSearch(const float* queries, int64_t nq, int32_t k, bool exact = false) const {
+  // search(query:k:strategy:filter:) for a batch: filter_masks = one mask per query (a row is eligible when it shares a bit)
+  SearchResults batchSearch(const float* queries, int64_t nq, int32_t k, bool exact = false,
+                            const uint64_t* filter_masks = nullptr) const {
     if (!trained_ || !ix_) throw NotTrained(VSK_ERR_NOT_TRAINED, "Index must be trained before use");
     SearchResults r; r.nq = nq; r.k = k;
     r.distances.resize((size_t)nq * k); r.ids.resize((size_t)nq * k);
-    check(vsk_ivf_search(ix_, queries, nq, k, exact ? nlist_ : nprobe_, r.distances.data(), r.ids.data()), dev_->ctx());
+    check(vsk_ivf_search_filtered(ix_, queries, nq, k, exact ? nlist_ : nprobe_, filter_masks, r.distances.data(), r.ids.data()),
+          dev_->ctx());
+    return r;
+  }
+  // Rows sharded over the ranks of the device's communicator (every rank holds a slice of every list, same centroids):
+  // see FlatIndex::shardedSearch for the layouts.
+  void setIdBase(int64_t base) { check(vsk_index_set_id_base(ix_, base), dev_->ctx()); }
+  SearchResults shardedSearch(const float* queries, int64_t nq, int32_t k, const uint64_t* filter_masks = nullptr,
+                              bool gather = false, int64_t* firstQuery = nullptr) const {
+    if (!trained_ || !ix_) throw NotTrained(VSK_ERR_NOT_TRAINED, "Index must be trained before use");
+    const auto cm = dev_->communicator();
+    int64_t first = 0, count = nq;
+    if (!gather) vsk_sharded_slice(nq, cm.first, cm.second, &first, &count);
+    SearchResults r; r.nq = count; r.k = k;
+    r.distances.resize((size_t)std::max<int64_t>(count, 1) * k); r.ids.resize((size_t)std::max<int64_t>(count, 1) * k);
+    check(vsk_ivf_search_sharded(ix_, queries, nq, k, nprobe_, filter_masks, gather ? VSK_SHARDED_ALL : VSK_SHARDED_SLICE,
+                                 r.distances.data(), r.ids.data()), dev_->ctx());
+    r.distances.resize((size_t)count * k); r.ids.resize((size_t)count * k);
+    if (firstQuery) *firstQuery = first;
     return r;
   }
   const std::vector<float>& centroids() const { return centroids_; }
