@@ -124,6 +124,28 @@ __device__ __forceinline__ float max32(const float (&v)[32]) {
   return m[0];
 }
 
+// max of three in one instruction (sm_100 has a three-input max; NaN operands are passed over as in fmaxf)
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
+// largest of v[O .. O+7]: four instructions, depth three
+template <int O>
+__device__ __forceinline__ float max8(const float (&v)[32]) {
+  return max3(v[O + 6], v[O + 7], fmaxf(max3(v[O], v[O + 1], v[O + 2]), max3(v[O + 3], v[O + 4], v[O + 5])));
+}
+
+// bit j of the result: v[O + j] >= bar, j = 0..7
+template <int O>
+__device__ __forceinline__ uint32_t ge_bits8(const float (&v)[32], float bar) {
+  uint32_t bits = 0;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) bits |= (v[O + j] >= bar) ? (1u << j) : 0u;
+  return bits;
+}
+
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 fp16), 128-byte
 // swizzled, rows packed: 8-row groups 1024 bytes apart.
 __device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {

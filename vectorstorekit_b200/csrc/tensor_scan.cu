@@ -606,6 +606,14 @@ struct AsArgs {
   uint32_t wait_limit;
 };
 
+// The accumulator a value must reach to be a hit: alpha * acc <= thr with alpha < 0 holds for every acc >= thr / alpha;
+// thr * (1 / alpha) and the product alpha * acc each differ from the exact quotient by a few units in the last place,
+// so the bar is lowered by 2^-20 of its size (and a denormal's worth): no hit of the product form is lost.
+__device__ __forceinline__ float as_bar(float thr, float inv_alpha) {
+  const float b = thr * inv_alpha;
+  return b - fabsf(b) * 9.5367431640625e-7f - 1e-37f;
+}
+
 template <int MODE>
 __global__ void __launch_bounds__(AS_THREADS, 1)
 assign_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_c, AsArgs a) {
@@ -751,6 +759,7 @@ assign_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
     const int part = ew >> 2;
     const int c0 = part * GROUPS;
     const float alpha = __ldg(a.alpha);
+    const float inv_alpha = 1.0f / alpha;
     int64_t local = 0;
     bool ok = true;
     for (int b = b_first; ok && b < nb; b += b_step) {
@@ -763,6 +772,7 @@ assign_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
         const int64_t q = t * TM + et;
         const bool qok = q < a.n;
         const float thr = thr_next;
+        const float bar = as_bar(thr, inv_alpha);
         if (MODE == SCAN_THRESHOLD) {   // the next tile's threshold is in flight while this tile is processed
           const int64_t qn = (t + t_step) * TM + et;
           thr_next = (t + t_step < qtiles && qn < a.n) ? __ldg(a.thr + qn) : CUDART_INF_F;
@@ -785,26 +795,36 @@ assign_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
           __syncwarp();
           if (lane == 0) mbar_arrive(&sm->tmem_empty[acc]);
           const int left0 = a.k - (col_base + c0 * 32), left1 = left0 - 32;
-          // value = alpha * accumulator with alpha < 0: the smallest value is alpha times the largest accumulator
-          const bool mine0 = qok && left0 > 0 && max32(v0) * alpha <= thr;
-          const bool mine1 = qok && left1 > 0 && max32(v1) * alpha <= thr;
-          const bool partial = (left0 > 0 && left0 < 32) || (left1 > 0 && left1 < 32);   // the block's last, short group
-          if (!partial && !__any_sync(0xffffffffu, mine0 || mine1)) continue;
-#pragma unroll
-          for (int g = 0; g < 2; ++g) {
-            const int left = g == 0 ? left0 : left1;
-            if (left <= 0 || !(g == 0 ? mine0 : mine1)) continue;
-            const uint32_t colmask = left >= 32 ? 0xffffffffu : ((1u << left) - 1u);
-            uint32_t bits = 0;
-#pragma unroll
-            for (int j = 0; j < 32; ++j) bits |= ((g == 0 ? v0[j] : v1[j]) * alpha <= thr) ? (1u << j) : 0u;
-            bits &= colmask;
-            while (bits) {   // one or two hits as a rule
+          // value = alpha * accumulator <= thr with alpha < 0 is accumulator >= bar (bar = thr / alpha, lowered by more
+          // than the roundings of either form can differ: the hits are a superset, and every logged hit is evaluated
+          // exactly afterwards).  Eight columns at a time: the largest of eight costs four instructions, and only a
+          // set of eight that holds a hit is searched for its columns.
+          const float m00 = max8<0>(v0), m01 = max8<8>(v0), m02 = max8<16>(v0), m03 = max8<24>(v0);
+          const float m10 = max8<0>(v1), m11 = max8<8>(v1), m12 = max8<16>(v1), m13 = max8<24>(v1);
+          const bool mine0 = qok && left0 > 0 && max3(m00, m01, fmaxf(m02, m03)) >= bar;
+          const bool mine1 = qok && left1 > 0 && max3(m10, m11, fmaxf(m12, m13)) >= bar;
+          if (!__any_sync(0xffffffffu, mine0 || mine1)) continue;
+          auto log_hits = [&](uint32_t bits, int first_col) {   // one or two hits as a rule
+            bits = (first_col + 8 <= a.k) ? bits : (first_col < a.k ? bits & ((1u << (a.k - first_col)) - 1u) : 0u);
+            while (bits) {
               const int j = __ffs((int)bits) - 1;
               bits &= bits - 1u;
               const int slot = atomicAdd(&sm->log_n, 1);
-              if (slot < a.log_cap) my_log[slot] = make_uint2((uint32_t)q, (uint32_t)(col_base + (c0 + g) * 32 + j));
+              if (slot < a.log_cap) my_log[slot] = make_uint2((uint32_t)q, (uint32_t)(first_col + j));
             }
+          };
+          const int col0 = col_base + c0 * 32;
+          if (mine0) {
+            if (m00 >= bar) log_hits(ge_bits8<0>(v0, bar), col0);
+            if (m01 >= bar) log_hits(ge_bits8<8>(v0, bar), col0 + 8);
+            if (m02 >= bar) log_hits(ge_bits8<16>(v0, bar), col0 + 16);
+            if (m03 >= bar) log_hits(ge_bits8<24>(v0, bar), col0 + 24);
+          }
+          if (mine1) {
+            if (m10 >= bar) log_hits(ge_bits8<0>(v1, bar), col0 + 32);
+            if (m11 >= bar) log_hits(ge_bits8<8>(v1, bar), col0 + 40);
+            if (m12 >= bar) log_hits(ge_bits8<16>(v1, bar), col0 + 48);
+            if (m13 >= bar) log_hits(ge_bits8<24>(v1, bar), col0 + 56);
           }
           continue;
         }
