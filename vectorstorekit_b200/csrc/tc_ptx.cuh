@@ -38,6 +38,30 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// True in exactly one lane of a converged warp.  A warp that runs its loop converged and issues through the elected
+// lane keeps descriptors, coordinates and barrier addresses warp-uniform (the tensor and copy instructions take their
+// operands from uniform registers; inside an `if (lane == 0)` region every operand is moved there per instruction).
+__device__ __forceinline__ bool elect_one() {
+  uint32_t is_leader;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(is_leader));
+  return is_leader != 0;
+}
+// One look at the barrier, never suspended: true when the phase with this parity has completed.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 // Bounded wait.  Returns false (and raises the abort flag and the error word) when the limit runs out
 // or another role has already aborted.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int32_t* err, int code,
@@ -155,6 +179,20 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
   d |= (uint64_t)(1024 >> 4) << 32;            // stride between 8-row groups: 1024 bytes
   d |= (uint64_t)1 << 46;                      // descriptor version of this architecture
   d |= (uint64_t)2 << 61;                      // 128-byte swizzle
+  return d;
+}
+
+// The same for a tile of ONE K16 step: rows of 32 bytes (16 fp16), 32-byte swizzled, 8-row groups 256 bytes apart
+// (what a TMA box of 16 columns with CU_TENSOR_MAP_SWIZZLE_32B writes).
+constexpr int A_NARROW_BYTES = TM * 32;   // 4 KB
+constexpr int B_NARROW_BYTES = TN * 32;   // 8 KB
+__device__ __forceinline__ uint64_t make_desc_narrow(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3fff);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(256 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)6 << 61;                      // 32-byte swizzle
   return d;
 }
 

@@ -568,7 +568,7 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 constexpr int AS_EW = 16;
 constexpr int AS_THREADS = 64 + 32 * AS_EW;
 constexpr int AS_MAX_KB = 4;                       // k-blocks of the resident block (d + 16 fold columns <= 256)
-constexpr int AS_RING_BYTES = 192 * 1024;          // resident block + data-tile stages
+constexpr int AS_RING_BYTES = 216 * 1024;          // resident block + data-tile stages
 constexpr int AS_MAX_STAGES = 8;
 
 struct AsSmem {
@@ -591,6 +591,7 @@ struct AsArgs {
   int32_t kblocks;            // dim16 / 64, <= AS_MAX_KB
   int32_t k16_last;           // K16 steps of the last K block that hold operand columns; 0 = all 4
   int32_t max_stages;         // measurement: cap on the data-tile stages (0 = as many as fit)
+  int32_t narrow_ok;          // the two 16-column tensor maps are valid (see `narrow` in the kernel)
   int32_t groups;             // CTAs per centroid block (1 when there are more blocks than CTAs)
   const float* alpha;         // value = alpha * accumulator = |c|^2 - 2 x.c
   const float* thr;           // [n] SCAN_THRESHOLD: a centroid is listed for a row iff value <= thr[row]
@@ -616,18 +617,26 @@ __device__ __forceinline__ float as_bar(float thr, float inv_alpha) {
 
 template <int MODE>
 __global__ void __launch_bounds__(AS_THREADS, 1)
-assign_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_c, AsArgs a) {
+assign_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_c,
+                   const __grid_constant__ CUtensorMap map_xn, const __grid_constant__ CUtensorMap map_cn, AsArgs a) {
   extern __shared__ uint8_t smem_raw[];
   AsSmem* sm = reinterpret_cast<AsSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t wait_limit = a.wait_limit ? a.wait_limit : WAIT_LIMIT;
   const int nb = (a.k + TN - 1) / TN;                       // centroid blocks
   const int64_t qtiles = (a.n + TM - 1) / TM;               // data tiles
-  const int bres_bytes = a.kblocks * B_BYTES;
+  // When only the first K16 step of the last K block holds operand columns (d a multiple of 64: the 16 fold columns
+  // start a block of their own), that block is fetched and kept as a 16-column tile (32-byte swizzle: 4 KB of a data
+  // tile, 8 KB of the centroid block) instead of 64 columns of which 48 are zeros: a quarter less to fetch per data
+  // tile at d = 128, and room for four whole-tile stages instead of two.
+  const bool narrow = a.narrow_ok != 0 && a.max_stages == 0 && a.k16_last == 1 && a.kblocks >= 2;
+  const int nfull = narrow ? a.kblocks - 1 : a.kblocks;   // K blocks held as 64-column tiles
+  const int bres_bytes = nfull * B_BYTES + (narrow ? B_NARROW_BYTES : 0);
+  const int tile_bytes = nfull * A_BYTES + (narrow ? A_NARROW_BYTES : 0);
   // A stage of the data ring holds ALL K blocks of a data tile when two such stages fit (one wait, one batch of MMAs
   // and one commit per tile instead of per K block); otherwise, or when max_stages asks for it, one K block.
-  const int skb = (a.max_stages == 0 && 2 * a.kblocks * A_BYTES <= AS_RING_BYTES - bres_bytes) ? a.kblocks : 1;
-  const int stage_bytes = skb * A_BYTES;
+  const int skb = (a.max_stages == 0 && 2 * tile_bytes <= AS_RING_BYTES - bres_bytes) ? a.kblocks : 1;
+  const int stage_bytes = skb == a.kblocks ? tile_bytes : A_BYTES;
   int stages = min(AS_MAX_STAGES, (AS_RING_BYTES - bres_bytes) / stage_bytes);
   if (a.max_stages > 0) stages = max(2, min(stages, a.max_stages));
   // this CTA's centroid blocks and its share of the data tiles
@@ -679,7 +688,8 @@ assign_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
         // the resident block may be replaced once every MMA that read the previous one has retired
         if (!mbar_wait(&sm->b_empty, bph ^ 1, &sm->abort_flag, a.err, 5, wait_limit)) { ok = false; break; }
         mbar_expect_tx(&sm->b_full, (uint32_t)bres_bytes);
-        for (int kb = 0; kb < a.kblocks; ++kb) tma_load_2d(sm->ring + kb * B_BYTES, &map_c, &sm->b_full, kb * TK, b * TN);
+        for (int kb = 0; kb < nfull; ++kb) tma_load_2d(sm->ring + kb * B_BYTES, &map_c, &sm->b_full, kb * TK, b * TN);
+        if (narrow) tma_load_2d(sm->ring + nfull * B_BYTES, &map_cn, &sm->b_full, nfull * TK, b * TN);
         b_issued = true;
         b_issued_ph = bph;
         bph ^= 1;
@@ -687,8 +697,10 @@ assign_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
           for (int kb = 0; kb < a.kblocks; kb += skb) {
             if (!mbar_wait(&sm->a_empty[s], ph ^ 1, &sm->abort_flag, a.err, 1, wait_limit)) { ok = false; break; }
             mbar_expect_tx(&sm->a_full[s], (uint32_t)stage_bytes);
-            for (int j = 0; j < skb; ++j)
+            const int nj = skb == a.kblocks ? nfull : 1;
+            for (int j = 0; j < nj; ++j)
               tma_load_2d(a_ring + s * stage_bytes + j * A_BYTES, &map_x, &sm->a_full[s], (kb + j) * TK, (int32_t)(t * TM));
+            if (narrow) tma_load_2d(a_ring + s * stage_bytes + nfull * A_BYTES, &map_xn, &sm->a_full[s], nfull * TK, (int32_t)(t * TM));
             issued |= 1u << s;
             issued_ph = (issued_ph & ~(1u << s)) | (ph << s);
             if (++s == stages) { s = 0; ph ^= 1; }
@@ -710,45 +722,84 @@ assign_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
-    if (lane == 0) {
+    // The whole warp runs the loop converged and one elected lane issues: descriptors and barrier addresses stay
+    // warp-uniform, so an MMA costs the issuing warp a few instructions (inside a single-lane region each operand of
+    // each MMA was moved to a uniform register first, and the issue of one MMA took longer than its execution).
+    {
       int s = 0;
       uint32_t ph = 0, bph = 0;
       int64_t local = 0;
       bool ok = true;
+      bool pre_acc = false, pre_stage = false;
       for (int b = b_first; ok && b < nb; b += b_step) {
-        if (!mbar_wait(&sm->b_full, bph, &sm->abort_flag, a.err, 6, wait_limit)) { ok = false; break; }
+        if (!__all_sync(0xffffffffu, mbar_wait(&sm->b_full, bph, &sm->abort_flag, a.err, 6, wait_limit))) { ok = false; break; }
         bph ^= 1;
         tc_fence_after();
         for (int64_t t = t_first; ok && t < qtiles; t += t_step, ++local) {
           const int acc = (int)(local & 1);
           const uint32_t aph = (uint32_t)((local >> 1) & 1);
-          if (!mbar_wait(&sm->tmem_empty[acc], aph ^ 1, &sm->abort_flag, a.err, 2, wait_limit)) { ok = false; break; }
-          tc_fence_after();
+          if (!pre_acc && !__all_sync(0xffffffffu, mbar_wait(&sm->tmem_empty[acc], aph ^ 1, &sm->abort_flag, a.err, 2, wait_limit))) { ok = false; break; }
+          pre_acc = false;
           const uint32_t tmem_d = tmem_base + (uint32_t)(acc * TN);
           for (int kb0 = 0; kb0 < a.kblocks; kb0 += skb) {
-            if (!mbar_wait(&sm->a_full[s], ph, &sm->abort_flag, a.err, 3, wait_limit)) { ok = false; break; }
+            if (!pre_stage && !__all_sync(0xffffffffu, mbar_wait(&sm->a_full[s], ph, &sm->abort_flag, a.err, 3, wait_limit))) { ok = false; break; }
+            pre_stage = false;
             tc_fence_after();
-            for (int j = 0; j < skb; ++j) {
+            // The barriers of the NEXT step are looked at (one test, never a wait) before the last MMAs of this step are
+            // issued, while the tensor pipe still has work queued: what is seen complete there is not waited for again,
+            // so the next step's MMAs follow without the pipe running dry over two barrier waits.
+            const bool tile_ends = kb0 + skb >= a.kblocks;
+            const int ns = s + 1 == stages ? 0 : s + 1;
+            const uint32_t nph = s + 1 == stages ? ph ^ 1 : ph;
+            const bool more = !tile_ends || t + t_step < qtiles;   // the next step belongs to this centroid block
+            const int nj = skb == a.kblocks ? nfull : 1;
+            for (int j = 0; j < nj; ++j) {
               const int kb = kb0 + j;
               const uint64_t adesc = make_desc(smem_u32(a_ring + s * stage_bytes + j * A_BYTES));
               const uint64_t bdesc = make_desc(smem_u32(sm->ring + kb * B_BYTES));
               const int nk4 = (kb == a.kblocks - 1 && a.k16_last > 0) ? a.k16_last : TK / 16;
+              if (j == nj - 1 && more) {
+                pre_stage = __all_sync(0xffffffffu, mbar_test_wait(&sm->a_full[ns], nph));
+                if (tile_ends)
+                  pre_acc = __all_sync(0xffffffffu, mbar_test_wait(&sm->tmem_empty[acc ^ 1], (uint32_t)(((local + 1) >> 1) & 1) ^ 1u));
+              }
+              if (elect_one()) {
 #pragma unroll
-              for (int k4 = 0; k4 < TK / 16; ++k4)
-                if (k4 < nk4) tc_mma(tmem_d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), kIdesc, (kb | k4) ? 1u : 0u);
+                for (int k4 = 0; k4 < TK / 16; ++k4)
+                  if (k4 < nk4) tc_mma(tmem_d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), kIdesc, (kb | k4) ? 1u : 0u);
+              }
+              __syncwarp();
             }
-            tc_commit(&sm->a_empty[s]);
-            if (++s == stages) { s = 0; ph ^= 1; }
+            if (narrow) {
+              const uint64_t adesc = make_desc_narrow(smem_u32(a_ring + s * stage_bytes + nfull * A_BYTES));
+              const uint64_t bdesc = make_desc_narrow(smem_u32(sm->ring + nfull * B_BYTES));
+              // a second look for what the first one came too early for (the other accumulator is handed back about
+              // four MMAs after this tile's first)
+              if (more && !pre_stage) pre_stage = __all_sync(0xffffffffu, mbar_test_wait(&sm->a_full[ns], nph));
+              if (more && tile_ends && !pre_acc)
+                pre_acc = __all_sync(0xffffffffu, mbar_test_wait(&sm->tmem_empty[acc ^ 1], (uint32_t)(((local + 1) >> 1) & 1) ^ 1u));
+              if (elect_one()) tc_mma(tmem_d, adesc, bdesc, kIdesc, 1u);
+              __syncwarp();
+            }
+            if (elect_one()) tc_commit(&sm->a_empty[s]);
+            __syncwarp();
+            s = ns;
+            ph = nph;
           }
-          if (ok) tc_commit(&sm->tmem_full[acc]);
+          if (ok && elect_one()) tc_commit(&sm->tmem_full[acc]);
+          __syncwarp();
         }
-        if (ok) tc_commit(&sm->b_empty);   // arrives when every MMA issued so far (all readers of this block) has retired
+        if (ok && elect_one()) tc_commit(&sm->b_empty);   // arrives when every MMA issued so far (all readers of this block) has retired
+        __syncwarp();
       }
-      tc_commit(&sm->drain);
-      for (uint32_t it = 0; it < wait_limit; ++it) {
-        if (mbar_try_wait(&sm->drain, 0)) break;
-        __nanosleep(64);
+      if (lane == 0) {
+        tc_commit(&sm->drain);
+        for (uint32_t it = 0; it < wait_limit; ++it) {
+          if (mbar_try_wait(&sm->drain, 0)) break;
+          __nanosleep(64);
+        }
       }
+      __syncwarp();
     }
   } else {
     // ---------------- epilogue: one data row per thread, a quarter of the block's columns per warp ----------------
@@ -1347,6 +1398,21 @@ int32_t make_map(Ctx* ctx, const __half* base, int64_t rows, int32_t dim16, int 
   return VSK_OK;
 }
 
+// The same matrix seen through a box of 16 columns x box_rows with the 32-byte swizzle: one K16 step of a tile.
+int32_t make_map_narrow(Ctx* ctx, const __half* base, int64_t rows, int32_t dim16, int box_rows, CUtensorMap* map) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(ctx, VSK_ERR_EXECUTION_FAILED, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t gdim[2] = {(cuuint64_t)dim16, (cuuint64_t)rows};
+  cuuint64_t gstride[1] = {(cuuint64_t)dim16 * 2};
+  cuuint32_t box[2] = {16u, (cuuint32_t)box_rows};
+  cuuint32_t estride[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(base), gdim, gstride, box, estride,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(ctx, VSK_ERR_EXECUTION_FAILED, "cuTensorMapEncodeTiled (16-column box) failed with %d", (int)r);
+  return VSK_OK;
+}
+
 template <int METRIC>
 void launch_prep(Ctx* ctx, const float* x, int64_t n, int dim, int dim16, const float* scale, __half* out, float* aux,
                  float* nrm16, float* err16, float* nrm, PrepStats* stats, FoldArgs fold = FoldArgs{0, 0, 0}) {
@@ -1780,8 +1846,8 @@ __global__ void assign_fill_fold_kernel(__half* __restrict__ rows16, int64_t n, 
 }
 
 template <int MODE>
-int32_t launch_assign_scan(Ctx* ctx, const CUtensorMap& mx, const CUtensorMap& mc, AsArgs a, unsigned* grid_out = nullptr,
-                           int64_t* log_cap_out = nullptr) {
+int32_t launch_assign_scan(Ctx* ctx, const CUtensorMap& mx, const CUtensorMap& mc, const CUtensorMap& mxn, const CUtensorMap& mcn,
+                           AsArgs a, unsigned* grid_out = nullptr, int64_t* log_cap_out = nullptr) {
   static bool attr_done = false;
   if (!attr_done) {
     VSK_CUDA(ctx, cudaFuncSetAttribute(assign_scan_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAsSmemBytes));
@@ -1803,7 +1869,7 @@ int32_t launch_assign_scan(Ctx* ctx, const CUtensorMap& mx, const CUtensorMap& m
   if (grid_out) *grid_out = grid;
   if (log_cap_out) *log_cap_out = a.log_cap;
   prof_begin(ctx);
-  assign_scan_kernel<MODE><<<grid, AS_THREADS, kAsSmemBytes, ctx->stream>>>(mx, mc, a);
+  assign_scan_kernel<MODE><<<grid, AS_THREADS, kAsSmemBytes, ctx->stream>>>(mx, mc, mxn, mcn, a);
   prof_end(ctx);
   tl_mark(ctx, MODE == SCAN_ARGMIN ? "assign_argmin" : "assign_scan");
   ctx->stats.kernel_launches++;
@@ -2619,6 +2685,7 @@ int32_t tensor_assign_prepare(Ctx* ctx, const float* rows, int64_t n, int32_t di
   ctx->stats.kernel_launches += 2;
   VSK_CUDA(ctx, cudaGetLastError());
   VSK_TRY(make_map(ctx, ta->rows16, n, ta->dim16, TM, (CUtensorMap*)ta->map_rows));
+  VSK_TRY(make_map_narrow(ctx, ta->rows16, n, ta->dim16, TM, (CUtensorMap*)ta->map_rows_narrow));
   return VSK_OK;
 }
 
@@ -2671,6 +2738,9 @@ int32_t tensor_assign(Ctx* ctx, TensorAssign* ta, const float* rows, const float
   CUtensorMap mc;
   VSK_TRY(make_map(ctx, c16, k, dim16, TN, &mc));
   const CUtensorMap& mr = *(const CUtensorMap*)ta->map_rows;
+  CUtensorMap mcn;
+  VSK_TRY(make_map_narrow(ctx, c16, k, dim16, TN, &mcn));
+  const CUtensorMap& mrn = *(const CUtensorMap*)ta->map_rows_narrow;
   if (ta->stationary) {
     AsArgs sa{};
     sa.n = n;
@@ -2678,6 +2748,7 @@ int32_t tensor_assign(Ctx* ctx, TensorAssign* ta, const float* rows, const float
     sa.kblocks = dim16 / TK;
     sa.k16_last = k16_last_of(fold_col0(dim) + kFoldCols, dim16);
     sa.max_stages = ctx->tuning.assign_stages;
+    sa.narrow_ok = 1;
     sa.alpha = fsm + 4;
     sa.thr = ta->thr;
     // the hit log lives in the rows' key lists (n x kAssignCap words of 8 bytes), its per-CTA counts in `count`
@@ -2714,12 +2785,12 @@ int32_t tensor_assign(Ctx* ctx, TensorAssign* ta, const float* rows, const float
                               ta->shift, st + 2 * n, 0.02f);
       } else {
         VSK_CUDA(ctx, cudaMemsetAsync(ta->best, 0xff, (size_t)n * sizeof(unsigned long long), ctx->stream));
-        VSK_TRY(launch_assign_scan<SCAN_ARGMIN>(ctx, mr, mc, sa));
+        VSK_TRY(launch_assign_scan<SCAN_ARGMIN>(ctx, mr, mc, mrn, mcn, sa));
         assign_threshold_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, ctx->stream>>>(ta->best, eps, n, ta->thr, ta->count);
       }
       VSK_CUDA(ctx, cudaMemsetAsync(ta->best, 0xff, (size_t)n * sizeof(unsigned long long), ctx->stream));
       tl_mark(ctx, "assign_thresholds");
-      VSK_TRY(launch_assign_scan<SCAN_THRESHOLD>(ctx, mr, mc, sa, &sgrid, &log_cap));
+      VSK_TRY(launch_assign_scan<SCAN_THRESHOLD>(ctx, mr, mc, mrn, mcn, sa, &sgrid, &log_cap));
       if (dim % 4 == 0 && ((uintptr_t)rows & 15) == 0 && ((uintptr_t)centroids & 15) == 0)
         assign_log_exact_kernel<true><<<dim3(64, sgrid), 256, 0, ctx->stream>>>(rows, dim, centroids, sa.log, sa.log_count, log_cap, ta->best);
       else

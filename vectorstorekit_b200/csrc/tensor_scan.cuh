@@ -65,6 +65,7 @@ struct TensorAssign {
   bool have_prev = false;
   bool bound_allowed = true;          // thresholds from the triangle inequality where a centroid has hardly moved
   alignas(64) unsigned char map_rows[128] = {};  // TMA tensor map of rows16
+  alignas(64) unsigned char map_rows_narrow[128] = {};  // the same through a 16-column box (the fold columns' K16 step)
 };
 int32_t tensor_assign_prepare(Ctx* ctx, const float* rows, int64_t n, int32_t dim, TensorAssign* ta);
 // assign_holds_previous: `assign` holds, for every row, a valid centroid index (the previous iteration's
