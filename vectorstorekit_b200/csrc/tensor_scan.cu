@@ -225,45 +225,70 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
-    if (lane == 0) {
+    // The whole warp runs the loop converged and one elected lane issues, so descriptors and barrier addresses stay
+    // warp-uniform.  The barriers of the NEXT step (the next ring stage; after a tile's last stage also the other
+    // accumulator) are looked at - one test, never a wait - before the last K block of the current step is issued,
+    // while the tensor pipe has MMAs queued: what is seen complete there is not waited for again.
+    {
       int s = 0;
       uint32_t ph = 0;
       int64_t local = 0;
       bool ok = true;
+      bool pre_acc = false, pre_stage = false;
       for (;; ++local) {
         int64_t qt_unused, nt_unused;
         if (!ok || !tile_at(local, qt_unused, nt_unused)) break;
+        const bool tile_follows = tile_at(local + 1, qt_unused, nt_unused);
         const int acc = (int)(local & 1);
         const uint32_t aph = (uint32_t)((local >> 1) & 1);
-        if (!mbar_wait(&sm->tmem_empty[acc], aph ^ 1, &sm->abort_flag, a.err, 2, wait_limit)) { ok = false; break; }
-        tc_fence_after();
+        if (!pre_acc && !__all_sync(0xffffffffu, mbar_wait(&sm->tmem_empty[acc], aph ^ 1, &sm->abort_flag, a.err, 2, wait_limit))) { ok = false; break; }
+        pre_acc = false;
         const uint32_t tmem_d = tmem_base + (uint32_t)(acc * TN);
         for (int kb0 = 0; kb0 < a.kblocks; kb0 += kps) {
-          if (!mbar_wait(&sm->full[s], ph, &sm->abort_flag, a.err, 3, wait_limit)) { ok = false; break; }
+          if (!pre_stage && !__all_sync(0xffffffffu, mbar_wait(&sm->full[s], ph, &sm->abort_flag, a.err, 3, wait_limit))) { ok = false; break; }
+          pre_stage = false;
           tc_fence_after();
           const int nkb = min(kps, a.kblocks - kb0);
+          const bool tile_ends = kb0 + kps >= a.kblocks;
+          const int ns = s + 1 == nstages ? 0 : s + 1;
+          const uint32_t nph = s + 1 == nstages ? ph ^ 1 : ph;
+          const bool more = !tile_ends || tile_follows;
           for (int j = 0; j < nkb; ++j) {
             const int kb = kb0 + j;
             const uint64_t adesc = make_desc(smem_u32(sm->ring + (s * kps + j) * STAGE_BYTES));
             const uint64_t bdesc = make_desc(smem_u32(sm->ring + (s * kps + j) * STAGE_BYTES + A_BYTES));
             const int nk4 = (kb == a.kblocks - 1 && a.k16_last > 0) ? a.k16_last : TK / 16;
-#pragma unroll
-            for (int k4 = 0; k4 < TK / 16; ++k4) {
-              // 16 fp16 = 32 bytes further along K inside the swizzle atom: +2 in 16-byte units
-              if (k4 < nk4) tc_mma(tmem_d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), kIdesc, (kb | k4) ? 1u : 0u);
+            if (j == nkb - 1 && more) {
+              pre_stage = __all_sync(0xffffffffu, mbar_test_wait(&sm->full[ns], nph));
+              if (tile_ends)
+                pre_acc = __all_sync(0xffffffffu, mbar_test_wait(&sm->tmem_empty[acc ^ 1], (uint32_t)(((local + 1) >> 1) & 1) ^ 1u));
             }
+            if (elect_one()) {
+#pragma unroll
+              for (int k4 = 0; k4 < TK / 16; ++k4) {
+                // 16 fp16 = 32 bytes further along K inside the swizzle atom: +2 in 16-byte units
+                if (k4 < nk4) tc_mma(tmem_d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), kIdesc, (kb | k4) ? 1u : 0u);
+              }
+            }
+            __syncwarp();
           }
-          tc_commit(&sm->empty[s]);   // the stage is free once these MMAs have read it
-          if (++s == nstages) { s = 0; ph ^= 1; }
+          if (elect_one()) tc_commit(&sm->empty[s]);   // the stage is free once these MMAs have read it
+          __syncwarp();
+          s = ns;
+          ph = nph;
         }
-        if (ok) tc_commit(&sm->tmem_full[acc]);
+        if (ok && elect_one()) tc_commit(&sm->tmem_full[acc]);
+        __syncwarp();
       }
       // all issued MMAs must retire before tensor memory is freed
-      tc_commit(&sm->drain);
-      for (uint32_t it = 0; it < wait_limit; ++it) {
-        if (mbar_try_wait(&sm->drain, 0)) break;
-        __nanosleep(64);
+      if (lane == 0) {
+        tc_commit(&sm->drain);
+        for (uint32_t it = 0; it < wait_limit; ++it) {
+          if (mbar_try_wait(&sm->drain, 0)) break;
+          __nanosleep(64);
+        }
       }
+      __syncwarp();
     }
   } else {
     // ---------------- epilogue: one query per thread, half of the tile's columns per warp ----------------
