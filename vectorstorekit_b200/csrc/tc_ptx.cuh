@@ -196,6 +196,28 @@ __device__ __forceinline__ uint64_t make_desc_narrow(uint32_t smem_addr) {
   return d;
 }
 
+// The descriptors above split into the word that changes with the address and the constant word, and barrier
+// operations that take a shared-memory address as a 32-bit number: an issuer loop that keeps its state in 32-bit
+// registers spends fewer instructions between the last MMA of one tile and the first of the next.
+__device__ __forceinline__ uint32_t desc_lo(uint32_t smem_addr) { return ((smem_addr >> 4) & 0x3fffu) | (1u << 16); }
+constexpr uint32_t kDescHi = (uint32_t)(1024 >> 4) | (1u << 14) | (2u << 29);
+constexpr uint32_t kDescHiNarrow = (uint32_t)(256 >> 4) | (1u << 14) | (6u << 29);
+__device__ __forceinline__ uint64_t desc_pack(uint32_t lo, uint32_t hi) { return ((uint64_t)hi << 32) | lo; }
+__device__ __forceinline__ bool mbar_test_wait_a(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ void tc_commit_a(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
 // Instruction descriptor: fp32 accumulate, fp16 A and B, both K-major, N = 256, M = 128.
 constexpr uint32_t kIdesc = (1u << 4) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(TM >> 4) << 24);
 

@@ -747,10 +747,82 @@ assign_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
-    // The whole warp runs the loop converged and one elected lane issues: descriptors and barrier addresses stay
-    // warp-uniform, so an MMA costs the issuing warp a few instructions (inside a single-lane region each operand of
-    // each MMA was moved to a uniform register first, and the issue of one MMA took longer than its execution).
-    {
+    // Measured with clock stamps in this warp: an M128 N256 K16 MMA executes in 128 cycles and the pipe queues only a
+    // few, so the nine MMAs of a d = 128 tile are issued over about 1 250 cycles, and every cycle this warp then spends
+    // before the next tile's first MMA (commits, loop, two barrier waits of 200 - 250 cycles each even when the barrier
+    // has long completed) is a cycle the pipe idles: 2 130 cycles per tile at first, 1 152 of them MMA execution.
+    if (skb == a.kblocks) {
+      // A whole data tile per ring stage (the usual case): one lane, all loop state in 32-bit registers.  What this
+      // thread executes between the last MMA of a tile and the first of the next is time the tensor pipe idles once
+      // its short queue has drained, so the barriers of the next tile are looked at (one test, never a wait) while
+      // this tile's last MMAs are still to be issued, and nothing is recomputed that can be carried along.
+      if (lane == 0) {
+        const uint32_t a_lo0 = desc_lo(smem_u32(a_ring)), stage_lo = (uint32_t)stage_bytes >> 4;
+        uint32_t b_lo[AS_MAX_KB];
+#pragma unroll
+        for (int kb = 0; kb < AS_MAX_KB; ++kb) b_lo[kb] = desc_lo(smem_u32(sm->ring + kb * B_BYTES));
+        const uint32_t bn_lo = desc_lo(smem_u32(sm->ring + nfull * B_BYTES));
+        const uint32_t full0 = smem_u32(&sm->a_full[0]), empty0 = smem_u32(&sm->a_empty[0]);
+        const uint32_t tfull0 = smem_u32(&sm->tmem_full[0]), tempty0 = smem_u32(&sm->tmem_empty[0]);
+        const int last_nk4 = (!narrow && a.k16_last > 0) ? a.k16_last : TK / 16;   // MMAs of the last 64-column block
+        const int32_t tiles_cta = t_first < qtiles ? (int32_t)((qtiles - t_first + t_step - 1) / t_step) : 0;
+        uint32_t s = 0, ph = 0, bph = 0, acc = 0, aph = 0;
+        bool ok = true, pre_acc = false, pre_stage = false;
+        for (int b = b_first; ok && b < nb; b += b_step) {
+          if (!mbar_wait(&sm->b_full, bph, &sm->abort_flag, a.err, 6, wait_limit)) { ok = false; break; }
+          bph ^= 1;
+          for (int32_t left = tiles_cta; left > 0; --left) {
+            if (!pre_acc && !mbar_wait(&sm->tmem_empty[acc], aph ^ 1, &sm->abort_flag, a.err, 2, wait_limit)) { ok = false; break; }
+            if (!pre_stage && !mbar_wait(&sm->a_full[s], ph, &sm->abort_flag, a.err, 3, wait_limit)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t tmem_d = tmem_base + acc * (uint32_t)TN;
+            const uint32_t a_lo = a_lo0 + s * stage_lo;
+            const uint32_t ns = s + 1 == (uint32_t)stages ? 0u : s + 1;
+            const uint32_t nph = s + 1 == (uint32_t)stages ? ph ^ 1u : ph;
+            const uint32_t naph = acc ? aph ^ 1u : aph;   // the other accumulator's use count flips parity every second tile
+            const bool more = left > 1;                   // the next tile belongs to this centroid block
+            pre_acc = false;
+            pre_stage = false;
+#pragma unroll
+            for (int kb = 0; kb < AS_MAX_KB; ++kb) {
+              if (kb < nfull) {
+                if (kb == nfull - 1 && more) {
+                  pre_stage = mbar_test_wait_a(full0 + ns * 8u, nph);
+                  pre_acc = mbar_test_wait_a(tempty0 + (acc ^ 1u) * 8u, naph ^ 1u);
+                }
+                const int nk4 = kb == nfull - 1 ? last_nk4 : TK / 16;
+#pragma unroll
+                for (int k4 = 0; k4 < TK / 16; ++k4)
+                  if (k4 < nk4)
+                    tc_mma(tmem_d, desc_pack(a_lo + (uint32_t)(kb * (A_BYTES >> 4) + k4 * 2), kDescHi),
+                           desc_pack(b_lo[kb] + (uint32_t)(k4 * 2), kDescHi), kIdesc, (kb | k4) ? 1u : 0u);
+              }
+            }
+            if (narrow) {
+              // a second look for what the first one came too early for
+              if (more && !pre_stage) pre_stage = mbar_test_wait_a(full0 + ns * 8u, nph);
+              if (more && !pre_acc) pre_acc = mbar_test_wait_a(tempty0 + (acc ^ 1u) * 8u, naph ^ 1u);
+              tc_mma(tmem_d, desc_pack(a_lo + (uint32_t)(nfull * (A_BYTES >> 4)), kDescHiNarrow), desc_pack(bn_lo, kDescHiNarrow), kIdesc, 1u);
+            }
+            tc_commit_a(empty0 + s * 8u);
+            tc_commit_a(tfull0 + acc * 8u);
+            s = ns;
+            ph = nph;
+            aph = naph;
+            acc ^= 1u;
+          }
+          if (ok) tc_commit(&sm->b_empty);   // arrives when every MMA issued so far (all readers of this block) has retired
+        }
+        tc_commit(&sm->drain);
+        for (uint32_t it = 0; it < wait_limit; ++it) {
+          if (mbar_try_wait(&sm->drain, 0)) break;
+          __nanosleep(64);
+        }
+      }
+      __syncwarp();
+    } else {
+      // One K block per ring stage (long rows, or a stage cap set for measurement): the whole warp runs the loop
+      // converged and one elected lane issues; the same look-ahead, per stage.
       int s = 0;
       uint32_t ph = 0, bph = 0;
       int64_t local = 0;
