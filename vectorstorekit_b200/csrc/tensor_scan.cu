@@ -225,70 +225,53 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
-    // The whole warp runs the loop converged and one elected lane issues, so descriptors and barrier addresses stay
-    // warp-uniform.  The barriers of the NEXT step (the next ring stage; after a tile's last stage also the other
-    // accumulator) are looked at - one test, never a wait - before the last K block of the current step is issued,
-    // while the tensor pipe has MMAs queued: what is seen complete there is not waited for again.
-    {
-      int s = 0;
-      uint32_t ph = 0;
-      int64_t local = 0;
+    // One lane, loop state in 32-bit registers, the number of tiles worked out once (the tile's coordinates, which
+    // cost a 64-bit division per tile, are of no use to this role).  A converged warp with an elected lane and a
+    // look-ahead at the next stage's barriers was measured 2 - 3 % slower here and is not used.
+    if (lane == 0) {
+      int64_t count;
+      if (a.tiles) count = unit < a.num_tiles ? (a.num_tiles - unit + units - 1) / units : 0;
+      else if (a.row_tile_fastest) count = unit < qtiles ? ((qtiles - unit + units - 1) / units) * ntiles : 0;
+      else count = unit < tiles ? (tiles - unit + units - 1) / units : 0;
+      const uint32_t ring_lo = desc_lo(smem_u32(sm->ring));
+      const uint32_t full0 = smem_u32(&sm->full[0]), empty0 = smem_u32(&sm->empty[0]), tfull0 = smem_u32(&sm->tmem_full[0]);
+      const int last_nk4 = a.k16_last > 0 ? a.k16_last : TK / 16;
+      uint32_t s = 0, ph = 0, acc = 0, aph = 0;
       bool ok = true;
-      bool pre_acc = false, pre_stage = false;
-      for (;; ++local) {
-        int64_t qt_unused, nt_unused;
-        if (!ok || !tile_at(local, qt_unused, nt_unused)) break;
-        const bool tile_follows = tile_at(local + 1, qt_unused, nt_unused);
-        const int acc = (int)(local & 1);
-        const uint32_t aph = (uint32_t)((local >> 1) & 1);
-        if (!pre_acc && !__all_sync(0xffffffffu, mbar_wait(&sm->tmem_empty[acc], aph ^ 1, &sm->abort_flag, a.err, 2, wait_limit))) { ok = false; break; }
-        pre_acc = false;
-        const uint32_t tmem_d = tmem_base + (uint32_t)(acc * TN);
+      for (int64_t left = count; ok && left > 0; --left) {
+        if (!mbar_wait(&sm->tmem_empty[acc], aph ^ 1, &sm->abort_flag, a.err, 2, wait_limit)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * (uint32_t)TN;
         for (int kb0 = 0; kb0 < a.kblocks; kb0 += kps) {
-          if (!pre_stage && !__all_sync(0xffffffffu, mbar_wait(&sm->full[s], ph, &sm->abort_flag, a.err, 3, wait_limit))) { ok = false; break; }
-          pre_stage = false;
+          if (!mbar_wait(&sm->full[s], ph, &sm->abort_flag, a.err, 3, wait_limit)) { ok = false; break; }
           tc_fence_after();
           const int nkb = min(kps, a.kblocks - kb0);
-          const bool tile_ends = kb0 + kps >= a.kblocks;
-          const int ns = s + 1 == nstages ? 0 : s + 1;
-          const uint32_t nph = s + 1 == nstages ? ph ^ 1 : ph;
-          const bool more = !tile_ends || tile_follows;
           for (int j = 0; j < nkb; ++j) {
             const int kb = kb0 + j;
-            const uint64_t adesc = make_desc(smem_u32(sm->ring + (s * kps + j) * STAGE_BYTES));
-            const uint64_t bdesc = make_desc(smem_u32(sm->ring + (s * kps + j) * STAGE_BYTES + A_BYTES));
-            const int nk4 = (kb == a.kblocks - 1 && a.k16_last > 0) ? a.k16_last : TK / 16;
-            if (j == nkb - 1 && more) {
-              pre_stage = __all_sync(0xffffffffu, mbar_test_wait(&sm->full[ns], nph));
-              if (tile_ends)
-                pre_acc = __all_sync(0xffffffffu, mbar_test_wait(&sm->tmem_empty[acc ^ 1], (uint32_t)(((local + 1) >> 1) & 1) ^ 1u));
-            }
-            if (elect_one()) {
+            const uint32_t a_lo = ring_lo + (uint32_t)((s * kps + j) * (STAGE_BYTES >> 4));
+            const uint32_t b_lo = a_lo + (uint32_t)(A_BYTES >> 4);
+            const int nk4 = kb == a.kblocks - 1 ? last_nk4 : TK / 16;
 #pragma unroll
-              for (int k4 = 0; k4 < TK / 16; ++k4) {
-                // 16 fp16 = 32 bytes further along K inside the swizzle atom: +2 in 16-byte units
-                if (k4 < nk4) tc_mma(tmem_d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), kIdesc, (kb | k4) ? 1u : 0u);
-              }
+            for (int k4 = 0; k4 < TK / 16; ++k4) {
+              // 16 fp16 = 32 bytes further along K inside the swizzle atom: +2 in 16-byte units
+              if (k4 < nk4)
+                tc_mma(tmem_d, desc_pack(a_lo + (uint32_t)(k4 * 2), kDescHi), desc_pack(b_lo + (uint32_t)(k4 * 2), kDescHi), kIdesc,
+                       (kb | k4) ? 1u : 0u);
             }
-            __syncwarp();
           }
-          if (elect_one()) tc_commit(&sm->empty[s]);   // the stage is free once these MMAs have read it
-          __syncwarp();
-          s = ns;
-          ph = nph;
+          tc_commit_a(empty0 + s * 8u);   // the stage is free once these MMAs have read it
+          if (++s == (uint32_t)nstages) { s = 0; ph ^= 1u; }
         }
-        if (ok && elect_one()) tc_commit(&sm->tmem_full[acc]);
-        __syncwarp();
+        if (ok) tc_commit_a(tfull0 + acc * 8u);
+        aph = acc ? aph ^ 1u : aph;
+        acc ^= 1u;
       }
       // all issued MMAs must retire before tensor memory is freed
-      if (lane == 0) {
-        tc_commit(&sm->drain);
-        for (uint32_t it = 0; it < wait_limit; ++it) {
-          if (mbar_try_wait(&sm->drain, 0)) break;
-          __nanosleep(64);
-        }
+      tc_commit(&sm->drain);
+      for (uint32_t it = 0; it < wait_limit; ++it) {
+        if (mbar_try_wait(&sm->drain, 0)) break;
+        __nanosleep(64);
       }
-      __syncwarp();
     }
   } else {
     // ---------------- epilogue: one query per thread, half of the tile's columns per warp ----------------
