@@ -103,15 +103,18 @@ def test_lloyd_iterations_on_the_tensor_path_equal_the_fp32_path(vsk, dev):
     assert np.max(np.abs(c0 - c1)) < 5e-2
 
 
+@pytest.mark.parametrize("d", [64, 192, 240])
 @pytest.mark.parametrize("data", ["unstructured", "clustered"])
-def test_every_lloyd_step_assigns_each_row_to_a_nearest_centroid(vsk, dev, data):
+def test_every_lloyd_step_assigns_each_row_to_a_nearest_centroid(vsk, dev, data, d):
     """Step by step through the trainer (the caller hands in the centroids of each step): after every step each row's
     centroid must be a nearest one under the direct formula - checked in fp64 - whichever way the step's thresholds
     were formed.  On unstructured data (no gaps between clusters) many centroids sit inside the looser triangle
     bound; the hit log may fill, in which case the step repeats itself with exact thresholds."""
     import torch
+    # d = 64 and 192: the fold columns start a K block of their own and travel as a 16-column tile (one and three
+    # 64-column blocks before it); d = 240: they fill the last block's fourth K16 step, and a ring stage is one K block
     g = torch.Generator(device="cuda").manual_seed(23)
-    n, d, k = 200_000, 64, 1024
+    n, k = 200_000, 1024
     if data == "unstructured":
         x = torch.randn((n, d), generator=g, device="cuda")
     else:
