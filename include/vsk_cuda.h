@@ -141,8 +141,9 @@ typedef struct vsk_tuning {
                                    the counterpart of commandBufferTimeout (Acceleration/Metal/MetalErrors.swift:30) */
   int32_t test_stall_scan;      /* testing only: 1 makes the next contraction launch leave one operand stage
                                    unfilled, so that a bounded wait runs out; resets itself to 0 */
-  int32_t assign_stages;        /* measurement only: caps the data-tile stages of the k-means assignment kernel's operand
-                                   ring (0 = as many as fit) */
+  int32_t assign_stages;        /* measurement only: 0 = the k-means assignment kernel's operand ring holds a whole
+                                   data tile per stage, as many stages as fit (fold columns as a 16-column tile where
+                                   they begin a K block of their own); n > 0 = stages of one K block, at most n */
   int32_t stage_kblocks;        /* K blocks (64 operand columns) per stage of the contraction kernel's operand ring: 1 =
                                    four stages of 48 KB, 2 = two stages of 96 KB (half the hand-overs per tile) */
   int32_t reserved[6];
