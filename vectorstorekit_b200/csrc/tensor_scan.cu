@@ -565,10 +565,13 @@ tc_scan_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 // tile, a third of the traffic (a sixth with the row term folded in), so the MMAs set the pace again.
 //   grid      blocks of 256 centroids x groups of CTAs; CTA (b, g) holds centroid block b and takes data tiles
 //             g, g + groups, ...  (more blocks than SMs: a CTA takes several blocks in turn)
-//   warp 0    TMA producer: the centroid block once, then the data tiles through a ring of 16 KB stages
-//   warp 1    tcgen05.mma issuer: per data tile and k-block one M128 N256 K16 x 4 against the resident block
+//   warp 0    TMA producer: the centroid block once, then the data tiles through a ring whose stage holds a whole
+//             data tile (a K block where a tile is too large for two such stages); fold columns that begin a K block
+//             of their own travel as a 16-column tile
+//   warp 1    tcgen05.mma issuer: per data tile M128 N256 K16 x 4 per k-block against the resident block; it looks at
+//             the next tile's barriers while this tile's last MMAs are still to be issued
 //   warps 2.. epilogue (16 warps): the centroid's |c|^2 / 2 rides inside the contraction (fold columns), so a value
-//             is alpha * accumulator and the test for "no hit in these 32 columns" is one max per value.
+//             is alpha * accumulator and "no hit in these eight columns" is their largest accumulator against a bar.
 //             Threshold mode: a hit (rare: the threshold is the row's previous assignment plus the error band)
 //             is logged as {row, centroid} in the CTA's own stretch of a log, its slot taken from a shared-memory
 //             counter; arg-min mode (first iteration): one atomicMin per row, centroid block and column part.
