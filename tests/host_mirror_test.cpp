@@ -86,6 +86,30 @@ int main() {
   auto s2 = ix.shardedSearch(q, 1, 2, nullptr, true);
   if (first != 0 || s1.ids != r.ids || s1.distances != r.distances || s2.ids != r.ids) return 11;
   dev->leaveCommunicator();
+  // IVF mirror: two centroids, rows filed in two inserts (the second without a rebuild), a filter on the second
+  // batch's rows, and the one-rank sharded form (the reference's flow: IVFIndexTests.swift:60-140, :536-590)
+  {
+    vsk::IVFIndex ivf(dev, 4, 2, 2, 5);
+    const float train[] = {1, 0, 0, 0, 0, 1, 0, 0, 0.9f, 0.1f, 0, 0, 0.1f, 0.9f, 0, 0};
+    try {
+      ivf.batchSearch(q, 1, 1);
+      return 18;                                // search before train must be refused
+    } catch (const vsk::NotTrained&) {
+    }
+    ivf.train(train, 4);
+    const uint64_t m1[] = {1, 1}, m2[] = {2, 2};
+    ivf.insert(train, 2, m1);                   // rows 0, 1
+    ivf.insert(train + 8, 2, m2);               // rows 2, 3 behind them
+    auto a = ivf.batchSearch(q, 1, 4);
+    if (a.ids[0] != 0 || a.ids[1] != 2 || a.ids[2] != 3 || a.ids[3] != 1) return 19;
+    const uint64_t only2[] = {2};
+    auto f = ivf.batchSearch(q, 1, 2, false, only2);
+    if (f.ids[0] != 2 || f.ids[1] != 3) return 20;
+    dev->joinCommunicator(1, 0, {});
+    auto sh = ivf.shardedSearch(q, 1, 4, nullptr, true);
+    dev->leaveCommunicator();
+    if (sh.ids != a.ids || sh.distances != a.distances) return 21;
+  }
   // product quantiser: 2 segments of 2 dimensions, 16 codewords; row 1 sits on codewords (3, 5)
   vsk::ProductQuantizer pq(dev, 4, 2, 4);
   std::vector<float> cb(2 * 16 * 2);
