@@ -293,6 +293,24 @@ class Bench:
         n = self.hi - self.lo
         self.extra = {"train_s": t1 - t0, "train_s_per_iteration": (t1 - t0) / wl["iters"], "build_s": t2 - t1,
                       "train_flops_per_iteration": 2.0 * n * wl["nlist"] * wl["dim"]}
+        if self.world == 1:
+            # The assignment contraction of a Lloyd iteration, timed by the library's own event log (CUDA events on its
+            # stream) over a few more iterations on the same rows, outside every timed region: the launches marked
+            # "assign_scan" are the threshold-mode contractions (the first iteration's arg-min launch has another name).
+            self.dev.timeline(True)
+            km = self.vsk.KMeansClustering(self.dev, maxIterations=6, tolerance=-1.0)
+            km.cluster(self.rows, wl["nlist"], self.rows[:wl["nlist"]].contiguous())
+            t.cuda.synchronize()
+            marks = self.dev.timeline_read()
+            self.dev.timeline(False)
+            scans = [ms - marks[i - 1][2] for i, (_, what, ms) in enumerate(marks) if what == "assign_scan" and i > 0]
+            if len(scans) > 2:
+                scan_ms = float(np.median(scans[1:]))      # the first follows the arg-min launch's looser thresholds
+                tf = self.extra["train_flops_per_iteration"] / (scan_ms * 1e-3) / 1e12
+                pk = peaks()
+                self.extra["train_contraction"] = {"kernel": "assign_scan_kernel", "ms_per_launch": scan_ms, "achieved": tf,
+                                                   "unit": "TFLOP/s", "peak": pk["bf16_tflops"],
+                                                   "frac": tf / pk["bf16_tflops"], "peak_source": pk["source"]}
         asg = ix.assignments()
         sizes = np.bincount(asg, minlength=wl["nlist"])
         self.extra["list_len_mean"] = float(sizes.mean())
