@@ -59,6 +59,19 @@ def test_one_rank_communicator_equals_plain_search(vsk, cpu_oracle):
             dd, di = iv.shardedSearch(torch.as_tensor(q, device="cuda"), 12, gather=gather)
             assert np.array_equal(di.cpu().numpy(), pi) and np.array_equal(dd.cpu().numpy(), pd)
         iv.close()
+        # ... and with row masks and per-query filter masks
+        rng = np.random.default_rng(11)
+        rm = (np.uint64(1) << rng.integers(0, 4, x.shape[0]).astype(np.uint64))
+        qm = (np.uint64(1) << rng.integers(0, 4, q.shape[0]).astype(np.uint64)) | np.uint64(8)
+        iv = vsk.IVFIndex(dev, 96, numberOfCentroids=64, numberOfProbes=8, maxIterations=2, tolerance=-1.0)
+        iv.train(x, x[:64].copy())
+        iv.insert(x, rm)
+        pd, pi = iv.batchSearch(q, 12, filter_masks=qm)
+        sd, si = iv.shardedSearch(q, 12, filter_masks=qm, gather=True)
+        assert np.array_equal(si, pi) and np.array_equal(sd, pd)
+        ok = pi >= 0
+        assert ok.any() and np.all((rm[pi[ok]] & np.broadcast_to(qm[:, None], pi.shape)[ok]) != 0)
+        iv.close()
         dev.comm_destroy()
         assert dev.comm_info() == (1, 0)
     finally:
