@@ -572,6 +572,41 @@ def run_reference(args, wl):
         "gpu_launches": 0}))
 
 
+# The default run (flat cosine, one GPU) also runs the other configurations, each as a child process of a few steps,
+# and carries their figures in the same JSON line, so that one run records every configuration on the same box.
+OTHER_WORKLOADS = (("c1", 50), ("c3", 5), ("c4e", 3), ("c5", 3), ("pq", 3))   # (workload, timed steps)
+OTHERS_BUDGET_S = 150.0
+
+
+def run_other_workloads(args):
+    import subprocess
+    out, t_start = {}, time.perf_counter()
+    env = {k_: v for k_, v in os.environ.items() if k_ not in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_ADDR", "MASTER_PORT")}
+    for w, steps in OTHER_WORKLOADS:
+        left = OTHERS_BUDGET_S - (time.perf_counter() - t_start)
+        if left < 20.0:
+            out[w] = {"skipped": "the time set aside for the other configurations was used up"}
+            continue
+        cmd = [sys.executable, os.path.abspath(__file__), "--workload", w, "--steps", str(steps), "--warmup", "3",
+               "--no-cpu-baseline", "--no-others", "--path", args.path]
+        try:
+            p_ = subprocess.run(cmd, capture_output=True, text=True, timeout=left, cwd=ROOT, env=env)
+            d = json.loads([ln for ln in p_.stdout.splitlines() if ln.startswith("{")][-1])
+            r = d.get("roofline") or {}
+            o = {"workload": d["config"]["workload"], "value": d["value"], "unit": d["unit"], "ms_per_step": d["ms_per_step"],
+                 "steps": d["steps"], "warmup": d["warmup"], "e2e": (d.get("e2e") or {}).get("value"),
+                 "gpu_launches": d.get("gpu_launches"), "fallback_queries": (d.get("stats") or {}).get("fallback_queries"),
+                 "roofline": {k_: r.get(k_) for k_ in ("bound", "achieved", "peak", "unit", "frac", "kernel_ms_per_step", "peak_source")},
+                 "clocks": d.get("clocks")}
+            for k_ in ("train_contraction", "train_s_per_iteration"):
+                if k_ in (d.get("workload_detail") or {}):
+                    o[k_] = d["workload_detail"][k_]
+            out[w] = o
+        except Exception as e:   # a child that fails or runs out of time never costs the main line
+            out[w] = {"failed": repr(e)[:300]}
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -582,6 +617,8 @@ def main():
     ap.add_argument("--path", default="tensor", choices=["tensor", "fp32"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-others", action="store_true",
+                    help="the default run (c2, one GPU) does not also run the other configurations as child processes")
     ap.add_argument("--tuning", action="append", default=[], metavar="FIELD=VALUE",
                     help="a field of the library's vsk_tuning (e.g. overlap_min_queries=0, chunk_growth=4)")
     ap.add_argument("--queries", type=int, default=0,
@@ -782,6 +819,9 @@ def main():
         line["clocks"] = sampler.summary()
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = b.cpu_baseline()
+        if (world == 1 and args.workload == "c2" and not args.no_others and not args.no_cpu_baseline and not args.no_e2e
+                and not args.tuning and args.queries == 0):
+            line["other_workloads"] = run_other_workloads(args)
         print(json.dumps(line), flush=True)
     # release the library's objects in order (the context closes the indices created on it first); left to the
     # interpreter's shutdown, finalisers of the Bench object's reference cycle run in no particular order
