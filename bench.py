@@ -20,6 +20,8 @@ roofline  the scan kernels' device time from CUDA events recorded around each la
           with the library's profiling on (profiling runs a batch on one stream, so that an event pair brackets
           one kernel alone; the first region runs large batches as two halves on two streams)
 cpu_baseline / --impl reference: the CPU restatement of the reference's search on the host cores
+other_workloads  (default run on one GPU only) c1, c3, one rank's shard of c4, c5 and pq, each run as a child process
+          of a few steps: value, ms_per_step, e2e, roofline, clocks (and c3's k-means contraction) of each
 """
 import argparse
 import ctypes as C
