@@ -1037,7 +1037,7 @@ assign_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
 // One warp per logged hit: the exact squared distance of the row to the listed centroid, direct fp32 formula, merged
 // into best[row] - smallest (value, centroid), the reference's strict '<' scan (KMeansClustering.swift:283-288).
 template <bool VEC>
-__global__ void assign_log_exact_kernel(const float* __restrict__ x, int dim, const float* __restrict__ cent,
+__global__ void __launch_bounds__(256, 6) assign_log_exact_kernel(const float* __restrict__ x, int dim, const float* __restrict__ cent,
                                         const uint2* __restrict__ log, const int32_t* __restrict__ log_count, int64_t log_cap,
                                         unsigned long long* __restrict__ best) {
   const int cta = blockIdx.y;
