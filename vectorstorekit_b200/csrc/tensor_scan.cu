@@ -970,48 +970,26 @@ assign_scan_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
           tc_ld32(trow + (uint32_t)(c * 32), v);
           const int left = a.k - (col_base + c * 32);   // valid centroids from this group's first column on
           if (left <= 0) continue;
-          if (MODE == SCAN_ARGMIN) {
-            // alpha < 0: the smallest value of the group is alpha times its largest accumulator - one max per value;
-            // the column is looked for only when the group beats the best so far (ever more rarely as groups go by)
-            float amax = -CUDART_INF_F;
-            if (left >= 32) {
+          // alpha < 0: the smallest value of the group is alpha times its largest accumulator - one max per value;
+          // the column is looked for only when the group beats the best so far (ever more rarely as groups go by)
+          float amax = -CUDART_INF_F;
+          if (left >= 32) {
 #pragma unroll
-              for (int j = 0; j < 32; ++j) amax = fmaxf(amax, v[j]);
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) amax = j < left ? fmaxf(amax, v[j]) : amax;
-            }
-            const float gmin = amax * alpha;
-            if (gmin < bv) {   // strict '<': an earlier (lower) centroid keeps a tie
-              bv = gmin;
-              int jj = 31;
-#pragma unroll
-              for (int j = 31; j >= 0; --j) jj = (j < left && v[j] == amax) ? j : jj;   // the lowest column holding the max
-              bj = c * 32 + jj;
-            }
+            for (int j = 0; j < 32; ++j) amax = fmaxf(amax, v[j]);
           } else {
-            // value = alpha * accumulator with alpha < 0: the smallest value is alpha times the largest accumulator
-            float amax = v[0];
 #pragma unroll
-            for (int j = 1; j < 32; ++j) amax = fmaxf(amax, v[j]);
-            const bool mine = qok && amax * alpha <= thr;   // this row has a hit among the 32 columns
-            if (left >= 32 && !__any_sync(0xffffffffu, mine)) continue;
-            if (mine || left < 32) {
-              const uint32_t colmask = left >= 32 ? 0xffffffffu : ((1u << left) - 1u);
-              uint32_t bits = 0;
+            for (int j = 0; j < 32; ++j) amax = j < left ? fmaxf(amax, v[j]) : amax;
+          }
+          const float gmin = amax * alpha;
+          if (gmin < bv) {   // strict '<': an earlier (lower) centroid keeps a tie
+            bv = gmin;
+            int jj = 31;
 #pragma unroll
-              for (int j = 0; j < 32; ++j) bits |= (v[j] * alpha <= thr) ? (1u << j) : 0u;
-              bits = qok ? (bits & colmask) : 0u;
-              while (bits) {   // one or two hits as a rule
-                const int j = __ffs((int)bits) - 1;
-                bits &= bits - 1u;
-                const int slot = atomicAdd(&sm->log_n, 1);
-                if (slot < a.log_cap) my_log[slot] = make_uint2((uint32_t)q, (uint32_t)(col_base + c * 32 + j));
-              }
-            }
+            for (int j = 31; j >= 0; --j) jj = (j < left && v[j] == amax) ? j : jj;   // the lowest column holding the max
+            bj = c * 32 + jj;
           }
         }
-        if (MODE == SCAN_ARGMIN && qok && bv < CUDART_INF_F)
+        if (qok && bv < CUDART_INF_F)
           atomicMin(a.best + q, (unsigned long long)make_key(bv, (uint32_t)(col_base + bj)));
         tc_fence_before();
         __syncwarp();
