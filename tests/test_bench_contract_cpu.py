@@ -33,3 +33,17 @@ def test_reference_arm_prints_one_contract_line():
 
 def test_reference_arm_other_ranks_exit_without_work():
     assert _run({"RANK": "1", "WORLD_SIZE": "2", "LOCAL_RANK": "1"}) == []
+
+
+def test_the_default_run_s_other_configurations_exist_and_cannot_recurse():
+    """The default one-GPU run records further configurations as child processes: each must be a workload of the
+    bench, none the default one, and a child must be told not to start children of its own."""
+    sys.path.insert(0, ROOT)
+    import importlib
+    bench = importlib.import_module("bench")
+    names = [w for w, _ in bench.OTHER_WORKLOADS]
+    assert names and all(w in bench.WORKLOADS for w in names) and "c2" not in names
+    assert all(steps >= 3 for _, steps in bench.OTHER_WORKLOADS)
+    src = open(os.path.join(ROOT, "bench.py")).read()
+    body = src[src.index("def run_other_workloads"):src.index("def main()")]
+    assert '"--no-others"' in body and "timeout=" in body and "except Exception" in body
