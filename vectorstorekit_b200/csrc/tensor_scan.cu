@@ -581,6 +581,10 @@ constexpr int AS_THREADS = 64 + 32 * AS_EW;
 constexpr int AS_MAX_KB = 4;                       // k-blocks of the resident block (d + 16 fold columns <= 256)
 constexpr int AS_RING_BYTES = 216 * 1024;          // resident block + data-tile stages
 constexpr int AS_MAX_STAGES = 8;
+// The 16-column fold tile is only loaded and issued in whole-tile stages: two such stages must fit beside the largest
+// resident block that has one (the condition is tightest at the largest number of K blocks).
+static_assert(2 * ((AS_MAX_KB - 1) * A_BYTES + A_NARROW_BYTES) <= AS_RING_BYTES - ((AS_MAX_KB - 1) * B_BYTES + B_NARROW_BYTES),
+              "a 16-column fold tile implies whole-tile stages");
 
 struct AsSmem {
   uint8_t ring[AS_RING_BYTES];   // [kblocks x 32 KB centroid block][stages x 16 KB data k-blocks]
