@@ -20,7 +20,7 @@ roofline  the scan kernels' device time from CUDA events recorded around each la
           with the library's profiling on (profiling runs a batch on one stream, so that an event pair brackets
           one kernel alone; the first region runs large batches as two halves on two streams)
 cpu_baseline / --impl reference: the CPU restatement of the reference's search on the host cores
-other_workloads  (default run on one GPU only) c1, c3, one rank's shard of c4, c5 and pq, each run as a child process
+other_workloads  (default run on one GPU only) c1, c2 with filters (c2f), c3, one rank's shard of c4, c5 and pq, each run as a child process
           of a few steps: value, ms_per_step, e2e, roofline, clocks (and c3's k-means contraction) of each
 """
 import argparse
@@ -576,7 +576,7 @@ def run_reference(args, wl):
 
 # The default run (flat cosine, one GPU) also runs the other configurations, each as a child process of a few steps,
 # and carries their figures in the same JSON line, so that one run records every configuration on the same box.
-OTHER_WORKLOADS = (("c1", 50), ("c3", 5), ("c4e", 3), ("c5", 3), ("pq", 3))   # (workload, timed steps)
+OTHER_WORKLOADS = (("c1", 50), ("c2f", 5), ("c3", 5), ("c4e", 3), ("c5", 3), ("pq", 3))   # (workload, timed steps)
 OTHERS_BUDGET_S = 150.0
 
 
