@@ -199,6 +199,8 @@ __device__ __forceinline__ uint64_t make_desc_narrow(uint32_t smem_addr) {
 // The descriptors above split into the word that changes with the address and the constant word, and barrier
 // operations that take a shared-memory address as a 32-bit number: an issuer loop that keeps its state in 32-bit
 // registers spends fewer instructions between the last MMA of one tile and the first of the next.
+// (A CTA's shared memory ends below 256 KB, so an address in 16-byte units stays below 2^14: offsets inside the CTA's
+// buffers may be added to the low word without a carry into the field above it.)
 __device__ __forceinline__ uint32_t desc_lo(uint32_t smem_addr) { return ((smem_addr >> 4) & 0x3fffu) | (1u << 16); }
 constexpr uint32_t kDescHi = (uint32_t)(1024 >> 4) | (1u << 14) | (2u << 29);
 constexpr uint32_t kDescHiNarrow = (uint32_t)(256 >> 4) | (1u << 14) | (6u << 29);
